@@ -1,0 +1,240 @@
+/*
+ * b200_kernels.h - C ABI of the B200 (sm_100a) quantized-inference kernels.
+ *
+ * This is the boundary between host code (the nGraph backend plugin, or any
+ * other caller) and the hand-written CUDA kernels.  Plain pointers and sizes
+ * only: no C++ types, no exceptions, no framework types.  Unless a function
+ * says otherwise every data pointer is a DEVICE pointer valid on the current
+ * CUDA device and `stream` is a cudaStream_t passed as void* (NULL = the
+ * legacy default stream).  Calls are asynchronous with respect to the host.
+ *
+ * Every entry point returns a b200_status: 0 on success, a negative value
+ * for an argument the kernel cannot run (nothing is launched), a positive
+ * value for a CUDA runtime/driver error.  There is no CPU fallback: when
+ * there is no usable GPU the functions return B200_ERR_CUDA.
+ *
+ * Each declaration cites the interface of the nGraph reference
+ * (path:line inside the ngraph source tree) whose arithmetic it reproduces.
+ */
+#ifndef B200_KERNELS_H
+#define B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+typedef enum b200_status
+{
+    B200_OK = 0,
+    B200_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad rank, bad enum            */
+    B200_ERR_UNSUPPORTED = -2,      /* legal in nGraph, not implemented on device  */
+    B200_ERR_TOO_LARGE = -3,        /* exceeds a documented size limit             */
+    B200_ERR_DEVICE_STATUS = -4,    /* a kernel gave up on a bounded wait          */
+    B200_ERR_CUDA = 1               /* cudaGetLastError() / driver error           */
+} b200_status;
+
+/* Element types, a subset of ngraph::element::Type_t (src/ngraph/type/element_type.hpp:40-59). */
+typedef enum b200_dtype
+{
+    B200_U8 = 0,
+    B200_I8 = 1,
+    B200_I32 = 2,
+    B200_F32 = 3
+} b200_dtype;
+
+/* Same ordinal order as op::v0::Quantize::RoundMode (src/ngraph/op/quantize.hpp:38-81). */
+typedef enum b200_round_mode
+{
+    B200_ROUND_NEAREST_TOWARD_INFINITY = 0,
+    B200_ROUND_NEAREST_TOWARD_ZERO = 1,
+    B200_ROUND_NEAREST_UPWARD = 2,
+    B200_ROUND_NEAREST_DOWNWARD = 3,
+    B200_ROUND_NEAREST_TOWARD_EVEN = 4,
+    B200_ROUND_TOWARD_INFINITY = 5,
+    B200_ROUND_TOWARD_ZERO = 6,
+    B200_ROUND_UP = 7,
+    B200_ROUND_DOWN = 8
+} b200_round_mode;
+
+#define B200_MAX_RANK 8
+
+/* Human readable text for a status code (static storage). */
+B200_API const char* b200_status_string(int status);
+
+/* Text of the last CUDA error seen by this library on the calling thread (static storage). */
+B200_API const char* b200_last_cuda_error(void);
+
+/* Number of kernels this library has launched since load (or since the last reset). */
+B200_API uint64_t b200_launch_count(void);
+B200_API void b200_reset_launch_count(void);
+
+/*
+ * Quantize: f32 -> u8 / i8 / i32.
+ *
+ * Replaces runtime::reference::quantize<float,QUANT>
+ * (src/ngraph/runtime/reference/quantize.hpp:30-117) as dispatched by the
+ * INTERPRETER for op::v0::Quantize (src/ngraph/runtime/interpreter/int_executable.hpp:1405-1451).
+ *
+ *   q = x / scale[proj]            IEEE single-precision division
+ *   q = round(q)                   per round_mode, the literal floor/ceil(+-0.5) sequences
+ *   q = q + (float)zero_point[proj]
+ *   q = clamp(q, QUANT::min, QUANT::max);  out = (QUANT)q
+ *
+ * `shape`/`rank` describe the row-major input; `axes` (ascending, n_axes of
+ * them) are the quantisation axes, scale and zero_point are row-major tensors
+ * over exactly those axes (n_axes == 0: one element each).  zero_point has
+ * the output element type.  A NaN input produces 0.
+ */
+B200_API int b200_quantize(const float* input,
+                           const float* scale,
+                           const void* zero_point,
+                           void* output,
+                           int quant_type, /* b200_dtype: U8, I8 or I32 */
+                           const int64_t* shape,
+                           int rank,
+                           const int64_t* axes,
+                           int n_axes,
+                           int round_mode, /* b200_round_mode */
+                           void* stream);
+
+/*
+ * Dequantize: u8 / i8 / i32 -> f32.
+ *
+ * Replaces runtime::reference::dequantize<QUANT,float>
+ * (src/ngraph/runtime/reference/dequantize.hpp:32-52), INTERPRETER case at
+ * src/ngraph/runtime/interpreter/int_executable.hpp:830-862.
+ *
+ *   out = (float)(in - zero_point[proj]) * scale[proj]
+ */
+B200_API int b200_dequantize(const void* input,
+                             const float* scale,
+                             const void* zero_point,
+                             float* output,
+                             int quant_type, /* b200_dtype: U8, I8 or I32 */
+                             const int64_t* shape,
+                             int rank,
+                             const int64_t* axes,
+                             int n_axes,
+                             void* stream);
+
+/*
+ * Epilogue shared by the int8 contractions.  For accumulator acc (int32):
+ *
+ *   fused (round_half_away == 0), the contract of the experimental fused ops as the
+ *   CPU backend hands it to oneDNN (src/ngraph/runtime/cpu/builder/quantized_conv.cpp:455-474,
+ *   src/ngraph/runtime/cpu/dnnl_emitter.hpp:679-695,737-761), results pinned by
+ *   test/builder_quantization.cpp:146-492,995-1098:
+ *       v = (float)(acc + bias[n]) * scale[n or 0]
+ *       v = v + sum_scale * (float)sum_in            (only when sum_in != NULL)
+ *       v = max(v, 0)                                (only when relu)
+ *       out = f32: v        u8/i8: saturate(round_half_even(v))      i32: (int32) the same
+ *
+ *   core (round_half_away == 1), the requantisation of runtime::reference::dot /
+ *   convolution (src/ngraph/runtime/reference/dot.hpp:152-159,
+ *   src/ngraph/runtime/reference/convolution.hpp:252-258):
+ *       out = saturate( (OUT)roundf((float)acc * scale[0]) + out_zero_point )
+ *   (the reference does not saturate: an out-of-range cast there is undefined behaviour).
+ *
+ * All float steps are separate IEEE operations (no fused multiply-add).
+ */
+typedef struct b200_epilogue
+{
+    const int32_t* bias;   /* [N] or NULL                                             */
+    const float* scale;    /* [scale_count], device memory (never an immediate)       */
+    int64_t scale_count;   /* 1 (per tensor) or N (per output channel)                */
+    const void* sum_in;    /* same shape/layout as the output, or NULL                */
+    int sum_type;          /* b200_dtype of sum_in: U8 or I8                          */
+    const float* sum_scale;/* one element, device memory; required with sum_in        */
+    int relu;              /* 0 / 1                                                   */
+    int round_half_away;   /* 0 = fused-op contract (RNE), 1 = core-op contract       */
+    int32_t out_zero_point;/* core contract only                                      */
+    int out_type;          /* b200_dtype: U8, I8, I32 or F32                          */
+} b200_epilogue;
+
+/*
+ * Int8 matrix product with fused epilogue on the tcgen05 tensor cores.
+ *
+ *   acc[m,n] = sum_k A[m,k] * W[n,k]       A: [M,K] u8 or i8, W: [N,K] i8, both row-major
+ *   out[m,n] = epilogue(acc[m,n])          out: [M,N] row-major
+ *
+ * Replaces op::v0::QuantizedDotBias as the CPU backend runs it
+ * (src/ngraph/op/experimental/quantized_dot_bias.cpp:27-56,
+ * src/ngraph/runtime/cpu/builder/quantized_dot.cpp:36-125) and, with the core
+ * epilogue and W = transpose(B), op::v0::QuantizedDot with zero zero-points
+ * (src/ngraph/op/quantized_dot.cpp:58-201, src/ngraph/runtime/reference/dot.hpp:38-167).
+ *
+ * K must be a multiple of 16 and all of A, W 16-byte aligned.
+ */
+B200_API int b200_qgemm(const void* A,
+                        int a_type, /* B200_U8 or B200_I8 */
+                        const int8_t* W,
+                        void* out,
+                        int64_t M,
+                        int64_t N,
+                        int64_t K,
+                        const b200_epilogue* epilogue,
+                        void* stream);
+
+/*
+ * Int8 2-D convolution (implicit GEMM on tcgen05) with fused epilogue.
+ *
+ *   data    [N,H,W,C]    u8 (or i8), channels-last, C a multiple of 16
+ *   filters [K,R,S,C]    i8, channels-last
+ *   out     [N,P,Q,K]    channels-last; P,Q from the usual convolution arithmetic
+ *   sum_in  [N,P,Q,K]    (epilogue.sum_in) when used
+ *
+ * Replaces op::v0::QuantizedConvolutionBias / ...BiasAdd / ...BiasSignedAdd /
+ * QuantizedConvolutionRelu (src/ngraph/op/experimental/quantized_conv_bias.cpp:26-237,
+ * src/ngraph/op/experimental/quantized_conv_relu.cpp:25-80) as the CPU backend runs
+ * them (src/ngraph/runtime/cpu/builder/quantized_conv.cpp:414-754), and the
+ * accumulation of runtime::reference::general_convolution with zero zero-points
+ * (src/ngraph/runtime/reference/convolution.hpp:59-265): padding positions contribute 0.
+ * The nGraph ops are NCHW/KCRS; b200_nchw_to_nhwc_u8 / b200_nhwc_to_nchw_u8 convert.
+ */
+typedef struct b200_conv_params
+{
+    int64_t N, H, W, C; /* data                                        */
+    int64_t K, R, S;    /* filters                                     */
+    int64_t stride_h, stride_w;
+    int64_t pad_h, pad_w;           /* padding below                    */
+    int64_t pad_h_above, pad_w_above;
+    int64_t dilation_h, dilation_w; /* window dilation                  */
+} b200_conv_params;
+
+B200_API int b200_qconv(const void* data,
+                        int data_type, /* B200_U8 or B200_I8 */
+                        const int8_t* filters,
+                        void* out,
+                        const b200_conv_params* params,
+                        const b200_epilogue* epilogue,
+                        void* stream);
+
+/* Output spatial size of b200_qconv for the given params. */
+B200_API int b200_qconv_out_shape(const b200_conv_params* params, int64_t* P, int64_t* Q);
+
+/*
+ * Layout conversions for 1-byte tensors between nGraph's public NCHW / KCRS and the
+ * channels-last layout the contraction kernels consume.  `c_pad` >= C is the channel
+ * count of the channels-last side (extra channels are written as zero / ignored).
+ */
+B200_API int b200_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W,
+                                  int64_t c_pad, void* stream);
+B200_API int b200_nhwc_to_nchw_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W,
+                                  int64_t c_pad, void* stream);
+
+/* Transpose a row-major [rows, cols] 1-byte matrix (B [K,N] of QuantizedDot -> W [N,K]). */
+B200_API int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_t cols, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KERNELS_H */

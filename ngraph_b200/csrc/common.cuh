@@ -1,0 +1,114 @@
+// Shared host/device helpers for the B200 kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <atomic>
+#include "b200_kernels.h"
+
+namespace b200
+{
+    // Count of kernels launched through this library (read by b200_launch_count).
+    extern std::atomic<uint64_t> g_launches;
+
+    // Records the CUDA error text for b200_last_cuda_error and maps to a status.
+    int cuda_status(cudaError_t err, const char* where);
+
+    inline int after_launch(const char* where)
+    {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return cuda_status(cudaGetLastError(), where);
+    }
+
+    inline size_t dtype_size(int t)
+    {
+        return (t == B200_U8 || t == B200_I8) ? 1 : 4;
+    }
+
+    template <typename T>
+    struct QLimits;
+    template <>
+    struct QLimits<uint8_t>
+    {
+        static constexpr float lo = 0.0f, hi = 255.0f;
+    };
+    template <>
+    struct QLimits<int8_t>
+    {
+        static constexpr float lo = -128.0f, hi = 127.0f;
+    };
+    template <>
+    struct QLimits<int32_t>
+    {
+        static constexpr float lo = -2147483648.0f, hi = 2147483648.0f;
+    };
+
+    // The rounding step of reference::quantize (runtime/reference/quantize.hpp:51-103),
+    // written with explicit round-to-nearest adds so the compiler can neither contract
+    // nor reassociate them.
+    template <int MODE>
+    __device__ __forceinline__ float round_quant(float q)
+    {
+        if (MODE == B200_ROUND_NEAREST_TOWARD_INFINITY)
+        {
+            float a = floorf(__fadd_rn(fabsf(q), 0.5f));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_NEAREST_TOWARD_ZERO)
+        {
+            float a = ceilf(__fsub_rn(fabsf(q), 0.5f));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_NEAREST_UPWARD)
+        {
+            return floorf(__fadd_rn(q, 0.5f));
+        }
+        else if (MODE == B200_ROUND_NEAREST_DOWNWARD)
+        {
+            return ceilf(__fsub_rn(q, 0.5f));
+        }
+        else if (MODE == B200_ROUND_NEAREST_TOWARD_EVEN)
+        {
+            float up = floorf(__fadd_rn(q, 0.5f));
+            float dn = ceilf(__fsub_rn(q, 0.5f));
+            // fmod(up, 2.0) == 0  <=>  up/2 is an integer (exact: halving is exact in binary fp)
+            float h = __fmul_rn(up, 0.5f);
+            return (floorf(h) == h) ? up : dn;
+        }
+        else if (MODE == B200_ROUND_TOWARD_INFINITY)
+        {
+            float a = ceilf(fabsf(q));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_TOWARD_ZERO)
+        {
+            float a = floorf(fabsf(q));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_UP)
+        {
+            return ceilf(q);
+        }
+        else
+        {
+            return floorf(q);
+        }
+    }
+
+    // clamp + cast of reference::quantize (quantize.hpp:109-115).  NaN -> 0.
+    template <typename Q>
+    __device__ __forceinline__ Q clamp_cast(float q)
+    {
+        float c = fminf(fmaxf(q, QLimits<Q>::lo), QLimits<Q>::hi);
+        int v = __float2int_rz(c); // saturating for the int32 upper edge
+        return (q != q) ? Q(0) : static_cast<Q>(v);
+    }
+
+    template <typename Q, int MODE>
+    __device__ __forceinline__ Q quantize_one(float x, float scale, float zp)
+    {
+        float q = __fdiv_rn(x, scale);
+        q = round_quant<MODE>(q);
+        q = __fadd_rn(q, zp);
+        return clamp_cast<Q>(q);
+    }
+}
