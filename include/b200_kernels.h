@@ -78,6 +78,13 @@ B200_API uint64_t b200_launch_count(void);
 B200_API void b200_reset_launch_count(void);
 
 /*
+ * Reads and clears the device status word the contraction kernels set when one of their
+ * bounded waits (mbarrier / TMEM) gives up instead of hanging.  Synchronises with the device.
+ * Returns B200_OK (and *status_out = 0) or B200_ERR_DEVICE_STATUS (and the code in *status_out).
+ */
+B200_API int b200_device_status(int* status_out);
+
+/*
  * Quantize: f32 -> u8 / i8 / i32.
  *
  * Replaces runtime::reference::quantize<float,QUANT>
@@ -233,6 +240,28 @@ B200_API int b200_nhwc_to_nchw_u8(const void* in, void* out, int64_t N, int64_t 
 
 /* Transpose a row-major [rows, cols] 1-byte matrix (B [K,N] of QuantizedDot -> W [N,K]). */
 B200_API int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * MaxPool on channels-last u8 [N,H,W,C] -> [N,P,Q,C], C a multiple of 16.  Padding positions are
+ * skipped as in runtime::reference::max_pool (src/ngraph/runtime/reference/max_pool.hpp:124-236).
+ */
+B200_API int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C,
+                                  int64_t win_h, int64_t win_w, int64_t stride_h, int64_t stride_w,
+                                  int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                  void* stream);
+
+/*
+ * Global average pooling head on channels-last u8 [N,H,W,C] -> u8 [N,C]:
+ *   Dequantize(scale_in, zp 0) -> AvgPool over the whole H x W window -> Quantize(scale_out, zp 0, RNE)
+ * with the float sum taken sequentially in H,W order and one division by H*W, as
+ * runtime::reference::avg_pool does for f32 (src/ngraph/runtime/reference/avg_pool.hpp:160-236).
+ * (AvgPool directly on u8 accumulates in uint8 in the reference and wraps; the quantized graphs
+ * therefore pool in f32, which is also where the CPU backend's fusion starts:
+ * src/ngraph/runtime/cpu/pass/cpu_fusion.cpp:2160-2200.)  scale_in / scale_out: one float each, device memory.
+ */
+B200_API int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const float* scale_in,
+                                           const float* scale_out, int64_t N, int64_t H, int64_t W, int64_t C,
+                                           void* stream);
 
 #ifdef __cplusplus
 }

@@ -433,15 +433,15 @@ static void fused_dot_cases(Json& j)
 
 static void fused_conv_cases(Json& j)
 {
-    ConvGeom geoms[3] = {{Shape{2, 16, 6, 5}, Shape{8, 16, 3, 3}, Strides{1, 1}, Strides{1, 1}, CoordinateDiff{1, 1}, CoordinateDiff{1, 1}},
-                         {Shape{1, 16, 9, 8}, Shape{4, 16, 3, 3}, Strides{2, 2}, Strides{1, 1}, CoordinateDiff{1, 1}, CoordinateDiff{1, 1}},
-                         {Shape{2, 32, 4, 4}, Shape{16, 32, 1, 1}, Strides{1, 1}, Strides{1, 1}, CoordinateDiff{0, 0}, CoordinateDiff{0, 0}}};
+    ConvGeom geoms[3] = {{Shape{2, 64, 6, 5}, Shape{8, 64, 3, 3}, Strides{1, 1}, Strides{1, 1}, CoordinateDiff{1, 1}, CoordinateDiff{1, 1}},
+                         {Shape{1, 64, 9, 8}, Shape{4, 64, 3, 3}, Strides{2, 2}, Strides{1, 1}, CoordinateDiff{1, 1}, CoordinateDiff{1, 1}},
+                         {Shape{2, 128, 4, 4}, Shape{16, 128, 1, 1}, Strides{1, 1}, Strides{1, 1}, CoordinateDiff{0, 0}, CoordinateDiff{0, 0}}};
     // kind: 0 bias, 1 bias+relu, 2 bias+add+relu (u8 sum), 3 bias+signed add+relu (i8 sum, i8 out then Convert u8), 4 relu only
     int id = 0;
     for (auto& g : geoms)
         for (int kind = 0; kind < 5; ++kind)
-            for (int per_channel = 0; per_channel < 2; ++per_channel)
             {
+                const int per_channel = (id & 1);
                 Rng r(5000 + id);
                 size_t Kc = g.filt[0];
                 Blob D = rand_int_blob<uint8_t>(r, element::u8, g.data, 0, 255);

@@ -1,0 +1,249 @@
+"""Parity of the tcgen05 int8 contractions (b200_qgemm / b200_qconv through the C ABI) with the
+golden fixtures and with the CPU oracle on seeded inputs.  Integer outputs bit-exact; f32 outputs
+bit-exact too (the epilogue is the same sequence of IEEE single operations)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from tests.fixtures import NP, blob, f32_from_bits, interpreter_cases, reference_tests, typed
+
+pytestmark = pytest.mark.gpu
+
+FUSED_CONV = ("QuantizedConvolutionBias", "QuantizedConvolutionBiasRelu", "QuantizedConvolutionBiasAdd",
+              "QuantizedConvolutionBiasSignedAdd", "QuantizedConvolutionRelu")
+TDT = {np.dtype(np.uint8): torch.uint8, np.dtype(np.int8): torch.int8, np.dtype(np.int32): torch.int32,
+       np.dtype(np.float32): torch.float32}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ngraph_b200 import ops as o
+    return o
+
+
+@pytest.fixture(autouse=True)
+def device_status_clean():
+    yield
+    from ngraph_b200 import lib
+    lib.device_status()
+
+
+def dev(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def pad_k(a, mult=16):
+    """Zero-pad the reduction (last) axis to a multiple of 16 bytes (zeros do not change the sums)."""
+    k = a.shape[-1]
+    kp = (k + mult - 1) // mult * mult
+    if kp == k:
+        return a
+    out = np.zeros(a.shape[:-1] + (kp,), a.dtype)
+    out[..., :k] = a
+    return out
+
+
+def same_f32(got, exp):
+    np.testing.assert_array_equal(np.where(got == 0, 0.0, got).view(np.uint32), np.where(exp == 0, 0.0, exp).view(np.uint32))
+
+
+def nhwc(a):
+    return np.ascontiguousarray(a.transpose(0, 2, 3, 1))
+
+
+def run_conv(ops, data_nchw, filt_kcrs, bias, scale, cs, out_dt, relu, sum_in=None, sum_scale=None, core=False, out_zp=0):
+    cp = ops.conv_params((cs.N, cs.H, cs.W, cs.C), (cs.K, cs.R, cs.S, cs.C), (cs.stride_h, cs.stride_w),
+                         (cs.pad_h, cs.pad_w), (cs.pad_h_above, cs.pad_w_above), (cs.dil_h, cs.dil_w))
+    out = ops.qconv(dev(nhwc(data_nchw)), dev(nhwc(filt_kcrs)), dev(np.atleast_1d(scale).astype(np.float32)),
+                    TDT[np.dtype(out_dt)], cp, bias=dev(bias), relu=relu,
+                    sum_in=None if sum_in is None else dev(nhwc(sum_in)),
+                    sum_scale=None if sum_in is None else dev(np.array([sum_scale], np.float32)), core=core, out_zp=out_zp)
+    return out.cpu().numpy().transpose(0, 3, 1, 2)
+
+
+# ---------------------------------------------------------------- fixtures
+def test_reference_quantized_dot_bias_vectors(ops):
+    for case in reference_tests("QuantizedDotBias"):
+        out_dt = NP[case["expected"]["dtype"]]
+        a = pad_k(typed(case["data"], case["shape_a"]))
+        w = pad_k(typed(case["weights"], case["shape_b"]))
+        got = ops.qgemm(dev(a), dev(w), dev(np.array([f32_from_bits(case["scale_bits"])], np.float32)), TDT[np.dtype(out_dt)],
+                        bias=dev(typed(case["bias"])), relu=case["relu"]).cpu().numpy()
+        np.testing.assert_array_equal(got.ravel(), typed(case["expected"]), err_msg=case["name"])
+
+
+def test_reference_quantized_dot_vectors(ops):
+    for case in reference_tests("QuantizedDot"):
+        c = case["consts"]
+        if c["input_zero_point"] or c["filter_zero_point"] or case["b"]["dtype"] != "i8":
+            continue  # u8 x u8 and non-zero zero points are outside the tensor-core path
+        a = pad_k(typed(case["a"], case["shape_a"]))
+        w = pad_k(np.ascontiguousarray(typed(case["b"], case["shape_b"]).T))
+        scale = np.float32(c["input_scale"]) * np.float32(c["filter_scale"]) / np.float32(c["output_scale"])
+        out_dt = NP[case["expected"]["dtype"]]
+        got = ops.qgemm(dev(a), dev(w), dev(np.array([scale], np.float32)), TDT[np.dtype(out_dt)], core=True,
+                        out_zp=c["output_zero_point"]).cpu().numpy()
+        np.testing.assert_array_equal(got.ravel(), typed(case["expected"]), err_msg=case["name"])
+
+
+def test_interpreter_fused_dot(ops):
+    for case in interpreter_cases("QuantizedDotBias"):
+        i = {k: blob(v) for k, v in case["inputs"].items()}
+        exp = blob(case["outputs"]["y"])
+        got = ops.qgemm(dev(i["data"]), dev(i["weights"]), dev(i["scale"]), TDT[exp.dtype], bias=dev(i["bias"]),
+                        relu=bool(case["attrs"]["relu"])).cpu().numpy()
+        if exp.dtype == np.float32:
+            same_f32(got, exp)
+        else:
+            np.testing.assert_array_equal(got, exp, err_msg=case["name"])
+
+
+def test_interpreter_fused_convolution(ops):
+    for case in interpreter_cases(FUSED_CONV):
+        i = {k: blob(v) for k, v in case["inputs"].items()}
+        a = case["attrs"]
+        exp = blob(case["outputs"]["y"])
+        cs = ref.conv_shape(i["data"].shape, i["filters"].shape, a["stride"], a["pad_below"], a["pad_above"], a["dilation"])
+        signed = case["op"] == "QuantizedConvolutionBiasSignedAdd"
+        out_dt = np.int8 if signed else exp.dtype
+        kw = {}
+        if "sum_in" in i:
+            kw = dict(sum_in=i["sum_in"], sum_scale=i["sum_scale"].ravel()[0])
+        got = run_conv(ops, i["data"], i["filters"], i.get("bias"), i["scale"], cs, out_dt, bool(a["relu"]), **kw)
+        np.testing.assert_array_equal(got.astype(exp.dtype), exp, err_msg=case["name"])
+
+
+# ---------------------------------------------------------------- seeded, against the oracle
+GEMM_SHAPES = [(1, 16, 16), (7, 10, 48), (128, 128, 128), (129, 65, 144), (300, 1000, 2048), (256, 1024, 1024),
+               (513, 272, 400)]
+
+
+@pytest.mark.parametrize("mnk", GEMM_SHAPES)
+@pytest.mark.parametrize("a_signed", [False, True])
+def test_qgemm_vs_oracle(ops, mnk, a_signed):
+    m, n, k = mnk
+    rng = np.random.default_rng(m * 31 + n * 7 + k + a_signed)
+    a = rng.integers(-128, 128, size=(m, k)).astype(np.int8) if a_signed else rng.integers(0, 256, size=(m, k)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(n, k)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=n).astype(np.int32)
+    acc_sigma = np.sqrt(k) * 74 * (74 if a_signed else 147)
+    for per_channel in (False, True):
+        scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=n if per_channel else 1)) * 40.0 / acc_sigma).astype(np.float32)
+        for out_dt, relu in ((np.uint8, True), (np.int8, False), (np.float32, False), (np.float32, True), (np.int32, False)):
+            exp = ref.qgemm_fused(a, w, bias, scale, out_dt, relu=relu)
+            got = ops.qgemm(dev(a), dev(w), dev(scale), TDT[np.dtype(out_dt)], bias=dev(bias), relu=relu).cpu().numpy()
+            if out_dt == np.float32:
+                same_f32(got, exp)
+            else:
+                np.testing.assert_array_equal(got, exp, err_msg="%s %s relu=%d" % (mnk, out_dt, relu))
+    # core contract (QuantizedDot): half-away rounding, output zero point, saturation
+    scale1 = np.float32(30.0 / acc_sigma)
+    for out_dt, zp in ((np.int8, 3), (np.uint8, 100), (np.int32, -5)):
+        exp = ref.qgemm_core(a, w, scale1, zp, out_dt)
+        got = ops.qgemm(dev(a), dev(w), dev(np.array([scale1], np.float32)), TDT[np.dtype(out_dt)], core=True, out_zp=zp).cpu().numpy()
+        np.testing.assert_array_equal(got, exp, err_msg="core %s %s" % (mnk, out_dt))
+
+
+def test_qgemm_sum_input(ops):
+    rng = np.random.default_rng(5)
+    m, n, k = 200, 96, 256
+    a = rng.integers(0, 256, size=(m, k)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(n, k)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=n).astype(np.int32)
+    scale = np.full(n, 2e-4, np.float32)
+    for sdt in (np.uint8, np.int8):
+        s = rng.integers(np.iinfo(sdt).min, np.iinfo(sdt).max + 1, size=(m, n)).astype(sdt)
+        exp = ref.qgemm_fused(a, w, bias, scale, np.uint8, relu=True, sum_in=s, sum_scale=np.float32(0.37))
+        got = ops.qgemm(dev(a), dev(w), dev(scale), torch.uint8, bias=dev(bias), relu=True, sum_in=dev(s),
+                        sum_scale=dev(np.array([0.37], np.float32))).cpu().numpy()
+        np.testing.assert_array_equal(got, exp)
+
+
+CONV_CASES = [
+    # N, C, H, W, K, R, S, stride, pad_below, pad_above, dilation
+    (2, 64, 8, 8, 64, 3, 3, (1, 1), (1, 1), (1, 1), (1, 1)),
+    (3, 64, 7, 7, 32, 3, 3, (1, 1), (1, 1), (1, 1), (1, 1)),
+    (2, 128, 14, 14, 96, 1, 1, (1, 1), (0, 0), (0, 0), (1, 1)),
+    (2, 128, 14, 14, 256, 1, 1, (2, 2), (0, 0), (0, 0), (1, 1)),
+    (2, 64, 15, 13, 64, 3, 3, (2, 2), (1, 1), (1, 1), (1, 1)),
+    (1, 64, 12, 12, 16, 3, 3, (1, 1), (2, 2), (2, 2), (2, 2)),
+    (2, 256, 9, 9, 40, 3, 3, (1, 2), (1, 0), (0, 1), (1, 1)),
+    (5, 64, 5, 6, 8, 5, 3, (1, 1), (2, 1), (2, 1), (1, 1)),
+]
+
+
+@pytest.mark.parametrize("cfg", CONV_CASES)
+def test_qconv_vs_oracle(ops, cfg):
+    n, c, h, w, k, r, s, stride, pb, pa, dil = cfg
+    rng = np.random.default_rng(hash(cfg) % (2 ** 31))
+    data = rng.integers(0, 256, size=(n, c, h, w)).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=(k, c, r, s)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=k).astype(np.int32)
+    cs = ref.conv_shape(data.shape, filt.shape, stride, pb, pa, dil)
+    acc_sigma = np.sqrt(c * r * s) * 74 * 147
+    scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=k)) * 60.0 / acc_sigma).astype(np.float32)
+    p, q = ref.conv_out_hw(cs)
+    for out_dt, relu in ((np.uint8, True), (np.int8, False)):
+        exp = ref.qconv_fused(data, filt, bias, scale, cs, out_dt, relu=relu)
+        got = run_conv(ops, data, filt, bias, scale, cs, out_dt, relu)
+        np.testing.assert_array_equal(got, exp, err_msg=str(cfg))
+    sum_u8 = rng.integers(0, 256, size=(n, k, p, q)).astype(np.uint8)
+    exp = ref.qconv_fused(data, filt, bias, scale, cs, np.uint8, relu=True, sum_in=sum_u8, sum_scale=np.float32(0.61))
+    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.61)
+    np.testing.assert_array_equal(got, exp, err_msg="add " + str(cfg))
+    sum_i8 = rng.integers(-128, 128, size=(n, k, p, q)).astype(np.int8)
+    exp = ref.qconv_fused(data, filt, bias, scale[:1], cs, np.int8, relu=True, sum_in=sum_i8, sum_scale=np.float32(1.3))
+    got = run_conv(ops, data, filt, bias, scale[:1], cs, np.int8, True, sum_in=sum_i8, sum_scale=1.3)
+    np.testing.assert_array_equal(got, exp, err_msg="signed add " + str(cfg))
+    # core contract: QuantizedConvolution -> i32 with unit scales (raw accumulators) and -> i8 requantised
+    exp = ref.qconv_core(data, filt, cs, 1.0, 0, 1.0, 0, 1.0, 0, np.int32)
+    got = run_conv(ops, data, filt, None, np.float32(1.0), cs, np.int32, False, core=True)
+    np.testing.assert_array_equal(got, exp, err_msg="core i32 " + str(cfg))
+
+
+def test_qconv_baseline_layer(ops):
+    """BASELINE config 3: QuantizedConvolutionBias+Relu, u8 [32,64,56,56] * i8 [64,64,3,3], per-channel
+    scales, i32 bias, stride 1 pad 1 -> u8.  The oracle runs on a batch slice (a few seconds); the rest
+    of the batch is checked through linearity in the batch index (each image is independent)."""
+    rng = np.random.default_rng(3)
+    data = rng.integers(0, 256, size=(32, 64, 56, 56)).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=(64, 64, 3, 3)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=64).astype(np.int32)
+    sf = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), size=64)).astype(np.float32)
+    scale = (np.float32(0.02) * sf / np.float32(0.05)).astype(np.float32)
+    cs = ref.conv_shape(data.shape, filt.shape, (1, 1), (1, 1), (1, 1), (1, 1))
+    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True)
+    sl = [0, 17, 31]
+    cs1 = ref.conv_shape((len(sl),) + data.shape[1:], filt.shape, (1, 1), (1, 1), (1, 1), (1, 1))
+    exp = ref.qconv_fused(data[sl], filt, bias, scale, cs1, np.uint8, relu=True)
+    np.testing.assert_array_equal(got[sl], exp)
+    # batch independence: running images one by one through the device gives the same bytes
+    for b in (5, 20):
+        cs_b = ref.conv_shape((1,) + data.shape[1:], filt.shape, (1, 1), (1, 1), (1, 1), (1, 1))
+        one = run_conv(ops, data[b:b + 1], filt, bias, scale, cs_b, np.uint8, True)
+        np.testing.assert_array_equal(one[0], got[b])
+
+
+def test_layout_and_pooling(ops):
+    rng = np.random.default_rng(11)
+    x = rng.integers(0, 256, size=(3, 5, 7, 9)).astype(np.uint8)
+    y = ops.nchw_to_nhwc(dev(x), 16).cpu().numpy()
+    assert y.shape == (3, 7, 9, 16)
+    np.testing.assert_array_equal(y[..., :5], x.transpose(0, 2, 3, 1))
+    assert not y[..., 5:].any()
+    np.testing.assert_array_equal(ops.nhwc_to_nchw(dev(y), 5).cpu().numpy(), x)
+    m = rng.integers(-128, 128, size=(37, 70)).astype(np.int8)
+    np.testing.assert_array_equal(ops.transpose_u8(dev(m)).cpu().numpy(), m.T)
+    for case in interpreter_cases("MaxPool"):
+        a = case["attrs"]
+        xi = blob(case["inputs"]["x"])
+        got = ops.maxpool_nhwc(dev(nhwc(xi)), a["window"], a["stride"], a["pad_below"], a["pad_above"]).cpu().numpy()
+        np.testing.assert_array_equal(got.transpose(0, 3, 1, 2), blob(case["outputs"]["y"]))
+    for case in interpreter_cases("GlobalAvgPoolQ"):
+        i = {k: blob(v) for k, v in case["inputs"].items()}
+        got = ops.global_avgpool_q(dev(nhwc(i["x"])), dev(i["s_in"].reshape(1)), dev(i["s_out"].reshape(1))).cpu().numpy()
+        np.testing.assert_array_equal(got, blob(case["outputs"]["y"]).reshape(got.shape))
+    big = rng.integers(0, 256, size=(4, 64, 30, 30)).astype(np.uint8)
+    got = ops.maxpool_nhwc(dev(nhwc(big)), (3, 3), (2, 2), (1, 1), (1, 1)).cpu().numpy()
+    np.testing.assert_array_equal(got.transpose(0, 3, 1, 2), ref.maxpool_u8(big, (3, 3), (2, 2), (1, 1), (1, 1)))
