@@ -263,6 +263,28 @@ B200_API int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const floa
                                            const float* scale_out, int64_t N, int64_t H, int64_t W, int64_t C,
                                            void* stream);
 
+/*
+ * Patch matrix for a convolution whose input has at most 4 channels (a network stem such as
+ * 7x7 stride 2 on RGB): the tensor cores want 16-byte channel runs, which 3 channels cannot give.
+ *   in  : channels-last u8 with exactly 4 channels per pixel [N,H,W,4] (see b200_nchw_to_nhwc_u8, c_pad 4)
+ *   out : [N*P*Q, R*32] u8; row (n,p,q), segment r holds the 8 pixels w = q*stride_w - pad_w + 0..7 of input
+ *         row h = p*stride_h - pad_h + r, 4 bytes each; taps s >= S and out-of-image pixels are zero.
+ * b200_qgemm on this matrix with the filter packed the same way ([K, R*32]) is the convolution
+ * (same accumulation as runtime::reference::general_convolution, src/ngraph/runtime/reference/convolution.hpp:59-265).
+ * S <= 8, window dilation 1.
+ */
+B200_API int b200_im2col_c4_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t R, int64_t S,
+                               int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                               int64_t pad_h_above, int64_t pad_w_above, void* stream);
+
+/*
+ * out[0] = input_scale[0] * filter_scale[0] / output_scale[0] in fp32, left to right: the requantisation
+ * scale of op::v0::QuantizedDot / QuantizedConvolution (src/ngraph/runtime/reference/dot.hpp:154,
+ * src/ngraph/runtime/reference/convolution.hpp:254) when the three scales are run-time tensors.
+ */
+B200_API int b200_requant_scale(const float* input_scale, const float* filter_scale, const float* output_scale,
+                                float* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

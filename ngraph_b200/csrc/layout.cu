@@ -214,3 +214,76 @@ extern "C" int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const fl
         static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), scale_in, scale_out, int(N), int(H * W), int(C));
     return after_launch("b200_global_avgpool_q_nhwc_u8");
 }
+
+namespace b200
+{
+    // Patch matrix of a small-channel convolution (the network stem): input channels-last with
+    // 4 channels per pixel, output row m = (n, p, q), R segments of 32 bytes = 8 taps x 4 channels
+    // (taps s >= S and out-of-image pixels are zero).  One thread per (m, r) segment.
+    __global__ void __launch_bounds__(256) im2col_c4_kernel(const uint32_t* __restrict__ in, uint4* __restrict__ out,
+                                                            int N, int H, int W, int P, int Q, int R, int S,
+                                                            int stride_h, int stride_w, int pad_h, int pad_w)
+    {
+        int64_t total = int64_t(N) * P * Q * R;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            int r = int(i % R);
+            int64_t m = i / R;
+            int q = int(m % Q);
+            int64_t t = m / Q;
+            int p = int(t % P);
+            int n = int(t / P);
+            int h = p * stride_h - pad_h + r;
+            int w0 = q * stride_w - pad_w;
+            uint32_t v[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+            {
+                int w = w0 + s;
+                bool ok = s < S && h >= 0 && h < H && w >= 0 && w < W;
+                v[s] = ok ? in[(int64_t(n) * H + h) * W + w] : 0u;
+            }
+            out[2 * i] = make_uint4(v[0], v[1], v[2], v[3]);
+            out[2 * i + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+        }
+    }
+
+    __global__ void requant_scale_kernel(const float* a, const float* b, const float* c, float* out)
+    {
+        // runtime/reference/dot.hpp:154: scale = input0_scale * input1_scale / output_scale, left to right
+        out[0] = __fdiv_rn(__fmul_rn(a[0], b[0]), c[0]);
+    }
+}
+
+extern "C" int b200_im2col_c4_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t R, int64_t S,
+                                 int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                                 int64_t pad_h_above, int64_t pad_w_above, void* stream)
+{
+    using namespace b200;
+    if (N < 0 || H <= 0 || W <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (S > 8)
+        return B200_ERR_UNSUPPORTED;
+    int64_t P = (H + pad_h + pad_h_above - R) / stride_h + 1, Q = (W + pad_w + pad_w_above - S) / stride_w + 1;
+    if (N == 0 || P <= 0 || Q <= 0)
+        return B200_OK;
+    if (!in || !out || (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(in) & 3))
+        return B200_ERR_INVALID_ARGUMENT;
+    int64_t total = N * P * Q * R;
+    int64_t blocks = (total + 255) / 256;
+    unsigned grid = unsigned(blocks < 148 * 64 ? blocks : 148 * 64);
+    im2col_c4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint32_t*>(in), static_cast<uint4*>(out), int(N), int(H), int(W), int(P), int(Q), int(R), int(S),
+        int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    return after_launch("b200_im2col_c4_u8");
+}
+
+extern "C" int b200_requant_scale(const float* input_scale, const float* filter_scale, const float* output_scale,
+                                  float* out, void* stream)
+{
+    using namespace b200;
+    if (!input_scale || !filter_scale || !output_scale || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    requant_scale_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(input_scale, filter_scale, output_scale, out);
+    return after_launch("b200_requant_scale");
+}

@@ -276,7 +276,8 @@ namespace b200
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
-            const bool vec_ok = (esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0);
+            const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
+                                ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
             uint32_t tile_it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
             {
