@@ -309,13 +309,14 @@ def main():
     ap.add_argument("--workload", default="qconv", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (images / rows); for small profiler captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload](args.batch) if args.batch else WORKLOADS[args.workload]()
 
     if args.impl == "reference":
         run_reference(args, wl, rank)

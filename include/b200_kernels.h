@@ -114,6 +114,14 @@ B200_API int b200_quantize(const float* input,
                            void* stream);
 
 /*
+ * Quantize to 8 bits with ROUND_NEAREST_TOWARD_EVEN normally replaces the per-element IEEE division
+ * by a per-row correctly rounded reciprocal plus two fused multiply-adds that reproduce the correctly
+ * rounded quotient bit for bit (see quantize.cu).  b200_set_fast_division(0) makes every Quantize use
+ * the plain division instead (the tests compare the two over all 2^32 inputs); returns the old setting.
+ */
+B200_API int b200_set_fast_division(int enable);
+
+/*
  * Dequantize: u8 / i8 / i32 -> f32.
  *
  * Replaces runtime::reference::dequantize<QUANT,float>
@@ -237,6 +245,9 @@ B200_API int b200_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t 
                                   int64_t c_pad, void* stream);
 B200_API int b200_nhwc_to_nchw_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W,
                                   int64_t c_pad, void* stream);
+
+/* Channels-last [N,HW,C] -> [N,C,HW] for 4-byte elements (int32 / f32 outputs of the convolution). */
+B200_API int b200_nhwc_to_nchw_b32(const void* in, void* out, int64_t N, int64_t C, int64_t HW, void* stream);
 
 /* Transpose a row-major [rows, cols] 1-byte matrix (B [K,N] of QuantizedDot -> W [N,K]). */
 B200_API int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_t cols, void* stream);

@@ -1,0 +1,1151 @@
+// nGraph runtime backend "B200": see b200_backend.hpp.
+//
+// compile() turns the Function into a straight-line list of kernel launches ("steps") over device
+// buffers ("slots"); call() binds the Parameter / Result tensors and enqueues the steps on the
+// backend's stream.  There is no host fallback: an op the kernels cannot run makes compile() throw
+// ngraph::unsupported_op, exactly like the other backends do for ops they lack.
+//
+// Data layout.  nGraph tensors are row-major (images NCHW, filters KCRS).  The int8 convolution
+// kernels are channels-last, so every 4-D one-byte tensor may exist in two materialisations:
+// canonical (what Parameters, Results and non-convolution ops see) and NHWC.  Convolutions, u8
+// MaxPool and the pooling head consume and produce NHWC directly; a conversion kernel is emitted
+// only where a consumer needs the other form, so activations stay channels-last between
+// quantized layers and NCHW appears only at graph edges.  Constant filters are packed to KRSC
+// once at compile time.
+#include "b200_backend.hpp"
+
+#include <cstring>
+#include <sstream>
+
+#include "b200_kernels.h"
+#include "ngraph/descriptor/layout/dense_tensor_layout.hpp"
+#include "ngraph/except.hpp"
+#include "ngraph/graph_util.hpp"
+#include "ngraph/op/avg_pool.hpp"
+#include "ngraph/op/constant.hpp"
+#include "ngraph/op/convert.hpp"
+#include "ngraph/op/dequantize.hpp"
+#include "ngraph/op/experimental/quantized_conv_bias.hpp"
+#include "ngraph/op/experimental/quantized_conv_relu.hpp"
+#include "ngraph/op/experimental/quantized_dot_bias.hpp"
+#include "ngraph/op/max_pool.hpp"
+#include "ngraph/op/parameter.hpp"
+#include "ngraph/op/quantize.hpp"
+#include "ngraph/op/quantized_convolution.hpp"
+#include "ngraph/op/quantized_dot.hpp"
+#include "ngraph/op/reshape.hpp"
+#include "ngraph/op/result.hpp"
+#include "ngraph/pass/constant_folding.hpp"
+#include "ngraph/pass/fused_op_decomposition.hpp"
+#include "ngraph/pass/like_replacement.hpp"
+#include "ngraph/pass/manager.hpp"
+#include "ngraph/runtime/backend_manager.hpp"
+#include "ngraph/util.hpp"
+
+using namespace ngraph;
+using namespace ngraph::runtime::b200;
+
+// ------------------------------------------------------------------------------------ helpers
+namespace
+{
+    void cuda_check(cudaError_t e, const char* what)
+    {
+        if (e != cudaSuccess)
+        {
+            std::stringstream ss;
+            ss << "B200 backend: " << what << ": " << cudaGetErrorString(e);
+            throw std::runtime_error(ss.str());
+        }
+    }
+
+    void kernel_check(int status, const std::string& what)
+    {
+        if (status != B200_OK)
+        {
+            std::stringstream ss;
+            ss << "B200 backend: " << what << ": " << b200_status_string(status);
+            if (status > 0)
+                ss << " (" << b200_last_cuda_error() << ")";
+            throw std::runtime_error(ss.str());
+        }
+    }
+
+    [[noreturn]] void unsupported(const Node& node, const std::string& why)
+    {
+        std::stringstream ss;
+        ss << "B200 backend: unsupported op " << node.description() << " (" << node.get_name() << "): " << why;
+        throw unsupported_op(ss.str());
+    }
+
+    int dtype_of(const element::Type& et)
+    {
+        if (et == element::u8) return B200_U8;
+        if (et == element::i8) return B200_I8;
+        if (et == element::i32) return B200_I32;
+        if (et == element::f32) return B200_F32;
+        return -1;
+    }
+
+    size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+    std::shared_ptr<const op::v0::Constant> as_constant(const Output<Node>& out)
+    {
+        return as_type_ptr<op::v0::Constant>(out.get_node_shared_ptr());
+    }
+
+    template <typename N>
+    size_t single_user_count(const Output<N>& out)
+    {
+        return out.get_target_inputs().size();
+    }
+
+    template <typename N>
+    const Node* only_user(const Output<N>& out)
+    {
+        auto t = out.get_target_inputs();
+        return t.size() == 1 ? t.begin()->get_node() : nullptr;
+    }
+
+    // Dequantize(u8, per-tensor, zero point 0) -> AvgPool(f32, window == whole image, no padding)
+    // -> Quantize(u8, per-tensor, zero point 0, ROUND_NEAREST_TOWARD_EVEN): the pooling head of a
+    // quantized network (src/ngraph/runtime/cpu/pass/cpu_fusion.cpp:2160-2200 starts from the same shape).
+    struct AvgPoolHead
+    {
+        const op::v0::Dequantize* dq = nullptr;
+        const op::v0::AvgPool* pool = nullptr;
+        const op::v0::Quantize* q = nullptr;
+    };
+
+    bool constant_zero(const Output<Node>& out)
+    {
+        auto c = as_constant(out);
+        if (!c)
+            return false;
+        size_t n = shape_size(c->get_output_shape(0)) * c->get_output_element_type(0).size();
+        const char* p = static_cast<const char*>(c->get_data_ptr());
+        for (size_t i = 0; i < n; ++i)
+            if (p[i] != 0)
+                return false;
+        return true;
+    }
+
+    bool match_head(const Node* qn, AvgPoolHead& h)
+    {
+        auto q = as_type<const op::v0::Quantize>(qn);
+        if (!q || q->get_output_element_type(0) != element::u8 || !q->get_axes().empty() ||
+            q->get_round_mode() != op::v0::Quantize::RoundMode::ROUND_NEAREST_TOWARD_EVEN ||
+            !constant_zero(q->input_value(2)))
+            return false;
+        auto pool = as_type<const op::v0::AvgPool>(q->input_value(0).get_node());
+        if (!pool || single_user_count(q->input_value(0)) != 1 || pool->get_output_element_type(0) != element::f32)
+            return false;
+        const Shape& in = pool->get_input_shape(0);
+        if (in.size() != 4 || pool->get_window_shape() != Shape{in[2], in[3]})
+            return false;
+        for (size_t v : pool->get_padding_below())
+            if (v != 0) return false;
+        for (size_t v : pool->get_padding_above())
+            if (v != 0) return false;
+        auto dq = as_type<const op::v0::Dequantize>(pool->input_value(0).get_node());
+        if (!dq || single_user_count(pool->input_value(0)) != 1 || dq->get_input_element_type(0) != element::u8 ||
+            !dq->get_axes().empty() || !constant_zero(dq->input_value(2)))
+            return false;
+        h.dq = dq;
+        h.pool = pool;
+        h.q = q;
+        return true;
+    }
+}
+
+// ------------------------------------------------------------------------------------ device context
+DeviceContext::DeviceContext(int dev)
+    : device(dev)
+{
+    int count = 0;
+    cuda_check(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+    if (dev < 0 || dev >= count)
+        throw std::runtime_error("B200 backend: no CUDA device " + std::to_string(dev));
+    cuda_check(cudaSetDevice(dev), "cudaSetDevice");
+    cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+}
+
+DeviceContext::~DeviceContext()
+{
+    if (stream)
+    {
+        cudaSetDevice(device);
+        cudaStreamDestroy(stream);
+    }
+}
+
+void DeviceContext::make_current() const
+{
+    cuda_check(cudaSetDevice(device), "cudaSetDevice");
+}
+
+void DeviceContext::synchronize() const
+{
+    cuda_check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+}
+
+// ------------------------------------------------------------------------------------ tensor
+B200Tensor::B200Tensor(const std::shared_ptr<DeviceContext>& ctx,
+                       const element::Type& type,
+                       const Shape& shape,
+                       void* device_pointer)
+    : runtime::Tensor(std::make_shared<descriptor::Tensor>(type, shape, "external"))
+    , m_ctx(ctx)
+{
+    m_descriptor->set_tensor_layout(std::make_shared<descriptor::layout::DenseTensorLayout>(*m_descriptor));
+    m_bytes = shape_size(shape) * type.size();
+    m_ctx->make_current();
+    if (device_pointer)
+    {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, device_pointer) != cudaSuccess ||
+            (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged))
+        {
+            cudaGetLastError();
+            throw ngraph_error("The pointer passed to B200Tensor is not a device pointer.");
+        }
+        m_ptr = device_pointer;
+    }
+    else
+    {
+        cuda_check(cudaMalloc(&m_ptr, m_bytes ? m_bytes : 16), "cudaMalloc(tensor)");
+        m_owned = true;
+    }
+}
+
+B200Tensor::~B200Tensor()
+{
+    if (m_owned && m_ptr)
+    {
+        cudaSetDevice(m_ctx->device);
+        cudaFree(m_ptr);
+    }
+}
+
+void B200Tensor::write(const void* p, size_t n)
+{
+    if (n > m_bytes)
+        throw std::out_of_range("B200Tensor::write: access past the end of the tensor");
+    m_ctx->make_current();
+    cuda_check(cudaMemcpyAsync(m_ptr, p, n, cudaMemcpyHostToDevice, m_ctx->stream), "cudaMemcpy H2D");
+    m_ctx->synchronize(); // the caller may release p as soon as write() returns
+}
+
+void B200Tensor::read(void* p, size_t n) const
+{
+    if (n > m_bytes)
+        throw std::out_of_range("B200Tensor::read: access past the end of the tensor");
+    m_ctx->make_current();
+    cuda_check(cudaMemcpyAsync(p, m_ptr, n, cudaMemcpyDeviceToHost, m_ctx->stream), "cudaMemcpy D2H");
+    m_ctx->synchronize(); // kernels of earlier call()s on this stream have completed here
+    int code = 0;
+    if (b200_device_status(&code) != B200_OK)
+        throw std::runtime_error("B200 backend: a kernel gave up on a bounded wait (device status " +
+                                 std::to_string(code) + ")");
+}
+
+void B200Tensor::copy_from(const runtime::Tensor& source)
+{
+    auto src = dynamic_cast<const B200Tensor*>(&source);
+    if (!src || src->m_ctx->device != m_ctx->device)
+    {
+        std::vector<char> tmp(source.get_size_in_bytes());
+        source.read(tmp.data(), tmp.size());
+        write(tmp.data(), tmp.size());
+        return;
+    }
+    if (src->m_bytes != m_bytes)
+        throw std::runtime_error("B200Tensor::copy_from: size mismatch");
+    m_ctx->make_current();
+    cuda_check(cudaMemcpyAsync(m_ptr, src->m_ptr, m_bytes, cudaMemcpyDeviceToDevice, m_ctx->stream), "cudaMemcpy D2D");
+}
+
+// ------------------------------------------------------------------------------------ backend
+B200Backend::B200Backend(const std::string& options)
+{
+    int dev = 0;
+    if (!options.empty())
+    {
+        try
+        {
+            dev = std::stoi(options);
+        }
+        catch (...)
+        {
+            throw std::runtime_error("B200 backend: options must be a CUDA device ordinal, got '" + options + "'");
+        }
+    }
+    m_ctx = std::make_shared<DeviceContext>(dev);
+}
+
+std::shared_ptr<runtime::Tensor> B200Backend::create_tensor()
+{
+    throw std::runtime_error("B200 backend does not support dynamic tensors");
+}
+
+std::shared_ptr<runtime::Tensor> B200Backend::create_tensor(const element::Type& type, const Shape& shape)
+{
+    return std::make_shared<B200Tensor>(m_ctx, type, shape);
+}
+
+std::shared_ptr<runtime::Tensor>
+    B200Backend::create_tensor(const element::Type& type, const Shape& shape, void* memory_pointer)
+{
+    return std::make_shared<B200Tensor>(m_ctx, type, shape, memory_pointer);
+}
+
+std::shared_ptr<runtime::Executable> B200Backend::compile(std::shared_ptr<Function> func, bool enable_performance_data)
+{
+    std::lock_guard<std::mutex> lock(m_mutex);
+    auto it = m_cache.find(func);
+    if (it != m_cache.end())
+        return it->second;
+    auto exec = std::make_shared<B200Executable>(m_ctx, func, enable_performance_data);
+    m_cache.insert({func, exec});
+    return exec;
+}
+
+void B200Backend::remove_compiled_function(std::shared_ptr<runtime::Executable> exec)
+{
+    std::lock_guard<std::mutex> lock(m_mutex);
+    for (auto it = m_cache.begin(); it != m_cache.end(); ++it)
+        if (it->second == exec)
+        {
+            m_cache.erase(it);
+            break;
+        }
+}
+
+bool B200Backend::is_device_memory(void* ptr)
+{
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+bool B200Backend::is_supported(const Node& node) const
+{
+    // the op set of the quantized-inference path; shapes/types are checked at compile()
+    return is_type<op::v0::Parameter>(&node) || is_type<op::v0::Constant>(&node) || is_type<op::v0::Result>(&node) ||
+           is_type<op::v0::Quantize>(&node) || is_type<op::v0::Dequantize>(&node) ||
+           is_type<op::v0::QuantizedDot>(&node) || is_type<op::v0::QuantizedDotBias>(&node) ||
+           is_type<op::v0::QuantizedConvolution>(&node) || is_type<op::v0::QuantizedConvolutionBias>(&node) ||
+           is_type<op::v0::QuantizedConvolutionBiasAdd>(&node) ||
+           is_type<op::v0::QuantizedConvolutionBiasSignedAdd>(&node) ||
+           is_type<op::v0::QuantizedConvolutionRelu>(&node) || is_type<op::v0::MaxPool>(&node) ||
+           is_type<op::v0::AvgPool>(&node) || is_type<op::v0::Reshape>(&node) || is_type<op::v0::Convert>(&node);
+}
+
+extern "C" B200_BACKEND_API void ngraph_register_b200_backend()
+{
+    runtime::BackendManager::register_backend(
+        "B200", [](const std::string& config) { return std::make_shared<B200Backend>(config); });
+}
+
+// ------------------------------------------------------------------------------------ executable: compile
+int B200Executable::new_slot(Slot::Kind kind, size_t bytes, size_t index)
+{
+    Slot s;
+    s.kind = kind;
+    s.bytes = bytes;
+    s.index = index;
+    if (kind == Slot::ARENA)
+    {
+        s.offset = m_arena_bytes;
+        m_arena_bytes += align_up(bytes ? bytes : 16, 256);
+    }
+    m_slots.push_back(s);
+    return int(m_slots.size()) - 1;
+}
+
+int B200Executable::upload_constant(const void* data, size_t bytes)
+{
+    Slot s;
+    s.kind = Slot::CONSTANT;
+    s.bytes = bytes;
+    s.offset = align_up(m_constant_host.size(), 256);
+    m_constant_host.resize(s.offset + align_up(bytes ? bytes : 16, 256), 0);
+    if (bytes)
+        memcpy(m_constant_host.data() + s.offset, data, bytes);
+    m_slots.push_back(s);
+    return int(m_slots.size()) - 1;
+}
+
+B200Executable::Value& B200Executable::value_of(const Output<Node>& out)
+{
+    auto it = m_values.find(&out.get_tensor());
+    if (it == m_values.end())
+        throw std::runtime_error("B200 backend: value used before it was produced: " + out.get_node()->get_name());
+    return it->second;
+}
+
+void B200Executable::emit(const std::shared_ptr<const Node>& node, const std::string& what,
+                          std::function<int(const Ptrs&, cudaStream_t)> run)
+{
+    m_steps.push_back(Step{node, what, std::move(run)});
+}
+
+int B200Executable::canonical_slot(const Output<Node>& out)
+{
+    Value& v = value_of(out);
+    if (v.skipped)
+        throw std::runtime_error("B200 backend: internal error, fused value requested: " + out.get_node()->get_name());
+    if (v.canonical >= 0)
+        return v.canonical;
+    if (v.nhwc < 0)
+        throw std::runtime_error("B200 backend: internal error, value has no materialisation");
+    // channels-last -> NCHW
+    const Shape sh = v.shape;
+    int dst = new_slot(Slot::ARENA, shape_size(sh) * v.et.size());
+    int src = v.nhwc;
+    emit(out.get_node_shared_ptr(), "nhwc_to_nchw", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_nhwc_to_nchw_u8(p[src], p[dst], sh[0], sh[1], sh[2], sh[3], sh[1], st);
+    });
+    v.canonical = dst;
+    return dst;
+}
+
+int B200Executable::nhwc_slot(const Output<Node>& out)
+{
+    Value& v = value_of(out);
+    if (v.nhwc >= 0)
+        return v.nhwc;
+    if (v.shape.size() != 4 || v.et.size() != 1)
+        throw std::runtime_error("B200 backend: channels-last form exists for 4-D one-byte tensors only");
+    const Shape sh = v.shape;
+    int src = canonical_slot(out);
+    int dst = new_slot(Slot::ARENA, shape_size(sh));
+    emit(out.get_node_shared_ptr(), "nchw_to_nhwc", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_nchw_to_nhwc_u8(p[src], p[dst], sh[0], sh[1], sh[2], sh[3], sh[1], st);
+    });
+    value_of(out).nhwc = dst;
+    return dst;
+}
+
+// KCRS i8 filters -> KRSC (channels padded to c_pad) in device memory
+int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad)
+{
+    const Shape& fs = filters.get_shape();
+    auto c = as_constant(filters);
+    if (c)
+    {
+        const int8_t* src = static_cast<const int8_t*>(c->get_data_ptr());
+        size_t K = fs[0], C = fs[1], R = fs[2], S = fs[3];
+        std::vector<int8_t> packed(K * R * S * c_pad, 0);
+        for (size_t k = 0; k < K; ++k)
+            for (size_t ch = 0; ch < C; ++ch)
+                for (size_t r = 0; r < R; ++r)
+                    for (size_t s = 0; s < S; ++s)
+                        packed[((k * R + r) * S + s) * c_pad + ch] = src[((k * C + ch) * R + r) * S + s];
+        return upload_constant(packed.data(), packed.size());
+    }
+    if (c_pad != fs[1])
+        throw std::runtime_error("B200 backend: run-time filters need a channel count the kernels take directly");
+    return nhwc_slot(filters);
+}
+
+// scale = a * b / c in fp32, left to right (runtime/reference/dot.hpp:154)
+int B200Executable::scalar_product_scale(const Output<Node>& a, const Output<Node>& b, const Output<Node>& c)
+{
+    auto ca = as_constant(a), cb = as_constant(b), cc = as_constant(c);
+    if (ca && cb && cc)
+    {
+        volatile float s = *static_cast<const float*>(ca->get_data_ptr()) * *static_cast<const float*>(cb->get_data_ptr());
+        volatile float r = s / *static_cast<const float*>(cc->get_data_ptr());
+        float v = r;
+        return upload_constant(&v, sizeof(float));
+    }
+    int sa = canonical_slot(a), sb = canonical_slot(b), sc = canonical_slot(c);
+    int dst = new_slot(Slot::ARENA, sizeof(float));
+    emit(a.get_node_shared_ptr(), "requant_scale", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_requant_scale(static_cast<const float*>(p[sa]), static_cast<const float*>(p[sb]),
+                                  static_cast<const float*>(p[sc]), static_cast<float*>(p[dst]), st);
+    });
+    return dst;
+}
+
+bool B200Executable::avgpool_head_member(const Node* node)
+{
+    AvgPoolHead h;
+    if (auto dq = as_type<const op::v0::Dequantize>(node))
+    {
+        const Node* pool = only_user(dq->output(0));
+        const Node* q = pool ? only_user(pool->output(0)) : nullptr;
+        return q && match_head(q, h) && h.dq == dq;
+    }
+    if (auto pool = as_type<const op::v0::AvgPool>(node))
+    {
+        const Node* q = only_user(pool->output(0));
+        return q && match_head(q, h) && h.pool == pool;
+    }
+    return false;
+}
+
+B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
+                               const std::shared_ptr<Function>& func,
+                               bool enable_performance_data)
+    : m_ctx(ctx)
+    , m_perf(enable_performance_data)
+{
+    m_ctx->make_current();
+    m_function = clone_function(*func); // never mutate the caller's graph
+    {
+        pass::Manager pm;
+        pm.register_pass<pass::LikeReplacement>();
+        pm.register_pass<pass::FusedOpDecomposition>();
+        pm.register_pass<pass::ConstantFolding>();
+        pm.run_passes(m_function);
+    }
+
+    size_t pi = 0;
+    for (auto& param : m_function->get_parameters())
+    {
+        Value v;
+        v.et = param->get_output_element_type(0);
+        v.shape = param->get_output_shape(0);
+        v.canonical = new_slot(Slot::PARAMETER, shape_size(v.shape) * v.et.size(), pi++);
+        m_values[&param->output(0).get_tensor()] = v;
+    }
+    for (auto& node : m_function->get_ordered_ops())
+        compile_node(node);
+
+    // results: produce the canonical form, then copy into the caller's tensor
+    size_t ri = 0;
+    for (auto& result : m_function->get_results())
+    {
+        Output<Node> src = result->input_value(0);
+        int from = canonical_slot(src);
+        Value& v = value_of(src);
+        int to = new_slot(Slot::RESULT, shape_size(v.shape) * v.et.size(), ri++);
+        m_result_copies.push_back({from, to});
+    }
+
+    if (m_arena_bytes)
+        cuda_check(cudaMalloc(&m_arena, m_arena_bytes), "cudaMalloc(arena)");
+    if (!m_constant_host.empty())
+    {
+        cuda_check(cudaMalloc(&m_constants, m_constant_host.size()), "cudaMalloc(constants)");
+        cuda_check(cudaMemcpy(m_constants, m_constant_host.data(), m_constant_host.size(), cudaMemcpyHostToDevice),
+                   "cudaMemcpy(constants)");
+        std::vector<char>().swap(m_constant_host);
+    }
+    if (m_perf)
+    {
+        m_events.resize(2 * m_steps.size());
+        for (auto& e : m_events)
+            cuda_check(cudaEventCreate(&e), "cudaEventCreate");
+        m_step_us.assign(m_steps.size(), 0.0);
+    }
+    set_parameters_and_results(*func);
+}
+
+B200Executable::~B200Executable()
+{
+    cudaSetDevice(m_ctx->device);
+    cudaStreamSynchronize(m_ctx->stream);
+    for (auto& e : m_events)
+        cudaEventDestroy(e);
+    if (m_arena) cudaFree(m_arena);
+    if (m_constants) cudaFree(m_constants);
+}
+
+void B200Executable::compile_node(const std::shared_ptr<Node>& node)
+{
+    if (is_type<op::v0::Parameter>(node) || is_type<op::v0::Result>(node))
+        return;
+    if (auto c = as_type_ptr<op::v0::Constant>(node))
+    {
+        Value v;
+        v.et = c->get_output_element_type(0);
+        v.shape = c->get_output_shape(0);
+        v.constant = c;
+        if (dtype_of(v.et) >= 0) // other element types can only feed ConstantFolding, never a kernel
+            v.canonical = upload_constant(c->get_data_ptr(), shape_size(v.shape) * v.et.size());
+        m_values[&node->output(0).get_tensor()] = v;
+        return;
+    }
+    Value out;
+    out.et = node->get_output_element_type(0);
+    out.shape = node->get_output_shape(0);
+    if (node->get_output_size() != 1)
+        unsupported(*node, "multiple outputs");
+    m_values[&node->output(0).get_tensor()] = out;
+
+    if (is_type<op::v0::Quantize>(node)) return compile_quantize(node);
+    if (is_type<op::v0::Dequantize>(node)) return compile_dequantize(node);
+    if (is_type<op::v0::QuantizedConvolutionBias>(node) || is_type<op::v0::QuantizedConvolutionBiasAdd>(node) ||
+        is_type<op::v0::QuantizedConvolutionBiasSignedAdd>(node) || is_type<op::v0::QuantizedConvolutionRelu>(node))
+        return compile_fused_conv(node);
+    if (is_type<op::v0::QuantizedConvolution>(node)) return compile_core_conv(node);
+    if (is_type<op::v0::QuantizedDotBias>(node)) return compile_dot_bias(node);
+    if (is_type<op::v0::QuantizedDot>(node)) return compile_core_dot(node);
+    if (is_type<op::v0::MaxPool>(node)) return compile_max_pool(node);
+    if (is_type<op::v0::AvgPool>(node))
+    {
+        if (avgpool_head_member(node.get()))
+        {
+            value_of(node->output(0)).skipped = true;
+            return;
+        }
+        unsupported(*node, "only the Dequantize -> global AvgPool -> Quantize head runs on the device");
+    }
+    if (auto rs = as_type_ptr<op::v0::Reshape>(node))
+    {
+        Value& in = value_of(node->input_value(0));
+        Value& o = value_of(node->output(0));
+        if (!rs->get_is_transpose())
+        {
+            o.canonical = canonical_slot(node->input_value(0)); // same bytes, new shape
+            return;
+        }
+        if (in.shape.size() == 2 && in.et.size() == 1)
+        {
+            int src = canonical_slot(node->input_value(0));
+            int dst = new_slot(Slot::ARENA, shape_size(in.shape));
+            int64_t r = in.shape[0], c = in.shape[1];
+            emit(node, "transpose", [=](const Ptrs& p, cudaStream_t st) { return b200_transpose_u8(p[src], p[dst], r, c, st); });
+            o.canonical = dst;
+            return;
+        }
+        unsupported(*node, "transposing Reshape other than a 2-D one-byte matrix");
+    }
+    if (auto cv = as_type_ptr<op::v0::Convert>(node))
+    {
+        const element::Type& from = node->get_input_element_type(0);
+        const element::Type& to = node->get_output_element_type(0);
+        if (from.size() == 1 && to.size() == 1 && from.is_integral() && to.is_integral())
+        {
+            // i8 <-> u8 static_cast keeps the byte: alias both materialisations
+            Value in = value_of(node->input_value(0));
+            Value& o = value_of(node->output(0));
+            o.canonical = in.canonical;
+            o.nhwc = in.nhwc;
+            if (o.canonical < 0 && o.nhwc < 0)
+                o.canonical = canonical_slot(node->input_value(0));
+            return;
+        }
+        unsupported(*node, "Convert other than between i8 and u8");
+    }
+    unsupported(*node, "not part of the quantized-inference op set");
+}
+
+static std::vector<int64_t> to_i64(const Shape& s)
+{
+    return std::vector<int64_t>(s.begin(), s.end());
+}
+
+void B200Executable::compile_quantize(const std::shared_ptr<Node>& node)
+{
+    auto q = as_type_ptr<op::v0::Quantize>(node);
+    AvgPoolHead head;
+    if (match_head(node.get(), head))
+    {
+        if (try_compile_avgpool_head(node))
+            return;
+    }
+    if (node->get_input_element_type(0) != element::f32)
+        unsupported(*node, "input element type " + node->get_input_element_type(0).get_type_name());
+    int qt = dtype_of(q->get_output_element_type(0));
+    if (qt != B200_U8 && qt != B200_I8 && qt != B200_I32)
+        unsupported(*node, "output element type");
+    int x = canonical_slot(node->input_value(0)), s = canonical_slot(node->input_value(1)),
+        z = canonical_slot(node->input_value(2));
+    std::vector<int64_t> shape = to_i64(node->get_input_shape(0));
+    std::vector<int64_t> axes(q->get_axes().begin(), q->get_axes().end());
+    int mode = static_cast<int>(q->get_round_mode());
+    int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * q->get_output_element_type(0).size());
+    emit(node, "quantize", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_quantize(static_cast<const float*>(p[x]), static_cast<const float*>(p[s]), p[z], p[y], qt,
+                             shape.data(), int(shape.size()), axes.data(), int(axes.size()), mode, st);
+    });
+    value_of(node->output(0)).canonical = y;
+}
+
+bool B200Executable::try_compile_avgpool_head(const std::shared_ptr<Node>& node)
+{
+    AvgPoolHead h;
+    if (!match_head(node.get(), h))
+        return false;
+    Output<Node> data = h.dq->input_value(0);
+    const Shape& in = data.get_shape();
+    if (in.size() != 4)
+        return false;
+    int x = nhwc_slot(data);
+    int s_in = canonical_slot(h.dq->input_value(1)), s_out = canonical_slot(h.q->input_value(1));
+    int y = new_slot(Slot::ARENA, in[0] * in[1]);
+    int64_t N = in[0], C = in[1], H = in[2], W = in[3];
+    emit(node, "global_avgpool_q", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_global_avgpool_q_nhwc_u8(p[x], p[y], static_cast<const float*>(p[s_in]),
+                                             static_cast<const float*>(p[s_out]), N, H, W, C, st);
+    });
+    Value& o = value_of(node->output(0));
+    o.canonical = y; // [N,C,1,1]: channels-last and NCHW coincide
+    o.nhwc = y;
+    return true;
+}
+
+void B200Executable::compile_dequantize(const std::shared_ptr<Node>& node)
+{
+    auto dq = as_type_ptr<op::v0::Dequantize>(node);
+    if (avgpool_head_member(node.get()))
+    {
+        value_of(node->output(0)).skipped = true;
+        return;
+    }
+    if (node->get_output_element_type(0) != element::f32)
+        unsupported(*node, "output element type");
+    int qt = dtype_of(node->get_input_element_type(0));
+    if (qt != B200_U8 && qt != B200_I8 && qt != B200_I32)
+        unsupported(*node, "input element type");
+    int x = canonical_slot(node->input_value(0)), s = canonical_slot(node->input_value(1)),
+        z = canonical_slot(node->input_value(2));
+    std::vector<int64_t> shape = to_i64(node->get_input_shape(0));
+    std::vector<int64_t> axes(dq->get_axes().begin(), dq->get_axes().end());
+    int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * sizeof(float));
+    emit(node, "dequantize", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_dequantize(p[x], static_cast<const float*>(p[s]), p[z], static_cast<float*>(p[y]), qt, shape.data(),
+                               int(shape.size()), axes.data(), int(axes.size()), st);
+    });
+    value_of(node->output(0)).canonical = y;
+}
+
+namespace
+{
+    struct ConvAttrs
+    {
+        Strides strides, dilation, data_dilation;
+        CoordinateDiff below, above;
+    };
+
+    template <typename T>
+    ConvAttrs attrs_of(const std::shared_ptr<T>& op)
+    {
+        return ConvAttrs{op->get_window_movement_strides(), op->get_window_dilation_strides(),
+                         op->get_data_dilation_strides(), op->get_padding_below(), op->get_padding_above()};
+    }
+}
+
+// Shared by the fused and the core convolution: emits the layout work and the kernel launch.
+static b200_conv_params make_conv_params(const Node& node, const ConvAttrs& a, const Shape& ds, const Shape& fs, size_t c_dev)
+{
+    if (ds.size() != 4 || fs.size() != 4)
+        unsupported(node, "only 2-D convolutions");
+    for (size_t v : a.data_dilation)
+        if (v != 1)
+            unsupported(node, "data dilation");
+    for (auto v : a.below)
+        if (v < 0) unsupported(node, "negative padding");
+    for (auto v : a.above)
+        if (v < 0) unsupported(node, "negative padding");
+    b200_conv_params c;
+    c.N = ds[0]; c.H = ds[2]; c.W = ds[3]; c.C = c_dev;
+    c.K = fs[0]; c.R = fs[2]; c.S = fs[3];
+    c.stride_h = a.strides[0]; c.stride_w = a.strides[1];
+    c.pad_h = a.below[0]; c.pad_w = a.below[1];
+    c.pad_h_above = a.above[0]; c.pad_w_above = a.above[1];
+    c.dilation_h = a.dilation[0]; c.dilation_w = a.dilation[1];
+    return c;
+}
+
+void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
+{
+    ConvAttrs a;
+    bool relu = false;
+    int bias_in = -1, scale_in = -1, sum_in = -1, sum_scale_in = -1;
+    if (auto op = as_type_ptr<op::v0::QuantizedConvolutionBias>(node))
+    {
+        a = attrs_of(op); relu = op->with_relu(); bias_in = 2; scale_in = 3;
+    }
+    else if (auto op = as_type_ptr<op::v0::QuantizedConvolutionBiasAdd>(node))
+    {
+        a = attrs_of(op); relu = op->with_relu(); bias_in = 2; sum_in = 3; scale_in = 4; sum_scale_in = 5;
+    }
+    else if (auto op = as_type_ptr<op::v0::QuantizedConvolutionBiasSignedAdd>(node))
+    {
+        a = attrs_of(op); relu = op->with_relu(); bias_in = 2; sum_in = 3; scale_in = 4; sum_scale_in = 5;
+    }
+    else
+    {
+        auto op2 = as_type_ptr<op::v0::QuantizedConvolutionRelu>(node);
+        a = attrs_of(op2); relu = true; scale_in = 2;
+    }
+    const Shape ds = node->get_input_shape(0), fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    int dt = dtype_of(node->get_input_element_type(0));
+    if ((dt != B200_U8 && dt != B200_I8) || node->get_input_element_type(1) != element::i8)
+        unsupported(*node, "data must be u8/i8 and filters i8");
+    if (bias_in >= 0 && node->get_input_element_type(bias_in) != element::i32)
+        unsupported(*node, "bias must be i32 (the builders quantise f32 bias to i32)");
+    if (node->get_input_element_type(scale_in) != element::f32)
+        unsupported(*node, "scale must be f32");
+    size_t n_scale = shape_size(node->get_input_shape(scale_in));
+    if (n_scale != 1 && n_scale != fs[0])
+        unsupported(*node, "scale must have 1 or K elements");
+    int out_t = dtype_of(node->get_output_element_type(0));
+
+    b200_epilogue e;
+    memset(&e, 0, sizeof(e));
+    e.relu = relu;
+    e.scale_count = int64_t(n_scale);
+    e.out_type = out_t;
+    int bias = bias_in >= 0 ? canonical_slot(node->input_value(bias_in)) : -1;
+    int scale = canonical_slot(node->input_value(scale_in));
+    int sum = -1, sum_scale = -1;
+    if (sum_in >= 0)
+    {
+        sum = nhwc_slot(node->input_value(sum_in));
+        sum_scale = canonical_slot(node->input_value(sum_scale_in));
+        e.sum_type = dtype_of(node->get_input_element_type(sum_in));
+    }
+    int y = new_slot(Slot::ARENA, shape_size(os));
+    const size_t C = ds[1];
+
+    if (C <= 4 && fs[3] <= 8 && a.dilation[0] == 1 && a.dilation[1] == 1)
+    {
+        // small-channel stem: 4-channel pixels -> patch matrix -> matrix product
+        b200_conv_params c = make_conv_params(*node, a, ds, fs, 4);
+        int64_t P = 0, Q = 0;
+        b200_qconv_out_shape(&c, &P, &Q);
+        auto cf = as_constant(node->input_value(1));
+        if (!cf)
+            unsupported(*node, "the small-channel path needs constant filters");
+        const int8_t* src = static_cast<const int8_t*>(cf->get_data_ptr());
+        size_t K = fs[0], R = fs[2], S = fs[3];
+        std::vector<int8_t> w(K * R * 32, 0);
+        for (size_t k = 0; k < K; ++k)
+            for (size_t ch = 0; ch < C; ++ch)
+                for (size_t r = 0; r < R; ++r)
+                    for (size_t s = 0; s < S; ++s)
+                        w[(k * R + r) * 32 + s * 4 + ch] = src[((k * C + ch) * R + r) * S + s];
+        int wslot = upload_constant(w.data(), w.size());
+        int xc = canonical_slot(node->input_value(0));
+        int x4 = new_slot(Slot::ARENA, ds[0] * ds[2] * ds[3] * 4);
+        int64_t M = int64_t(ds[0]) * P * Q, KK = int64_t(R) * 32;
+        int patches = new_slot(Slot::ARENA, size_t(M) * size_t(KK));
+        int64_t N = ds[0], H = ds[2], W = ds[3], Ci = C;
+        emit(node, "nchw_to_nhwc4", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_nchw_to_nhwc_u8(p[xc], p[x4], N, Ci, H, W, 4, st);
+        });
+        emit(node, "im2col_c4", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_im2col_c4_u8(p[x4], p[patches], c.N, c.H, c.W, c.R, c.S, c.stride_h, c.stride_w, c.pad_h, c.pad_w,
+                                     c.pad_h_above, c.pad_w_above, st);
+        });
+        int64_t Kout = fs[0];
+        emit(node, "stem_qgemm", [=](const Ptrs& p, cudaStream_t st) {
+            b200_epilogue ee = e;
+            ee.bias = bias >= 0 ? static_cast<const int32_t*>(p[bias]) : nullptr;
+            ee.scale = static_cast<const float*>(p[scale]);
+            ee.sum_in = sum >= 0 ? p[sum] : nullptr;
+            ee.sum_scale = sum_scale >= 0 ? static_cast<const float*>(p[sum_scale]) : nullptr;
+            return b200_qgemm(p[patches], dt, static_cast<const int8_t*>(p[wslot]), p[y], M, Kout, KK, &ee, st);
+        });
+        value_of(node->output(0)).nhwc = y;
+        return;
+    }
+
+    const size_t c_dev = align_up(C, 64);
+    int x;
+    if (c_dev == C)
+        x = nhwc_slot(node->input_value(0));
+    else
+    {
+        // channel counts the tensor-core path cannot take directly are zero-padded to a multiple of 64
+        int xc = canonical_slot(node->input_value(0));
+        x = new_slot(Slot::ARENA, ds[0] * ds[2] * ds[3] * c_dev);
+        int64_t N = ds[0], H = ds[2], W = ds[3], Ci = C, Cp = c_dev;
+        emit(node, "nchw_to_nhwc_pad", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
+        });
+    }
+    int w = packed_filters(node->input_value(1), c_dev);
+    b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
+    emit(node, "qconv", [=](const Ptrs& p, cudaStream_t st) {
+        b200_epilogue ee = e;
+        ee.bias = bias >= 0 ? static_cast<const int32_t*>(p[bias]) : nullptr;
+        ee.scale = static_cast<const float*>(p[scale]);
+        ee.sum_in = sum >= 0 ? p[sum] : nullptr;
+        ee.sum_scale = sum_scale >= 0 ? static_cast<const float*>(p[sum_scale]) : nullptr;
+        return b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &ee, st);
+    });
+    value_of(node->output(0)).nhwc = y;
+}
+
+void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
+{
+    auto op = as_type_ptr<op::v0::QuantizedConvolution>(node);
+    ConvAttrs a = attrs_of(op);
+    const Shape ds = node->get_input_shape(0), fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    int dt = dtype_of(node->get_input_element_type(0));
+    if (dt != B200_U8 || node->get_input_element_type(1) != element::i8)
+        unsupported(*node, "data must be u8 and filters i8 (u8 x u8 has no tensor-core form)");
+    if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
+        unsupported(*node, "non-zero input / filter zero points");
+    auto zo = as_constant(node->input_value(7));
+    if (!zo)
+        unsupported(*node, "output zero point must be a constant");
+    int out_t = dtype_of(node->get_output_element_type(0));
+    int32_t out_zp = 0;
+    if (out_t == B200_U8) out_zp = *static_cast<const uint8_t*>(zo->get_data_ptr());
+    else if (out_t == B200_I8) out_zp = *static_cast<const int8_t*>(zo->get_data_ptr());
+    else if (out_t == B200_I32) out_zp = *static_cast<const int32_t*>(zo->get_data_ptr());
+    else unsupported(*node, "output element type");
+    int scale = scalar_product_scale(node->input_value(2), node->input_value(4), node->input_value(6));
+    const size_t C = ds[1];
+    const size_t c_dev = align_up(C, 64);
+    int x;
+    if (c_dev == C)
+        x = nhwc_slot(node->input_value(0));
+    else
+    {
+        int xc = canonical_slot(node->input_value(0));
+        x = new_slot(Slot::ARENA, ds[0] * ds[2] * ds[3] * c_dev);
+        int64_t N = ds[0], H = ds[2], W = ds[3], Ci = C, Cp = c_dev;
+        emit(node, "nchw_to_nhwc_pad", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
+        });
+    }
+    int w = packed_filters(node->input_value(1), c_dev);
+    b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
+    const size_t esz = node->get_output_element_type(0).size();
+    int y = new_slot(Slot::ARENA, shape_size(os) * esz);
+    emit(node, "qconv_core", [=](const Ptrs& p, cudaStream_t st) {
+        b200_epilogue e;
+        memset(&e, 0, sizeof(e));
+        e.scale = static_cast<const float*>(p[scale]);
+        e.scale_count = 1;
+        e.round_half_away = 1;
+        e.out_zero_point = out_zp;
+        e.out_type = out_t;
+        return b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &e, st);
+    });
+    Value& o = value_of(node->output(0));
+    if (esz == 1)
+        o.nhwc = y;
+    else
+    {
+        // 4-byte outputs: bring [N,P,Q,K] back to NCHW with the byte transposer (4 bytes per element)
+        int yc = new_slot(Slot::ARENA, shape_size(os) * esz);
+        int64_t N = os[0], K = os[1], PQ = os[2] * os[3];
+        emit(node, "nhwc_to_nchw_i32", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_nhwc_to_nchw_b32(p[y], p[yc], N, K, PQ, st);
+        });
+        o.canonical = yc;
+    }
+}
+
+void B200Executable::compile_dot_bias(const std::shared_ptr<Node>& node)
+{
+    auto op = as_type_ptr<op::v0::QuantizedDotBias>(node);
+    const Shape as = node->get_input_shape(0), ws = node->get_input_shape(1);
+    int dt = dtype_of(node->get_input_element_type(0));
+    if ((dt != B200_U8 && dt != B200_I8) || node->get_input_element_type(1) != element::i8)
+        unsupported(*node, "data must be u8/i8 and weights i8");
+    if (node->get_input_element_type(2) != element::i32)
+        unsupported(*node, "bias must be i32");
+    if (as.size() != 2 || ws.size() != 2 || as[1] % 16 != 0)
+        unsupported(*node, "2-D operands with a reduction length that is a multiple of 16");
+    size_t n_scale = shape_size(node->get_input_shape(3));
+    if (n_scale != 1 && n_scale != ws[0])
+        unsupported(*node, "scale must have 1 or N elements");
+    int a = canonical_slot(node->input_value(0)), w = canonical_slot(node->input_value(1)),
+        bias = canonical_slot(node->input_value(2)), scale = canonical_slot(node->input_value(3));
+    int out_t = dtype_of(node->get_output_element_type(0));
+    int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * node->get_output_element_type(0).size());
+    int64_t M = as[0], K = as[1], N = ws[0];
+    bool relu = op->with_relu();
+    emit(node, "qgemm", [=](const Ptrs& p, cudaStream_t st) {
+        b200_epilogue e;
+        memset(&e, 0, sizeof(e));
+        e.bias = static_cast<const int32_t*>(p[bias]);
+        e.scale = static_cast<const float*>(p[scale]);
+        e.scale_count = int64_t(n_scale);
+        e.relu = relu;
+        e.out_type = out_t;
+        return b200_qgemm(p[a], dt, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
+    });
+    value_of(node->output(0)).canonical = y;
+}
+
+void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
+{
+    auto op = as_type_ptr<op::v0::QuantizedDot>(node);
+    const Shape as = node->get_input_shape(0), bs = node->get_input_shape(1);
+    if (node->get_input_element_type(0) != element::u8 || node->get_input_element_type(1) != element::i8)
+        unsupported(*node, "input0 must be u8 and input1 i8 (u8 x u8 has no tensor-core form)");
+    if (as.size() != 2 || bs.size() != 2 || op->get_reduction_axes_count() != 1 || as[1] % 16 != 0)
+        unsupported(*node, "2-D operands with a reduction length that is a multiple of 16");
+    if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
+        unsupported(*node, "non-zero input zero points");
+    auto zo = as_constant(node->input_value(7));
+    if (!zo)
+        unsupported(*node, "output zero point must be a constant");
+    int out_t = dtype_of(node->get_output_element_type(0));
+    int32_t out_zp = 0;
+    if (out_t == B200_U8) out_zp = *static_cast<const uint8_t*>(zo->get_data_ptr());
+    else if (out_t == B200_I8) out_zp = *static_cast<const int8_t*>(zo->get_data_ptr());
+    else if (out_t == B200_I32) out_zp = *static_cast<const int32_t*>(zo->get_data_ptr());
+    else unsupported(*node, "output element type");
+    int scale = scalar_product_scale(node->input_value(2), node->input_value(4), node->input_value(6));
+    int a = canonical_slot(node->input_value(0));
+    int64_t M = as[0], K = as[1], N = bs[1];
+    // B [K,N] -> W [N,K]: once at compile time for constants, one transpose kernel per call otherwise
+    int w;
+    if (auto cb = as_constant(node->input_value(1)))
+    {
+        const int8_t* src = static_cast<const int8_t*>(cb->get_data_ptr());
+        std::vector<int8_t> t(size_t(N) * K);
+        for (int64_t k = 0; k < K; ++k)
+            for (int64_t n = 0; n < N; ++n)
+                t[n * K + k] = src[k * N + n];
+        w = upload_constant(t.data(), t.size());
+    }
+    else
+    {
+        int b = canonical_slot(node->input_value(1));
+        w = new_slot(Slot::ARENA, size_t(N) * K);
+        emit(node, "transpose_b", [=](const Ptrs& p, cudaStream_t st) { return b200_transpose_u8(p[b], p[w], K, N, st); });
+    }
+    int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * node->get_output_element_type(0).size());
+    emit(node, "qgemm_core", [=](const Ptrs& p, cudaStream_t st) {
+        b200_epilogue e;
+        memset(&e, 0, sizeof(e));
+        e.scale = static_cast<const float*>(p[scale]);
+        e.scale_count = 1;
+        e.round_half_away = 1;
+        e.out_zero_point = out_zp;
+        e.out_type = out_t;
+        return b200_qgemm(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
+    });
+    value_of(node->output(0)).canonical = y;
+}
+
+void B200Executable::compile_max_pool(const std::shared_ptr<Node>& node)
+{
+    auto op = as_type_ptr<op::v0::MaxPool>(node);
+    const Shape is = node->get_input_shape(0), os = node->get_output_shape(0);
+    if (node->get_input_element_type(0) != element::u8 || is.size() != 4 || is[1] % 16 != 0)
+        unsupported(*node, "u8 NCHW input with a multiple of 16 channels");
+    int x = nhwc_slot(node->input_value(0));
+    int y = new_slot(Slot::ARENA, shape_size(os));
+    int64_t N = is[0], C = is[1], H = is[2], W = is[3];
+    int64_t wh = op->get_window_shape()[0], ww = op->get_window_shape()[1];
+    int64_t sh = op->get_window_movement_strides()[0], sw = op->get_window_movement_strides()[1];
+    int64_t pb0 = op->get_padding_below()[0], pb1 = op->get_padding_below()[1];
+    int64_t pa0 = op->get_padding_above()[0], pa1 = op->get_padding_above()[1];
+    emit(node, "maxpool", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_maxpool_nhwc_u8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st);
+    });
+    value_of(node->output(0)).nhwc = y;
+}
+
+// ------------------------------------------------------------------------------------ executable: call
+bool B200Executable::call(const std::vector<std::shared_ptr<runtime::Tensor>>& outputs,
+                          const std::vector<std::shared_ptr<runtime::Tensor>>& inputs)
+{
+    std::lock_guard<std::mutex> lock(m_call_mutex);
+    m_ctx->make_current();
+    if (inputs.size() != m_function->get_parameters().size() || outputs.size() != m_function->get_results().size())
+        throw std::runtime_error("B200 backend: call() tensor count does not match the Function");
+    Ptrs ptrs(m_slots.size(), nullptr);
+    for (size_t i = 0; i < m_slots.size(); ++i)
+    {
+        const Slot& s = m_slots[i];
+        switch (s.kind)
+        {
+        case Slot::ARENA: ptrs[i] = static_cast<char*>(m_arena) + s.offset; break;
+        case Slot::CONSTANT: ptrs[i] = static_cast<char*>(m_constants) + s.offset; break;
+        case Slot::PARAMETER:
+        case Slot::RESULT:
+        {
+            auto t = std::dynamic_pointer_cast<B200Tensor>(s.kind == Slot::PARAMETER ? inputs[s.index] : outputs[s.index]);
+            if (!t)
+                throw std::invalid_argument("B200 backend: call() was given a tensor that another backend created");
+            if (t->context()->device != m_ctx->device)
+                throw std::invalid_argument("B200 backend: tensor lives on another device");
+            if (t->get_size_in_bytes() < s.bytes)
+                throw std::invalid_argument("B200 backend: tensor smaller than the Function's parameter/result");
+            ptrs[i] = t->device_ptr();
+            break;
+        }
+        }
+    }
+    cudaStream_t st = m_ctx->stream;
+    for (size_t i = 0; i < m_steps.size(); ++i)
+    {
+        if (m_perf) cudaEventRecord(m_events[2 * i], st);
+        kernel_check(m_steps[i].run(ptrs, st), m_steps[i].what + " for " + m_steps[i].node->get_name());
+        if (m_perf) cudaEventRecord(m_events[2 * i + 1], st);
+    }
+    for (auto& rc : m_result_copies)
+        if (ptrs[rc.first] != ptrs[rc.second])
+            cuda_check(cudaMemcpyAsync(ptrs[rc.second], ptrs[rc.first], m_slots[rc.second].bytes, cudaMemcpyDeviceToDevice, st),
+                       "result copy");
+    if (m_perf)
+    {
+        m_ctx->synchronize();
+        for (size_t i = 0; i < m_steps.size(); ++i)
+        {
+            float ms = 0;
+            cudaEventElapsedTime(&ms, m_events[2 * i], m_events[2 * i + 1]);
+            m_step_us[i] += ms * 1000.0;
+        }
+        ++m_calls;
+    }
+    // no synchronisation here: Tensor::read() orders itself after this call on the same stream
+    return true;
+}
+
+std::vector<runtime::PerformanceCounter> B200Executable::get_performance_data() const
+{
+    std::vector<runtime::PerformanceCounter> rc;
+    std::map<const Node*, size_t> index;
+    for (size_t i = 0; i < m_steps.size(); ++i)
+    {
+        const Node* n = m_steps[i].node.get();
+        size_t us = m_perf ? size_t(m_step_us[i]) : 0;
+        auto it = index.find(n);
+        if (it == index.end())
+        {
+            index[n] = rc.size();
+            rc.emplace_back(m_steps[i].node, us, m_calls);
+        }
+        else
+            rc[it->second].m_total_microseconds += us;
+    }
+    return rc;
+}
+
+std::shared_ptr<runtime::Tensor> B200Executable::create_input_tensor(size_t input_index)
+{
+    auto p = get_parameters().at(input_index);
+    return std::make_shared<B200Tensor>(m_ctx, p->get_output_element_type(0), p->get_output_shape(0));
+}
+
+std::shared_ptr<runtime::Tensor> B200Executable::create_output_tensor(size_t output_index)
+{
+    auto r = get_results().at(output_index);
+    return std::make_shared<B200Tensor>(m_ctx, r->get_output_element_type(0), r->get_output_shape(0));
+}
+
+std::vector<std::shared_ptr<runtime::Tensor>> B200Executable::create_input_tensor(size_t input_index, size_t pipeline_depth)
+{
+    std::vector<std::shared_ptr<runtime::Tensor>> v;
+    for (size_t i = 0; i < pipeline_depth; ++i)
+        v.push_back(create_input_tensor(input_index));
+    return v;
+}
+
+std::vector<std::shared_ptr<runtime::Tensor>> B200Executable::create_output_tensor(size_t output_index, size_t pipeline_depth)
+{
+    std::vector<std::shared_ptr<runtime::Tensor>> v;
+    for (size_t i = 0; i < pipeline_depth; ++i)
+        v.push_back(create_output_tensor(output_index));
+    return v;
+}

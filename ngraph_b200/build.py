@@ -51,5 +51,59 @@ def build_kernels(force=False, verbose=False):
     return KERNEL_LIB
 
 
+PLUGIN_LIB = os.path.join(HERE, "libb200_backend.so")
+NGRAPH_LIB_DIR = os.path.join(ROOT, "oracle", "_ref", "lib")
+
+
+def ngraph_include_dir():
+    """nGraph's public headers (the plugin compiles against them, like every nGraph backend)."""
+    for d in (os.environ.get("NGRAPH_SRC", ""), "/root/reference/src"):
+        if d and os.path.exists(os.path.join(d, "ngraph", "runtime", "backend.hpp")):
+            return d
+    return None
+
+
+def host_cxx_flags(inc):
+    return ["-std=c++14", "-O2", "-fPIC", "-w", "-include", "cstdint", "-include", "limits", "-DNGRAPH_JSON_DISABLE",
+            "-I" + inc, "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include"]
+
+
+def build_plugin(force=False):
+    """g++ the nGraph backend plugin against nGraph's headers and libngraph.so.  Skipped (returns None)
+    where nGraph's headers or library are not available: the prebuilt .so is used there."""
+    inc = ngraph_include_dir()
+    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "b200_backend.hpp")]
+    if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
+        return PLUGIN_LIB if os.path.exists(PLUGIN_LIB) else None
+    build_kernels()
+    if not force and _newer(PLUGIN_LIB, src + [KERNEL_LIB]):
+        return PLUGIN_LIB
+    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], "-o", PLUGIN_LIB,
+           "-L" + HERE, "-lb200_kernels", "-L" + NGRAPH_LIB_DIR, "-lngraph", "-L/usr/local/cuda/lib64", "-lcudart_static",
+           "-ldl", "-lrt", "-lpthread", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
+    subprocess.check_call(cmd)
+    return PLUGIN_LIB
+
+
+CAPI_LIB = os.path.join(HERE, "libng_capi.so")
+
+
+def build_capi(force=False):
+    """The C facade over nGraph's C++ API that the Python tests and the benchmark drive (ctypes)."""
+    inc = ngraph_include_dir()
+    src = os.path.join(HERE, "harness", "ng_capi.cpp")
+    if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
+        return CAPI_LIB if os.path.exists(CAPI_LIB) else None
+    if not force and _newer(CAPI_LIB, [src]):
+        return CAPI_LIB
+    flags = [f for f in host_cxx_flags(inc) if f != "-std=c++14"] + ["-std=c++11"]
+    cmd = ["/usr/bin/g++"] + flags + ["-shared", src, "-o", CAPI_LIB, "-L" + NGRAPH_LIB_DIR, "-lngraph", "-ldl",
+                             "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
+    subprocess.check_call(cmd)
+    return CAPI_LIB
+
+
 if __name__ == "__main__":
     print(build_kernels(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_plugin(force="--force" in sys.argv))
+    print(build_capi(force="--force" in sys.argv))

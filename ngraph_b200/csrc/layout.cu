@@ -287,3 +287,48 @@ extern "C" int b200_requant_scale(const float* input_scale, const float* filter_
     requant_scale_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(input_scale, filter_scale, output_scale, out);
     return after_launch("b200_requant_scale");
 }
+
+namespace b200
+{
+    // [batch, rows, cols] -> [batch, cols, rows] for 4-byte elements (int32 / f32 convolution outputs)
+    __global__ void __launch_bounds__(256) transpose_b32_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                                                int64_t rows, int64_t cols)
+    {
+        __shared__ uint32_t tile[TT][TT + 1];
+        const int64_t b = blockIdx.z;
+        const int64_t r0 = int64_t(blockIdx.y) * TT, c0 = int64_t(blockIdx.x) * TT;
+        const uint32_t* ip = in + b * rows * cols;
+        uint32_t* op = out + b * rows * cols;
+        const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+        for (int j = ty; j < TT; j += 8)
+        {
+            int64_t r = r0 + j, c = c0 + tx;
+            if (r < rows && c < cols)
+                tile[j][tx] = ip[r * cols + c];
+        }
+        __syncthreads();
+        for (int j = ty; j < TT; j += 8)
+        {
+            int64_t c = c0 + j, r = r0 + tx;
+            if (c < cols && r < rows)
+                op[c * rows + r] = tile[tx][j];
+        }
+    }
+}
+
+extern "C" int b200_nhwc_to_nchw_b32(const void* in, void* out, int64_t N, int64_t C, int64_t HW, void* stream)
+{
+    using namespace b200;
+    if (N < 0 || C < 0 || HW < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (N * C * HW == 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    dim3 grid(unsigned((C + TT - 1) / TT), unsigned((HW + TT - 1) / TT), unsigned(N));
+    if (grid.y > 65535 || grid.z > 65535)
+        return B200_ERR_TOO_LARGE;
+    transpose_b32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
+                                                                           static_cast<uint32_t*>(out), HW, C);
+    return after_launch("b200_nhwc_to_nchw_b32");
+}

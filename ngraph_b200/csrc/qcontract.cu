@@ -15,7 +15,7 @@
 //   maps over the s-strided pixel sub-lattices of the input (no element strides, no gather).
 //   The filter [K,R,S,C] is a plain [K, R*S*C] row-major matrix, so B tiles are 2-D boxes.
 // * warp 0: TMA producer; warp 1: TMEM allocation + MMA issue (one elected thread);
-//   warps 2-5: epilogue (tcgen05.ld -> bias/scale/sum/ReLU/round/saturate -> global).
+//   warps 2-9: epilogue (tcgen05.ld -> bias/scale/sum/ReLU/round/saturate -> global).
 //   Two TMEM accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.
 // * Every wait is bounded (ptx::mbar_wait); a timeout sets g_contract_status, the CTA
 //   drains and frees its TMEM, and the host reports B200_ERR_DEVICE_STATUS.
@@ -61,7 +61,7 @@ namespace b200
     };
 
     constexpr int BM = 128;
-    constexpr int NUM_THREADS = 192;
+    constexpr int NUM_THREADS = 320; // producer warp, MMA warp, 8 epilogue warps
 
     template <int BN, int BK>
     struct Cfg
@@ -93,34 +93,16 @@ namespace b200
         int64_t off; // element offset of column 0 of this row in out / sum_in
     };
 
-    // Converts one accumulator to the output value; returns it as raw 32 bits
-    // (f32 bit pattern, or the integer result before narrowing).
-    __device__ __forceinline__ uint32_t epilogue_one(const ContractParams& p, int32_t acc, int32_t bias, float scale,
-                                                     bool has_sum, float sum_v, float sum_scale)
+    // Core requantisation of one accumulator (reference::dot / convolution, dot.hpp:152-159):
+    // (OUT)round(float(acc) * scale) + zero_point, saturated.  Returns the integer as raw 32 bits.
+    __device__ __forceinline__ uint32_t epilogue_core(const ContractParams& p, int32_t acc, float scale)
     {
-        if (p.half_away)
-        {
-            // reference::dot / convolution requantisation (dot.hpp:152-159): (OUT)round(float(acc)*scale) + zp
-            float r = roundf(__fmul_rn(__int2float_rn(acc), scale));
-            long long v = __float2ll_rn(r) + static_cast<long long>(p.out_zp);
-            long long lo = p.out_type == B200_U8 ? 0ll : p.out_type == B200_I8 ? -128ll : -2147483648ll;
-            long long hi = p.out_type == B200_U8 ? 255ll : p.out_type == B200_I8 ? 127ll : 2147483647ll;
-            v = v < lo ? lo : (v > hi ? hi : v);
-            return (r != r) ? 0u : static_cast<uint32_t>(static_cast<int32_t>(v));
-        }
-        float v = __fmul_rn(__int2float_rn(acc + bias), scale);
-        if (has_sum)
-            v = __fadd_rn(v, __fmul_rn(sum_scale, sum_v));
-        if (p.relu)
-            v = (v > 0.0f) ? v : 0.0f;
-        if (p.out_type == B200_F32)
-            return __float_as_uint(v);
-        float q = round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(v);
-        if (p.out_type == B200_U8)
-            return static_cast<uint32_t>(clamp_cast<uint8_t>(q));
-        if (p.out_type == B200_I8)
-            return static_cast<uint32_t>(static_cast<int32_t>(clamp_cast<int8_t>(q)));
-        return static_cast<uint32_t>(clamp_cast<int32_t>(q));
+        float r = roundf(__fmul_rn(__int2float_rn(acc), scale));
+        long long v = __float2ll_rn(r) + static_cast<long long>(p.out_zp);
+        long long lo = p.out_type == B200_U8 ? 0ll : p.out_type == B200_I8 ? -128ll : -2147483648ll;
+        long long hi = p.out_type == B200_U8 ? 255ll : p.out_type == B200_I8 ? 127ll : 2147483647ll;
+        v = v < lo ? lo : (v > hi ? hi : v);
+        return (r != r) ? 0u : static_cast<uint32_t>(static_cast<int32_t>(v));
     }
 
     template <int BN, int BK>
@@ -131,6 +113,8 @@ namespace b200
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
+        __shared__ __align__(16) float epi_scale[8][BN / 2];   // per epilogue warp: its column half of the tile
+        __shared__ __align__(16) int32_t epi_bias[8][BN / 2];
 
         const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
         const uint32_t bars = smem_base + C::STAGES * C::STAGE_BYTES;
@@ -154,7 +138,7 @@ namespace b200
             for (int b = 0; b < 2; ++b)
             {
                 ptx::mbar_init(tfull_bar(b), 1);
-                ptx::mbar_init(tempty_bar(b), 4);
+                ptx::mbar_init(tempty_bar(b), 8);
             }
             ptx::fence_barrier_init();
         }
@@ -270,9 +254,12 @@ namespace b200
         }
         else
         {
-            // ------------------------------------------------------------ epilogue (warps 2..5)
-            const int quarter = warp & 3;            // TMEM lanes this warp may read
-            const int row = quarter * 32 + lane;     // accumulator row of this thread
+            // ------------------------------------------------------------ epilogue (warps 2..9)
+            // TMEM lane quarter (warp id % 4) is fixed by the hardware; the two warps that share a
+            // quarter split the tile's columns between them.
+            const int quarter = warp & 3;
+            const int half = (warp - 2) >> 2;
+            const int row = quarter * 32 + lane; // accumulator row of this thread
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
@@ -284,6 +271,17 @@ namespace b200
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int acc = tile_it & 1;
                 const uint32_t acc_ph = (tile_it >> 1) & 1;
+                // stage this warp's share of the tile's per-channel scale and bias (warp-private buffer,
+                // so a warp-level sync is all the ordering it needs)
+                __syncwarp();
+                for (int j = lane; j < BN / 2; j += 32)
+                {
+                    const int col = tn * BN + half * (BN / 2) + j;
+                    const bool in_n = col < p.N;
+                    epi_scale[warp - 2][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
+                    epi_bias[warp - 2][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
+                }
+                __syncwarp();
                 EpiRow er;
                 if (p.conv)
                 {
@@ -310,7 +308,7 @@ namespace b200
                 }
                 ptx::tc_fence_after_sync();
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32)
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32)
                 {
                     uint32_t v[32];
                     __syncwarp();
@@ -320,40 +318,79 @@ namespace b200
                     if (col0 >= p.N)
                         continue; // warp-uniform
                     const bool full_chunk = col0 + 32 <= p.N;
-                    // sum_in for this row chunk (32 contiguous bytes)
-                    uint32_t sumw[8];
-                    if (has_sum && er.valid && full_chunk && vec_ok)
+                    const bool fast = full_chunk && vec_ok;
+                    const float* sc = &epi_scale[warp - 2][c0 - half * (BN / 2)];
+                    const int32_t* bi = &epi_bias[warp - 2][c0 - half * (BN / 2)];
+                    if (p.half_away)
                     {
-                        const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + col0);
-                        uint4 s0 = sp[0], s1 = sp[1];
-                        sumw[0] = s0.x; sumw[1] = s0.y; sumw[2] = s0.z; sumw[3] = s0.w;
-                        sumw[4] = s1.x; sumw[5] = s1.y; sumw[6] = s1.z; sumw[7] = s1.w;
-                    }
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = epilogue_core(p, int32_t(v[j]), sc[j]);
+                    }
+                    else
                     {
-                        const int col = col0 + j;
-                        const bool in_n = full_chunk || col < p.N;
-                        const int cc = in_n ? col : 0;
-                        const int32_t b = p.bias ? __ldg(p.bias + cc) : 0;
-                        const float sc = __ldg(p.scale + (p.scale_per_channel ? cc : 0));
-                        float sv = 0.0f;
-                        if (has_sum && er.valid && in_n)
+                        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu]
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            f[j] = __fmul_rn(__int2float_rn(int32_t(v[j]) + bi[j]), sc[j]);
+                        if (has_sum && er.valid)
                         {
-                            if (full_chunk && vec_ok)
+                            if (fast)
                             {
-                                uint32_t byte = (sumw[j >> 2] >> (8 * (j & 3))) & 0xFF;
-                                sv = p.sum_type == B200_U8 ? float(byte) : float(int8_t(byte));
+                                const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + col0);
+                                const uint4 s0 = sp[0], s1 = sp[1];
+                                const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                {
+                                    const uint32_t byte = (sw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+                                    const float sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
+                                    f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, sv));
+                                }
                             }
                             else
-                                sv = load_sum(p.sum_in, p.sum_type, er.off + col);
+                            {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.N)
+                                        f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, load_sum(p.sum_in, p.sum_type, er.off + col0 + j)));
+                            }
                         }
-                        v[j] = epilogue_one(p, int32_t(v[j]), b, sc, has_sum, sv, sum_scale);
+                        if (p.relu)
+                        {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                f[j] = (f[j] > 0.0f) ? f[j] : 0.0f; // reference::relu; NaN -> 0 as there
+                        }
+                        if (p.out_type == B200_F32)
+                        {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                v[j] = __float_as_uint(f[j]);
+                        }
+                        else if (p.out_type == B200_I32)
+                        {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                v[j] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[j])));
+                        }
+                        else
+                        {
+                            // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal
+                            // floor(v+0.5)/ceil(v-0.5)/parity sequence equals round-to-nearest-even for
+                            // |v| < 2^23 and everything beyond saturates, so one saturating cvt.rni
+                            // (NaN -> 0) followed by the integer clamp gives the same byte.
+                            const int lo = p.out_type == B200_U8 ? 0 : -128, hi = p.out_type == B200_U8 ? 255 : 127;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                v[j] = uint32_t(min(max(__float2int_rn(f[j]), lo), hi));
+                        }
                     }
                     if (er.valid && esz == 1)
                     {
                         uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
-                        if (full_chunk && vec_ok)
+                        if (fast)
                         {
                             uint32_t w[8];
 #pragma unroll
@@ -374,7 +411,7 @@ namespace b200
                     else if (er.valid)
                     {
                         uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
-                        if (full_chunk && vec_ok)
+                        if (fast)
                         {
 #pragma unroll
                             for (int j = 0; j < 8; ++j)

@@ -106,6 +106,93 @@ namespace b200
         }
     }
 
+    // Round-to-nearest-even Quantize to 8 bits with the division strength-reduced per row.
+    //
+    // The row's scale s is uniform, so y = RN(1/s) is computed once (correctly rounded reciprocal)
+    // and each quotient is  q0 = RN(x*y);  e = x - q0*s (exact in one FMA);  q = RN(q0 + e*y),
+    // which is the correctly rounded x/s (Markstein's division theorem) whenever s is a normal
+    // number whose significand is not all ones and nothing over/underflows.  Blocks whose scale
+    // fails that test, and quotients of magnitude >= 2^24 (whose result saturates regardless of
+    // the last bit), take the other branches below, so every output byte equals the plain
+    // x / s -> floor(q+0.5)/ceil(q-0.5)/parity -> +zero_point -> clamp sequence of the reference.
+    // (For |q| < 2^23 that rounding sequence is round-half-even, i.e. one cvt.rni; beyond it clamps.)
+    __device__ __forceinline__ bool scale_allows_fast_division(float s)
+    {
+        const uint32_t b = __float_as_uint(s);
+        const uint32_t ex = (b >> 23) & 0xFF, man = b & 0x7FFFFF;
+        return ex >= 127 - 40 && ex <= 127 + 40 && man != 0x7FFFFF;
+    }
+
+    template <typename Q>
+    __device__ __forceinline__ int quantize_rne_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
+    {
+        const float q0 = __fmul_rn(x, y);
+        const float e = __fmaf_rn(-q0, s, x);
+        const float q1 = __fmaf_rn(e, y, q0);
+        const float q = (fabsf(q0) < 16777216.0f) ? q1 : q0; // huge, inf and NaN quotients skip the correction
+        const int i = __float2int_rn(q);                     // saturating
+        const int r = min(max(i, lo_minus_zp), hi_minus_zp) + zp;
+        return (x != x) ? 0 : r;                             // NaN -> 0, as clamp_cast
+    }
+
+    template <typename Q>
+    __global__ void __launch_bounds__(QT) quantize_rows_rne8_kernel(const float* __restrict__ x,
+                                                                   const float* __restrict__ scale,
+                                                                   const Q* __restrict__ zp,
+                                                                   Q* __restrict__ out,
+                                                                   int64_t inner,
+                                                                   uint32_t chunks_per_row,
+                                                                   int64_t n_scales)
+    {
+        const int64_t row = blockIdx.x / chunks_per_row;
+        const uint32_t chunk = blockIdx.x - uint32_t(row) * chunks_per_row;
+        const int64_t sidx = row % n_scales;
+        const float s = scale[sidx];
+        const int zi = static_cast<int>(zp[sidx]);
+        const float z = static_cast<float>(zi);
+        const int64_t row_off = int64_t(chunk) * QCHUNK;
+        const int64_t rem = inner - row_off;
+        const float* xp = x + row * inner + row_off;
+        Q* op = out + row * inner + row_off;
+        const bool fast = scale_allows_fast_division(s);
+        const float y = __frcp_rn(s);
+        const int lo = int(QLimits<Q>::lo) - zi, hi = int(QLimits<Q>::hi) - zi;
+
+        float4 v[QU];
+#pragma unroll
+        for (int u = 0; u < QU; ++u)
+        {
+            int64_t off = (int64_t(u) * QT + threadIdx.x) * 4;
+            if (off + 4 <= rem)
+                v[u] = *reinterpret_cast<const float4*>(xp + off);
+        }
+#pragma unroll
+        for (int u = 0; u < QU; ++u)
+        {
+            int64_t off = (int64_t(u) * QT + threadIdx.x) * 4;
+            if (off + 4 <= rem)
+            {
+                if (fast)
+                {
+                    const int a = quantize_rne_fast<Q>(v[u].x, s, y, lo, hi, zi), b = quantize_rne_fast<Q>(v[u].y, s, y, lo, hi, zi);
+                    const int c = quantize_rne_fast<Q>(v[u].z, s, y, lo, hi, zi), d = quantize_rne_fast<Q>(v[u].w, s, y, lo, hi, zi);
+                    *reinterpret_cast<uint32_t*>(op + off) =
+                        uint32_t(a & 0xFF) | (uint32_t(b & 0xFF) << 8) | (uint32_t(c & 0xFF) << 16) | (uint32_t(d & 0xFF) << 24);
+                }
+                else
+                {
+                    store4<Q>(op + off, quantize_one<Q, 4>(v[u].x, s, z), quantize_one<Q, 4>(v[u].y, s, z),
+                              quantize_one<Q, 4>(v[u].z, s, z), quantize_one<Q, 4>(v[u].w, s, z));
+                }
+            }
+            else
+            {
+                for (int64_t e = off; e < rem && e < off + 4; ++e)
+                    op[e] = quantize_one<Q, 4>(xp[e], s, z);
+            }
+        }
+    }
+
     template <typename Q, int MODE>
     __global__ void __launch_bounds__(QT) quantize_generic_kernel(const float* __restrict__ x,
                                                                   const float* __restrict__ scale,
@@ -300,11 +387,31 @@ namespace b200
         return unsigned(b < cap ? (b > 0 ? b : 1) : cap);
     }
 
+    std::atomic<int> g_fast_division{1};
+
+    template <typename Q>
+    static void launch_rne8(const float* x, const float* scale, const void* zp, void* out, const QuantPlan& p,
+                            uint32_t chunks, cudaStream_t st)
+    {
+        quantize_rows_rne8_kernel<Q><<<unsigned(chunks * p.rows), QT, 0, st>>>(
+            x, scale, static_cast<const Q*>(zp), static_cast<Q*>(out), p.inner, chunks, p.n_scales);
+    }
+    template <>
+    void launch_rne8<int32_t>(const float*, const float*, const void*, void*, const QuantPlan&, uint32_t, cudaStream_t)
+    {
+    }
+
     template <typename Q, int MODE>
     static int launch_quantize(const float* x, const float* scale, const void* zp, void* out,
                                const QuantPlan& p, cudaStream_t st)
     {
-        if (use_rows(p, x, out))
+        if (use_rows(p, x, out) && MODE == B200_ROUND_NEAREST_TOWARD_EVEN && sizeof(Q) == 1 &&
+            g_fast_division.load(std::memory_order_relaxed))
+        {
+            uint32_t chunks = uint32_t((p.inner + QCHUNK - 1) / QCHUNK);
+            launch_rne8<Q>(x, scale, zp, out, p, chunks, st);
+        }
+        else if (use_rows(p, x, out))
         {
             uint32_t chunks = uint32_t((p.inner + QCHUNK - 1) / QCHUNK);
             quantize_rows_kernel<Q, MODE><<<unsigned(chunks * p.rows), QT, 0, st>>>(
@@ -354,6 +461,12 @@ namespace b200
         }
         return after_launch("b200_dequantize");
     }
+}
+
+extern "C" int b200_set_fast_division(int enable)
+{
+    int old = b200::g_fast_division.exchange(enable ? 1 : 0);
+    return old;
 }
 
 extern "C" int b200_quantize(const float* input, const float* scale, const void* zero_point, void* output,

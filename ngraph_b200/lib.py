@@ -43,6 +43,7 @@ def _load():
         "b200_launch_count": (ctypes.c_uint64, []),
         "b200_reset_launch_count": (None, []),
         "b200_device_status": (ci, [ctypes.POINTER(ci)]),
+        "b200_set_fast_division": (ci, [ci]),
         "b200_quantize": (ci, [vp, vp, vp, vp, ci, p64, ci, p64, ci, ci, vp]),
         "b200_dequantize": (ci, [vp, vp, vp, vp, ci, p64, ci, p64, ci, vp]),
         "b200_qgemm": (ci, [vp, ci, vp, vp, i64, i64, i64, ctypes.POINTER(Epilogue), vp]),
@@ -51,6 +52,7 @@ def _load():
         "b200_nchw_to_nhwc_u8": (ci, [vp, vp, i64, i64, i64, i64, i64, vp]),
         "b200_nhwc_to_nchw_u8": (ci, [vp, vp, i64, i64, i64, i64, i64, vp]),
         "b200_transpose_u8": (ci, [vp, vp, i64, i64, vp]),
+        "b200_nhwc_to_nchw_b32": (ci, [vp, vp, i64, i64, i64, vp]),
         "b200_maxpool_nhwc_u8": (ci, [vp, vp] + [i64] * 12 + [vp]),
         "b200_global_avgpool_q_nhwc_u8": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
         "b200_im2col_c4_u8": (ci, [vp, vp] + [i64] * 11 + [vp]),

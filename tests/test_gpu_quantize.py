@@ -154,3 +154,29 @@ def test_roundtrip_property_full_size(ops):
     idx = torch.arange(0, x.numel(), 4099, device="cuda")
     exp = ref.quantize(x.view(-1)[idx].cpu().numpy(), np.float32(0.05), np.uint8(128))
     np.testing.assert_array_equal(q.view(-1)[idx].cpu().numpy(), exp)
+
+
+def test_fast_division_is_exact_for_every_float(ops):
+    """The strength-reduced division of the RNE 8-bit kernel against the plain IEEE division, over ALL
+    2^32 float bit patterns, for the benchmark's scales (0.05 and log-uniform per-channel values) and a
+    few awkward ones.  Any difference in any output byte fails."""
+    from ngraph_b200 import lib
+    rng = np.random.default_rng(99)
+    scales = [0.05, 1.0, 3.0, 0.1, 1e-3, 7.0 / 255.0, 0.02, 1.9999999, 1.0000001]
+    scales += list(np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=7)))
+    chunk = 1 << 28
+    base = torch.arange(chunk, dtype=torch.int64, device="cuda")
+    for qdt, zpv in ((torch.uint8, 128), (torch.int8, 0)):
+        zp = torch.full((), zpv, dtype=qdt, device="cuda")
+        for sv in scales:
+            s = torch.full((), float(np.float32(sv)), device="cuda")
+            for c in range(16):
+                x = (base + c * chunk).to(torch.int32).view(torch.float32) if c < 8 else \
+                    (base + c * chunk - (1 << 32)).to(torch.int32).view(torch.float32)
+                fast = ops.quantize(x, s, zp)
+                old = lib.LIB.b200_set_fast_division(0)
+                try:
+                    exact = ops.quantize(x, s, zp)
+                finally:
+                    lib.LIB.b200_set_fast_division(old)
+                assert torch.equal(fast, exact), "scale %r chunk %d: %d bytes differ" % (sv, c, int((fast != exact).sum()))

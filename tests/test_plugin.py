@@ -1,0 +1,305 @@
+"""The nGraph backend plugin (libb200_backend.so) driven the way any nGraph client drives a backend:
+build a Function, Backend::create("B200"), compile, create_tensor, write, call_with_validate, read.
+GPU tests run the same Function (or, for the fused ops INTERPRETER lacks, its decomposition) on
+nGraph's own INTERPRETER backend in the same process and compare: integers bit-exact, f32 bit-exact."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+from tests.fixtures import blob, interpreter_cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ng = pytest.importorskip("ngraph_b200.ngraph_api")
+from oracle import interpreter  # noqa: E402
+
+needs_ngraph = pytest.mark.skipif(not interpreter.available(), reason="nGraph host library / INTERPRETER not built here")
+
+
+# ---------------------------------------------------------------- CPU: boundary and harness
+def test_plugin_exports_registration_symbol():
+    path = os.path.join(ROOT, "ngraph_b200", "libb200_backend.so")
+    if not os.path.exists(path):
+        pytest.skip("plugin not built (needs nGraph headers)")
+    ng.capi()  # libngraph must be in the process before the plugin resolves its symbols
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    assert hasattr(lib, "ngraph_register_b200_backend")
+
+
+@needs_ngraph
+def test_backend_registers_and_fails_loudly_without_a_device():
+    import torch
+    ng.load_b200()
+    assert "B200" in ng.registered_backends()
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    with pytest.raises(ng.NgraphError):
+        ng.Backend("B200")  # no CUDA device: creation raises, nothing falls back to the host
+
+
+@needs_ngraph
+def test_bogus_backend_name_raises():
+    with pytest.raises(ng.NgraphError):
+        ng.Backend("NO_SUCH_BACKEND")
+
+
+@needs_ngraph
+def test_decomposed_oracle_graphs_match_fixtures():
+    """oracle/interpreter.py's decompositions, run on INTERPRETER here, reproduce the committed fixtures."""
+    be = interpreter.backend()
+    for case in interpreter_cases("QuantizedDotBias")[:4]:
+        i = {k: blob(v) for k, v in case["inputs"].items()}
+        exp = blob(case["outputs"]["y"])
+        x, w = ng.parameter(np.uint8, i["data"].shape), ng.parameter(np.int8, i["weights"].shape)
+        b, s = ng.parameter(np.int32, i["bias"].shape), ng.parameter(np.float32, i["scale"].shape)
+        y = interpreter.decomposed_dot_bias(x, w, b, s, exp.dtype, bool(case["attrs"]["relu"]))
+        got = be.compile(ng.Function([y], [x, w, b, s])).run(i["data"], i["weights"], i["bias"], i["scale"])[0]
+        np.testing.assert_array_equal(got.view(np.uint8), exp.view(np.uint8), err_msg=case["name"])
+    for case in interpreter_cases("QuantizedConvolutionBiasAdd")[:2] + interpreter_cases("QuantizedConvolutionBiasSignedAdd")[:1]:
+        i = {k: blob(v) for k, v in case["inputs"].items()}
+        a = case["attrs"]
+        exp = blob(case["outputs"]["y"])
+        d, f = ng.parameter(np.uint8, i["data"].shape), ng.parameter(np.int8, i["filters"].shape)
+        b, s = ng.parameter(np.int32, i["bias"].shape), ng.parameter(np.float32, i["scale"].shape)
+        sm, ss = ng.parameter(i["sum_in"].dtype, i["sum_in"].shape), ng.parameter(np.float32, i["sum_scale"].shape)
+        y = interpreter.decomposed_conv(d, f, b, s, exp.dtype, True, a["stride"], a["dilation"], a["pad_below"], a["pad_above"],
+                                        sum_in=sm, sum_scale=ss, signed=case["op"].endswith("SignedAdd"))
+        got = be.compile(ng.Function([y], [d, f, b, s, sm, ss])).run(i["data"], i["filters"], i["bias"], i["scale"],
+                                                                      i["sum_in"], i["sum_scale"])[0]
+        np.testing.assert_array_equal(got, exp, err_msg=case["name"])
+
+
+# ---------------------------------------------------------------- GPU: B200 vs INTERPRETER, same process
+@pytest.fixture(scope="module")
+def backends():
+    ng.load_b200()
+    return ng.Backend("B200"), interpreter.backend()
+
+
+def run_both(backends, fn_b200, fn_ref, inputs):
+    b200, ref = backends
+    got = b200.compile(fn_b200).run(*inputs)
+    exp = ref.compile(fn_ref).run(*inputs)
+    return got, exp
+
+
+def same_bits(got, exp, msg=""):
+    assert got.dtype == exp.dtype and got.shape == exp.shape, (got.dtype, exp.dtype, got.shape, exp.shape)
+    if got.dtype == np.float32:
+        g, e = np.where(got == 0, 0.0, got).astype(np.float32), np.where(exp == 0, 0.0, exp).astype(np.float32)
+        np.testing.assert_array_equal(g.view(np.uint32), e.view(np.uint32), err_msg=msg)
+    else:
+        np.testing.assert_array_equal(got, exp, err_msg=msg)
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("mode", range(9))
+def test_quantize_dequantize_graph(backends, mode):
+    rng = np.random.default_rng(mode)
+    x = (rng.standard_normal((2, 64, 16, 16)) * 3).astype(np.float32)
+    x.ravel()[::7] = (np.round(x.ravel()[::7] / 0.05) + 0.5) * np.float32(0.05)
+    for dtype, zp, axes in ((np.uint8, 128, ()), (np.int8, 0, ()), (np.uint8, None, (1,)), (np.int8, None, (1,))):
+        ss = tuple(x.shape[a] for a in axes)
+        scale = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=ss)).astype(np.float32) if axes else np.float32(0.05)
+        zpa = np.full(ss, 7, dtype) if zp is None else np.array(zp, dtype)
+        p = ng.parameter(np.float32, x.shape)
+        q = ng.quantize(p, scale, zpa, dtype, axes, mode)
+        dq = ng.dequantize(q, scale, zpa, axes)
+        fn = ng.Function([q, dq], [p])
+        got, exp = run_both(backends, fn, fn, [x])
+        same_bits(got[0], exp[0], "quantize %s %s" % (dtype, axes))
+        same_bits(got[1], exp[1], "dequantize %s %s" % (dtype, axes))
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_dynamic_scale_parameters(backends):
+    """scale and zero point as run-time tensors (test/backend/quantize_dequantize.in.cpp:981-1056)."""
+    x = np.array([0, 3, 128, 255], np.uint8)
+    p, s, z = ng.parameter(np.uint8, (4,)), ng.parameter(np.float32, ()), ng.parameter(np.uint8, ())
+    fn = ng.Function([ng.dequantize(p, s, z)], [p, s, z])
+    got, exp = run_both(backends, fn, fn, [x, np.float32(2), np.uint8(128)])
+    same_bits(got[0], exp[0])
+    np.testing.assert_array_equal(got[0], np.array([-256, -250, 0, 254], np.float32))
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_quantized_dot_core(backends):
+    rng = np.random.default_rng(1)
+    a = rng.integers(0, 256, size=(37, 64)).astype(np.uint8)
+    b = rng.integers(-127, 128, size=(64, 24)).astype(np.int8)
+    for out_dtype, so, zo in ((np.int8, 3000.0, 3), (np.uint8, 2500.0, 90), (np.int32, 0.5, -4)):
+        pa, pb = ng.parameter(np.uint8, a.shape), ng.parameter(np.int8, b.shape)
+        fn = ng.Function([ng.quantized_dot(pa, pb, 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa, pb])
+        got, exp = run_both(backends, fn, fn, [a, b])
+        same_bits(got[0], exp[0], str(out_dtype))
+        # and with B as a Constant (transposed once at compile time)
+        fn2 = ng.Function([ng.quantized_dot(pa, ng.constant(b), 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa])
+        got2 = backends[0].compile(fn2).run(a)
+        same_bits(got2[0], exp[0], "constant B " + str(out_dtype))
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_quantized_dot_bias(backends):
+    rng = np.random.default_rng(2)
+    x = rng.integers(0, 256, size=(50, 128)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(40, 128)).astype(np.int8)
+    bias = rng.integers(-1000, 1000, size=40).astype(np.int32)
+    for per_channel in (False, True):
+        scale = (np.exp(rng.uniform(-1, 1, size=40 if per_channel else 1)) * 3e-4).astype(np.float32)
+        for requant, relu in ((False, False), (False, True), (True, False), (True, True)):
+            out_dtype = (np.uint8 if relu else np.int8) if requant else np.float32
+            px = ng.parameter(np.uint8, x.shape)
+            ps = ng.parameter(np.float32, scale.shape)  # the scale is a run-time tensor
+            fused = ng.Function([ng.quantized_dot_bias(px, w, bias, ps, requant, relu)], [px, ps])
+            px2, ps2 = ng.parameter(np.uint8, x.shape), ng.parameter(np.float32, scale.shape)
+            ref = ng.Function([interpreter.decomposed_dot_bias(px2, ng.constant(w), ng.constant(bias), ps2, out_dtype, relu)],
+                              [px2, ps2])
+            got, exp = run_both(backends, fused, ref, [x, scale])
+            same_bits(got[0], exp[0], "requant %s relu %s" % (requant, relu))
+
+
+CONVS = [
+    # data NCHW, filters KCRS, stride, pad_below, pad_above, dilation
+    ((2, 64, 9, 9), (32, 64, 3, 3), (1, 1), (1, 1), (1, 1), (1, 1)),
+    ((2, 128, 8, 8), (64, 128, 1, 1), (2, 2), (0, 0), (0, 0), (1, 1)),
+    ((1, 64, 11, 10), (16, 64, 3, 3), (2, 2), (1, 1), (1, 1), (1, 1)),
+    ((2, 3, 20, 20), (8, 3, 7, 7), (2, 2), (3, 3), (3, 3), (1, 1)),      # small-channel stem path
+    ((2, 16, 6, 6), (8, 16, 3, 3), (1, 1), (1, 1), (1, 1), (1, 1)),      # channels padded to 64 on the device
+]
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("cfg", CONVS)
+def test_fused_convolutions(backends, cfg):
+    ds, fs, stride, pb, pa, dil = cfg
+    rng = np.random.default_rng(sum(ds) + sum(fs))
+    data = rng.integers(0, 256, size=ds).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=fs).astype(np.int8)
+    bias = rng.integers(-1000, 1000, size=fs[0]).astype(np.int32)
+    sigma = np.sqrt(fs[1] * fs[2] * fs[3]) * 74 * 147
+    geom = dict(stride=stride, dilation=dil, pad_below=pb, pad_above=pa)
+    for per_channel in (False, True):
+        scale = (np.exp(rng.uniform(-0.7, 0.7, size=fs[0] if per_channel else 1)) * 60.0 / sigma).astype(np.float32)
+        for relu in (False, True):
+            out_dtype = np.uint8 if relu else np.int8
+            d = ng.parameter(np.uint8, ds)
+            fused = ng.Function([ng.quantized_conv_bias(d, filt, bias, scale, relu, **geom)], [d])
+            d2 = ng.parameter(np.uint8, ds)
+            ref = ng.Function([interpreter.decomposed_conv(d2, ng.constant(filt), ng.constant(bias), ng.constant(scale),
+                                                           out_dtype, relu, **geom)], [d2])
+            got, exp = run_both(backends, fused, ref, [data])
+            same_bits(got[0], exp[0], "bias relu=%s per_channel=%s" % (relu, per_channel))
+    # QuantizedConvolutionRelu (no bias)
+    d = ng.parameter(np.uint8, ds)
+    fused = ng.Function([ng.quantized_conv_relu(d, filt, scale, **geom)], [d])
+    d2 = ng.parameter(np.uint8, ds)
+    ref = ng.Function([interpreter.decomposed_conv(d2, ng.constant(filt), None, ng.constant(scale), np.uint8, True, **geom)], [d2])
+    got, exp = run_both(backends, fused, ref, [data])
+    same_bits(got[0], exp[0], "conv relu")
+    # BiasAdd (u8 sum) and BiasSignedAdd (i8 sum, i8 result converted to u8 as the builder does)
+    os_ = exp[0].shape
+    for signed in (False, True):
+        sdt = np.int8 if signed else np.uint8
+        s_in = rng.integers(np.iinfo(sdt).min, np.iinfo(sdt).max + 1, size=os_).astype(sdt)
+        ssc = np.array([0.73], np.float32)
+        d, sm = ng.parameter(np.uint8, ds), ng.parameter(sdt, os_)
+        y = ng.quantized_conv_bias_add(d, filt, bias, sm, scale, ssc, True, signed, **geom)
+        if signed:
+            y = ng.convert(y, np.uint8)
+        fused = ng.Function([y], [d, sm])
+        d2, sm2 = ng.parameter(np.uint8, ds), ng.parameter(sdt, os_)
+        ref = ng.Function([interpreter.decomposed_conv(d2, ng.constant(filt), ng.constant(bias), ng.constant(scale), np.uint8, True,
+                                                       sum_in=sm2, sum_scale=ng.constant(ssc), signed=signed, **geom)], [d2, sm2])
+        got, exp2 = run_both(backends, fused, ref, [data, s_in])
+        same_bits(got[0], exp2[0], "add signed=%s" % signed)
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_core_quantized_convolution(backends):
+    rng = np.random.default_rng(5)
+    ds, fs = (2, 64, 7, 7), (24, 64, 3, 3)
+    data = rng.integers(0, 256, size=ds).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=fs).astype(np.int8)
+    for out_dtype, so, zo in ((np.int32, 1.0, 0), (np.int8, 4000.0, 2), (np.uint8, 4000.0, 100)):
+        d, f = ng.parameter(np.uint8, ds), ng.parameter(np.int8, fs)
+        fn = ng.Function([ng.quantized_convolution(d, f, 1.0, 0, 1.0, 0, so, zo, out_dtype, pad_below=(1, 1))], [d, f])
+        got, exp = run_both(backends, fn, fn, [data, filt])
+        same_bits(got[0], exp[0], str(out_dtype))
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_small_network_with_pooling_head(backends):
+    """Quantize -> conv+relu -> maxpool -> conv+add+relu -> Dequantize/AvgPool/Quantize head -> QuantizedDot -> Dequantize:
+    the shape of the int8 ResNet graphs, end to end through both backends."""
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((4, 64, 12, 12)).astype(np.float32)
+    w1 = rng.integers(-127, 128, size=(64, 64, 3, 3)).astype(np.int8)
+    w2 = rng.integers(-127, 128, size=(64, 64, 1, 1)).astype(np.int8)
+    b1 = rng.integers(-500, 500, size=64).astype(np.int32)
+    s1 = (np.exp(rng.uniform(-0.5, 0.5, size=64)) * 2e-4).astype(np.float32)
+    s2 = (np.exp(rng.uniform(-0.5, 0.5, size=64)) * 6e-4).astype(np.float32)
+    wd = rng.integers(-127, 128, size=(64, 10)).astype(np.int8)
+
+    def build(fused):
+        p = ng.parameter(np.float32, x.shape)
+        q = ng.quantize(p, np.float32(0.02), np.uint8(0), np.uint8)
+        if fused:
+            c1 = ng.quantized_conv_bias(q, w1, b1, s1, True, pad_below=(1, 1))
+        else:
+            c1 = interpreter.decomposed_conv(q, ng.constant(w1), ng.constant(b1), ng.constant(s1), np.uint8, True, pad_below=(1, 1))
+        mp = ng.max_pool(c1, (3, 3), (2, 2), (1, 1))
+        if fused:
+            c2 = ng.quantized_conv_bias_add(mp, w2, b1, mp, s2, np.array([0.5], np.float32), True, False)
+        else:
+            c2 = interpreter.decomposed_conv(mp, ng.constant(w2), ng.constant(b1), ng.constant(s2), np.uint8, True, sum_in=mp,
+                                             sum_scale=ng.constant(np.array([0.5], np.float32)))
+        hw = c2.shape[2:]
+        pooled = ng.quantize(ng.avg_pool(ng.dequantize(c2, np.float32(0.05), np.uint8(0)), hw), np.float32(0.04), np.uint8(0), np.uint8)
+        flat = ng.reshape(pooled, (0, 1, 2, 3), (x.shape[0], 64))
+        logits = ng.quantized_dot(flat, ng.constant(wd), 0.04, 0, 0.01, 0, 0.5, 0, np.int8)
+        return ng.Function([ng.dequantize(logits, np.float32(0.5), np.int8(0)), c2], [p])
+
+    got, exp = run_both(backends, build(True), build(False), [x])
+    same_bits(got[1], exp[1], "feature map")
+    same_bits(got[0], exp[0], "logits")
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_api_contract(backends):
+    """create_tensor / validate / foreign tensors / unsupported ops (test/backend/api.in.cpp,
+    validate_call.in.cpp, unhandled_op.in.cpp restated)."""
+    b200, ref = backends
+    p = ng.parameter(np.float32, (2, 3))
+    fn = ng.Function([ng.quantize(p, np.float32(1), np.uint8(0), np.uint8)], [p])
+    exe = b200.compile(fn)
+    good_in, good_out = b200.create_tensor(np.float32, (2, 3)), b200.create_tensor(np.uint8, (2, 3))
+    good_in.write(np.arange(6, dtype=np.float32))
+    exe.call([good_out], [good_in])
+    np.testing.assert_array_equal(good_out.read().ravel(), np.arange(6, dtype=np.uint8))
+    with pytest.raises(ng.NgraphError):  # wrong input count
+        exe.call([good_out], [good_in, good_in])
+    with pytest.raises(ng.NgraphError):  # wrong input type
+        exe.call([good_out], [b200.create_tensor(np.int32, (2, 3))])
+    with pytest.raises(ng.NgraphError):  # wrong input shape
+        exe.call([good_out], [b200.create_tensor(np.float32, (3, 2))])
+    with pytest.raises(ng.NgraphError):  # wrong output type
+        exe.call([b200.create_tensor(np.float32, (2, 3))], [good_in])
+    with pytest.raises(ng.NgraphError):  # a tensor created by another backend
+        exe.call([good_out], [ref.create_tensor(np.float32, (2, 3))])
+    with pytest.raises(ng.NgraphError):  # an op outside the quantized path is rejected at compile, no host fallback
+        q = ng.parameter(np.float32, (4,))
+        b200.compile(ng.Function([ng.relu(q)], [q]))
+    # per-node performance counters
+    exe2 = b200.compile(ng.Function([ng.quantize(p, np.float32(1), np.uint8(0), np.uint8)], [p]), perf=True)
+    exe2.call([good_out], [good_in])
+    names = [n for n, us, calls in exe2.performance_data()]
+    assert any(n.startswith("Quantize") for n in names)
