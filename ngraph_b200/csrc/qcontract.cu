@@ -28,6 +28,17 @@
 
 namespace b200
 {
+#ifdef B200_PROFILE_WAITS
+    // debug build only: wait cycles per role of CTA 0 ([0] producer/empty, [1] mma/full, [2] mma/tempty,
+    // [3] epilogue/tfull, [4] epilogue body, [5] kernel total, [6] tiles of CTA 0)
+    __device__ long long g_wait_cycles[8];
+#define PROF_T0() long long prof_t0 = clock64()
+#define PROF_ADD(i) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[i]), (unsigned long long)(clock64() - prof_t0)); } while (0)
+#else
+#define PROF_T0() do { } while (0)
+#define PROF_ADD(i) do { } while (0)
+#endif
+
     __device__ int g_contract_status = 0; // 0 ok; otherwise 1000*role + detail of the wait that gave up
 
     struct ContractParams
@@ -154,6 +165,9 @@ namespace b200
 
         const int num_tiles = p.tiles_m * p.tiles_n;
         int fail = 0;
+#ifdef B200_PROFILE_WAITS
+        const long long prof_kernel_t0 = clock64();
+#endif
 
         if (warp == 0)
         {
@@ -179,11 +193,13 @@ namespace b200
                     {
                         const int s = it % C::STAGES;
                         const uint32_t ph = (it / C::STAGES) & 1;
+                        PROF_T0();
                         if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
                         {
                             fail = 1001;
                             break;
                         }
+                        PROF_ADD(0);
                         const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
                         const uint32_t b_dst = a_dst + C::A_BYTES;
                         ptx::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
@@ -216,10 +232,14 @@ namespace b200
                 {
                     const int acc = tile_it & 1;
                     const uint32_t acc_ph = (tile_it >> 1) & 1;
-                    if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp))
                     {
-                        fail = 2001;
-                        break;
+                        PROF_T0();
+                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp))
+                        {
+                            fail = 2001;
+                            break;
+                        }
+                        PROF_ADD(2);
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
@@ -227,10 +247,14 @@ namespace b200
                     {
                         const int s = it % C::STAGES;
                         const uint32_t ph = (it / C::STAGES) & 1;
-                        if (!ptx::mbar_wait(full_bar(s), ph, abortp))
                         {
-                            fail = 2002;
-                            break;
+                            PROF_T0();
+                            if (!ptx::mbar_wait(full_bar(s), ph, abortp))
+                            {
+                                fail = 2002;
+                                break;
+                            }
+                            PROF_ADD(1);
                         }
                         ptx::tc_fence_after_sync();
                         const uint32_t a_src = smem_base + s * C::STAGE_BYTES;
@@ -301,12 +325,18 @@ namespace b200
                     er.valid = m < p.M;
                     er.off = int64_t(m) * p.N;
                 }
-                if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp))
                 {
-                    fail = 3001;
-                    break;
+                    PROF_T0();
+                    if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp))
+                    {
+                        fail = 3001;
+                        break;
+                    }
+                    if (warp == 2 && lane == 0)
+                        PROF_ADD(3);
                 }
                 ptx::tc_fence_after_sync();
+                PROF_T0();
 #pragma unroll 1
                 for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32)
                 {
@@ -426,6 +456,14 @@ namespace b200
                         }
                     }
                 }
+                if (warp == 2 && lane == 0)
+                {
+                    PROF_ADD(4);
+#ifdef B200_PROFILE_WAITS
+                    if (blockIdx.x == 0)
+                        atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[6]), 1ull);
+#endif
+                }
                 // all of this warp's TMEM reads are done: hand the accumulator back
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -435,6 +473,10 @@ namespace b200
         }
 
         // ------------------------------------------------------------ common tail
+#ifdef B200_PROFILE_WAITS
+        if (blockIdx.x == 0 && threadIdx.x == 0)
+            atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[5]), (unsigned long long)(clock64() - prof_kernel_t0));
+#endif
         if (fail)
             atomicCAS(&g_contract_status, 0, fail);
         __syncwarp();
@@ -603,6 +645,18 @@ namespace b200
         return (tiles256 >= 2 * num_sms() && n_out % 256 == 0) ? 256 : 128;
     }
 }
+
+#ifdef B200_PROFILE_WAITS
+extern "C" __attribute__((visibility("default"))) int b200_debug_wait_cycles(long long* out8, int reset)
+{
+    long long z[8] = {0};
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out8, b200::g_wait_cycles, sizeof(z));
+    if (reset)
+        cudaMemcpyToSymbol(b200::g_wait_cycles, z, sizeof(z));
+    return 0;
+}
+#endif
 
 extern "C" int b200_device_status(int* status_out)
 {

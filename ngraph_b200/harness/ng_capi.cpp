@@ -190,6 +190,15 @@ NGC_API void* ngc_quantized_conv_relu(void* data, void* filt, const int64_t* g, 
     }, nullptr);
 }
 
+NGC_API void* ngc_convolution(void* data, void* filt, const int64_t* g)
+{
+    return guarded([&]() -> void* {
+        Geom gg = geom_of(g);
+        return box(std::make_shared<op::v0::Convolution>(val(data), val(filt), gg.strides, gg.dilation, gg.below, gg.above,
+                                                         Strides{1, 1}));
+    }, nullptr);
+}
+
 NGC_API void* ngc_max_pool(void* x, const int64_t* win, const int64_t* stride, const int64_t* below, const int64_t* above)
 {
     return guarded([&]() -> void* {

@@ -7,7 +7,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200_kernels.so")
+LIB_PATH = os.environ.get("B200_KERNELS_LIB", os.path.join(HERE, "libb200_kernels.so"))
 
 U8, I8, I32, F32 = 0, 1, 2, 3
 

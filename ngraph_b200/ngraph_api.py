@@ -45,6 +45,7 @@ def capi():
             "ngc_quantized_conv_bias": (vp, [vp, vp, vp, p64, vp, ci]),
             "ngc_quantized_conv_bias_add": (vp, [vp, vp, vp, vp, p64, vp, vp, ci, ci]),
             "ngc_quantized_conv_relu": (vp, [vp, vp, p64, vp]),
+            "ngc_convolution": (vp, [vp, vp, p64]),
             "ngc_max_pool": (vp, [vp, p64, p64, p64, p64]), "ngc_avg_pool": (vp, [vp, p64, p64]),
             "ngc_convert": (vp, [vp, ci]), "ngc_reshape": (vp, [vp, p64, ci, p64, ci]), "ngc_relu": (vp, [vp]),
             "ngc_add": (vp, [vp, vp]), "ngc_multiply": (vp, [vp, vp]), "ngc_dot": (vp, [vp, vp, i64]),
@@ -189,6 +190,11 @@ def quantized_conv_relu(data, filt, scale, stride=(1, 1), dilation=(1, 1), pad_b
     filt, scale = _val(filt), _val(scale, np.float32)
     return Value(capi().ngc_quantized_conv_relu(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above), scale.h),
                  "QuantizedConvolutionRelu")
+
+
+def convolution(data, filt, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None):
+    filt = _val(filt)
+    return Value(capi().ngc_convolution(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above)), "Convolution")
 
 
 def max_pool(x, window, stride, pad_below=(0, 0), pad_above=None):

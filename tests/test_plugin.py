@@ -128,10 +128,11 @@ def test_dynamic_scale_parameters(backends):
 @pytest.mark.gpu
 @needs_ngraph
 def test_quantized_dot_core(backends):
+    # INTERPRETER implements u8 x i8 -> i8 and -> i32 only (int_executable.hpp:1573-1644)
     rng = np.random.default_rng(1)
     a = rng.integers(0, 256, size=(37, 64)).astype(np.uint8)
     b = rng.integers(-127, 128, size=(64, 24)).astype(np.int8)
-    for out_dtype, so, zo in ((np.int8, 3000.0, 3), (np.uint8, 2500.0, 90), (np.int32, 0.5, -4)):
+    for out_dtype, so, zo in ((np.int8, 3000.0, 3), (np.int32, 0.5, -4)):
         pa, pb = ng.parameter(np.uint8, a.shape), ng.parameter(np.int8, b.shape)
         fn = ng.Function([ng.quantized_dot(pa, pb, 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa, pb])
         got, exp = run_both(backends, fn, fn, [a, b])
@@ -227,7 +228,7 @@ def test_core_quantized_convolution(backends):
     ds, fs = (2, 64, 7, 7), (24, 64, 3, 3)
     data = rng.integers(0, 256, size=ds).astype(np.uint8)
     filt = rng.integers(-127, 128, size=fs).astype(np.int8)
-    for out_dtype, so, zo in ((np.int32, 1.0, 0), (np.int8, 4000.0, 2), (np.uint8, 4000.0, 100)):
+    for out_dtype, so, zo in ((np.int32, 1.0, 0), (np.int8, 12000.0, 2), (np.uint8, 12000.0, 100)):  # in range: the reference wraps
         d, f = ng.parameter(np.uint8, ds), ng.parameter(np.int8, fs)
         fn = ng.Function([ng.quantized_convolution(d, f, 1.0, 0, 1.0, 0, so, zo, out_dtype, pad_below=(1, 1))], [d, f])
         got, exp = run_both(backends, fn, fn, [data, filt])
