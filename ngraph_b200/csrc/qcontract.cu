@@ -15,8 +15,12 @@
 //   maps over the s-strided pixel sub-lattices of the input (no element strides, no gather).
 //   The filter [K,R,S,C] is a plain [K, R*S*C] row-major matrix, so B tiles are 2-D boxes.
 // * warp 0: TMA producer; warp 1: TMEM allocation + MMA issue (one elected thread);
-//   warps 2-9: epilogue (tcgen05.ld -> bias/scale/sum/ReLU/round/saturate -> global).
-//   Two TMEM accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.
+//   warps 2-9: epilogue.  Two TMEM accumulator buffers let the epilogue of tile i overlap the
+//   MMAs of tile i+1.  Each epilogue warp owns 32 accumulator rows (its TMEM lane quarter) and
+//   half of the tile's columns: tcgen05.ld -> bias/scale/sum/ReLU/round/saturate in registers ->
+//   (one-byte outputs) a swizzled shared-memory staging block of its own -> one TMA store, so
+//   global writes are whole lines and rows/columns outside the tensor are clipped by the TMA
+//   unit.  Four-byte outputs and ragged widths are written straight from registers.
 // * Every wait is bounded (ptx::mbar_wait); a timeout sets g_contract_status, the CTA
 //   drains and frees its TMEM, and the host reports B200_ERR_DEVICE_STATUS.
 #include <cuda.h>
@@ -41,18 +45,26 @@ namespace b200
 
     __device__ int g_contract_status = 0; // 0 ok; otherwise 1000*role + detail of the wait that gave up
 
+    constexpr int MAX_TAPS = 64;
+
+    struct Tap // one filter tap of the convolution, resolved on the host
+    {
+        short dh, dw; // displacement of the input patch, in pixels of the tap's sub-lattice
+        short map;    // which sub-lattice tensor map
+        short pad;
+    };
+
     struct ContractParams
     {
-        int M, N;           // GEMM rows (conv: unused) and output channels
-        int num_kblocks;
+        int M, N;            // GEMM rows (conv: unused) and output channels
         int tiles_m, tiles_n;
+        int ntaps, cblocks;  // k-blocks = ntaps * cblocks (GEMM: 1 tap)
         // convolution
         int conv;
-        int S, cblocks;     // filter width, channel blocks per tap
-        int dil_h, dil_w, pad_h, pad_w, stride_h, stride_w;
-        int TW, TH, TN;     // output patch covered by one tile (TW*TH*TN == 128)
+        int TW, TH, TN;      // output patch covered by one tile (TW*TH*TN == 128)
         int tiles_q, tiles_p; // patches along Q and P (tiles_m = tiles_q*tiles_p*ceil(NB/TN))
-        int NB, P, Q;       // batch and output spatial size
+        int NB, P, Q;        // batch and output spatial size
+        int sub_w, sub_h;    // 32 consecutive tile rows as a sub-patch: sub_w x sub_h x (32/(sub_w*sub_h))
         // epilogue
         const int32_t* bias;
         const float* scale;
@@ -61,18 +73,23 @@ namespace b200
         int sum_type;
         const float* sum_scale;
         int relu, half_away, out_zp, out_type;
+        int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
+        int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
         uint32_t idesc;
+        Tap taps[MAX_TAPS];
     };
 
     struct TensorMaps
     {
         CUtensorMap a[4]; // GEMM: a[0] (2-D).  Conv: one 4-D map per (h parity, w parity) sub-lattice
         CUtensorMap b;
+        CUtensorMap out;  // used when ContractParams::tma_store
     };
 
     constexpr int BM = 128;
     constexpr int NUM_THREADS = 320; // producer warp, MMA warp, 8 epilogue warps
+    constexpr int SMEM_LIMIT = 232448; // 227 KB per CTA
 
     template <int BN, int BK>
     struct Cfg
@@ -80,16 +97,13 @@ namespace b200
         static constexpr int A_BYTES = BM * BK;
         static constexpr int B_BYTES = BN * BK;
         static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-        static constexpr int STAGES = (196608 / STAGE_BYTES) > 8 ? 8 : (196608 / STAGE_BYTES);
+        static constexpr int OUT_BYTES = BM * BN;      // 8 staging blocks of 32 rows x BN/2 bytes
+        static constexpr int FIXED = OUT_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+        static constexpr int FIT = (SMEM_LIMIT - FIXED - 64) / STAGE_BYTES;
+        static constexpr int STAGES = FIT > 8 ? 8 : FIT;
         static constexpr int TMEM_COLS = 2 * BN;
-        static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+        static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED;
     };
-
-    __device__ __forceinline__ int floor_div(int a, int b)
-    {
-        int q = a / b;
-        return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q;
-    }
 
     // ---- epilogue arithmetic ----------------------------------------------------------------
     __device__ __forceinline__ float load_sum(const void* p, int type, int64_t i)
@@ -97,12 +111,6 @@ namespace b200
         return type == B200_U8 ? static_cast<float>(static_cast<const uint8_t*>(p)[i])
                                : static_cast<float>(static_cast<const int8_t*>(p)[i]);
     }
-
-    struct EpiRow
-    {
-        bool valid;
-        int64_t off; // element offset of column 0 of this row in out / sum_in
-    };
 
     // Core requantisation of one accumulator (reference::dot / convolution, dot.hpp:152-159):
     // (OUT)round(float(acc) * scale) + zero_point, saturated.  Returns the integer as raw 32 bits.
@@ -116,19 +124,151 @@ namespace b200
         return (r != r) ? 0u : static_cast<uint32_t>(static_cast<int32_t>(v));
     }
 
+    // four int32 -> four saturated bytes, v0 in the lowest byte
+    __device__ __forceinline__ uint32_t pack4_u8(int v0, int v1, int v2, int v3)
+    {
+        uint32_t t, d;
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(t) : "r"(v3), "r"(v2));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(t));
+        return d;
+    }
+    __device__ __forceinline__ uint32_t pack4_s8(int v0, int v1, int v2, int v3)
+    {
+        uint32_t t, d;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(t) : "r"(v3), "r"(v2));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(t));
+        return d;
+    }
+
+    struct EpiRow
+    {
+        bool valid;
+        int64_t off; // element offset of column 0 of this row in out / sum_in
+    };
+
+    // One 32-column chunk of one accumulator row: v[] holds the int32 accumulators on entry and the
+    // output values on return (f32 bit patterns / int32), w[] the packed bytes for one-byte outputs.
+    __device__ __forceinline__ void epilogue_chunk(const ContractParams& p, uint32_t (&v)[32], uint32_t (&w)[8], int col0,
+                                                   bool full_chunk, bool has_sum, const uint32_t* sumw, bool sum_regs,
+                                                   float sum_scale, const EpiRow& er)
+    {
+        if (p.half_away)
+        {
+            const float sc = __ldg(p.scale);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v[j] = epilogue_core(p, int32_t(v[j]), sc);
+            if (p.out_type != B200_I32)
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    w[j] = (v[4 * j] & 0xFF) | ((v[4 * j + 1] & 0xFF) << 8) | ((v[4 * j + 2] & 0xFF) << 16) | ((v[4 * j + 3] & 0xFF) << 24);
+            }
+            return;
+        }
+        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu]
+        float f[32];
+        if (full_chunk && p.vec_params)
+        {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4)
+            {
+                const float4 s4 = p.scale_per_channel ? __ldg(reinterpret_cast<const float4*>(p.scale + col0) + j4)
+                                                      : make_float4(__ldg(p.scale), __ldg(p.scale), __ldg(p.scale), __ldg(p.scale));
+                const int4 b4 = p.bias ? __ldg(reinterpret_cast<const int4*>(p.bias + col0) + j4) : make_int4(0, 0, 0, 0);
+                f[4 * j4 + 0] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
+                f[4 * j4 + 1] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
+                f[4 * j4 + 2] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
+                f[4 * j4 + 3] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+            {
+                const int cc = (col0 + j < p.N) ? col0 + j : 0;
+                const int32_t b = p.bias ? __ldg(p.bias + cc) : 0;
+                const float sc = __ldg(p.scale + (p.scale_per_channel ? cc : 0));
+                f[j] = __fmul_rn(__int2float_rn(int32_t(v[j]) + b), sc);
+            }
+        }
+        if (has_sum && er.valid)
+        {
+            if (sum_regs)
+            {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                {
+                    const uint32_t byte = (sumw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+                    const float sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
+                    f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, sv));
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N)
+                        f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, load_sum(p.sum_in, p.sum_type, er.off + col0 + j)));
+            }
+        }
+        if (p.relu)
+        {
+            // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0); the sign of a zero result does not
+            // survive the conversions below and is normalised by the f32 comparison in the tests
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                f[j] = fmaxf(f[j], 0.0f);
+        }
+        if (p.out_type == B200_F32)
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v[j] = __float_as_uint(f[j]);
+        }
+        else if (p.out_type == B200_I32)
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v[j] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[j])));
+        }
+        else
+        {
+            // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) /
+            // ceil(v-0.5) / parity sequence equals round-half-even for |v| < 2^23 and everything beyond
+            // saturates, so cvt.rni (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
+            if (p.out_type == B200_U8)
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    w[j] = pack4_u8(__float2int_rn(f[4 * j]), __float2int_rn(f[4 * j + 1]), __float2int_rn(f[4 * j + 2]),
+                                    __float2int_rn(f[4 * j + 3]));
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    w[j] = pack4_s8(__float2int_rn(f[4 * j]), __float2int_rn(f[4 * j + 1]), __float2int_rn(f[4 * j + 2]),
+                                    __float2int_rn(f[4 * j + 3]));
+            }
+        }
+    }
+
     template <int BN, int BK>
     __global__ void __launch_bounds__(NUM_THREADS, 1)
         qcontract_kernel(const __grid_constant__ TensorMaps maps, const __grid_constant__ ContractParams p)
     {
         using C = Cfg<BN, BK>;
+        constexpr int HALF = BN / 2;       // columns (= bytes of a one-byte output row) per epilogue warp
+        constexpr int CHUNKS = HALF / 32;  // 32-column chunks per epilogue warp
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
-        __shared__ __align__(16) float epi_scale[8][BN / 2];   // per epilogue warp: its column half of the tile
-        __shared__ __align__(16) int32_t epi_bias[8][BN / 2];
 
         const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-        const uint32_t bars = smem_base + C::STAGES * C::STAGE_BYTES;
+        const uint32_t out_base = smem_base + C::STAGES * C::STAGE_BYTES; // 1024-aligned: STAGE_BYTES is a multiple of 1024
+        const uint32_t bars = out_base + C::OUT_BYTES;
         auto full_bar = [&](int s) { return bars + 8u * s; };
         auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
         auto tfull_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
@@ -176,7 +316,8 @@ namespace b200
             {
                 ptx::prefetch_tmap(&maps.b);
                 ptx::prefetch_tmap(&maps.a[0]);
-                uint32_t it = 0;
+                int s = 0;
+                uint32_t ph = 0;
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
                 {
                     const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -189,35 +330,34 @@ namespace b200
                         p0 = (t % p.tiles_p) * p.TH;
                         n0 = (t / p.tiles_p) * p.TN;
                     }
-                    for (int kb = 0; kb < p.num_kblocks; ++kb, ++it)
+                    int kcol = 0; // byte column of the k-block in the B matrix
+                    for (int tap = 0; tap < p.ntaps && !fail; ++tap)
                     {
-                        const int s = it % C::STAGES;
-                        const uint32_t ph = (it / C::STAGES) & 1;
-                        PROF_T0();
-                        if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
+                        const Tap tp = p.taps[tap];
+                        const CUtensorMap* amap = &maps.a[tp.map];
+                        for (int cb = 0; cb < p.cblocks; ++cb, kcol += BK)
                         {
-                            fail = 1001;
-                            break;
+                            PROF_T0();
+                            if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
+                            {
+                                fail = 1001;
+                                break;
+                            }
+                            PROF_ADD(0);
+                            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+                            const uint32_t b_dst = a_dst + C::A_BYTES;
+                            ptx::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                            if (p.conv)
+                                ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
+                            else
+                                ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
+                            ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                            if (++s == C::STAGES)
+                            {
+                                s = 0;
+                                ph ^= 1;
+                            }
                         }
-                        PROF_ADD(0);
-                        const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
-                        const uint32_t b_dst = a_dst + C::A_BYTES;
-                        ptx::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-                        if (p.conv)
-                        {
-                            const int rs = kb / p.cblocks, cb = kb - rs * p.cblocks;
-                            const int r = rs / p.S, sx = rs - r * p.S;
-                            const int off_h = r * p.dil_h - p.pad_h, off_w = sx * p.dil_w - p.pad_w;
-                            const int dh = floor_div(off_h, p.stride_h), dw = floor_div(off_w, p.stride_w);
-                            const int par_h = off_h - dh * p.stride_h, par_w = off_w - dw * p.stride_w;
-                            ptx::tma_load_4d(a_dst, &maps.a[par_h * p.stride_w + par_w], full_bar(s), cb * BK, q0 + dw,
-                                             p0 + dh, n0);
-                        }
-                        else
-                        {
-                            ptx::tma_load_2d(a_dst, &maps.a[0], full_bar(s), kb * BK, tm * BM);
-                        }
-                        ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kb * BK, tn * BN);
                     }
                 }
             }
@@ -227,7 +367,11 @@ namespace b200
             // ------------------------------------------------------------ MMA issuer
             if (ptx::elect_one())
             {
-                uint32_t it = 0, tile_it = 0;
+                int s = 0;
+                uint32_t ph = 0, tile_it = 0;
+                const int num_kblocks = p.ntaps * p.cblocks;
+                const uint64_t a_desc0 = ptx::smem_desc_kmajor(smem_base, BK);
+                const uint64_t b_desc0 = ptx::smem_desc_kmajor(smem_base + C::A_BYTES, BK);
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
                     const int acc = tile_it & 1;
@@ -243,10 +387,8 @@ namespace b200
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    for (int kb = 0; kb < p.num_kblocks; ++kb, ++it)
+                    for (int kb = 0; kb < num_kblocks; ++kb)
                     {
-                        const int s = it % C::STAGES;
-                        const uint32_t ph = (it / C::STAGES) & 1;
                         {
                             PROF_T0();
                             if (!ptx::mbar_wait(full_bar(s), ph, abortp))
@@ -257,10 +399,9 @@ namespace b200
                             PROF_ADD(1);
                         }
                         ptx::tc_fence_after_sync();
-                        const uint32_t a_src = smem_base + s * C::STAGE_BYTES;
-                        const uint32_t b_src = a_src + C::A_BYTES;
-                        const uint64_t a_desc = ptx::smem_desc_kmajor(a_src, BK);
-                        const uint64_t b_desc = ptx::smem_desc_kmajor(b_src, BK);
+                        // stage s starts s*STAGE_BYTES further on: the descriptor's address field counts 16-byte units
+                        const uint64_t a_desc = a_desc0 + uint64_t(s) * (C::STAGE_BYTES >> 4);
+                        const uint64_t b_desc = b_desc0 + uint64_t(s) * (C::STAGE_BYTES >> 4);
 #pragma unroll
                         for (int k = 0; k < BK / 32; ++k)
                         {
@@ -269,6 +410,11 @@ namespace b200
                                         (kb | k) != 0 ? 1u : 0u);
                         }
                         ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
+                        if (++s == C::STAGES)
+                        {
+                            s = 0;
+                            ph ^= 1;
+                        }
                     }
                     if (fail)
                         break;
@@ -289,31 +435,27 @@ namespace b200
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
+            // this warp's staging block: 32 rows x HALF bytes, swizzled like the TMA store expects
+            const uint32_t stage_blk = out_base + uint32_t(warp - 2) * (32 * HALF);
+            const uint32_t sw_xor = HALF == 128 ? uint32_t(lane & 7) : HALF == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
+            const uint32_t stage_row = stage_blk + uint32_t(lane) * HALF;
+            bool store_pending = false;
             uint32_t tile_it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
             {
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int acc = tile_it & 1;
                 const uint32_t acc_ph = (tile_it >> 1) & 1;
-                // stage this warp's share of the tile's per-channel scale and bias (warp-private buffer,
-                // so a warp-level sync is all the ordering it needs)
-                __syncwarp();
-                for (int j = lane; j < BN / 2; j += 32)
-                {
-                    const int col = tn * BN + half * (BN / 2) + j;
-                    const bool in_n = col < p.N;
-                    epi_scale[warp - 2][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
-                    epi_bias[warp - 2][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
-                }
-                __syncwarp();
+                const int colw = tn * BN + half * HALF; // first output column of this warp
                 EpiRow er;
+                int q0 = 0, p0 = 0, n0 = 0;
                 if (p.conv)
                 {
                     int t = tm;
-                    const int q0 = (t % p.tiles_q) * p.TW;
+                    q0 = (t % p.tiles_q) * p.TW;
                     t /= p.tiles_q;
-                    const int p0 = (t % p.tiles_p) * p.TH;
-                    const int n0 = (t / p.tiles_p) * p.TN;
+                    p0 = (t % p.tiles_p) * p.TH;
+                    n0 = (t / p.tiles_p) * p.TN;
                     const int tw = row % p.TW, th = (row / p.TW) % p.TH, tnn = row / (p.TW * p.TH);
                     const int q = q0 + tw, pp = p0 + th, n = n0 + tnn;
                     er.valid = q < p.Q && pp < p.P && n < p.NB;
@@ -324,6 +466,23 @@ namespace b200
                     const int m = tm * BM + row;
                     er.valid = m < p.M;
                     er.off = int64_t(m) * p.N;
+                }
+                // the residual does not depend on the accumulator: fetch it before waiting for the MMAs
+                uint32_t sumw[CHUNKS][8];
+                const bool sum_regs = has_sum && vec_ok && er.valid;
+                if (sum_regs)
+                {
+#pragma unroll
+                    for (int c = 0; c < CHUNKS; ++c)
+                    {
+                        if (colw + 32 * c + 32 <= p.N)
+                        {
+                            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
+                            const uint4 s0 = sp[0], s1 = sp[1];
+                            sumw[c][0] = s0.x; sumw[c][1] = s0.y; sumw[c][2] = s0.z; sumw[c][3] = s0.w;
+                            sumw[c][4] = s1.x; sumw[c][5] = s1.y; sumw[c][6] = s1.z; sumw[c][7] = s1.w;
+                        }
+                    }
                 }
                 {
                     PROF_T0();
@@ -337,122 +496,66 @@ namespace b200
                 }
                 ptx::tc_fence_after_sync();
                 PROF_T0();
-#pragma unroll 1
-                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32)
+                if (store_pending)
                 {
-                    uint32_t v[32];
+                    // the previous tile's TMA store must have finished reading the staging block
+                    if (lane == 0)
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     __syncwarp();
-                    ptx::tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c0, v);
+                    store_pending = false;
+                }
+                const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * HALF;
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c)
+                {
+                    uint32_t v[32], w[8];
+                    __syncwarp();
+                    ptx::tmem_ld_32x32(t_addr + 32 * c, v);
                     ptx::tmem_ld_wait();
-                    const int col0 = tn * BN + c0;
-                    if (col0 >= p.N)
-                        continue; // warp-uniform
-                    const bool full_chunk = col0 + 32 <= p.N;
-                    const bool fast = full_chunk && vec_ok;
-                    const float* sc = &epi_scale[warp - 2][c0 - half * (BN / 2)];
-                    const int32_t* bi = &epi_bias[warp - 2][c0 - half * (BN / 2)];
-                    if (p.half_away)
+                    const int col0 = colw + 32 * c;
+                    if (col0 < p.N) // warp-uniform
                     {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            v[j] = epilogue_core(p, int32_t(v[j]), sc[j]);
-                    }
-                    else
-                    {
-                        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu]
-                        float f[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            f[j] = __fmul_rn(__int2float_rn(int32_t(v[j]) + bi[j]), sc[j]);
-                        if (has_sum && er.valid)
+                        const bool full_chunk = col0 + 32 <= p.N;
+                        epilogue_chunk(p, v, w, col0, full_chunk, has_sum, sumw[c], sum_regs && full_chunk, sum_scale, er);
+                        if (p.tma_store)
                         {
-                            if (fast)
+                            // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
+                            const uint32_t c16 = uint32_t(2 * c);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((c16 ^ sw_xor) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((c16 + 1) ^ sw_xor) << 4)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        }
+                        else if (er.valid && esz == 1)
+                        {
+                            uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
+                            if (full_chunk && vec_ok)
                             {
-                                const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + col0);
-                                const uint4 s0 = sp[0], s1 = sp[1];
-                                const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                {
-                                    const uint32_t byte = (sw[j >> 2] >> (8 * (j & 3))) & 0xFF;
-                                    const float sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
-                                    f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, sv));
-                                }
+                                reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
                             }
                             else
                             {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
                                     if (col0 + j < p.N)
-                                        f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, load_sum(p.sum_in, p.sum_type, er.off + col0 + j)));
+                                        op[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
                             }
                         }
-                        if (p.relu)
+                        else if (er.valid)
                         {
+                            uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
+                            if (full_chunk && vec_ok)
+                            {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                f[j] = (f[j] > 0.0f) ? f[j] : 0.0f; // reference::relu; NaN -> 0 as there
-                        }
-                        if (p.out_type == B200_F32)
-                        {
+                                for (int j = 0; j < 8; ++j)
+                                    reinterpret_cast<uint4*>(op)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            }
+                            else
+                            {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                v[j] = __float_as_uint(f[j]);
-                        }
-                        else if (p.out_type == B200_I32)
-                        {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                v[j] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[j])));
-                        }
-                        else
-                        {
-                            // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal
-                            // floor(v+0.5)/ceil(v-0.5)/parity sequence equals round-to-nearest-even for
-                            // |v| < 2^23 and everything beyond saturates, so one saturating cvt.rni
-                            // (NaN -> 0) followed by the integer clamp gives the same byte.
-                            const int lo = p.out_type == B200_U8 ? 0 : -128, hi = p.out_type == B200_U8 ? 255 : 127;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                v[j] = uint32_t(min(max(__float2int_rn(f[j]), lo), hi));
-                        }
-                    }
-                    if (er.valid && esz == 1)
-                    {
-                        uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
-                        if (fast)
-                        {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                w[j] = (v[4 * j] & 0xFF) | ((v[4 * j + 1] & 0xFF) << 8) | ((v[4 * j + 2] & 0xFF) << 16) |
-                                       ((v[4 * j + 3] & 0xFF) << 24);
-                            reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N)
-                                    op[j] = uint8_t(v[j]);
-                        }
-                    }
-                    else if (er.valid)
-                    {
-                        uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
-                        if (fast)
-                        {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4*>(op)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N)
-                                    op[j] = v[j];
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.N)
+                                        op[j] = v[j];
+                            }
                         }
                     }
                 }
@@ -469,7 +572,37 @@ namespace b200
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(tempty_bar(acc));
+                if (p.tma_store && colw < p.N)
+                {
+                    // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
+                    // rows / columns that fall outside the output tensor are clipped by the TMA unit
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0)
+                    {
+                        // lane 0 holds the first row of the block: a block that starts outside the tensor is skipped
+                        if (p.conv && er.valid)
+                        {
+                            const int row0 = quarter * 32;
+                            const int tw0 = row0 % p.TW, th0 = (row0 / p.TW) % p.TH, tn0 = row0 / (p.TW * p.TH);
+                            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + tw0),
+                                         "r"(p0 + th0), "r"(n0 + tn0) : "memory");
+                        }
+                        else if (!p.conv && er.valid)
+                        {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(tm * BM + quarter * 32)
+                                         : "memory");
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    store_pending = true;
+                }
             }
+            // stores must be complete (not just read) before the CTA exits
+            if (lane == 0)
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
 
         // ------------------------------------------------------------ common tail
@@ -623,6 +756,9 @@ namespace b200
         p.out_zp = e->out_zero_point;
         p.out_type = e->out_type;
         p.out = out;
+        p.vec_params = ((reinterpret_cast<uintptr_t>(e->scale) | reinterpret_cast<uintptr_t>(e->bias)) & 15) == 0;
+        const bool one_byte = e->out_type == B200_U8 || e->out_type == B200_I8;
+        p.tma_store = one_byte && (p.N % 16 == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         (void)a_type;
     }
 
@@ -694,7 +830,8 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
     ContractParams p = {};
     p.M = int(M);
     p.N = int(N);
-    p.num_kblocks = int((K + bk - 1) / bk);
+    p.ntaps = 1;
+    p.cblocks = int((K + bk - 1) / bk);
     p.tiles_m = int((M + BM - 1) / BM);
     const int bn = pick_bn(N, p.tiles_m);
     p.tiles_n = int((N + bn - 1) / bn);
@@ -714,6 +851,15 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
     rc = make_map(&maps.b, W, 2, dims_b, str, box_b, bk);
     if (rc != B200_OK)
         return rc;
+    if (p.tma_store)
+    {
+        // each epilogue warp stores 32 rows x bn/2 bytes
+        uint64_t dims_o[2] = {uint64_t(N), uint64_t(M)}, str_o[1] = {uint64_t(N)};
+        uint32_t box_o[2] = {uint32_t(bn / 2), 32u};
+        rc = make_map(&maps.out, out, 2, dims_o, str_o, box_o, bn / 2);
+        if (rc != B200_OK)
+            return rc;
+    }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -781,23 +927,36 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
     if (c->N * P * Q > 0x7FFFFFFF || c->R * c->S * c->C > 0x7FFFFFFF)
         return B200_ERR_TOO_LARGE;
 
+    if (c->R * c->S > MAX_TAPS)
+        return B200_ERR_UNSUPPORTED;
+
     const int bk = (c->C % 128 == 0) ? 128 : 64;
     ContractParams p = {};
     p.conv = 1;
     p.N = int(c->K);
-    p.S = int(c->S);
     p.cblocks = int(c->C / bk);
-    p.num_kblocks = int(c->R * c->S * p.cblocks);
-    p.dil_h = int(c->dilation_h);
-    p.dil_w = int(c->dilation_w);
-    p.pad_h = int(c->pad_h);
-    p.pad_w = int(c->pad_w);
-    p.stride_h = int(c->stride_h);
-    p.stride_w = int(c->stride_w);
+    p.ntaps = int(c->R * c->S);
+    const int sh = int(c->stride_h), sw = int(c->stride_w);
+    for (int r = 0; r < c->R; ++r)
+        for (int sx = 0; sx < c->S; ++sx)
+        {
+            // input pixel of output (p,q) for this tap: (p*sh + off_h, q*sw + off_w); split the offset into the
+            // sub-lattice (off mod stride) and a displacement inside that sub-lattice (floor division)
+            const int off_h = int(r * c->dilation_h - c->pad_h), off_w = int(sx * c->dilation_w - c->pad_w);
+            const int dh = (off_h >= 0) ? off_h / sh : -((-off_h + sh - 1) / sh);
+            const int dw = (off_w >= 0) ? off_w / sw : -((-off_w + sw - 1) / sw);
+            Tap& t = p.taps[r * c->S + sx];
+            t.dh = short(dh);
+            t.dw = short(dw);
+            t.map = short((off_h - dh * sh) * sw + (off_w - dw * sw));
+            t.pad = 0;
+        }
     p.NB = int(c->N);
     p.P = int(P);
     p.Q = int(Q);
     pick_patch(c->N, P, Q, p.TW, p.TH, p.TN);
+    p.sub_w = p.TW < 32 ? p.TW : 32;
+    p.sub_h = (p.TH < 32 / p.sub_w) ? p.TH : 32 / p.sub_w;
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((c->N + p.TN - 1) / p.TN);
@@ -809,16 +968,15 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
     TensorMaps maps;
     memset(&maps, 0, sizeof(maps));
     // one map per pixel sub-lattice (h % stride_h, w % stride_w) of the channels-last input
-    for (int ph = 0; ph < p.stride_h; ++ph)
-        for (int pw = 0; pw < p.stride_w; ++pw)
+    for (int ph = 0; ph < sh; ++ph)
+        for (int pw = 0; pw < sw; ++pw)
         {
-            uint64_t dims[4] = {uint64_t(c->C), uint64_t((c->W - pw + p.stride_w - 1) / p.stride_w),
-                                uint64_t((c->H - ph + p.stride_h - 1) / p.stride_h), uint64_t(c->N)};
-            uint64_t str[3] = {uint64_t(c->C) * p.stride_w, uint64_t(c->C) * c->W * p.stride_h,
-                               uint64_t(c->C) * c->W * c->H};
+            uint64_t dims[4] = {uint64_t(c->C), uint64_t((c->W - pw + sw - 1) / sw), uint64_t((c->H - ph + sh - 1) / sh),
+                                uint64_t(c->N)};
+            uint64_t str[3] = {uint64_t(c->C) * sw, uint64_t(c->C) * c->W * sh, uint64_t(c->C) * c->W * c->H};
             uint32_t box[4] = {uint32_t(bk), uint32_t(p.TW), uint32_t(p.TH), uint32_t(p.TN)};
             const uint8_t* base = static_cast<const uint8_t*>(data) + (int64_t(ph) * c->W + pw) * c->C;
-            rc = make_map(&maps.a[ph * p.stride_w + pw], base, 4, dims, str, box, bk);
+            rc = make_map(&maps.a[ph * sw + pw], base, 4, dims, str, box, bk);
             if (rc != B200_OK)
                 return rc;
         }
@@ -828,5 +986,15 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
     rc = make_map(&maps.b, filters, 2, dims_b, str_b, box_b, bk);
     if (rc != B200_OK)
         return rc;
+    if (p.tma_store)
+    {
+        // each epilogue warp stores the 32 tile rows of its TMEM lane quarter: a sub-patch of the tile
+        uint64_t dims_o[4] = {uint64_t(c->K), uint64_t(Q), uint64_t(P), uint64_t(c->N)};
+        uint64_t str_o[3] = {uint64_t(c->K), uint64_t(c->K) * Q, uint64_t(c->K) * Q * P};
+        uint32_t box_o[4] = {uint32_t(bn / 2), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, bn / 2);
+        if (rc != B200_OK)
+            return rc;
+    }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
