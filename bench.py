@@ -1,22 +1,29 @@
 #!/usr/bin/env python3
-"""Benchmark of the B200 quantized-inference path (and, with --impl reference, of nGraph's own CPU
-reference kernels on the host cores).
+"""Benchmark of the B200 quantized-inference path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl b200|reference]
 
-One JSON line on stdout (rank 0).  Workloads (synthetic, seeded; shapes from the baseline configs):
-    qconv     QuantizedConvolutionBias+Relu layer, u8 [B,64,56,56] * i8 [64,64,3,3], per-channel scales
-    qdot      QuantizedDotBias+Relu layer, u8 [M,1024] x i8 [1024,1024]
-    quantize  Quantize f32 -> u8, per-tensor, [B,64,256,256]
-A step is one pass of the hot path over one batch.  `value` is timed with CUDA events with the
-inputs resident in HBM; `e2e` includes the pinned-host -> device copy of the step's input and the
-device -> host copy of its result, through the same C-ABI calls.
+Prints ONE JSON line (rank 0).  Workloads (synthetic, seeded; shapes from the baseline configs):
+
+  resnet50  (default) int8 ResNet-50 v1.5, batch 128 per GPU, as an nGraph Function compiled and run
+            through the B200 backend plugin (Backend::create("B200:<dev>") -> compile -> call).
+            value = images/s with the input tensor resident in HBM; e2e = the same through
+            Tensor::write (pinned host -> device) + call + Tensor::read (logits -> host) every step.
+  qconv     one QuantizedConvolutionBias+Relu layer, u8 [B,64,56,56] * i8 [64,64,3,3] (C ABI directly)
+  qdot      one QuantizedDotBias+Relu layer, u8 [M,1024] x i8 [1024,1024]              (C ABI directly)
+  quantize  Quantize f32 -> u8, per tensor, [B,64,256,256]                             (C ABI directly)
+
+--impl reference times nGraph's own CPU implementation of the same path on the host cores: the
+INTERPRETER backend (reference kernels) on the decomposed graph, one process per core, each on a
+bounded sample (an image strip) sized from --steps so the run ends within minutes.
 """
 import argparse
 import json
 import os
+import pickle
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -71,16 +78,196 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "reasons": reasons, "samples": len(rows)}
 
 
+# ------------------------------------------------------------------------------------------ CPU reference (INTERPRETER)
+def _strip_height(budget_s):
+    """tallest image strip (full width) one INTERPRETER pass gets through within budget_s (~38 s per full image)"""
+    for h in (224, 128, 96, 64, 32):
+        if 38.0 * h / 224 <= budget_s:
+            return h
+    return 32
+
+
+def cpu_worker(pickle_path, strip_h, reps):
+    """child process: INTERPRETER on the decomposed ResNet-50 graph over one image strip"""
+    from ngraph_b200 import ngraph_api as ng
+    from ngraph_b200.harness.resnet50_int8 import synthetic_images
+    from oracle import interpreter
+    model = pickle.load(open(pickle_path, "rb"))
+    fn, _ = model.build(ng, 1, fused=False, decomposed=interpreter, image_hw=(strip_h, 224))
+    be = interpreter.backend()
+    exe = be.compile(fn)
+    x = synthetic_images(1, 77, 224)[:, :, :strip_h, :]
+    tin, tout = ng.Tensor(be, np.float32, x.shape), ng.Tensor(be, np.float32, (1, model.classes))
+    tin.write(x)
+    t0 = time.time()
+    for _ in range(reps):
+        exe.call([tout], [tin])
+    dt = time.time() - t0
+    out = tout.read()
+    print(json.dumps({"seconds": dt, "reps": reps, "checksum": float(np.abs(out).sum()), "logits": out[0, :8].tolist()}))
+
+
+def cpu_reference_rate(model, budget_s, procs=None):
+    """images/s of nGraph's reference kernels (INTERPRETER) over `procs` processes, each on one strip"""
+    procs = procs or max(1, os.cpu_count() or 1)
+    strip_h = _strip_height(budget_s)
+    with tempfile.NamedTemporaryFile(suffix=".pkl", delete=False) as f:
+        pickle.dump(model, f)
+        path = f.name
+    try:
+        cmd = [sys.executable, os.path.abspath(__file__), "--cpu-worker", path, str(strip_h), "1"]
+        ps = [subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=ROOT) for _ in range(procs)]
+        outs = [p.communicate() for p in ps]
+    finally:
+        os.unlink(path)
+    res = []
+    for (o, e), p in zip(outs, ps):
+        if p.returncode != 0:
+            raise RuntimeError("INTERPRETER worker failed: " + e[-500:])
+        res.append(json.loads(o.strip().splitlines()[-1]))
+    frac = model.macs_per_image((strip_h, 224)) / model.macs_per_image()
+    slowest = max(r["seconds"] for r in res)
+    rate = procs * frac / slowest
+    sample = "INTERPRETER (nGraph reference kernels) on the decomposed graph, %d processes x one %dx224 strip (%.3f image by MACs), %.1f s" \
+             % (procs, strip_h, frac, slowest)
+    return rate, procs, sample, strip_h, res[0]
+
+
 # ------------------------------------------------------------------------------------------ workloads
-class QConvLayer:
-    """BASELINE config: single QuantizedConvolutionBias+Relu layer (u8 NHWC on device)."""
-    name, metric, unit, dtype = "qconv", "QuantizedConvolutionBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
+class ResNet50:
+    name, metric, unit = "resnet50", "int8 ResNet-50 v1.5 inference throughput", "img/s"
+    dtype, bound = "u8*i8->i32 (f32 in, f32 logits out)", "tensor"
+
+    def __init__(self, batch=128):
+        self.batch = batch
+        self.model = None
+
+    def describe(self, world=1):
+        return {"workload": "int8 ResNet-50 v1.5, nGraph Function through the B200 backend plugin: 53 QuantizedConvolutionBias"
+                            "(+Relu/+Add+Relu), u8 MaxPool, Dequantize/AvgPool/Quantize head, QuantizedDot 2048->1000, Dequantize",
+                "batch_per_gpu": self.batch, "global_batch": self.batch * world, "input": "f32 NCHW [B,3,224,224] normalised",
+                "weights": "random He-normal, per-channel i8; activation scales from a seeded 8-image calibration",
+                "parallelism": "batch-sharded replicas, outputs gathered with NCCL all_gather",
+                "l2": "per-step activation working set (~2 GB) >> 126 MB L2"}
+
+    def build_model(self):
+        from ngraph_b200.harness.resnet50_int8 import QuantizedResNet50
+        if self.model is None:
+            self.model = QuantizedResNet50(seed=0, calibration_batch=8)
+        return self.model
+
+    def setup(self, torch, rank, local_rank, world):
+        from ngraph_b200 import ngraph_api as ng
+        from ngraph_b200.harness.resnet50_int8 import synthetic_images
+        self.torch, self.ng, self.world = torch, ng, world
+        model = self.build_model()
+        ng.load_b200()
+        stream = torch.cuda.current_stream().cuda_stream
+        self.backend = ng.Backend("B200:%d,stream=%d" % (local_rank, stream))
+        self.fn, _ = model.build(ng, self.batch, fused=True)
+        self.exe = self.backend.compile(self.fn)
+        x = synthetic_images(min(self.batch, 16), 100 + rank)
+        x = np.tile(x, ((self.batch + x.shape[0] - 1) // x.shape[0], 1, 1, 1))[:self.batch]
+        self.x_dev = torch.from_numpy(x).cuda()
+        self.logits = torch.empty((self.batch, model.classes), dtype=torch.float32, device="cuda")
+        self.t_in = self.backend.create_tensor(np.float32, x.shape, self.x_dev.data_ptr())
+        self.t_out = self.backend.create_tensor(np.float32, tuple(self.logits.shape), self.logits.data_ptr())
+        self.pin_in = torch.from_numpy(x).pin_memory()
+        self.pin_out = torch.empty((self.batch, model.classes), dtype=torch.float32).pin_memory()
+        self.gathered = torch.empty((world * self.batch, model.classes), dtype=torch.float32, device="cuda") if world > 1 else None
+
+    def units_per_step(self):
+        return float(self.batch)
+
+    def step(self):
+        self.exe.call([self.t_out], [self.t_in], validate=False)
+        if self.gathered is not None:
+            self.torch.distributed.all_gather_into_tensor(self.gathered, self.logits)
+
+    def step_e2e(self):
+        self.t_in.write_ptr(self.pin_in.data_ptr(), self.pin_in.numel() * 4)
+        self.exe.call([self.t_out], [self.t_in], validate=False)
+        if self.gathered is not None:
+            self.torch.distributed.all_gather_into_tensor(self.gathered, self.logits)
+        self.t_out.read_ptr(self.pin_out.data_ptr(), self.pin_out.numel() * 4)
+
+    def io_bytes(self):
+        return self.pin_in.numel() * 4, self.pin_out.numel() * 4
+
+    def roofline(self, peaks, per_step_ms):
+        """dominant kernel = the tcgen05 contraction kernel (all convolutions + the dot): its time per step
+        from per-node CUDA events in a separate instrumented pass over the same graph"""
+        ng = self.ng
+        exe = self.backend.compile(self.model.build(ng, self.batch, fused=True)[0], perf=True)
+        passes = 5
+        for _ in range(passes):
+            exe.call([self.t_out], [self.t_in], validate=False)
+        self.torch.cuda.synchronize()
+        rows = exe.performance_data()
+        contr_us = sum(us for n, us, c in rows if n.startswith("QuantizedConvolution") or n.startswith("QuantizedDot")) / passes
+        total_us = sum(us for n, us, c in rows) / passes
+        ops = 2.0 * self.model.macs_per_image() * self.batch
+        achieved = ops / (contr_us * 1e-6) / 1e12
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        top = sorted(((us / passes, n) for n, us, c in rows), reverse=True)[:6]
+        if os.environ.get("B200_BENCH_NODE_TABLE"):  # per-node table for the profile notes
+            with open(os.environ["B200_BENCH_NODE_TABLE"], "w") as f:
+                for n, us, c in rows:
+                    f.write("%10.1f us  %s\n" % (us / passes, n))
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
+                "kernel": "qcontract_kernel (53 convolutions + dot)", "kernel_us_per_step": contr_us, "all_nodes_us_per_step": total_us,
+                "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)",
+                "slowest_nodes_us": [[round(u, 1), n] for u, n in top]}
+
+    def check_and_cpu_baseline(self, skip_cpu):
+        """INTERPRETER on an image strip: timing for cpu_baseline and the parity check of the B200 output"""
+        if skip_cpu:
+            return None, None
+        from ngraph_b200.harness.resnet50_int8 import synthetic_images
+        ng, model = self.ng, self.model
+        rate, procs, sample, strip_h, first = cpu_reference_rate(model, budget_s=20.0)
+        x = synthetic_images(1, 77, 224)[:, :, :strip_h, :]  # the strip the workers ran, through the plugin
+        fn, _ = model.build(ng, 1, fused=True, image_hw=(strip_h, 224))
+        got = self.backend.compile(fn).run(x)[0]
+        ok = bool(np.array_equal(np.asarray(first["logits"], np.float32), got[0, :8])) and \
+            abs(float(np.abs(got).sum()) - first["checksum"]) <= 1e-5 * max(1.0, first["checksum"])
+        return {"value": rate, "unit": "img/s", "cores": procs, "kind": "reference", "sample": sample}, ok
+
+
+class MicroWorkload:
+    """single-kernel workloads called through the C ABI (ngraph_b200.ops)"""
     bound = "tensor"
+
+    def setup(self, torch, rank, local_rank, world):
+        from ngraph_b200 import ops
+        self.torch, self.ops = torch, ops
+        self.alloc(1 + rank)
+
+    def roofline(self, peaks, per_step_ms):
+        alg = self.alg_per_launch()
+        if self.bound == "hbm":
+            achieved, peak, unit, src = alg / (per_step_ms / 1e3) / 1e9, peaks["hbm_gbs"], "GB/s", peaks["source"]
+        else:
+            achieved, peak, unit = alg / (per_step_ms / 1e3) / 1e12, 2.0 * peaks["bf16_tflops"], "TOP/s"
+            src = peaks["source"] + ": 2 x bf16 burst (int8 peak not measured separately)"
+        return {"bound": self.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None,
+                "peak_source": src}
+
+    def check_and_cpu_baseline(self, skip_cpu):
+        ok = self.check()
+        if skip_cpu:
+            return None, ok
+        v, sample = self.cpu_sample()
+        return {"value": v, "unit": self.unit, "cores": 1, "kind": "port", "sample": sample}, ok
+
+
+class QConvLayer(MicroWorkload):
+    name, metric, unit, dtype = "qconv", "QuantizedConvolutionBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
 
     def __init__(self, batch=32):
         self.B, self.C, self.H, self.W, self.K = batch, 64, 56, 56, 64
 
-    def describe(self):
+    def describe(self, world=1):
         return {"workload": "QuantizedConvolutionBias+Relu u8[%d,64,56,56]*i8[64,64,3,3] s1 p1, per-channel scales, "
                             "i32 bias -> u8" % self.B, "layout": "channels-last on device",
                 "l2": "input+output 2x%.1f MB per step, rotated over 24 buffers (> 126 MB L2)" % (self.B * 64 * 3136 / 1e6)}
@@ -92,12 +279,12 @@ class QConvLayer:
              "bias": rng.integers(-1000, 1001, size=self.K).astype(np.int32)}
         sf = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), size=self.K)).astype(np.float32)
         d["scale"] = (np.float32(0.02) * sf / np.float32(0.05)).astype(np.float32)
+        self.h = d
         return d
 
-    def setup(self, torch, ops, seed):
-        self.torch, self.ops = torch, ops
+    def alloc(self, seed):
+        torch, ops = self.torch, self.ops
         h = self.host_inputs(seed)
-        self.h = h
         self.nbuf = 24
         self.data = [torch.from_numpy(h["data"]).cuda() for _ in range(self.nbuf)]
         self.out = [torch.empty((self.B, 56, 56, self.K), dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
@@ -107,11 +294,11 @@ class QConvLayer:
         self.pin_out = torch.empty((self.B, 56, 56, self.K), dtype=torch.uint8).pin_memory()
         self.i = 0
 
-    def units_per_step(self):  # tera-ops per step
+    def units_per_step(self):
         return 2.0 * self.B * 56 * 56 * self.K * self.C * 9 / 1e12
 
     def alg_per_launch(self):
-        return self.units_per_step() * 1e12  # ops of the one launch
+        return self.units_per_step() * 1e12
 
     def step(self):
         i = self.i = (self.i + 1) % self.nbuf
@@ -126,46 +313,40 @@ class QConvLayer:
     def io_bytes(self):
         return self.pin_in.numel(), self.pin_out.numel()
 
-    def check(self):
+    def _oracle(self, nimg):
         from oracle import ref
-        cs = ref.conv_shape((2, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1))
-        nchw = np.ascontiguousarray(self.h["data"][:2].transpose(0, 3, 1, 2))
-        kcrs = np.ascontiguousarray(self.h["filt"].transpose(0, 3, 1, 2))
-        exp = ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True)
-        got = self.out[self.i][:2].cpu().numpy().transpose(0, 3, 1, 2)
-        return bool(np.array_equal(got, exp))
-
-    def cpu_sample(self):
-        from oracle import ref
-        nimg = 2
         cs = ref.conv_shape((nimg, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1))
         nchw = np.ascontiguousarray(self.h["data"][:nimg].transpose(0, 3, 1, 2))
         kcrs = np.ascontiguousarray(self.h["filt"].transpose(0, 3, 1, 2))
-        t = time.time()
-        reps = 0
+        return ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True)
+
+    def check(self):
+        got = self.out[self.i][:2].cpu().numpy().transpose(0, 3, 1, 2)
+        return bool(np.array_equal(got, self._oracle(2)))
+
+    def cpu_sample(self):
+        t, reps = time.time(), 0
         while time.time() - t < 10.0:
-            ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True)
+            self._oracle(2)
             reps += 1
         dt = time.time() - t
-        return reps * 2.0 * nimg * 56 * 56 * 64 * 64 * 9 / 1e12 / dt, "%d images of the batch, %d passes, %.1f s" % (nimg, reps, dt)
+        return reps * 2.0 * 2 * 56 * 56 * 64 * 64 * 9 / 1e12 / dt, "C port of the reference arithmetic, 2 images of the batch, %d passes, %.1f s" % (reps, dt)
 
 
-class QDotLayer:
-    """BASELINE config: QuantizedDotBias+Relu, X u8 [M,1024], W i8 [1024,1024], bias, requantise to u8."""
+class QDotLayer(MicroWorkload):
     name, metric, unit, dtype = "qdot", "QuantizedDotBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
-    bound = "tensor"
 
     def __init__(self, m=32768):
         self.M, self.N, self.K = m, 1024, 1024
 
-    def describe(self):
+    def describe(self, world=1):
         return {"workload": "QuantizedDotBias+Relu u8[%d,1024] x i8[1024,1024], i32 bias, scale 0.004 -> u8" % self.M,
                 "l2": "rotated over 8 input/output buffers"}
 
     def host_inputs(self, seed):
+        from oracle import ref
         rng = np.random.default_rng(seed)
         x = rng.standard_normal((4096, self.K)).astype(np.float32)
-        from oracle import ref
         self.h_a = ref.quantize(x[:4096], np.float32(0.02), np.uint8(0))
         self.h_a = np.tile(self.h_a, ((self.M + 4095) // 4096, 1))[:self.M]
         self.h_w = rng.integers(-127, 128, size=(self.N, self.K)).astype(np.int8)
@@ -173,8 +354,8 @@ class QDotLayer:
         self.h_bias = ref.quantize(bias_f, np.float32(0.02) * np.float32(0.01), np.int32(0))
         self.h_scale = np.array([np.float32(0.02) * np.float32(0.01) / np.float32(0.05)], np.float32)
 
-    def setup(self, torch, ops, seed):
-        self.torch, self.ops = torch, ops
+    def alloc(self, seed):
+        torch = self.torch
         self.host_inputs(seed)
         self.nbuf = 8
         self.a = [torch.from_numpy(self.h_a).cuda() for _ in range(self.nbuf)]
@@ -215,18 +396,17 @@ class QDotLayer:
             ref.qgemm_fused(self.h_a[:rows], self.h_w, self.h_bias, self.h_scale, np.uint8, relu=True)
             reps += 1
         dt = time.time() - t
-        return reps * 2.0 * rows * self.N * self.K / 1e12 / dt, "%d rows of the batch, %d passes, %.1f s" % (rows, reps, dt)
+        return reps * 2.0 * rows * self.N * self.K / 1e12 / dt, "C port of the reference arithmetic, %d rows, %d passes, %.1f s" % (rows, reps, dt)
 
 
-class QuantizeSweepPoint:
-    """BASELINE config: Quantize f32 -> u8 (zero point 128, scale 0.05, ROUND_NEAREST_TOWARD_EVEN), [B,64,256,256]."""
+class QuantizeSweepPoint(MicroWorkload):
     name, metric, unit, dtype = "quantize", "Quantize f32->u8 bandwidth", "GB/s", "f32->u8"
     bound = "hbm"
 
     def __init__(self, batch=64):
         self.shape = (batch, 64, 256, 256)
 
-    def describe(self):
+    def describe(self, world=1):
         n = int(np.prod(self.shape))
         return {"workload": "Quantize f32%s -> u8 per-tensor scale 0.05 zp 128 RNE" % (list(self.shape),),
                 "l2": "input %.0f MB per step (> 126 MB L2)" % (n * 4 / 1e6)}
@@ -234,8 +414,8 @@ class QuantizeSweepPoint:
     def host_inputs(self, seed):
         self.h_x = np.random.default_rng(seed).standard_normal(1 << 24).astype(np.float32)
 
-    def setup(self, torch, ops, seed):
-        self.torch, self.ops = torch, ops
+    def alloc(self, seed):
+        torch = self.torch
         self.host_inputs(seed)
         g = torch.Generator(device="cuda")
         g.manual_seed(seed)
@@ -247,7 +427,7 @@ class QuantizeSweepPoint:
         self.pin_in.copy_(self.x)
         self.pin_out = torch.empty(self.shape, dtype=torch.uint8).pin_memory()
 
-    def units_per_step(self):  # GB per step (5 bytes per element)
+    def units_per_step(self):
         return 5.0 * self.x.numel() / 1e9
 
     def alg_per_launch(self):
@@ -272,41 +452,52 @@ class QuantizeSweepPoint:
 
     def cpu_sample(self):
         from oracle import ref
-        n = 1 << 24
-        x = self.h_x
         t, reps = time.time(), 0
         while time.time() - t < 10.0:
-            ref.quantize(x, np.float32(0.05), np.uint8(128))
+            ref.quantize(self.h_x, np.float32(0.05), np.uint8(128))
             reps += 1
         dt = time.time() - t
-        return reps * 5.0 * n / 1e9 / dt, "%d elements, %d passes, %.1f s" % (n, reps, dt)
+        return reps * 5.0 * self.h_x.size / 1e9 / dt, "C port of the reference arithmetic, %d elements, %d passes, %.1f s" % (self.h_x.size, reps, dt)
 
 
-WORKLOADS = {"qconv": QConvLayer, "qdot": QDotLayer, "quantize": QuantizeSweepPoint}
+WORKLOADS = {"resnet50": ResNet50, "qconv": QConvLayer, "qdot": QDotLayer, "quantize": QuantizeSweepPoint}
 
 
 def run_reference(args, wl, rank):
-    """The reference arm: nGraph's reference arithmetic on the host cores (bounded sample per step)."""
+    """The reference arm: nGraph's own CPU arithmetic for the path on the host cores, rank 0 only."""
     if rank != 0:
         return
-    h = wl.host_inputs(1)
-    if h is not None:
-        wl.h = h
-    value, sample = wl.cpu_sample()
+    total = args.steps + args.warmup
+    if isinstance(wl, ResNet50):
+        model = wl.build_model()
+        budget = max(4.0, 200.0 / max(total, 1))  # seconds per step
+        rates, sample, procs = [], "", 1
+        for i in range(total):
+            rate, procs, sample, _, _ = cpu_reference_rate(model, budget)
+            if i >= args.warmup:
+                rates.append(rate)
+        value, cores, kind = float(np.mean(rates)), procs, "reference"
+    else:
+        wl.host_inputs(1)
+        value, sample = wl.cpu_sample()
+        cores, kind = 1, "port"
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(),
-            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": 1, "kind": "port", "sample": sample},
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(args.gpus),
+            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 def main():
+    if len(sys.argv) >= 5 and sys.argv[1] == "--cpu-worker":
+        cpu_worker(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]))
+        return
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="qconv", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (images / rows); for small profiler captures")
@@ -329,9 +520,9 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from ngraph_b200 import lib, ops
+    from ngraph_b200 import lib
 
-    wl.setup(torch, ops, seed=1 + rank)
+    wl.setup(torch, rank, local_rank, world)
     peaks = measured_peaks()
 
     def barrier():
@@ -343,7 +534,6 @@ def main():
         wl.step()
     barrier()
     lib.device_status()
-    ok = wl.check()
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -385,23 +575,19 @@ def main():
         value = wl.units_per_step() * world / (per_step / 1e3)
         e2e_value = wl.units_per_step() * world / (ms_e2e / args.steps / 1e3)
         h2d, d2h = wl.io_bytes()
-        if wl.bound == "hbm":
-            achieved, peak, runit = wl.alg_per_launch() / (per_step / 1e3) / 1e9, peaks["hbm_gbs"], "GB/s"
-        else:
-            achieved, peak, runit = wl.alg_per_launch() / (per_step / 1e3) / 1e12, 2.0 * peaks["bf16_tflops"], "TOP/s"
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(),
-                "parity_vs_oracle": ok, "gpu_launches": launches, "clocks": clocks,
+                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(world),
+                "gpu_launches": launches, "clocks": clocks,
                 "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
-                             "traffic": None,
-                             "peak_source": peaks["source"] + (" (int8 peak taken as 2 x measured bf16 burst)" if wl.bound == "tensor" else "")}}
-        if not args.no_cpu_baseline:
-            v, sample = wl.cpu_sample()
-            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": 1, "kind": "port", "sample": sample}
+                "roofline": wl.roofline(peaks, per_step)}
+        cpu, ok = wl.check_and_cpu_baseline(args.no_cpu_baseline or world > 1)
+        line["parity_vs_oracle"] = ok
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

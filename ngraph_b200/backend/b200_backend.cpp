@@ -169,9 +169,21 @@ DeviceContext::DeviceContext(int dev)
     cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
 }
 
+DeviceContext::DeviceContext(int dev, cudaStream_t external)
+    : device(dev)
+    , stream(external)
+    , owns_stream(false)
+{
+    int count = 0;
+    cuda_check(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+    if (dev < 0 || dev >= count)
+        throw std::runtime_error("B200 backend: no CUDA device " + std::to_string(dev));
+    cuda_check(cudaSetDevice(dev), "cudaSetDevice");
+}
+
 DeviceContext::~DeviceContext()
 {
-    if (stream)
+    if (stream && owns_stream)
     {
         cudaSetDevice(device);
         cudaStreamDestroy(stream);
@@ -267,19 +279,36 @@ void B200Tensor::copy_from(const runtime::Tensor& source)
 // ------------------------------------------------------------------------------------ backend
 B200Backend::B200Backend(const std::string& options)
 {
+    // "<device ordinal>[,stream=<cudaStream_t as an integer>]": with stream= the backend enqueues on the
+    // caller's stream (and never destroys it) instead of creating its own
     int dev = 0;
-    if (!options.empty())
+    unsigned long long stream = 0;
+    bool have_stream = false;
+    std::stringstream ss(options);
+    std::string item;
+    bool first = true;
+    while (std::getline(ss, item, ','))
     {
         try
         {
-            dev = std::stoi(options);
+            if (item.rfind("stream=", 0) == 0)
+            {
+                stream = std::stoull(item.substr(7), nullptr, 0);
+                have_stream = true;
+            }
+            else if (first && !item.empty())
+                dev = std::stoi(item);
+            else if (!item.empty())
+                throw std::invalid_argument(item);
         }
         catch (...)
         {
-            throw std::runtime_error("B200 backend: options must be a CUDA device ordinal, got '" + options + "'");
+            throw std::runtime_error("B200 backend: bad option '" + item + "' (expected '<device>[,stream=<handle>]')");
         }
+        first = false;
     }
-    m_ctx = std::make_shared<DeviceContext>(dev);
+    m_ctx = have_stream ? std::make_shared<DeviceContext>(dev, reinterpret_cast<cudaStream_t>(stream))
+                        : std::make_shared<DeviceContext>(dev);
 }
 
 std::shared_ptr<runtime::Tensor> B200Backend::create_tensor()

@@ -2,8 +2,8 @@
 // include/b200_kernels.h.  Loaded by runtime::BackendManager through
 // ngraph_register_b200_backend() (src/ngraph/runtime/backend_manager.cpp:78-142 in nGraph).
 //
-// Backend options (the text after ':' in Backend::create("B200:<options>")): the CUDA device
-// ordinal, default 0.
+// Backend options (the text after ':' in Backend::create("B200:<options>")):
+// "<CUDA device ordinal>[,stream=<cudaStream_t as an integer>]", default device 0 and a stream of its own.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -36,7 +36,9 @@ namespace ngraph
             {
                 int device = 0;
                 cudaStream_t stream = nullptr;
+                bool owns_stream = true;
                 explicit DeviceContext(int dev);
+                DeviceContext(int dev, cudaStream_t external); // enqueue on the caller's stream
                 ~DeviceContext();
                 void make_current() const;
                 void synchronize() const; // waits for the stream, then raises on a device status word

@@ -114,27 +114,30 @@ class QuantizedResNet50:
         self.s_pool = np.float32(max(float(pooled.max()), 1e-6) / 255)
         pq = torch.clamp(torch.round(pooled / float(self.s_pool)), 0, 255)
         logits = (pq @ t(self.fc_q).float()) * float(self.s_pool) * float(self.s_fc)
-        self.s_logits = np.float32(max(float(logits.abs().max()), 1e-6) / 127)
+        # 2x headroom: other inputs exceed the calibration maximum, and where the device saturates the
+        # reference's QuantizedDot wraps (runtime/reference/dot.hpp:156 casts without clamping)
+        self.s_logits = np.float32(2.0 * max(float(logits.abs().max()), 1e-6) / 127)
 
     # ------------------------------------------------------------------ graph
-    def macs_per_image(self, size=None):
-        size = size or self.image_size
-        total = 0
-        h = (size + 6 - 7) // 2 + 1
-        total += h * h * 64 * 3 * 49
-        h = (h + 2 - 3) // 2 + 1
+    def macs_per_image(self, hw=None):
+        """multiply-accumulates of the convolutions and the final QuantizedDot for one image of size hw"""
+        h, w = hw or (self.image_size, self.image_size)
+        out = lambda n, k, s, p: (n + 2 * p - k) // s + 1
+        h, w = out(h, 7, 2, 3), out(w, 7, 2, 3)
+        total = h * w * 64 * 3 * 49
+        h, w = out(h, 3, 2, 1), out(w, 3, 2, 1)
         cin = 64
         for blocks, mid, cout, stride in STAGES:
             for b in range(blocks):
                 s = stride if b == 0 else 1
-                ho = (h - 1) // s + 1
+                ho, wo = out(h, 3, s, 1), out(w, 3, s, 1)
                 if b == 0:
-                    total += ho * ho * cin * cout
-                total += h * h * cin * mid + ho * ho * mid * mid * 9 + ho * ho * mid * cout
-                h, cin = ho, cout
+                    total += ho * wo * cin * cout
+                total += h * w * cin * mid + ho * wo * mid * mid * 9 + ho * wo * mid * cout
+                h, w, cin = ho, wo, cout
         return total + 2048 * self.classes
 
-    def build(self, ng, batch, fused=True, decomposed=None, image_hw=None):
+    def build(self, ng, batch, fused=True, decomposed=None, image_hw=None, intermediate_results=False):
         """Returns (Function, parameter).  fused=True: the graph a client hands to the B200 backend.
         fused=False: every fused op replaced by `decomposed` (oracle.interpreter), for INTERPRETER."""
         h, w = image_hw or (self.image_size, self.image_size)
@@ -157,8 +160,11 @@ class QuantizedResNet50:
             return decomposed.decomposed_conv(inp, ng.constant(L["w_q"]), ng.constant(L["bias_q"]), ng.constant(L["scale"]),
                                               out_dtype, L["relu"], **geom, **kw)
 
+        taps = []
         a = conv("stem", a)
+        taps.append(a)
         a = ng.max_pool(a, (3, 3), (2, 2), (1, 1))
+        taps.append(a)
         for si, (blocks, mid, cout, stride) in enumerate(STAGES):
             for b in range(blocks):
                 pre = "s%db%d" % (si + 1, b)
@@ -166,10 +172,13 @@ class QuantizedResNet50:
                 y = conv(pre + "_c1", a)
                 y = conv(pre + "_c2", y)
                 a = conv(pre + "_c3", y, res=short)
+                taps.append(a)
         fh, fw = a.shape[2], a.shape[3]
         pooled = ng.quantize(ng.avg_pool(ng.dequantize(a, self.s_feat, np.uint8(0)), (fh, fw)), self.s_pool, np.uint8(0),
                              np.uint8, (), 4)
         flat = ng.reshape(pooled, (0, 1, 2, 3), (batch, 2048))
         logits = ng.quantized_dot(flat, ng.constant(self.fc_q), self.s_pool, 0, self.s_fc, 0, self.s_logits, 0, np.int8)
         out = ng.dequantize(logits, self.s_logits, np.int8(0))
+        if intermediate_results:  # stem, maxpool, the 16 block outputs, pooled features, i8 logits, f32 logits
+            return ng.Function(taps + [pooled, logits, out], [x]), x
         return ng.Function([out], [x]), x

@@ -1,0 +1,65 @@
+"""int8 ResNet-50 v1.5 (BASELINE's headline graph) through the B200 plugin against nGraph's INTERPRETER.
+
+INTERPRETER needs ~38 s per 224x224 image, so parity runs on reduced spatial sizes (the network is
+fully convolutional up to the pooling head; every layer, channel count, stride, residual join and the
+head are exercised) and checks batch independence at the full 224x224 size on the device."""
+import numpy as np
+import pytest
+
+ng = pytest.importorskip("ngraph_b200.ngraph_api")
+from ngraph_b200.harness.resnet50_int8 import QuantizedResNet50, conv_specs, synthetic_images  # noqa: E402
+from oracle import interpreter  # noqa: E402
+
+needs_ngraph = pytest.mark.skipif(not interpreter.available(), reason="nGraph host library / INTERPRETER not built here")
+
+
+@pytest.fixture(scope="module")
+def model():
+    return QuantizedResNet50(seed=0, calibration_batch=2, calibration_size=64)
+
+
+def test_layer_table():
+    specs = conv_specs()
+    assert len(specs) == 53
+    assert sum(1 for s in specs if s[7]) == 16       # residual joins
+    assert sum(1 for s in specs if s[3] == 3) == 16  # 3x3 convolutions
+
+
+def test_mac_count(model):
+    assert abs(model.macs_per_image() / 1e9 - 4.089) < 0.01  # ResNet-50 v1.5 at 224x224
+
+
+@needs_ngraph
+def test_fused_graph_is_what_a_quantizing_client_builds(model):
+    fn, _ = model.build(ng, 2, fused=True, image_hw=(32, 32))
+    assert ng.capi().ngc_function_op_count(fn.h) > 200
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_resnet50_parity_with_interpreter(model):
+    ng.load_b200()
+    b200, ref = ng.Backend("B200"), interpreter.backend()
+    for hw, batch in (((32, 32), 2), ((64, 96), 1)):
+        x = synthetic_images(batch, 7, 224)[:, :, :hw[0], :hw[1]]
+        fused, _ = model.build(ng, batch, fused=True, image_hw=hw)
+        plain, _ = model.build(ng, batch, fused=False, decomposed=interpreter, image_hw=hw)
+        got = b200.compile(fused).run(x)[0]
+        exp = ref.compile(plain).run(x)[0]
+        assert got.shape == exp.shape == (batch, 1000)
+        np.testing.assert_array_equal(got.view(np.uint32), exp.view(np.uint32), err_msg=str(hw))
+        assert np.abs(exp).max() > 0
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_resnet50_full_size_batch_independence(model):
+    """224x224, batch 8: every image's logits equal the ones it gets when run alone (batch 1) - the
+    size-independent property that stands in for a full-size oracle run."""
+    ng.load_b200()
+    b200 = ng.Backend("B200")
+    x = synthetic_images(8, 9, 224)
+    all_at_once = b200.compile(model.build(ng, 8, fused=True)[0]).run(x)[0]
+    one = b200.compile(model.build(ng, 1, fused=True)[0])
+    for i in (0, 3, 7):
+        np.testing.assert_array_equal(one.run(x[i:i + 1])[0][0], all_at_once[i])
