@@ -54,6 +54,16 @@ namespace b200
         short pad;
     };
 
+    // How shared memory is split for one launch (decided on the host, in launch_contract).
+    struct SmemPlan
+    {
+        int b_resident;   // B (all k-blocks of the one column tile) is loaded once and kept
+        int b_res_bytes;  // bytes of the resident B region (0 otherwise)
+        int stage_bytes;  // A (+ B when not resident) per pipeline stage
+        int stages;
+        int total_bytes;  // dynamic shared memory of the launch
+    };
+
     struct ContractParams
     {
         int M, N;            // GEMM rows (conv: unused) and output channels
@@ -77,6 +87,7 @@ namespace b200
         int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
         uint32_t idesc;
+        SmemPlan smem;
         Tap taps[MAX_TAPS];
     };
 
@@ -91,18 +102,18 @@ namespace b200
     constexpr int NUM_THREADS = 320; // producer warp, MMA warp, 8 epilogue warps
     constexpr int SMEM_LIMIT = 232448; // 227 KB per CTA
 
+    constexpr int MAX_STAGES = 16;
+    constexpr int BAR_BYTES = 512;          // (2*MAX_STAGES + 5) mbarriers
+    constexpr int B_RESIDENT_MAX = 73728;   // a whole filter / weight matrix up to this size stays in shared memory
+
     template <int BN, int BK>
     struct Cfg
     {
         static constexpr int A_BYTES = BM * BK;
         static constexpr int B_BYTES = BN * BK;
-        static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
         static constexpr int OUT_BYTES = BM * BN;      // 8 staging blocks of 32 rows x BN/2 bytes
-        static constexpr int FIXED = OUT_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-        static constexpr int FIT = (SMEM_LIMIT - FIXED - 64) / STAGE_BYTES;
-        static constexpr int STAGES = FIT > 8 ? 8 : FIT;
+        static constexpr int FIXED = 2 * OUT_BYTES /*double buffered*/ + 1024 /*align slack*/ + BAR_BYTES;
         static constexpr int TMEM_COLS = 2 * BN;
-        static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED;
     };
 
     // ---- epilogue arithmetic ----------------------------------------------------------------
@@ -166,91 +177,80 @@ namespace b200
             }
             return;
         }
-        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu]
-        float f[32];
-        if (full_chunk && p.vec_params)
-        {
+        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu], four columns at a time
+        const bool vec = full_chunk && p.vec_params;
+        const bool one_byte = p.out_type == B200_U8 || p.out_type == B200_I8;
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4)
+        for (int j4 = 0; j4 < 8; ++j4)
+        {
+            float f[4];
+            if (vec)
             {
                 const float4 s4 = p.scale_per_channel ? __ldg(reinterpret_cast<const float4*>(p.scale + col0) + j4)
                                                       : make_float4(__ldg(p.scale), __ldg(p.scale), __ldg(p.scale), __ldg(p.scale));
                 const int4 b4 = p.bias ? __ldg(reinterpret_cast<const int4*>(p.bias + col0) + j4) : make_int4(0, 0, 0, 0);
-                f[4 * j4 + 0] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
-                f[4 * j4 + 1] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
-                f[4 * j4 + 2] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
-                f[4 * j4 + 3] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
+                f[0] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
+                f[1] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
+                f[2] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
+                f[3] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
             }
-        }
-        else
-        {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-            {
-                const int cc = (col0 + j < p.N) ? col0 + j : 0;
-                const int32_t b = p.bias ? __ldg(p.bias + cc) : 0;
-                const float sc = __ldg(p.scale + (p.scale_per_channel ? cc : 0));
-                f[j] = __fmul_rn(__int2float_rn(int32_t(v[j]) + b), sc);
-            }
-        }
-        if (has_sum && er.valid)
-        {
-            if (sum_regs)
+            else
             {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
+                for (int i = 0; i < 4; ++i)
                 {
-                    const uint32_t byte = (sumw[j >> 2] >> (8 * (j & 3))) & 0xFF;
-                    const float sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
-                    f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, sv));
+                    const int col = col0 + 4 * j4 + i;
+                    const int cc = col < p.N ? col : 0;
+                    const int32_t b = p.bias ? __ldg(p.bias + cc) : 0;
+                    f[i] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + i]) + b), __ldg(p.scale + (p.scale_per_channel ? cc : 0)));
                 }
             }
+            if (has_sum && er.valid)
+            {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                {
+                    float sv;
+                    if (sum_regs)
+                    {
+                        const uint32_t byte = (sumw[j4] >> (8 * i)) & 0xFF;
+                        sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
+                    }
+                    else
+                    {
+                        const int col = col0 + 4 * j4 + i;
+                        sv = col < p.N ? load_sum(p.sum_in, p.sum_type, er.off + col) : 0.0f;
+                    }
+                    f[i] = __fadd_rn(f[i], __fmul_rn(sum_scale, sv));
+                }
+            }
+            if (p.relu)
+            {
+                // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0); the sign of a zero result does not
+                // survive the integer conversions, and the f32 comparisons in the tests treat -0 == +0
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    f[i] = fmaxf(f[i], 0.0f);
+            }
+            if (one_byte)
+            {
+                // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) /
+                // ceil(v-0.5) / parity sequence equals round-half-even for |v| < 2^23 and everything beyond
+                // saturates, so cvt.rni (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
+                const int i0 = __float2int_rn(f[0]), i1 = __float2int_rn(f[1]), i2 = __float2int_rn(f[2]), i3 = __float2int_rn(f[3]);
+                w[j4] = p.out_type == B200_U8 ? pack4_u8(i0, i1, i2, i3) : pack4_s8(i0, i1, i2, i3);
+            }
+            else if (p.out_type == B200_F32)
+            {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    v[4 * j4 + i] = __float_as_uint(f[i]);
+            }
             else
             {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col0 + j < p.N)
-                        f[j] = __fadd_rn(f[j], __fmul_rn(sum_scale, load_sum(p.sum_in, p.sum_type, er.off + col0 + j)));
-            }
-        }
-        if (p.relu)
-        {
-            // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0); the sign of a zero result does not
-            // survive the conversions below and is normalised by the f32 comparison in the tests
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                f[j] = fmaxf(f[j], 0.0f);
-        }
-        if (p.out_type == B200_F32)
-        {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                v[j] = __float_as_uint(f[j]);
-        }
-        else if (p.out_type == B200_I32)
-        {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                v[j] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[j])));
-        }
-        else
-        {
-            // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) /
-            // ceil(v-0.5) / parity sequence equals round-half-even for |v| < 2^23 and everything beyond
-            // saturates, so cvt.rni (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
-            if (p.out_type == B200_U8)
-            {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    w[j] = pack4_u8(__float2int_rn(f[4 * j]), __float2int_rn(f[4 * j + 1]), __float2int_rn(f[4 * j + 2]),
-                                    __float2int_rn(f[4 * j + 3]));
-            }
-            else
-            {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    w[j] = pack4_s8(__float2int_rn(f[4 * j]), __float2int_rn(f[4 * j + 1]), __float2int_rn(f[4 * j + 2]),
-                                    __float2int_rn(f[4 * j + 3]));
+                for (int i = 0; i < 4; ++i)
+                    v[4 * j4 + i] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[i])));
             }
         }
     }
@@ -266,13 +266,18 @@ namespace b200
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
 
-        const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-        const uint32_t out_base = smem_base + C::STAGES * C::STAGE_BYTES; // 1024-aligned: STAGE_BYTES is a multiple of 1024
-        const uint32_t bars = out_base + C::OUT_BYTES;
+        // [resident B] [stages x (A [+ B])] [2 x output staging] [mbarriers]; every region is a multiple of 1024 bytes
+        const int STAGES = p.smem.stages;
+        const uint32_t stage_bytes = uint32_t(p.smem.stage_bytes);
+        const uint32_t bres_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+        const uint32_t smem_base = bres_base + uint32_t(p.smem.b_res_bytes);
+        const uint32_t out_base = smem_base + uint32_t(STAGES) * stage_bytes;
+        const uint32_t bars = out_base + 2 * C::OUT_BYTES;
         auto full_bar = [&](int s) { return bars + 8u * s; };
-        auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-        auto tfull_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
-        auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+        auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+        auto tfull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
+        auto tempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 2 + b); };
+        const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 4);
 
         const int warp = threadIdx.x >> 5;
         const int lane = threadIdx.x & 31;
@@ -281,11 +286,12 @@ namespace b200
         if (threadIdx.x == 0)
         {
             abort_flag = 0;
-            for (int s = 0; s < C::STAGES; ++s)
+            for (int s = 0; s < STAGES; ++s)
             {
                 ptx::mbar_init(full_bar(s), 1);
                 ptx::mbar_init(empty_bar(s), 1);
             }
+            ptx::mbar_init(bres_bar, 1);
             for (int b = 0; b < 2; ++b)
             {
                 ptx::mbar_init(tfull_bar(b), 1);
@@ -318,6 +324,14 @@ namespace b200
                 ptx::prefetch_tmap(&maps.a[0]);
                 int s = 0;
                 uint32_t ph = 0;
+                if (p.smem.b_resident)
+                {
+                    // the single column tile's weights, all k-blocks, once
+                    ptx::mbar_expect_tx(bres_bar, uint32_t(p.smem.b_res_bytes));
+                    const int nkb = p.ntaps * p.cblocks;
+                    for (int kb = 0; kb < nkb; ++kb)
+                        ptx::tma_load_2d(bres_base + kb * C::B_BYTES, &maps.b, bres_bar, kb * BK, 0);
+                }
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
                 {
                     const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -344,15 +358,16 @@ namespace b200
                                 break;
                             }
                             PROF_ADD(0);
-                            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+                            const uint32_t a_dst = smem_base + s * stage_bytes;
                             const uint32_t b_dst = a_dst + C::A_BYTES;
-                            ptx::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                            ptx::mbar_expect_tx(full_bar(s), stage_bytes);
                             if (p.conv)
                                 ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
                             else
                                 ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
-                            ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
-                            if (++s == C::STAGES)
+                            if (!p.smem.b_resident)
+                                ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                            if (++s == STAGES)
                             {
                                 s = 0;
                                 ph ^= 1;
@@ -371,7 +386,11 @@ namespace b200
                 uint32_t ph = 0, tile_it = 0;
                 const int num_kblocks = p.ntaps * p.cblocks;
                 const uint64_t a_desc0 = ptx::smem_desc_kmajor(smem_base, BK);
-                const uint64_t b_desc0 = ptx::smem_desc_kmajor(smem_base + C::A_BYTES, BK);
+                const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + C::A_BYTES, BK);
+                // descriptor address fields count 16-byte units
+                const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
+                if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp))
+                    fail = 2003;
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
                     const int acc = tile_it & 1;
@@ -399,9 +418,8 @@ namespace b200
                             PROF_ADD(1);
                         }
                         ptx::tc_fence_after_sync();
-                        // stage s starts s*STAGE_BYTES further on: the descriptor's address field counts 16-byte units
-                        const uint64_t a_desc = a_desc0 + uint64_t(s) * (C::STAGE_BYTES >> 4);
-                        const uint64_t b_desc = b_desc0 + uint64_t(s) * (C::STAGE_BYTES >> 4);
+                        const uint64_t a_desc = a_desc0 + uint64_t(s) * (stage_bytes >> 4);
+                        const uint64_t b_desc = b_desc0 + uint64_t(p.smem.b_resident ? kb : s) * b_step;
 #pragma unroll
                         for (int k = 0; k < BK / 32; ++k)
                         {
@@ -410,7 +428,7 @@ namespace b200
                                         (kb | k) != 0 ? 1u : 0u);
                         }
                         ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
-                        if (++s == C::STAGES)
+                        if (++s == STAGES)
                         {
                             s = 0;
                             ph ^= 1;
@@ -435,11 +453,10 @@ namespace b200
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
-            // this warp's staging block: 32 rows x HALF bytes, swizzled like the TMA store expects
-            const uint32_t stage_blk = out_base + uint32_t(warp - 2) * (32 * HALF);
+            // this warp's two staging blocks (alternating per tile): 32 rows x HALF bytes, swizzled like the TMA store expects
+            const uint32_t stage_blk0 = out_base + uint32_t(warp - 2) * (32 * HALF);
             const uint32_t sw_xor = HALF == 128 ? uint32_t(lane & 7) : HALF == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
-            const uint32_t stage_row = stage_blk + uint32_t(lane) * HALF;
-            bool store_pending = false;
+            int stores_in_flight = 0;
             uint32_t tile_it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
             {
@@ -467,23 +484,20 @@ namespace b200
                     er.valid = m < p.M;
                     er.off = int64_t(m) * p.N;
                 }
-                // the residual does not depend on the accumulator: fetch it before waiting for the MMAs
-                uint32_t sumw[CHUNKS][8];
+                // the residual does not depend on the accumulator: chunk 0's is fetched before waiting for the
+                // MMAs, chunk c+1's while chunk c is converted
+                uint32_t sumw[2][8];
                 const bool sum_regs = has_sum && vec_ok && er.valid;
-                if (sum_regs)
-                {
-#pragma unroll
-                    for (int c = 0; c < CHUNKS; ++c)
+                auto fetch_sum = [&](int c, uint32_t (&dst)[8]) {
+                    if (sum_regs && colw + 32 * c + 32 <= p.N)
                     {
-                        if (colw + 32 * c + 32 <= p.N)
-                        {
-                            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
-                            const uint4 s0 = sp[0], s1 = sp[1];
-                            sumw[c][0] = s0.x; sumw[c][1] = s0.y; sumw[c][2] = s0.z; sumw[c][3] = s0.w;
-                            sumw[c][4] = s1.x; sumw[c][5] = s1.y; sumw[c][6] = s1.z; sumw[c][7] = s1.w;
-                        }
+                        const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
+                        const uint4 s0 = sp[0], s1 = sp[1];
+                        dst[0] = s0.x; dst[1] = s0.y; dst[2] = s0.z; dst[3] = s0.w;
+                        dst[4] = s1.x; dst[5] = s1.y; dst[6] = s1.z; dst[7] = s1.w;
                     }
-                }
+                };
+                fetch_sum(0, sumw[0]);
                 {
                     PROF_T0();
                     if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp))
@@ -496,27 +510,38 @@ namespace b200
                 }
                 ptx::tc_fence_after_sync();
                 PROF_T0();
-                if (store_pending)
+                const uint32_t stage_blk = stage_blk0 + (tile_it & 1) * C::OUT_BYTES;
+                const uint32_t stage_row = stage_blk + uint32_t(lane) * HALF;
+                if (stores_in_flight == 2)
                 {
-                    // the previous tile's TMA store must have finished reading the staging block
+                    // the TMA store issued two tiles ago must have finished reading this staging block
                     if (lane == 0)
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
-                    store_pending = false;
+                    stores_in_flight = 1;
                 }
                 const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * HALF;
+                // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c is converted
+                uint32_t vbuf[2][32];
+                __syncwarp();
+                ptx::tmem_ld_32x32(t_addr, vbuf[0]);
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c)
                 {
-                    uint32_t v[32], w[8];
-                    __syncwarp();
-                    ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                    uint32_t (&v)[32] = vbuf[c & 1];
+                    uint32_t w[8];
                     ptx::tmem_ld_wait();
+                    if (c + 1 < CHUNKS)
+                    {
+                        __syncwarp();
+                        ptx::tmem_ld_32x32(t_addr + 32 * (c + 1), vbuf[(c + 1) & 1]);
+                        fetch_sum(c + 1, sumw[(c + 1) & 1]);
+                    }
                     const int col0 = colw + 32 * c;
                     if (col0 < p.N) // warp-uniform
                     {
                         const bool full_chunk = col0 + 32 <= p.N;
-                        epilogue_chunk(p, v, w, col0, full_chunk, has_sum, sumw[c], sum_regs && full_chunk, sum_scale, er);
+                        epilogue_chunk(p, v, w, col0, full_chunk, has_sum, sumw[c & 1], sum_regs && full_chunk, sum_scale, er);
                         if (p.tma_store)
                         {
                             // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
@@ -597,7 +622,7 @@ namespace b200
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                    store_pending = true;
+                    ++stores_in_flight;
                 }
             }
             // stores must be complete (not just read) before the CTA exits
@@ -694,7 +719,7 @@ namespace b200
     }
 
     template <int BN, int BK>
-    static int launch_contract(const TensorMaps& maps, const ContractParams& p, cudaStream_t st)
+    static int launch_contract(const TensorMaps& maps, ContractParams& p, cudaStream_t st)
     {
         using C = Cfg<BN, BK>;
         static bool attr_set[64] = {false};
@@ -704,18 +729,30 @@ namespace b200
         if (!attr_set[dev])
         {
             cudaError_t e = cudaFuncSetAttribute(qcontract_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 C::SMEM_BYTES);
+                                                 SMEM_LIMIT);
             if (e != cudaSuccess)
                 return cuda_status(e, "cudaFuncSetAttribute(qcontract)");
             attr_set[dev] = true;
         }
+        // shared-memory plan: keep B resident when there is a single column tile and it is small; give the
+        // rest to pipeline stages (more bytes in flight hide the HBM latency of the activation stream)
+        const int nkb = p.ntaps * p.cblocks;
+        SmemPlan& sp = p.smem;
+        sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
+        sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
+        sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
+        int fit = (SMEM_LIMIT - C::FIXED - sp.b_res_bytes - 64) / sp.stage_bytes;
+        sp.stages = fit > MAX_STAGES ? MAX_STAGES : fit;
+        if (sp.stages < 2)
+            return B200_ERR_UNSUPPORTED;
+        sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + C::FIXED;
         int tiles = p.tiles_m * p.tiles_n;
         int grid = tiles < num_sms() ? tiles : num_sms();
-        qcontract_kernel<BN, BK><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(maps, p);
+        qcontract_kernel<BN, BK><<<grid, NUM_THREADS, sp.total_bytes, st>>>(maps, p);
         return after_launch("qcontract_kernel");
     }
 
-    static int dispatch_contract(int bn, int bk, const TensorMaps& maps, const ContractParams& p, cudaStream_t st)
+    static int dispatch_contract(int bn, int bk, const TensorMaps& maps, ContractParams& p, cudaStream_t st)
     {
         if (bk == 128)
         {
