@@ -265,17 +265,25 @@ class QConvLayer(MicroWorkload):
     name, metric, unit, dtype = "qconv", "QuantizedConvolutionBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
 
     def __init__(self, batch=32):
-        self.B, self.C, self.H, self.W, self.K = batch, 64, 56, 56, 64
+        # BASELINE's layer by default; B200_BENCH_CONV="C,K,R,HW" times another ResNet layer shape (stride 1, same padding)
+        c, k, r, hw = (int(v) for v in os.environ.get("B200_BENCH_CONV", "64,64,3,56").split(","))
+        self.B, self.C, self.H, self.W, self.K, self.R = batch, c, hw, hw, k, r
 
     def describe(self, world=1):
-        return {"workload": "QuantizedConvolutionBias+Relu u8[%d,64,56,56]*i8[64,64,3,3] s1 p1, per-channel scales, "
-                            "i32 bias -> u8" % self.B, "layout": "channels-last on device",
-                "l2": "input+output 2x%.1f MB per step, rotated over 24 buffers (> 126 MB L2)" % (self.B * 64 * 3136 / 1e6)}
+        return {"workload": "QuantizedConvolutionBias+Relu u8[%d,%d,%d,%d]*i8[%d,%d,%d,%d] s1 same-pad, per-channel scales, "
+                            "i32 bias -> u8" % (self.B, self.C, self.H, self.W, self.K, self.C, self.R, self.R),
+                "layout": "channels-last on device",
+                "l2": "input %.1f MB + output %.1f MB per step, rotated over %d buffers (> 126 MB L2)"
+                      % (self.B * self.C * self.H * self.W / 1e6, self.B * self.K * self.H * self.W / 1e6, self.nbufs())}
+
+    def nbufs(self):
+        per = self.B * (self.C + self.K) * self.H * self.W
+        return max(2, min(24, int(300e6 // per) + 1))
 
     def host_inputs(self, seed):
         rng = np.random.default_rng(seed)
         d = {"data": rng.integers(0, 256, size=(self.B, self.H, self.W, self.C), dtype=np.uint8),
-             "filt": rng.integers(-127, 128, size=(self.K, 3, 3, self.C)).astype(np.int8),
+             "filt": rng.integers(-127, 128, size=(self.K, self.R, self.R, self.C)).astype(np.int8),
              "bias": rng.integers(-1000, 1001, size=self.K).astype(np.int32)}
         sf = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), size=self.K)).astype(np.float32)
         d["scale"] = (np.float32(0.02) * sf / np.float32(0.05)).astype(np.float32)
@@ -285,17 +293,18 @@ class QConvLayer(MicroWorkload):
     def alloc(self, seed):
         torch, ops = self.torch, self.ops
         h = self.host_inputs(seed)
-        self.nbuf = 24
+        self.nbuf = self.nbufs()
         self.data = [torch.from_numpy(h["data"]).cuda() for _ in range(self.nbuf)]
-        self.out = [torch.empty((self.B, 56, 56, self.K), dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
+        self.out = [torch.empty((self.B, self.H, self.W, self.K), dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
         self.filt, self.bias, self.scale = (torch.from_numpy(h[k]).cuda() for k in ("filt", "bias", "scale"))
-        self.cp = ops.conv_params((self.B, 56, 56, 64), (64, 3, 3, 64), (1, 1), (1, 1))
+        pad = self.R // 2
+        self.cp = ops.conv_params((self.B, self.H, self.W, self.C), (self.K, self.R, self.R, self.C), (1, 1), (pad, pad))
         self.pin_in = torch.from_numpy(h["data"]).pin_memory()
-        self.pin_out = torch.empty((self.B, 56, 56, self.K), dtype=torch.uint8).pin_memory()
+        self.pin_out = torch.empty((self.B, self.H, self.W, self.K), dtype=torch.uint8).pin_memory()
         self.i = 0
 
     def units_per_step(self):
-        return 2.0 * self.B * 56 * 56 * self.K * self.C * 9 / 1e12
+        return 2.0 * self.B * self.H * self.W * self.K * self.C * self.R * self.R / 1e12
 
     def alg_per_launch(self):
         return self.units_per_step() * 1e12
@@ -315,7 +324,8 @@ class QConvLayer(MicroWorkload):
 
     def _oracle(self, nimg):
         from oracle import ref
-        cs = ref.conv_shape((nimg, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1))
+        pad = self.R // 2
+        cs = ref.conv_shape((nimg, self.C, self.H, self.W), (self.K, self.C, self.R, self.R), (1, 1), (pad, pad))
         nchw = np.ascontiguousarray(self.h["data"][:nimg].transpose(0, 3, 1, 2))
         kcrs = np.ascontiguousarray(self.h["filt"].transpose(0, 3, 1, 2))
         return ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True)
@@ -330,7 +340,7 @@ class QConvLayer(MicroWorkload):
             self._oracle(2)
             reps += 1
         dt = time.time() - t
-        return reps * 2.0 * 2 * 56 * 56 * 64 * 64 * 9 / 1e12 / dt, "C port of the reference arithmetic, 2 images of the batch, %d passes, %.1f s" % (reps, dt)
+        return reps * 2.0 * 2 * self.H * self.W * self.K * self.C * self.R * self.R / 1e12 / dt, "C port of the reference arithmetic, 2 images of the batch, %d passes, %.1f s" % (reps, dt)
 
 
 class QDotLayer(MicroWorkload):

@@ -14,8 +14,9 @@
 //   (runtime/reference/convolution.hpp:227-251).  A stride s > 1 is handled with s*s tensor
 //   maps over the s-strided pixel sub-lattices of the input (no element strides, no gather).
 //   The filter [K,R,S,C] is a plain [K, R*S*C] row-major matrix, so B tiles are 2-D boxes.
-// * warp 0: TMA producer; warp 1: TMEM allocation + MMA issue (one elected thread);
-//   warps 2-9: epilogue.  Two TMEM accumulator buffers let the epilogue of tile i overlap the
+// * warp 0: TMEM allocation + MMA issue (one elected thread); warps 1-3: TMA producers (k-block i is
+//   issued by producer i mod 3: one thread cannot issue TMA boxes fast enough to keep HBM busy);
+//   warps 4-11: epilogue.  Two TMEM accumulator buffers let the epilogue of tile i overlap the
 //   MMAs of tile i+1.  Each epilogue warp owns 32 accumulator rows (its TMEM lane quarter) and
 //   half of the tile's columns: tcgen05.ld -> bias/scale/sum/ReLU/round/saturate in registers ->
 //   (one-byte outputs) a swizzled shared-memory staging block of its own -> one TMA store, so
@@ -61,6 +62,7 @@ namespace b200
         int b_res_bytes;  // bytes of the resident B region (0 otherwise)
         int stage_bytes;  // A (+ B when not resident) per pipeline stage
         int stages;
+        int out_bytes;    // output staging (0 when results are written from registers)
         int total_bytes;  // dynamic shared memory of the launch
     };
 
@@ -99,8 +101,9 @@ namespace b200
     };
 
     constexpr int BM = 128;
-    constexpr int NUM_THREADS = 320; // producer warp, MMA warp, 8 epilogue warps
-    constexpr int SMEM_LIMIT = 232448; // 227 KB per CTA
+    constexpr int NUM_PRODUCERS = 3;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
+    constexpr int NUM_THREADS = 384; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-11: epilogue
+    constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
 
     constexpr int MAX_STAGES = 16;
     constexpr int BAR_BYTES = 512;          // (2*MAX_STAGES + 5) mbarriers
@@ -157,101 +160,108 @@ namespace b200
         int64_t off; // element offset of column 0 of this row in out / sum_in
     };
 
-    // One 32-column chunk of one accumulator row: v[] holds the int32 accumulators on entry and the
-    // output values on return (f32 bit patterns / int32), w[] the packed bytes for one-byte outputs.
-    __device__ __forceinline__ void epilogue_chunk(const ContractParams& p, uint32_t (&v)[32], uint32_t (&w)[8], int col0,
-                                                   bool full_chunk, bool has_sum, const uint32_t* sumw, bool sum_regs,
-                                                   float sum_scale, const EpiRow& er)
+    // Shared-memory read of four consecutive staged scales / biases (same address in every lane: a broadcast).
+    __device__ __forceinline__ float4 lds_f4(uint32_t addr)
     {
-        if (p.half_away)
-        {
-            const float sc = __ldg(p.scale);
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                v[j] = epilogue_core(p, int32_t(v[j]), sc);
-            if (p.out_type != B200_I32)
-            {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    w[j] = (v[4 * j] & 0xFF) | ((v[4 * j + 1] & 0xFF) << 8) | ((v[4 * j + 2] & 0xFF) << 16) | ((v[4 * j + 3] & 0xFF) << 24);
-            }
-            return;
-        }
-        // v <- float(acc + bias) * scale  [+ sum_scale * float(sum)]  [relu], four columns at a time
-        const bool vec = full_chunk && p.vec_params;
-        const bool one_byte = p.out_type == B200_U8 || p.out_type == B200_I8;
+        float4 r;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(addr));
+        return r;
+    }
+    __device__ __forceinline__ int4 lds_i4(uint32_t addr)
+    {
+        int4 r;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+        return r;
+    }
+
+    // One 32-column chunk of one accumulator row, fused-op contract, one-byte output (the hot case):
+    // w[] <- saturate(round_half_even(relu(float(acc + bias) * scale [+ sum_scale * float(sum)]))).
+    // sc / bi: shared-memory addresses of this chunk's 32 staged scales / biases.
+    template <bool HAS_SUM>
+    __device__ __forceinline__ void epilogue_chunk_bytes(const uint32_t (&v)[32], uint32_t (&w)[8], uint32_t sc, uint32_t bi,
+                                                         const uint32_t* sumw, float sum_scale, bool sum_u8, bool relu, bool out_u8)
+    {
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4)
         {
-            float f[4];
-            if (vec)
+            const float4 s4 = lds_f4(sc + 16 * j4);
+            const int4 b4 = lds_i4(bi + 16 * j4);
+            float f0 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
+            float f1 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
+            float f2 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
+            float f3 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
+            if (HAS_SUM)
             {
-                const float4 s4 = p.scale_per_channel ? __ldg(reinterpret_cast<const float4*>(p.scale + col0) + j4)
-                                                      : make_float4(__ldg(p.scale), __ldg(p.scale), __ldg(p.scale), __ldg(p.scale));
-                const int4 b4 = p.bias ? __ldg(reinterpret_cast<const int4*>(p.bias + col0) + j4) : make_int4(0, 0, 0, 0);
-                f[0] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
-                f[1] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
-                f[2] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
-                f[3] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
+                const uint32_t sw = sumw[j4];
+                const int m0 = sum_u8 ? int(sw & 0xFF) : int(int8_t(sw)), m1 = sum_u8 ? int((sw >> 8) & 0xFF) : int(int8_t(sw >> 8));
+                const int m2 = sum_u8 ? int((sw >> 16) & 0xFF) : int(int8_t(sw >> 16)), m3 = sum_u8 ? int(sw >> 24) : int(int8_t(sw >> 24));
+                f0 = __fadd_rn(f0, __fmul_rn(sum_scale, __int2float_rn(m0)));
+                f1 = __fadd_rn(f1, __fmul_rn(sum_scale, __int2float_rn(m1)));
+                f2 = __fadd_rn(f2, __fmul_rn(sum_scale, __int2float_rn(m2)));
+                f3 = __fadd_rn(f3, __fmul_rn(sum_scale, __int2float_rn(m3)));
             }
-            else
+            if (relu && !out_u8) // for u8 the unsigned saturation below already is max(v, 0)
             {
+                // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0)
+                f0 = fmaxf(f0, 0.0f);
+                f1 = fmaxf(f1, 0.0f);
+                f2 = fmaxf(f2, 0.0f);
+                f3 = fmaxf(f3, 0.0f);
+            }
+            // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) / ceil(v-0.5) /
+            // parity sequence equals round-half-even for |v| < 2^23 and everything beyond saturates, so cvt.rni
+            // (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
+            const int i0 = __float2int_rn(f0), i1 = __float2int_rn(f1), i2 = __float2int_rn(f2), i3 = __float2int_rn(f3);
+            w[j4] = out_u8 ? pack4_u8(i0, i1, i2, i3) : pack4_s8(i0, i1, i2, i3);
+        }
+    }
+
+    // Every other case (core contract, 4-byte outputs, ragged / unaligned residuals): v[] holds the int32
+    // accumulators on entry and the output values on return (f32 bit patterns / int32), w[] the packed bytes
+    // for one-byte outputs.
+    __device__ __forceinline__ void epilogue_chunk_general(const ContractParams& p, uint32_t (&v)[32], uint32_t (&w)[8], int col0,
+                                                           uint32_t sc, uint32_t bi, bool has_sum, float sum_scale, const EpiRow& er)
+    {
+        const bool one_byte = p.out_type == B200_U8 || p.out_type == B200_I8;
+        if (p.half_away)
+        {
+            const float scale = __ldg(p.scale);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v[j] = epilogue_core(p, int32_t(v[j]), scale);
+        }
+        else
+        {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4)
+            {
+                const float4 s4 = lds_f4(sc + 16 * j4);
+                const int4 b4 = lds_i4(bi + 16 * j4);
+                const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+                const int bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                 {
-                    const int col = col0 + 4 * j4 + i;
-                    const int cc = col < p.N ? col : 0;
-                    const int32_t b = p.bias ? __ldg(p.bias + cc) : 0;
-                    f[i] = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + i]) + b), __ldg(p.scale + (p.scale_per_channel ? cc : 0)));
-                }
-            }
-            if (has_sum && er.valid)
-            {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    float sv;
-                    if (sum_regs)
-                    {
-                        const uint32_t byte = (sumw[j4] >> (8 * i)) & 0xFF;
-                        sv = p.sum_type == B200_U8 ? float(byte) : float(int(int8_t(byte)));
-                    }
+                    const int j = 4 * j4 + i;
+                    float f = __fmul_rn(__int2float_rn(int32_t(v[j]) + bb[i]), ss[i]);
+                    if (has_sum && er.valid && col0 + j < p.N)
+                        f = __fadd_rn(f, __fmul_rn(sum_scale, load_sum(p.sum_in, p.sum_type, er.off + col0 + j)));
+                    if (p.relu)
+                        f = fmaxf(f, 0.0f);
+                    if (p.out_type == B200_F32)
+                        v[j] = __float_as_uint(f);
+                    else if (p.out_type == B200_I32)
+                        v[j] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f)));
                     else
-                    {
-                        const int col = col0 + 4 * j4 + i;
-                        sv = col < p.N ? load_sum(p.sum_in, p.sum_type, er.off + col) : 0.0f;
-                    }
-                    f[i] = __fadd_rn(f[i], __fmul_rn(sum_scale, sv));
+                        v[j] = uint32_t(min(max(__float2int_rn(f), p.out_type == B200_U8 ? 0 : -128), p.out_type == B200_U8 ? 255 : 127));
                 }
             }
-            if (p.relu)
-            {
-                // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0); the sign of a zero result does not
-                // survive the integer conversions, and the f32 comparisons in the tests treat -0 == +0
+        }
+        if (one_byte)
+        {
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    f[i] = fmaxf(f[i], 0.0f);
-            }
-            if (one_byte)
-            {
-                // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) /
-                // ceil(v-0.5) / parity sequence equals round-half-even for |v| < 2^23 and everything beyond
-                // saturates, so cvt.rni (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
-                const int i0 = __float2int_rn(f[0]), i1 = __float2int_rn(f[1]), i2 = __float2int_rn(f[2]), i3 = __float2int_rn(f[3]);
-                w[j4] = p.out_type == B200_U8 ? pack4_u8(i0, i1, i2, i3) : pack4_s8(i0, i1, i2, i3);
-            }
-            else if (p.out_type == B200_F32)
-            {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    v[4 * j4 + i] = __float_as_uint(f[i]);
-            }
-            else
-            {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    v[4 * j4 + i] = uint32_t(clamp_cast<int32_t>(round_quant<B200_ROUND_NEAREST_TOWARD_EVEN>(f[i])));
-            }
+            for (int j = 0; j < 8; ++j)
+                w[j] = (v[4 * j] & 0xFF) | ((v[4 * j + 1] & 0xFF) << 8) | ((v[4 * j + 2] & 0xFF) << 16) | ((v[4 * j + 3] & 0xFF) << 24);
         }
     }
 
@@ -265,6 +275,9 @@ namespace b200
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
+        // per epilogue warp: scale and bias of its column half of the current column tile
+        __shared__ __align__(16) float epi_scale[8][HALF];
+        __shared__ __align__(16) int32_t epi_bias[8][HALF];
 
         // [resident B] [stages x (A [+ B])] [2 x output staging] [mbarriers]; every region is a multiple of 1024 bytes
         const int STAGES = p.smem.stages;
@@ -272,7 +285,7 @@ namespace b200
         const uint32_t bres_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
         const uint32_t smem_base = bres_base + uint32_t(p.smem.b_res_bytes);
         const uint32_t out_base = smem_base + uint32_t(STAGES) * stage_bytes;
-        const uint32_t bars = out_base + 2 * C::OUT_BYTES;
+        const uint32_t bars = out_base + uint32_t(p.smem.out_bytes);
         auto full_bar = [&](int s) { return bars + 8u * s; };
         auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
         auto tfull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
@@ -299,7 +312,7 @@ namespace b200
             }
             ptx::fence_barrier_init();
         }
-        if (warp == 1)
+        if (warp == 0)
         {
             ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), C::TMEM_COLS);
             ptx::tmem_relinquish();
@@ -315,16 +328,17 @@ namespace b200
         const long long prof_kernel_t0 = clock64();
 #endif
 
-        if (warp == 0)
+        if (warp >= 1 && warp <= NUM_PRODUCERS)
         {
-            // ------------------------------------------------------------ TMA producer
+            // ------------------------------------------------------------ TMA producers
             if (ptx::elect_one())
             {
+                const int pw = warp - 1; // this producer issues the k-blocks whose running index is pw mod NUM_PRODUCERS
                 ptx::prefetch_tmap(&maps.b);
                 ptx::prefetch_tmap(&maps.a[0]);
-                int s = 0;
+                int s = 0, turn = 0;
                 uint32_t ph = 0;
-                if (p.smem.b_resident)
+                if (p.smem.b_resident && pw == 0)
                 {
                     // the single column tile's weights, all k-blocks, once
                     ptx::mbar_expect_tx(bres_bar, uint32_t(p.smem.b_res_bytes));
@@ -351,22 +365,28 @@ namespace b200
                         const CUtensorMap* amap = &maps.a[tp.map];
                         for (int cb = 0; cb < p.cblocks; ++cb, kcol += BK)
                         {
-                            PROF_T0();
-                            if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
+                            if (turn == pw)
                             {
-                                fail = 1001;
-                                break;
+                                PROF_T0();
+                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
+                                {
+                                    fail = 1001;
+                                    break;
+                                }
+                                if (pw == 0)
+                                    PROF_ADD(0);
+                                const uint32_t a_dst = smem_base + s * stage_bytes;
+                                const uint32_t b_dst = a_dst + C::A_BYTES;
+                                ptx::mbar_expect_tx(full_bar(s), stage_bytes);
+                                if (p.conv)
+                                    ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
+                                else
+                                    ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
+                                if (!p.smem.b_resident)
+                                    ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
                             }
-                            PROF_ADD(0);
-                            const uint32_t a_dst = smem_base + s * stage_bytes;
-                            const uint32_t b_dst = a_dst + C::A_BYTES;
-                            ptx::mbar_expect_tx(full_bar(s), stage_bytes);
-                            if (p.conv)
-                                ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
-                            else
-                                ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
-                            if (!p.smem.b_resident)
-                                ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                            if (++turn == NUM_PRODUCERS)
+                                turn = 0;
                             if (++s == STAGES)
                             {
                                 s = 0;
@@ -377,7 +397,7 @@ namespace b200
                 }
             }
         }
-        else if (warp == 1)
+        else if (warp == 0)
         {
             // ------------------------------------------------------------ MMA issuer
             if (ptx::elect_one())
@@ -442,11 +462,12 @@ namespace b200
         }
         else
         {
-            // ------------------------------------------------------------ epilogue (warps 2..9)
+            // ------------------------------------------------------------ epilogue (warps 4..11)
             // TMEM lane quarter (warp id % 4) is fixed by the hardware; the two warps that share a
             // quarter split the tile's columns between them.
             const int quarter = warp & 3;
-            const int half = (warp - 2) >> 2;
+            const int half = (warp - 4) >> 2;
+            const int ew = warp - 4; // 0..7
             const int row = quarter * 32 + lane; // accumulator row of this thread
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
@@ -454,9 +475,11 @@ namespace b200
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
             // this warp's two staging blocks (alternating per tile): 32 rows x HALF bytes, swizzled like the TMA store expects
-            const uint32_t stage_blk0 = out_base + uint32_t(warp - 2) * (32 * HALF);
+            const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * HALF);
             const uint32_t sw_xor = HALF == 128 ? uint32_t(lane & 7) : HALF == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
             int stores_in_flight = 0;
+            int staged_tn = -1;
+            const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
             uint32_t tile_it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
             {
@@ -464,6 +487,20 @@ namespace b200
                 const int acc = tile_it & 1;
                 const uint32_t acc_ph = (tile_it >> 1) & 1;
                 const int colw = tn * BN + half * HALF; // first output column of this warp
+                if (tn != staged_tn)
+                {
+                    // (re)stage this warp's scales and biases; the column tile changes at most tiles_n times per CTA
+                    __syncwarp();
+                    for (int j = lane; j < HALF; j += 32)
+                    {
+                        const int col = colw + j;
+                        const bool in_n = col < p.N;
+                        epi_scale[ew][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
+                        epi_bias[ew][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
+                    }
+                    __syncwarp();
+                    staged_tn = tn;
+                }
                 EpiRow er;
                 int q0 = 0, p0 = 0, n0 = 0;
                 if (p.conv)
@@ -505,7 +542,7 @@ namespace b200
                         fail = 3001;
                         break;
                     }
-                    if (warp == 2 && lane == 0)
+                    if (warp == 4 && lane == 0)
                         PROF_ADD(3);
                 }
                 ptx::tc_fence_after_sync();
@@ -541,7 +578,14 @@ namespace b200
                     if (col0 < p.N) // warp-uniform
                     {
                         const bool full_chunk = col0 + 32 <= p.N;
-                        epilogue_chunk(p, v, w, col0, full_chunk, has_sum, sumw[c & 1], sum_regs && full_chunk, sum_scale, er);
+                        const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
+                        const bool bytes_path = !p.half_away && esz == 1 && (!has_sum || (sum_regs && full_chunk) || !er.valid);
+                        if (bytes_path && has_sum && er.valid)
+                            epilogue_chunk_bytes<true>(v, w, sc, bi, sumw[c & 1], sum_scale, p.sum_type == B200_U8, p.relu != 0, p.out_type == B200_U8);
+                        else if (bytes_path)
+                            epilogue_chunk_bytes<false>(v, w, sc, bi, sumw[c & 1], sum_scale, false, p.relu != 0, p.out_type == B200_U8);
+                        else
+                            epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
                         if (p.tma_store)
                         {
                             // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
@@ -584,7 +628,7 @@ namespace b200
                         }
                     }
                 }
-                if (warp == 2 && lane == 0)
+                if (warp == 4 && lane == 0)
                 {
                     PROF_ADD(4);
 #ifdef B200_PROFILE_WAITS
@@ -647,7 +691,7 @@ namespace b200
                 __nanosleep(1000);
             __syncthreads();
         }
-        if (warp == 1)
+        if (warp == 0)
         {
             ptx::tc_fence_after_sync();
             ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -741,11 +785,21 @@ namespace b200
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
-        int fit = (SMEM_LIMIT - C::FIXED - sp.b_res_bytes - 64) / sp.stage_bytes;
+        int fixed = C::FIXED;
+        if (p.tma_store && nkb >= 16 && (SMEM_LIMIT - C::FIXED - 64) / sp.stage_bytes < 4)
+        {
+            // long reductions are MMA-bound: pipeline depth matters more than store efficiency, so the
+            // output staging blocks are given to the stage ring and results are written from registers
+            p.tma_store = 0;
+        }
+        if (!p.tma_store)
+            fixed -= 2 * C::OUT_BYTES;
+        int fit = (SMEM_LIMIT - fixed - sp.b_res_bytes - 64) / sp.stage_bytes;
         sp.stages = fit > MAX_STAGES ? MAX_STAGES : fit;
         if (sp.stages < 2)
             return B200_ERR_UNSUPPORTED;
-        sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + C::FIXED;
+        sp.out_bytes = p.tma_store ? 2 * C::OUT_BYTES : 0;
+        sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + fixed;
         int tiles = p.tiles_m * p.tiles_n;
         int grid = tiles < num_sms() ? tiles : num_sms();
         qcontract_kernel<BN, BK><<<grid, NUM_THREADS, sp.total_bytes, st>>>(maps, p);
