@@ -289,6 +289,30 @@ B200_API int b200_im2col_c4_u8(const void* in, void* out, int64_t N, int64_t H, 
                                int64_t pad_h_above, int64_t pad_w_above, void* stream);
 
 /*
+ * Stride-2 convolutions over <= 4 input channels (network stems, e.g. 7x7 stride 2 on RGB) on the tensor cores,
+ * without a patch matrix: the NCHW input is regrouped into 2x2-pixel cells of 4 channels (16 bytes per cell, zero
+ * outside the image); one output pixel then needs, per filter row pair, 4 neighbouring cells = 64 contiguous bytes.
+ *   b200_stem_geometry          P, Q (output size), Hc, Wc (cell grid), Rc (cell rows per window); unsupported if a
+ *                               filter row spans more than 4 cell columns (S > 7 or 8)
+ *   b200_stem_pack_filter_host  HOST function: KCRS i8 filter -> [K, Rc*64] in the matching order (done once, at compile)
+ *   b200_stem_pack_input        device: NCHW one-byte input -> cell grid [N, Hc, Wc, 16]
+ *   b200_qconv_stem             the convolution with the fused epilogue; out is channels-last [N,P,Q,K]
+ * Same accumulation as runtime::reference::general_convolution (src/ngraph/runtime/reference/convolution.hpp:59-265)
+ * for strides {2,2}, window dilation 1; used for QuantizedConvolutionBias and friends like b200_qconv.
+ */
+B200_API int b200_stem_geometry(int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                                int64_t pad_h_above, int64_t pad_w_above, int64_t* P, int64_t* Q, int64_t* Hc,
+                                int64_t* Wc, int64_t* Rc);
+B200_API int b200_stem_pack_filter_host(const int8_t* kcrs, int8_t* packed, int64_t K, int64_t C, int64_t R, int64_t S,
+                                        int64_t pad_h, int64_t pad_w);
+B200_API int b200_stem_pack_input(const void* in_nchw, void* cells, int64_t N, int64_t C, int64_t H, int64_t W,
+                                  int64_t R, int64_t S, int64_t pad_h, int64_t pad_w, int64_t pad_h_above,
+                                  int64_t pad_w_above, void* stream);
+B200_API int b200_qconv_stem(const void* cells, int data_type, const int8_t* packed_filters, void* out, int64_t N,
+                             int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                             int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue, void* stream);
+
+/*
  * out[0] = input_scale[0] * filter_scale[0] / output_scale[0] in fp32, left to right: the requantisation
  * scale of op::v0::QuantizedDot / QuantizedConvolution (src/ngraph/runtime/reference/dot.hpp:154,
  * src/ngraph/runtime/reference/convolution.hpp:254) when the three scales are run-time tensors.

@@ -836,6 +836,42 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
     int y = new_slot(Slot::ARENA, shape_size(os));
     const size_t C = ds[1];
 
+    if (C <= 4 && a.strides[0] == 2 && a.strides[1] == 2 && a.dilation[0] == 1 && a.dilation[1] == 1 &&
+        as_constant(node->input_value(1)))
+    {
+        // stride-2 small-channel stem: 2x2x4 cells, then an implicit GEMM over overlapping 64-byte windows
+        b200_conv_params c = make_conv_params(*node, a, ds, fs, 4);
+        int64_t P, Q, Hc, Wc, Rc;
+        if (b200_stem_geometry(c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above, c.pad_w_above, &P, &Q, &Hc, &Wc, &Rc) ==
+            B200_OK)
+        {
+            auto cf = as_constant(node->input_value(1));
+            std::vector<int8_t> w(size_t(c.K) * size_t(Rc) * 64);
+            kernel_check(b200_stem_pack_filter_host(static_cast<const int8_t*>(cf->get_data_ptr()), w.data(), c.K, int64_t(C), c.R,
+                                             c.S, c.pad_h, c.pad_w),
+                  "b200_stem_pack_filter_host");
+            int wslot = upload_constant(w.data(), w.size());
+            int xc = canonical_slot(node->input_value(0));
+            int cells = new_slot(Slot::ARENA, size_t(c.N) * size_t(Hc) * size_t(Wc) * 16);
+            int64_t Ci = C;
+            emit(node, "stem_cells", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_stem_pack_input(p[xc], p[cells], c.N, Ci, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above,
+                                            c.pad_w_above, st);
+            });
+            emit(node, "stem_qconv", [=](const Ptrs& p, cudaStream_t st) {
+                b200_epilogue ee = e;
+                ee.bias = bias >= 0 ? static_cast<const int32_t*>(p[bias]) : nullptr;
+                ee.scale = static_cast<const float*>(p[scale]);
+                ee.sum_in = sum >= 0 ? p[sum] : nullptr;
+                ee.sum_scale = sum_scale >= 0 ? static_cast<const float*>(p[sum_scale]) : nullptr;
+                return b200_qconv_stem(p[cells], dt, static_cast<const int8_t*>(p[wslot]), p[y], c.N, c.H, c.W, c.K, c.R, c.S,
+                                       c.pad_h, c.pad_w, c.pad_h_above, c.pad_w_above, &ee, st);
+            });
+            value_of(node->output(0)).nhwc = y;
+            return;
+        }
+    }
+
     if (C <= 4 && fs[3] <= 8 && a.dilation[0] == 1 && a.dilation[1] == 1)
     {
         // small-channel stem: 4-channel pixels -> patch matrix -> matrix product

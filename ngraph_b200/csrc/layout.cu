@@ -110,6 +110,44 @@ namespace b200
         }
     }
 
+    // The same with the window size known at compile time: all window loads are issued before the first
+    // max (out-of-image taps read as 0, the identity of an unsigned max), index arithmetic in 32 bits.
+    template <int WH, int WW>
+    __global__ void __launch_bounds__(256) maxpool_nhwc_u8_fixed_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                                        int N, int H, int W, int C16, int P, int Q, int stride_h,
+                                                                        int stride_w, int pad_h, int pad_w)
+    {
+        const uint32_t total = uint32_t(N) * P * Q * C16;
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+        {
+            uint32_t c = i % C16, t = i / C16;
+            uint32_t q = t % Q;
+            t /= Q;
+            uint32_t p = t % P, n = t / P;
+            const int h0 = int(p) * stride_h - pad_h, w0 = int(q) * stride_w - pad_w;
+            uint4 v[WH * WW];
+#pragma unroll
+            for (int r = 0; r < WH; ++r)
+#pragma unroll
+                for (int s = 0; s < WW; ++s)
+                {
+                    const int h = h0 + r, w = w0 + s;
+                    const bool ok = h >= 0 && h < H && w >= 0 && w < W;
+                    v[r * WW + s] = ok ? in[(size_t(n) * H + h) * W * C16 + size_t(w) * C16 + c] : make_uint4(0, 0, 0, 0);
+                }
+            uint4 m = v[0];
+#pragma unroll
+            for (int k = 1; k < WH * WW; ++k)
+            {
+                m.x = __vmaxu4(m.x, v[k].x);
+                m.y = __vmaxu4(m.y, v[k].y);
+                m.z = __vmaxu4(m.z, v[k].z);
+                m.w = __vmaxu4(m.w, v[k].w);
+            }
+            out[i] = m;
+        }
+    }
+
     // Global average head on channels-last u8: Dequantize(s_in, zp 0) -> AvgPool over H x W
     // (runtime::reference::avg_pool: sequential float sum in H,W order, one division by the count)
     // -> Quantize(s_out, zp 0, ROUND_NEAREST_TOWARD_EVEN).  One thread per (n, c); threads of a warp
@@ -193,9 +231,20 @@ extern "C" int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_
     int64_t total = N * P * Q * (C / 16);
     int64_t blocks = (total + 255) / 256;
     unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
-    maxpool_nhwc_u8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H), int(W), int(C / 16), int(P), int(Q),
-        int(win_h), int(win_w), int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    const bool small = total < (int64_t(1) << 31) && N * H * W * (C / 16) < (int64_t(1) << 31);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint4* in4 = static_cast<const uint4*>(in);
+    uint4* out4 = static_cast<uint4*>(out);
+    if (small && win_h == 3 && win_w == 3)
+        maxpool_nhwc_u8_fixed_kernel<3, 3><<<grid, 256, 0, st>>>(in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q),
+                                                                 int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    else if (small && win_h == 2 && win_w == 2)
+        maxpool_nhwc_u8_fixed_kernel<2, 2><<<grid, 256, 0, st>>>(in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q),
+                                                                 int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    else
+        maxpool_nhwc_u8_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H),
+                                                     int(W), int(C / 16), int(P), int(Q), int(win_h), int(win_w),
+                                                     int(stride_h), int(stride_w), int(pad_h), int(pad_w));
     return after_launch("b200_maxpool_nhwc_u8");
 }
 
@@ -331,4 +380,113 @@ extern "C" int b200_nhwc_to_nchw_b32(const void* in, void* out, int64_t N, int64
     transpose_b32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
                                                                            static_cast<uint32_t*>(out), HW, C);
     return after_launch("b200_nhwc_to_nchw_b32");
+}
+
+// ---- stride-2, few-channel convolutions (network stems) as a space-to-depth problem --------------
+//
+// A stride-2 convolution over <= 4 channels reads, for output (p,q) and filter row r, the input row
+// 2p - pad + r.  Grouping input pixels into 2x2 cells of 4 channels (16 bytes per cell, rows/cols shifted by
+// the padding rounded up to even, zero outside the image) turns it into a stride-1 convolution over cells:
+// filter row r and column s land in cell row (r+e_h)/2, cell column (s+e_w)/2 (e = pad & 1), at sub-pixel
+// ((r+e_h)&1, (s+e_w)&1).  With at most 4 cell columns per filter row, the cells one output pixel needs from
+// one cell row are 64 CONTIGUOUS bytes, i.e. one K-block of the tensor-core kernel, fetched by a tensor map
+// whose pixel dimension advances 16 bytes per step (overlapping windows).
+namespace b200
+{
+    __global__ void __launch_bounds__(256) s2d_pack_kernel(const uint8_t* __restrict__ in, uint4* __restrict__ out, int N, int C,
+                                                           int H, int W, int Hc, int Wc, int eh, int ew)
+    {
+        // eh / ew: even shift of image rows / columns inside the cell grid
+        int64_t total = int64_t(N) * Hc * Wc;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            int cw = int(i % Wc);
+            int64_t t = i / Wc;
+            int ch = int(t % Hc);
+            int n = int(t / Hc);
+            uint32_t words[4] = {0, 0, 0, 0}; // (dy,dx) -> 4 channel bytes
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int dx = 0; dx < 2; ++dx)
+                {
+                    int h = 2 * ch + dy - eh, w = 2 * cw + dx - ew;
+                    if (h >= 0 && h < H && w >= 0 && w < W)
+                    {
+                        uint32_t v = 0;
+                        for (int c = 0; c < C; ++c)
+                            v |= uint32_t(in[((int64_t(n) * C + c) * H + h) * W + w]) << (8 * c);
+                        words[dy * 2 + dx] = v;
+                    }
+                }
+            out[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        }
+    }
+}
+
+extern "C" int b200_stem_geometry(int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                                  int64_t pad_h_above, int64_t pad_w_above, int64_t* P, int64_t* Q, int64_t* Hc, int64_t* Wc,
+                                  int64_t* Rc)
+{
+    if (H <= 0 || W <= 0 || R <= 0 || S <= 0 || pad_h < 0 || pad_w < 0 || !P || !Q || !Hc || !Wc || !Rc)
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t eh = pad_h & 1, ew = pad_w & 1;
+    const int64_t rc = (R - 1 + eh) / 2 + 1, sc = (S - 1 + ew) / 2 + 1;
+    if (sc > 4)
+        return B200_ERR_UNSUPPORTED;
+    *P = (H + pad_h + pad_h_above - R) / 2 + 1;
+    *Q = (W + pad_w + pad_w_above - S) / 2 + 1;
+    if (*P <= 0 || *Q <= 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    *Rc = rc;
+    *Hc = *P + rc - 1;
+    *Wc = *Q + 3; // four cell columns per window
+    return B200_OK;
+}
+
+extern "C" int b200_stem_pack_filter_host(const int8_t* kcrs, int8_t* packed, int64_t K, int64_t C, int64_t R, int64_t S,
+                                          int64_t pad_h, int64_t pad_w)
+{
+    if (!kcrs || !packed || K <= 0 || C <= 0 || C > 4 || R <= 0 || S <= 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t eh = pad_h & 1, ew = pad_w & 1;
+    const int64_t rc = (R - 1 + eh) / 2 + 1, sc = (S - 1 + ew) / 2 + 1;
+    if (sc > 4)
+        return B200_ERR_UNSUPPORTED;
+    for (int64_t i = 0; i < K * rc * 64; ++i)
+        packed[i] = 0;
+    for (int64_t k = 0; k < K; ++k)
+        for (int64_t c = 0; c < C; ++c)
+            for (int64_t r = 0; r < R; ++r)
+                for (int64_t s = 0; s < S; ++s)
+                {
+                    const int64_t rr = (r + eh) / 2, dy = (r + eh) & 1, ss = (s + ew) / 2, dx = (s + ew) & 1;
+                    packed[(k * rc + rr) * 64 + ss * 16 + (dy * 2 + dx) * 4 + c] = kcrs[((k * C + c) * R + r) * S + s];
+                }
+    return B200_OK;
+}
+
+extern "C" int b200_stem_pack_input(const void* in_nchw, void* cells, int64_t N, int64_t C, int64_t H, int64_t W, int64_t R,
+                                    int64_t S, int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                    void* stream)
+{
+    using namespace b200;
+    if (N < 0 || C <= 0 || C > 4)
+        return B200_ERR_INVALID_ARGUMENT;
+    int64_t P, Q, Hc, Wc, Rc;
+    int rc = b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc);
+    if (rc != B200_OK)
+        return rc;
+    if (N == 0)
+        return B200_OK;
+    if (!in_nchw || !cells || (reinterpret_cast<uintptr_t>(cells) & 15))
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t eh = pad_h + (pad_h & 1), ew = pad_w + (pad_w & 1);
+    int64_t total = N * Hc * Wc;
+    int64_t blocks = (total + 255) / 256;
+    unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
+    s2d_pack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(in_nchw),
+                                                                       static_cast<uint4*>(cells), int(N), int(C), int(H), int(W),
+                                                                       int(Hc), int(Wc), int(eh), int(ew));
+    return after_launch("b200_stem_pack_input");
 }

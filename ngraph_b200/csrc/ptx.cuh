@@ -68,13 +68,17 @@ namespace b200
 
         // Bounded wait: gives up after `limit_ns` (or as soon as another thread of the CTA
         // has given up), records that in *abort_flag and returns false.  Never spins forever.
+        // `backoff_ns` > 0 sleeps between polls so that a waiting warp does not take issue slots
+        // from the warps that do the arithmetic on the same scheduler.
         __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint64_t limit_ns = 2000000000ull)
+                                                  uint32_t backoff_ns = 0, uint64_t limit_ns = 2000000000ull)
         {
             uint32_t spins = 0;
             uint64_t t0 = 0;
             while (!mbar_try_wait(bar, parity))
             {
+                if (backoff_ns)
+                    __nanosleep(backoff_ns);
                 if ((++spins & 0xFF) == 0)
                 {
                     if (*abort_flag)

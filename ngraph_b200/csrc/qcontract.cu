@@ -16,7 +16,7 @@
 //   The filter [K,R,S,C] is a plain [K, R*S*C] row-major matrix, so B tiles are 2-D boxes.
 // * warp 0: TMEM allocation + MMA issue (one elected thread); warps 1-3: TMA producers (k-block i is
 //   issued by producer i mod 3: one thread cannot issue TMA boxes fast enough to keep HBM busy);
-//   warps 4-11: epilogue.  Two TMEM accumulator buffers let the epilogue of tile i overlap the
+//   warps 4-19: epilogue (four per TMEM lane quarter; two when BN = 64).  Two TMEM accumulator buffers let the epilogue of tile i overlap the
 //   MMAs of tile i+1.  Each epilogue warp owns 32 accumulator rows (its TMEM lane quarter) and
 //   half of the tile's columns: tcgen05.ld -> bias/scale/sum/ReLU/round/saturate in registers ->
 //   (one-byte outputs) a swizzled shared-memory staging block of its own -> one TMA store, so
@@ -36,12 +36,16 @@ namespace b200
 #ifdef B200_PROFILE_WAITS
     // debug build only: wait cycles per role of CTA 0 ([0] producer/empty, [1] mma/full, [2] mma/tempty,
     // [3] epilogue/tfull, [4] epilogue body, [5] kernel total, [6] tiles of CTA 0)
-    __device__ long long g_wait_cycles[8];
+    __device__ long long g_wait_cycles[16];
+#define PROF_MARK(var) long long var = clock64()
+#define PROF_SPAN(i, a, b) do { if (blockIdx.x == 0 && warp == 4 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[i]), (unsigned long long)((b) - (a))); } while (0)
 #define PROF_T0() long long prof_t0 = clock64()
 #define PROF_ADD(i) do { if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[i]), (unsigned long long)(clock64() - prof_t0)); } while (0)
 #else
 #define PROF_T0() do { } while (0)
 #define PROF_ADD(i) do { } while (0)
+#define PROF_MARK(var) do { } while (0)
+#define PROF_SPAN(i, a, b) do { } while (0)
 #endif
 
     __device__ int g_contract_status = 0; // 0 ok; otherwise 1000*role + detail of the wait that gave up
@@ -77,6 +81,7 @@ namespace b200
         int tiles_q, tiles_p; // patches along Q and P (tiles_m = tiles_q*tiles_p*ceil(NB/TN))
         int NB, P, Q;        // batch and output spatial size
         int sub_w, sub_h;    // 32 consecutive tile rows as a sub-patch: sub_w x sub_h x (32/(sub_w*sub_h))
+        float inv_tiles_m, inv_tiles_q, inv_tiles_p; // reciprocals for the per-tile index decode (divmod_small)
         // epilogue
         const int32_t* bias;
         const float* scale;
@@ -102,7 +107,7 @@ namespace b200
 
     constexpr int BM = 128;
     constexpr int NUM_PRODUCERS = 3;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
-    constexpr int NUM_THREADS = 384; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-11: epilogue
+    constexpr int NUM_THREADS = 640; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-19: epilogue (4-11 when BN = 64)
     constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
 
     constexpr int MAX_STAGES = 16;
@@ -114,10 +119,30 @@ namespace b200
     {
         static constexpr int A_BYTES = BM * BK;
         static constexpr int B_BYTES = BN * BK;
-        static constexpr int OUT_BYTES = BM * BN;      // 8 staging blocks of 32 rows x BN/2 bytes
+        static constexpr int OUT_BYTES = BM * BN;      // one staging block of 32 rows per epilogue warp
         static constexpr int FIXED = 2 * OUT_BYTES /*double buffered*/ + 1024 /*align slack*/ + BAR_BYTES;
         static constexpr int TMEM_COLS = 2 * BN;
     };
+
+    // n / d and n % d for 0 <= n < 2^24 without an integer division: float estimate, one correction step
+    __device__ __forceinline__ void divmod_small(int n, int d, float inv_d, int& q, int& r)
+    {
+        q = __float2int_rz(__int2float_rn(n) * inv_d);
+        r = n - q * d;
+        if (r < 0)
+        {
+            --q;
+            r += d;
+        }
+        else if (r >= d)
+        {
+            ++q;
+            r -= d;
+        }
+    }
+
+    // tile index -> (row tile, column tile) and, for the convolution, the patch origin (q0, p0, n0)
+    __device__ __forceinline__ void decode_tile(const ContractParams& p, int tile, int& tm, int& tn, int& q0, int& p0, int& n0);
 
     // ---- epilogue arithmetic ----------------------------------------------------------------
     __device__ __forceinline__ float load_sum(const void* p, int type, int64_t i)
@@ -265,19 +290,35 @@ namespace b200
         }
     }
 
+    __device__ __forceinline__ void decode_tile(const ContractParams& p, int tile, int& tm, int& tn, int& q0, int& p0, int& n0)
+    {
+        divmod_small(tile, p.tiles_m, p.inv_tiles_m, tn, tm);
+        q0 = p0 = n0 = 0;
+        if (p.conv)
+        {
+            int t, tq, tp, tnb;
+            divmod_small(tm, p.tiles_q, p.inv_tiles_q, t, tq);
+            divmod_small(t, p.tiles_p, p.inv_tiles_p, tnb, tp);
+            q0 = tq * p.TW;
+            p0 = tp * p.TH;
+            n0 = tnb * p.TN;
+        }
+    }
+
     template <int BN, int BK>
     __global__ void __launch_bounds__(NUM_THREADS, 1)
         qcontract_kernel(const __grid_constant__ TensorMaps maps, const __grid_constant__ ContractParams p)
     {
         using C = Cfg<BN, BK>;
-        constexpr int HALF = BN / 2;       // columns (= bytes of a one-byte output row) per epilogue warp
-        constexpr int CHUNKS = HALF / 32;  // 32-column chunks per epilogue warp
+        constexpr int SPLIT = BN >= 128 ? 4 : 2; // epilogue warps per TMEM lane quarter
+        constexpr int COLS = BN / SPLIT;         // columns (= bytes of a one-byte output row) per epilogue warp: 64 or 32
+        constexpr int CHUNKS = COLS / 32;        // 32-column chunks per epilogue warp
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
         // per epilogue warp: scale and bias of its column half of the current column tile
-        __shared__ __align__(16) float epi_scale[8][HALF];
-        __shared__ __align__(16) int32_t epi_bias[8][HALF];
+        __shared__ __align__(16) float epi_scale[4 * SPLIT][COLS];
+        __shared__ __align__(16) int32_t epi_bias[4 * SPLIT][COLS];
 
         // [resident B] [stages x (A [+ B])] [2 x output staging] [mbarriers]; every region is a multiple of 1024 bytes
         const int STAGES = p.smem.stages;
@@ -308,7 +349,7 @@ namespace b200
             for (int b = 0; b < 2; ++b)
             {
                 ptx::mbar_init(tfull_bar(b), 1);
-                ptx::mbar_init(tempty_bar(b), 8);
+                ptx::mbar_init(tempty_bar(b), 4 * SPLIT);
             }
             ptx::fence_barrier_init();
         }
@@ -348,16 +389,8 @@ namespace b200
                 }
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
                 {
-                    const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                    int q0 = 0, p0 = 0, n0 = 0;
-                    if (p.conv)
-                    {
-                        int t = tm;
-                        q0 = (t % p.tiles_q) * p.TW;
-                        t /= p.tiles_q;
-                        p0 = (t % p.tiles_p) * p.TH;
-                        n0 = (t / p.tiles_p) * p.TN;
-                    }
+                    int tm, tn, q0, p0, n0;
+                    decode_tile(p, tile, tm, tn, q0, p0, n0);
                     int kcol = 0; // byte column of the k-block in the B matrix
                     for (int tap = 0; tap < p.ntaps && !fail; ++tap)
                     {
@@ -368,7 +401,7 @@ namespace b200
                             if (turn == pw)
                             {
                                 PROF_T0();
-                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp))
+                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp, 64))
                                 {
                                     fail = 1001;
                                     break;
@@ -409,7 +442,7 @@ namespace b200
                 const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + C::A_BYTES, BK);
                 // descriptor address fields count 16-byte units
                 const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
-                if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp))
+                if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp, 32))
                     fail = 2003;
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
@@ -417,7 +450,7 @@ namespace b200
                     const uint32_t acc_ph = (tile_it >> 1) & 1;
                     {
                         PROF_T0();
-                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp))
+                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, 32))
                         {
                             fail = 2001;
                             break;
@@ -430,7 +463,7 @@ namespace b200
                     {
                         {
                             PROF_T0();
-                            if (!ptx::mbar_wait(full_bar(s), ph, abortp))
+                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, 20))
                             {
                                 fail = 2002;
                                 break;
@@ -462,36 +495,51 @@ namespace b200
         }
         else
         {
-            // ------------------------------------------------------------ epilogue (warps 4..11)
-            // TMEM lane quarter (warp id % 4) is fixed by the hardware; the two warps that share a
-            // quarter split the tile's columns between them.
+            // ------------------------------------------------------------ epilogue (warps 4..)
+            // TMEM lane quarter (warp id % 4) is fixed by the hardware; the SPLIT warps that share a quarter
+            // split the tile's columns between them (COLS each).  Warps beyond 4*SPLIT have nothing to do.
             const int quarter = warp & 3;
-            const int half = (warp - 4) >> 2;
-            const int ew = warp - 4; // 0..7
+            const int part = (warp - 4) >> 2;    // which column part of the tile
+            const int ew = warp - 4;             // 0 .. 4*SPLIT-1
+            if (part < SPLIT)
+            {
             const int row = quarter * 32 + lane; // accumulator row of this thread
+            // position of this row (and of the warp's first row) inside the output patch: the same for every tile
+            int row_w = 0, row_h = 0, row_n = 0, blk_w = 0, blk_h = 0, blk_n = 0;
+            if (p.conv)
+            {
+                row_w = row % p.TW;
+                row_h = (row / p.TW) % p.TH;
+                row_n = row / (p.TW * p.TH);
+                const int row0 = quarter * 32;
+                blk_w = row0 % p.TW;
+                blk_h = (row0 / p.TW) % p.TH;
+                blk_n = row0 / (p.TW * p.TH);
+            }
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
-            // this warp's two staging blocks (alternating per tile): 32 rows x HALF bytes, swizzled like the TMA store expects
-            const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * HALF);
-            const uint32_t sw_xor = HALF == 128 ? uint32_t(lane & 7) : HALF == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
+            // this warp's two staging blocks (alternating per tile): 32 rows x COLS bytes, swizzled like the TMA store expects
+            const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * COLS);
+            const uint32_t sw_xor = COLS == 128 ? uint32_t(lane & 7) : COLS == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
             int stores_in_flight = 0;
             int staged_tn = -1;
             const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
             uint32_t tile_it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
             {
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                int tm, tn, q0, p0, n0;
+                decode_tile(p, tile, tm, tn, q0, p0, n0);
                 const int acc = tile_it & 1;
                 const uint32_t acc_ph = (tile_it >> 1) & 1;
-                const int colw = tn * BN + half * HALF; // first output column of this warp
+                const int colw = tn * BN + part * COLS; // first output column of this warp
                 if (tn != staged_tn)
                 {
                     // (re)stage this warp's scales and biases; the column tile changes at most tiles_n times per CTA
                     __syncwarp();
-                    for (int j = lane; j < HALF; j += 32)
+                    for (int j = lane; j < COLS; j += 32)
                     {
                         const int col = colw + j;
                         const bool in_n = col < p.N;
@@ -502,16 +550,9 @@ namespace b200
                     staged_tn = tn;
                 }
                 EpiRow er;
-                int q0 = 0, p0 = 0, n0 = 0;
                 if (p.conv)
                 {
-                    int t = tm;
-                    q0 = (t % p.tiles_q) * p.TW;
-                    t /= p.tiles_q;
-                    p0 = (t % p.tiles_p) * p.TH;
-                    n0 = (t / p.tiles_p) * p.TN;
-                    const int tw = row % p.TW, th = (row / p.TW) % p.TH, tnn = row / (p.TW * p.TH);
-                    const int q = q0 + tw, pp = p0 + th, n = n0 + tnn;
+                    const int q = q0 + row_w, pp = p0 + row_h, n = n0 + row_n;
                     er.valid = q < p.Q && pp < p.P && n < p.NB;
                     er.off = ((int64_t(n) * p.P + pp) * p.Q + q) * p.N;
                 }
@@ -521,23 +562,22 @@ namespace b200
                     er.valid = m < p.M;
                     er.off = int64_t(m) * p.N;
                 }
-                // the residual does not depend on the accumulator: chunk 0's is fetched before waiting for the
-                // MMAs, chunk c+1's while chunk c is converted
-                uint32_t sumw[2][8];
+                // the residual does not depend on the accumulator: the first chunk's is fetched before waiting for the MMAs
+                uint32_t sumw[8];
                 const bool sum_regs = has_sum && vec_ok && er.valid;
-                auto fetch_sum = [&](int c, uint32_t (&dst)[8]) {
+                auto fetch_sum = [&](int c) {
                     if (sum_regs && colw + 32 * c + 32 <= p.N)
                     {
                         const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
                         const uint4 s0 = sp[0], s1 = sp[1];
-                        dst[0] = s0.x; dst[1] = s0.y; dst[2] = s0.z; dst[3] = s0.w;
-                        dst[4] = s1.x; dst[5] = s1.y; dst[6] = s1.z; dst[7] = s1.w;
+                        sumw[0] = s0.x; sumw[1] = s0.y; sumw[2] = s0.z; sumw[3] = s0.w;
+                        sumw[4] = s1.x; sumw[5] = s1.y; sumw[6] = s1.z; sumw[7] = s1.w;
                     }
                 };
-                fetch_sum(0, sumw[0]);
+                fetch_sum(0);
                 {
                     PROF_T0();
-                    if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp))
+                    if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp, 32))
                     {
                         fail = 3001;
                         break;
@@ -548,32 +588,31 @@ namespace b200
                 ptx::tc_fence_after_sync();
                 PROF_T0();
                 const uint32_t stage_blk = stage_blk0 + (tile_it & 1) * C::OUT_BYTES;
-                const uint32_t stage_row = stage_blk + uint32_t(lane) * HALF;
+                const uint32_t stage_row = stage_blk + uint32_t(lane) * COLS;
                 if (stores_in_flight == 2)
                 {
                     // the TMA store issued two tiles ago must have finished reading this staging block
+                    PROF_MARK(t_w0);
                     if (lane == 0)
                         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
+                    PROF_MARK(t_w1);
+                    PROF_SPAN(10, t_w0, t_w1);
                     stores_in_flight = 1;
                 }
-                const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * HALF;
-                // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c is converted
-                uint32_t vbuf[2][32];
-                __syncwarp();
-                ptx::tmem_ld_32x32(t_addr, vbuf[0]);
-#pragma unroll
+                const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + part * COLS;
+#pragma unroll 1
                 for (int c = 0; c < CHUNKS; ++c)
                 {
-                    uint32_t (&v)[32] = vbuf[c & 1];
-                    uint32_t w[8];
+                    uint32_t v[32], w[8];
+                    if (c > 0)
+                        fetch_sum(c);
+                    __syncwarp();
+                    PROF_MARK(t_a);
+                    ptx::tmem_ld_32x32(t_addr + 32 * c, v);
                     ptx::tmem_ld_wait();
-                    if (c + 1 < CHUNKS)
-                    {
-                        __syncwarp();
-                        ptx::tmem_ld_32x32(t_addr + 32 * (c + 1), vbuf[(c + 1) & 1]);
-                        fetch_sum(c + 1, sumw[(c + 1) & 1]);
-                    }
+                    PROF_MARK(t_b);
+                    PROF_SPAN(8, t_a, t_b);
                     const int col0 = colw + 32 * c;
                     if (col0 < p.N) // warp-uniform
                     {
@@ -581,11 +620,13 @@ namespace b200
                         const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
                         const bool bytes_path = !p.half_away && esz == 1 && (!has_sum || (sum_regs && full_chunk) || !er.valid);
                         if (bytes_path && has_sum && er.valid)
-                            epilogue_chunk_bytes<true>(v, w, sc, bi, sumw[c & 1], sum_scale, p.sum_type == B200_U8, p.relu != 0, p.out_type == B200_U8);
+                            epilogue_chunk_bytes<true>(v, w, sc, bi, sumw, sum_scale, p.sum_type == B200_U8, p.relu != 0, p.out_type == B200_U8);
                         else if (bytes_path)
-                            epilogue_chunk_bytes<false>(v, w, sc, bi, sumw[c & 1], sum_scale, false, p.relu != 0, p.out_type == B200_U8);
+                            epilogue_chunk_bytes<false>(v, w, sc, bi, sumw, sum_scale, false, p.relu != 0, p.out_type == B200_U8);
                         else
                             epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
+                        PROF_MARK(t_c);
+                        PROF_SPAN(9, t_b, t_c);
                         if (p.tma_store)
                         {
                             // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
@@ -652,11 +693,9 @@ namespace b200
                         // lane 0 holds the first row of the block: a block that starts outside the tensor is skipped
                         if (p.conv && er.valid)
                         {
-                            const int row0 = quarter * 32;
-                            const int tw0 = row0 % p.TW, th0 = (row0 / p.TW) % p.TH, tn0 = row0 / (p.TW * p.TH);
                             asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + tw0),
-                                         "r"(p0 + th0), "r"(n0 + tn0) : "memory");
+                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + blk_w),
+                                         "r"(p0 + blk_h), "r"(n0 + blk_n) : "memory");
                         }
                         else if (!p.conv && er.valid)
                         {
@@ -672,6 +711,7 @@ namespace b200
             // stores must be complete (not just read) before the CTA exits
             if (lane == 0)
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            }
         }
 
         // ------------------------------------------------------------ common tail
@@ -780,6 +820,11 @@ namespace b200
         }
         // shared-memory plan: keep B resident when there is a single column tile and it is small; give the
         // rest to pipeline stages (more bytes in flight hide the HBM latency of the activation stream)
+        p.inv_tiles_m = 1.0f / float(p.tiles_m);
+        p.inv_tiles_q = p.conv ? 1.0f / float(p.tiles_q) : 1.0f;
+        p.inv_tiles_p = p.conv ? 1.0f / float(p.tiles_p) : 1.0f;
+        if (int64_t(p.tiles_m) * p.tiles_n >= (1 << 24))
+            return B200_ERR_TOO_LARGE;
         const int nkb = p.ntaps * p.cblocks;
         SmemPlan& sp = p.smem;
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
@@ -876,7 +921,7 @@ namespace b200
 #ifdef B200_PROFILE_WAITS
 extern "C" __attribute__((visibility("default"))) int b200_debug_wait_cycles(long long* out8, int reset)
 {
-    long long z[8] = {0};
+    long long z[16] = {0};
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out8, b200::g_wait_cycles, sizeof(z));
     if (reset)
@@ -944,10 +989,11 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
         return rc;
     if (p.tma_store)
     {
-        // each epilogue warp stores 32 rows x bn/2 bytes
+        // each epilogue warp stores 32 rows x (its share of the tile's columns) bytes
+        const int cols = bn >= 128 ? bn / 4 : bn / 2;
         uint64_t dims_o[2] = {uint64_t(N), uint64_t(M)}, str_o[1] = {uint64_t(N)};
-        uint32_t box_o[2] = {uint32_t(bn / 2), 32u};
-        rc = make_map(&maps.out, out, 2, dims_o, str_o, box_o, bn / 2);
+        uint32_t box_o[2] = {uint32_t(cols), 32u};
+        rc = make_map(&maps.out, out, 2, dims_o, str_o, box_o, cols);
         if (rc != B200_OK)
             return rc;
     }
@@ -1082,8 +1128,90 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
         // each epilogue warp stores the 32 tile rows of its TMEM lane quarter: a sub-patch of the tile
         uint64_t dims_o[4] = {uint64_t(c->K), uint64_t(Q), uint64_t(P), uint64_t(c->N)};
         uint64_t str_o[3] = {uint64_t(c->K), uint64_t(c->K) * Q, uint64_t(c->K) * Q * P};
-        uint32_t box_o[4] = {uint32_t(bn / 2), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
-        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, bn / 2);
+        const int cols = bn >= 128 ? bn / 4 : bn / 2;
+        uint32_t box_o[4] = {uint32_t(cols), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, cols);
+        if (rc != B200_OK)
+            return rc;
+    }
+    return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
+}
+
+// Stride-2, <= 4 channel convolution on the cell grid made by b200_stem_pack_input (see layout.cu): Rc taps
+// (cell rows) of one 64-byte K-block each; the A tensor map's pixel dimension advances one cell (16 bytes)
+// per output column, so neighbouring windows overlap.
+extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* packed_filters, void* out, int64_t N,
+                               int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                               int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue, void* stream)
+{
+    using namespace b200;
+    if (data_type != B200_U8 && data_type != B200_I8)
+        return B200_ERR_INVALID_ARGUMENT;
+    int64_t P, Q, Hc, Wc, Rc;
+    int rc = b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc);
+    if (rc != B200_OK)
+        return rc;
+    if (N < 0 || K <= 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    rc = check_epilogue(epilogue, K);
+    if (rc != B200_OK)
+        return rc;
+    if (N == 0)
+        return B200_OK;
+    if (!cells || !packed_filters || !out || (reinterpret_cast<uintptr_t>(cells) & 15) ||
+        (reinterpret_cast<uintptr_t>(packed_filters) & 15))
+        return B200_ERR_INVALID_ARGUMENT;
+    if (N * P * Q > 0x7FFFFFFF || Rc > MAX_TAPS)
+        return B200_ERR_TOO_LARGE;
+
+    const int bk = 64;
+    ContractParams p = {};
+    p.conv = 1;
+    p.N = int(K);
+    p.cblocks = 1;
+    p.ntaps = int(Rc);
+    for (int r = 0; r < Rc; ++r)
+    {
+        p.taps[r].dh = short(r);
+        p.taps[r].dw = 0;
+        p.taps[r].map = 0;
+        p.taps[r].pad = 0;
+    }
+    p.NB = int(N);
+    p.P = int(P);
+    p.Q = int(Q);
+    pick_patch(N, P, Q, p.TW, p.TH, p.TN);
+    p.sub_w = p.TW < 32 ? p.TW : 32;
+    p.sub_h = (p.TH < 32 / p.sub_w) ? p.TH : 32 / p.sub_w;
+    p.tiles_q = int((Q + p.TW - 1) / p.TW);
+    p.tiles_p = int((P + p.TH - 1) / p.TH);
+    p.tiles_m = p.tiles_q * p.tiles_p * int((N + p.TN - 1) / p.TN);
+    const int bn = pick_bn(K, p.tiles_m);
+    p.tiles_n = int((K + bn - 1) / bn);
+    fill_epilogue(p, epilogue, out, data_type);
+    p.idesc = make_idesc(data_type, bn);
+
+    TensorMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    // windows of 4 cells (64 bytes) starting at every cell: dimension 1 steps 16 bytes
+    uint64_t dims[4] = {64, uint64_t(Q), uint64_t(Hc), uint64_t(N)};
+    uint64_t str[3] = {16, uint64_t(Wc) * 16, uint64_t(Wc) * Hc * 16};
+    uint32_t box[4] = {64, uint32_t(p.TW), uint32_t(p.TH), uint32_t(p.TN)};
+    rc = make_map(&maps.a[0], cells, 4, dims, str, box, bk);
+    if (rc != B200_OK)
+        return rc;
+    uint64_t dims_b[2] = {uint64_t(Rc) * 64, uint64_t(K)}, str_b[1] = {uint64_t(Rc) * 64};
+    uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
+    rc = make_map(&maps.b, packed_filters, 2, dims_b, str_b, box_b, bk);
+    if (rc != B200_OK)
+        return rc;
+    if (p.tma_store)
+    {
+        uint64_t dims_o[4] = {uint64_t(K), uint64_t(Q), uint64_t(P), uint64_t(N)};
+        uint64_t str_o[3] = {uint64_t(K), uint64_t(K) * Q, uint64_t(K) * Q * P};
+        const int cols = bn >= 128 ? bn / 4 : bn / 2;
+        uint32_t box_o[4] = {uint32_t(cols), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, cols);
         if (rc != B200_OK)
             return rc;
     }

@@ -119,6 +119,37 @@ def qconv(data, filters, scale, out_dtype, cp, bias=None, relu=False, sum_in=Non
     return out
 
 
+def stem_geometry(h, w, r, s, pad_below, pad_above):
+    vals = [ctypes.c_int64() for _ in range(5)]
+    check(LIB.b200_stem_geometry(h, w, r, s, pad_below[0], pad_below[1], pad_above[0], pad_above[1],
+                                 *[ctypes.byref(v) for v in vals]), "b200_stem_geometry")
+    return tuple(v.value for v in vals)  # P, Q, Hc, Wc, Rc
+
+
+def qconv_stem(data_nchw, filters_kcrs, scale, out_dtype, pad_below, pad_above=None, bias=None, relu=False):
+    """Stride-2 convolution over <= 4 channels: NCHW one-byte data, host KCRS int8 filters (numpy) -> [N,P,Q,K]."""
+    import numpy as np
+    pad_above = pad_below if pad_above is None else pad_above
+    data = _dev(data_nchw)
+    n, c, h, w = data.shape
+    f = np.ascontiguousarray(filters_kcrs, dtype=np.int8)
+    k, c2, r, s = f.shape
+    assert c == c2
+    p, q, hc, wc, rc = stem_geometry(h, w, r, s, pad_below, pad_above)
+    packed = np.empty((k, rc * 64), np.int8)
+    check(LIB.b200_stem_pack_filter_host(f.ctypes.data, packed.ctypes.data, k, c, r, s, pad_below[0], pad_below[1]),
+          "b200_stem_pack_filter_host")
+    packed_d = torch.from_numpy(packed).to(data.device)
+    cells = torch.empty((n, hc, wc, 16), dtype=torch.uint8, device=data.device)
+    check(LIB.b200_stem_pack_input(_ptr(data), _ptr(cells), n, c, h, w, r, s, pad_below[0], pad_below[1], pad_above[0],
+                                   pad_above[1], _stream()), "b200_stem_pack_input")
+    e, keep = _epilogue(k, scale, out_dtype, bias, relu)
+    out = torch.empty((n, p, q, k), dtype=out_dtype, device=data.device)
+    check(LIB.b200_qconv_stem(_ptr(cells), _DT[data.dtype], _ptr(packed_d), _ptr(out), n, h, w, k, r, s, pad_below[0],
+                              pad_below[1], pad_above[0], pad_above[1], ctypes.byref(e), _stream()), "b200_qconv_stem")
+    return out
+
+
 def nchw_to_nhwc(x, c_pad=None):
     x = _dev(x)
     assert x.element_size() == 1

@@ -247,3 +247,37 @@ def test_layout_and_pooling(ops):
     big = rng.integers(0, 256, size=(4, 64, 30, 30)).astype(np.uint8)
     got = ops.maxpool_nhwc(dev(nhwc(big)), (3, 3), (2, 2), (1, 1), (1, 1)).cpu().numpy()
     np.testing.assert_array_equal(got.transpose(0, 3, 1, 2), ref.maxpool_u8(big, (3, 3), (2, 2), (1, 1), (1, 1)))
+
+
+# ---------------------------------------------------------------- stride-2 small-channel stem (space-to-depth path)
+STEM_CASES = [
+    # N, C, H, W, K, R, S, pad_below, pad_above, data dtype
+    (2, 3, 32, 32, 64, 7, 7, (3, 3), (3, 3), np.int8),     # the ResNet stem geometry, small image
+    (1, 3, 224, 224, 64, 7, 7, (3, 3), (3, 3), np.uint8),  # full ResNet stem
+    (3, 1, 17, 23, 16, 3, 3, (1, 1), (1, 1), np.uint8),    # odd sizes, one channel
+    (2, 4, 20, 18, 32, 5, 7, (2, 3), (1, 2), np.uint8),    # asymmetric padding, four channels
+    (2, 2, 16, 16, 24, 8, 8, (0, 0), (0, 0), np.int8),     # even filter without padding
+    (1, 3, 9, 9, 8, 7, 7, (2, 2), (3, 3), np.uint8),       # even padding below
+]
+
+
+@pytest.mark.parametrize("case", STEM_CASES, ids=lambda c: "x".join(str(v) for v in c[:7]))
+def test_qconv_stem_vs_oracle(ops, case):
+    n, c, h, w, k, r, s, pb, pa, dt = case
+    rng = np.random.default_rng(hash(case[:7]) & 0xFFFF)
+    info = np.iinfo(dt)
+    data = rng.integers(info.min, info.max + 1, (n, c, h, w)).astype(dt)
+    filt = rng.integers(-127, 128, (k, c, r, s)).astype(np.int8)
+    bias = rng.integers(-2000, 2000, k).astype(np.int32)
+    scale = (rng.uniform(0.5, 1.5, k) * 255.0 / (c * r * s * 127 * 40)).astype(np.float32)
+    cs = ref.conv_shape(data.shape, filt.shape, (2, 2), pb, pa)
+    for out_dt, relu in ((np.uint8, True), (np.int8, False)):
+        exp = ref.qconv_fused(data, filt, bias, scale, cs, out_dt, relu=relu)
+        got = ops.qconv_stem(dev(data), filt, dev(scale), TDT[np.dtype(out_dt)], pb, pa, bias=dev(bias), relu=relu)
+        np.testing.assert_array_equal(got.cpu().numpy().transpose(0, 3, 1, 2), exp)
+
+
+def test_stem_rejects_wide_filters(ops):
+    from ngraph_b200 import lib
+    with pytest.raises(lib.B200Error):
+        ops.stem_geometry(32, 32, 9, 9, (0, 0), (0, 0))
