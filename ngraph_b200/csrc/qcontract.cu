@@ -28,6 +28,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -90,6 +91,7 @@ namespace b200
         int sum_type;
         const float* sum_scale;
         int relu, half_away, out_zp, out_type;
+        int one;             // the constant 1, opaque to the compiler (see add_fma_pipe)
         int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
         int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
@@ -109,6 +111,23 @@ namespace b200
     constexpr int NUM_PRODUCERS = 3;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
     constexpr int NUM_THREADS = 640; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-19: epilogue (4-11 when BN = 64)
     constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
+
+    // Sleep between two polls of an mbarrier, per waiting role: a polling warp takes issue slots from the epilogue
+    // warps of its scheduler, so the waits that are long in steady state sleep longest.
+#ifndef B200_BACKOFF_EMPTY_NS
+#define B200_BACKOFF_EMPTY_NS 64
+#endif
+#ifndef B200_BACKOFF_FULL_NS
+#define B200_BACKOFF_FULL_NS 20
+#endif
+#ifndef B200_BACKOFF_TEMPTY_NS
+#define B200_BACKOFF_TEMPTY_NS 32
+#endif
+#ifndef B200_BACKOFF_TFULL_NS
+#define B200_BACKOFF_TFULL_NS 32
+#endif
+    constexpr uint32_t BACKOFF_EMPTY_NS = B200_BACKOFF_EMPTY_NS, BACKOFF_FULL_NS = B200_BACKOFF_FULL_NS,
+                       BACKOFF_TEMPTY_NS = B200_BACKOFF_TEMPTY_NS, BACKOFF_TFULL_NS = B200_BACKOFF_TFULL_NS;
 
     constexpr int MAX_STAGES = 16;
     constexpr int BAR_BYTES = 512;          // (2*MAX_STAGES + 5) mbarriers
@@ -199,45 +218,99 @@ namespace b200
         return r;
     }
 
+    // acc + bias as a multiply-add by a run-time 1: the integer multiply-add runs on the FMA pipe, which has
+    // issue slots to spare here, while a plain add would join the conversions and packs on the ALU pipe
+    // (the pipe that bounds this epilogue).
+    __device__ __forceinline__ int32_t add_fma_pipe(int32_t a, int32_t b, int32_t one)
+    {
+        int32_t d;
+        asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(one), "r"(b));
+        return d;
+    }
+
+    // Two IEEE single operations in one instruction (sm_100 packed fp32): each half is rounded on its own, so the
+    // results are those of two scalar operations.
+    struct F2
+    {
+        float x, y;
+    };
+    __device__ __forceinline__ uint64_t pack_f2(float a, float b)
+    {
+        uint64_t r;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+        return r;
+    }
+    __device__ __forceinline__ F2 unpack_f2(uint64_t v)
+    {
+        F2 r;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+        return r;
+    }
+    __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+    {
+        uint64_t d;
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+        return d;
+    }
+    __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+    {
+        uint64_t d;
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+        return d;
+    }
+
     // One 32-column chunk of one accumulator row, fused-op contract, one-byte output (the hot case):
     // w[] <- saturate(round_half_even(relu(float(acc + bias) * scale [+ sum_scale * float(sum)]))).
-    // sc / bi: shared-memory addresses of this chunk's 32 staged scales / biases.
-    template <bool HAS_SUM>
+    // sc / bi: shared-memory addresses of this chunk's 32 staged scales / biases.  The variant is chosen once
+    // per chunk so that the unrolled body has no branches.  RELU_F is only needed for int8 outputs: for u8
+    // the unsigned saturation already is max(v, 0).
+    template <bool HAS_SUM, bool RELU_F, bool OUT_U8>
     __device__ __forceinline__ void epilogue_chunk_bytes(const uint32_t (&v)[32], uint32_t (&w)[8], uint32_t sc, uint32_t bi,
-                                                         const uint32_t* sumw, float sum_scale, bool sum_u8, bool relu, bool out_u8)
+                                                         const uint32_t* sumw, float sum_scale, uint32_t sum_flip, float sum_magic,
+                                                         int32_t one)
     {
+        const uint64_t sum_scale2 = pack_f2(sum_scale, sum_scale), neg_magic2 = pack_f2(-sum_magic, -sum_magic);
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4)
         {
             const float4 s4 = lds_f4(sc + 16 * j4);
             const int4 b4 = lds_i4(bi + 16 * j4);
-            float f0 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 0]) + b4.x), s4.x);
-            float f1 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 1]) + b4.y), s4.y);
-            float f2 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 2]) + b4.z), s4.z);
-            float f3 = __fmul_rn(__int2float_rn(int32_t(v[4 * j4 + 3]) + b4.w), s4.w);
+            const float a0 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 0]), b4.x, one));
+            const float a1 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 1]), b4.y, one));
+            const float a2 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 2]), b4.z, one));
+            const float a3 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 3]), b4.w, one));
+            uint64_t f01 = mul2(pack_f2(a0, a1), pack_f2(s4.x, s4.y));
+            uint64_t f23 = mul2(pack_f2(a2, a3), pack_f2(s4.z, s4.w));
             if (HAS_SUM)
             {
-                const uint32_t sw = sumw[j4];
-                const int m0 = sum_u8 ? int(sw & 0xFF) : int(int8_t(sw)), m1 = sum_u8 ? int((sw >> 8) & 0xFF) : int(int8_t(sw >> 8));
-                const int m2 = sum_u8 ? int((sw >> 16) & 0xFF) : int(int8_t(sw >> 16)), m3 = sum_u8 ? int(sw >> 24) : int(int8_t(sw >> 24));
-                f0 = __fadd_rn(f0, __fmul_rn(sum_scale, __int2float_rn(m0)));
-                f1 = __fadd_rn(f1, __fmul_rn(sum_scale, __int2float_rn(m1)));
-                f2 = __fadd_rn(f2, __fmul_rn(sum_scale, __int2float_rn(m2)));
-                f3 = __fadd_rn(f3, __fmul_rn(sum_scale, __int2float_rn(m3)));
+                // float(byte) without a conversion instruction: the byte is placed in the mantissa of 2^23 and 2^23
+                // (+128 when the byte is a biased int8) is subtracted, both steps exact
+                const uint32_t sw = sumw[j4] ^ sum_flip; // int8 residuals become biased bytes (value + 128)
+                const uint64_t m01 = pack_f2(__uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7650u)),
+                                             __uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7651u)));
+                const uint64_t m23 = pack_f2(__uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7652u)),
+                                             __uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7653u)));
+                // the products and the final additions are rounded separately (the fused ops add the residual term
+                // unfused); the additions are scalar intrinsics, which the compiler never contracts with a multiply
+                const F2 t01 = unpack_f2(mul2(sum_scale2, add2(m01, neg_magic2))), t23 = unpack_f2(mul2(sum_scale2, add2(m23, neg_magic2)));
+                const F2 g01 = unpack_f2(f01), g23 = unpack_f2(f23);
+                f01 = pack_f2(__fadd_rn(g01.x, t01.x), __fadd_rn(g01.y, t01.y));
+                f23 = pack_f2(__fadd_rn(g23.x, t23.x), __fadd_rn(g23.y, t23.y));
             }
-            if (relu && !out_u8) // for u8 the unsigned saturation below already is max(v, 0)
+            F2 r01 = unpack_f2(f01), r23 = unpack_f2(f23);
+            if (RELU_F)
             {
                 // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0)
-                f0 = fmaxf(f0, 0.0f);
-                f1 = fmaxf(f1, 0.0f);
-                f2 = fmaxf(f2, 0.0f);
-                f3 = fmaxf(f3, 0.0f);
+                r01.x = fmaxf(r01.x, 0.0f);
+                r01.y = fmaxf(r01.y, 0.0f);
+                r23.x = fmaxf(r23.x, 0.0f);
+                r23.y = fmaxf(r23.y, 0.0f);
             }
             // Quantize(scale 1, zp 0, ROUND_NEAREST_TOWARD_EVEN) to 8 bits: the literal floor(v+0.5) / ceil(v-0.5) /
             // parity sequence equals round-half-even for |v| < 2^23 and everything beyond saturates, so cvt.rni
             // (saturating, NaN -> 0) followed by a saturating pack gives the same byte.
-            const int i0 = __float2int_rn(f0), i1 = __float2int_rn(f1), i2 = __float2int_rn(f2), i3 = __float2int_rn(f3);
-            w[j4] = out_u8 ? pack4_u8(i0, i1, i2, i3) : pack4_s8(i0, i1, i2, i3);
+            const int i0 = __float2int_rn(r01.x), i1 = __float2int_rn(r01.y), i2 = __float2int_rn(r23.x), i3 = __float2int_rn(r23.y);
+            w[j4] = OUT_U8 ? pack4_u8(i0, i1, i2, i3) : pack4_s8(i0, i1, i2, i3);
         }
     }
 
@@ -401,7 +474,7 @@ namespace b200
                             if (turn == pw)
                             {
                                 PROF_T0();
-                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp, 64))
+                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp, BACKOFF_EMPTY_NS))
                                 {
                                     fail = 1001;
                                     break;
@@ -442,7 +515,7 @@ namespace b200
                 const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + C::A_BYTES, BK);
                 // descriptor address fields count 16-byte units
                 const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
-                if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp, 32))
+                if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp, BACKOFF_FULL_NS))
                     fail = 2003;
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
@@ -450,7 +523,7 @@ namespace b200
                     const uint32_t acc_ph = (tile_it >> 1) & 1;
                     {
                         PROF_T0();
-                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, 32))
+                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS))
                         {
                             fail = 2001;
                             break;
@@ -463,7 +536,7 @@ namespace b200
                     {
                         {
                             PROF_T0();
-                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, 20))
+                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
                             {
                                 fail = 2002;
                                 break;
@@ -518,195 +591,300 @@ namespace b200
             }
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
+            const uint32_t sum_flip = p.sum_type == B200_U8 ? 0u : 0x80808080u;
+            const float sum_magic = p.sum_type == B200_U8 ? 8388608.0f : 8388736.0f;
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
             // this warp's two staging blocks (alternating per tile): 32 rows x COLS bytes, swizzled like the TMA store expects
             const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * COLS);
             const uint32_t sw_xor = COLS == 128 ? uint32_t(lane & 7) : COLS == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
-            int stores_in_flight = 0;
-            int staged_tn = -1;
+            // branch-free chunk body for the fused contract with one-byte outputs: u8 {0: plain, 1: +sum},
+            // i8 {2, 3}, i8 with relu {4, 5}; -1: the general path (core contract, 4-byte outputs, unaligned residuals)
+            int bytes_variant = -1;
+            if (!p.half_away && esz == 1 && (!has_sum || vec_ok))
+                bytes_variant = (p.out_type == B200_U8 ? 0 : (p.relu ? 4 : 2)) + (has_sum ? 1 : 0);
             const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
-            uint32_t tile_it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
-            {
-                int tm, tn, q0, p0, n0;
-                decode_tile(p, tile, tm, tn, q0, p0, n0);
-                const int acc = tile_it & 1;
-                const uint32_t acc_ph = (tile_it >> 1) & 1;
-                const int colw = tn * BN + part * COLS; // first output column of this warp
-                if (tn != staged_tn)
+            // per-row addresses are only needed for residual loads and for stores that do not go through TMA
+            const bool need_rows = has_sum || !p.tma_store;
+
+            // The tile loop, compiled once per MODE.  MODE 0..5 = bytes_variant with TMA stores and a width that is a
+            // multiple of COLS (every chunk full, every residual vector aligned): all the per-chunk decisions
+            // are made at compile time.  MODE -1 is the general loop (any contract, type and width).
+            auto epilogue_loop = [&](auto mode_tag) {
+                constexpr int MODE = decltype(mode_tag)::value;
+                constexpr bool FAST = MODE >= 0;
+                constexpr bool F_SUM = FAST && (MODE & 1), F_RELU = MODE >= 4, F_U8 = MODE >= 0 && MODE < 2;
+                int stores_in_flight = 0;
+                int staged_tn = -1;
+                uint32_t tile_it = 0;
+                // Tile coordinates: every 32 tiles each lane decodes one of the warp's next 32 tiles (the divisions are
+                // done once per tile instead of once per tile and lane) and the loop broadcasts them with shuffles.
+                int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
+                for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
-                    // (re)stage this warp's scales and biases; the column tile changes at most tiles_n times per CTA
-                    __syncwarp();
-                    for (int j = lane; j < COLS; j += 32)
+                    if ((tile_it & 31) == 0)
                     {
-                        const int col = colw + j;
-                        const bool in_n = col < p.N;
-                        epi_scale[ew][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
-                        epi_bias[ew][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
+                        const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * gridDim.x;
+                        if (t < num_tiles)
+                        {
+                            int tm_, tn_, q0_, p0_, n0_;
+                            decode_tile(p, static_cast<int>(t), tm_, tn_, q0_, p0_, n0_);
+                            info_a = p.conv ? q0_ : tm_;
+                            info_b = p0_;
+                            info_c = n0_;
+                            info_d = tn_;
+                        }
                     }
-                    __syncwarp();
-                    staged_tn = tn;
-                }
-                EpiRow er;
-                if (p.conv)
-                {
-                    const int q = q0 + row_w, pp = p0 + row_h, n = n0 + row_n;
-                    er.valid = q < p.Q && pp < p.P && n < p.NB;
-                    er.off = ((int64_t(n) * p.P + pp) * p.Q + q) * p.N;
-                }
-                else
-                {
-                    const int m = tm * BM + row;
-                    er.valid = m < p.M;
-                    er.off = int64_t(m) * p.N;
-                }
-                // the residual does not depend on the accumulator: the first chunk's is fetched before waiting for the MMAs
-                uint32_t sumw[8];
-                const bool sum_regs = has_sum && vec_ok && er.valid;
-                auto fetch_sum = [&](int c) {
-                    if (sum_regs && colw + 32 * c + 32 <= p.N)
+                    const int src_lane = tile_it & 31;
+                    const int ia = __shfl_sync(0xffffffffu, info_a, src_lane);
+                    const int p0 = __shfl_sync(0xffffffffu, info_b, src_lane);
+                    const int n0 = __shfl_sync(0xffffffffu, info_c, src_lane);
+                    const int tn = __shfl_sync(0xffffffffu, info_d, src_lane);
+                    const int tm = ia, q0 = ia;
+                    const int acc = tile_it & 1;
+                    const uint32_t acc_ph = (tile_it >> 1) & 1;
+                    const int colw = tn * BN + part * COLS; // first output column of this warp
+                    if (tn != staged_tn)
                     {
-                        const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
-                        const uint4 s0 = sp[0], s1 = sp[1];
-                        sumw[0] = s0.x; sumw[1] = s0.y; sumw[2] = s0.z; sumw[3] = s0.w;
-                        sumw[4] = s1.x; sumw[5] = s1.y; sumw[6] = s1.z; sumw[7] = s1.w;
+                        // (re)stage this warp's scales and biases; the column tile changes at most tiles_n times per CTA
+                        __syncwarp();
+                        for (int j = lane; j < COLS; j += 32)
+                        {
+                            const int col = colw + j;
+                            const bool in_n = col < p.N;
+                            epi_scale[ew][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
+                            epi_bias[ew][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
+                        }
+                        __syncwarp();
+                        staged_tn = tn;
                     }
-                };
-                fetch_sum(0);
-                {
+                    EpiRow er;
+                    er.valid = false;
+                    er.off = 0;
+                    // is the first row of this warp's 32-row block inside the tensor (else the whole block is outside)
+                    bool blk_valid;
+                    const bool rows = FAST ? F_SUM : need_rows;
+                    if (p.conv)
+                    {
+                        blk_valid = q0 + blk_w < p.Q && p0 + blk_h < p.P && n0 + blk_n < p.NB;
+                        if (rows)
+                        {
+                            const int q = q0 + row_w, pp = p0 + row_h, n = n0 + row_n;
+                            er.valid = q < p.Q && pp < p.P && n < p.NB;
+                            er.off = ((int64_t(n) * p.P + pp) * p.Q + q) * p.N;
+                        }
+                    }
+                    else
+                    {
+                        blk_valid = tm * BM + quarter * 32 < p.M;
+                        if (rows)
+                        {
+                            const int m = tm * BM + row;
+                            er.valid = m < p.M;
+                            er.off = int64_t(m) * p.N;
+                        }
+                    }
+                    // The residual does not depend on the accumulator: it is fetched before waiting for the MMAs (every
+                    // chunk's in the fast modes, the first chunk's otherwise).  Rows outside the tensor and columns
+                    // beyond the width compute on a zero residual and are never stored.
+                    uint32_t sumw[FAST ? CHUNKS : 1][8];
+#pragma unroll
+                    for (int c = 0; c < (FAST ? CHUNKS : 1); ++c)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            sumw[c][j] = 0;
+                    const bool sum_regs = (FAST ? F_SUM : (has_sum && vec_ok)) && er.valid;
+                    auto fetch_sum = [&](int c, uint32_t (&dst)[8]) {
+                        if (sum_regs && colw + 32 * c + 32 <= p.N)
+                        {
+                            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
+                            const uint4 s0 = sp[0], s1 = sp[1];
+                            dst[0] = s0.x; dst[1] = s0.y; dst[2] = s0.z; dst[3] = s0.w;
+                            dst[4] = s1.x; dst[5] = s1.y; dst[6] = s1.z; dst[7] = s1.w;
+                        }
+                    };
+                    if (FAST)
+                    {
+                        if (F_SUM)
+                        {
+#pragma unroll
+                            for (int c = 0; c < CHUNKS; ++c)
+                                fetch_sum(c, sumw[FAST ? c : 0]);
+                        }
+                    }
+                    else
+                        fetch_sum(0, sumw[0]);
+                    {
+                        PROF_T0();
+                        // the verdict is made warp-uniform: the loop body uses full-mask shuffles and warp syncs
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp, BACKOFF_TFULL_NS)))
+                        {
+                            fail = 3001;
+                            break;
+                        }
+                        if (warp == 4 && lane == 0)
+                            PROF_ADD(3);
+                    }
+                    ptx::tc_fence_after_sync();
                     PROF_T0();
-                    if (!ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp, 32))
+                    const uint32_t stage_blk = stage_blk0 + (tile_it & 1) * C::OUT_BYTES;
+                    const uint32_t stage_row = stage_blk + uint32_t(lane) * COLS;
+                    if (stores_in_flight == 2)
                     {
-                        fail = 3001;
-                        break;
+                        // the TMA store issued two tiles ago must have finished reading this staging block
+                        PROF_MARK(t_w0);
+                        if (lane == 0)
+                            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+                        PROF_MARK(t_w1);
+                        PROF_SPAN(10, t_w0, t_w1);
+                        stores_in_flight = 1;
+                    }
+                    const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + part * COLS;
+                    auto stage_bytes_out = [&](int c, const uint32_t (&w)[8]) {
+                        // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
+                        const uint32_t c16 = uint32_t(2 * c);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((c16 ^ sw_xor) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((c16 + 1) ^ sw_xor) << 4)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                    };
+                    if (FAST)
+                    {
+#pragma unroll
+                        for (int c = 0; c < CHUNKS; ++c)
+                        {
+                            uint32_t v[32], w[8];
+                            PROF_MARK(t_a);
+                            ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                            ptx::tmem_ld_wait();
+                            PROF_MARK(t_b);
+                            PROF_SPAN(8, t_a, t_b);
+                            epilogue_chunk_bytes<F_SUM, F_RELU, F_U8>(v, w, sc_base + 128u * c, bi_base + 128u * c, sumw[FAST ? c : 0], sum_scale,
+                                                                      sum_flip, sum_magic, p.one);
+                            PROF_MARK(t_c);
+                            PROF_SPAN(9, t_b, t_c);
+                            stage_bytes_out(c, w);
+                        }
+                    }
+                    else
+                    {
+#pragma unroll 1
+                    for (int c = 0; c < CHUNKS; ++c)
+                    {
+                        uint32_t v[32], w[8];
+                        if (c > 0)
+                            fetch_sum(c, sumw[0]);
+                        __syncwarp();
+                        ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                        ptx::tmem_ld_wait();
+                        const int col0 = colw + 32 * c;
+                        if (col0 < p.N) // warp-uniform
+                        {
+                            const bool full_chunk = col0 + 32 <= p.N;
+                            const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
+                            const bool bytes_path = bytes_variant >= 0 && (!has_sum || full_chunk);
+                            if (bytes_path)
+                            {
+                                switch (bytes_variant)
+                                {
+                                case 0: epilogue_chunk_bytes<false, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 1: epilogue_chunk_bytes<true, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 2: epilogue_chunk_bytes<false, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 3: epilogue_chunk_bytes<true, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 4: epilogue_chunk_bytes<false, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                default: epilogue_chunk_bytes<true, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                }
+                            }
+                            else
+                                epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
+                            if (p.tma_store)
+                                stage_bytes_out(c, w);
+                            else if (er.valid && esz == 1)
+                            {
+                                uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
+                                if (full_chunk && vec_ok)
+                                {
+                                    reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                    reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (col0 + j < p.N)
+                                            op[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+                                }
+                            }
+                            else if (er.valid)
+                            {
+                                uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
+                                if (full_chunk && vec_ok)
+                                {
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        reinterpret_cast<uint4*>(op)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (col0 + j < p.N)
+                                            op[j] = v[j];
+                                }
+                            }
+                        }
+                    }
                     }
                     if (warp == 4 && lane == 0)
-                        PROF_ADD(3);
-                }
-                ptx::tc_fence_after_sync();
-                PROF_T0();
-                const uint32_t stage_blk = stage_blk0 + (tile_it & 1) * C::OUT_BYTES;
-                const uint32_t stage_row = stage_blk + uint32_t(lane) * COLS;
-                if (stores_in_flight == 2)
-                {
-                    // the TMA store issued two tiles ago must have finished reading this staging block
-                    PROF_MARK(t_w0);
-                    if (lane == 0)
-                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    __syncwarp();
-                    PROF_MARK(t_w1);
-                    PROF_SPAN(10, t_w0, t_w1);
-                    stores_in_flight = 1;
-                }
-                const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + part * COLS;
-#pragma unroll 1
-                for (int c = 0; c < CHUNKS; ++c)
-                {
-                    uint32_t v[32], w[8];
-                    if (c > 0)
-                        fetch_sum(c);
-                    __syncwarp();
-                    PROF_MARK(t_a);
-                    ptx::tmem_ld_32x32(t_addr + 32 * c, v);
-                    ptx::tmem_ld_wait();
-                    PROF_MARK(t_b);
-                    PROF_SPAN(8, t_a, t_b);
-                    const int col0 = colw + 32 * c;
-                    if (col0 < p.N) // warp-uniform
                     {
-                        const bool full_chunk = col0 + 32 <= p.N;
-                        const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
-                        const bool bytes_path = !p.half_away && esz == 1 && (!has_sum || (sum_regs && full_chunk) || !er.valid);
-                        if (bytes_path && has_sum && er.valid)
-                            epilogue_chunk_bytes<true>(v, w, sc, bi, sumw, sum_scale, p.sum_type == B200_U8, p.relu != 0, p.out_type == B200_U8);
-                        else if (bytes_path)
-                            epilogue_chunk_bytes<false>(v, w, sc, bi, sumw, sum_scale, false, p.relu != 0, p.out_type == B200_U8);
-                        else
-                            epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
-                        PROF_MARK(t_c);
-                        PROF_SPAN(9, t_b, t_c);
-                        if (p.tma_store)
-                        {
-                            // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
-                            const uint32_t c16 = uint32_t(2 * c);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((c16 ^ sw_xor) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((c16 + 1) ^ sw_xor) << 4)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-                        }
-                        else if (er.valid && esz == 1)
-                        {
-                            uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
-                            if (full_chunk && vec_ok)
-                            {
-                                reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                            }
-                            else
-                            {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (col0 + j < p.N)
-                                        op[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
-                            }
-                        }
-                        else if (er.valid)
-                        {
-                            uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
-                            if (full_chunk && vec_ok)
-                            {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    reinterpret_cast<uint4*>(op)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            }
-                            else
-                            {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (col0 + j < p.N)
-                                        op[j] = v[j];
-                            }
-                        }
-                    }
-                }
-                if (warp == 4 && lane == 0)
-                {
-                    PROF_ADD(4);
+                        PROF_ADD(4);
 #ifdef B200_PROFILE_WAITS
-                    if (blockIdx.x == 0)
-                        atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[6]), 1ull);
+                        if (blockIdx.x == 0)
+                            atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[6]), 1ull);
 #endif
-                }
-                // all of this warp's TMEM reads are done: hand the accumulator back
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0)
-                    ptx::mbar_arrive(tempty_bar(acc));
-                if (p.tma_store && colw < p.N)
-                {
-                    // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
-                    // rows / columns that fall outside the output tensor are clipped by the TMA unit
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    }
+                    // all of this warp's TMEM reads are done: hand the accumulator back
+                    ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0)
+                        ptx::mbar_arrive(tempty_bar(acc));
+                    if ((FAST || p.tma_store) && colw < p.N)
                     {
-                        // lane 0 holds the first row of the block: a block that starts outside the tensor is skipped
-                        if (p.conv && er.valid)
+                        // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
+                        // rows / columns that fall outside the output tensor are clipped by the TMA unit
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0)
                         {
-                            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + blk_w),
-                                         "r"(p0 + blk_h), "r"(n0 + blk_n) : "memory");
+                            // a block whose first row lies outside the tensor is skipped
+                            if (p.conv && blk_valid)
+                            {
+                                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                                             ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + blk_w),
+                                             "r"(p0 + blk_h), "r"(n0 + blk_n) : "memory");
+                            }
+                            else if (!p.conv && blk_valid)
+                            {
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                             ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(tm * BM + quarter * 32)
+                                             : "memory");
+                            }
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
-                        else if (!p.conv && er.valid)
-                        {
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                                         ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(tm * BM + quarter * 32)
-                                         : "memory");
-                        }
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        ++stores_in_flight;
                     }
-                    ++stores_in_flight;
                 }
+            };
+            const int fast_mode = (bytes_variant >= 0 && p.tma_store && p.N % COLS == 0) ? bytes_variant : -1;
+            switch (fast_mode)
+            {
+            case 0: epilogue_loop(std::integral_constant<int, 0>{}); break;
+            case 1: epilogue_loop(std::integral_constant<int, 1>{}); break;
+            case 2: epilogue_loop(std::integral_constant<int, 2>{}); break;
+            case 3: epilogue_loop(std::integral_constant<int, 3>{}); break;
+            case 4: epilogue_loop(std::integral_constant<int, 4>{}); break;
+            case 5: epilogue_loop(std::integral_constant<int, 5>{}); break;
+            default: epilogue_loop(std::integral_constant<int, -1>{}); break;
             }
             // stores must be complete (not just read) before the CTA exits
             if (lane == 0)
@@ -888,6 +1066,7 @@ namespace b200
         p.sum_type = e->sum_type;
         p.sum_scale = e->sum_scale;
         p.relu = e->relu;
+        p.one = 1;
         p.half_away = e->round_half_away;
         p.out_zp = e->out_zero_point;
         p.out_type = e->out_type;

@@ -147,17 +147,18 @@ def test_qgemm_vs_oracle(ops, mnk, a_signed):
 
 def test_qgemm_sum_input(ops):
     rng = np.random.default_rng(5)
-    m, n, k = 200, 96, 256
+    m, n, k = 2000, 96, 256  # enough outputs that a product fused with the residual addition (one rounding) would show
     a = rng.integers(0, 256, size=(m, k)).astype(np.uint8)
     w = rng.integers(-127, 128, size=(n, k)).astype(np.int8)
     bias = rng.integers(-1000, 1001, size=n).astype(np.int32)
     scale = np.full(n, 2e-4, np.float32)
     for sdt in (np.uint8, np.int8):
         s = rng.integers(np.iinfo(sdt).min, np.iinfo(sdt).max + 1, size=(m, n)).astype(sdt)
-        exp = ref.qgemm_fused(a, w, bias, scale, np.uint8, relu=True, sum_in=s, sum_scale=np.float32(0.37))
-        got = ops.qgemm(dev(a), dev(w), dev(scale), torch.uint8, bias=dev(bias), relu=True, sum_in=dev(s),
-                        sum_scale=dev(np.array([0.37], np.float32))).cpu().numpy()
-        np.testing.assert_array_equal(got, exp)
+        for out_dt, relu in ((np.uint8, True), (np.int8, False), (np.int8, True)):
+            exp = ref.qgemm_fused(a, w, bias, scale, out_dt, relu=relu, sum_in=s, sum_scale=np.float32(0.37))
+            got = ops.qgemm(dev(a), dev(w), dev(scale), TDT[np.dtype(out_dt)], bias=dev(bias), relu=relu, sum_in=dev(s),
+                            sum_scale=dev(np.array([0.37], np.float32))).cpu().numpy()
+            np.testing.assert_array_equal(got, exp)
 
 
 CONV_CASES = [
