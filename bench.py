@@ -265,19 +265,23 @@ class QConvLayer(MicroWorkload):
     name, metric, unit, dtype = "qconv", "QuantizedConvolutionBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
 
     def __init__(self, batch=32):
-        # BASELINE's layer by default; B200_BENCH_CONV="C,K,R,HW" times another ResNet layer shape (stride 1, same padding)
-        c, k, r, hw = (int(v) for v in os.environ.get("B200_BENCH_CONV", "64,64,3,56").split(","))
+        # BASELINE's layer by default; B200_BENCH_CONV="C,K,R,HW[,sum]" times another ResNet layer shape (stride 1,
+        # same padding); a fifth field 1 adds a u8 residual input (QuantizedConvolutionBiasAdd)
+        f = [int(v) for v in os.environ.get("B200_BENCH_CONV", "64,64,3,56").split(",")]
+        c, k, r, hw = f[:4]
+        self.with_sum = len(f) > 4 and f[4] != 0
         self.B, self.C, self.H, self.W, self.K, self.R = batch, c, hw, hw, k, r
 
     def describe(self, world=1):
-        return {"workload": "QuantizedConvolutionBias+Relu u8[%d,%d,%d,%d]*i8[%d,%d,%d,%d] s1 same-pad, per-channel scales, "
-                            "i32 bias -> u8" % (self.B, self.C, self.H, self.W, self.K, self.C, self.R, self.R),
+        return {"workload": "QuantizedConvolutionBias%s+Relu u8[%d,%d,%d,%d]*i8[%d,%d,%d,%d] s1 same-pad, per-channel scales, "
+                            "i32 bias -> u8" % ("Add (u8 residual)" if self.with_sum else "", self.B, self.C, self.H, self.W, self.K,
+                                                self.C, self.R, self.R),
                 "layout": "channels-last on device",
                 "l2": "input %.1f MB + output %.1f MB per step, rotated over %d buffers (> 126 MB L2)"
                       % (self.B * self.C * self.H * self.W / 1e6, self.B * self.K * self.H * self.W / 1e6, self.nbufs())}
 
     def nbufs(self):
-        per = self.B * (self.C + self.K) * self.H * self.W
+        per = self.B * (self.C + self.K * (2 if self.with_sum else 1)) * self.H * self.W
         return max(2, min(24, int(300e6 // per) + 1))
 
     def host_inputs(self, seed):
@@ -287,6 +291,7 @@ class QConvLayer(MicroWorkload):
              "bias": rng.integers(-1000, 1001, size=self.K).astype(np.int32)}
         sf = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), size=self.K)).astype(np.float32)
         d["scale"] = (np.float32(0.02) * sf / np.float32(0.05)).astype(np.float32)
+        d["sum"] = rng.integers(0, 256, size=(self.B, self.H, self.W, self.K), dtype=np.uint8) if self.with_sum else None
         self.h = d
         return d
 
@@ -297,6 +302,8 @@ class QConvLayer(MicroWorkload):
         self.data = [torch.from_numpy(h["data"]).cuda() for _ in range(self.nbuf)]
         self.out = [torch.empty((self.B, self.H, self.W, self.K), dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
         self.filt, self.bias, self.scale = (torch.from_numpy(h[k]).cuda() for k in ("filt", "bias", "scale"))
+        self.sum = [torch.from_numpy(h["sum"]).cuda() for _ in range(self.nbuf)] if self.with_sum else None
+        self.sum_scale = torch.full((1,), 0.37, device="cuda") if self.with_sum else None
         pad = self.R // 2
         self.cp = ops.conv_params((self.B, self.H, self.W, self.C), (self.K, self.R, self.R, self.C), (1, 1), (pad, pad))
         self.pin_in = torch.from_numpy(h["data"]).pin_memory()
@@ -309,14 +316,18 @@ class QConvLayer(MicroWorkload):
     def alg_per_launch(self):
         return self.units_per_step() * 1e12
 
+    def _launch(self, i):
+        self.ops.qconv(self.data[i], self.filt, self.scale, self.torch.uint8, self.cp, bias=self.bias, relu=True, out=self.out[i],
+                       sum_in=self.sum[i] if self.with_sum else None, sum_scale=self.sum_scale)
+
     def step(self):
         i = self.i = (self.i + 1) % self.nbuf
-        self.ops.qconv(self.data[i], self.filt, self.scale, self.torch.uint8, self.cp, bias=self.bias, relu=True, out=self.out[i])
+        self._launch(i)
 
     def step_e2e(self):
         i = self.i = (self.i + 1) % self.nbuf
         self.data[i].copy_(self.pin_in, non_blocking=True)
-        self.ops.qconv(self.data[i], self.filt, self.scale, self.torch.uint8, self.cp, bias=self.bias, relu=True, out=self.out[i])
+        self._launch(i)
         self.pin_out.copy_(self.out[i], non_blocking=True)
 
     def io_bytes(self):
@@ -328,6 +339,9 @@ class QConvLayer(MicroWorkload):
         cs = ref.conv_shape((nimg, self.C, self.H, self.W), (self.K, self.C, self.R, self.R), (1, 1), (pad, pad))
         nchw = np.ascontiguousarray(self.h["data"][:nimg].transpose(0, 3, 1, 2))
         kcrs = np.ascontiguousarray(self.h["filt"].transpose(0, 3, 1, 2))
+        if self.with_sum:
+            return ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True,
+                                   sum_in=np.ascontiguousarray(self.h["sum"][:nimg].transpose(0, 3, 1, 2)), sum_scale=np.float32(0.37))
         return ref.qconv_fused(nchw, kcrs, self.h["bias"], self.h["scale"], cs, np.uint8, relu=True)
 
     def check(self):

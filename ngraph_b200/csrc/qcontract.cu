@@ -252,6 +252,12 @@ namespace b200
         asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
         return d;
     }
+    __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+    {
+        uint64_t d;
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+        return d;
+    }
     __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
     {
         uint64_t d;
@@ -264,12 +270,19 @@ namespace b200
     // sc / bi: shared-memory addresses of this chunk's 32 staged scales / biases.  The variant is chosen once
     // per chunk so that the unrolled body has no branches.  RELU_F is only needed for int8 outputs: for u8
     // the unsigned saturation already is max(v, 0).
-    template <bool HAS_SUM, bool RELU_F, bool OUT_U8>
+    // SUM: 0 no residual; 1 u8 residual with a finite sum_scale * 2^23; 2 any residual.
+    // float(byte) is made without a conversion instruction: the byte is placed in the mantissa of 2^23, giving
+    // m = 2^23 + byte exactly.  SUM 1: sum_scale * byte = fma(sum_scale, m, -(sum_scale * 2^23)), exact product and
+    // exact constant, one rounding, i.e. the rounded product itself.  SUM 2: int8 residuals are biased by 128 first
+    // (xor 0x80), m - (2^23 + 128) is exact, then one multiply.
+    template <int SUM, bool RELU_F, bool OUT_U8>
     __device__ __forceinline__ void epilogue_chunk_bytes(const uint32_t (&v)[32], uint32_t (&w)[8], uint32_t sc, uint32_t bi,
                                                          const uint32_t* sumw, float sum_scale, uint32_t sum_flip, float sum_magic,
                                                          int32_t one)
     {
         const uint64_t sum_scale2 = pack_f2(sum_scale, sum_scale), neg_magic2 = pack_f2(-sum_magic, -sum_magic);
+        const float neg_c = -__fmul_rn(sum_scale, 8388608.0f);
+        const uint64_t neg_c2 = pack_f2(neg_c, neg_c);
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4)
         {
@@ -279,25 +292,24 @@ namespace b200
             const float a1 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 1]), b4.y, one));
             const float a2 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 2]), b4.z, one));
             const float a3 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 3]), b4.w, one));
-            uint64_t f01 = mul2(pack_f2(a0, a1), pack_f2(s4.x, s4.y));
-            uint64_t f23 = mul2(pack_f2(a2, a3), pack_f2(s4.z, s4.w));
-            if (HAS_SUM)
+            F2 r01 = unpack_f2(mul2(pack_f2(a0, a1), pack_f2(s4.x, s4.y)));
+            F2 r23 = unpack_f2(mul2(pack_f2(a2, a3), pack_f2(s4.z, s4.w)));
+            if (SUM != 0)
             {
-                // float(byte) without a conversion instruction: the byte is placed in the mantissa of 2^23 and 2^23
-                // (+128 when the byte is a biased int8) is subtracted, both steps exact
-                const uint32_t sw = sumw[j4] ^ sum_flip; // int8 residuals become biased bytes (value + 128)
+                const uint32_t sw = SUM == 1 ? sumw[j4] : (sumw[j4] ^ sum_flip);
                 const uint64_t m01 = pack_f2(__uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7650u)),
                                              __uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7651u)));
                 const uint64_t m23 = pack_f2(__uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7652u)),
                                              __uint_as_float(__byte_perm(sw, 0x4B000000u, 0x7653u)));
-                // the products and the final additions are rounded separately (the fused ops add the residual term
-                // unfused); the additions are scalar intrinsics, which the compiler never contracts with a multiply
-                const F2 t01 = unpack_f2(mul2(sum_scale2, add2(m01, neg_magic2))), t23 = unpack_f2(mul2(sum_scale2, add2(m23, neg_magic2)));
-                const F2 g01 = unpack_f2(f01), g23 = unpack_f2(f23);
-                f01 = pack_f2(__fadd_rn(g01.x, t01.x), __fadd_rn(g01.y, t01.y));
-                f23 = pack_f2(__fadd_rn(g23.x, t23.x), __fadd_rn(g23.y, t23.y));
+                const F2 t01 = unpack_f2(SUM == 1 ? fma2(sum_scale2, m01, neg_c2) : mul2(sum_scale2, add2(m01, neg_magic2)));
+                const F2 t23 = unpack_f2(SUM == 1 ? fma2(sum_scale2, m23, neg_c2) : mul2(sum_scale2, add2(m23, neg_magic2)));
+                // the residual term is added unfused (the reference's fused ops round the product and the sum separately).
+                // Scalar intrinsics: a packed add after a packed multiply is contracted into a packed fma by the assembler.
+                r01.x = __fadd_rn(r01.x, t01.x);
+                r01.y = __fadd_rn(r01.y, t01.y);
+                r23.x = __fadd_rn(r23.x, t23.x);
+                r23.y = __fadd_rn(r23.y, t23.y);
             }
-            F2 r01 = unpack_f2(f01), r23 = unpack_f2(f23);
             if (RELU_F)
             {
                 // max(v, 0): NaN -> 0 like reference::relu (v > 0 ? v : 0)
@@ -599,11 +611,15 @@ namespace b200
             // this warp's two staging blocks (alternating per tile): 32 rows x COLS bytes, swizzled like the TMA store expects
             const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * COLS);
             const uint32_t sw_xor = COLS == 128 ? uint32_t(lane & 7) : COLS == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
-            // branch-free chunk body for the fused contract with one-byte outputs: u8 {0: plain, 1: +sum},
-            // i8 {2, 3}, i8 with relu {4, 5}; -1: the general path (core contract, 4-byte outputs, unaligned residuals)
+            // branch-free chunk body for the fused contract with one-byte outputs: 3 * (0: u8, 1: i8, 2: i8 with relu) +
+            // (0: no residual, 1: u8 residual through the fma form, 2: any residual); -1: the general path (core
+            // contract, 4-byte outputs, unaligned residuals)
             int bytes_variant = -1;
             if (!p.half_away && esz == 1 && (!has_sum || vec_ok))
-                bytes_variant = (p.out_type == B200_U8 ? 0 : (p.relu ? 4 : 2)) + (has_sum ? 1 : 0);
+            {
+                const bool fma_form = p.sum_type == B200_U8 && fabsf(__fmul_rn(sum_scale, 8388608.0f)) <= 3.4028234664e38f;
+                bytes_variant = 3 * (p.out_type == B200_U8 ? 0 : (p.relu ? 2 : 1)) + (has_sum ? (fma_form ? 1 : 2) : 0);
+            }
             const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
             // per-row addresses are only needed for residual loads and for stores that do not go through TMA
             const bool need_rows = has_sum || !p.tma_store;
@@ -614,7 +630,8 @@ namespace b200
             auto epilogue_loop = [&](auto mode_tag) {
                 constexpr int MODE = decltype(mode_tag)::value;
                 constexpr bool FAST = MODE >= 0;
-                constexpr bool F_SUM = FAST && (MODE & 1), F_RELU = MODE >= 4, F_U8 = MODE >= 0 && MODE < 2;
+                constexpr int F_SUMK = FAST ? MODE % 3 : 0;
+                constexpr bool F_SUM = F_SUMK != 0, F_RELU = MODE >= 6, F_U8 = MODE >= 0 && MODE < 3;
                 int stores_in_flight = 0;
                 int staged_tn = -1;
                 uint32_t tile_it = 0;
@@ -696,7 +713,7 @@ namespace b200
                             sumw[c][j] = 0;
                     const bool sum_regs = (FAST ? F_SUM : (has_sum && vec_ok)) && er.valid;
                     auto fetch_sum = [&](int c, uint32_t (&dst)[8]) {
-                        if (sum_regs && colw + 32 * c + 32 <= p.N)
+                        if (sum_regs && (FAST ? colw < p.N : colw + 32 * c + 32 <= p.N))
                         {
                             const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
                             const uint4 s0 = sp[0], s1 = sp[1];
@@ -759,7 +776,7 @@ namespace b200
                             ptx::tmem_ld_wait();
                             PROF_MARK(t_b);
                             PROF_SPAN(8, t_a, t_b);
-                            epilogue_chunk_bytes<F_SUM, F_RELU, F_U8>(v, w, sc_base + 128u * c, bi_base + 128u * c, sumw[FAST ? c : 0], sum_scale,
+                            epilogue_chunk_bytes<F_SUMK, F_RELU, F_U8>(v, w, sc_base + 128u * c, bi_base + 128u * c, sumw[FAST ? c : 0], sum_scale,
                                                                       sum_flip, sum_magic, p.one);
                             PROF_MARK(t_c);
                             PROF_SPAN(9, t_b, t_c);
@@ -787,12 +804,15 @@ namespace b200
                             {
                                 switch (bytes_variant)
                                 {
-                                case 0: epilogue_chunk_bytes<false, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 1: epilogue_chunk_bytes<true, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 2: epilogue_chunk_bytes<false, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 3: epilogue_chunk_bytes<true, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 4: epilogue_chunk_bytes<false, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                default: epilogue_chunk_bytes<true, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 0: epilogue_chunk_bytes<0, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 1: epilogue_chunk_bytes<1, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 2: epilogue_chunk_bytes<2, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 3: epilogue_chunk_bytes<0, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 4: epilogue_chunk_bytes<1, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 5: epilogue_chunk_bytes<2, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 6: epilogue_chunk_bytes<0, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                case 7: epilogue_chunk_bytes<1, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
+                                default: epilogue_chunk_bytes<2, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
                                 }
                             }
                             else
@@ -884,6 +904,9 @@ namespace b200
             case 3: epilogue_loop(std::integral_constant<int, 3>{}); break;
             case 4: epilogue_loop(std::integral_constant<int, 4>{}); break;
             case 5: epilogue_loop(std::integral_constant<int, 5>{}); break;
+            case 6: epilogue_loop(std::integral_constant<int, 6>{}); break;
+            case 7: epilogue_loop(std::integral_constant<int, 7>{}); break;
+            case 8: epilogue_loop(std::integral_constant<int, 8>{}); break;
             default: epilogue_loop(std::integral_constant<int, -1>{}); break;
             }
             // stores must be complete (not just read) before the CTA exits
