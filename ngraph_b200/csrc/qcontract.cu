@@ -67,7 +67,8 @@ namespace b200
         int b_res_bytes;  // bytes of the resident B region (0 otherwise)
         int stage_bytes;  // A (+ B when not resident) per pipeline stage
         int stages;
-        int out_bytes;    // output staging (0 when results are written from registers)
+        int out_bufs;     // output staging buffers: 0 (results written from registers), 2, or 3 (residual fetched by TMA)
+        int out_bytes;    // out_bufs * OUT_BYTES
         int total_bytes;  // dynamic shared memory of the launch
     };
 
@@ -93,6 +94,7 @@ namespace b200
         int relu, half_away, out_zp, out_type;
         int one;             // the constant 1, opaque to the compiler (see add_fma_pipe)
         int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
+        int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
         int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
         uint32_t idesc;
@@ -105,11 +107,16 @@ namespace b200
         CUtensorMap a[4]; // GEMM: a[0] (2-D).  Conv: one 4-D map per (h parity, w parity) sub-lattice
         CUtensorMap b;
         CUtensorMap out;  // used when ContractParams::tma_store
+        CUtensorMap sum;  // the residual, same geometry as out; used when ContractParams::tma_sum
     };
 
     constexpr int BM = 128;
     constexpr int NUM_PRODUCERS = 3;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
-    constexpr int NUM_THREADS = 640; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-19: epilogue (4-11 when BN = 64)
+    constexpr int NUM_THREADS = 640; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-19: epilogue
+    constexpr int EPI_WARPS = 16;
+    constexpr int COLS = 64;         // output columns (= bytes of a one-byte row) per epilogue warp and tile
+    constexpr int CHUNKS = COLS / 32;
+    constexpr int MAX_ACC = 8;       // accumulator buffers in TMEM: 512 columns / BN
     constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
 
     // Sleep between two polls of an mbarrier, per waiting role: a polling warp takes issue slots from the epilogue
@@ -130,7 +137,7 @@ namespace b200
                        BACKOFF_TEMPTY_NS = B200_BACKOFF_TEMPTY_NS, BACKOFF_TFULL_NS = B200_BACKOFF_TFULL_NS;
 
     constexpr int MAX_STAGES = 16;
-    constexpr int BAR_BYTES = 512;          // (2*MAX_STAGES + 5) mbarriers
+    constexpr int BAR_BYTES = 1024;         // 2*MAX_STAGES + 2*MAX_ACC + 1 + 3*EPI_WARPS mbarriers
     constexpr int B_RESIDENT_MAX = 73728;   // a whole filter / weight matrix up to this size stays in shared memory
 
     template <int BN, int BK>
@@ -138,9 +145,12 @@ namespace b200
     {
         static constexpr int A_BYTES = BM * BK;
         static constexpr int B_BYTES = BN * BK;
-        static constexpr int OUT_BYTES = BM * BN;      // one staging block of 32 rows per epilogue warp
-        static constexpr int FIXED = 2 * OUT_BYTES /*double buffered*/ + 1024 /*align slack*/ + BAR_BYTES;
-        static constexpr int TMEM_COLS = 2 * BN;
+        static constexpr int OUT_BYTES = EPI_WARPS * 32 * COLS; // one staging block of 32 rows x COLS bytes per epilogue warp
+        static constexpr int FIXED = 1024 /*align slack*/ + BAR_BYTES;
+        static constexpr int SPLIT = BN / COLS;        // epilogue warps per TMEM lane quarter and tile
+        static constexpr int GROUPS = 4 / SPLIT;       // warp groups, each working on a different tile
+        static constexpr int NACC = 2 * GROUPS;        // accumulator buffers: NACC * BN = 512 TMEM columns
+        static constexpr int TMEM_COLS = 512;
     };
 
     // n / d and n % d for 0 <= n < 2^24 without an integer division: float estimate, one correction step
@@ -395,17 +405,15 @@ namespace b200
         qcontract_kernel(const __grid_constant__ TensorMaps maps, const __grid_constant__ ContractParams p)
     {
         using C = Cfg<BN, BK>;
-        constexpr int SPLIT = BN >= 128 ? 4 : 2; // epilogue warps per TMEM lane quarter
-        constexpr int COLS = BN / SPLIT;         // columns (= bytes of a one-byte output row) per epilogue warp: 64 or 32
-        constexpr int CHUNKS = COLS / 32;        // 32-column chunks per epilogue warp
+        constexpr int SPLIT = C::SPLIT, GROUPS = C::GROUPS, NACC = C::NACC;
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
-        // per epilogue warp: scale and bias of its column half of the current column tile
-        __shared__ __align__(16) float epi_scale[4 * SPLIT][COLS];
-        __shared__ __align__(16) int32_t epi_bias[4 * SPLIT][COLS];
+        // per epilogue warp: scale and bias of its 64 columns of the current column tile
+        __shared__ __align__(16) float epi_scale[EPI_WARPS][COLS];
+        __shared__ __align__(16) int32_t epi_bias[EPI_WARPS][COLS];
 
-        // [resident B] [stages x (A [+ B])] [2 x output staging] [mbarriers]; every region is a multiple of 1024 bytes
+        // [resident B] [stages x (A [+ B])] [0, 2 or 3 x output staging] [mbarriers]; every region is a multiple of 1024 bytes
         const int STAGES = p.smem.stages;
         const uint32_t stage_bytes = uint32_t(p.smem.stage_bytes);
         const uint32_t bres_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -415,8 +423,10 @@ namespace b200
         auto full_bar = [&](int s) { return bars + 8u * s; };
         auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
         auto tfull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
-        auto tempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 2 + b); };
-        const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 4);
+        auto tempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + MAX_ACC + b); };
+        const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 2 * MAX_ACC);
+        // residual landed in staging block b of epilogue warp w
+        auto sum_bar = [&](int w, int b) { return bars + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 1 + 3 * w + b); };
 
         const int warp = threadIdx.x >> 5;
         const int lane = threadIdx.x & 31;
@@ -431,11 +441,14 @@ namespace b200
                 ptx::mbar_init(empty_bar(s), 1);
             }
             ptx::mbar_init(bres_bar, 1);
-            for (int b = 0; b < 2; ++b)
+            for (int b = 0; b < NACC; ++b)
             {
                 ptx::mbar_init(tfull_bar(b), 1);
                 ptx::mbar_init(tempty_bar(b), 4 * SPLIT);
             }
+            for (int w = 0; w < EPI_WARPS; ++w)
+                for (int b = 0; b < 3; ++b)
+                    ptx::mbar_init(sum_bar(w, b), 1);
             ptx::fence_barrier_init();
         }
         if (warp == 0)
@@ -531,8 +544,8 @@ namespace b200
                     fail = 2003;
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
                 {
-                    const int acc = tile_it & 1;
-                    const uint32_t acc_ph = (tile_it >> 1) & 1;
+                    const int acc = tile_it % NACC;
+                    const uint32_t acc_ph = (tile_it / NACC) & 1;
                     {
                         PROF_T0();
                         if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS))
@@ -580,15 +593,15 @@ namespace b200
         }
         else
         {
-            // ------------------------------------------------------------ epilogue (warps 4..)
-            // TMEM lane quarter (warp id % 4) is fixed by the hardware; the SPLIT warps that share a quarter
-            // split the tile's columns between them (COLS each).  Warps beyond 4*SPLIT have nothing to do.
+            // ------------------------------------------------------------ epilogue (warps 4..19)
+            // The TMEM lane quarter a warp may read (warp id % 4) is fixed by the hardware.  Every warp owns 32 rows x
+            // 64 columns of a tile, so a tile takes 4 * SPLIT warps; the GROUPS warp groups work on different tiles
+            // at the same time (tile_it % GROUPS), each with two of the NACC accumulator buffers.
             const int quarter = warp & 3;
-            const int part = (warp - 4) >> 2;    // which column part of the tile
-            const int ew = warp - 4;             // 0 .. 4*SPLIT-1
-            if (part < SPLIT)
-            {
-            const int row = quarter * 32 + lane; // accumulator row of this thread
+            const int ew = warp - 4;                 // 0 .. 15
+            const int group = (ew >> 2) / SPLIT;     // which tiles: tile_it % GROUPS == group
+            const int part = (ew >> 2) % SPLIT;      // which 64 columns of the tile
+            const int row = quarter * 32 + lane;     // accumulator row of this thread
             // position of this row (and of the warp's first row) inside the output patch: the same for every tile
             int row_w = 0, row_h = 0, row_n = 0, blk_w = 0, blk_h = 0, blk_n = 0;
             if (p.conv)
@@ -608,9 +621,9 @@ namespace b200
             const int esz = (p.out_type == B200_U8 || p.out_type == B200_I8) ? 1 : 4;
             const bool vec_ok = ((esz == 1) ? ((p.N & 15) == 0) : ((p.N & 3) == 0)) &&
                                 ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.sum_in)) & 15) == 0;
-            // this warp's two staging blocks (alternating per tile): 32 rows x COLS bytes, swizzled like the TMA store expects
+            // this warp's staging blocks (one per tile in flight): 32 rows x 64 bytes, swizzled like the TMA unit expects
             const uint32_t stage_blk0 = out_base + uint32_t(ew) * (32 * COLS);
-            const uint32_t sw_xor = COLS == 128 ? uint32_t(lane & 7) : COLS == 64 ? uint32_t((lane >> 1) & 3) : uint32_t((lane >> 2) & 1);
+            const uint32_t sw_xor = uint32_t((lane >> 1) & 3);
             // branch-free chunk body for the fused contract with one-byte outputs: 3 * (0: u8, 1: i8, 2: i8 with relu) +
             // (0: no residual, 1: u8 residual through the fma form, 2: any residual); -1: the general path (core
             // contract, 4-byte outputs, unaligned residuals)
@@ -623,26 +636,49 @@ namespace b200
             const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
             // per-row addresses are only needed for residual loads and for stores that do not go through TMA
             const bool need_rows = has_sum || !p.tma_store;
+            const int tile_step = GROUPS * int(gridDim.x); // distance between two tiles of this warp
 
-            // The tile loop, compiled once per MODE.  MODE 0..5 = bytes_variant with TMA stores and a width that is a
-            // multiple of COLS (every chunk full, every residual vector aligned): all the per-chunk decisions
-            // are made at compile time.  MODE -1 is the general loop (any contract, type and width).
+            // The tile loop, compiled once per MODE.  MODE 0..8 = bytes_variant with TMA stores, a width that is a
+            // multiple of 64 (every chunk full) and, where there is a residual, the residual fetched by TMA into the
+            // staging block its result is stored from: all the per-chunk decisions are made at compile time.
+            // MODE -1 is the general loop (any contract, type and width).
             auto epilogue_loop = [&](auto mode_tag) {
                 constexpr int MODE = decltype(mode_tag)::value;
                 constexpr bool FAST = MODE >= 0;
                 constexpr int F_SUMK = FAST ? MODE % 3 : 0;
                 constexpr bool F_SUM = F_SUMK != 0, F_RELU = MODE >= 6, F_U8 = MODE >= 0 && MODE < 3;
-                int stores_in_flight = 0;
+                constexpr int NBUF = F_SUM ? 3 : 2; // staging blocks per warp
                 int staged_tn = -1;
-                uint32_t tile_it = 0;
-                // Tile coordinates: every 32 tiles each lane decodes one of the warp's next 32 tiles (the divisions are
-                // done once per tile instead of once per tile and lane) and the loop broadcasts them with shuffles.
+                int blk = 0;             // staging block of the current tile: j % NBUF
+                uint32_t sum_ph = 0;     // parity of sum_bar(ew, blk) for the current tile: (j / 3) & 1
+                // Tile coordinates: each lane decodes one of the warp's next tiles (the divisions are done once per tile
+                // instead of once per tile and lane) and the loop broadcasts them with shuffles.  The window is
+                // refreshed every 31 tiles so that the next tile's coordinates are always in it.
                 int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
-                for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
+                int idx = 31;
+                auto coords_of = [&](int lane_idx, int& a_, int& p0_, int& n0_, int& tn_) {
+                    a_ = __shfl_sync(0xffffffffu, info_a, lane_idx);
+                    p0_ = __shfl_sync(0xffffffffu, info_b, lane_idx);
+                    n0_ = __shfl_sync(0xffffffffu, info_c, lane_idx);
+                    tn_ = __shfl_sync(0xffffffffu, info_d, lane_idx);
+                };
+                // lane 0: fetch the residual of tile (a_, p0_, n0_, tn_) into staging block b
+                auto fetch_residual = [&](int b, int a_, int p0_, int n0_, int tn_) {
+                    const uint32_t bar = sum_bar(ew, b), dst = stage_blk0 + uint32_t(b) * C::OUT_BYTES;
+                    const int col = tn_ * BN + part * COLS;
+                    ptx::mbar_expect_tx(bar, 32 * COLS);
+                    if (p.conv)
+                        ptx::tma_load_4d(dst, &maps.sum, bar, col, a_ + blk_w, p0_ + blk_h, n0_ + blk_n);
+                    else
+                        ptx::tma_load_2d(dst, &maps.sum, bar, col, a_ * BM + quarter * 32);
+                };
+                uint32_t tile_it = uint32_t(group);
+                int j = 0;
+                for (int tile = int(blockIdx.x) + group * int(gridDim.x); tile < num_tiles && !fail; tile += tile_step, tile_it += GROUPS, ++j)
                 {
-                    if ((tile_it & 31) == 0)
+                    if (idx == 31)
                     {
-                        const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * gridDim.x;
+                        const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * tile_step;
                         if (t < num_tiles)
                         {
                             int tm_, tn_, q0_, p0_, n0_;
@@ -652,36 +688,60 @@ namespace b200
                             info_c = n0_;
                             info_d = tn_;
                         }
+                        idx = 0;
                     }
-                    const int src_lane = tile_it & 31;
-                    const int ia = __shfl_sync(0xffffffffu, info_a, src_lane);
-                    const int p0 = __shfl_sync(0xffffffffu, info_b, src_lane);
-                    const int n0 = __shfl_sync(0xffffffffu, info_c, src_lane);
-                    const int tn = __shfl_sync(0xffffffffu, info_d, src_lane);
+                    int ia, p0, n0, tn;
+                    coords_of(idx, ia, p0, n0, tn);
                     const int tm = ia, q0 = ia;
-                    const int acc = tile_it & 1;
-                    const uint32_t acc_ph = (tile_it >> 1) & 1;
+                    const int acc = tile_it % NACC;
+                    const uint32_t acc_ph = (tile_it / NACC) & 1;
                     const int colw = tn * BN + part * COLS; // first output column of this warp
+                    const uint32_t stage_blk = stage_blk0 + uint32_t(blk) * C::OUT_BYTES;
+                    const uint32_t stage_row = stage_blk + uint32_t(lane) * COLS;
+                    if (F_SUM)
+                    {
+                        // Residual of this warp's NEXT tile -> the block that tile's result will be stored from.  That block
+                        // was last used two tiles ago: all but the most recent store must have finished reading.
+                        const bool has_next = tile + tile_step < num_tiles;
+                        int na, np0, nn0, ntn;
+                        coords_of(idx + 1, na, np0, nn0, ntn);
+                        if (lane == 0)
+                        {
+                            if (j == 0)
+                                fetch_residual(0, ia, p0, n0, tn);
+                            if (has_next)
+                            {
+                                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                                fetch_residual(blk == 2 ? 0 : blk + 1, na, np0, nn0, ntn);
+                            }
+                        }
+                    }
+                    else if (j >= 2)
+                    {
+                        // the TMA store issued two tiles ago must have finished reading this staging block
+                        if (lane == 0)
+                            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    }
                     if (tn != staged_tn)
                     {
                         // (re)stage this warp's scales and biases; the column tile changes at most tiles_n times per CTA
                         __syncwarp();
-                        for (int j = lane; j < COLS; j += 32)
+                        for (int jj = lane; jj < COLS; jj += 32)
                         {
-                            const int col = colw + j;
+                            const int col = colw + jj;
                             const bool in_n = col < p.N;
-                            epi_scale[ew][j] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
-                            epi_bias[ew][j] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
+                            epi_scale[ew][jj] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
+                            epi_bias[ew][jj] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
                         }
-                        __syncwarp();
                         staged_tn = tn;
                     }
+                    __syncwarp(); // staged scales visible; the staging block is free for every lane
                     EpiRow er;
                     er.valid = false;
                     er.off = 0;
                     // is the first row of this warp's 32-row block inside the tensor (else the whole block is outside)
                     bool blk_valid;
-                    const bool rows = FAST ? F_SUM : need_rows;
+                    const bool rows = FAST ? false : need_rows;
                     if (p.conv)
                     {
                         blk_valid = q0 + blk_w < p.Q && p0 + blk_h < p.P && n0 + blk_n < p.NB;
@@ -702,40 +762,29 @@ namespace b200
                             er.off = int64_t(m) * p.N;
                         }
                     }
-                    // The residual does not depend on the accumulator: it is fetched before waiting for the MMAs (every
-                    // chunk's in the fast modes, the first chunk's otherwise).  Rows outside the tensor and columns
-                    // beyond the width compute on a zero residual and are never stored.
-                    uint32_t sumw[FAST ? CHUNKS : 1][8];
-#pragma unroll
-                    for (int c = 0; c < (FAST ? CHUNKS : 1); ++c)
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            sumw[c][j] = 0;
-                    const bool sum_regs = (FAST ? F_SUM : (has_sum && vec_ok)) && er.valid;
-                    auto fetch_sum = [&](int c, uint32_t (&dst)[8]) {
-                        if (sum_regs && (FAST ? colw < p.N : colw + 32 * c + 32 <= p.N))
+                    // General loop: the residual does not depend on the accumulator, so the first chunk's is fetched before
+                    // waiting for the MMAs.  Rows outside the tensor and columns beyond the width compute on a zero
+                    // residual and are never stored.
+                    uint32_t sumw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    const bool sum_regs = !FAST && has_sum && vec_ok && er.valid;
+                    auto fetch_sum = [&](int c) {
+                        if (sum_regs && colw + 32 * c + 32 <= p.N)
                         {
                             const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.sum_in) + er.off + colw + 32 * c);
                             const uint4 s0 = sp[0], s1 = sp[1];
-                            dst[0] = s0.x; dst[1] = s0.y; dst[2] = s0.z; dst[3] = s0.w;
-                            dst[4] = s1.x; dst[5] = s1.y; dst[6] = s1.z; dst[7] = s1.w;
+                            sumw[0] = s0.x; sumw[1] = s0.y; sumw[2] = s0.z; sumw[3] = s0.w;
+                            sumw[4] = s1.x; sumw[5] = s1.y; sumw[6] = s1.z; sumw[7] = s1.w;
                         }
                     };
-                    if (FAST)
-                    {
-                        if (F_SUM)
-                        {
-#pragma unroll
-                            for (int c = 0; c < CHUNKS; ++c)
-                                fetch_sum(c, sumw[FAST ? c : 0]);
-                        }
-                    }
-                    else
-                        fetch_sum(0, sumw[0]);
+                    if (!FAST)
+                        fetch_sum(0);
                     {
                         PROF_T0();
                         // the verdict is made warp-uniform: the loop body uses full-mask shuffles and warp syncs
-                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp, BACKOFF_TFULL_NS)))
+                        bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abortp, BACKOFF_TFULL_NS);
+                        if (F_SUM)
+                            ok = ok && ptx::mbar_wait(sum_bar(ew, blk), sum_ph, abortp, BACKOFF_TFULL_NS);
+                        if (!__all_sync(0xffffffffu, ok))
                         {
                             fail = 3001;
                             break;
@@ -745,25 +794,12 @@ namespace b200
                     }
                     ptx::tc_fence_after_sync();
                     PROF_T0();
-                    const uint32_t stage_blk = stage_blk0 + (tile_it & 1) * C::OUT_BYTES;
-                    const uint32_t stage_row = stage_blk + uint32_t(lane) * COLS;
-                    if (stores_in_flight == 2)
-                    {
-                        // the TMA store issued two tiles ago must have finished reading this staging block
-                        PROF_MARK(t_w0);
-                        if (lane == 0)
-                            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                        __syncwarp();
-                        PROF_MARK(t_w1);
-                        PROF_SPAN(10, t_w0, t_w1);
-                        stores_in_flight = 1;
-                    }
                     const uint32_t t_addr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + part * COLS;
+                    // a row's 32 bytes of chunk c are two 16-byte pieces of the swizzled staging block
+                    auto piece = [&](int c, int half) { return stage_row + (((uint32_t(2 * c + half)) ^ sw_xor) << 4); };
                     auto stage_bytes_out = [&](int c, const uint32_t (&w)[8]) {
-                        // 32 bytes of this row -> two 16-byte pieces of the swizzled staging block
-                        const uint32_t c16 = uint32_t(2 * c);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((c16 ^ sw_xor) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((c16 + 1) ^ sw_xor) << 4)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(piece(c, 0)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(piece(c, 1)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
                     };
                     if (FAST)
                     {
@@ -773,11 +809,17 @@ namespace b200
                             uint32_t v[32], w[8];
                             PROF_MARK(t_a);
                             ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                            if (F_SUM)
+                            {
+                                // the residual bytes sit where the result bytes will go
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(sumw[0]), "=r"(sumw[1]), "=r"(sumw[2]), "=r"(sumw[3]) : "r"(piece(c, 0)) : "memory");
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(sumw[4]), "=r"(sumw[5]), "=r"(sumw[6]), "=r"(sumw[7]) : "r"(piece(c, 1)) : "memory");
+                            }
                             ptx::tmem_ld_wait();
                             PROF_MARK(t_b);
                             PROF_SPAN(8, t_a, t_b);
-                            epilogue_chunk_bytes<F_SUMK, F_RELU, F_U8>(v, w, sc_base + 128u * c, bi_base + 128u * c, sumw[FAST ? c : 0], sum_scale,
-                                                                      sum_flip, sum_magic, p.one);
+                            epilogue_chunk_bytes<F_SUMK, F_RELU, F_U8>(v, w, sc_base + 128u * c, bi_base + 128u * c, sumw, sum_scale, sum_flip,
+                                                                       sum_magic, p.one);
                             PROF_MARK(t_c);
                             PROF_SPAN(9, t_b, t_c);
                             stage_bytes_out(c, w);
@@ -786,74 +828,74 @@ namespace b200
                     else
                     {
 #pragma unroll 1
-                    for (int c = 0; c < CHUNKS; ++c)
-                    {
-                        uint32_t v[32], w[8];
-                        if (c > 0)
-                            fetch_sum(c, sumw[0]);
-                        __syncwarp();
-                        ptx::tmem_ld_32x32(t_addr + 32 * c, v);
-                        ptx::tmem_ld_wait();
-                        const int col0 = colw + 32 * c;
-                        if (col0 < p.N) // warp-uniform
+                        for (int c = 0; c < CHUNKS; ++c)
                         {
-                            const bool full_chunk = col0 + 32 <= p.N;
-                            const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
-                            const bool bytes_path = bytes_variant >= 0 && (!has_sum || full_chunk);
-                            if (bytes_path)
+                            uint32_t v[32], w[8];
+                            if (c > 0)
+                                fetch_sum(c);
+                            __syncwarp();
+                            ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                            ptx::tmem_ld_wait();
+                            const int col0 = colw + 32 * c;
+                            if (col0 < p.N) // warp-uniform
                             {
-                                switch (bytes_variant)
+                                const bool full_chunk = col0 + 32 <= p.N;
+                                const uint32_t sc = sc_base + 128u * c, bi = bi_base + 128u * c;
+                                const bool bytes_path = bytes_variant >= 0 && (!has_sum || full_chunk);
+                                if (bytes_path)
                                 {
-                                case 0: epilogue_chunk_bytes<0, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 1: epilogue_chunk_bytes<1, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 2: epilogue_chunk_bytes<2, false, true>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 3: epilogue_chunk_bytes<0, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 4: epilogue_chunk_bytes<1, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 5: epilogue_chunk_bytes<2, false, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 6: epilogue_chunk_bytes<0, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                case 7: epilogue_chunk_bytes<1, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                default: epilogue_chunk_bytes<2, true, false>(v, w, sc, bi, sumw[0], sum_scale, sum_flip, sum_magic, p.one); break;
-                                }
-                            }
-                            else
-                                epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
-                            if (p.tma_store)
-                                stage_bytes_out(c, w);
-                            else if (er.valid && esz == 1)
-                            {
-                                uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
-                                if (full_chunk && vec_ok)
-                                {
-                                    reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                    reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                                    switch (bytes_variant)
+                                    {
+                                    case 0: epilogue_chunk_bytes<0, false, true>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 1: epilogue_chunk_bytes<1, false, true>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 2: epilogue_chunk_bytes<2, false, true>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 3: epilogue_chunk_bytes<0, false, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 4: epilogue_chunk_bytes<1, false, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 5: epilogue_chunk_bytes<2, false, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 6: epilogue_chunk_bytes<0, true, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    case 7: epilogue_chunk_bytes<1, true, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    default: epilogue_chunk_bytes<2, true, false>(v, w, sc, bi, sumw, sum_scale, sum_flip, sum_magic, p.one); break;
+                                    }
                                 }
                                 else
+                                    epilogue_chunk_general(p, v, w, col0, sc, bi, has_sum, sum_scale, er);
+                                if (p.tma_store)
+                                    stage_bytes_out(c, w);
+                                else if (er.valid && esz == 1)
                                 {
+                                    uint8_t* op = static_cast<uint8_t*>(p.out) + er.off + col0;
+                                    if (full_chunk && vec_ok)
+                                    {
+                                        reinterpret_cast<uint4*>(op)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                        reinterpret_cast<uint4*>(op)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                                    }
+                                    else
+                                    {
 #pragma unroll
-                                    for (int j = 0; j < 32; ++j)
-                                        if (col0 + j < p.N)
-                                            op[j] = uint8_t(w[j >> 2] >> (8 * (j & 3)));
+                                        for (int jj = 0; jj < 32; ++jj)
+                                            if (col0 + jj < p.N)
+                                                op[jj] = uint8_t(w[jj >> 2] >> (8 * (jj & 3)));
+                                    }
                                 }
-                            }
-                            else if (er.valid)
-                            {
-                                uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
-                                if (full_chunk && vec_ok)
+                                else if (er.valid)
                                 {
+                                    uint32_t* op = static_cast<uint32_t*>(p.out) + er.off + col0;
+                                    if (full_chunk && vec_ok)
+                                    {
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j)
-                                        reinterpret_cast<uint4*>(op)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                                }
-                                else
-                                {
+                                        for (int jj = 0; jj < 8; ++jj)
+                                            reinterpret_cast<uint4*>(op)[jj] = make_uint4(v[4 * jj], v[4 * jj + 1], v[4 * jj + 2], v[4 * jj + 3]);
+                                    }
+                                    else
+                                    {
 #pragma unroll
-                                    for (int j = 0; j < 32; ++j)
-                                        if (col0 + j < p.N)
-                                            op[j] = v[j];
+                                        for (int jj = 0; jj < 32; ++jj)
+                                            if (col0 + jj < p.N)
+                                                op[jj] = v[jj];
+                                    }
                                 }
                             }
                         }
-                    }
                     }
                     if (warp == 4 && lane == 0)
                     {
@@ -868,7 +910,7 @@ namespace b200
                     __syncwarp();
                     if (lane == 0)
                         ptx::mbar_arrive(tempty_bar(acc));
-                    if ((FAST || p.tma_store) && colw < p.N)
+                    if (FAST || p.tma_store)
                     {
                         // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
                         // rows / columns that fall outside the output tensor are clipped by the TMA unit
@@ -876,14 +918,14 @@ namespace b200
                         __syncwarp();
                         if (lane == 0)
                         {
-                            // a block whose first row lies outside the tensor is skipped
-                            if (p.conv && blk_valid)
+                            // a block whose first row or column lies outside the tensor is skipped (its group stays empty)
+                            if (p.conv && blk_valid && colw < p.N)
                             {
                                 asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                                              ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(q0 + blk_w),
                                              "r"(p0 + blk_h), "r"(n0 + blk_n) : "memory");
                             }
-                            else if (!p.conv && blk_valid)
+                            else if (!p.conv && blk_valid && colw < p.N)
                             {
                                 asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                                              ::"l"(reinterpret_cast<uint64_t>(&maps.out)), "r"(stage_blk), "r"(colw), "r"(tm * BM + quarter * 32)
@@ -891,12 +933,17 @@ namespace b200
                             }
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
-                        ++stores_in_flight;
+                    }
+                    ++idx;
+                    if (++blk == NBUF)
+                    {
+                        blk = 0;
+                        sum_ph ^= 1;
                     }
                 }
             };
-            const int fast_mode = (bytes_variant >= 0 && p.tma_store && p.N % COLS == 0) ? bytes_variant : -1;
-            switch (fast_mode)
+            const bool fast_ok = bytes_variant >= 0 && p.tma_store && p.N % COLS == 0 && (!has_sum || p.tma_sum);
+            switch (fast_ok ? bytes_variant : -1)
             {
             case 0: epilogue_loop(std::integral_constant<int, 0>{}); break;
             case 1: epilogue_loop(std::integral_constant<int, 1>{}); break;
@@ -912,7 +959,6 @@ namespace b200
             // stores must be complete (not just read) before the CTA exits
             if (lane == 0)
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-            }
         }
 
         // ------------------------------------------------------------ common tail
@@ -1031,21 +1077,24 @@ namespace b200
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
-        int fixed = C::FIXED;
-        if (p.tma_store && nkb >= 16 && (SMEM_LIMIT - C::FIXED - 64) / sp.stage_bytes < 4)
+        const int room = SMEM_LIMIT - C::FIXED - sp.b_res_bytes - 64;
+        if (p.tma_store && nkb >= 16 && (room - 2 * C::OUT_BYTES) / sp.stage_bytes < 4)
         {
             // long reductions are MMA-bound: pipeline depth matters more than store efficiency, so the
             // output staging blocks are given to the stage ring and results are written from registers
             p.tma_store = 0;
         }
-        if (!p.tma_store)
-            fixed -= 2 * C::OUT_BYTES;
-        int fit = (SMEM_LIMIT - fixed - sp.b_res_bytes - 64) / sp.stage_bytes;
+        // the residual comes in through the staging blocks (three per warp) when everything about it is regular
+        p.tma_sum = p.tma_sum && p.tma_store && p.sum_in && !p.half_away && p.N % COLS == 0;
+        if (p.tma_sum && (room - 3 * C::OUT_BYTES) / sp.stage_bytes < 2)
+            p.tma_sum = 0;
+        sp.out_bufs = p.tma_store ? (p.tma_sum ? 3 : 2) : 0;
+        sp.out_bytes = sp.out_bufs * C::OUT_BYTES;
+        int fit = (room - sp.out_bytes) / sp.stage_bytes;
         sp.stages = fit > MAX_STAGES ? MAX_STAGES : fit;
         if (sp.stages < 2)
             return B200_ERR_UNSUPPORTED;
-        sp.out_bytes = p.tma_store ? 2 * C::OUT_BYTES : 0;
-        sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + fixed;
+        sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + sp.out_bytes + C::FIXED;
         int tiles = p.tiles_m * p.tiles_n;
         int grid = tiles < num_sms() ? tiles : num_sms();
         qcontract_kernel<BN, BK><<<grid, NUM_THREADS, sp.total_bytes, st>>>(maps, p);
@@ -1108,7 +1157,7 @@ namespace b200
         return (2u << 4) | (a_fmt << 7) | (1u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
     }
 
-    static int pick_bn(int64_t n_out, int64_t tiles_m)
+    static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual)
     {
         if (n_out <= 64)
             return 64;
@@ -1116,7 +1165,29 @@ namespace b200
             return 128;
         // wide outputs: 256-wide tiles halve the A re-reads, but keep enough tiles to fill the SMs
         int64_t tiles256 = tiles_m * ((n_out + 255) / 256);
-        return (tiles256 >= 2 * num_sms() && n_out % 256 == 0) ? 256 : 128;
+        int bn = (tiles256 >= 2 * num_sms() && n_out % 256 == 0) ? 256 : 128;
+        // a residual takes a third staging buffer: with 48 KB stages only two would be left
+        if (bn == 256 && bk == 128 && residual)
+            bn = 128;
+        return bn;
+    }
+
+    // The output map (one epilogue warp's 32 rows x 64 columns per store) and, when there is an aligned residual of
+    // the same geometry, the map it is fetched through.  A shape the TMA unit cannot take falls back to register stores.
+    static void make_out_maps(TensorMaps& maps, ContractParams& p, int rank, const uint64_t* dims, const uint64_t* strides,
+                              const uint32_t* box)
+    {
+        if (!p.tma_store)
+            return;
+        if (make_map(&maps.out, p.out, rank, dims, strides, box, COLS) != B200_OK)
+        {
+            p.tma_store = 0;
+            return;
+        }
+        p.tma_sum = 0;
+        if (p.sum_in && (reinterpret_cast<uintptr_t>(p.sum_in) & 15) == 0 &&
+            make_map(&maps.sum, p.sum_in, rank, dims, strides, box, COLS) == B200_OK)
+            p.tma_sum = 1;
     }
 }
 
@@ -1171,7 +1242,7 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
     p.ntaps = 1;
     p.cblocks = int((K + bk - 1) / bk);
     p.tiles_m = int((M + BM - 1) / BM);
-    const int bn = pick_bn(N, p.tiles_m);
+    const int bn = pick_bn(N, p.tiles_m, bk, epilogue && epilogue->sum_in);
     p.tiles_n = int((N + bn - 1) / bn);
     p.conv = 0;
     fill_epilogue(p, epilogue, out, a_type);
@@ -1189,15 +1260,10 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
     rc = make_map(&maps.b, W, 2, dims_b, str, box_b, bk);
     if (rc != B200_OK)
         return rc;
-    if (p.tma_store)
     {
-        // each epilogue warp stores 32 rows x (its share of the tile's columns) bytes
-        const int cols = bn >= 128 ? bn / 4 : bn / 2;
         uint64_t dims_o[2] = {uint64_t(N), uint64_t(M)}, str_o[1] = {uint64_t(N)};
-        uint32_t box_o[2] = {uint32_t(cols), 32u};
-        rc = make_map(&maps.out, out, 2, dims_o, str_o, box_o, cols);
-        if (rc != B200_OK)
-            return rc;
+        uint32_t box_o[2] = {uint32_t(COLS), 32u};
+        make_out_maps(maps, p, 2, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
@@ -1299,7 +1365,7 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((c->N + p.TN - 1) / p.TN);
-    const int bn = pick_bn(c->K, p.tiles_m);
+    const int bn = pick_bn(c->K, p.tiles_m, bk, epilogue && epilogue->sum_in);
     p.tiles_n = int((c->K + bn - 1) / bn);
     fill_epilogue(p, epilogue, out, data_type);
     p.idesc = make_idesc(data_type, bn);
@@ -1325,16 +1391,12 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
     rc = make_map(&maps.b, filters, 2, dims_b, str_b, box_b, bk);
     if (rc != B200_OK)
         return rc;
-    if (p.tma_store)
     {
         // each epilogue warp stores the 32 tile rows of its TMEM lane quarter: a sub-patch of the tile
         uint64_t dims_o[4] = {uint64_t(c->K), uint64_t(Q), uint64_t(P), uint64_t(c->N)};
         uint64_t str_o[3] = {uint64_t(c->K), uint64_t(c->K) * Q, uint64_t(c->K) * Q * P};
-        const int cols = bn >= 128 ? bn / 4 : bn / 2;
-        uint32_t box_o[4] = {uint32_t(cols), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
-        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, cols);
-        if (rc != B200_OK)
-            return rc;
+        uint32_t box_o[4] = {uint32_t(COLS), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        make_out_maps(maps, p, 4, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
@@ -1388,7 +1450,7 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((N + p.TN - 1) / p.TN);
-    const int bn = pick_bn(K, p.tiles_m);
+    const int bn = pick_bn(K, p.tiles_m, bk, epilogue && epilogue->sum_in);
     p.tiles_n = int((K + bn - 1) / bn);
     fill_epilogue(p, epilogue, out, data_type);
     p.idesc = make_idesc(data_type, bn);
@@ -1407,15 +1469,11 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     rc = make_map(&maps.b, packed_filters, 2, dims_b, str_b, box_b, bk);
     if (rc != B200_OK)
         return rc;
-    if (p.tma_store)
     {
         uint64_t dims_o[4] = {uint64_t(K), uint64_t(Q), uint64_t(P), uint64_t(N)};
         uint64_t str_o[3] = {uint64_t(K), uint64_t(K) * Q, uint64_t(K) * Q * P};
-        const int cols = bn >= 128 ? bn / 4 : bn / 2;
-        uint32_t box_o[4] = {uint32_t(cols), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
-        rc = make_map(&maps.out, out, 4, dims_o, str_o, box_o, cols);
-        if (rc != B200_OK)
-            return rc;
+        uint32_t box_o[4] = {uint32_t(COLS), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        make_out_maps(maps, p, 4, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
