@@ -167,6 +167,7 @@ DeviceContext::DeviceContext(int dev)
         throw std::runtime_error("B200 backend: no CUDA device " + std::to_string(dev));
     cuda_check(cudaSetDevice(dev), "cudaSetDevice");
     cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    cuda_check(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
 }
 
 DeviceContext::DeviceContext(int dev, cudaStream_t external)
@@ -179,15 +180,16 @@ DeviceContext::DeviceContext(int dev, cudaStream_t external)
     if (dev < 0 || dev >= count)
         throw std::runtime_error("B200 backend: no CUDA device " + std::to_string(dev));
     cuda_check(cudaSetDevice(dev), "cudaSetDevice");
+    cuda_check(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
 }
 
 DeviceContext::~DeviceContext()
 {
+    cudaSetDevice(device);
+    if (copy_stream)
+        cudaStreamDestroy(copy_stream);
     if (stream && owns_stream)
-    {
-        cudaSetDevice(device);
         cudaStreamDestroy(stream);
-    }
 }
 
 void DeviceContext::make_current() const
@@ -231,11 +233,31 @@ B200Tensor::B200Tensor(const std::shared_ptr<DeviceContext>& ctx,
 
 B200Tensor::~B200Tensor()
 {
-    if (m_owned && m_ptr)
+    cudaSetDevice(m_ctx->device);
+    if (m_last_use)
     {
-        cudaSetDevice(m_ctx->device);
-        cudaFree(m_ptr);
+        cudaEventSynchronize(m_last_use); // no kernel may still be using the memory when it is released
+        cudaEventDestroy(m_last_use);
     }
+    if (m_owned && m_ptr)
+        cudaFree(m_ptr);
+}
+
+void B200Tensor::mark_used(cudaStream_t compute_stream)
+{
+    if (!m_last_use)
+        cuda_check(cudaEventCreateWithFlags(&m_last_use, cudaEventDisableTiming), "cudaEventCreate");
+    cuda_check(cudaEventRecord(m_last_use, compute_stream), "cudaEventRecord");
+}
+
+void B200Tensor::order_copy_after_use() const
+{
+    // A tensor no call() has used yet may still be the target of work the client enqueued on an external compute
+    // stream (a device pointer wrapped with create_tensor): order after everything on that stream, once.
+    if (m_last_use)
+        cuda_check(cudaStreamWaitEvent(m_ctx->copy_stream, m_last_use, 0), "cudaStreamWaitEvent");
+    else
+        cuda_check(cudaStreamSynchronize(m_ctx->stream), "cudaStreamSynchronize");
 }
 
 void B200Tensor::write(const void* p, size_t n)
@@ -243,8 +265,10 @@ void B200Tensor::write(const void* p, size_t n)
     if (n > m_bytes)
         throw std::out_of_range("B200Tensor::write: access past the end of the tensor");
     m_ctx->make_current();
-    cuda_check(cudaMemcpyAsync(m_ptr, p, n, cudaMemcpyHostToDevice, m_ctx->stream), "cudaMemcpy H2D");
-    m_ctx->synchronize(); // the caller may release p as soon as write() returns
+    order_copy_after_use();
+    cuda_check(cudaMemcpyAsync(m_ptr, p, n, cudaMemcpyHostToDevice, m_ctx->copy_stream), "cudaMemcpy H2D");
+    // the caller may release p as soon as write() returns, and a later call() sees the data
+    cuda_check(cudaStreamSynchronize(m_ctx->copy_stream), "cudaStreamSynchronize");
 }
 
 void B200Tensor::read(void* p, size_t n) const
@@ -252,8 +276,9 @@ void B200Tensor::read(void* p, size_t n) const
     if (n > m_bytes)
         throw std::out_of_range("B200Tensor::read: access past the end of the tensor");
     m_ctx->make_current();
-    cuda_check(cudaMemcpyAsync(p, m_ptr, n, cudaMemcpyDeviceToHost, m_ctx->stream), "cudaMemcpy D2H");
-    m_ctx->synchronize(); // kernels of earlier call()s on this stream have completed here
+    order_copy_after_use(); // the call() that produced this tensor has completed when the copy starts
+    cuda_check(cudaMemcpyAsync(p, m_ptr, n, cudaMemcpyDeviceToHost, m_ctx->copy_stream), "cudaMemcpy D2H");
+    cuda_check(cudaStreamSynchronize(m_ctx->copy_stream), "cudaStreamSynchronize");
     int code = 0;
     if (b200_device_status(&code) != B200_OK)
         throw std::runtime_error("B200 backend: a kernel gave up on a bounded wait (device status " +
@@ -274,6 +299,7 @@ void B200Tensor::copy_from(const runtime::Tensor& source)
         throw std::runtime_error("B200Tensor::copy_from: size mismatch");
     m_ctx->make_current();
     cuda_check(cudaMemcpyAsync(m_ptr, src->m_ptr, m_bytes, cudaMemcpyDeviceToDevice, m_ctx->stream), "cudaMemcpy D2D");
+    mark_used(m_ctx->stream);
 }
 
 // ------------------------------------------------------------------------------------ backend
@@ -1163,7 +1189,13 @@ bool B200Executable::call(const std::vector<std::shared_ptr<runtime::Tensor>>& o
         }
         ++m_calls;
     }
-    // no synchronisation here: Tensor::read() orders itself after this call on the same stream
+    // no synchronisation here: Tensor::read() / write() order themselves after this call through the tensor
+    for (auto& t : inputs)
+        if (auto bt = std::dynamic_pointer_cast<B200Tensor>(t))
+            bt->mark_used(st);
+    for (auto& t : outputs)
+        if (auto bt = std::dynamic_pointer_cast<B200Tensor>(t))
+            bt->mark_used(st);
     return true;
 }
 

@@ -36,6 +36,9 @@ namespace ngraph
             {
                 int device = 0;
                 cudaStream_t stream = nullptr;
+                // Tensor::write / read copy on a stream of their own, ordered against the compute stream only through
+                // the tensor they touch: a host thread can fill the next input while the previous call still runs
+                cudaStream_t copy_stream = nullptr;
                 bool owns_stream = true;
                 explicit DeviceContext(int dev);
                 DeviceContext(int dev, cudaStream_t external); // enqueue on the caller's stream
@@ -56,12 +59,16 @@ namespace ngraph
                 void read(void* p, size_t n) const override;
                 void copy_from(const runtime::Tensor& source) override;
                 void* device_ptr() const { return m_ptr; }
+                // called by Executable::call after its last kernel: later write()s and read()s of this tensor wait for it
+                void mark_used(cudaStream_t compute_stream);
                 const std::shared_ptr<DeviceContext>& context() const { return m_ctx; }
             private:
                 std::shared_ptr<DeviceContext> m_ctx;
                 void* m_ptr = nullptr;
                 size_t m_bytes = 0;
                 bool m_owned = false;
+                cudaEvent_t m_last_use = nullptr; // recorded on the compute stream by the last call() that used the tensor
+                void order_copy_after_use() const;
             };
 
             class B200Executable;

@@ -1161,6 +1161,9 @@ namespace b200
     {
         if (n_out <= 64)
             return 64;
+        // a handful of tiles (small batch x wide layer): narrow tiles spread the weight stream over more SMs
+        if (tiles_m * ((n_out + 127) / 128) * 4 <= num_sms())
+            return 64;
         if (n_out <= 128)
             return 128;
         // wide outputs: 256-wide tiles halve the A re-reads, but keep enough tiles to fill the SMs
