@@ -54,7 +54,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -534,7 +534,7 @@ def main():
         return
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -589,7 +589,6 @@ def main():
     t1 = time.time()
     launches = lib.launch_count()
     ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop(t0, t1)
 
     # end to end: pinned host -> device, kernels, device -> pinned host, every step
     for _ in range(2):
@@ -602,6 +601,7 @@ def main():
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0, time.time())  # both timed regions (device-resident and end-to-end)
     lib.device_status()
 
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")

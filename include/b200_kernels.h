@@ -289,6 +289,26 @@ B200_API int b200_im2col_c4_u8(const void* in, void* out, int64_t N, int64_t H, 
                                int64_t pad_h_above, int64_t pad_w_above, void* stream);
 
 /*
+ * Constant weights in the layout the tensor cores read them in.  nGraph's CPU backend reorders constant weights into
+ * DNNL's blocked formats (src/ngraph/runtime/cpu/pass/cpu_layout.cpp:531-720, ConvolutionLayout<QuantizedConvolution*>
+ * inserting ConvertLayout nodes that constant folding then applies to the weights); this is the B200 counterpart.
+ *   b200_packed_weights_bytes   size of the image of an [N, K] int8 matrix for k-blocks of bk (64 or 128) bytes
+ *   b200_pack_weights_host      HOST function: row-major [N, K] -> image (done once, when the graph is compiled)
+ *   b200_qconv_weight_block     the bk b200_qconv_packed expects for C input channels
+ *   b200_qgemm_packed           b200_qgemm with packed_weights = image of W[N, K] for bk = 128
+ *   b200_qconv_packed           b200_qconv with packed_filters = image of the [K, R*S*C] filter matrix (KRSC order)
+ * Results are identical to the unpacked entry points; only the way weights reach shared memory differs (one bulk copy
+ * per tile and k-block instead of one TMA box row per output channel).
+ */
+B200_API int64_t b200_packed_weights_bytes(int64_t N, int64_t K, int64_t bk);
+B200_API int b200_pack_weights_host(const int8_t* w, int8_t* packed, int64_t N, int64_t K, int64_t bk);
+B200_API int64_t b200_qconv_weight_block(int64_t C);
+B200_API int b200_qgemm_packed(const void* A, int a_type, const int8_t* packed_weights, void* out, int64_t M, int64_t N,
+                               int64_t K, const b200_epilogue* epilogue, void* stream);
+B200_API int b200_qconv_packed(const void* data, int data_type, const int8_t* packed_filters, void* out,
+                               const b200_conv_params* c, const b200_epilogue* epilogue, void* stream);
+
+/*
  * Stride-2 convolutions over <= 4 input channels (network stems, e.g. 7x7 stride 2 on RGB) on the tensor cores,
  * without a patch matrix: the NCHW input is regrouped into 2x2-pixel cells of 4 channels (16 bytes per cell, zero
  * outside the image); one output pixel then needs, per filter row pair, 4 neighbouring cells = 64 contiguous bytes.

@@ -486,7 +486,7 @@ int B200Executable::nhwc_slot(const Output<Node>& out)
 }
 
 // KCRS i8 filters -> KRSC (channels padded to c_pad) in device memory
-int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad)
+int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad, bool* is_image)
 {
     const Shape& fs = filters.get_shape();
     auto c = as_constant(filters);
@@ -500,8 +500,16 @@ int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad)
                 for (size_t r = 0; r < R; ++r)
                     for (size_t s = 0; s < S; ++s)
                         packed[((k * R + r) * S + s) * c_pad + ch] = src[((k * C + ch) * R + r) * S + s];
-        return upload_constant(packed.data(), packed.size());
+        // constant filters go to the device in the tensor cores' shared-memory image (one bulk copy per tile and k-block)
+        const int64_t kg = int64_t(R * S * c_pad), bk = b200_qconv_weight_block(int64_t(c_pad));
+        std::vector<int8_t> image(size_t(b200_packed_weights_bytes(int64_t(K), kg, bk)));
+        kernel_check(b200_pack_weights_host(packed.data(), image.data(), int64_t(K), kg, bk), "b200_pack_weights_host");
+        if (is_image)
+            *is_image = true;
+        return upload_constant(image.data(), image.size());
     }
+    if (is_image)
+        *is_image = false;
     if (c_pad != fs[1])
         throw std::runtime_error("B200 backend: run-time filters need a channel count the kernels take directly");
     return nhwc_slot(filters);
@@ -955,7 +963,8 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
             return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
         });
     }
-    int w = packed_filters(node->input_value(1), c_dev);
+    bool image = false;
+    int w = packed_filters(node->input_value(1), c_dev, &image);
     b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
     emit(node, "qconv", [=](const Ptrs& p, cudaStream_t st) {
         b200_epilogue ee = e;
@@ -963,7 +972,8 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
         ee.scale = static_cast<const float*>(p[scale]);
         ee.sum_in = sum >= 0 ? p[sum] : nullptr;
         ee.sum_scale = sum_scale >= 0 ? static_cast<const float*>(p[sum_scale]) : nullptr;
-        return b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &ee, st);
+        return image ? b200_qconv_packed(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &ee, st)
+                     : b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &ee, st);
     });
     value_of(node->output(0)).nhwc = y;
 }
@@ -1002,7 +1012,8 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
             return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
         });
     }
-    int w = packed_filters(node->input_value(1), c_dev);
+    bool image = false;
+    int w = packed_filters(node->input_value(1), c_dev, &image);
     b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
     const size_t esz = node->get_output_element_type(0).size();
     int y = new_slot(Slot::ARENA, shape_size(os) * esz);
@@ -1014,7 +1025,8 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
         e.round_half_away = 1;
         e.out_zero_point = out_zp;
         e.out_type = out_t;
-        return b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &e, st);
+        return image ? b200_qconv_packed(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &e, st)
+                     : b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[y], &c, &e, st);
     });
     Value& o = value_of(node->output(0));
     if (esz == 1)
@@ -1045,8 +1057,22 @@ void B200Executable::compile_dot_bias(const std::shared_ptr<Node>& node)
     size_t n_scale = shape_size(node->get_input_shape(3));
     if (n_scale != 1 && n_scale != ws[0])
         unsupported(*node, "scale must have 1 or N elements");
-    int a = canonical_slot(node->input_value(0)), w = canonical_slot(node->input_value(1)),
-        bias = canonical_slot(node->input_value(2)), scale = canonical_slot(node->input_value(3));
+    int a = canonical_slot(node->input_value(0)), bias = canonical_slot(node->input_value(2)),
+        scale = canonical_slot(node->input_value(3));
+    // constant weights [N,K] go to the device in the packed image
+    int w;
+    bool w_image = false;
+    if (auto cw = as_constant(node->input_value(1)))
+    {
+        std::vector<int8_t> image(size_t(b200_packed_weights_bytes(int64_t(ws[0]), int64_t(ws[1]), 128)));
+        kernel_check(b200_pack_weights_host(static_cast<const int8_t*>(cw->get_data_ptr()), image.data(), int64_t(ws[0]),
+                                            int64_t(ws[1]), 128),
+                     "b200_pack_weights_host");
+        w = upload_constant(image.data(), image.size());
+        w_image = true;
+    }
+    else
+        w = canonical_slot(node->input_value(1));
     int out_t = dtype_of(node->get_output_element_type(0));
     int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * node->get_output_element_type(0).size());
     int64_t M = as[0], K = as[1], N = ws[0];
@@ -1059,7 +1085,8 @@ void B200Executable::compile_dot_bias(const std::shared_ptr<Node>& node)
         e.scale_count = int64_t(n_scale);
         e.relu = relu;
         e.out_type = out_t;
-        return b200_qgemm(p[a], dt, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
+        return w_image ? b200_qgemm_packed(p[a], dt, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st)
+                       : b200_qgemm(p[a], dt, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
     });
     value_of(node->output(0)).canonical = y;
 }
@@ -1086,8 +1113,10 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
     int scale = scalar_product_scale(node->input_value(2), node->input_value(4), node->input_value(6));
     int a = canonical_slot(node->input_value(0));
     int64_t M = as[0], K = as[1], N = bs[1];
-    // B [K,N] -> W [N,K]: once at compile time for constants, one transpose kernel per call otherwise
+    // B [K,N] -> W [N,K]: once at compile time for constants (and into the packed image), one transpose kernel per
+    // call otherwise
     int w;
+    bool w_image = false;
     if (auto cb = as_constant(node->input_value(1)))
     {
         const int8_t* src = static_cast<const int8_t*>(cb->get_data_ptr());
@@ -1095,7 +1124,10 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
         for (int64_t k = 0; k < K; ++k)
             for (int64_t n = 0; n < N; ++n)
                 t[n * K + k] = src[k * N + n];
-        w = upload_constant(t.data(), t.size());
+        std::vector<int8_t> image(size_t(b200_packed_weights_bytes(N, K, 128)));
+        kernel_check(b200_pack_weights_host(t.data(), image.data(), N, K, 128), "b200_pack_weights_host");
+        w = upload_constant(image.data(), image.size());
+        w_image = true;
     }
     else
     {
@@ -1112,7 +1144,8 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
         e.round_half_away = 1;
         e.out_zero_point = out_zp;
         e.out_type = out_t;
-        return b200_qgemm(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
+        return w_image ? b200_qgemm_packed(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st)
+                       : b200_qgemm(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
     });
     value_of(node->output(0)).canonical = y;
 }

@@ -26,6 +26,7 @@
 //   drains and frees its TMEM, and the host reports B200_ERR_DEVICE_STATUS.
 #include <cuda.h>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <type_traits>
@@ -94,6 +95,8 @@ namespace b200
         int relu, half_away, out_zp, out_type;
         int one;             // the constant 1, opaque to the compiler (see add_fma_pipe)
         int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
+        const int8_t* b_packed; // weights in the block image made by b200_pack_weights_host (null: plain [N,K] matrix through maps.b)
+        int b_blocks_n;      // 64-row blocks per k-block in that image: ceil(N / 64)
         int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
         int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
@@ -406,6 +409,10 @@ namespace b200
     {
         using C = Cfg<BN, BK>;
         constexpr int SPLIT = C::SPLIT, GROUPS = C::GROUPS, NACC = C::NACC;
+#ifdef B200_PROFILE_WAITS
+        const unsigned long long prof_entry_ns = ptx::globaltimer();
+        const long long prof_entry_clk = clock64();
+#endif
         extern __shared__ uint8_t smem_raw[];
         __shared__ int abort_flag;
         __shared__ uint32_t tmem_base_slot;
@@ -460,11 +467,17 @@ namespace b200
         __syncthreads();
         ptx::tc_fence_after_sync();
         const uint32_t tmem_base = tmem_base_slot;
+        // everything above touched only this CTA's own state; from here on global memory of earlier kernels is read
+        // and their inputs are overwritten (no-ops when the launch is not a programmatic dependent one)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
         const int num_tiles = p.tiles_m * p.tiles_n;
         int fail = 0;
 #ifdef B200_PROFILE_WAITS
         const long long prof_kernel_t0 = clock64();
+        if (blockIdx.x == 0 && threadIdx.x == 0)
+            atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[11]), (unsigned long long)(prof_kernel_t0 - prof_entry_clk));
 #endif
 
         if (warp >= 1 && warp <= NUM_PRODUCERS)
@@ -480,10 +493,21 @@ namespace b200
                 if (p.smem.b_resident && pw == 0)
                 {
                     // the single column tile's weights, all k-blocks, once
-                    ptx::mbar_expect_tx(bres_bar, uint32_t(p.smem.b_res_bytes));
                     const int nkb = p.ntaps * p.cblocks;
-                    for (int kb = 0; kb < nkb; ++kb)
-                        ptx::tma_load_2d(bres_base + kb * C::B_BYTES, &maps.b, bres_bar, kb * BK, 0);
+                    if (p.b_packed)
+                    {
+                        // packed image: the column tile's rows of one k-block are one contiguous piece
+                        const uint32_t bytes = uint32_t(min(BN / 64, p.b_blocks_n)) * (64 * BK);
+                        ptx::mbar_expect_tx(bres_bar, bytes * uint32_t(nkb));
+                        for (int kb = 0; kb < nkb; ++kb)
+                            ptx::bulk_load(bres_base + kb * C::B_BYTES, p.b_packed + size_t(kb) * p.b_blocks_n * (64 * BK), bytes, bres_bar);
+                    }
+                    else
+                    {
+                        ptx::mbar_expect_tx(bres_bar, uint32_t(p.smem.b_res_bytes));
+                        for (int kb = 0; kb < nkb; ++kb)
+                            ptx::tma_load_2d(bres_base + kb * C::B_BYTES, &maps.b, bres_bar, kb * BK, 0);
+                    }
                 }
                 for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
                 {
@@ -508,13 +532,22 @@ namespace b200
                                     PROF_ADD(0);
                                 const uint32_t a_dst = smem_base + s * stage_bytes;
                                 const uint32_t b_dst = a_dst + C::A_BYTES;
-                                ptx::mbar_expect_tx(full_bar(s), stage_bytes);
+                                // packed weights: this column tile's 64-row blocks of the k-block, one contiguous piece
+                                const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
+                                const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
+                                ptx::mbar_expect_tx(full_bar(s), uint32_t(C::A_BYTES) + b_bytes);
                                 if (p.conv)
                                     ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
                                 else
                                     ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
                                 if (!p.smem.b_resident)
-                                    ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                                {
+                                    if (p.b_packed)
+                                        ptx::bulk_load(b_dst, p.b_packed + (size_t(kcol / BK) * p.b_blocks_n + size_t(tn) * (BN / 64)) * (64 * BK),
+                                                       b_bytes, full_bar(s));
+                                    else
+                                        ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                                }
                             }
                             if (++turn == NUM_PRODUCERS)
                                 turn = 0;
@@ -983,6 +1016,14 @@ namespace b200
             ptx::tc_fence_after_sync();
             ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
         }
+#ifdef B200_PROFILE_WAITS
+        if (threadIdx.x == 0)
+        {
+            // [12] earliest CTA entry, [13] latest CTA exit (ns, global timer), [14] latest main-loop end
+            atomicMin(reinterpret_cast<unsigned long long*>(&g_wait_cycles[12]), prof_entry_ns);
+            atomicMax(reinterpret_cast<unsigned long long*>(&g_wait_cycles[13]), ptx::globaltimer());
+        }
+#endif
     }
 
     // ---------------------------------------------------------------------------- host side
@@ -1097,7 +1138,24 @@ namespace b200
         sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + sp.out_bytes + C::FIXED;
         int tiles = p.tiles_m * p.tiles_n;
         int grid = tiles < num_sms() ? tiles : num_sms();
-        qcontract_kernel<BN, BK><<<grid, NUM_THREADS, sp.total_bytes, st>>>(maps, p);
+        // Programmatic dependent launch: the CTAs of this launch may become resident while the previous kernel of the
+        // stream drains (SM by SM), set up their barriers, tensor memory and descriptors, and then wait in
+        // griddepcontrol.wait for that kernel's completion and memory flush before touching global memory.
+        static const bool pdl = getenv("B200_NO_PDL") == nullptr;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(unsigned(grid));
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = size_t(sp.total_bytes);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        cudaError_t le = cudaLaunchKernelEx(&cfg, qcontract_kernel<BN, BK>, maps, p);
+        if (le != cudaSuccess)
+            return cuda_status(le, "cudaLaunchKernelEx(qcontract_kernel)");
         return after_launch("qcontract_kernel");
     }
 
@@ -1200,6 +1258,7 @@ extern "C" __attribute__((visibility("default"))) int b200_debug_wait_cycles(lon
     long long z[16] = {0};
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out8, b200::g_wait_cycles, sizeof(z));
+    z[12] = 0x7fffffffffffffffll; // slot of an atomicMin
     if (reset)
         cudaMemcpyToSymbol(b200::g_wait_cycles, z, sizeof(z));
     return 0;
@@ -1220,8 +1279,8 @@ extern "C" int b200_device_status(int* status_out)
     return v == 0 ? B200_OK : B200_ERR_DEVICE_STATUS;
 }
 
-extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out, int64_t M, int64_t N, int64_t K,
-                          const b200_epilogue* epilogue, void* stream)
+static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, void* out, int64_t M, int64_t N, int64_t K,
+                      const b200_epilogue* epilogue, void* stream)
 {
     using namespace b200;
     if (M < 0 || N < 0 || K < 0 || (a_type != B200_U8 && a_type != B200_I8))
@@ -1258,17 +1317,73 @@ extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out,
     rc = make_map(&maps.a[0], A, 2, dims_a, str, box_a, bk);
     if (rc != B200_OK)
         return rc;
-    uint64_t dims_b[2] = {uint64_t(K), uint64_t(N)};
-    uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
-    rc = make_map(&maps.b, W, 2, dims_b, str, box_b, bk);
-    if (rc != B200_OK)
-        return rc;
+    if (packed)
+    {
+        p.b_packed = W;
+        p.b_blocks_n = int((N + 63) / 64);
+    }
+    else
+    {
+        uint64_t dims_b[2] = {uint64_t(K), uint64_t(N)};
+        uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
+        rc = make_map(&maps.b, W, 2, dims_b, str, box_b, bk);
+        if (rc != B200_OK)
+            return rc;
+    }
     {
         uint64_t dims_o[2] = {uint64_t(N), uint64_t(M)}, str_o[1] = {uint64_t(N)};
         uint32_t box_o[2] = {uint32_t(COLS), 32u};
         make_out_maps(maps, p, 2, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_qgemm(const void* A, int a_type, const int8_t* W, void* out, int64_t M, int64_t N, int64_t K,
+                          const b200_epilogue* epilogue, void* stream)
+{
+    return qgemm_impl(A, a_type, W, false, out, M, N, K, epilogue, stream);
+}
+
+extern "C" int b200_qgemm_packed(const void* A, int a_type, const int8_t* packed_weights, void* out, int64_t M, int64_t N,
+                                 int64_t K, const b200_epilogue* epilogue, void* stream)
+{
+    return qgemm_impl(A, a_type, packed_weights, true, out, M, N, K, epilogue, stream);
+}
+
+// ---- packed weight image ---------------------------------------------------------------------------------
+// [N, K] row-major int8 -> k-blocks of `bk` bytes, each a run of 64-row blocks, each block stored exactly as the tensor
+// cores want it in shared memory (K-major rows of bk bytes, 16-byte pieces XOR-swizzled by the row: piece ^ (row & 7)
+// for 128-byte rows, piece ^ ((row >> 1) & 3) for 64-byte rows).  The kernel then fetches a tile's weights with one
+// bulk copy per k-block instead of one TMA box row per output channel.  Rows beyond N and bytes beyond K are zero.
+extern "C" int64_t b200_packed_weights_bytes(int64_t N, int64_t K, int64_t bk)
+{
+    if (N <= 0 || K <= 0 || (bk != 64 && bk != 128))
+        return 0;
+    return ((N + 63) / 64) * 64 * ((K + bk - 1) / bk) * bk;
+}
+
+extern "C" int b200_pack_weights_host(const int8_t* w, int8_t* packed, int64_t N, int64_t K, int64_t bk)
+{
+    if (!w || !packed || N <= 0 || K <= 0 || (bk != 64 && bk != 128))
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t nb = (N + 63) / 64, kbs = (K + bk - 1) / bk;
+    memset(packed, 0, size_t(nb * 64 * kbs * bk));
+    for (int64_t n = 0; n < N; ++n)
+    {
+        const int64_t blk = n / 64, r = n % 64;
+        const int64_t flip = bk == 128 ? (r & 7) : ((r >> 1) & 3);
+        for (int64_t k = 0; k < K; ++k)
+        {
+            const int64_t kb = k / bk, c = k % bk;
+            packed[((kb * nb + blk) * 64 + r) * bk + (((c >> 4) ^ flip) << 4) + (c & 15)] = w[n * K + k];
+        }
+    }
+    return B200_OK;
+}
+
+extern "C" int64_t b200_qconv_weight_block(int64_t C)
+{
+    return (C % 128 == 0) ? 128 : 64;
 }
 
 static int64_t conv_out_dim(int64_t in, int64_t lo, int64_t hi, int64_t win, int64_t dil, int64_t stride)
@@ -1309,8 +1424,8 @@ static void pick_patch(int64_t NB, int64_t P, int64_t Q, int& TW, int& TH, int& 
         }
 }
 
-extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters, void* out,
-                          const b200_conv_params* c, const b200_epilogue* epilogue, void* stream)
+static int qconv_impl(const void* data, int data_type, const int8_t* filters, bool packed, void* out,
+                      const b200_conv_params* c, const b200_epilogue* epilogue, void* stream)
 {
     using namespace b200;
     if (!c || (data_type != B200_U8 && data_type != B200_I8))
@@ -1388,12 +1503,20 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
             if (rc != B200_OK)
                 return rc;
         }
-    const uint64_t kg = uint64_t(c->R * c->S * c->C);
-    uint64_t dims_b[2] = {kg, uint64_t(c->K)}, str_b[1] = {kg};
-    uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
-    rc = make_map(&maps.b, filters, 2, dims_b, str_b, box_b, bk);
-    if (rc != B200_OK)
-        return rc;
+    if (packed)
+    {
+        p.b_packed = filters;
+        p.b_blocks_n = int((c->K + 63) / 64);
+    }
+    else
+    {
+        const uint64_t kg = uint64_t(c->R * c->S * c->C);
+        uint64_t dims_b[2] = {kg, uint64_t(c->K)}, str_b[1] = {kg};
+        uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
+        rc = make_map(&maps.b, filters, 2, dims_b, str_b, box_b, bk);
+        if (rc != B200_OK)
+            return rc;
+    }
     {
         // each epilogue warp stores the 32 tile rows of its TMEM lane quarter: a sub-patch of the tile
         uint64_t dims_o[4] = {uint64_t(c->K), uint64_t(Q), uint64_t(P), uint64_t(c->N)};
@@ -1402,6 +1525,18 @@ extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters
         make_out_maps(maps, p, 4, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_qconv(const void* data, int data_type, const int8_t* filters, void* out,
+                          const b200_conv_params* c, const b200_epilogue* epilogue, void* stream)
+{
+    return qconv_impl(data, data_type, filters, false, out, c, epilogue, stream);
+}
+
+extern "C" int b200_qconv_packed(const void* data, int data_type, const int8_t* packed_filters, void* out,
+                                 const b200_conv_params* c, const b200_epilogue* epilogue, void* stream)
+{
+    return qconv_impl(data, data_type, packed_filters, true, out, c, epilogue, stream);
 }
 
 // Stride-2, <= 4 channel convolution on the cell grid made by b200_stem_pack_input (see layout.cu): Rc taps

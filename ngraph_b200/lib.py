@@ -57,6 +57,11 @@ def _load():
         "b200_global_avgpool_q_nhwc_u8": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
         "b200_im2col_c4_u8": (ci, [vp, vp] + [i64] * 11 + [vp]),
         "b200_requant_scale": (ci, [vp, vp, vp, vp, vp]),
+        "b200_packed_weights_bytes": (i64, [i64] * 3),
+        "b200_pack_weights_host": (ci, [vp, vp] + [i64] * 3),
+        "b200_qconv_weight_block": (i64, [i64]),
+        "b200_qgemm_packed": (ci, [vp, ci, vp, vp, i64, i64, i64, ctypes.POINTER(Epilogue), vp]),
+        "b200_qconv_packed": (ci, [vp, ci, vp, vp, ctypes.POINTER(ConvParams), ctypes.POINTER(Epilogue), vp]),
         "b200_stem_geometry": (ci, [i64] * 8 + [p64] * 5),
         "b200_stem_pack_filter_host": (ci, [vp, vp] + [i64] * 6),
         "b200_stem_pack_input": (ci, [vp, vp] + [i64] * 10 + [vp]),

@@ -52,13 +52,15 @@ def nhwc(a):
     return np.ascontiguousarray(a.transpose(0, 2, 3, 1))
 
 
-def run_conv(ops, data_nchw, filt_kcrs, bias, scale, cs, out_dt, relu, sum_in=None, sum_scale=None, core=False, out_zp=0):
+def run_conv(ops, data_nchw, filt_kcrs, bias, scale, cs, out_dt, relu, sum_in=None, sum_scale=None, core=False, out_zp=0,
+             packed=False):
     cp = ops.conv_params((cs.N, cs.H, cs.W, cs.C), (cs.K, cs.R, cs.S, cs.C), (cs.stride_h, cs.stride_w),
                          (cs.pad_h, cs.pad_w), (cs.pad_h_above, cs.pad_w_above), (cs.dil_h, cs.dil_w))
     out = ops.qconv(dev(nhwc(data_nchw)), dev(nhwc(filt_kcrs)), dev(np.atleast_1d(scale).astype(np.float32)),
                     TDT[np.dtype(out_dt)], cp, bias=dev(bias), relu=relu,
                     sum_in=None if sum_in is None else dev(nhwc(sum_in)),
-                    sum_scale=None if sum_in is None else dev(np.array([sum_scale], np.float32)), core=core, out_zp=out_zp)
+                    sum_scale=None if sum_in is None else dev(np.array([sum_scale], np.float32)), core=core, out_zp=out_zp,
+                    packed=packed)
     return out.cpu().numpy().transpose(0, 3, 1, 2)
 
 
@@ -132,11 +134,12 @@ def test_qgemm_vs_oracle(ops, mnk, a_signed):
         scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=n if per_channel else 1)) * 40.0 / acc_sigma).astype(np.float32)
         for out_dt, relu in ((np.uint8, True), (np.int8, False), (np.float32, False), (np.float32, True), (np.int32, False)):
             exp = ref.qgemm_fused(a, w, bias, scale, out_dt, relu=relu)
-            got = ops.qgemm(dev(a), dev(w), dev(scale), TDT[np.dtype(out_dt)], bias=dev(bias), relu=relu).cpu().numpy()
-            if out_dt == np.float32:
-                same_f32(got, exp)
-            else:
-                np.testing.assert_array_equal(got, exp, err_msg="%s %s relu=%d" % (mnk, out_dt, relu))
+            for packed in (False, True):  # plain [N,K] weights through TMA / the packed image through bulk copies
+                got = ops.qgemm(dev(a), dev(w), dev(scale), TDT[np.dtype(out_dt)], bias=dev(bias), relu=relu, packed=packed).cpu().numpy()
+                if out_dt == np.float32:
+                    same_f32(got, exp)
+                else:
+                    np.testing.assert_array_equal(got, exp, err_msg="%s %s relu=%d packed=%d" % (mnk, out_dt, relu, packed))
     # core contract (QuantizedDot): half-away rounding, output zero point, saturation
     scale1 = np.float32(30.0 / acc_sigma)
     for out_dt, zp in ((np.int8, 3), (np.uint8, 100), (np.int32, -5)):
@@ -171,6 +174,8 @@ CONV_CASES = [
     (1, 64, 12, 12, 16, 3, 3, (1, 1), (2, 2), (2, 2), (2, 2)),
     (2, 256, 9, 9, 40, 3, 3, (1, 2), (1, 0), (0, 1), (1, 1)),
     (5, 64, 5, 6, 8, 5, 3, (1, 1), (2, 1), (2, 1), (1, 1)),
+    (4, 128, 10, 10, 320, 3, 3, (1, 1), (1, 1), (1, 1), (1, 1)),   # three column tiles, the last one ragged
+    (40, 64, 16, 16, 192, 1, 1, (1, 1), (0, 0), (0, 0), (1, 1)),   # 80 row tiles x width 192
 ]
 
 
@@ -187,12 +192,14 @@ def test_qconv_vs_oracle(ops, cfg):
     p, q = ref.conv_out_hw(cs)
     for out_dt, relu in ((np.uint8, True), (np.int8, False)):
         exp = ref.qconv_fused(data, filt, bias, scale, cs, out_dt, relu=relu)
-        got = run_conv(ops, data, filt, bias, scale, cs, out_dt, relu)
-        np.testing.assert_array_equal(got, exp, err_msg=str(cfg))
+        for packed in (False, True):
+            got = run_conv(ops, data, filt, bias, scale, cs, out_dt, relu, packed=packed)
+            np.testing.assert_array_equal(got, exp, err_msg="%s packed=%d" % (cfg, packed))
     sum_u8 = rng.integers(0, 256, size=(n, k, p, q)).astype(np.uint8)
     exp = ref.qconv_fused(data, filt, bias, scale, cs, np.uint8, relu=True, sum_in=sum_u8, sum_scale=np.float32(0.61))
-    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.61)
-    np.testing.assert_array_equal(got, exp, err_msg="add " + str(cfg))
+    for packed in (False, True):
+        got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.61, packed=packed)
+        np.testing.assert_array_equal(got, exp, err_msg="add %s packed=%d" % (cfg, packed))
     sum_i8 = rng.integers(-128, 128, size=(n, k, p, q)).astype(np.int8)
     exp = ref.qconv_fused(data, filt, bias, scale[:1], cs, np.int8, relu=True, sum_in=sum_i8, sum_scale=np.float32(1.3))
     got = run_conv(ops, data, filt, bias, scale[:1], cs, np.int8, True, sum_in=sum_i8, sum_scale=1.3)
