@@ -159,7 +159,8 @@ class ResNet50:
     def setup(self, torch, rank, local_rank, world):
         from ngraph_b200 import ngraph_api as ng
         from ngraph_b200.harness.resnet50_int8 import synthetic_images
-        self.torch, self.ng, self.world = torch, ng, world
+        from ngraph_b200 import sharding
+        self.torch, self.ng, self.world, self.sharding = torch, ng, world, sharding
         model = self.build_model()
         ng.load_b200()
         stream = torch.cuda.current_stream().cuda_stream
@@ -188,7 +189,7 @@ class ResNet50:
     def step(self):
         self.exe.call([self.t_out], [self.t_in], validate=False)
         if self.gathered is not None:
-            self.torch.distributed.all_gather_into_tensor(self.gathered, self.logits)
+            self.sharding.gather_rows(self.logits, [self.batch] * self.world, out=self.gathered)
 
     def step_e2e(self):
         """One batch end to end through the plugin's public API: Tensor::write of the batch (pinned host memory),
@@ -201,7 +202,7 @@ class ResNet50:
             self.e2e_primed = True
         self.exe.call([self.t_out], [self.t_pipe[cur]], validate=False)
         if self.gathered is not None:
-            self.torch.distributed.all_gather_into_tensor(self.gathered, self.logits)
+            self.sharding.gather_rows(self.logits, [self.batch] * self.world, out=self.gathered)
         self.t_pipe[cur ^ 1].write_ptr(self.pin_in.data_ptr(), nbytes)  # next batch, overlapping this one's kernels
         self.t_out.read_ptr(self.pin_out.data_ptr(), self.pin_out.numel() * 4)
         self.e2e_i += 1
