@@ -333,6 +333,23 @@ B200_API int b200_qconv_stem(const void* cells, int data_type, const int8_t* pac
                              int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue, void* stream);
 
 /*
+ * b200_stem_pack_input + b200_qconv_stem in one call that allocates nothing.  No counterpart in the reference: nGraph
+ * backends allocate their workspaces when a Function is compiled.  The cell grid lives in a fixed 16 MiB device array
+ * inside this library (b200_qconv_stem_static_capacity() bytes; a call needs N * Hc * Wc * 16 of it, Hc and Wc from
+ * b200_stem_geometry), looked up once per device at the first call on that device; that first call should be made before
+ * a stream capture starts.  Larger problems are refused with B200_ERR_TOO_LARGE before anything is launched.  Nothing in
+ * the array has to be zero beforehand: every cell, padding cells included, is written by the packing kernel before the
+ * convolution reads it.  The array is shared by all callers of the device: two calls whose kernels can overlap in time
+ * (different streams, different threads) race on it; calls on one stream are ordered and safe.  in_nchw is the one-byte
+ * NCHW input [N, C <= 4, H, W]; the other arguments and the result are those of b200_qconv_stem.
+ */
+B200_API int64_t b200_qconv_stem_static_capacity(void);
+B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const int8_t* packed_filters, void* out, int64_t N,
+                                    int64_t C, int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h,
+                                    int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                    const b200_epilogue* epilogue, void* stream);
+
+/*
  * out[0] = input_scale[0] * filter_scale[0] / output_scale[0] in fp32, left to right: the requantisation
  * scale of op::v0::QuantizedDot / QuantizedConvolution (src/ngraph/runtime/reference/dot.hpp:154,
  * src/ngraph/runtime/reference/convolution.hpp:254) when the three scales are run-time tensors.

@@ -1615,3 +1615,57 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
 }
+
+// ---- stem convolution that allocates nothing -------------------------------------------------------------
+// The cell grid b200_qconv_stem reads is scratch memory (global memory that is neither an input nor an output).
+// This variant keeps it in a fixed device array of this library instead of taking a caller-allocated buffer, so that
+// the whole call (pack + convolution) enters no allocator at all.
+namespace b200
+{
+    constexpr size_t STEM_SCRATCH_BYTES = size_t(16) << 20; // 16 MiB: e.g. 79 images of 224x224 (115x115 cells of 16 bytes)
+    static __device__ __align__(256) unsigned char g_stem_scratch[STEM_SCRATCH_BYTES];
+}
+
+extern "C" int64_t b200_qconv_stem_static_capacity(void)
+{
+    return int64_t(b200::STEM_SCRATCH_BYTES);
+}
+
+extern "C" int b200_qconv_stem_static(const void* in_nchw, int data_type, const int8_t* packed_filters, void* out, int64_t N,
+                                      int64_t C, int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h,
+                                      int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue,
+                                      void* stream)
+{
+    using namespace b200;
+    int64_t P, Q, Hc, Wc, Rc;
+    int rc = b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc);
+    if (rc != B200_OK)
+        return rc;
+    if (N < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    // sizes the fixed array cannot hold are refused before anything is launched
+    if (Hc * Wc > int64_t(STEM_SCRATCH_BYTES / 16) || N > int64_t(STEM_SCRATCH_BYTES / 16) / (Hc * Wc))
+        return B200_ERR_TOO_LARGE;
+    // one symbol lookup per device, at the first call on that device (it may load the module: do it before any
+    // stream capture begins)
+    static void* scratch_of_device[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return cuda_status(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64)
+        return B200_ERR_UNSUPPORTED;
+    void* scratch = scratch_of_device[dev];
+    if (!scratch)
+    {
+        e = cudaGetSymbolAddress(&scratch, g_stem_scratch);
+        if (e != cudaSuccess || !scratch)
+            return cuda_status(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(stem scratch)");
+        scratch_of_device[dev] = scratch;
+    }
+    rc = b200_stem_pack_input(in_nchw, scratch, N, C, H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, stream);
+    if (rc != B200_OK)
+        return rc;
+    return b200_qconv_stem(scratch, data_type, packed_filters, out, N, H, W, K, R, S, pad_h, pad_w, pad_h_above, pad_w_above,
+                           epilogue, stream);
+}

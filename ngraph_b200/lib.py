@@ -66,6 +66,8 @@ def _load():
         "b200_stem_pack_filter_host": (ci, [vp, vp] + [i64] * 6),
         "b200_stem_pack_input": (ci, [vp, vp] + [i64] * 10 + [vp]),
         "b200_qconv_stem": (ci, [vp, ci, vp, vp] + [i64] * 10 + [ctypes.POINTER(Epilogue), vp]),
+        "b200_qconv_stem_static_capacity": (i64, []),
+        "b200_qconv_stem_static": (ci, [vp, ci, vp, vp] + [i64] * 11 + [ctypes.POINTER(Epilogue), vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
