@@ -315,7 +315,11 @@ B200_API int b200_qconv_packed(const void* data, int data_type, const int8_t* pa
  *   b200_stem_geometry          P, Q (output size), Hc, Wc (cell grid), Rc (cell rows per window); unsupported if a
  *                               filter row spans more than 4 cell columns (S > 7 or 8)
  *   b200_stem_pack_filter_host  HOST function: KCRS i8 filter -> [K, Rc*64] in the matching order (done once, at compile)
+ *   b200_stem_cells_bytes       bytes the cell grid buffer must have: N*Hc*Wc*16 plus 2112 bytes the convolution may
+ *                               read past the last cell (their contents do not matter and are never written)
  *   b200_stem_pack_input        device: NCHW one-byte input -> cell grid [N, Hc, Wc, 16]
+ *   b200_stem_pack_input_f32    device: the same from the f32 input of a per-tensor op::v0::Quantize (scale[1], zero
+ *                               point[1] of q_type u8 / i8, round_mode as in b200_quantize): Quantize fused into the packing
  *   b200_qconv_stem             the convolution with the fused epilogue; out is channels-last [N,P,Q,K]
  * Same accumulation as runtime::reference::general_convolution (src/ngraph/runtime/reference/convolution.hpp:59-265)
  * for strides {2,2}, window dilation 1; used for QuantizedConvolutionBias and friends like b200_qconv.
@@ -323,11 +327,17 @@ B200_API int b200_qconv_packed(const void* data, int data_type, const int8_t* pa
 B200_API int b200_stem_geometry(int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
                                 int64_t pad_h_above, int64_t pad_w_above, int64_t* P, int64_t* Q, int64_t* Hc,
                                 int64_t* Wc, int64_t* Rc);
+B200_API int64_t b200_stem_cells_bytes(int64_t N, int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                                       int64_t pad_h_above, int64_t pad_w_above);
 B200_API int b200_stem_pack_filter_host(const int8_t* kcrs, int8_t* packed, int64_t K, int64_t C, int64_t R, int64_t S,
                                         int64_t pad_h, int64_t pad_w);
 B200_API int b200_stem_pack_input(const void* in_nchw, void* cells, int64_t N, int64_t C, int64_t H, int64_t W,
                                   int64_t R, int64_t S, int64_t pad_h, int64_t pad_w, int64_t pad_h_above,
                                   int64_t pad_w_above, void* stream);
+B200_API int b200_stem_pack_input_f32(const float* in_nchw, const float* scale, const void* zero_point, int q_type,
+                                      int round_mode, void* cells, int64_t N, int64_t C, int64_t H, int64_t W, int64_t R,
+                                      int64_t S, int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                      void* stream);
 B200_API int b200_qconv_stem(const void* cells, int data_type, const int8_t* packed_filters, void* out, int64_t N,
                              int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
                              int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue, void* stream);
@@ -335,8 +345,7 @@ B200_API int b200_qconv_stem(const void* cells, int data_type, const int8_t* pac
 /*
  * b200_stem_pack_input + b200_qconv_stem in one call that allocates nothing.  No counterpart in the reference: nGraph
  * backends allocate their workspaces when a Function is compiled.  The cell grid lives in a fixed 16 MiB device array
- * inside this library (b200_qconv_stem_static_capacity() bytes; a call needs N * Hc * Wc * 16 of it, Hc and Wc from
- * b200_stem_geometry), looked up once per device at the first call on that device; that first call should be made before
+ * inside this library (b200_qconv_stem_static_capacity() bytes; a call needs b200_stem_cells_bytes(...) of it), looked up once per device at the first call on that device; that first call should be made before
  * a stream capture starts.  Larger problems are refused with B200_ERR_TOO_LARGE before anything is launched.  Nothing in
  * the array has to be zero beforehand: every cell, padding cells included, is written by the packing kernel before the
  * convolution reads it.  The array is shared by all callers of the device: two calls whose kernels can overlap in time

@@ -705,6 +705,60 @@ static std::vector<int64_t> to_i64(const Shape& s)
     return std::vector<int64_t>(s.begin(), s.end());
 }
 
+namespace
+{
+    // A stride-2 convolution over <= 4 channels with constant filters (a network stem): the cell-grid path applies.
+    bool stem_geometry_of(const Node* conv, b200_conv_params& c, int64_t geo[5])
+    {
+        Strides strides, dilation, data_dilation;
+        CoordinateDiff below, above;
+        if (auto o = as_type<const op::v0::QuantizedConvolutionBias>(conv))
+        {
+            strides = o->get_window_movement_strides(); dilation = o->get_window_dilation_strides();
+            data_dilation = o->get_data_dilation_strides(); below = o->get_padding_below(); above = o->get_padding_above();
+        }
+        else if (auto o2 = as_type<const op::v0::QuantizedConvolutionRelu>(conv))
+        {
+            strides = o2->get_window_movement_strides(); dilation = o2->get_window_dilation_strides();
+            data_dilation = o2->get_data_dilation_strides(); below = o2->get_padding_below(); above = o2->get_padding_above();
+        }
+        else
+            return false;
+        const Shape& ds = conv->get_input_shape(0);
+        const Shape& fs = conv->get_input_shape(1);
+        if (ds.size() != 4 || fs.size() != 4 || ds[1] > 4 || strides != Strides{2, 2} || dilation != Strides{1, 1} ||
+            data_dilation != Strides{1, 1} || !as_constant(conv->input_value(1)))
+            return false;
+        for (auto v : below) if (v < 0) return false;
+        for (auto v : above) if (v < 0) return false;
+        c.N = ds[0]; c.H = ds[2]; c.W = ds[3]; c.C = 4;
+        c.K = fs[0]; c.R = fs[2]; c.S = fs[3];
+        c.stride_h = c.stride_w = 2;
+        c.pad_h = below[0]; c.pad_w = below[1]; c.pad_h_above = above[0]; c.pad_w_above = above[1];
+        c.dilation_h = c.dilation_w = 1;
+        return b200_stem_geometry(c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above, c.pad_w_above, &geo[0], &geo[1], &geo[2],
+                                  &geo[3], &geo[4]) == B200_OK;
+    }
+
+    // Quantize(f32 -> u8/i8, per-tensor) whose only consumer is the data input of such a stem convolution: the
+    // quantisation is done by the kernel that packs the stem's cell grid and the one-byte image is never written.
+    bool quantize_feeds_stem(const Node* qn)
+    {
+        auto q = as_type<const op::v0::Quantize>(qn);
+        if (!q || !q->get_axes().empty() || q->get_input_element_type(0) != element::f32)
+            return false;
+        const element::Type& ot = q->get_output_element_type(0);
+        if (ot != element::u8 && ot != element::i8)
+            return false;
+        auto users = q->output(0).get_target_inputs();
+        if (users.size() != 1 || users.begin()->get_index() != 0)
+            return false;
+        b200_conv_params c;
+        int64_t geo[5];
+        return stem_geometry_of(users.begin()->get_node(), c, geo);
+    }
+}
+
 void B200Executable::compile_quantize(const std::shared_ptr<Node>& node)
 {
     auto q = as_type_ptr<op::v0::Quantize>(node);
@@ -713,6 +767,11 @@ void B200Executable::compile_quantize(const std::shared_ptr<Node>& node)
     {
         if (try_compile_avgpool_head(node))
             return;
+    }
+    if (quantize_feeds_stem(node.get()))
+    {
+        value_of(node->output(0)).skipped = true; // emitted together with the convolution
+        return;
     }
     if (node->get_input_element_type(0) != element::f32)
         unsupported(*node, "input element type " + node->get_input_element_type(0).get_type_name());
@@ -885,13 +944,30 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
                                              c.S, c.pad_h, c.pad_w),
                   "b200_stem_pack_filter_host");
             int wslot = upload_constant(w.data(), w.size());
-            int xc = canonical_slot(node->input_value(0));
-            int cells = new_slot(Slot::ARENA, size_t(c.N) * size_t(Hc) * size_t(Wc) * 16);
+            int cells = new_slot(Slot::ARENA, size_t(b200_stem_cells_bytes(c.N, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above,
+                                                                           c.pad_w_above)));
             int64_t Ci = C;
-            emit(node, "stem_cells", [=](const Ptrs& p, cudaStream_t st) {
-                return b200_stem_pack_input(p[xc], p[cells], c.N, Ci, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above,
-                                            c.pad_w_above, st);
-            });
+            if (value_of(node->input_value(0)).skipped)
+            {
+                // the producing Quantize was held back (quantize_feeds_stem): quantise while packing
+                auto qn = as_type_ptr<op::v0::Quantize>(node->input_value(0).get_node_shared_ptr());
+                int xf = canonical_slot(qn->input_value(0)), qs = canonical_slot(qn->input_value(1)),
+                    qz = canonical_slot(qn->input_value(2));
+                int mode = static_cast<int>(qn->get_round_mode());
+                emit(qn, "stem_cells_quantize", [=](const Ptrs& p, cudaStream_t st) {
+                    return b200_stem_pack_input_f32(static_cast<const float*>(p[xf]), static_cast<const float*>(p[qs]), p[qz], dt,
+                                                    mode, p[cells], c.N, Ci, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w,
+                                                    c.pad_h_above, c.pad_w_above, st);
+                });
+            }
+            else
+            {
+                int xc = canonical_slot(node->input_value(0));
+                emit(node, "stem_cells", [=](const Ptrs& p, cudaStream_t st) {
+                    return b200_stem_pack_input(p[xc], p[cells], c.N, Ci, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above,
+                                                c.pad_w_above, st);
+                });
+            }
             emit(node, "stem_qconv", [=](const Ptrs& p, cudaStream_t st) {
                 b200_epilogue ee = e;
                 ee.bias = bias >= 0 ? static_cast<const int32_t*>(p[bias]) : nullptr;

@@ -9,6 +9,8 @@ namespace b200
 {
     // Count of kernels launched through this library (read by b200_launch_count).
     extern std::atomic<uint64_t> g_launches;
+    // b200_set_fast_division: 0 makes every Quantize kernel use the plain IEEE division
+    extern std::atomic<int> g_fast_division;
 
     // Records the CUDA error text for b200_last_cuda_error and maps to a status.
     int cuda_status(cudaError_t err, const char* where);
@@ -111,4 +113,26 @@ namespace b200
         q = __fadd_rn(q, zp);
         return clamp_cast<Q>(q);
     }
+
+    // Fast path of round-to-nearest-even Quantize to 8 bits (see quantize_rows_rne8_kernel): is the scale one for
+    // which y = RN(1/s), q0 = RN(x*y), e = fma(-q0,s,x), q = fma(e,y,q0) is the correctly rounded x / s.
+    __device__ __forceinline__ bool scale_allows_fast_division(float s)
+    {
+        const uint32_t b = __float_as_uint(s);
+        const uint32_t ex = (b >> 23) & 0xFF, man = b & 0x7FFFFF;
+        return ex >= 127 - 40 && ex <= 127 + 40 && man != 0x7FFFFF;
+    }
+
+    template <typename Q>
+    __device__ __forceinline__ int quantize_rne_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
+    {
+        const float q0 = __fmul_rn(x, y);
+        const float e = __fmaf_rn(-q0, s, x);
+        const float q1 = __fmaf_rn(e, y, q0);
+        const float q = (fabsf(q0) < 16777216.0f) ? q1 : q0; // huge, inf and NaN quotients skip the correction
+        const int i = __float2int_rn(q);                     // saturating
+        const int r = min(max(i, lo_minus_zp), hi_minus_zp) + zp;
+        return (x != x) ? 0 : r;                             // NaN -> 0, as clamp_cast
+    }
+
 }

@@ -424,6 +424,110 @@ namespace b200
     }
 }
 
+namespace b200
+{
+    // Quantize (per-tensor scale and zero point, any round mode) fused into the cell packing: the f32 NCHW image is
+    // read once and the one-byte NCHW intermediate never exists.  Same arithmetic as quantize_one in the Quantize
+    // kernels (IEEE division, the reference's rounding sequence, clamp).
+    template <typename Q>
+    __device__ __forceinline__ uint32_t quantize_byte(float x, float scale, float zp, int mode)
+    {
+        Q v;
+        switch (mode)
+        {
+        case B200_ROUND_NEAREST_TOWARD_INFINITY: v = quantize_one<Q, B200_ROUND_NEAREST_TOWARD_INFINITY>(x, scale, zp); break;
+        case B200_ROUND_NEAREST_TOWARD_ZERO: v = quantize_one<Q, B200_ROUND_NEAREST_TOWARD_ZERO>(x, scale, zp); break;
+        case B200_ROUND_NEAREST_UPWARD: v = quantize_one<Q, B200_ROUND_NEAREST_UPWARD>(x, scale, zp); break;
+        case B200_ROUND_NEAREST_DOWNWARD: v = quantize_one<Q, B200_ROUND_NEAREST_DOWNWARD>(x, scale, zp); break;
+        case B200_ROUND_NEAREST_TOWARD_EVEN: v = quantize_one<Q, B200_ROUND_NEAREST_TOWARD_EVEN>(x, scale, zp); break;
+        case B200_ROUND_TOWARD_INFINITY: v = quantize_one<Q, B200_ROUND_TOWARD_INFINITY>(x, scale, zp); break;
+        case B200_ROUND_TOWARD_ZERO: v = quantize_one<Q, B200_ROUND_TOWARD_ZERO>(x, scale, zp); break;
+        case B200_ROUND_UP: v = quantize_one<Q, B200_ROUND_UP>(x, scale, zp); break;
+        default: v = quantize_one<Q, B200_ROUND_DOWN>(x, scale, zp); break;
+        }
+        return uint32_t(uint8_t(v));
+    }
+
+    // One thread per cell.  FAST: round-to-nearest-even with a scale that allows the division-free quotient.
+    // PAIRS: W even and the image 8-byte aligned, so the two pixels of a cell row are one float2 load.
+    template <typename Q, bool FAST, bool PAIRS>
+    __global__ void __launch_bounds__(256) s2d_pack_f32_kernel(const float* __restrict__ in, const float* __restrict__ scale,
+                                                               const Q* __restrict__ zero_point, int mode, uint4* __restrict__ out,
+                                                               int N, int C, int H, int W, int Hc, int Wc, int eh, int ew)
+    {
+        const float s = __ldg(scale);
+        const int zi = int(__ldg(zero_point));
+        const float zp = float(zi), y = __frcp_rn(s);
+        const int lo = int(QLimits<Q>::lo) - zi, hi = int(QLimits<Q>::hi) - zi;
+        const bool fast = FAST && scale_allows_fast_division(s); // the scale is only known here
+        auto quant = [&](float x) -> uint32_t {
+            if (fast)
+                return uint32_t(quantize_rne_fast<Q>(x, s, y, lo, hi, zi)) & 0xFFu;
+            return quantize_byte<Q>(x, s, zp, mode);
+        };
+        // pixels outside the image stay zero BYTES: the convolution pads the quantized tensor (the reference skips
+        // padding positions), not the real-valued one
+        const uint32_t total = uint32_t(N) * Hc * Wc;
+        const size_t plane = size_t(H) * W;
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+        {
+            const uint32_t cw = i % Wc, t = i / Wc;
+            const uint32_t ch = t % Hc, n = t / Hc;
+            const int w0 = 2 * int(cw) - ew, h0 = 2 * int(ch) - eh;
+            float v[2][2][4];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+            {
+                const int h = h0 + dy;
+                const bool row_ok = h >= 0 && h < H;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                {
+                    v[dy][0][c] = v[dy][1][c] = 0.0f;
+                    if (c < C && row_ok)
+                    {
+                        const float* rowp = in + (size_t(n) * C + c) * plane + size_t(h) * W;
+                        if (PAIRS)
+                        {
+                            if (w0 >= 0 && w0 + 1 < W)
+                            {
+                                const float2 f = *reinterpret_cast<const float2*>(rowp + w0);
+                                v[dy][0][c] = f.x;
+                                v[dy][1][c] = f.y;
+                            }
+                        }
+                        else
+                        {
+                            if (w0 >= 0 && w0 < W)
+                                v[dy][0][c] = rowp[w0];
+                            if (w0 + 1 >= 0 && w0 + 1 < W)
+                                v[dy][1][c] = rowp[w0 + 1];
+                        }
+                    }
+                }
+            }
+            uint32_t words[4];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int dx = 0; dx < 2; ++dx)
+                {
+                    const int h = h0 + dy, w = w0 + dx;
+                    uint32_t word = 0;
+                    if (h >= 0 && h < H && w >= 0 && w < W)
+                    {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c < C)
+                                word |= quant(v[dy][dx][c]) << (8 * c);
+                    }
+                    words[dy * 2 + dx] = word;
+                }
+            out[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        }
+    }
+}
+
 extern "C" int b200_stem_geometry(int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
                                   int64_t pad_h_above, int64_t pad_w_above, int64_t* P, int64_t* Q, int64_t* Hc, int64_t* Wc,
                                   int64_t* Rc)
@@ -489,4 +593,53 @@ extern "C" int b200_stem_pack_input(const void* in_nchw, void* cells, int64_t N,
                                                                        static_cast<uint4*>(cells), int(N), int(C), int(H), int(W),
                                                                        int(Hc), int(Wc), int(eh), int(ew));
     return after_launch("b200_stem_pack_input");
+}
+
+extern "C" int b200_stem_pack_input_f32(const float* in_nchw, const float* scale, const void* zero_point, int q_type,
+                                        int round_mode, void* cells, int64_t N, int64_t C, int64_t H, int64_t W, int64_t R,
+                                        int64_t S, int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                        void* stream)
+{
+    using namespace b200;
+    if (N < 0 || C <= 0 || C > 4 || (q_type != B200_U8 && q_type != B200_I8) || round_mode < 0 || round_mode > B200_ROUND_DOWN)
+        return B200_ERR_INVALID_ARGUMENT;
+    int64_t P, Q, Hc, Wc, Rc;
+    int rc = b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc);
+    if (rc != B200_OK)
+        return rc;
+    if (N == 0)
+        return B200_OK;
+    if (!in_nchw || !scale || !zero_point || !cells || (reinterpret_cast<uintptr_t>(cells) & 15))
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t eh = pad_h + (pad_h & 1), ew = pad_w + (pad_w & 1);
+    int64_t total = N * Hc * Wc;
+    int64_t blocks = (total + 255) / 256;
+    unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (total >= (int64_t(1) << 31))
+        return B200_ERR_TOO_LARGE;
+    // float2 loads need an even width, an even column shift (always) and an 8-byte aligned image
+    const bool pairs = (W % 2 == 0) && (reinterpret_cast<uintptr_t>(in_nchw) & 7) == 0;
+    // round-to-nearest-even may take the division-free quotient; the kernel checks the scale (it lives on the device)
+    const bool rne = round_mode == B200_ROUND_NEAREST_TOWARD_EVEN && (g_fast_division.load(std::memory_order_relaxed) != 0);
+#define B200_S2D_LAUNCH(Q, FAST, PAIRS)                                                                                         \
+    s2d_pack_f32_kernel<Q, FAST, PAIRS><<<grid, 256, 0, st>>>(in_nchw, scale, static_cast<const Q*>(zero_point), round_mode,     \
+                                                              static_cast<uint4*>(cells), int(N), int(C), int(H), int(W), int(Hc), \
+                                                              int(Wc), int(eh), int(ew))
+    if (q_type == B200_U8)
+    {
+        if (rne && pairs) B200_S2D_LAUNCH(uint8_t, true, true);
+        else if (rne) B200_S2D_LAUNCH(uint8_t, true, false);
+        else if (pairs) B200_S2D_LAUNCH(uint8_t, false, true);
+        else B200_S2D_LAUNCH(uint8_t, false, false);
+    }
+    else
+    {
+        if (rne && pairs) B200_S2D_LAUNCH(int8_t, true, true);
+        else if (rne) B200_S2D_LAUNCH(int8_t, true, false);
+        else if (pairs) B200_S2D_LAUNCH(int8_t, false, true);
+        else B200_S2D_LAUNCH(int8_t, false, false);
+    }
+#undef B200_S2D_LAUNCH
+    return after_launch("b200_stem_pack_input_f32");
 }

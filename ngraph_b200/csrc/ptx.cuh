@@ -197,5 +197,18 @@ namespace b200
             d |= layout << 61;
             return d;
         }
+
+        // Shared-memory matrix descriptor, K-major, no swizzle, for an operand whose rows are overlapping windows of a
+        // linear byte run: row r starts at 16*r bytes.  Canonical no-swizzle layout: 8-row groups of 16-byte pieces;
+        // leading byte offset (between K pieces) = 16, stride byte offset (between 8-row groups) = 128.
+        __device__ __forceinline__ uint64_t smem_desc_overlapping_rows(uint32_t smem_addr)
+        {
+            uint64_t d = 0;
+            d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+            d |= uint64_t(16 >> 4) << 16;
+            d |= uint64_t(128 >> 4) << 32;
+            d |= uint64_t(1) << 46;
+            return d;
+        }
     }
 }

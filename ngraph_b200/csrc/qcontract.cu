@@ -95,6 +95,8 @@ namespace b200
         int relu, half_away, out_zp, out_type;
         int one;             // the constant 1, opaque to the compiler (see add_fma_pipe)
         int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
+        const uint8_t* a_cells; // stem: cell grid read as overlapping windows straight from linear memory (null otherwise)
+        int cells_w, cells_h;   // its row length and row count per image, in cells
         const int8_t* b_packed; // weights in the block image made by b200_pack_weights_host (null: plain [N,K] matrix through maps.b)
         int b_blocks_n;      // 64-row blocks per k-block in that image: ceil(N / 64)
         int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
@@ -120,6 +122,8 @@ namespace b200
     constexpr int COLS = 64;         // output columns (= bytes of a one-byte row) per epilogue warp and tile
     constexpr int CHUNKS = COLS / 32;
     constexpr int MAX_ACC = 8;       // accumulator buffers in TMEM: 512 columns / BN
+    constexpr uint32_t LINEAR_A_BYTES = (128 + 3) * 16; // stem: 128 windows of 4 cells = a run of 131 cells
+    constexpr int64_t STEM_CELLS_SLACK = 2112;          // bytes a run may reach past the last cell of the grid
     constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
 
     // Sleep between two polls of an mbarrier, per waiting role: a polling warp takes issue slots from the epilogue
@@ -483,13 +487,15 @@ namespace b200
         if (warp >= 1 && warp <= NUM_PRODUCERS)
         {
             // ------------------------------------------------------------ TMA producers
+            // One elected lane of each producer warp issues the loads of the k-blocks whose running index (over all tiles of this
+            // CTA) is pw mod NUM_PRODUCERS.  The other lanes only help with the tile coordinates: every 32 tiles each
+            // lane decodes one tile (the integer divisions would otherwise be a serial chain of several hundred cycles
+            // per tile in the issuing thread, more than a small tile's loads take) and the loop broadcasts them.
+            const int pw = warp - 1;
             if (ptx::elect_one())
             {
-                const int pw = warp - 1; // this producer issues the k-blocks whose running index is pw mod NUM_PRODUCERS
                 ptx::prefetch_tmap(&maps.b);
                 ptx::prefetch_tmap(&maps.a[0]);
-                int s = 0, turn = 0;
-                uint32_t ph = 0;
                 if (p.smem.b_resident && pw == 0)
                 {
                     // the single column tile's weights, all k-blocks, once
@@ -509,56 +515,112 @@ namespace b200
                             ptx::tma_load_2d(bres_base + kb * C::B_BYTES, &maps.b, bres_bar, kb * BK, 0);
                     }
                 }
-                for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
+            }
+            const int nkb = p.ntaps * p.cblocks;
+            int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
+            int idx = 32;
+            // this producer's next k-block, as (offset inside the current tile, pipeline stage, stage parity); it advances
+            // by NUM_PRODUCERS k-blocks at a time and carries over from tile to tile
+            int j = pw, s = pw;
+            uint32_t ph = 0;
+            while (s >= STAGES)
+            {
+                s -= STAGES;
+                ph ^= 1;
+            }
+            for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
+            {
+                if (idx == 32)
                 {
-                    int tm, tn, q0, p0, n0;
-                    decode_tile(p, tile, tm, tn, q0, p0, n0);
-                    int kcol = 0; // byte column of the k-block in the B matrix
-                    for (int tap = 0; tap < p.ntaps && !fail; ++tap)
+                    const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * gridDim.x;
+                    if (t < num_tiles)
                     {
-                        const Tap tp = p.taps[tap];
-                        const CUtensorMap* amap = &maps.a[tp.map];
-                        for (int cb = 0; cb < p.cblocks; ++cb, kcol += BK)
+                        int tm_, tn_, q0_, p0_, n0_;
+                        decode_tile(p, static_cast<int>(t), tm_, tn_, q0_, p0_, n0_);
+                        info_a = p.conv ? q0_ : tm_;
+                        info_b = p0_;
+                        info_c = n0_;
+                        info_d = tn_;
+                    }
+                    idx = 0;
+                }
+                const int ia = __shfl_sync(0xffffffffu, info_a, idx);
+                const int p0 = __shfl_sync(0xffffffffu, info_b, idx);
+                const int n0 = __shfl_sync(0xffffffffu, info_c, idx);
+                const int tn = __shfl_sync(0xffffffffu, info_d, idx);
+                ++idx;
+                // exactly one lane issues (elect.sync lets the compiler keep the TMA operands in uniform registers)
+                bool issued_here = false;
+                if (ptx::elect_one())
+                {
+                    issued_here = true;
+                    const int tm = ia, q0 = ia;
+                    // packed weights: this column tile's 64-row blocks of a k-block are one contiguous piece
+                    const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
+                    const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
+                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES : uint32_t(C::A_BYTES)) + b_bytes;
+                    int tap = 0, cb = j; // k-block j of the tile = (tap, channel block)
+                    while (cb >= p.cblocks)
+                    {
+                        cb -= p.cblocks;
+                        ++tap;
+                    }
+                    for (; j < nkb; j += NUM_PRODUCERS)
+                    {
+                        PROF_T0();
+                        if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp, BACKOFF_EMPTY_NS))
                         {
-                            if (turn == pw)
-                            {
-                                PROF_T0();
-                                if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abortp, BACKOFF_EMPTY_NS))
-                                {
-                                    fail = 1001;
-                                    break;
-                                }
-                                if (pw == 0)
-                                    PROF_ADD(0);
-                                const uint32_t a_dst = smem_base + s * stage_bytes;
-                                const uint32_t b_dst = a_dst + C::A_BYTES;
-                                // packed weights: this column tile's 64-row blocks of the k-block, one contiguous piece
-                                const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
-                                const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
-                                ptx::mbar_expect_tx(full_bar(s), uint32_t(C::A_BYTES) + b_bytes);
-                                if (p.conv)
-                                    ptx::tma_load_4d(a_dst, amap, full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
-                                else
-                                    ptx::tma_load_2d(a_dst, amap, full_bar(s), kcol, tm * BM);
-                                if (!p.smem.b_resident)
-                                {
-                                    if (p.b_packed)
-                                        ptx::bulk_load(b_dst, p.b_packed + (size_t(kcol / BK) * p.b_blocks_n + size_t(tn) * (BN / 64)) * (64 * BK),
-                                                       b_bytes, full_bar(s));
-                                    else
-                                        ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
-                                }
-                            }
-                            if (++turn == NUM_PRODUCERS)
-                                turn = 0;
-                            if (++s == STAGES)
-                            {
-                                s = 0;
-                                ph ^= 1;
-                            }
+                            fail = 1001;
+                            break;
+                        }
+                        if (pw == 0)
+                            PROF_ADD(0);
+                        const Tap tp = p.taps[tap];
+                        const int kcol = j * BK; // byte column of the k-block in the B matrix
+                        const uint32_t a_dst = smem_base + s * stage_bytes;
+                        const uint32_t b_dst = a_dst + C::A_BYTES;
+                        ptx::mbar_expect_tx(full_bar(s), tx_bytes);
+                        if (p.a_cells)
+                        {
+                            // 128 output pixels of one output row need cells q0 .. q0+130 of cell row p0 + tap: one run
+                            const size_t cell = (size_t(n0) * p.cells_h + size_t(p0 + tp.dh)) * p.cells_w + size_t(q0);
+                            ptx::bulk_load(a_dst, p.a_cells + cell * 16, LINEAR_A_BYTES, full_bar(s));
+                        }
+                        else if (p.conv)
+                            ptx::tma_load_4d(a_dst, &maps.a[tp.map], full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
+                        else
+                            ptx::tma_load_2d(a_dst, &maps.a[0], full_bar(s), kcol, tm * BM);
+                        if (!p.smem.b_resident)
+                        {
+                            if (p.b_packed)
+                                ptx::bulk_load(b_dst, p.b_packed + (size_t(j) * p.b_blocks_n + size_t(tn) * (BN / 64)) * (64 * BK), b_bytes,
+                                               full_bar(s));
+                            else
+                                ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                        }
+                        // advance to this producer's next k-block
+                        cb += NUM_PRODUCERS;
+                        while (cb >= p.cblocks)
+                        {
+                            cb -= p.cblocks;
+                            ++tap;
+                        }
+                        s += NUM_PRODUCERS;
+                        if (s >= STAGES)
+                        {
+                            s -= STAGES;
+                            ph ^= 1;
                         }
                     }
+                    j -= nkb; // offset of the next k-block inside the next tile
                 }
+                // the issuing lane's pipeline position (and a wait that gave up) is handed to every lane, whichever lane
+                // the next election picks
+                const int src = __ffs(__ballot_sync(0xffffffffu, issued_here)) - 1;
+                j = __shfl_sync(0xffffffffu, j, src);
+                s = __shfl_sync(0xffffffffu, s, src);
+                ph = __shfl_sync(0xffffffffu, ph, src);
+                fail = __shfl_sync(0xffffffffu, fail, src);
             }
         }
         else if (warp == 0)
@@ -569,7 +631,9 @@ namespace b200
                 int s = 0;
                 uint32_t ph = 0, tile_it = 0;
                 const int num_kblocks = p.ntaps * p.cblocks;
-                const uint64_t a_desc0 = ptx::smem_desc_kmajor(smem_base, BK);
+                // stem cells: row m of the A tile is the 64 bytes starting at cell m of a linear run, so rows overlap:
+                // 16-byte K pieces 16 bytes apart, rows 16 bytes apart, 8-row groups 128 bytes apart, no swizzle
+                const uint64_t a_desc0 = p.a_cells ? ptx::smem_desc_overlapping_rows(smem_base) : ptx::smem_desc_kmajor(smem_base, BK);
                 const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + C::A_BYTES, BK);
                 // descriptor address fields count 16-byte units
                 const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
@@ -602,6 +666,7 @@ namespace b200
                             PROF_ADD(1);
                         }
                         ptx::tc_fence_after_sync();
+                        PROF_MARK(t_issue0);
                         const uint64_t a_desc = a_desc0 + uint64_t(s) * (stage_bytes >> 4);
                         const uint64_t b_desc = b_desc0 + uint64_t(p.smem.b_resident ? kb : s) * b_step;
 #pragma unroll
@@ -612,6 +677,10 @@ namespace b200
                                         (kb | k) != 0 ? 1u : 0u);
                         }
                         ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
+#ifdef B200_PROFILE_WAITS
+                        if (blockIdx.x == 0)
+                            atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[7]), (unsigned long long)(clock64() - t_issue0));
+#endif
                         if (++s == STAGES)
                         {
                             s = 0;
@@ -1542,6 +1611,15 @@ extern "C" int b200_qconv_packed(const void* data, int data_type, const int8_t* 
 // Stride-2, <= 4 channel convolution on the cell grid made by b200_stem_pack_input (see layout.cu): Rc taps
 // (cell rows) of one 64-byte K-block each; the A tensor map's pixel dimension advances one cell (16 bytes)
 // per output column, so neighbouring windows overlap.
+extern "C" int64_t b200_stem_cells_bytes(int64_t N, int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
+                                         int64_t pad_h_above, int64_t pad_w_above)
+{
+    int64_t P, Q, Hc, Wc, Rc;
+    if (N < 0 || b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc) != B200_OK)
+        return 0;
+    return N * Hc * Wc * 16 + b200::STEM_CELLS_SLACK;
+}
+
 extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* packed_filters, void* out, int64_t N,
                                int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
                                int64_t pad_h_above, int64_t pad_w_above, const b200_epilogue* epilogue, void* stream)
@@ -1582,7 +1660,22 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     p.NB = int(N);
     p.P = int(P);
     p.Q = int(Q);
-    pick_patch(N, P, Q, p.TW, p.TH, p.TN);
+    // Wide outputs: a tile is 128 consecutive pixels of one output row and its A operand is a linear run of cells
+    // read as overlapping windows (one bulk copy per tap instead of 128 box rows).  Narrow outputs would waste most
+    // of such a tile and take tensor-map windows over a 2-D/3-D patch instead.
+    static const bool windows_only = getenv("B200_STEM_WINDOWS") != nullptr;
+    const bool linear = Q >= 64 && !windows_only;
+    if (linear)
+    {
+        p.TW = 128;
+        p.TH = 1;
+        p.TN = 1;
+        p.a_cells = static_cast<const uint8_t*>(cells);
+        p.cells_w = int(Wc);
+        p.cells_h = int(Hc);
+    }
+    else
+        pick_patch(N, P, Q, p.TW, p.TH, p.TN);
     p.sub_w = p.TW < 32 ? p.TW : 32;
     p.sub_h = (p.TH < 32 / p.sub_w) ? p.TH : 32 / p.sub_w;
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
@@ -1644,7 +1737,8 @@ extern "C" int b200_qconv_stem_static(const void* in_nchw, int data_type, const 
     if (N < 0)
         return B200_ERR_INVALID_ARGUMENT;
     // sizes the fixed array cannot hold are refused before anything is launched
-    if (Hc * Wc > int64_t(STEM_SCRATCH_BYTES / 16) || N > int64_t(STEM_SCRATCH_BYTES / 16) / (Hc * Wc))
+    const int64_t room = int64_t(STEM_SCRATCH_BYTES - STEM_CELLS_SLACK) / 16;
+    if (Hc * Wc > room || N > room / (Hc * Wc))
         return B200_ERR_TOO_LARGE;
     // one symbol lookup per device, at the first call on that device (it may load the module: do it before any
     // stream capture begins)

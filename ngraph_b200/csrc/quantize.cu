@@ -116,25 +116,6 @@ namespace b200
     // the last bit), take the other branches below, so every output byte equals the plain
     // x / s -> floor(q+0.5)/ceil(q-0.5)/parity -> +zero_point -> clamp sequence of the reference.
     // (For |q| < 2^23 that rounding sequence is round-half-even, i.e. one cvt.rni; beyond it clamps.)
-    __device__ __forceinline__ bool scale_allows_fast_division(float s)
-    {
-        const uint32_t b = __float_as_uint(s);
-        const uint32_t ex = (b >> 23) & 0xFF, man = b & 0x7FFFFF;
-        return ex >= 127 - 40 && ex <= 127 + 40 && man != 0x7FFFFF;
-    }
-
-    template <typename Q>
-    __device__ __forceinline__ int quantize_rne_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
-    {
-        const float q0 = __fmul_rn(x, y);
-        const float e = __fmaf_rn(-q0, s, x);
-        const float q1 = __fmaf_rn(e, y, q0);
-        const float q = (fabsf(q0) < 16777216.0f) ? q1 : q0; // huge, inf and NaN quotients skip the correction
-        const int i = __float2int_rn(q);                     // saturating
-        const int r = min(max(i, lo_minus_zp), hi_minus_zp) + zp;
-        return (x != x) ? 0 : r;                             // NaN -> 0, as clamp_cast
-    }
-
     template <typename Q>
     __global__ void __launch_bounds__(QT) quantize_rows_rne8_kernel(const float* __restrict__ x,
                                                                    const float* __restrict__ scale,

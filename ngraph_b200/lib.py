@@ -63,8 +63,10 @@ def _load():
         "b200_qgemm_packed": (ci, [vp, ci, vp, vp, i64, i64, i64, ctypes.POINTER(Epilogue), vp]),
         "b200_qconv_packed": (ci, [vp, ci, vp, vp, ctypes.POINTER(ConvParams), ctypes.POINTER(Epilogue), vp]),
         "b200_stem_geometry": (ci, [i64] * 8 + [p64] * 5),
+        "b200_stem_cells_bytes": (i64, [i64] * 9),
         "b200_stem_pack_filter_host": (ci, [vp, vp] + [i64] * 6),
         "b200_stem_pack_input": (ci, [vp, vp] + [i64] * 10 + [vp]),
+        "b200_stem_pack_input_f32": (ci, [vp, vp, vp, ci, ci, vp] + [i64] * 10 + [vp]),
         "b200_qconv_stem": (ci, [vp, ci, vp, vp] + [i64] * 10 + [ctypes.POINTER(Epilogue), vp]),
         "b200_qconv_stem_static_capacity": (i64, []),
         "b200_qconv_stem_static": (ci, [vp, ci, vp, vp] + [i64] * 11 + [ctypes.POINTER(Epilogue), vp]),

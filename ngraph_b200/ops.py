@@ -164,7 +164,8 @@ def qconv_stem(data_nchw, filters_kcrs, scale, out_dtype, pad_below, pad_above=N
     check(LIB.b200_stem_pack_filter_host(f.ctypes.data, packed.ctypes.data, k, c, r, s, pad_below[0], pad_below[1]),
           "b200_stem_pack_filter_host")
     packed_d = torch.from_numpy(packed).to(data.device)
-    cells = torch.empty((n, hc, wc, 16), dtype=torch.uint8, device=data.device)
+    cells = torch.empty(LIB.b200_stem_cells_bytes(n, h, w, r, s, pad_below[0], pad_below[1], pad_above[0], pad_above[1]),
+                        dtype=torch.uint8, device=data.device)
     check(LIB.b200_stem_pack_input(_ptr(data), _ptr(cells), n, c, h, w, r, s, pad_below[0], pad_below[1], pad_above[0],
                                    pad_above[1], _stream()), "b200_stem_pack_input")
     e, keep = _epilogue(k, scale, out_dtype, bias, relu)

@@ -266,6 +266,8 @@ STEM_CASES = [
     (2, 4, 20, 18, 32, 5, 7, (2, 3), (1, 2), np.uint8),    # asymmetric padding, four channels
     (2, 2, 16, 16, 24, 8, 8, (0, 0), (0, 0), np.int8),     # even filter without padding
     (1, 3, 9, 9, 8, 7, 7, (2, 2), (3, 3), np.uint8),       # even padding below
+    (2, 3, 20, 140, 64, 7, 7, (3, 3), (3, 3), np.int8),    # 70 output columns: one partly filled 128-pixel row tile
+    (1, 4, 12, 300, 32, 5, 5, (2, 2), (2, 2), np.uint8),   # 150 output columns: two row tiles, the second ragged
 ]
 
 
@@ -289,3 +291,26 @@ def test_stem_rejects_wide_filters(ops):
     from ngraph_b200 import lib
     with pytest.raises(lib.B200Error):
         ops.stem_geometry(32, 32, 9, 9, (0, 0), (0, 0))
+
+
+@pytest.mark.parametrize("q_np", [np.uint8, np.int8])
+def test_stem_pack_with_fused_quantize(ops, q_np):
+    """b200_stem_pack_input_f32 == b200_quantize followed by b200_stem_pack_input, every round mode."""
+    from ngraph_b200.lib import LIB, check
+    rng = np.random.default_rng(17)
+    n, c, h, w = 2, 3, 37, 41
+    x = (rng.standard_normal((n, c, h, w)) * 60).astype(np.float32)
+    x.flat[:64] = (np.arange(64) - 32) * 0.5 * 0.7  # exact .5 ties after the division by 0.7
+    xd = dev(x)
+    scale = dev(np.array([0.7], np.float32))
+    zp = dev(np.array([3], q_np))
+    p, q, hc, wc, rc = ops.stem_geometry(h, w, 7, 7, (3, 3), (3, 3))
+    st = torch.cuda.current_stream().cuda_stream
+    for mode in range(9):
+        qx = ops.quantize(xd, scale, zp, round_mode=mode)
+        want = torch.empty((n, hc, wc, 16), dtype=torch.uint8, device="cuda")
+        check(LIB.b200_stem_pack_input(qx.data_ptr(), want.data_ptr(), n, c, h, w, 7, 7, 3, 3, 3, 3, st), "pack")
+        got = torch.full((n, hc, wc, 16), 99, dtype=torch.uint8, device="cuda")
+        check(LIB.b200_stem_pack_input_f32(xd.data_ptr(), scale.data_ptr(), zp.data_ptr(), 0 if q_np == np.uint8 else 1, mode,
+                                           got.data_ptr(), n, c, h, w, 7, 7, 3, 3, 3, 3, st), "pack f32")
+        assert torch.equal(got, want), "round mode %d" % mode
