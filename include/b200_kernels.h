@@ -48,7 +48,8 @@ typedef enum b200_dtype
     B200_U8 = 0,
     B200_I8 = 1,
     B200_I32 = 2,
-    B200_F32 = 3
+    B200_F32 = 3,
+    B200_I64 = 4 /* index tensors only (b200_gather_rows_b32) */
 } b200_dtype;
 
 /* Same ordinal order as op::v0::Quantize::RoundMode (src/ngraph/op/quantize.hpp:38-81). */
@@ -357,6 +358,58 @@ B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const in
                                     int64_t C, int64_t H, int64_t W, int64_t K, int64_t R, int64_t S, int64_t pad_h,
                                     int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
                                     const b200_epilogue* epilogue, void* stream);
+
+/*
+ * f32 glue operators: the float islands of a quantized graph (softmax, LayerNorm and GELU after
+ * pass::FusedOpDecomposition, residual adds, dynamic activation scales), each with the arithmetic of the reference
+ * kernel the INTERPRETER backend runs, so that results are identical and not merely close:
+ *   b200_f32_binary      Add, Subtract, Multiply, Divide, Maximum, Minimum on equal shapes
+ *                        (runtime/reference/add.hpp, subtract.hpp, multiply.hpp, divide.hpp, maximum.hpp, minimum.hpp)
+ *   b200_f32_unary       Abs, Negative, Sqrt, Exp, Erf, Relu (abs.hpp, negate.hpp, sqrt.hpp, exp.hpp, erf.hpp, relu.hpp);
+ *                        Exp and Erf are the double routine rounded to float
+ *   b200_broadcast_b32   op::v0::Broadcast for 4-byte elements (broadcast.hpp): out_shape and the axes that are new
+ *   b200_permute_b32     the axis permutation of a transposing op::v0::Reshape for 4-byte elements (reshape.hpp):
+ *                        output axis i is input axis order[i]
+ *   b200_reduce_f32      op::v0::Sum (Kahan-compensated, sum.hpp:56-90) and op::v0::Max (max.hpp:32-58) over an axis set,
+ *                        inputs taken in row-major order like the reference
+ *   b200_bmm_f32         op::v0::BatchMatMul / 2-D op::v0::Dot on f32 (batch_mat_mul.hpp, dot.hpp:108-160): a[b,M,K] x
+ *                        b[b,K,N], the sum over k in double, in order, rounded to float once
+ *   b200_gather_rows_b32 op::v0::Gather with axis 0 on a 2-D table of 4-byte elements and an i32 / i64 index vector
+ *                        (gather.hpp); an index outside the table yields zeros (the reference does not check)
+ */
+typedef enum b200_f32_op
+{
+    B200_F32_ADD = 0,
+    B200_F32_SUB = 1,
+    B200_F32_MUL = 2,
+    B200_F32_DIV = 3,
+    B200_F32_MAX = 4,
+    B200_F32_MIN = 5,
+    B200_F32_ABS = 6,
+    B200_F32_NEG = 7,
+    B200_F32_SQRT = 8,
+    B200_F32_EXP = 9,
+    B200_F32_ERF = 10,
+    B200_F32_RELU = 11
+} b200_f32_op;
+
+typedef enum b200_reduce_op
+{
+    B200_REDUCE_SUM = 0,
+    B200_REDUCE_MAX = 1
+} b200_reduce_op;
+
+B200_API int b200_f32_binary(int op, const float* a, const float* b, float* out, int64_t n, void* stream);
+B200_API int b200_f32_unary(int op, const float* x, float* out, int64_t n, void* stream);
+B200_API int b200_broadcast_b32(const void* in, void* out, const int64_t* out_shape, int rank, const int64_t* broadcast_axes,
+                                int n_axes, void* stream);
+B200_API int b200_permute_b32(const void* in, void* out, const int64_t* in_shape, int rank, const int64_t* order, void* stream);
+B200_API int b200_reduce_f32(int op, const float* in, float* out, const int64_t* shape, int rank, const int64_t* axes,
+                             int n_axes, void* stream);
+B200_API int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N,
+                          void* stream);
+B200_API int b200_gather_rows_b32(const void* table, int64_t n_rows, int64_t row_elements, const void* indices, int index_type,
+                                  int64_t n_indices, void* out, void* stream);
 
 /*
  * out[0] = input_scale[0] * filter_scale[0] / output_scale[0] in fp32, left to right: the requantisation

@@ -21,7 +21,26 @@
 #include "ngraph/descriptor/layout/dense_tensor_layout.hpp"
 #include "ngraph/except.hpp"
 #include "ngraph/graph_util.hpp"
+#include "ngraph/op/abs.hpp"
+#include "ngraph/op/add.hpp"
 #include "ngraph/op/avg_pool.hpp"
+#include "ngraph/op/broadcast.hpp"
+#include "ngraph/op/divide.hpp"
+#include "ngraph/op/dot.hpp"
+#include "ngraph/op/erf.hpp"
+#include "ngraph/op/exp.hpp"
+#include "ngraph/op/experimental/batch_mat_mul.hpp"
+#include "ngraph/op/gather.hpp"
+#include "ngraph/op/max.hpp"
+#include "ngraph/op/maximum.hpp"
+#include "ngraph/op/minimum.hpp"
+#include "ngraph/op/multiply.hpp"
+#include "ngraph/op/negative.hpp"
+#include "ngraph/op/relu.hpp"
+#include "ngraph/op/softmax.hpp"
+#include "ngraph/op/sqrt.hpp"
+#include "ngraph/op/subtract.hpp"
+#include "ngraph/op/sum.hpp"
 #include "ngraph/op/constant.hpp"
 #include "ngraph/op/convert.hpp"
 #include "ngraph/op/dequantize.hpp"
@@ -83,6 +102,7 @@ namespace
         if (et == element::i8) return B200_I8;
         if (et == element::i32) return B200_I32;
         if (et == element::f32) return B200_F32;
+        if (et == element::i64) return B200_I64;
         return -1;
     }
 
@@ -396,7 +416,15 @@ bool B200Backend::is_supported(const Node& node) const
            is_type<op::v0::QuantizedConvolutionBiasAdd>(&node) ||
            is_type<op::v0::QuantizedConvolutionBiasSignedAdd>(&node) ||
            is_type<op::v0::QuantizedConvolutionRelu>(&node) || is_type<op::v0::MaxPool>(&node) ||
-           is_type<op::v0::AvgPool>(&node) || is_type<op::v0::Reshape>(&node) || is_type<op::v0::Convert>(&node);
+           is_type<op::v0::AvgPool>(&node) || is_type<op::v0::Reshape>(&node) || is_type<op::v0::Convert>(&node) ||
+           // f32 glue
+           is_type<op::v1::Add>(&node) || is_type<op::v1::Subtract>(&node) || is_type<op::v1::Multiply>(&node) ||
+           is_type<op::v1::Divide>(&node) || is_type<op::v1::Maximum>(&node) || is_type<op::v1::Minimum>(&node) ||
+           is_type<op::v0::Abs>(&node) || is_type<op::v0::Negative>(&node) || is_type<op::v0::Sqrt>(&node) ||
+           is_type<op::v0::Exp>(&node) || is_type<op::v0::Erf>(&node) || is_type<op::v0::Relu>(&node) ||
+           is_type<op::v0::Broadcast>(&node) || is_type<op::v0::Sum>(&node) || is_type<op::v0::Max>(&node) ||
+           is_type<op::v0::Softmax>(&node) || is_type<op::v0::BatchMatMul>(&node) || is_type<op::v0::Dot>(&node) ||
+           is_type<op::v0::Gather>(&node);
 }
 
 extern "C" B200_BACKEND_API void ngraph_register_b200_backend()
@@ -678,7 +706,19 @@ void B200Executable::compile_node(const std::shared_ptr<Node>& node)
             o.canonical = dst;
             return;
         }
-        unsupported(*node, "transposing Reshape other than a 2-D one-byte matrix");
+        if (in.et.size() == 4 && in.shape.size() <= 8)
+        {
+            int src = canonical_slot(node->input_value(0));
+            int dst = new_slot(Slot::ARENA, shape_size(in.shape) * 4);
+            std::vector<int64_t> shape(in.shape.begin(), in.shape.end());
+            std::vector<int64_t> order(rs->get_input_order().begin(), rs->get_input_order().end());
+            emit(node, "permute", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_permute_b32(p[src], p[dst], shape.data(), int(shape.size()), order.data(), st);
+            });
+            o.canonical = dst;
+            return;
+        }
+        unsupported(*node, "transposing Reshape other than a 2-D one-byte matrix or a 4-byte tensor");
     }
     if (auto cv = as_type_ptr<op::v0::Convert>(node))
     {
@@ -697,7 +737,191 @@ void B200Executable::compile_node(const std::shared_ptr<Node>& node)
         }
         unsupported(*node, "Convert other than between i8 and u8");
     }
+    if (compile_f32_glue(node))
+        return;
     unsupported(*node, "not part of the quantized-inference op set");
+}
+
+// The float islands of a quantized graph (dynamic activation scales, softmax, LayerNorm / GELU after
+// FusedOpDecomposition, residual adds, attention matrix products, embedding lookups): one kernel per op, each with
+// the arithmetic of the reference kernel (include/b200_kernels.h).  Returns false if `node` is not one of them.
+bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
+{
+    const element::Type& ot = node->get_output_element_type(0);
+    const Shape os = node->get_output_shape(0);
+    const int64_t n_out = int64_t(shape_size(os));
+    auto all_f32 = [&]() {
+        for (size_t i = 0; i < node->get_input_size(); ++i)
+            if (node->get_input_element_type(i) != element::f32)
+                return false;
+        return ot == element::f32;
+    };
+
+    int bop = -1;
+    if (is_type<op::v1::Add>(node)) bop = B200_F32_ADD;
+    else if (is_type<op::v1::Subtract>(node)) bop = B200_F32_SUB;
+    else if (is_type<op::v1::Multiply>(node)) bop = B200_F32_MUL;
+    else if (is_type<op::v1::Divide>(node)) bop = B200_F32_DIV;
+    else if (is_type<op::v1::Maximum>(node)) bop = B200_F32_MAX;
+    else if (is_type<op::v1::Minimum>(node)) bop = B200_F32_MIN;
+    if (bop >= 0)
+    {
+        if (!all_f32())
+            unsupported(*node, "elementwise arithmetic on element types other than f32");
+        if (node->get_input_shape(0) != os || node->get_input_shape(1) != os)
+            unsupported(*node, "implicit broadcasting (use an explicit Broadcast)");
+        int a = canonical_slot(node->input_value(0)), b = canonical_slot(node->input_value(1));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit(node, "f32_binary", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_f32_binary(bop, static_cast<const float*>(p[a]), static_cast<const float*>(p[b]), static_cast<float*>(p[y]),
+                                   n_out, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    int uop = -1;
+    if (is_type<op::v0::Abs>(node)) uop = B200_F32_ABS;
+    else if (is_type<op::v0::Negative>(node)) uop = B200_F32_NEG;
+    else if (is_type<op::v0::Sqrt>(node)) uop = B200_F32_SQRT;
+    else if (is_type<op::v0::Exp>(node)) uop = B200_F32_EXP;
+    else if (is_type<op::v0::Erf>(node)) uop = B200_F32_ERF;
+    else if (is_type<op::v0::Relu>(node)) uop = B200_F32_RELU;
+    if (uop >= 0)
+    {
+        if (!all_f32())
+            unsupported(*node, "elementwise arithmetic on element types other than f32");
+        int x = canonical_slot(node->input_value(0));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit(node, "f32_unary", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_f32_unary(uop, static_cast<const float*>(p[x]), static_cast<float*>(p[y]), n_out, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    if (auto bc = as_type_ptr<op::v0::Broadcast>(node))
+    {
+        if (ot.size() != 4 || os.size() > 8)
+            unsupported(*node, "Broadcast of element types that are not 4 bytes wide");
+        int x = canonical_slot(node->input_value(0));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        std::vector<int64_t> shape(os.begin(), os.end());
+        std::vector<int64_t> axes(bc->get_broadcast_axes().begin(), bc->get_broadcast_axes().end());
+        emit(node, "broadcast", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_broadcast_b32(p[x], p[y], shape.data(), int(shape.size()), axes.data(), int(axes.size()), st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    // one reduction: emitted into a given slot so that Softmax can reuse it
+    auto emit_reduce = [&](int rop, int x, const Shape& in_shape, const AxisSet& axes_set, int y) {
+        std::vector<int64_t> shape(in_shape.begin(), in_shape.end());
+        std::vector<int64_t> axes(axes_set.begin(), axes_set.end());
+        emit(node, rop == B200_REDUCE_SUM ? "reduce_sum" : "reduce_max", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_reduce_f32(rop, static_cast<const float*>(p[x]), static_cast<float*>(p[y]), shape.data(), int(shape.size()),
+                                   axes.data(), int(axes.size()), st);
+        });
+    };
+    const bool is_sum = is_type<op::v0::Sum>(node), is_max = is_type<op::v0::Max>(node);
+    if (is_sum || is_max)
+    {
+        if (node->get_input_element_type(0) != element::f32 || node->get_input_shape(0).size() > 8)
+            unsupported(*node, "reductions on element types other than f32");
+        AxisSet axes = is_sum ? as_type_ptr<op::v0::Sum>(node)->get_reduction_axes() : as_type_ptr<op::v0::Max>(node)->get_reduction_axes();
+        int x = canonical_slot(node->input_value(0));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit_reduce(is_sum ? B200_REDUCE_SUM : B200_REDUCE_MAX, x, node->get_input_shape(0), axes, y);
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    if (auto sm = as_type_ptr<op::v0::Softmax>(node))
+    {
+        // runtime/reference/softmax.hpp: max over the axes, exp(x - max), Kahan sum, divide: the same five steps
+        if (!all_f32() && node->get_input_element_type(0) != element::f32)
+            unsupported(*node, "Softmax on element types other than f32");
+        const AxisSet axes = sm->get_axes();
+        Shape red;
+        for (size_t i = 0; i < os.size(); ++i)
+            if (!axes.count(i))
+                red.push_back(os[i]);
+        const int64_t n_red = int64_t(shape_size(red));
+        int x = canonical_slot(node->input_value(0));
+        int small = new_slot(Slot::ARENA, size_t(n_red) * 4), wide = new_slot(Slot::ARENA, size_t(n_out) * 4),
+            e = new_slot(Slot::ARENA, size_t(n_out) * 4), y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        std::vector<int64_t> shape(os.begin(), os.end());
+        std::vector<int64_t> ax(axes.begin(), axes.end());
+        auto emit_wide = [&]() {
+            emit(node, "softmax_broadcast", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_broadcast_b32(p[small], p[wide], shape.data(), int(shape.size()), ax.data(), int(ax.size()), st);
+            });
+        };
+        emit_reduce(B200_REDUCE_MAX, x, os, axes, small);
+        emit_wide();
+        emit(node, "softmax_sub", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_f32_binary(B200_F32_SUB, static_cast<const float*>(p[x]), static_cast<const float*>(p[wide]),
+                                   static_cast<float*>(p[e]), n_out, st);
+        });
+        emit(node, "softmax_exp", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_f32_unary(B200_F32_EXP, static_cast<const float*>(p[e]), static_cast<float*>(p[e]), n_out, st);
+        });
+        emit_reduce(B200_REDUCE_SUM, e, os, axes, small);
+        emit_wide();
+        emit(node, "softmax_div", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_f32_binary(B200_F32_DIV, static_cast<const float*>(p[e]), static_cast<const float*>(p[wide]),
+                                   static_cast<float*>(p[y]), n_out, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    const bool is_bmm = is_type<op::v0::BatchMatMul>(node);
+    auto dot = as_type_ptr<op::v0::Dot>(node);
+    if (is_bmm || dot)
+    {
+        const Shape as = node->get_input_shape(0), bs = node->get_input_shape(1);
+        if (!all_f32())
+            unsupported(*node, "matrix products on element types other than f32 (int8 goes through QuantizedDot)");
+        int64_t batch = 1, M, K, N;
+        if (is_bmm)
+        {
+            batch = int64_t(as[0]); M = int64_t(as[1]); K = int64_t(as[2]); N = int64_t(bs[2]);
+        }
+        else
+        {
+            if (as.size() != 2 || bs.size() != 2 || dot->get_reduction_axes_count() != 1)
+                unsupported(*node, "Dot other than matrix x matrix");
+            M = int64_t(as[0]); K = int64_t(as[1]); N = int64_t(bs[1]);
+        }
+        int a = canonical_slot(node->input_value(0)), b = canonical_slot(node->input_value(1));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit(node, "bmm_f32", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_bmm_f32(static_cast<const float*>(p[a]), static_cast<const float*>(p[b]), static_cast<float*>(p[y]), batch, M,
+                                K, N, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+
+    if (auto g = as_type_ptr<op::v0::Gather>(node))
+    {
+        const Shape ps = node->get_input_shape(0), is = node->get_input_shape(1);
+        const element::Type& it = node->get_input_element_type(1);
+        if (ot.size() != 4 || ps.size() != 2 || is.size() != 1 || g->get_axis() != 0 || (it != element::i32 && it != element::i64))
+            unsupported(*node, "Gather other than rows of a 2-D 4-byte table by an i32 / i64 index vector");
+        int t = canonical_slot(node->input_value(0)), idx = canonical_slot(node->input_value(1));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        const int64_t rows = int64_t(ps[0]), width = int64_t(ps[1]), count = int64_t(is[0]);
+        const int itype = dtype_of(it);
+        emit(node, "gather_rows", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_gather_rows_b32(p[t], rows, width, p[idx], itype, count, p[y], st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+    return false;
 }
 
 static std::vector<int64_t> to_i64(const Shape& s)

@@ -153,6 +153,7 @@ namespace ngraph
                 void compile_dot_bias(const std::shared_ptr<Node>& node);
                 void compile_core_dot(const std::shared_ptr<Node>& node);
                 void compile_max_pool(const std::shared_ptr<Node>& node);
+                bool compile_f32_glue(const std::shared_ptr<Node>& node);
                 bool try_compile_avgpool_head(const std::shared_ptr<Node>& quantize_node);
                 int packed_filters(const Output<Node>& filters, size_t c_pad, bool* is_image = nullptr);
                 int scalar_product_scale(const Output<Node>& a, const Output<Node>& b, const Output<Node>& c);

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 KERNEL_LIB = os.path.join(HERE, "libb200_kernels.so")
-KERNEL_SOURCES = ["abi.cu", "quantize.cu", "qcontract.cu", "layout.cu"]
+KERNEL_SOURCES = ["abi.cu", "quantize.cu", "qcontract.cu", "layout.cu", "glue_f32.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler",
               "-fPIC,-fvisibility=hidden", "-I" + os.path.join(ROOT, "include")]
 
@@ -91,13 +91,13 @@ CAPI_LIB = os.path.join(HERE, "libng_capi.so")
 def build_capi(force=False):
     """The C facade over nGraph's C++ API that the Python tests and the benchmark drive (ctypes)."""
     inc = ngraph_include_dir()
-    src = os.path.join(HERE, "harness", "ng_capi.cpp")
+    srcs = [os.path.join(HERE, "harness", "ng_capi.cpp"), os.path.join(HERE, "harness", "bert_int8.cpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return CAPI_LIB if os.path.exists(CAPI_LIB) else None
-    if not force and _newer(CAPI_LIB, [src]):
+    if not force and _newer(CAPI_LIB, srcs):
         return CAPI_LIB
     flags = [f for f in host_cxx_flags(inc) if f != "-std=c++14"] + ["-std=c++11"]
-    cmd = ["/usr/bin/g++"] + flags + ["-shared", src, "-o", CAPI_LIB, "-L" + NGRAPH_LIB_DIR, "-lngraph", "-ldl",
+    cmd = ["/usr/bin/g++"] + flags + ["-shared"] + srcs + ["-o", CAPI_LIB, "-L" + NGRAPH_LIB_DIR, "-lngraph", "-ldl",
                              "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
     subprocess.check_call(cmd)
     return CAPI_LIB

@@ -1,0 +1,429 @@
+// f32 glue operators of quantized graphs (the float islands between int8 contractions: softmax, LayerNorm,
+// GELU, residual adds, dynamic activation scales) with the arithmetic of nGraph's reference kernels:
+//
+//   elementwise +, -, *, /, max, min, abs, neg, sqrt, relu   IEEE single, one rounding each, nothing contracted
+//   exp, erf                                                   reference: std::exp / std::erf on float; here the double
+//                                                              routine rounded to float (differs from a given libm in
+//                                                              the last bit on a small share of inputs)
+//   Sum          runtime/reference/sum.hpp:56-90     Kahan-compensated, inputs taken in row-major order
+//   Max          runtime/reference/max.hpp:32-58     start at -inf, replace when x > max
+//   Broadcast    runtime/reference/broadcast.hpp     output coordinate with the broadcast axes dropped
+//   BatchMatMul  runtime/reference/batch_mat_mul.hpp -> dot.hpp:108-160: the sum over k runs in DOUBLE, in order,
+//                over exact products, and is rounded to float once
+//   Gather       runtime/reference/gather.hpp        rows of a matrix picked by an index vector
+//   Reshape      runtime/reference/reshape.hpp       axis permutation followed by a free re-interpretation
+//
+// All are HBM-bound (or, for the reductions and the matrix product, latency-bound on purpose: they keep the
+// reference's summation order so that results are identical, not merely close).
+#include <cuda_runtime.h>
+#include <math.h>
+#include "common.cuh"
+
+namespace b200
+{
+    constexpr int MAX_RANK = 8;
+    struct Dims
+    {
+        int rank;
+        int64_t out_dim[MAX_RANK];    // shape of the tensor the thread index runs over
+        int64_t in_stride[MAX_RANK];  // element stride in the other tensor for each of those axes (0: axis absent)
+    };
+
+    __device__ __forceinline__ int64_t mapped_offset(const Dims& d, int64_t idx)
+    {
+        int64_t off = 0;
+#pragma unroll 1
+        for (int a = d.rank - 1; a >= 0; --a)
+        {
+            const int64_t c = idx % d.out_dim[a];
+            idx /= d.out_dim[a];
+            off += c * d.in_stride[a];
+        }
+        return off;
+    }
+
+    template <int OP>
+    __device__ __forceinline__ float binary_op(float a, float b)
+    {
+        switch (OP)
+        {
+        case B200_F32_ADD: return __fadd_rn(a, b);
+        case B200_F32_SUB: return __fsub_rn(a, b);
+        case B200_F32_MUL: return __fmul_rn(a, b);
+        case B200_F32_DIV: return __fdiv_rn(a, b);
+        case B200_F32_MAX: return a > b ? a : b; // reference::maximum
+        default: return a < b ? a : b;           // reference::minimum
+        }
+    }
+
+    template <int OP>
+    __global__ void __launch_bounds__(256) binary_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                         float* __restrict__ out, int64_t n)
+    {
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+            out[i] = binary_op<OP>(a[i], b[i]);
+    }
+
+    template <int OP>
+    __device__ __forceinline__ float unary_op(float x)
+    {
+        switch (OP)
+        {
+        case B200_F32_ABS: return fabsf(x);
+        case B200_F32_NEG: return -x;
+        case B200_F32_SQRT: return __fsqrt_rn(x);
+        case B200_F32_EXP: return static_cast<float>(exp(static_cast<double>(x)));
+        case B200_F32_ERF: return static_cast<float>(erf(static_cast<double>(x)));
+        default: return x > 0.0f ? x : 0.0f; // reference::relu
+        }
+    }
+
+    template <int OP>
+    __global__ void __launch_bounds__(256) unary_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t n)
+    {
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+            out[i] = unary_op<OP>(x[i]);
+    }
+
+    // out[idx] = in[mapped(idx)] for 4-byte elements: Broadcast (stride 0 on the new axes) and axis permutations
+    __global__ void __launch_bounds__(256) remap_b32_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, Dims d,
+                                                            int64_t n)
+    {
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+            out[i] = in[mapped_offset(d, i)];
+    }
+
+    // One thread per output element; the reduced coordinates are walked in row-major order, as the reference does.
+    // keep: the kept axes (thread index -> input offset); red: the reduced axes.
+    template <bool IS_SUM>
+    __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ in, float* __restrict__ out, Dims keep, Dims red,
+                                                         int64_t n_out, int64_t n_red)
+    {
+        for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += int64_t(gridDim.x) * blockDim.x)
+        {
+            const float* base = in + mapped_offset(keep, o);
+            if (IS_SUM)
+            {
+                float z = 0.0f, c = 0.0f;
+                for (int64_t r = 0; r < n_red; ++r)
+                {
+                    const float x = base[mapped_offset(red, r)];
+                    if (isfinite(x) && isfinite(z))
+                    {
+                        const float y = __fsub_rn(x, c);
+                        const float t = __fadd_rn(z, y);
+                        c = __fsub_rn(__fsub_rn(t, z), y);
+                        z = t;
+                    }
+                    else
+                        z = __fadd_rn(z, x);
+                }
+                out[o] = z;
+            }
+            else
+            {
+                float m = -INFINITY;
+                for (int64_t r = 0; r < n_red; ++r)
+                {
+                    const float x = base[mapped_offset(red, r)];
+                    if (x > m)
+                        m = x;
+                }
+                out[o] = m;
+            }
+        }
+    }
+
+    // Max with few outputs and long reductions (a whole-tensor max for a dynamic activation scale): one block per
+    // output.  The result of a max does not depend on the order the inputs are taken in (NaNs never win the
+    // x > max test, in any order), so this equals the sequential reference loop.
+    __global__ void __launch_bounds__(256) reduce_max_block_kernel(const float* __restrict__ in, float* __restrict__ out, Dims keep,
+                                                                   Dims red, int64_t n_red)
+    {
+        __shared__ float partial[8];
+        const float* base = in + mapped_offset(keep, blockIdx.x);
+        float m = -INFINITY;
+        for (int64_t r = threadIdx.x; r < n_red; r += blockDim.x)
+        {
+            const float x = base[mapped_offset(red, r)];
+            if (x > m)
+                m = x;
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1)
+        {
+            const float o = __shfl_xor_sync(0xffffffffu, m, d);
+            if (o > m)
+                m = o;
+        }
+        if ((threadIdx.x & 31) == 0)
+            partial[threadIdx.x >> 5] = m;
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            for (int w = 1; w < 8; ++w)
+                if (partial[w] > m)
+                    m = partial[w];
+            out[blockIdx.x] = m;
+        }
+    }
+
+    // out[b, m, n] = float(sum_k double(a[b, m, k]) * double(b[b, k, n])), k ascending
+    __global__ void __launch_bounds__(256) bmm_f32_kernel(const float* __restrict__ a, const float* __restrict__ bm,
+                                                          float* __restrict__ out, int64_t B, int M, int K, int N)
+    {
+        const int64_t total = B * M * N;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int n = int(i % N);
+            const int64_t t = i / N;
+            const int m = int(t % M);
+            const int64_t b = t / M;
+            const float* ap = a + (b * M + m) * K;
+            const float* bp = bm + b * K * N + n;
+            double sum = 0.0;
+            for (int k = 0; k < K; ++k)
+                sum = __dadd_rn(sum, __dmul_rn(double(ap[k]), double(bp[int64_t(k) * N])));
+            out[i] = static_cast<float>(sum);
+        }
+    }
+
+    template <typename I>
+    __global__ void __launch_bounds__(256) gather_rows_kernel(const uint32_t* __restrict__ table, const I* __restrict__ idx,
+                                                              uint32_t* __restrict__ out, int64_t n_idx, int64_t row_words,
+                                                              int64_t n_rows)
+    {
+        const int64_t total = n_idx * row_words;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int64_t r = i / row_words, w = i - r * row_words;
+            const int64_t src = int64_t(idx[r]);
+            out[i] = (src >= 0 && src < n_rows) ? table[src * row_words + w] : 0u; // the reference does not check
+        }
+    }
+
+    static unsigned grid_for(int64_t n, int threads)
+    {
+        int64_t blocks = (n + threads - 1) / threads;
+        const int64_t cap = int64_t(148) * 16;
+        return unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+    }
+}
+
+extern "C" int b200_f32_binary(int op, const float* a, const float* b, float* out, int64_t n, void* stream)
+{
+    using namespace b200;
+    if (n < 0 || op < B200_F32_ADD || op > B200_F32_MIN)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (n == 0)
+        return B200_OK;
+    if (!a || !b || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(n, 256);
+    switch (op)
+    {
+    case B200_F32_ADD: binary_kernel<B200_F32_ADD><<<g, 256, 0, st>>>(a, b, out, n); break;
+    case B200_F32_SUB: binary_kernel<B200_F32_SUB><<<g, 256, 0, st>>>(a, b, out, n); break;
+    case B200_F32_MUL: binary_kernel<B200_F32_MUL><<<g, 256, 0, st>>>(a, b, out, n); break;
+    case B200_F32_DIV: binary_kernel<B200_F32_DIV><<<g, 256, 0, st>>>(a, b, out, n); break;
+    case B200_F32_MAX: binary_kernel<B200_F32_MAX><<<g, 256, 0, st>>>(a, b, out, n); break;
+    default: binary_kernel<B200_F32_MIN><<<g, 256, 0, st>>>(a, b, out, n); break;
+    }
+    return after_launch("b200_f32_binary");
+}
+
+extern "C" int b200_f32_unary(int op, const float* x, float* out, int64_t n, void* stream)
+{
+    using namespace b200;
+    if (n < 0 || op < B200_F32_ABS || op > B200_F32_RELU)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (n == 0)
+        return B200_OK;
+    if (!x || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned g = grid_for(n, 256);
+    switch (op)
+    {
+    case B200_F32_ABS: unary_kernel<B200_F32_ABS><<<g, 256, 0, st>>>(x, out, n); break;
+    case B200_F32_NEG: unary_kernel<B200_F32_NEG><<<g, 256, 0, st>>>(x, out, n); break;
+    case B200_F32_SQRT: unary_kernel<B200_F32_SQRT><<<g, 256, 0, st>>>(x, out, n); break;
+    case B200_F32_EXP: unary_kernel<B200_F32_EXP><<<g, 256, 0, st>>>(x, out, n); break;
+    case B200_F32_ERF: unary_kernel<B200_F32_ERF><<<g, 256, 0, st>>>(x, out, n); break;
+    default: unary_kernel<B200_F32_RELU><<<g, 256, 0, st>>>(x, out, n); break;
+    }
+    return after_launch("b200_f32_unary");
+}
+
+namespace b200
+{
+    static bool valid_shape(const int64_t* shape, int rank)
+    {
+        if (rank < 0 || rank > MAX_RANK || (rank > 0 && !shape))
+            return false;
+        for (int i = 0; i < rank; ++i)
+            if (shape[i] < 0)
+                return false;
+        return true;
+    }
+    static int64_t count_of(const int64_t* shape, int rank)
+    {
+        int64_t n = 1;
+        for (int i = 0; i < rank; ++i)
+            n *= shape[i];
+        return n;
+    }
+}
+
+extern "C" int b200_broadcast_b32(const void* in, void* out, const int64_t* out_shape, int rank, const int64_t* broadcast_axes,
+                                  int n_axes, void* stream)
+{
+    using namespace b200;
+    if (!valid_shape(out_shape, rank) || n_axes < 0 || n_axes > rank || (n_axes > 0 && !broadcast_axes))
+        return B200_ERR_INVALID_ARGUMENT;
+    bool is_new[MAX_RANK] = {false};
+    for (int i = 0; i < n_axes; ++i)
+    {
+        if (broadcast_axes[i] < 0 || broadcast_axes[i] >= rank || is_new[broadcast_axes[i]])
+            return B200_ERR_INVALID_ARGUMENT;
+        is_new[broadcast_axes[i]] = true;
+    }
+    const int64_t n = count_of(out_shape, rank);
+    if (n == 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    Dims d;
+    d.rank = rank;
+    int64_t stride = 1;
+    for (int a = rank - 1; a >= 0; --a)
+    {
+        d.out_dim[a] = out_shape[a];
+        d.in_stride[a] = is_new[a] ? 0 : stride;
+        if (!is_new[a])
+            stride *= out_shape[a];
+    }
+    remap_b32_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
+                                                                                      static_cast<uint32_t*>(out), d, n);
+    return after_launch("b200_broadcast_b32");
+}
+
+extern "C" int b200_permute_b32(const void* in, void* out, const int64_t* in_shape, int rank, const int64_t* order, void* stream)
+{
+    using namespace b200;
+    if (!valid_shape(in_shape, rank) || (rank > 0 && !order))
+        return B200_ERR_INVALID_ARGUMENT;
+    bool seen[MAX_RANK] = {false};
+    for (int i = 0; i < rank; ++i)
+    {
+        if (order[i] < 0 || order[i] >= rank || seen[order[i]])
+            return B200_ERR_INVALID_ARGUMENT;
+        seen[order[i]] = true;
+    }
+    const int64_t n = count_of(in_shape, rank);
+    if (n == 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    int64_t in_stride[MAX_RANK];
+    int64_t s = 1;
+    for (int a = rank - 1; a >= 0; --a)
+    {
+        in_stride[a] = s;
+        s *= in_shape[a];
+    }
+    Dims d;
+    d.rank = rank;
+    for (int a = 0; a < rank; ++a)
+    {
+        d.out_dim[a] = in_shape[order[a]];
+        d.in_stride[a] = in_stride[order[a]];
+    }
+    remap_b32_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
+                                                                                      static_cast<uint32_t*>(out), d, n);
+    return after_launch("b200_permute_b32");
+}
+
+extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_t* shape, int rank, const int64_t* axes, int n_axes,
+                               void* stream)
+{
+    using namespace b200;
+    if ((op != B200_REDUCE_SUM && op != B200_REDUCE_MAX) || !valid_shape(shape, rank) || n_axes < 0 || n_axes > rank ||
+        (n_axes > 0 && !axes))
+        return B200_ERR_INVALID_ARGUMENT;
+    bool reduced[MAX_RANK] = {false};
+    for (int i = 0; i < n_axes; ++i)
+    {
+        if (axes[i] < 0 || axes[i] >= rank || reduced[axes[i]])
+            return B200_ERR_INVALID_ARGUMENT;
+        reduced[axes[i]] = true;
+    }
+    int64_t stride[MAX_RANK];
+    int64_t s = 1;
+    for (int a = rank - 1; a >= 0; --a)
+    {
+        stride[a] = s;
+        s *= shape[a];
+    }
+    Dims keep, red;
+    keep.rank = red.rank = 0;
+    int64_t n_out = 1, n_red = 1;
+    for (int a = 0; a < rank; ++a)
+    {
+        Dims& d = reduced[a] ? red : keep;
+        d.out_dim[d.rank] = shape[a];
+        d.in_stride[d.rank] = stride[a];
+        ++d.rank;
+        (reduced[a] ? n_red : n_out) *= shape[a];
+    }
+    if (n_out == 0)
+        return B200_OK;
+    if (!out || (!in && n_red > 0))
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (op == B200_REDUCE_MAX && n_out <= 4096 && n_red >= 1024)
+        reduce_max_block_kernel<<<unsigned(n_out), 256, 0, st>>>(in, out, keep, red, n_red);
+    else if (op == B200_REDUCE_SUM)
+        reduce_kernel<true><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+    else
+        reduce_kernel<false><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+    return after_launch("b200_reduce_f32");
+}
+
+extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N, void* stream)
+{
+    using namespace b200;
+    if (batch < 0 || M < 0 || K < 0 || N < 0 || M > 0x7FFFFFFF || K > 0x7FFFFFFF || N > 0x7FFFFFFF)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (batch * M * N == 0)
+        return B200_OK;
+    if (!out || (K > 0 && (!a || !b)))
+        return B200_ERR_INVALID_ARGUMENT;
+    bmm_f32_kernel<<<grid_for(batch * M * N, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, batch, int(M), int(K),
+                                                                                                 int(N));
+    return after_launch("b200_bmm_f32");
+}
+
+extern "C" int b200_gather_rows_b32(const void* table, int64_t n_rows, int64_t row_elements, const void* indices, int index_type,
+                                    int64_t n_indices, void* out, void* stream)
+{
+    using namespace b200;
+    if (n_rows < 0 || row_elements < 0 || n_indices < 0 || (index_type != B200_I32 && index_type != B200_I64))
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t total = n_indices * row_elements;
+    if (total == 0)
+        return B200_OK;
+    if (!table || !indices || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (index_type == B200_I32)
+        gather_rows_kernel<int32_t><<<grid_for(total, 256), 256, 0, st>>>(static_cast<const uint32_t*>(table),
+                                                                          static_cast<const int32_t*>(indices),
+                                                                          static_cast<uint32_t*>(out), n_indices, row_elements, n_rows);
+    else
+        gather_rows_kernel<int64_t><<<grid_for(total, 256), 256, 0, st>>>(static_cast<const uint32_t*>(table),
+                                                                          static_cast<const int64_t*>(indices),
+                                                                          static_cast<uint32_t*>(out), n_indices, row_elements, n_rows);
+    return after_launch("b200_gather_rows_b32");
+}

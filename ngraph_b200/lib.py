@@ -57,6 +57,13 @@ def _load():
         "b200_global_avgpool_q_nhwc_u8": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
         "b200_im2col_c4_u8": (ci, [vp, vp] + [i64] * 11 + [vp]),
         "b200_requant_scale": (ci, [vp, vp, vp, vp, vp]),
+        "b200_f32_binary": (ci, [ci, vp, vp, vp, i64, vp]),
+        "b200_f32_unary": (ci, [ci, vp, vp, i64, vp]),
+        "b200_broadcast_b32": (ci, [vp, vp, p64, ci, p64, ci, vp]),
+        "b200_permute_b32": (ci, [vp, vp, p64, ci, p64, vp]),
+        "b200_reduce_f32": (ci, [ci, vp, vp, p64, ci, p64, ci, vp]),
+        "b200_bmm_f32": (ci, [vp, vp, vp, i64, i64, i64, i64, vp]),
+        "b200_gather_rows_b32": (ci, [vp, i64, i64, vp, ci, i64, vp, vp]),
         "b200_packed_weights_bytes": (i64, [i64] * 3),
         "b200_pack_weights_host": (ci, [vp, vp] + [i64] * 3),
         "b200_qconv_weight_block": (i64, [i64]),

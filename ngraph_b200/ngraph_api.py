@@ -53,6 +53,8 @@ def capi():
             "ngc_value_shape": (ci, [vp, p64, ci, ctypes.POINTER(ci)]),
             "ngc_function": (vp, [pvp, ci, pvp, ci]), "ngc_function_free": (None, [vp]),
             "ngc_function_op_count": (ci, [vp]),
+            "ngc_bert_encoder": (vp, [ci] * 7 + [ctypes.c_uint64, ci]),
+            "ngc_function_op_names": (ci, [vp, ci, ctypes.c_char_p, ci]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
             "ngc_tensor_create": (vp, [vp, ci, p64, ci]), "ngc_tensor_wrap": (vp, [vp, ci, p64, ci, vp]),
             "ngc_tensor_free": (None, [vp]),
@@ -247,6 +249,37 @@ class Function:
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
             _lib.ngc_function_free(self.h)
+
+
+class _Spec:
+    """dtype and shape of a Parameter / Result of a Function that was built on the C++ side"""
+
+    def __init__(self, dtype, shape):
+        self.dtype, self.shape = np.dtype(dtype), tuple(shape)
+
+
+class BuiltFunction(Function):
+    def __init__(self, handle, params, results, what):
+        if not handle:
+            _err(what)
+        self.h, self.params, self.results = handle, params, results
+
+
+def bert_encoder(layers, hidden, heads, ffn, seq, batch, vocab, seed=1, decomposed=False):
+    """int8 BERT-base-shaped encoder (ngraph_b200/harness/bert_int8.cpp): Function(ids i32 [B*S], segments i32 [B*S])
+    -> f32 [B*S, hidden].  decomposed=True replaces QuantizedDotBias by ops the INTERPRETER backend implements."""
+    h = capi().ngc_bert_encoder(layers, hidden, heads, ffn, seq, batch, vocab, seed, int(decomposed))
+    m = batch * seq
+    return BuiltFunction(h, [_Spec(np.int32, (m,)), _Spec(np.int32, (m,))], [_Spec(np.float32, (m, hidden))], "bert_encoder")
+
+
+def function_op_names(function, lowered=True):
+    """op type names in topological order, optionally after the passes a backend runs before lowering"""
+    buf = ctypes.create_string_buffer(1 << 22)
+    n = capi().ngc_function_op_names(function.h, int(lowered), buf, len(buf))
+    if n < 0:
+        _err("function_op_names")
+    return buf.value.decode().split()
 
 
 class Tensor:

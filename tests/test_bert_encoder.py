@@ -1,0 +1,58 @@
+"""BASELINE config 5 in miniature: an int8 BERT-base-shaped encoder (QuantizedDotBias with per-channel i8 weights and
+dynamic per-tensor i8 activation scales; softmax, LayerNorm, GELU and residual adds in f32) through the B200 plugin
+against nGraph's INTERPRETER on the decomposed graph.  The CPU part checks the graph itself; the GPU part the parity."""
+import collections
+
+import numpy as np
+import pytest
+
+from oracle import interpreter
+
+needs_reference = pytest.mark.skipif(not interpreter.available(), reason="nGraph reference libraries are not built")
+
+DIMS = dict(layers=2, hidden=64, heads=4, ffn=128, seq=16, batch=2, vocab=100)
+
+
+def _inputs(dims, seed):
+    rng = np.random.default_rng(seed)
+    m = dims["batch"] * dims["seq"]
+    ids = rng.integers(0, dims["vocab"], m).astype(np.int32)
+    seg = np.zeros((dims["batch"], dims["seq"]), np.int32)
+    for b in range(dims["batch"]):
+        seg[b, rng.integers(1, dims["seq"]):] = 1  # segment ids 0/1 split at a random position
+    return ids, seg.reshape(m)
+
+
+@needs_reference
+def test_graph_lowering_uses_only_supported_ops():
+    from ngraph_b200 import ngraph_api as ng
+    fn = ng.bert_encoder(seed=3, **DIMS)
+    ops = collections.Counter(ng.function_op_names(fn, lowered=True))
+    assert ops["QuantizedDotBias"] == 6 * DIMS["layers"] and ops["Quantize"] == 6 * DIMS["layers"]
+    assert ops["Softmax"] == DIMS["layers"] and ops["BatchMatMul"] == 2 * DIMS["layers"]
+    supported = {"Parameter", "Constant", "Result", "Quantize", "QuantizedDotBias", "Add", "Subtract", "Multiply", "Divide", "Abs",
+                 "Max", "Sum", "Sqrt", "Erf", "Broadcast", "Reshape", "Softmax", "BatchMatMul", "Gather"}
+    assert set(ops) <= supported, set(ops) - supported
+
+
+@needs_reference
+def test_interpreter_runs_the_decomposed_encoder():
+    from ngraph_b200 import ngraph_api as ng
+    fn = ng.bert_encoder(seed=3, decomposed=True, **DIMS)
+    out = interpreter.backend().compile(fn).run(*_inputs(DIMS, 0))[0]
+    assert out.shape == (DIMS["batch"] * DIMS["seq"], DIMS["hidden"]) and np.isfinite(out).all()
+    # LayerNorm output: every row is normalised before the affine step, so it cannot be constant
+    assert out.std() > 0.1
+
+
+@pytest.mark.gpu
+@needs_reference
+@pytest.mark.parametrize("dims", [DIMS, dict(layers=1, hidden=128, heads=2, ffn=256, seq=24, batch=3, vocab=50)])
+def test_encoder_matches_interpreter(dims):
+    from ngraph_b200 import ngraph_api as ng
+    ng.load_b200()
+    ids, seg = _inputs(dims, 1)
+    want = interpreter.backend().compile(ng.bert_encoder(seed=5, decomposed=True, **dims)).run(ids, seg)[0]
+    got = ng.Backend("B200").compile(ng.bert_encoder(seed=5, **dims)).run(ids, seg)[0]
+    # every op reproduces the reference arithmetic (exp / erf up to the last bit), so the outputs agree far inside 1e-5
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)

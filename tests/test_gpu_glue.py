@@ -1,0 +1,138 @@
+"""The f32 glue kernels through the C ABI against numpy restatements of nGraph's reference kernels
+(runtime/reference/{sum,max,broadcast,reshape,batch_mat_mul,gather}.hpp and the elementwise headers): bit-exact, except
+exp / erf, which are held to one unit in the last place of the float result."""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+OPS = dict(add=0, sub=1, mul=2, div=3, max=4, min=5, abs=6, neg=7, sqrt=8, exp=9, erf=10, relu=11)
+
+
+@pytest.fixture(scope="module")
+def L():
+    from ngraph_b200 import lib
+    return lib
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def i64(v):
+    return (ctypes.c_int64 * max(len(v), 1))(*[int(x) for x in v])
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def test_elementwise_is_ieee_exact(L):
+    rng = np.random.default_rng(1)
+    a = (rng.standard_normal(100003) * 10 ** rng.uniform(-6, 6, 100003)).astype(np.float32)
+    b = (rng.standard_normal(100003) * 10 ** rng.uniform(-6, 6, 100003)).astype(np.float32)
+    a[:4] = [0.0, -0.0, np.inf, np.nan]
+    ad, bd, out = dev(a), dev(b), torch.empty(a.size, device="cuda")
+    with np.errstate(all="ignore"):
+        want = dict(add=a + b, sub=a - b, mul=a * b, div=a / b, max=np.where(a > b, a, b), min=np.where(a < b, a, b))
+        for name, exp in want.items():
+            L.check(L.LIB.b200_f32_binary(OPS[name], ad.data_ptr(), bd.data_ptr(), out.data_ptr(), a.size, stream()), name)
+            got = out.cpu().numpy()
+            ok = (bits(got) == bits(exp)) | (np.isnan(got) & np.isnan(exp))  # NaN payloads are not part of the contract
+            assert ok.all(), name
+        want = dict(abs=np.abs(a), neg=-a, sqrt=np.sqrt(a), relu=np.where(a > 0, a, np.float32(0)))
+        for name, exp in want.items():
+            L.check(L.LIB.b200_f32_unary(OPS[name], ad.data_ptr(), out.data_ptr(), a.size, stream()), name)
+            got = out.cpu().numpy()
+            ok = (bits(got) == bits(exp)) | (np.isnan(got) & np.isnan(exp))
+            assert ok.all(), name
+
+
+def test_exp_and_erf_within_one_ulp(L):
+    x = np.linspace(-20, 20, 200001).astype(np.float32)
+    xd, out = dev(x), torch.empty(x.size, device="cuda")
+    for name, fn in (("exp", math.exp), ("erf", math.erf)):
+        L.check(L.LIB.b200_f32_unary(OPS[name], xd.data_ptr(), out.data_ptr(), x.size, stream()), name)
+        exact = np.array([fn(float(v)) for v in x], np.float64)
+        got = out.cpu().numpy().astype(np.float64)
+        ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
+        assert (np.abs(got - exact) <= ulp).all(), name
+
+
+def kahan_sum_rows(x):
+    """reference::sum over the last axis: sequential, compensated, in float32"""
+    z = np.zeros(x.shape[:-1], np.float32)
+    c = np.zeros(x.shape[:-1], np.float32)
+    for k in range(x.shape[-1]):
+        v = x[..., k]
+        y = (v - c).astype(np.float32)
+        t = (z + y).astype(np.float32)
+        c = ((t - z).astype(np.float32) - y).astype(np.float32)
+        z = t
+    return z
+
+
+@pytest.mark.parametrize("shape,axes", [((37, 768), (1,)), ((6, 5, 384), (2,)), ((9, 33, 7), (0, 2)), ((50000,), (0,)), ((4, 3), ())])
+def test_sum_and_max_follow_the_reference_order(L, shape, axes):
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal(shape) * 100).astype(np.float32)
+    keep = [i for i in range(len(shape)) if i not in axes]
+    moved = np.transpose(x, keep + list(axes)).reshape([shape[i] for i in keep] + [-1])  # reduced axes last, row-major order
+    want_sum = kahan_sum_rows(moved) if axes else x.copy()
+    want_max = moved.max(axis=-1) if axes else x.copy()
+    xd = dev(x)
+    out = torch.empty(max(want_sum.size, 1), device="cuda")
+    for op, want in ((0, want_sum), (1, want_max)):
+        L.check(L.LIB.b200_reduce_f32(op, xd.data_ptr(), out.data_ptr(), i64(shape), len(shape), i64(axes), len(axes), stream()), "reduce")
+        np.testing.assert_array_equal(bits(out.cpu().numpy()[:want.size]), bits(want).ravel())
+
+
+def test_broadcast_and_permute(L):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((5, 7)).astype(np.float32)
+    out = torch.empty((3, 5, 4, 7), device="cuda")
+    xd = dev(x)
+    L.check(L.LIB.b200_broadcast_b32(xd.data_ptr(), out.data_ptr(), i64(out.shape), 4, i64([0, 2]), 2, stream()), "broadcast")
+    np.testing.assert_array_equal(out.cpu().numpy(), np.broadcast_to(x[None, :, None, :], (3, 5, 4, 7)))
+    s = torch.empty(6, device="cuda")
+    one = dev(np.float32([2.5]))
+    L.check(L.LIB.b200_broadcast_b32(one.data_ptr(), s.data_ptr(), i64([6]), 1, i64([0]), 1, stream()), "broadcast")
+    assert (s.cpu().numpy() == 2.5).all()
+    y = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    yd = dev(y)
+    for order in ((0, 2, 1, 3), (0, 2, 3, 1), (3, 2, 1, 0)):
+        o = torch.empty(y.size, device="cuda")
+        L.check(L.LIB.b200_permute_b32(yd.data_ptr(), o.data_ptr(), i64(y.shape), 4, i64(order), stream()), "permute")
+        np.testing.assert_array_equal(o.cpu().numpy(), np.transpose(y, order).ravel())
+
+
+def test_bmm_accumulates_in_double_in_order(L):
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((3, 17, 96)).astype(np.float32)
+    b = rng.standard_normal((3, 96, 21)).astype(np.float32)
+    acc = np.zeros((3, 17, 21), np.float64)
+    for k in range(96):
+        acc += a[:, :, k, None].astype(np.float64) * b[:, k, None, :].astype(np.float64)
+    out = torch.empty((3, 17, 21), device="cuda")
+    ad, bd = dev(a), dev(b)  # kept alive until the result has been read
+    L.check(L.LIB.b200_bmm_f32(ad.data_ptr(), bd.data_ptr(), out.data_ptr(), 3, 17, 96, 21, stream()), "bmm")
+    np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(acc.astype(np.float32)))
+
+
+def test_gather_rows(L):
+    rng = np.random.default_rng(5)
+    table = rng.standard_normal((50, 24)).astype(np.float32)
+    for dt, code in ((np.int32, 2), (np.int64, 4)):
+        idx = rng.integers(0, 50, 77).astype(dt)
+        out = torch.empty((77, 24), device="cuda")
+        td, idxd = dev(table), dev(idx)
+        L.check(L.LIB.b200_gather_rows_b32(td.data_ptr(), 50, 24, idxd.data_ptr(), code, 77, out.data_ptr(), stream()), "gather")
+        np.testing.assert_array_equal(out.cpu().numpy(), table[idx])

@@ -297,8 +297,8 @@ def test_api_contract(backends):
     with pytest.raises(ng.NgraphError):  # a tensor created by another backend
         exe.call([good_out], [ref.create_tensor(np.float32, (2, 3))])
     with pytest.raises(ng.NgraphError):  # an op outside the quantized path is rejected at compile, no host fallback
-        q = ng.parameter(np.float32, (4,))
-        b200.compile(ng.Function([ng.relu(q)], [q]))
+        q = ng.parameter(np.float32, (1, 2, 4, 4))
+        b200.compile(ng.Function([ng.avg_pool(q, (2, 2), (2, 2))], [q]))
     # per-node performance counters
     exe2 = b200.compile(ng.Function([ng.quantize(p, np.float32(1), np.uint8(0), np.uint8)], [p]), perf=True)
     exe2.call([good_out], [good_in])
