@@ -47,7 +47,8 @@ def test_interpreter_runs_the_decomposed_encoder():
 
 @pytest.mark.gpu
 @needs_reference
-@pytest.mark.parametrize("dims", [DIMS, dict(layers=1, hidden=128, heads=2, ffn=256, seq=24, batch=3, vocab=50)])
+@pytest.mark.parametrize("dims", [DIMS, dict(layers=1, hidden=128, heads=2, ffn=256, seq=24, batch=3, vocab=50),
+                                  dict(layers=2, hidden=256, heads=4, ffn=1024, seq=32, batch=2, vocab=500)])
 def test_encoder_matches_interpreter(dims):
     from ngraph_b200 import ngraph_api as ng
     ng.load_b200()
@@ -56,3 +57,19 @@ def test_encoder_matches_interpreter(dims):
     got = ng.Backend("B200").compile(ng.bert_encoder(seed=5, **dims)).run(ids, seg)[0]
     # every op reproduces the reference arithmetic (exp / erf up to the last bit), so the outputs agree far inside 1e-5
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_bert_base_width_runs_and_repeats():
+    """BERT-base widths (hidden 768, 12 heads, FFN 3072) at a short sequence: too large for the INTERPRETER in a test,
+    so the plugin is checked against itself (two compilations, same seed: identical bits) and for sane LayerNorm output."""
+    from ngraph_b200 import ngraph_api as ng
+    ng.load_b200()
+    dims = dict(layers=2, hidden=768, heads=12, ffn=3072, seq=128, batch=4, vocab=30522)
+    ids, seg = _inputs(dims, 9)
+    be = ng.Backend("B200")
+    a = be.compile(ng.bert_encoder(seed=2, **dims)).run(ids, seg)[0]
+    b = be.compile(ng.bert_encoder(seed=2, **dims)).run(ids, seg)[0]
+    assert np.isfinite(a).all() and np.array_equal(a, b)
+    assert 0.5 < a.std() < 2.0
