@@ -12,7 +12,8 @@ from tests.fixtures import blob, interpreter_cases
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ng = pytest.importorskip("ngraph_b200.ngraph_api")
-from oracle import interpreter  # noqa: E402
+from oracle import interpreter
+from oracle import ref as ref_c  # noqa: E402
 
 needs_ngraph = pytest.mark.skipif(not interpreter.available(), reason="nGraph host library / INTERPRETER not built here")
 
@@ -162,6 +163,38 @@ def test_quantized_dot_bias(backends):
                               [px2, ps2])
             got, exp = run_both(backends, fused, ref, [x, scale])
             same_bits(got[0], exp[0], "requant %s relu %s" % (requant, relu))
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("act_dtype", [np.uint8, np.int8])
+@pytest.mark.parametrize("out_scale", [0.05, 5.0])
+def test_baseline_quantized_dot_bias_layer(backends, act_dtype, out_scale):
+    """BASELINE config 1 as a graph: X f32 [256,1024] ~N(0,1) -> Quantize(0.02, zp 0, RNE) -> QuantizedDotBias+Relu with
+    W i8 [1024,1024] (scale 0.01), bias f32 ~N(0,0.1) quantised to i32 with scale 0.02*0.01, requantised with
+    0.02*0.01/out_scale.  out_scale 0.05 is the config as written (most outputs saturate); 5.0 is its non-saturating twin
+    that exercises the rounding.  u8 activations are the reference-runnable variant, i8 the one BASELINE names."""
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((256, 1024)).astype(np.float32)
+    w = rng.integers(-127, 128, size=(1024, 1024)).astype(np.int8)
+    bias_f = (rng.standard_normal(1024) * 0.1).astype(np.float32)
+    s_in, s_w = np.float32(0.02), np.float32(0.01)
+    bias = ref_c.quantize(bias_f, np.float32(s_in * s_w), np.int32(0))
+    scale = np.array([np.float32(np.float32(s_in * s_w) / np.float32(out_scale))], np.float32)
+    zp = act_dtype(0)
+
+    def build(fused):
+        px = ng.parameter(np.float32, x.shape)
+        q = ng.quantize(px, s_in, zp, act_dtype)
+        if fused:
+            return ng.Function([ng.quantized_dot_bias(q, w, bias, scale, True, True)], [px])
+        return ng.Function([interpreter.decomposed_dot_bias(q, ng.constant(w), ng.constant(bias), ng.constant(scale), np.uint8, True)],
+                           [px])
+
+    got, exp = run_both(backends, build(True), build(False), [x])
+    same_bits(got[0], exp[0])
+    saturated = float((got[0] == 255).mean())
+    assert (saturated > 0.15) if out_scale == 0.05 else (saturated < 0.01)  # half of the outputs are negative -> 0 after ReLU
 
 
 CONVS = [
