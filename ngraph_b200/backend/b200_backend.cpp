@@ -14,6 +14,9 @@
 // once at compile time.
 #include "b200_backend.hpp"
 
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 
@@ -442,11 +445,16 @@ int B200Executable::new_slot(Slot::Kind kind, size_t bytes, size_t index)
     s.index = index;
     if (kind == Slot::ARENA)
     {
+        // provisional: one region per slot; plan_arena() overlays slots whose lifetimes do not meet
         s.offset = m_arena_bytes;
         m_arena_bytes += align_up(bytes ? bytes : 16, 256);
     }
     m_slots.push_back(s);
-    return int(m_slots.size()) - 1;
+    const int id = int(m_slots.size()) - 1;
+    m_birth.push_back(m_steps.size()); // the next step to be emitted is the first that can write it
+    m_last.push_back(m_steps.size());
+    m_touched.push_back(id);
+    return id;
 }
 
 int B200Executable::upload_constant(const void* data, size_t bytes)
@@ -459,6 +467,8 @@ int B200Executable::upload_constant(const void* data, size_t bytes)
     if (bytes)
         memcpy(m_constant_host.data() + s.offset, data, bytes);
     m_slots.push_back(s);
+    m_birth.push_back(0); // lifetimes are kept per slot index; constants live forever
+    m_last.push_back(size_t(-1));
     return int(m_slots.size()) - 1;
 }
 
@@ -482,9 +492,13 @@ int B200Executable::canonical_slot(const Output<Node>& out)
     if (v.skipped)
         throw std::runtime_error("B200 backend: internal error, fused value requested: " + out.get_node()->get_name());
     if (v.canonical >= 0)
+    {
+        m_touched.push_back(v.canonical);
         return v.canonical;
+    }
     if (v.nhwc < 0)
         throw std::runtime_error("B200 backend: internal error, value has no materialisation");
+    m_touched.push_back(v.nhwc);
     // channels-last -> NCHW
     const Shape sh = v.shape;
     int dst = new_slot(Slot::ARENA, shape_size(sh) * v.et.size());
@@ -500,7 +514,10 @@ int B200Executable::nhwc_slot(const Output<Node>& out)
 {
     Value& v = value_of(out);
     if (v.nhwc >= 0)
+    {
+        m_touched.push_back(v.nhwc);
         return v.nhwc;
+    }
     if (v.shape.size() != 4 || v.et.size() != 1)
         throw std::runtime_error("B200 backend: channels-last form exists for 4-D one-byte tensors only");
     const Shape sh = v.shape;
@@ -617,7 +634,16 @@ B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
         Value& v = value_of(src);
         int to = new_slot(Slot::RESULT, shape_size(v.shape) * v.et.size(), ri++);
         m_result_copies.push_back({from, to});
+        m_last[from] = size_t(-1); // read by the copy into the caller's tensor after the last step
     }
+    // conversions emitted for the results read their sources at those (late) steps
+    {
+        const size_t last = m_steps.empty() ? 0 : m_steps.size() - 1;
+        for (int slot : m_touched)
+            m_last[slot] = std::max(m_last[slot], last);
+        m_touched.clear();
+    }
+    plan_arena();
 
     if (m_arena_bytes)
         cuda_check(cudaMalloc(&m_arena, m_arena_bytes), "cudaMalloc(arena)");
@@ -648,7 +674,60 @@ B200Executable::~B200Executable()
     if (m_constants) cudaFree(m_constants);
 }
 
+// Every slot a node's lowering asked for (or created) stays alive at least until the last step emitted for that node.
 void B200Executable::compile_node(const std::shared_ptr<Node>& node)
+{
+    m_touched.clear();
+    lower_node(node);
+    const size_t last = m_steps.empty() ? 0 : m_steps.size() - 1;
+    if (m_last.size() != m_slots.size() || m_birth.size() != m_slots.size())
+        throw std::runtime_error("B200 backend: internal error, slot lifetimes out of step with the slot table");
+    for (int slot : m_touched)
+        m_last.at(size_t(slot)) = std::max(m_last.at(size_t(slot)), last);
+    m_touched.clear();
+}
+
+// Arena layout from the lifetimes: slots in order of first write; a slot takes the lowest gap that fits among the slots
+// still alive (first fit).  A slot is released only by a step AFTER its last reader, never by that step itself, so no
+// kernel ever reads and writes the same region; kernels run in stream order (a programmatic dependent launch touches
+// global memory only after the previous kernel has completed).
+void B200Executable::plan_arena()
+{
+    if (getenv("B200_NO_ARENA_REUSE"))
+        return;
+    struct Live { size_t offset, bytes, last; };
+    std::vector<Live> live;
+    size_t peak = 0;
+    for (size_t i = 0; i < m_slots.size(); ++i)
+    {
+        Slot& s = m_slots[i];
+        if (s.kind != Slot::ARENA)
+            continue;
+        const size_t bytes = align_up(s.bytes ? s.bytes : 16, 256);
+        std::vector<Live> keep;
+        for (auto& l : live)
+            if (l.last >= m_birth[i])
+                keep.push_back(l);
+        live.swap(keep);
+        std::sort(live.begin(), live.end(), [](const Live& a, const Live& b) { return a.offset < b.offset; });
+        size_t at = 0;
+        for (auto& l : live)
+        {
+            if (at + bytes <= l.offset)
+                break;
+            at = std::max(at, l.offset + l.bytes);
+        }
+        s.offset = at;
+        live.push_back(Live{at, bytes, m_last[i]});
+        peak = std::max(peak, at + bytes);
+    }
+    if (getenv("B200_DEBUG_ARENA"))
+        fprintf(stderr, "B200 backend: arena %.1f MB (%.1f MB without reuse), %zu steps\n", peak / 1e6, m_arena_bytes / 1e6,
+                m_steps.size());
+    m_arena_bytes = peak;
+}
+
+void B200Executable::lower_node(const std::shared_ptr<Node>& node)
 {
     if (is_type<op::v0::Parameter>(node) || is_type<op::v0::Result>(node))
         return;

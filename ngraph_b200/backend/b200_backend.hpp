@@ -146,6 +146,8 @@ namespace ngraph
                 void emit(const std::shared_ptr<const Node>& node, const std::string& what,
                           std::function<int(const Ptrs&, cudaStream_t)> run);
                 void compile_node(const std::shared_ptr<Node>& node);
+                void lower_node(const std::shared_ptr<Node>& node);
+                void plan_arena();
                 void compile_quantize(const std::shared_ptr<Node>& node);
                 void compile_dequantize(const std::shared_ptr<Node>& node);
                 void compile_fused_conv(const std::shared_ptr<Node>& node);
@@ -167,6 +169,9 @@ namespace ngraph
                 std::vector<Step> m_steps;
                 std::map<const descriptor::Tensor*, Value> m_values;
                 std::vector<char> m_constant_host; // staged constants, uploaded once at the end of compile
+                // lifetimes of the slots, in step indices: first step that may write / last step that reads
+                std::vector<size_t> m_birth, m_last;
+                std::vector<int> m_touched; // slots requested while the current node is lowered
                 size_t m_arena_bytes = 0;
                 void* m_arena = nullptr;
                 void* m_constants = nullptr;
