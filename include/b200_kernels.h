@@ -52,6 +52,11 @@ typedef enum b200_dtype
     B200_I64 = 4 /* index tensors only (b200_gather_rows_b32) */
 } b200_dtype;
 
+/* OR-ed into the data / activation type argument of b200_qgemm* and b200_qconv*: the weights (filters) are u8, not i8
+ * (op::v0::QuantizedDot / QuantizedConvolution accept u8 x u8; the fused ops do not). */
+#define B200_WEIGHTS_U8 0x100
+
+
 /* Same ordinal order as op::v0::Quantize::RoundMode (src/ngraph/op/quantize.hpp:38-81). */
 typedef enum b200_round_mode
 {

@@ -1363,8 +1363,11 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
     ConvAttrs a = attrs_of(op);
     const Shape ds = node->get_input_shape(0), fs = node->get_input_shape(1), os = node->get_output_shape(0);
     int dt = dtype_of(node->get_input_element_type(0));
-    if (dt != B200_U8 || node->get_input_element_type(1) != element::i8)
-        unsupported(*node, "data must be u8 and filters i8 (u8 x u8 has no tensor-core form)");
+    const element::Type& ft = node->get_input_element_type(1);
+    if (dt != B200_U8 || (ft != element::i8 && ft != element::u8))
+        unsupported(*node, "data must be u8 and filters i8 or u8");
+    if (ft == element::u8)
+        dt |= B200_WEIGHTS_U8; // kind::i8 takes unsigned B operands as well
     if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
         unsupported(*node, "non-zero input / filter zero points");
     auto zo = as_constant(node->input_value(7));
@@ -1474,8 +1477,10 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
 {
     auto op = as_type_ptr<op::v0::QuantizedDot>(node);
     const Shape as = node->get_input_shape(0), bs = node->get_input_shape(1);
-    if (node->get_input_element_type(0) != element::u8 || node->get_input_element_type(1) != element::i8)
-        unsupported(*node, "input0 must be u8 and input1 i8 (u8 x u8 has no tensor-core form)");
+    const element::Type& bt = node->get_input_element_type(1);
+    if (node->get_input_element_type(0) != element::u8 || (bt != element::i8 && bt != element::u8))
+        unsupported(*node, "input0 must be u8 and input1 i8 or u8");
+    const int operands = B200_U8 | (bt == element::u8 ? B200_WEIGHTS_U8 : 0);
     if (as.size() != 2 || bs.size() != 2 || op->get_reduction_axes_count() != 1 || as[1] % 16 != 0)
         unsupported(*node, "2-D operands with a reduction length that is a multiple of 16");
     if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
@@ -1523,8 +1528,8 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
         e.round_half_away = 1;
         e.out_zero_point = out_zp;
         e.out_type = out_t;
-        return w_image ? b200_qgemm_packed(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st)
-                       : b200_qgemm(p[a], B200_U8, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
+        return w_image ? b200_qgemm_packed(p[a], operands, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st)
+                       : b200_qgemm(p[a], operands, static_cast<const int8_t*>(p[w]), p[y], M, N, K, &e, st);
     });
     value_of(node->output(0)).canonical = y;
 }

@@ -1278,10 +1278,17 @@ namespace b200
 
     // tcgen05 instruction descriptor, kind::i8: [4,6) D format (2 = s32), [7,10) A format
     // (0 = u8, 1 = s8), [10,13) B format, bits 15/16 A/B major (0 = K-major), [17,23) N>>3, [24,29) M>>4.
-    static uint32_t make_idesc(int a_type, int bn)
+    static uint32_t make_idesc(int operand_types, int bn)
     {
-        uint32_t a_fmt = a_type == B200_I8 ? 1u : 0u;
-        return (2u << 4) | (a_fmt << 7) | (1u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+        const uint32_t a_fmt = (operand_types & 0xFF) == B200_I8 ? 1u : 0u;
+        const uint32_t b_fmt = (operand_types & B200_WEIGHTS_U8) ? 0u : 1u;
+        return (2u << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+    }
+
+    // data / activation type in the low byte, B200_WEIGHTS_U8 for unsigned weights
+    static bool valid_operand_types(int t)
+    {
+        return (t & ~(0xFF | B200_WEIGHTS_U8)) == 0 && ((t & 0xFF) == B200_U8 || (t & 0xFF) == B200_I8);
     }
 
     static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual)
@@ -1352,7 +1359,7 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
                       const b200_epilogue* epilogue, void* stream)
 {
     using namespace b200;
-    if (M < 0 || N < 0 || K < 0 || (a_type != B200_U8 && a_type != B200_I8))
+    if (M < 0 || N < 0 || K < 0 || !valid_operand_types(a_type))
         return B200_ERR_INVALID_ARGUMENT;
     int rc = check_epilogue(epilogue, N);
     if (rc != B200_OK)
@@ -1497,7 +1504,7 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
                       const b200_conv_params* c, const b200_epilogue* epilogue, void* stream)
 {
     using namespace b200;
-    if (!c || (data_type != B200_U8 && data_type != B200_I8))
+    if (!c || !valid_operand_types(data_type))
         return B200_ERR_INVALID_ARGUMENT;
     int64_t P, Q;
     int rc = b200_qconv_out_shape(c, &P, &Q);

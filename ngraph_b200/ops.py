@@ -55,6 +55,14 @@ def dequantize(x, scale, zero_point, axes=(), out=None):
     return out
 
 
+WEIGHTS_U8 = 0x100
+
+
+def _operands(data, weights):
+    """data type code, plus the flag for unsigned weights"""
+    return _DT[data.dtype] | (WEIGHTS_U8 if weights.dtype == torch.uint8 else 0)
+
+
 def _epilogue(n_out, scale, out_dtype, bias=None, relu=False, sum_in=None, sum_scale=None, core=False, out_zp=0):
     scale = _dev(scale, torch.float32)
     keep = [scale]
@@ -82,7 +90,7 @@ def _epilogue(n_out, scale, out_dtype, bias=None, relu=False, sum_in=None, sum_s
 def pack_weights(w, bk):
     """Host int8 [N,K] matrix (numpy or CPU tensor) -> device tensor holding the packed image for k-blocks of bk bytes."""
     import numpy as np
-    w = np.ascontiguousarray(w.cpu().numpy() if isinstance(w, torch.Tensor) else w, dtype=np.int8)
+    w = np.ascontiguousarray(w.cpu().numpy() if isinstance(w, torch.Tensor) else w).view(np.int8)
     n, k = w.shape
     packed = np.empty(LIB.b200_packed_weights_bytes(n, k, bk), np.int8)
     check(LIB.b200_pack_weights_host(w.ctypes.data, packed.ctypes.data, n, k, bk), "b200_pack_weights_host")
@@ -93,7 +101,8 @@ def qgemm(a, w, scale, out_dtype, bias=None, relu=False, sum_in=None, sum_scale=
           packed=False):
     """out[M,N] = epilogue(a[M,K] @ w[N,K]^T): QuantizedDotBias (fused contract) or, with core=True,
     QuantizedDot's requantisation on a pre-transposed B.  packed=True sends the weights through the packed image."""
-    a, w = _dev(a), _dev(w, torch.int8)
+    a, w = _dev(a), _dev(w)
+    assert w.dtype in (torch.int8, torch.uint8)
     m, k = a.shape
     n, k2 = w.shape
     assert k == k2
@@ -101,11 +110,11 @@ def qgemm(a, w, scale, out_dtype, bias=None, relu=False, sum_in=None, sum_scale=
     out = torch.empty((m, n), dtype=out_dtype, device=a.device) if out is None else out
     if packed:
         pw = pack_weights(w, 128)
-        check(LIB.b200_qgemm_packed(_ptr(a), _DT[a.dtype], _ptr(pw), _ptr(out), m, n, k, ctypes.byref(e), _stream()),
+        check(LIB.b200_qgemm_packed(_ptr(a), _operands(a, w), _ptr(pw), _ptr(out), m, n, k, ctypes.byref(e), _stream()),
               "b200_qgemm_packed")
         torch.cuda.current_stream().synchronize()  # pw is released on return
         return out
-    check(LIB.b200_qgemm(_ptr(a), _DT[a.dtype], _ptr(w), _ptr(out), m, n, k, ctypes.byref(e), _stream()), "b200_qgemm")
+    check(LIB.b200_qgemm(_ptr(a), _operands(a, w), _ptr(w), _ptr(out), m, n, k, ctypes.byref(e), _stream()), "b200_qgemm")
     return out
 
 
@@ -127,18 +136,19 @@ def conv_out_hw(cp):
 def qconv(data, filters, scale, out_dtype, cp, bias=None, relu=False, sum_in=None, sum_scale=None, core=False, out_zp=0,
           out=None, packed=False):
     """Channels-last int8 convolution with the fused epilogue: data [N,H,W,C], filters [K,R,S,C] -> [N,P,Q,K]."""
-    data, filters = _dev(data), _dev(filters, torch.int8)
+    data, filters = _dev(data), _dev(filters)
+    assert filters.dtype in (torch.int8, torch.uint8)
     e, keep = _epilogue(cp.K, scale, out_dtype, bias, relu, sum_in, sum_scale, core, out_zp)
     p, q = conv_out_hw(cp)
     out = torch.empty((cp.N, p, q, cp.K), dtype=out_dtype, device=data.device) if out is None else out
     if packed:
         pw = filters if packed == "prepacked" else pack_weights(filters.reshape(cp.K, -1), LIB.b200_qconv_weight_block(cp.C))
-        check(LIB.b200_qconv_packed(_ptr(data), _DT[data.dtype], _ptr(pw), _ptr(out), ctypes.byref(cp), ctypes.byref(e),
+        check(LIB.b200_qconv_packed(_ptr(data), _operands(data, filters), _ptr(pw), _ptr(out), ctypes.byref(cp), ctypes.byref(e),
                                     _stream()), "b200_qconv_packed")
         if packed != "prepacked":
             torch.cuda.current_stream().synchronize()  # pw is released on return
         return out
-    check(LIB.b200_qconv(_ptr(data), _DT[data.dtype], _ptr(filters), _ptr(out), ctypes.byref(cp), ctypes.byref(e),
+    check(LIB.b200_qconv(_ptr(data), _operands(data, filters), _ptr(filters), _ptr(out), ctypes.byref(cp), ctypes.byref(e),
                          _stream()), "b200_qconv")
     return out
 

@@ -78,14 +78,40 @@ def test_reference_quantized_dot_bias_vectors(ops):
 def test_reference_quantized_dot_vectors(ops):
     for case in reference_tests("QuantizedDot"):
         c = case["consts"]
-        if c["input_zero_point"] or c["filter_zero_point"] or case["b"]["dtype"] != "i8":
-            continue  # u8 x u8 and non-zero zero points are outside the tensor-core path
+        if c["input_zero_point"] or c["filter_zero_point"]:
+            continue  # non-zero input zero points are outside the tensor-core path (none among the reference's vectors)
         a = pad_k(typed(case["a"], case["shape_a"]))
         w = pad_k(np.ascontiguousarray(typed(case["b"], case["shape_b"]).T))
         scale = np.float32(c["input_scale"]) * np.float32(c["filter_scale"]) / np.float32(c["output_scale"])
         out_dt = NP[case["expected"]["dtype"]]
         got = ops.qgemm(dev(a), dev(w), dev(np.array([scale], np.float32)), TDT[np.dtype(out_dt)], core=True,
                         out_zp=c["output_zero_point"]).cpu().numpy()
+        np.testing.assert_array_equal(got.ravel(), typed(case["expected"]), err_msg=case["name"])
+
+
+def test_reference_quantized_convolution_vectors(ops):
+    """test/backend/quantized_convolution.in.cpp: one input channel (zero-padded to 64 for the tensor cores), i8 and u8 filters"""
+    for case in reference_tests("QuantizedConvolution"):
+        if case["uses_builder"]:
+            v = [x[1] for x in case["f32_consts"]]
+            f32 = np.float32
+            sd, sf, so = f32(max(abs(v[0]), abs(v[1]))) / f32(255), f32(max(abs(v[2]), abs(v[3]))) / f32(127), \
+                f32(max(abs(v[4]), abs(v[5]))) / f32(127)
+            zo = 0
+        else:
+            c = case["consts"]
+            if c["input_zero_point"] or c["filter_zero_point"]:
+                continue
+            sd, sf, so, zo = np.float32(c["input_scale"]), np.float32(c["filter_scale"]), np.float32(c["output_scale"]), c["output_zero_point"]
+        data, filt = typed(case["a"], case["shape_a"]), typed(case["b"], case["shape_b"])
+        n, ch, h, w = data.shape
+        dpad = np.zeros((n, 64, h, w), data.dtype)
+        dpad[:, :ch] = data
+        fpad = np.zeros((filt.shape[0], 64) + filt.shape[2:], filt.dtype)
+        fpad[:, :ch] = filt
+        cs = ref.conv_shape(dpad.shape, fpad.shape, case["stride"], case["pad_below"], case["pad_above"], case["dilation"])
+        out_dt = NP[case["expected"]["dtype"]]
+        got = run_conv(ops, dpad, fpad, None, np.float32(sd * sf / so), cs, out_dt, False, core=True, out_zp=zo)
         np.testing.assert_array_equal(got.ravel(), typed(case["expected"]), err_msg=case["name"])
 
 

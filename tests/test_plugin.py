@@ -142,6 +142,15 @@ def test_quantized_dot_core(backends):
         fn2 = ng.Function([ng.quantized_dot(pa, ng.constant(b), 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa])
         got2 = backends[0].compile(fn2).run(a)
         same_bits(got2[0], exp[0], "constant B " + str(out_dtype))
+    # u8 x u8 (INTERPRETER: -> u8 and -> i32), run-time and constant B
+    bu = rng.integers(0, 256, size=(64, 24)).astype(np.uint8)
+    for out_dtype, so, zo in ((np.uint8, 9000.0, 5), (np.int32, 0.5, 7)):
+        pa, pb = ng.parameter(np.uint8, a.shape), ng.parameter(np.uint8, bu.shape)
+        fn = ng.Function([ng.quantized_dot(pa, pb, 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa, pb])
+        got, exp = run_both(backends, fn, fn, [a, bu])
+        same_bits(got[0], exp[0], "u8 x u8 " + str(out_dtype))
+        fn2 = ng.Function([ng.quantized_dot(pa, ng.constant(bu), 0.5, 0, 0.25, 0, so, zo, out_dtype)], [pa])
+        same_bits(backends[0].compile(fn2).run(a)[0], exp[0], "u8 x u8 constant B " + str(out_dtype))
 
 
 @pytest.mark.gpu
@@ -266,6 +275,15 @@ def test_core_quantized_convolution(backends):
         fn = ng.Function([ng.quantized_convolution(d, f, 1.0, 0, 1.0, 0, so, zo, out_dtype, pad_below=(1, 1))], [d, f])
         got, exp = run_both(backends, fn, fn, [data, filt])
         same_bits(got[0], exp[0], str(out_dtype))
+    # u8 filters (the reference's quantized_conv_int32_output test is u8 x u8)
+    filt_u = rng.integers(0, 256, size=fs).astype(np.uint8)
+    for out_dtype, so, zo in ((np.int32, 1.0, 0), (np.uint8, 100000.0, 3)):  # in range: the INTERPRETER wraps, the device saturates
+        d, f = ng.parameter(np.uint8, ds), ng.parameter(np.uint8, fs)
+        fn = ng.Function([ng.quantized_convolution(d, f, 1.0, 0, 1.0, 0, so, zo, out_dtype, pad_below=(1, 1))], [d, f])
+        got, exp = run_both(backends, fn, fn, [data, filt_u])
+        same_bits(got[0], exp[0], "u8 filters " + str(out_dtype))
+        fn2 = ng.Function([ng.quantized_convolution(d, ng.constant(filt_u), 1.0, 0, 1.0, 0, so, zo, out_dtype, pad_below=(1, 1))], [d])
+        same_bits(backends[0].compile(fn2).run(data)[0], exp[0], "u8 constant filters " + str(out_dtype))
 
 
 @pytest.mark.gpu
