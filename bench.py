@@ -235,9 +235,16 @@ class ResNet50:
                     f.write("%10.1f us  %s\n" % (us / passes, n))
         # dram__bytes_read.sum + dram__bytes_write.sum of the 54 contraction launches of one batch-128 step, from the ncu
         # capture summarised in profiles/resnet50_b128_launch_list.txt, averaged per launch and scaled by the batch
+        # the same launches against their own rooflines: a layer can go no faster than its ops at the tensor peak or its
+        # bytes at the HBM peak, whichever is longer; most 1x1 layers are on the HBM side
+        work = self.model.layer_work()
+        assert abs(sum(m for _, m, _, _ in work) - self.model.macs_per_image()) < 1
+        floor_us = sum(max(2.0 * m * self.batch / (peak * 1e12), (by * self.batch + wt) / (peaks["hbm_gbs"] * 1e9)) * 1e6
+                       for _, m, by, wt in work)
         traffic = (1976.9e6 + 350.8e6) / 54 * (self.batch / 128.0)
         return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": traffic,
                 "traffic_note": "average per contraction launch (54 per step), ncu capture at batch 128",
+                "per_layer_floor_us": floor_us, "frac_of_per_layer_floor": floor_us / contr_us,
                 "kernel": "qcontract_kernel (53 convolutions + dot)", "kernel_us_per_step": contr_us, "all_nodes_us_per_step": total_us,
                 "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)",
                 "slowest_nodes_us": [[round(u, 1), n] for u, n in top]}

@@ -501,6 +501,11 @@ int B200Executable::canonical_slot(const Output<Node>& out)
     m_touched.push_back(v.nhwc);
     // channels-last -> NCHW
     const Shape sh = v.shape;
+    if (sh.size() == 4 && (sh[1] == 1 || sh[2] * sh[3] == 1))
+    {
+        v.canonical = v.nhwc; // one channel or one pixel per image: both orders are the same bytes
+        return v.canonical;
+    }
     int dst = new_slot(Slot::ARENA, shape_size(sh) * v.et.size());
     int src = v.nhwc;
     emit(out.get_node_shared_ptr(), "nhwc_to_nchw", [=](const Ptrs& p, cudaStream_t st) {
@@ -522,6 +527,11 @@ int B200Executable::nhwc_slot(const Output<Node>& out)
         throw std::runtime_error("B200 backend: channels-last form exists for 4-D one-byte tensors only");
     const Shape sh = v.shape;
     int src = canonical_slot(out);
+    if (sh[1] == 1 || sh[2] * sh[3] == 1)
+    {
+        value_of(out).nhwc = src; // the same bytes in both orders
+        return src;
+    }
     int dst = new_slot(Slot::ARENA, shape_size(sh));
     emit(out.get_node_shared_ptr(), "nchw_to_nhwc", [=](const Ptrs& p, cudaStream_t st) {
         return b200_nchw_to_nhwc_u8(p[src], p[dst], sh[0], sh[1], sh[2], sh[3], sh[1], st);

@@ -443,24 +443,28 @@ namespace b200
         const int lane = threadIdx.x & 31;
         volatile int* abortp = &abort_flag;
 
+        // barrier initialisation is spread over the threads of warps 4 and up (one barrier each) while warp 0 allocates
+        // tensor memory: the set-up is on the critical path of every launch
         if (threadIdx.x == 0)
-        {
             abort_flag = 0;
-            for (int s = 0; s < STAGES; ++s)
+        {
+            const int t = int(threadIdx.x) - 128;
+            if (t >= 0 && t < STAGES)
             {
-                ptx::mbar_init(full_bar(s), 1);
-                ptx::mbar_init(empty_bar(s), 1);
+                ptx::mbar_init(full_bar(t), 1);
+                ptx::mbar_init(empty_bar(t), 1);
             }
-            ptx::mbar_init(bres_bar, 1);
-            for (int b = 0; b < NACC; ++b)
+            else if (t >= 32 && t < 32 + NACC)
             {
-                ptx::mbar_init(tfull_bar(b), 1);
-                ptx::mbar_init(tempty_bar(b), 4 * SPLIT);
+                ptx::mbar_init(tfull_bar(t - 32), 1);
+                ptx::mbar_init(tempty_bar(t - 32), 4 * SPLIT);
             }
-            for (int w = 0; w < EPI_WARPS; ++w)
-                for (int b = 0; b < 3; ++b)
-                    ptx::mbar_init(sum_bar(w, b), 1);
-            ptx::fence_barrier_init();
+            else if (t == 48)
+                ptx::mbar_init(bres_bar, 1);
+            else if (t >= 64 && t < 64 + 3 * EPI_WARPS)
+                ptx::mbar_init(sum_bar((t - 64) / 3, (t - 64) % 3), 1);
+            if (t >= 0 && t < 128)
+                ptx::fence_barrier_init();
         }
         if (warp == 0)
         {

@@ -119,6 +119,31 @@ class QuantizedResNet50:
         self.s_logits = np.float32(2.0 * max(float(logits.abs().max()), 1e-6) / 127)
 
     # ------------------------------------------------------------------ graph
+    def layer_work(self, hw=None):
+        """per contraction node in execution order: (name, multiply-accumulates, bytes read + written) for ONE image; bytes =
+        input and output activations (one byte each), the residual where there is one; weights are added per batch by the
+        caller (they are read once per launch, not per image)"""
+        h, w = hw or (self.image_size, self.image_size)
+        out = lambda n, k, s, p: (n + 2 * p - k) // s + 1
+        rows = []
+        hs, ws = out(h, 7, 2, 3), out(w, 7, 2, 3)
+        rows.append(("stem", hs * ws * 64 * 3 * 49, h * w * 3 * 4 + hs * ws * 64, 64 * 3 * 49))  # reads the f32 image
+        h, w = out(hs, 3, 2, 1), out(ws, 3, 2, 1)
+        cin = 64
+        for si, (blocks, mid, cout, stride) in enumerate(STAGES):
+            for b in range(blocks):
+                s = stride if b == 0 else 1
+                ho, wo = out(h, 3, s, 1), out(w, 3, s, 1)
+                pre = "s%db%d" % (si + 1, b)
+                if b == 0:
+                    rows.append((pre + "_down", ho * wo * cin * cout, h * w * cin + ho * wo * cout, cin * cout))
+                rows.append((pre + "_c1", h * w * cin * mid, h * w * cin + h * w * mid, cin * mid))
+                rows.append((pre + "_c2", ho * wo * mid * mid * 9, h * w * mid + ho * wo * mid, mid * mid * 9))
+                rows.append((pre + "_c3", ho * wo * mid * cout, ho * wo * mid + 2 * ho * wo * cout, mid * cout))
+                h, w, cin = ho, wo, cout
+        rows.append(("fc", 2048 * self.classes, 2048 + self.classes, 2048 * self.classes))
+        return rows
+
     def macs_per_image(self, hw=None):
         """multiply-accumulates of the convolutions and the final QuantizedDot for one image of size hw"""
         h, w = hw or (self.image_size, self.image_size)
