@@ -743,6 +743,9 @@ namespace b200
             // per-row addresses are only needed for residual loads and for stores that do not go through TMA
             const bool need_rows = has_sum || !p.tma_store;
             const int tile_step = GROUPS * int(gridDim.x); // distance between two tiles of this warp
+            // One thread per warp issues the warp's TMA loads / stores, bulk-group waits and barrier arrivals.  It is
+            // chosen by elect.sync at points where the warp is converged: the election is deterministic for a full
+            // mask (the bulk groups stay with one thread) and lets the compiler keep the operands in uniform registers.
 
             // The tile loop, compiled once per MODE.  MODE 0..8 = bytes_variant with TMA stores, a width that is a
             // multiple of 64 (every chunk full) and, where there is a residual, the residual fetched by TMA into the
@@ -811,7 +814,7 @@ namespace b200
                         const bool has_next = tile + tile_step < num_tiles;
                         int na, np0, nn0, ntn;
                         coords_of(idx + 1, na, np0, nn0, ntn);
-                        if (lane == 0)
+                        if (ptx::elect_one())
                         {
                             if (j == 0)
                                 fetch_residual(0, ia, p0, n0, tn);
@@ -825,7 +828,7 @@ namespace b200
                     else if (j >= 2)
                     {
                         // the TMA store issued two tiles ago must have finished reading this staging block
-                        if (lane == 0)
+                        if (ptx::elect_one())
                             asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     }
                     if (tn != staged_tn)
@@ -1014,7 +1017,7 @@ namespace b200
                     // all of this warp's TMEM reads are done: hand the accumulator back
                     ptx::tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0)
+                    if (ptx::elect_one())
                         ptx::mbar_arrive(tempty_bar(acc));
                     if (FAST || p.tma_store)
                     {
@@ -1022,7 +1025,7 @@ namespace b200
                         // rows / columns that fall outside the output tensor are clipped by the TMA unit
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
-                        if (lane == 0)
+                        if (ptx::elect_one())
                         {
                             // a block whose first row or column lies outside the tensor is skipped (its group stays empty)
                             if (p.conv && blk_valid && colw < p.N)
@@ -1063,7 +1066,7 @@ namespace b200
             default: epilogue_loop(std::integral_constant<int, -1>{}); break;
             }
             // stores must be complete (not just read) before the CTA exits
-            if (lane == 0)
+            if (ptx::elect_one())
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
 
