@@ -614,7 +614,7 @@ extern "C" int b200_stem_pack_input_f32(const float* in_nchw, const float* scale
     const int64_t eh = pad_h + (pad_h & 1), ew = pad_w + (pad_w & 1);
     int64_t total = N * Hc * Wc;
     int64_t blocks = (total + 255) / 256;
-    unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
+    unsigned grid = unsigned(blocks); // one cell per thread: the kernel is a single wave of loads, not a loop
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (total >= (int64_t(1) << 31))
         return B200_ERR_TOO_LARGE;
