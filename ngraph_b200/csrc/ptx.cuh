@@ -186,6 +186,9 @@ namespace b200
         // (64 or 128) long and stored with the matching TMA swizzle; 8-row groups are
         // 8*row_bytes apart (the stride byte offset).  Bits: [0,14) start>>4, [16,30) LBO>>4,
         // [32,46) SBO>>4, [46,48) descriptor version (1 on sm_100), [61,64) swizzle mode.
+        // The start may be any whole number of rows (and, for the K steps of one tile, 32-byte pieces) into a tile
+        // that the TMA unit wrote: the 16-byte swizzle is a function of the shared-memory address bits alone, so a
+        // descriptor that starts r rows into the tile reads rows r, r+1, ... correctly (measured; base-offset field 0).
         __device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t smem_addr, uint32_t row_bytes)
         {
             const uint64_t layout = row_bytes == 128 ? 2ull : row_bytes == 64 ? 4ull : 6ull;

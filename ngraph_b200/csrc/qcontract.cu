@@ -95,6 +95,10 @@ namespace b200
         int relu, half_away, out_zp, out_type;
         int one;             // the constant 1, opaque to the compiler (see add_fma_pipe)
         int tma_store;       // one-byte output, width a multiple of 16: staged in smem and stored by TMA
+        int halo;            // convolution with the input patch of a tile (halo included) loaded once per channel block
+        int RW;              // width of a row of tile positions: TW, or TW + S - 1 in halo mode (the extra positions are junk)
+        int halo_bytes;      // bytes of one halo load (the TMA box)
+        int blk_bytes;       // bytes of one epilogue warp's store / residual box
         const uint8_t* a_cells; // stem: cell grid read as overlapping windows straight from linear memory (null otherwise)
         int cells_w, cells_h;   // its row length and row count per image, in cells
         const int8_t* b_packed; // weights in the block image made by b200_pack_weights_host (null: plain [N,K] matrix through maps.b)
@@ -520,7 +524,8 @@ namespace b200
                     }
                 }
             }
-            const int nkb = p.ntaps * p.cblocks;
+            // pipeline stages one tile consumes: one per (tap, channel block), or one per channel block in halo mode
+            const int nkb = p.halo ? p.cblocks : p.ntaps * p.cblocks;
             int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
             int idx = 32;
             // this producer's next k-block, as (offset inside the current tile, pipeline stage, stage parity); it advances
@@ -562,7 +567,7 @@ namespace b200
                     // packed weights: this column tile's 64-row blocks of a k-block are one contiguous piece
                     const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
                     const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
-                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES : uint32_t(C::A_BYTES)) + b_bytes;
+                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES)) + b_bytes;
                     int tap = 0, cb = j; // k-block j of the tile = (tap, channel block)
                     while (cb >= p.cblocks)
                     {
@@ -584,7 +589,12 @@ namespace b200
                         const uint32_t a_dst = smem_base + s * stage_bytes;
                         const uint32_t b_dst = a_dst + C::A_BYTES;
                         ptx::mbar_expect_tx(full_bar(s), tx_bytes);
-                        if (p.a_cells)
+                        if (p.halo)
+                        {
+                            // the tile's input patch with its halo, channel block j: RW x (TH + R - 1) pixels, one box
+                            ptx::tma_load_4d(a_dst, &maps.a[0], full_bar(s), j * BK, q0 + p.taps[0].dw, p0 + p.taps[0].dh, n0);
+                        }
+                        else if (p.a_cells)
                         {
                             // 128 output pixels of one output row need cells q0 .. q0+130 of cell row p0 + tap: one run
                             const size_t cell = (size_t(n0) * p.cells_h + size_t(p0 + tp.dh)) * p.cells_w + size_t(q0);
@@ -658,6 +668,42 @@ namespace b200
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
+                    if (p.halo)
+                    {
+                        // One stage per channel block holds the patch with its halo, pixel rows of BK bytes; tap (r,s) reads
+                        // it through a descriptor whose start is shifted by r * RW + s rows.  The 16-byte swizzle follows the
+                        // shared-memory address bits, the same bits the TMA unit used when it wrote the patch.
+                        for (int cb = 0; cb < p.cblocks; ++cb)
+                        {
+                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
+                            {
+                                fail = 2002;
+                                break;
+                            }
+                            ptx::tc_fence_after_sync();
+                            const uint32_t stage_addr = smem_base + uint32_t(s) * stage_bytes;
+                            for (int tap = 0; tap < p.ntaps; ++tap)
+                            {
+                                const uint32_t a_addr = stage_addr + uint32_t(p.taps[tap].pad) * BK; // pad: row shift of the tap
+                                const uint64_t a_desc = ptx::smem_desc_kmajor(a_addr, BK);
+                                const uint64_t b_desc = b_desc0 + uint64_t(tap * p.cblocks + cb) * b_step;
+#pragma unroll
+                                for (int k = 0; k < BK / 32; ++k)
+                                    ptx::mma_i8(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc,
+                                                (cb | tap | k) != 0 ? 1u : 0u);
+                            }
+                            ptx::mma_commit(empty_bar(s));
+                            if (++s == STAGES)
+                            {
+                                s = 0;
+                                ph ^= 1;
+                            }
+                        }
+                        if (fail)
+                            break;
+                        ptx::mma_commit(tfull_bar(acc));
+                        continue;
+                    }
                     for (int kb = 0; kb < num_kblocks; ++kb)
                     {
                         {
@@ -712,13 +758,13 @@ namespace b200
             int row_w = 0, row_h = 0, row_n = 0, blk_w = 0, blk_h = 0, blk_n = 0;
             if (p.conv)
             {
-                row_w = row % p.TW;
-                row_h = (row / p.TW) % p.TH;
-                row_n = row / (p.TW * p.TH);
+                row_w = row % p.RW;
+                row_h = (row / p.RW) % p.TH;
+                row_n = row / (p.RW * p.TH);
                 const int row0 = quarter * 32;
-                blk_w = row0 % p.TW;
-                blk_h = (row0 / p.TW) % p.TH;
-                blk_n = row0 / (p.TW * p.TH);
+                blk_w = row0 % p.RW;
+                blk_h = (row0 / p.RW) % p.TH;
+                blk_n = row0 / (p.RW * p.TH);
             }
             const bool has_sum = p.sum_in != nullptr;
             const float sum_scale = has_sum ? __ldg(p.sum_scale) : 0.0f;
@@ -775,7 +821,7 @@ namespace b200
                 auto fetch_residual = [&](int b, int a_, int p0_, int n0_, int tn_) {
                     const uint32_t bar = sum_bar(ew, b), dst = stage_blk0 + uint32_t(b) * C::OUT_BYTES;
                     const int col = tn_ * BN + part * COLS;
-                    ptx::mbar_expect_tx(bar, 32 * COLS);
+                    ptx::mbar_expect_tx(bar, uint32_t(p.blk_bytes));
                     if (p.conv)
                         ptx::tma_load_4d(dst, &maps.sum, bar, col, a_ + blk_w, p0_ + blk_h, n0_ + blk_n);
                     else
@@ -857,7 +903,7 @@ namespace b200
                         if (rows)
                         {
                             const int q = q0 + row_w, pp = p0 + row_h, n = n0 + row_n;
-                            er.valid = q < p.Q && pp < p.P && n < p.NB;
+                            er.valid = row_w < p.TW && q < p.Q && pp < p.P && n < p.NB;
                             er.off = ((int64_t(n) * p.P + pp) * p.Q + q) * p.N;
                         }
                     }
@@ -1194,6 +1240,13 @@ namespace b200
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
+        if (p.halo)
+        {
+            if (!sp.b_resident)
+                return B200_ERR_UNSUPPORTED; // the caller only asks for halo mode when the weights stay resident
+            // the patch plus the rows the last taps read past it for the junk positions of the last tile row
+            sp.stage_bytes = ((p.halo_bytes + 64 * BK + 1023) / 1024) * 1024;
+        }
         const int room = SMEM_LIMIT - C::FIXED - sp.b_res_bytes - 64;
         if (p.tma_store && nkb >= 16 && (room - 2 * C::OUT_BYTES) / sp.stage_bytes < 4)
         {
@@ -1416,6 +1469,7 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
     {
         uint64_t dims_o[2] = {uint64_t(N), uint64_t(M)}, str_o[1] = {uint64_t(N)};
         uint32_t box_o[2] = {uint32_t(COLS), 32u};
+        p.blk_bytes = 32 * COLS;
         make_out_maps(maps, p, 2, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
@@ -1561,8 +1615,38 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     p.P = int(P);
     p.Q = int(Q);
     pick_patch(c->N, P, Q, p.TW, p.TH, p.TN);
+    // Halo mode (stride 1, no dilation, more than one tap, weights small enough to stay in shared memory): a tile is 4
+    // rows of 32 positions of which the first 32-(S-1) are output pixels; its input patch, halo included, is loaded ONCE
+    // per channel block and every tap reads it through a row-shifted descriptor, instead of one displaced copy per tap.
+    // It pays when operand delivery bounds the layer (few channels: short TMA box rows) and the wasted positions are few.
+    static const bool no_halo = getenv("B200_NO_HALO") != nullptr;
+    {
+        const int64_t RW = 32, TWh = RW - (c->S - 1), THh = 4;
+        const int64_t tiles_h = ((Q + TWh - 1) / TWh) * ((P + THh - 1) / THh) * c->N;
+        const int64_t tiles_n = int64_t(p.tiles_q = int((Q + p.TW - 1) / p.TW)) * ((P + p.TH - 1) / p.TH) * ((c->N + p.TN - 1) / p.TN);
+        // the weights must stay resident: one column tile, all taps and channel blocks within the resident budget
+        const int bn_h = pick_bn(c->K, tiles_h, bk, epilogue && epilogue->sum_in);
+        const bool weights_fit = bn_h >= c->K && c->R * c->S * c->C * int64_t(bn_h) <= B_RESIDENT_MAX;
+        if (!no_halo && sh == 1 && sw == 1 && c->dilation_h == 1 && c->dilation_w == 1 && c->R * c->S > 1 && c->S <= 8 && weights_fit &&
+            c->C <= 128 && tiles_h * 10 <= tiles_n * 13)
+        {
+            p.halo = 1;
+            p.RW = int(RW);
+            p.TW = int(TWh);
+            p.TH = int(THh);
+            p.TN = 1;
+            p.halo_bytes = int(bk * RW * (THh + c->R - 1));
+            for (int r = 0; r < c->R; ++r)
+                for (int sx = 0; sx < c->S; ++sx)
+                    p.taps[r * c->S + sx].pad = short(r * RW + sx); // row shift of the tap inside the patch
+        }
+    }
+    if (!p.halo)
+        p.RW = p.TW;
     p.sub_w = p.TW < 32 ? p.TW : 32;
     p.sub_h = (p.TH < 32 / p.sub_w) ? p.TH : 32 / p.sub_w;
+    if (p.halo)
+        p.sub_h = 1;
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((c->N + p.TN - 1) / p.TN);
@@ -1581,6 +1665,11 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
                                 uint64_t(c->N)};
             uint64_t str[3] = {uint64_t(c->C) * sw, uint64_t(c->C) * c->W * sh, uint64_t(c->C) * c->W * c->H};
             uint32_t box[4] = {uint32_t(bk), uint32_t(p.TW), uint32_t(p.TH), uint32_t(p.TN)};
+            if (p.halo)
+            {
+                box[1] = uint32_t(p.RW);
+                box[2] = uint32_t(p.TH + c->R - 1);
+            }
             const uint8_t* base = static_cast<const uint8_t*>(data) + (int64_t(ph) * c->W + pw) * c->C;
             rc = make_map(&maps.a[ph * sw + pw], base, 4, dims, str, box, bk);
             if (rc != B200_OK)
@@ -1605,6 +1694,9 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
         uint64_t dims_o[4] = {uint64_t(c->K), uint64_t(Q), uint64_t(P), uint64_t(c->N)};
         uint64_t str_o[3] = {uint64_t(c->K), uint64_t(c->K) * Q, uint64_t(c->K) * Q * P};
         uint32_t box_o[4] = {uint32_t(COLS), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        if (p.halo)
+            box_o[3] = 1; // one row of TW output pixels per warp; the 32 - TW junk positions behind them are not stored
+        p.blk_bytes = int(box_o[1] * box_o[2] * box_o[3]) * COLS;
         make_out_maps(maps, p, 4, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));
@@ -1718,6 +1810,8 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
         uint64_t dims_o[4] = {uint64_t(K), uint64_t(Q), uint64_t(P), uint64_t(N)};
         uint64_t str_o[3] = {uint64_t(K), uint64_t(K) * Q, uint64_t(K) * Q * P};
         uint32_t box_o[4] = {uint32_t(COLS), uint32_t(p.sub_w), uint32_t(p.sub_h), uint32_t(32 / (p.sub_w * p.sub_h))};
+        p.blk_bytes = 32 * COLS;
+        p.RW = p.TW;
         make_out_maps(maps, p, 4, dims_o, str_o, box_o);
     }
     return dispatch_contract(bn, bk, maps, p, static_cast<cudaStream_t>(stream));

@@ -340,3 +340,36 @@ def test_stem_pack_with_fused_quantize(ops, q_np):
         check(LIB.b200_stem_pack_input_f32(xd.data_ptr(), scale.data_ptr(), zp.data_ptr(), 0 if q_np == np.uint8 else 1, mode,
                                            got.data_ptr(), n, c, h, w, 7, 7, 3, 3, 3, 3, st), "pack f32")
         assert torch.equal(got, want), "round mode %d" % mode
+
+
+HALO_CASES = [
+    # N, C, H, W, K, R, S, pad: stride 1, weights small enough to stay in shared memory -> the patch-with-halo path
+    (2, 64, 56, 56, 64, 3, 3, (1, 1)),    # BASELINE's layer geometry, small batch
+    (3, 64, 31, 45, 64, 3, 3, (1, 1)),    # ragged in both directions
+    (2, 64, 20, 33, 32, 3, 3, (0, 0)),    # no padding
+    (1, 128, 17, 64, 32, 3, 3, (1, 1)),   # 128-byte rows
+    (2, 64, 12, 40, 48, 5, 3, (2, 1)),    # 5 x 3 filter
+]
+
+
+@pytest.mark.parametrize("case", HALO_CASES, ids=lambda c: "x".join(str(v) for v in c[:7]))
+def test_qconv_halo_path_vs_oracle(ops, case):
+    n, c, h, w, k, r, s, pad = case
+    rng = np.random.default_rng(hash(case[:7]) & 0xFFFF)
+    data = rng.integers(0, 256, (n, c, h, w)).astype(np.uint8)
+    filt = rng.integers(-127, 128, (k, c, r, s)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, k).astype(np.int32)
+    cs = ref.conv_shape(data.shape, filt.shape, (1, 1), pad, pad)
+    scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), k)) * 60.0 / (np.sqrt(c * r * s) * 74 * 147)).astype(np.float32)
+    p, q = ref.conv_out_hw(cs)
+    exp = ref.qconv_fused(data, filt, bias, scale, cs, np.uint8, relu=True)
+    for packed in (False, True):
+        got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, packed=packed)
+        np.testing.assert_array_equal(got, exp, err_msg="packed=%d" % packed)
+    sum_u8 = rng.integers(0, 256, (n, k, p, q)).astype(np.uint8)
+    exp = ref.qconv_fused(data, filt, bias, scale, cs, np.uint8, relu=True, sum_in=sum_u8, sum_scale=np.float32(0.4))
+    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.4)
+    np.testing.assert_array_equal(got, exp, err_msg="residual")
+    exp = ref.qconv_core(data, filt, cs, 1.0, 0, 1.0, 0, 1.0, 0, np.int32)
+    got = run_conv(ops, data, filt, None, np.float32(1.0), cs, np.int32, False, core=True)
+    np.testing.assert_array_equal(got, exp, err_msg="core i32")
