@@ -249,6 +249,22 @@ class ResNet50:
                 "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)",
                 "slowest_nodes_us": [[round(u, 1), n] for u, n in top]}
 
+    def extra_cpu_baselines(self):
+        """The north star asks for nGraph's DNNL CPU backend beside the number; that backend cannot be built offline, so the
+        oneDNN int8 primitives inside PyTorch run the same network on the same host cores as a labelled proxy."""
+        try:
+            import torch
+            from ngraph_b200.harness.resnet50_int8 import OneDnnProxy
+            threads = os.cpu_count() or 1
+            torch.set_num_threads(threads)
+            rate = OneDnnProxy(self.model).images_per_second(batch=32, seconds=8.0)
+            return {"cpu_baseline_onednn_proxy": {
+                "value": rate, "unit": "img/s", "cores": threads, "kind": "proxy",
+                "sample": "the same int8 ResNet-50 through torch.ops.quantized (oneDNN %s engine), batch 32, 8 s; stands in for nGraph's "
+                          "CPU backend (DNNL), which needs downloaded dependencies to build" % torch.backends.quantized.engine}}
+        except Exception as e:  # a baseline that cannot run is reported, never fatal
+            return {"cpu_baseline_onednn_proxy": {"unavailable": str(e)[:200]}}
+
     def check_and_cpu_baseline(self, skip_cpu):
         """INTERPRETER on an image strip: timing for cpu_baseline and the parity check of the B200 output"""
         if skip_cpu:
@@ -647,6 +663,9 @@ def main():
         line["parity_vs_oracle"] = ok
         if cpu is not None:
             line["cpu_baseline"] = cpu
+            extra = wl.extra_cpu_baselines() if hasattr(wl, "extra_cpu_baselines") else None
+            if extra:
+                line.update(extra)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

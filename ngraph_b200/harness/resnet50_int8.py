@@ -207,3 +207,65 @@ class QuantizedResNet50:
         if intermediate_results:  # stem, maxpool, the 16 block outputs, pooled features, i8 logits, f32 logits
             return ng.Function(taps + [pooled, logits, out], [x]), x
         return ng.Function([out], [x]), x
+
+
+class OneDnnProxy:
+    """The same int8 ResNet-50 (weights, per-channel weight scales, calibrated activation scales) on the host cores through
+    the oneDNN int8 primitives that ship inside PyTorch (torch.ops.quantized.* with the 'onednn' engine).
+
+    nGraph's own CPU backend drives the same library family (DNNL int8 convolution_forward / inner_product with output
+    scales, sum and ReLU post-ops: src/ngraph/runtime/cpu/builder/quantized_conv.cpp, dnnl_emitter.hpp) but cannot be
+    built without its downloaded dependencies, so this stands in for it as a TIMING baseline only: the residual add is a
+    separate quantized add here and activations are uint8 with zero point 128 where the nGraph graph uses int8, so
+    results are close to, not identical with, the reference's."""
+
+    def __init__(self, model):
+        import torch
+        torch.backends.quantized.engine = "onednn"
+        self.torch, self.model = torch, model
+        self.packed = {}
+        for name, L in model.layers.items():
+            w = torch.from_numpy(L["w_q"].astype(np.float32) * L["s_w"][:, None, None, None])
+            qw = torch.quantize_per_channel(w, torch.from_numpy(L["s_w"].astype(np.float64)), torch.zeros(L["cout"], dtype=torch.int64),
+                                            0, torch.qint8)
+            self.packed[name] = torch.ops.quantized.conv2d_prepack(qw, torch.from_numpy(L["bias_f"]), [L["stride"]] * 2,
+                                                                   [L["pad"]] * 2, [1, 1], 1)
+        fc = torch.from_numpy(model.fc_q.T.astype(np.float32) * float(model.s_fc)).contiguous()
+        self.fc = torch.ops.quantized.linear_prepack(torch.quantize_per_tensor(fc, float(model.s_fc), 0, torch.qint8), None)
+
+    def forward(self, x):
+        torch, m = self.torch, self.model
+        q = torch.ops.quantized
+        a = torch.quantize_per_tensor(torch.from_numpy(x), float(m.s_input), 128, torch.quint8).contiguous(memory_format=torch.channels_last)
+
+        def conv(name, inp, relu=None):
+            L = m.layers[name]
+            relu = L["relu"] if relu is None else relu
+            if relu:
+                return q.conv2d_relu(inp, self.packed[name], float(L["s_out"]), 0)
+            return q.conv2d(inp, self.packed[name], float(L["s_out"]), 128)
+
+        a = conv("stem", a)
+        a = torch.nn.functional.max_pool2d(a, 3, 2, 1)
+        for si, (blocks, mid, cout, stride) in enumerate(STAGES):
+            for b in range(blocks):
+                pre = "s%db%d" % (si + 1, b)
+                short = conv(pre + "_down", a) if b == 0 else a
+                y = conv(pre + "_c1", a)
+                y = conv(pre + "_c2", y)
+                L = m.layers[pre + "_c3"]
+                y = conv(pre + "_c3", y, relu=False)
+                a = q.add_relu(y, short, float(L["s_out"]), 0)
+        pooled = torch.nn.functional.adaptive_avg_pool2d(a, 1).flatten(1)
+        logits = q.linear(pooled, self.fc, float(m.s_logits), 128)
+        return logits.dequantize().numpy()
+
+    def images_per_second(self, batch=16, seconds=8.0):
+        import time
+        x = synthetic_images(batch, 5, self.model.image_size)
+        self.forward(x)
+        t0, n = time.time(), 0
+        while time.time() - t0 < seconds:
+            self.forward(x)
+            n += batch
+        return n / (time.time() - t0)
