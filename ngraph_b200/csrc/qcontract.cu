@@ -675,12 +675,17 @@ namespace b200
                         // shared-memory address bits, the same bits the TMA unit used when it wrote the patch.
                         for (int cb = 0; cb < p.cblocks; ++cb)
                         {
-                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
                             {
-                                fail = 2002;
-                                break;
+                                PROF_T0();
+                                if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
+                                {
+                                    fail = 2002;
+                                    break;
+                                }
+                                PROF_ADD(1);
                             }
                             ptx::tc_fence_after_sync();
+                            PROF_MARK(t_issue0);
                             const uint32_t stage_addr = smem_base + uint32_t(s) * stage_bytes;
                             for (int tap = 0; tap < p.ntaps; ++tap)
                             {
@@ -693,6 +698,10 @@ namespace b200
                                                 (cb | tap | k) != 0 ? 1u : 0u);
                             }
                             ptx::mma_commit(empty_bar(s));
+#ifdef B200_PROFILE_WAITS
+                            if (blockIdx.x == 0)
+                                atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[7]), (unsigned long long)(clock64() - t_issue0));
+#endif
                             if (++s == STAGES)
                             {
                                 s = 0;
