@@ -103,6 +103,7 @@ namespace b200
         int cells_w, cells_h;   // its row length and row count per image, in cells
         const int8_t* b_packed; // weights in the block image made by b200_pack_weights_host (null: plain [N,K] matrix through maps.b)
         int b_blocks_n;      // 64-row blocks per k-block in that image: ceil(N / 64)
+        int f32_staged;      // f32 output, regular shape: transposed through the staging blocks for coalesced stores
         int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
         int vec_params;      // scale / bias pointers are 16-byte aligned
         void* out;
@@ -808,9 +809,11 @@ namespace b200
             // MODE -1 is the general loop (any contract, type and width).
             auto epilogue_loop = [&](auto mode_tag) {
                 constexpr int MODE = decltype(mode_tag)::value;
-                constexpr bool FAST = MODE >= 0;
+                // MODE 9 / 10: f32 output without / with ReLU, no residual, width a multiple of 64: stored from registers
+                constexpr bool F_F32 = MODE >= 9;
+                constexpr bool FAST = MODE >= 0 && !F_F32; // the one-byte modes, staged and stored by TMA
                 constexpr int F_SUMK = FAST ? MODE % 3 : 0;
-                constexpr bool F_SUM = F_SUMK != 0, F_RELU = MODE >= 6, F_U8 = MODE >= 0 && MODE < 3;
+                constexpr bool F_SUM = F_SUMK != 0, F_RELU = MODE >= 6 && MODE != 9, F_U8 = MODE >= 0 && MODE < 3;
                 constexpr int NBUF = F_SUM ? 3 : 2; // staging blocks per warp
                 int staged_tn = -1;
                 int blk = 0;             // staging block of the current tile: j % NBUF
@@ -880,7 +883,7 @@ namespace b200
                             }
                         }
                     }
-                    else if (j >= 2)
+                    else if (j >= 2 && !F_F32)
                     {
                         // the TMA store issued two tiles ago must have finished reading this staging block
                         if (ptx::elect_one())
@@ -905,7 +908,7 @@ namespace b200
                     er.off = 0;
                     // is the first row of this warp's 32-row block inside the tensor (else the whole block is outside)
                     bool blk_valid;
-                    const bool rows = FAST ? false : need_rows;
+                    const bool rows = FAST ? false : (F_F32 ? true : need_rows);
                     if (p.conv)
                     {
                         blk_valid = q0 + blk_w < p.Q && p0 + blk_h < p.P && n0 + blk_n < p.NB;
@@ -930,7 +933,7 @@ namespace b200
                     // waiting for the MMAs.  Rows outside the tensor and columns beyond the width compute on a zero
                     // residual and are never stored.
                     uint32_t sumw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    const bool sum_regs = !FAST && has_sum && vec_ok && er.valid;
+                    const bool sum_regs = !FAST && !F_F32 && has_sum && vec_ok && er.valid;
                     auto fetch_sum = [&](int c) {
                         if (sum_regs && colw + 32 * c + 32 <= p.N)
                         {
@@ -940,7 +943,7 @@ namespace b200
                             sumw[4] = s1.x; sumw[5] = s1.y; sumw[6] = s1.z; sumw[7] = s1.w;
                         }
                     };
-                    if (!FAST)
+                    if (!FAST && !F_F32)
                         fetch_sum(0);
                     {
                         PROF_T0();
@@ -965,7 +968,56 @@ namespace b200
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(piece(c, 0)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(piece(c, 1)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
                     };
-                    if (FAST)
+                    if (F_F32)
+                    {
+                        // 32 rows x 32 columns of f32 per chunk = 4 KB = this warp's two staging blocks.  Each lane writes its
+                        // row (16-byte pieces XOR-swizzled by the row against bank conflicts), then the warp reads the chunk
+                        // back transposed so that one store instruction covers 4 rows x 128 contiguous bytes.
+                        const uint32_t f32_blk = out_base + uint32_t(ew) * 4096u;
+                        float* const obase = static_cast<float*>(p.out);
+                        const int my_row_ok = er.valid ? 1 : 0;
+#pragma unroll
+                        for (int c = 0; c < CHUNKS; ++c)
+                        {
+                            uint32_t v[32];
+                            ptx::tmem_ld_32x32(t_addr + 32 * c, v);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; ++j4)
+                            {
+                                const float4 s4 = lds_f4(sc_base + 128u * c + 16 * j4);
+                                const int4 b4 = lds_i4(bi_base + 128u * c + 16 * j4);
+                                const float a0 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 0]), b4.x, p.one));
+                                const float a1 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 1]), b4.y, p.one));
+                                const float a2 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 2]), b4.z, p.one));
+                                const float a3 = __int2float_rn(add_fma_pipe(int32_t(v[4 * j4 + 3]), b4.w, p.one));
+                                F2 r01 = unpack_f2(mul2(pack_f2(a0, a1), pack_f2(s4.x, s4.y)));
+                                F2 r23 = unpack_f2(mul2(pack_f2(a2, a3), pack_f2(s4.z, s4.w)));
+                                if (F_RELU)
+                                {
+                                    r01.x = fmaxf(r01.x, 0.0f);
+                                    r01.y = fmaxf(r01.y, 0.0f);
+                                    r23.x = fmaxf(r23.x, 0.0f);
+                                    r23.y = fmaxf(r23.y, 0.0f);
+                                }
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(f32_blk + uint32_t(lane) * 128u + (uint32_t(j4 ^ (lane & 7)) << 4)),
+                                             "f"(r01.x), "f"(r01.y), "f"(r23.x), "f"(r23.y) : "memory");
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                            {
+                                const int rr = 4 * i + (lane >> 3), jj = lane & 7;
+                                const long long roff = __shfl_sync(0xffffffffu, static_cast<long long>(er.off), rr);
+                                const int rok = __shfl_sync(0xffffffffu, my_row_ok, rr);
+                                const float4 val = lds_f4(f32_blk + uint32_t(rr) * 128u + (uint32_t(jj ^ (rr & 7)) << 4));
+                                if (rok && colw < p.N)
+                                    *reinterpret_cast<float4*>(obase + roff + colw + 32 * c + 4 * jj) = val;
+                            }
+                            __syncwarp();
+                        }
+                    }
+                    else if (FAST)
                     {
 #pragma unroll
                         for (int c = 0; c < CHUNKS; ++c)
@@ -1074,7 +1126,7 @@ namespace b200
                     __syncwarp();
                     if (ptx::elect_one())
                         ptx::mbar_arrive(tempty_bar(acc));
-                    if (FAST || p.tma_store)
+                    if (FAST || (!F_F32 && p.tma_store))
                     {
                         // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
                         // rows / columns that fall outside the output tensor are clipped by the TMA unit
@@ -1107,8 +1159,11 @@ namespace b200
                 }
             };
             const bool fast_ok = bytes_variant >= 0 && p.tma_store && p.N % COLS == 0 && (!has_sum || p.tma_sum);
-            switch (fast_ok ? bytes_variant : -1)
+            const bool f32_ok = p.f32_staged != 0 && p.smem.out_bufs == 2;
+            switch (fast_ok ? bytes_variant : f32_ok ? (p.relu ? 10 : 9) : -1)
             {
+            case 9: epilogue_loop(std::integral_constant<int, 9>{}); break;
+            case 10: epilogue_loop(std::integral_constant<int, 10>{}); break;
             case 0: epilogue_loop(std::integral_constant<int, 0>{}); break;
             case 1: epilogue_loop(std::integral_constant<int, 1>{}); break;
             case 2: epilogue_loop(std::integral_constant<int, 2>{}); break;
@@ -1267,7 +1322,7 @@ namespace b200
         p.tma_sum = p.tma_sum && p.tma_store && p.sum_in && !p.half_away && p.N % COLS == 0;
         if (p.tma_sum && (room - 3 * C::OUT_BYTES) / sp.stage_bytes < 2)
             p.tma_sum = 0;
-        sp.out_bufs = p.tma_store ? (p.tma_sum ? 3 : 2) : 0;
+        sp.out_bufs = p.tma_store ? (p.tma_sum ? 3 : 2) : (p.f32_staged ? 2 : 0);
         sp.out_bytes = sp.out_bufs * C::OUT_BYTES;
         int fit = (room - sp.out_bytes) / sp.stage_bytes;
         sp.stages = fit > MAX_STAGES ? MAX_STAGES : fit;
@@ -1342,6 +1397,8 @@ namespace b200
         p.vec_params = ((reinterpret_cast<uintptr_t>(e->scale) | reinterpret_cast<uintptr_t>(e->bias)) & 15) == 0;
         const bool one_byte = e->out_type == B200_U8 || e->out_type == B200_I8;
         p.tma_store = one_byte && (p.N % 16 == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        p.f32_staged = e->out_type == B200_F32 && !e->round_half_away && !e->sum_in && (p.N % COLS == 0) &&
+                       (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         (void)a_type;
     }
 
