@@ -377,6 +377,9 @@ B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const in
  *                        output axis i is input axis order[i]
  *   b200_reduce_f32      op::v0::Sum (Kahan-compensated, sum.hpp:56-90) and op::v0::Max (max.hpp:32-58) over an axis set,
  *                        inputs taken in row-major order like the reference
+ *   b200_softmax_rows_f32 op::v0::Softmax over the last axis of a [rows, row_elements] matrix (softmax.hpp: max, exp(x - max),
+ *                        Kahan sum, divide -- the same values as those five ops run one after another); rows longer
+ *                        than 1535 elements return B200_ERR_UNSUPPORTED
  *   b200_bmm_f32         op::v0::BatchMatMul / 2-D op::v0::Dot on f32 (batch_mat_mul.hpp, dot.hpp:108-160): a[b,M,K] x
  *                        b[b,K,N], the sum over k in double, in order, rounded to float once
  *   b200_gather_rows_b32 op::v0::Gather with axis 0 on a 2-D table of 4-byte elements and an i32 / i64 index vector
@@ -411,6 +414,7 @@ B200_API int b200_broadcast_b32(const void* in, void* out, const int64_t* out_sh
 B200_API int b200_permute_b32(const void* in, void* out, const int64_t* in_shape, int rank, const int64_t* order, void* stream);
 B200_API int b200_reduce_f32(int op, const float* in, float* out, const int64_t* shape, int rank, const int64_t* axes,
                              int n_axes, void* stream);
+B200_API int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, int64_t row_elements, void* stream);
 B200_API int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N,
                           void* stream);
 B200_API int b200_gather_rows_b32(const void* table, int64_t n_rows, int64_t row_elements, const void* indices, int index_type,

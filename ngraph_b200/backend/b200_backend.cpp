@@ -938,6 +938,17 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
                 red.push_back(os[i]);
         const int64_t n_red = int64_t(shape_size(red));
         int x = canonical_slot(node->input_value(0));
+        if (axes.size() == 1 && *axes.begin() == os.size() - 1 && os.back() >= 1 && os.back() <= 1535)
+        {
+            // the last axis of a matrix of rows: one kernel that keeps the rows in shared memory between the steps
+            const int64_t row = int64_t(os.back()), rows = n_out / row;
+            int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+            emit(node, "softmax_rows", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_softmax_rows_f32(static_cast<const float*>(p[x]), static_cast<float*>(p[y]), rows, row, st);
+            });
+            value_of(node->output(0)).canonical = y;
+            return true;
+        }
         int small = new_slot(Slot::ARENA, size_t(n_red) * 4), wide = new_slot(Slot::ARENA, size_t(n_out) * 4),
             e = new_slot(Slot::ARENA, size_t(n_out) * 4), y = new_slot(Slot::ARENA, size_t(n_out) * 4);
         std::vector<int64_t> shape(os.begin(), os.end());

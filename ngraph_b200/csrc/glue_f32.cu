@@ -168,23 +168,199 @@ namespace b200
         }
     }
 
-    // out[b, m, n] = float(sum_k double(a[b, m, k]) * double(b[b, k, n])), k ascending
-    __global__ void __launch_bounds__(256) bmm_f32_kernel(const float* __restrict__ a, const float* __restrict__ bm,
+    // Whole-tensor max (one output): many blocks, each over a contiguous slice, combined with an atomic on the ordered
+    // integer image of the float (non-negative floats order like signed ints, negative ones like reversed unsigned
+    // ints).  NaNs never win, as in the reference loop; the output must hold -inf on entry.
+    __global__ void __launch_bounds__(256) reduce_max_all_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n)
+    {
+        __shared__ float partial[8];
+        float m = -INFINITY;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const float x = in[i];
+            if (x > m)
+                m = x;
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1)
+        {
+            const float o = __shfl_xor_sync(0xffffffffu, m, d);
+            if (o > m)
+                m = o;
+        }
+        if ((threadIdx.x & 31) == 0)
+            partial[threadIdx.x >> 5] = m;
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            for (int w = 1; w < 8; ++w)
+                if (partial[w] > m)
+                    m = partial[w];
+            if (m >= 0.0f)
+                atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+            else if (m > -INFINITY)
+                atomicMin(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+        }
+    }
+
+    __global__ void fill_f32_kernel(float* out, float value, int64_t n)
+    {
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+            out[i] = value;
+    }
+
+    // One step of the reference's compensated sum (runtime/reference/sum.hpp:56-90).
+    __device__ __forceinline__ void kahan_step(float& z, float& c, float x)
+    {
+        if (isfinite(x) && isfinite(z))
+        {
+            const float y = __fsub_rn(x, c);
+            const float t = __fadd_rn(z, y);
+            c = __fsub_rn(__fsub_rn(t, z), y);
+            z = t;
+        }
+        else
+            z = __fadd_rn(z, x);
+    }
+
+    // Reductions and Softmax over the LAST axis of a [rows, L] matrix.  The compensated sum has to walk a row in order,
+    // so a row belongs to one thread; reading it straight from memory would make the 32 lanes of a warp touch 32
+    // different rows per load.  A block therefore stages 32 rows in shared memory with coalesced loads (row stride
+    // odd, so the lanes' walks hit different banks), lets all its threads do the order-free parts (max, exp, divide)
+    // and one warp the 32 ordered sums.
+    constexpr int ROWS_PER_TILE = 32;
+    __host__ __device__ inline int staged_row_stride(int L) { return L | 1; }
+
+    template <bool SOFTMAX>
+    __global__ void __launch_bounds__(128) staged_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int L)
+    {
+        extern __shared__ float tile[];
+        __shared__ float row_max[ROWS_PER_TILE], row_sum[ROWS_PER_TILE];
+        const int stride = staged_row_stride(L);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int64_t n_tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
+        for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x)
+        {
+            const int64_t row0 = t * ROWS_PER_TILE;
+            const int n_rows = int(rows - row0 < ROWS_PER_TILE ? rows - row0 : ROWS_PER_TILE);
+            const float* src = in + row0 * L;
+            for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                tile[(i / L) * stride + i % L] = src[i];
+            __syncthreads();
+            if (SOFTMAX)
+            {
+                // softmax.hpp: max over the axis (the largest value whatever the order), then exp(x - max)
+                for (int r = warp; r < n_rows; r += 4)
+                {
+                    float m = -INFINITY;
+                    for (int c = lane; c < L; c += 32)
+                    {
+                        const float x = tile[r * stride + c];
+                        m = x > m ? x : m;
+                    }
+                    for (int d = 16; d; d >>= 1)
+                    {
+                        const float o = __shfl_xor_sync(0xFFFFFFFFu, m, d);
+                        m = o > m ? o : m;
+                    }
+                    if (lane == 0)
+                        row_max[r] = m;
+                }
+                __syncthreads();
+                for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                {
+                    const int r = i / L;
+                    float& v = tile[r * stride + i % L];
+                    v = static_cast<float>(exp(static_cast<double>(__fsub_rn(v, row_max[r]))));
+                }
+                __syncthreads();
+            }
+            if (warp == 0 && lane < n_rows)
+            {
+                const float* row = tile + lane * stride;
+                float z = 0.0f, c = 0.0f;
+                for (int k = 0; k < L; ++k)
+                    kahan_step(z, c, row[k]);
+                if (SOFTMAX)
+                    row_sum[lane] = z;
+                else
+                    out[row0 + lane] = z;
+            }
+            __syncthreads();
+            if (SOFTMAX)
+            {
+                float* dst = out + row0 * L;
+                for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                {
+                    const int r = i / L;
+                    dst[i] = __fdiv_rn(tile[r * stride + i % L], row_sum[r]);
+                }
+                __syncthreads();
+            }
+        }
+    }
+
+    // Launch of the staged kernel; false when a tile of rows does not fit shared memory.
+    template <bool SOFTMAX>
+    bool launch_staged_rows(const float* in, float* out, int64_t rows, int64_t L, cudaStream_t st)
+    {
+        if (L < 1 || L > 1535)
+            return false;
+        const size_t bytes = size_t(ROWS_PER_TILE) * staged_row_stride(int(L)) * sizeof(float);
+        if (bytes > 48 * 1024 && // the attribute belongs to the current device's copy of the kernel: set it on each use
+            cudaFuncSetAttribute(staged_rows_kernel<SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return false;
+        const int64_t tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
+        const int64_t per_sm = (200 * 1024) / int64_t(bytes) < 8 ? (200 * 1024) / int64_t(bytes) : 8;
+        const int64_t grid = tiles < 148 * per_sm ? tiles : 148 * per_sm;
+        staged_rows_kernel<SOFTMAX><<<unsigned(grid), 128, bytes, st>>>(in, out, rows, int(L));
+        return true;
+    }
+
+    // out[b, m, n] = float(sum_k double(a[b, m, k]) * double(b[b, k, n])), k ascending.  One thread owns a 4 x 4 block
+    // of outputs, each with its own double accumulator walked in k order (so every output sees exactly the reference's
+    // sequence of additions); the block shares 4 + 4 operand loads per 16 multiply-adds.
+    __global__ void __launch_bounds__(128) bmm_f32_kernel(const float* __restrict__ a, const float* __restrict__ bm,
                                                           float* __restrict__ out, int64_t B, int M, int K, int N)
     {
-        const int64_t total = B * M * N;
+        const int tiles_n = (N + 3) / 4, tiles_m = (M + 3) / 4;
+        const int64_t total = B * tiles_m * tiles_n;
         for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
         {
-            const int n = int(i % N);
-            const int64_t t = i / N;
-            const int m = int(t % M);
-            const int64_t b = t / M;
-            const float* ap = a + (b * M + m) * K;
-            const float* bp = bm + b * K * N + n;
-            double sum = 0.0;
+            const int tn = int(i % tiles_n);
+            const int64_t t = i / tiles_n;
+            const int tm = int(t % tiles_m);
+            const int64_t b = t / tiles_m;
+            const int m0 = tm * 4, n0 = tn * 4;
+            const float* ap = a + (b * M + m0) * K;
+            const float* bp = bm + b * K * N + n0;
+            // rows / columns beyond the matrix read the last valid one (their results are not stored)
+            const int r1 = m0 + 1 < M ? 1 : 0, r2 = m0 + 2 < M ? 2 : r1, r3 = m0 + 3 < M ? 3 : r2;
+            const int c1 = n0 + 1 < N ? 1 : 0, c2 = n0 + 2 < N ? 2 : c1, c3 = n0 + 3 < N ? 3 : c2;
+            double acc[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    acc[r][c] = 0.0;
             for (int k = 0; k < K; ++k)
-                sum = __dadd_rn(sum, __dmul_rn(double(ap[k]), double(bp[int64_t(k) * N])));
-            out[i] = static_cast<float>(sum);
+            {
+                const double x0 = ap[k], x1 = ap[int64_t(r1) * K + k], x2 = ap[int64_t(r2) * K + k], x3 = ap[int64_t(r3) * K + k];
+                const float* brow = bp + int64_t(k) * N;
+                const double y0 = brow[0], y1 = brow[c1], y2 = brow[c2], y3 = brow[c3];
+                const double xs[4] = {x0, x1, x2, x3}, ys[4] = {y0, y1, y2, y3};
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        acc[r][c] = fma(xs[r], ys[c], acc[r][c]); // a product of two floats is exact in double: one rounding, like mul + add
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (m0 + r < M && n0 + c < N)
+                        out[(b * M + m0 + r) * N + n0 + c] = static_cast<float>(acc[r][c]);
         }
     }
 
@@ -382,13 +558,37 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
     if (!out || (!in && n_red > 0))
         return B200_ERR_INVALID_ARGUMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (op == B200_REDUCE_MAX && n_out <= 4096 && n_red >= 1024)
+    if (op == B200_REDUCE_MAX && n_out == 1 && n_red >= (int64_t(1) << 16))
+    {
+        // every axis reduced: the input is one contiguous run
+        fill_f32_kernel<<<1, 32, 0, st>>>(out, -INFINITY, 1);
+        reduce_max_all_kernel<<<grid_for(n_red / 4, 256), 256, 0, st>>>(in, out, n_red);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    else if (op == B200_REDUCE_MAX && n_out <= 4096 && n_red >= 1024)
         reduce_max_block_kernel<<<unsigned(n_out), 256, 0, st>>>(in, out, keep, red, n_red);
+    else if (op == B200_REDUCE_SUM && n_axes == 1 && axes[0] == rank - 1 && n_out >= 64 &&
+             launch_staged_rows<false>(in, out, n_out, n_red, st))
+        ; // the last axis of a matrix with many rows: staged through shared memory
     else if (op == B200_REDUCE_SUM)
         reduce_kernel<true><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     else
         reduce_kernel<false><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     return after_launch("b200_reduce_f32");
+}
+
+extern "C" int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, int64_t row_elements, void* stream)
+{
+    using namespace b200;
+    if (rows < 0 || row_elements < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (rows * row_elements == 0)
+        return B200_OK;
+    if (!x || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (!launch_staged_rows<true>(x, out, rows, row_elements, static_cast<cudaStream_t>(stream)))
+        return B200_ERR_UNSUPPORTED; // a row too long to stage: the caller composes the five steps instead
+    return after_launch("b200_softmax_rows_f32");
 }
 
 extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N, void* stream)
@@ -400,8 +600,8 @@ extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t 
         return B200_OK;
     if (!out || (K > 0 && (!a || !b)))
         return B200_ERR_INVALID_ARGUMENT;
-    bmm_f32_kernel<<<grid_for(batch * M * N, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, batch, int(M), int(K),
-                                                                                                 int(N));
+    const int64_t blocks4 = batch * ((M + 3) / 4) * ((N + 3) / 4);
+    bmm_f32_kernel<<<grid_for(blocks4, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, batch, int(M), int(K), int(N));
     return after_launch("b200_bmm_f32");
 }
 

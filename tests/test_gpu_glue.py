@@ -80,7 +80,8 @@ def kahan_sum_rows(x):
     return z
 
 
-@pytest.mark.parametrize("shape,axes", [((37, 768), (1,)), ((6, 5, 384), (2,)), ((9, 33, 7), (0, 2)), ((50000,), (0,)), ((4, 3), ())])
+@pytest.mark.parametrize("shape,axes", [((37, 768), (1,)), ((6, 5, 384), (2,)), ((9, 33, 7), (0, 2)), ((50000,), (0,)), ((4, 3), ()),
+                                        ((300, 1000), (0, 1)), ((200, 768), (1,)), ((70, 3, 33), (2,)), ((64, 1535), (1,))])
 def test_sum_and_max_follow_the_reference_order(L, shape, axes):
     rng = np.random.default_rng(2)
     x = (rng.standard_normal(shape) * 100).astype(np.float32)
@@ -93,6 +94,32 @@ def test_sum_and_max_follow_the_reference_order(L, shape, axes):
     for op, want in ((0, want_sum), (1, want_max)):
         L.check(L.LIB.b200_reduce_f32(op, xd.data_ptr(), out.data_ptr(), i64(shape), len(shape), i64(axes), len(axes), stream()), "reduce")
         np.testing.assert_array_equal(bits(out.cpu().numpy()[:want.size]), bits(want).ravel())
+
+
+@pytest.mark.parametrize("rows,n", [(100, 384), (65, 33), (3, 1535), (40, 1), (1000, 64)])
+def test_softmax_rows_equals_the_five_steps(L, rows, n):
+    """the fused last-axis Softmax against Max, Subtract, Exp, Sum, Divide run one after another (softmax.hpp)"""
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal((rows, n)) * 4).astype(np.float32)
+    x[0, 0] = np.inf if n > 1 else 1.0  # a row whose sum is not finite
+    xd = dev(x)
+    shape, last = i64([rows, n]), i64([1])
+    small = torch.empty(rows, device="cuda")
+    wide, e, want, got = (torch.empty((rows, n), device="cuda") for _ in range(4))
+    S = stream()
+    P = lambda t: t.data_ptr()
+    L.check(L.LIB.b200_reduce_f32(1, P(xd), P(small), shape, 2, last, 1, S), "max")
+    L.check(L.LIB.b200_broadcast_b32(P(small), P(wide), shape, 2, last, 1, S), "broadcast")
+    L.check(L.LIB.b200_f32_binary(OPS["sub"], P(xd), P(wide), P(e), x.size, S), "sub")
+    L.check(L.LIB.b200_f32_unary(OPS["exp"], P(e), P(e), x.size, S), "exp")
+    L.check(L.LIB.b200_reduce_f32(0, P(e), P(small), shape, 2, last, 1, S), "sum")
+    L.check(L.LIB.b200_broadcast_b32(P(small), P(wide), shape, 2, last, 1, S), "broadcast")
+    L.check(L.LIB.b200_f32_binary(OPS["div"], P(e), P(wide), P(want), x.size, S), "div")
+    L.check(L.LIB.b200_softmax_rows_f32(P(xd), P(got), rows, n, S), "softmax")
+    w, g = want.cpu().numpy(), got.cpu().numpy()
+    np.testing.assert_array_equal(np.isnan(w), np.isnan(g))
+    np.testing.assert_array_equal(bits(np.nan_to_num(g)), bits(np.nan_to_num(w)))
+    assert abs(float(g[1:].sum()) - (rows - 1)) < 1e-3 * rows
 
 
 def test_broadcast_and_permute(L):
