@@ -255,6 +255,13 @@ B200_API int b200_nhwc_to_nchw_u8(const void* in, void* out, int64_t N, int64_t 
 /* Channels-last [N,HW,C] -> [N,C,HW] for 4-byte elements (int32 / f32 outputs of the convolution). */
 B200_API int b200_nhwc_to_nchw_b32(const void* in, void* out, int64_t N, int64_t C, int64_t HW, void* stream);
 
+/*
+ * One operand of op::v0::Concat (runtime/reference/concat.hpp): `rows` dense rows of row_bytes bytes written to rows
+ * dst_pitch_bytes apart.  For axis a of a row-major tensor, rows = the product of the axes before a and row_bytes =
+ * the operand's elements from axis a on; the caller offsets dst by the bytes of the operands already placed.
+ */
+B200_API int b200_copy_rows(const void* src, void* dst, int64_t rows, int64_t row_bytes, int64_t dst_pitch_bytes, void* stream);
+
 /* Transpose a row-major [rows, cols] 1-byte matrix (B [K,N] of QuantizedDot -> W [N,K]). */
 B200_API int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_t cols, void* stream);
 

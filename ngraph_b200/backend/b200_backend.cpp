@@ -21,6 +21,8 @@
 #include <sstream>
 
 #include "b200_kernels.h"
+#include "quant_fusion.hpp"
+#include "ngraph/op/concat.hpp"
 #include "ngraph/descriptor/layout/dense_tensor_layout.hpp"
 #include "ngraph/except.hpp"
 #include "ngraph/graph_util.hpp"
@@ -427,7 +429,7 @@ bool B200Backend::is_supported(const Node& node) const
            is_type<op::v0::Exp>(&node) || is_type<op::v0::Erf>(&node) || is_type<op::v0::Relu>(&node) ||
            is_type<op::v0::Broadcast>(&node) || is_type<op::v0::Sum>(&node) || is_type<op::v0::Max>(&node) ||
            is_type<op::v0::Softmax>(&node) || is_type<op::v0::BatchMatMul>(&node) || is_type<op::v0::Dot>(&node) ||
-           is_type<op::v0::Gather>(&node);
+           is_type<op::v0::Gather>(&node) || is_type<op::v0::Concat>(&node);
 }
 
 extern "C" B200_BACKEND_API void ngraph_register_b200_backend()
@@ -607,6 +609,34 @@ bool B200Executable::avgpool_head_member(const Node* node)
     return false;
 }
 
+// The graph-level pipeline of compile(): what nGraph's backends run before they lower (cpu_external_function.cpp:1289-1335
+// keeps the CPU backend's list), with the plugin's own quantisation fusion in the place CPUQuantFusion has there.
+static void run_graph_passes(const std::shared_ptr<Function>& function)
+{
+    ngraph::pass::Manager pm;
+    pm.register_pass<ngraph::pass::LikeReplacement>();
+    pm.register_pass<ngraph::pass::FusedOpDecomposition>();
+    if (ngraph::runtime::b200::pass::quant_fusion_enabled())
+        pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
+    pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind
+    pm.run_passes(function);
+}
+
+// For tests and tools: applies compile()'s graph passes to *function (a std::shared_ptr<ngraph::Function>*) in place,
+// without touching a device.  Returns 0, or -1 if a pass threw.
+extern "C" B200_BACKEND_API int b200_backend_run_graph_passes(void* function)
+{
+    try
+    {
+        run_graph_passes(*static_cast<std::shared_ptr<Function>*>(function));
+        return 0;
+    }
+    catch (const std::exception&)
+    {
+        return -1;
+    }
+}
+
 B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
                                const std::shared_ptr<Function>& func,
                                bool enable_performance_data)
@@ -615,13 +645,7 @@ B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
 {
     m_ctx->make_current();
     m_function = clone_function(*func); // never mutate the caller's graph
-    {
-        pass::Manager pm;
-        pm.register_pass<pass::LikeReplacement>();
-        pm.register_pass<pass::FusedOpDecomposition>();
-        pm.register_pass<pass::ConstantFolding>();
-        pm.run_passes(m_function);
-    }
+    run_graph_passes(m_function);
 
     size_t pi = 0;
     for (auto& param : m_function->get_parameters())
@@ -825,6 +849,32 @@ void B200Executable::lower_node(const std::shared_ptr<Node>& node)
             return;
         }
         unsupported(*node, "Convert other than between i8 and u8");
+    }
+    if (auto cc = as_type_ptr<op::v0::Concat>(node))
+    {
+        // runtime/reference/concat.hpp on the row-major forms: each operand is a band of every output row
+        const Shape& os = node->get_output_shape(0);
+        const size_t axis = size_t(cc->get_concatenation_axis()), esz = node->get_output_element_type(0).size();
+        int64_t rows = 1, tail = 1;
+        for (size_t i = 0; i < axis; ++i) rows *= int64_t(os[i]);
+        for (size_t i = axis + 1; i < os.size(); ++i) tail *= int64_t(os[i]);
+        const int64_t pitch = int64_t(os[axis]) * tail * int64_t(esz);
+        std::vector<int> sources;
+        for (size_t i = 0; i < node->get_input_size(); ++i)
+            sources.push_back(canonical_slot(node->input_value(i)));
+        const int y = new_slot(Slot::ARENA, shape_size(os) * esz);
+        int64_t offset = 0;
+        for (size_t i = 0; i < sources.size(); ++i)
+        {
+            const int64_t band = int64_t(node->get_input_shape(i)[axis]) * tail * int64_t(esz);
+            const int x = sources[i];
+            emit(node, "concat", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_copy_rows(p[x], static_cast<char*>(p[y]) + offset, rows, band, pitch, st);
+            });
+            offset += band;
+        }
+        value_of(node->output(0)).canonical = y;
+        return;
     }
     if (compile_f32_glue(node))
         return;

@@ -72,13 +72,13 @@ def build_plugin(force=False):
     """g++ the nGraph backend plugin against nGraph's headers and libngraph.so.  Skipped (returns None)
     where nGraph's headers or library are not available: the prebuilt .so is used there."""
     inc = ngraph_include_dir()
-    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "b200_backend.hpp")]
+    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "quant_fusion.cpp", "b200_backend.hpp", "quant_fusion.hpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return PLUGIN_LIB if os.path.exists(PLUGIN_LIB) else None
     build_kernels()
     if not force and _newer(PLUGIN_LIB, src + [KERNEL_LIB]):
         return PLUGIN_LIB
-    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], "-o", PLUGIN_LIB,
+    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], src[1], "-o", PLUGIN_LIB,
            "-L" + HERE, "-lb200_kernels", "-L" + NGRAPH_LIB_DIR, "-lngraph", "-L/usr/local/cuda/lib64", "-lcudart_static",
            "-ldl", "-lrt", "-lpthread", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
     subprocess.check_call(cmd)

@@ -2,6 +2,8 @@
 // pooling glue of whole-graph inference.  All of them are plain HBM-bound byte movers.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace b200
 {
     constexpr int TT = 32; // transpose tile edge
@@ -201,6 +203,45 @@ extern "C" int b200_nhwc_to_nchw_u8(const void* in, void* out, int64_t N, int64_
     untranspose_bytes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), rows, cols, c_pad);
     return after_launch("b200_nhwc_to_nchw_u8");
+}
+
+namespace b200
+{
+    // rows of `row_bytes` bytes from a dense source into rows `dst_pitch` bytes apart: one operand of a Concat.
+    // V = 16: everything (pointers, row length, pitch) is a multiple of 16 bytes; V = 1: byte by byte.
+    template <int V>
+    __global__ void __launch_bounds__(256) copy_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
+                                                            int64_t row_units, int64_t dst_pitch_units)
+    {
+        using T = typename std::conditional<V == 16, uint4, uint8_t>::type;
+        const T* s = reinterpret_cast<const T*>(src);
+        T* d = reinterpret_cast<T*>(dst);
+        const int64_t total = rows * row_units;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+            d[(i / row_units) * dst_pitch_units + i % row_units] = s[i];
+    }
+}
+
+extern "C" int b200_copy_rows(const void* src, void* dst, int64_t rows, int64_t row_bytes, int64_t dst_pitch_bytes, void* stream)
+{
+    if (rows < 0 || row_bytes < 0 || dst_pitch_bytes < row_bytes)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (rows * row_bytes == 0)
+        return B200_OK;
+    if (!src || !dst)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool wide = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | uintptr_t(row_bytes) | uintptr_t(dst_pitch_bytes)) & 15) == 0;
+    const int64_t units = wide ? rows * (row_bytes / 16) : rows * row_bytes;
+    const int64_t blocks = (units + 255) / 256, cap = 148 * 16;
+    const unsigned grid = unsigned(blocks < cap ? blocks : cap);
+    if (wide)
+        b200::copy_rows_kernel<16><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, row_bytes / 16,
+                                                         dst_pitch_bytes / 16);
+    else
+        b200::copy_rows_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, row_bytes,
+                                                        dst_pitch_bytes);
+    return b200::after_launch("b200_copy_rows");
 }
 
 extern "C" int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_t cols, void* stream)

@@ -217,6 +217,15 @@ NGC_API void* ngc_avg_pool(void* x, const int64_t* win, const int64_t* stride)
     }, nullptr);
 }
 
+NGC_API void* ngc_concat(void** values, int n, int64_t axis)
+{
+    return guarded([&]() -> void* {
+        OutputVector parts;
+        for (int i = 0; i < n; ++i) parts.push_back(val(values[i]));
+        return box(std::make_shared<op::v0::Concat>(parts, axis));
+    }, nullptr);
+}
+
 NGC_API void* ngc_convert(void* x, int et)
 {
     return guarded([&]() -> void* { return box(std::make_shared<op::v0::Convert>(val(x), et_of(et))); }, nullptr);
@@ -282,6 +291,23 @@ NGC_API void* ngc_function(void** results, int n_results, void** params, int n_p
         return new std::shared_ptr<Function>(std::make_shared<Function>(rs, ps));
     }, nullptr);
 }
+// A copy of the Function after the graph passes a loaded plugin runs in compile(): `symbol` names the plugin's
+// exported pass runner (int f(std::shared_ptr<Function>*)), found among the libraries ngc_load_backend opened.
+NGC_API void* ngc_function_after_plugin_passes(void* function, const char* symbol)
+{
+    return guarded([&]() -> void* {
+        auto run = reinterpret_cast<int (*)(void*)>(dlsym(RTLD_DEFAULT, symbol));
+        if (!run) throw std::runtime_error(std::string("symbol not found: ") + symbol);
+        auto copy = new std::shared_ptr<Function>(clone_function(**static_cast<std::shared_ptr<Function>*>(function)));
+        if (run(copy) != 0)
+        {
+            delete copy;
+            throw std::runtime_error("the plugin's graph passes failed");
+        }
+        return copy;
+    }, nullptr);
+}
+
 NGC_API void ngc_function_free(void* f) { delete static_cast<std::shared_ptr<Function>*>(f); }
 
 NGC_API int ngc_function_op_count(void* f)

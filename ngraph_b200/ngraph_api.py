@@ -55,6 +55,8 @@ def capi():
             "ngc_function_op_count": (ci, [vp]),
             "ngc_bert_encoder": (vp, [ci] * 7 + [ctypes.c_uint64, ci]),
             "ngc_function_op_names": (ci, [vp, ci, ctypes.c_char_p, ci]),
+            "ngc_concat": (vp, [pvp, ci, i64]),
+            "ngc_function_after_plugin_passes": (vp, [vp, ctypes.c_char_p]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
             "ngc_tensor_create": (vp, [vp, ci, p64, ci]), "ngc_tensor_wrap": (vp, [vp, ci, p64, ci, vp]),
             "ngc_tensor_free": (None, [vp]),
@@ -208,6 +210,11 @@ def avg_pool(x, window, stride=(1, 1)):
     return Value(capi().ngc_avg_pool(x.h, _i64(window), _i64(stride)), "AvgPool")
 
 
+def concat(values, axis):
+    arr = (ctypes.c_void_p * len(values))(*[v.h for v in values])
+    return Value(capi().ngc_concat(arr, len(values), axis), "Concat")
+
+
 def convert(x, dtype):
     return Value(capi().ngc_convert(x.h, ET[np.dtype(dtype)]), "Convert")
 
@@ -271,6 +278,13 @@ def bert_encoder(layers, hidden, heads, ffn, seq, batch, vocab, seed=1, decompos
     h = capi().ngc_bert_encoder(layers, hidden, heads, ffn, seq, batch, vocab, seed, int(decomposed))
     m = batch * seq
     return BuiltFunction(h, [_Spec(np.int32, (m,)), _Spec(np.int32, (m,))], [_Spec(np.float32, (m, hidden))], "bert_encoder")
+
+
+def after_b200_passes(function):
+    """a copy of `function` after the graph passes the B200 plugin runs in compile() (quantisation fusion included);
+    needs load_b200() but no device"""
+    h = capi().ngc_function_after_plugin_passes(function.h, b"b200_backend_run_graph_passes")
+    return BuiltFunction(h, list(function.params), list(function.results), "after_b200_passes")
 
 
 def function_op_names(function, lowered=True):
