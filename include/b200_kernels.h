@@ -165,6 +165,9 @@ B200_API int b200_dequantize(const void* input,
  *       out = saturate( (OUT)roundf((float)acc * scale[0]) + out_zero_point )
  *   (the reference does not saturate: an out-of-range cast there is undefined behaviour).
  *
+ *   raw (round_half_away == 2): out = acc, int32, exact (out_type must be I32; scale, bias, sum_in and relu are not
+ *   used).  The first stage of contractions with non-zero zero points, see b200_requant_zero_points.
+ *
  * All float steps are separate IEEE operations (no fused multiply-add).
  */
 typedef struct b200_epilogue
@@ -176,7 +179,7 @@ typedef struct b200_epilogue
     int sum_type;          /* b200_dtype of sum_in: U8 or I8                          */
     const float* sum_scale;/* one element, device memory; required with sum_in        */
     int relu;              /* 0 / 1                                                   */
-    int round_half_away;   /* 0 = fused-op contract (RNE), 1 = core-op contract       */
+    int round_half_away;   /* 0 = fused-op contract (RNE), 1 = core-op contract, 2 = raw */
     int32_t out_zero_point;/* core contract only                                      */
     int out_type;          /* b200_dtype: U8, I8, I32 or F32                          */
 } b200_epilogue;
@@ -320,6 +323,38 @@ B200_API int b200_qgemm_packed(const void* A, int a_type, const int8_t* packed_w
                                int64_t K, const b200_epilogue* epilogue, void* stream);
 B200_API int b200_qconv_packed(const void* data, int data_type, const int8_t* packed_filters, void* out,
                                const b200_conv_params* c, const b200_epilogue* epilogue, void* stream);
+
+/*
+ * Non-zero input / filter zero points for op::v0::QuantizedConvolution and op::v0::QuantizedDot
+ * (src/ngraph/runtime/reference/convolution.hpp:236-258, dot.hpp:134-159): the reference multiplies (a - za) * (w - zw)
+ * over the taps inside the image.  On the device the contraction runs on the stored bytes with the raw epilogue
+ * (round_half_away == 2, int32 out) and one pass over those accumulators applies
+ *     acc = S - zw * (input window sum) - za * (filter sum over the valid taps) + (valid taps) * C * za * zw
+ * followed by the core requantisation (saturate((OUT)roundf((float)acc * scale[0]) + out_zero_point)).
+ *   b200_strided_sums         out[o*n_inner + i] = sum_c x[o*outer_stride + i*inner_stride + c*sum_stride], x u8 or i8: the
+ *                             filter's per-tap sums [K, R*S] from KCRS, the input's per-pixel channel sums [N, H*W] from
+ *                             NCHW, the row sums of A / column sums of B of a matrix product
+ *   b200_window_sums          per-pixel sums [N,H,W] -> per-output window sums [N,P,Q] (padding counts 0)
+ *   b200_requant_zero_points  acc [N,P,Q,K] int32 -> out [N,P,Q,K] of e->out_type (U8, I8, I32); e must be a core epilogue
+ *                             (round_half_away == 1, scale_count == 1).  filter_tap_sums [K,R,S] may be NULL when the
+ *                             input zero point is 0, window_sums [N,P,Q] when the filter zero point is 0.
+ * A matrix product [M,K] x [K,N] is the case N = 1, P = M, Q = 1, K = columns, H = M, W = 1, C = reduction length,
+ * R = S = 1, strides and dilations 1, padding 0.
+ */
+typedef struct b200_zero_point_params
+{
+    int64_t N, P, Q, K; /* accumulator / output extents, K (output channels) fastest */
+    int64_t H, W, C;    /* input image and channels per tap                          */
+    int64_t R, S;       /* filter window                                             */
+    int64_t stride_h, stride_w, dilation_h, dilation_w, pad_h, pad_w; /* padding below */
+    int32_t input_zero_point, filter_zero_point;
+} b200_zero_point_params;
+
+B200_API int b200_strided_sums(const void* x, int x_type, int32_t* out, int64_t n_outer, int64_t n_inner, int64_t n_sum,
+                               int64_t outer_stride, int64_t inner_stride, int64_t sum_stride, void* stream);
+B200_API int b200_window_sums(const int32_t* pixel_sums, int32_t* out, const b200_zero_point_params* z, void* stream);
+B200_API int b200_requant_zero_points(const int32_t* acc, const int32_t* filter_tap_sums, const int32_t* window_sums,
+                                      const b200_zero_point_params* z, const b200_epilogue* e, void* out, void* stream);
 
 /*
  * Stride-2 convolutions over <= 4 input channels (network stems, e.g. 7x7 stride 2 on RGB) on the tensor cores,

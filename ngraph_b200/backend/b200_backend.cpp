@@ -1428,6 +1428,21 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
     value_of(node->output(0)).nhwc = y;
 }
 
+// The value of a one-element u8 / i8 Constant (a per-tensor zero point); false for anything else.
+static bool scalar_zero_point(const Output<Node>& v, int32_t& value)
+{
+    auto c = as_type_ptr<op::v0::Constant>(v.get_node_shared_ptr());
+    if (!c || shape_size(c->get_output_shape(0)) != 1)
+        return false;
+    if (c->get_output_element_type(0) == element::u8)
+        value = *static_cast<const uint8_t*>(c->get_data_ptr());
+    else if (c->get_output_element_type(0) == element::i8)
+        value = *static_cast<const int8_t*>(c->get_data_ptr());
+    else
+        return false;
+    return true;
+}
+
 void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
 {
     auto op = as_type_ptr<op::v0::QuantizedConvolution>(node);
@@ -1439,8 +1454,9 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
         unsupported(*node, "data must be u8 and filters i8 or u8");
     if (ft == element::u8)
         dt |= B200_WEIGHTS_U8; // kind::i8 takes unsigned B operands as well
-    if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
-        unsupported(*node, "non-zero input / filter zero points");
+    int32_t za = 0, zf = 0;
+    if (!scalar_zero_point(node->input_value(3), za) || !scalar_zero_point(node->input_value(5), zf))
+        unsupported(*node, "input / filter zero points that are not per-tensor constants");
     auto zo = as_constant(node->input_value(7));
     if (!zo)
         unsupported(*node, "output zero point must be a constant");
@@ -1470,6 +1486,63 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
     b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
     const size_t esz = node->get_output_element_type(0).size();
     int y = new_slot(Slot::ARENA, shape_size(os) * esz);
+    if (za != 0 || zf != 0)
+    {
+        // (a - za) * (w - zf) over the taps inside the image: the contraction on the stored bytes with exact int32
+        // output, then one pass that subtracts the rank-one terms and requantises (zero_points.cu)
+        b200_zero_point_params z;
+        memset(&z, 0, sizeof(z));
+        z.N = int64_t(os[0]); z.K = int64_t(os[1]); z.P = int64_t(os[2]); z.Q = int64_t(os[3]);
+        z.H = int64_t(ds[2]); z.W = int64_t(ds[3]); z.C = int64_t(C); z.R = int64_t(fs[2]); z.S = int64_t(fs[3]);
+        z.stride_h = c.stride_h; z.stride_w = c.stride_w; z.dilation_h = c.dilation_h; z.dilation_w = c.dilation_w;
+        z.pad_h = c.pad_h; z.pad_w = c.pad_w;
+        z.input_zero_point = za; z.filter_zero_point = zf;
+        const int acc = new_slot(Slot::ARENA, shape_size(os) * 4);
+        emit(node, "qconv_raw", [=](const Ptrs& p, cudaStream_t st) {
+            b200_epilogue e;
+            memset(&e, 0, sizeof(e));
+            e.round_half_away = 2;
+            e.out_type = B200_I32;
+            return image ? b200_qconv_packed(p[x], dt, static_cast<const int8_t*>(p[w]), p[acc], &c, &e, st)
+                         : b200_qconv(p[x], dt, static_cast<const int8_t*>(p[w]), p[acc], &c, &e, st);
+        });
+        int taps = -1, windows = -1;
+        if (za != 0)
+        {
+            const int f = canonical_slot(node->input_value(1));
+            const int ft_code = ft == element::u8 ? B200_U8 : B200_I8;
+            taps = new_slot(Slot::ARENA, fs[0] * fs[2] * fs[3] * 4);
+            const int64_t K = fs[0], RS = fs[2] * fs[3], Cf = fs[1];
+            emit(node, "filter_tap_sums", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_strided_sums(p[f], ft_code, static_cast<int32_t*>(p[taps]), K, RS, Cf, Cf * RS, 1, RS, st);
+            });
+        }
+        if (zf != 0)
+        {
+            const int xc = canonical_slot(node->input_value(0));
+            const int pixels = new_slot(Slot::ARENA, ds[0] * ds[2] * ds[3] * 4);
+            windows = new_slot(Slot::ARENA, os[0] * os[2] * os[3] * 4);
+            const int64_t N = ds[0], HW = ds[2] * ds[3], Ci = C;
+            emit(node, "pixel_sums", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_strided_sums(p[xc], B200_U8, static_cast<int32_t*>(p[pixels]), N, HW, Ci, Ci * HW, 1, HW, st);
+            });
+            emit(node, "window_sums", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_window_sums(static_cast<const int32_t*>(p[pixels]), static_cast<int32_t*>(p[windows]), &z, st);
+            });
+        }
+        emit(node, "requant_zero_points", [=](const Ptrs& p, cudaStream_t st) {
+            b200_epilogue e;
+            memset(&e, 0, sizeof(e));
+            e.scale = static_cast<const float*>(p[scale]);
+            e.scale_count = 1;
+            e.round_half_away = 1;
+            e.out_zero_point = out_zp;
+            e.out_type = out_t;
+            return b200_requant_zero_points(static_cast<const int32_t*>(p[acc]), taps >= 0 ? static_cast<const int32_t*>(p[taps]) : nullptr,
+                                            windows >= 0 ? static_cast<const int32_t*>(p[windows]) : nullptr, &z, &e, p[y], st);
+        });
+    }
+    else
     emit(node, "qconv_core", [=](const Ptrs& p, cudaStream_t st) {
         b200_epilogue e;
         memset(&e, 0, sizeof(e));
@@ -1554,8 +1627,9 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
     const int operands = B200_U8 | (bt == element::u8 ? B200_WEIGHTS_U8 : 0);
     if (as.size() != 2 || bs.size() != 2 || op->get_reduction_axes_count() != 1 || as[1] % 16 != 0)
         unsupported(*node, "2-D operands with a reduction length that is a multiple of 16");
-    if (!constant_zero(node->input_value(3)) || !constant_zero(node->input_value(5)))
-        unsupported(*node, "non-zero input zero points");
+    int32_t za = 0, zb = 0;
+    if (!scalar_zero_point(node->input_value(3), za) || !scalar_zero_point(node->input_value(5), zb))
+        unsupported(*node, "input zero points that are not per-tensor constants");
     auto zo = as_constant(node->input_value(7));
     if (!zo)
         unsupported(*node, "output zero point must be a constant");
@@ -1591,6 +1665,53 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
         emit(node, "transpose_b", [=](const Ptrs& p, cudaStream_t st) { return b200_transpose_u8(p[b], p[w], K, N, st); });
     }
     int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * node->get_output_element_type(0).size());
+    if (za != 0 || zb != 0)
+    {
+        // sum_k (a - za) * (b - zb) = A.B - zb * rowsum(A) - za * colsum(B) + K * za * zb (zero_points.cu)
+        b200_zero_point_params z;
+        memset(&z, 0, sizeof(z));
+        z.N = 1; z.P = M; z.Q = 1; z.K = N; z.H = M; z.W = 1; z.C = K; z.R = z.S = 1;
+        z.stride_h = z.stride_w = z.dilation_h = z.dilation_w = 1;
+        z.input_zero_point = za; z.filter_zero_point = zb;
+        const int acc = new_slot(Slot::ARENA, size_t(M) * N * 4);
+        emit(node, "qgemm_raw", [=](const Ptrs& p, cudaStream_t st) {
+            b200_epilogue e;
+            memset(&e, 0, sizeof(e));
+            e.round_half_away = 2;
+            e.out_type = B200_I32;
+            return w_image ? b200_qgemm_packed(p[a], operands, static_cast<const int8_t*>(p[w]), p[acc], M, N, K, &e, st)
+                           : b200_qgemm(p[a], operands, static_cast<const int8_t*>(p[w]), p[acc], M, N, K, &e, st);
+        });
+        int cols = -1, rows = -1;
+        if (za != 0)
+        {
+            const int b = canonical_slot(node->input_value(1)); // B as the graph has it: [K, N]
+            const int bt_code = bt == element::u8 ? B200_U8 : B200_I8;
+            cols = new_slot(Slot::ARENA, size_t(N) * 4);
+            emit(node, "column_sums", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_strided_sums(p[b], bt_code, static_cast<int32_t*>(p[cols]), N, 1, K, 1, 0, N, st);
+            });
+        }
+        if (zb != 0)
+        {
+            rows = new_slot(Slot::ARENA, size_t(M) * 4);
+            emit(node, "row_sums", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_strided_sums(p[a], B200_U8, static_cast<int32_t*>(p[rows]), M, 1, K, K, 0, 1, st);
+            });
+        }
+        emit(node, "requant_zero_points", [=](const Ptrs& p, cudaStream_t st) {
+            b200_epilogue e;
+            memset(&e, 0, sizeof(e));
+            e.scale = static_cast<const float*>(p[scale]);
+            e.scale_count = 1;
+            e.round_half_away = 1;
+            e.out_zero_point = out_zp;
+            e.out_type = out_t;
+            return b200_requant_zero_points(static_cast<const int32_t*>(p[acc]), cols >= 0 ? static_cast<const int32_t*>(p[cols]) : nullptr,
+                                            rows >= 0 ? static_cast<const int32_t*>(p[rows]) : nullptr, &z, &e, p[y], st);
+        });
+    }
+    else
     emit(node, "qgemm_core", [=](const Ptrs& p, cudaStream_t st) {
         b200_epilogue e;
         memset(&e, 0, sizeof(e));

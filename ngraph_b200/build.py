@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 KERNEL_LIB = os.path.join(HERE, "libb200_kernels.so")
-KERNEL_SOURCES = ["abi.cu", "quantize.cu", "qcontract.cu", "layout.cu", "glue_f32.cu"]
+KERNEL_SOURCES = ["abi.cu", "quantize.cu", "qcontract.cu", "layout.cu", "glue_f32.cu", "zero_points.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler",
               "-fPIC,-fvisibility=hidden", "-I" + os.path.join(ROOT, "include")]
 

@@ -355,7 +355,11 @@ namespace b200
                                                            uint32_t sc, uint32_t bi, bool has_sum, float sum_scale, const EpiRow& er)
     {
         const bool one_byte = p.out_type == B200_U8 || p.out_type == B200_I8;
-        if (p.half_away)
+        if (p.half_away == 2)
+        {
+            // raw accumulators: v[] already holds them
+        }
+        else if (p.half_away)
         {
             const float scale = __ldg(p.scale);
 #pragma unroll
@@ -897,7 +901,7 @@ namespace b200
                         {
                             const int col = colw + jj;
                             const bool in_n = col < p.N;
-                            epi_scale[ew][jj] = in_n ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
+                            epi_scale[ew][jj] = (in_n && p.scale) ? __ldg(p.scale + (p.scale_per_channel ? col : 0)) : 0.0f;
                             epi_bias[ew][jj] = (in_n && p.bias) ? __ldg(p.bias + col) : 0;
                         }
                         staged_tn = tn;
@@ -1367,7 +1371,11 @@ namespace b200
 
     static int check_epilogue(const b200_epilogue* e, int64_t n_out)
     {
-        if (!e || !e->scale)
+        if (!e)
+            return B200_ERR_INVALID_ARGUMENT;
+        if (e->round_half_away == 2) // the accumulators themselves: nothing but the output type is looked at
+            return (e->out_type == B200_I32 && !e->sum_in && !e->bias && !e->relu) ? B200_OK : B200_ERR_INVALID_ARGUMENT;
+        if (!e->scale || (e->round_half_away != 0 && e->round_half_away != 1))
             return B200_ERR_INVALID_ARGUMENT;
         if (e->scale_count != 1 && e->scale_count != n_out)
             return B200_ERR_INVALID_ARGUMENT;
@@ -1383,8 +1391,8 @@ namespace b200
     static void fill_epilogue(ContractParams& p, const b200_epilogue* e, void* out, int a_type)
     {
         p.bias = e->bias;
-        p.scale = e->scale;
-        p.scale_per_channel = e->scale_count > 1;
+        p.scale = e->round_half_away == 2 ? nullptr : e->scale;
+        p.scale_per_channel = e->round_half_away != 2 && e->scale_count > 1;
         p.sum_in = e->sum_in;
         p.sum_type = e->sum_type;
         p.sum_scale = e->sum_scale;
@@ -1394,7 +1402,7 @@ namespace b200
         p.out_zp = e->out_zero_point;
         p.out_type = e->out_type;
         p.out = out;
-        p.vec_params = ((reinterpret_cast<uintptr_t>(e->scale) | reinterpret_cast<uintptr_t>(e->bias)) & 15) == 0;
+        p.vec_params = ((reinterpret_cast<uintptr_t>(p.scale) | reinterpret_cast<uintptr_t>(e->bias)) & 15) == 0;
         const bool one_byte = e->out_type == B200_U8 || e->out_type == B200_I8;
         p.tma_store = one_byte && (p.N % 16 == 0) && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         p.f32_staged = e->out_type == B200_F32 && !e->round_half_away && !e->sum_in && (p.N % COLS == 0) &&

@@ -62,6 +62,9 @@ def _load():
         "b200_broadcast_b32": (ci, [vp, vp, p64, ci, p64, ci, vp]),
         "b200_permute_b32": (ci, [vp, vp, p64, ci, p64, vp]),
         "b200_reduce_f32": (ci, [ci, vp, vp, p64, ci, p64, ci, vp]),
+        "b200_strided_sums": (ci, [vp, ci, vp] + [i64] * 6 + [vp]),
+        "b200_window_sums": (ci, [vp, vp, vp, vp]),
+        "b200_requant_zero_points": (ci, [vp, vp, vp, vp, ctypes.POINTER(Epilogue), vp, vp]),
         "b200_copy_rows": (ci, [vp, vp, i64, i64, i64, vp]),
         "b200_softmax_rows_f32": (ci, [vp, vp, i64, i64, vp]),
         "b200_bmm_f32": (ci, [vp, vp, vp, i64, i64, i64, i64, vp]),

@@ -155,6 +155,53 @@ def test_quantized_dot_core(backends):
 
 @pytest.mark.gpu
 @needs_ngraph
+@pytest.mark.parametrize("za,zb", [(128, 0), (0, -5), (37, 11)])
+def test_quantized_dot_with_zero_points(backends, za, zb):
+    """sum_k (a - za) * (b - zb) of reference::dot (dot.hpp:134-159): the device subtracts the rank-one terms from exact
+    int32 accumulators.  Large K on purpose: the accumulators pass 2^24, where a float would lose bits."""
+    rng = np.random.default_rng(za * 7 + zb + 100)
+    a = rng.integers(0, 256, size=(45, 2048)).astype(np.uint8)
+    b = rng.integers(-127, 128, size=(2048, 40)).astype(np.int8)
+    b[:, 0] = 127  # a column that drives the raw sum far beyond 2^24
+    for out_dtype, so, zo in ((np.int8, 40000.0, 3), (np.int32, 0.5, -4)):
+        pa, pb = ng.parameter(np.uint8, a.shape), ng.parameter(np.int8, b.shape)
+        fn = ng.Function([ng.quantized_dot(pa, pb, 0.5, za, 0.25, zb, so, zo, out_dtype)], [pa, pb])
+        got, exp = run_both(backends, fn, fn, [a, b])
+        same_bits(got[0], exp[0], str(out_dtype))
+        fn2 = ng.Function([ng.quantized_dot(pa, ng.constant(b), 0.5, za, 0.25, zb, so, zo, out_dtype)], [pa])
+        same_bits(backends[0].compile(fn2).run(a)[0], exp[0], "constant B " + str(out_dtype))
+    if zb >= 0:
+        bu = rng.integers(0, 256, size=(2048, 40)).astype(np.uint8)
+        pa, pb = ng.parameter(np.uint8, a.shape), ng.parameter(np.uint8, bu.shape)
+        fn = ng.Function([ng.quantized_dot(pa, pb, 0.5, za, 0.25, zb, 0.5, 9, np.int32)], [pa, pb])
+        got, exp = run_both(backends, fn, fn, [a, bu])
+        same_bits(got[0], exp[0], "u8 x u8")
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("za,zf", [(128, 0), (0, 9), (100, -7)])
+@pytest.mark.parametrize("geom", [dict(pad_below=(1, 1)), dict(stride=(2, 2), pad_below=(2, 1), pad_above=(0, 2), dilation=(2, 1)), dict()])
+def test_quantized_convolution_with_zero_points(backends, za, zf, geom):
+    """reference::convolution (convolution.hpp:236-258) skips the taps that fall into the padding, so the correction
+    terms depend on where the output pixel sits; borders, strides and dilation are all exercised."""
+    rng = np.random.default_rng(za + zf + len(geom) + 100)
+    for channels in (64, 48):  # 48: padded to the kernels' channel granule on the device (constant filters only)
+        ds, fs = (2, channels, 9, 8), (24, channels, 3, 3)
+        data = rng.integers(0, 256, size=ds).astype(np.uint8)
+        filt = rng.integers(-127, 128, size=fs).astype(np.int8)
+        for out_dtype, so, zo in ((np.int32, 1.0, 5), (np.int8, 60000.0, -2)):
+            d, f = ng.parameter(np.uint8, ds), ng.parameter(np.int8, fs)
+            fn = ng.Function([ng.quantized_convolution(d, f, 1.0, za, 1.0, zf, so, zo, out_dtype, **geom)], [d, f])
+            exp = backends[1].compile(fn).run(data, filt)[0]
+            if channels % 64 == 0:
+                same_bits(backends[0].compile(fn).run(data, filt)[0], exp, str(out_dtype))
+            fn2 = ng.Function([ng.quantized_convolution(d, ng.constant(filt), 1.0, za, 1.0, zf, so, zo, out_dtype, **geom)], [d])
+            same_bits(backends[0].compile(fn2).run(data)[0], exp, "constant filters %d %s" % (channels, out_dtype))
+
+
+@pytest.mark.gpu
+@needs_ngraph
 def test_quantized_dot_bias(backends):
     rng = np.random.default_rng(2)
     x = rng.integers(0, 256, size=(50, 128)).astype(np.uint8)
