@@ -417,7 +417,7 @@ B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const in
  *   b200_broadcast_b32   op::v0::Broadcast for 4-byte elements (broadcast.hpp): out_shape and the axes that are new
  *   b200_permute_b32     the axis permutation of a transposing op::v0::Reshape for 4-byte elements (reshape.hpp):
  *                        output axis i is input axis order[i]
- *   b200_reduce_f32      op::v0::Sum (Kahan-compensated, sum.hpp:56-90) and op::v0::Max (max.hpp:32-58) over an axis set,
+ *   b200_reduce_f32      op::v0::Sum (Kahan-compensated, sum.hpp:56-90), op::v0::Max (max.hpp:32-58) and op::v0::Min (min.hpp) over an axis set,
  *                        inputs taken in row-major order like the reference
  *   b200_softmax_rows_f32 op::v0::Softmax over the last axis of a [rows, row_elements] matrix (softmax.hpp: max, exp(x - max),
  *                        Kahan sum, divide -- the same values as those five ops run one after another); rows longer
@@ -446,7 +446,8 @@ typedef enum b200_f32_op
 typedef enum b200_reduce_op
 {
     B200_REDUCE_SUM = 0,
-    B200_REDUCE_MAX = 1
+    B200_REDUCE_MAX = 1,
+    B200_REDUCE_MIN = 2
 } b200_reduce_op;
 
 B200_API int b200_f32_binary(int op, const float* a, const float* b, float* out, int64_t n, void* stream);

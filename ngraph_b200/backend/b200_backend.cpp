@@ -37,6 +37,7 @@
 #include "ngraph/op/experimental/batch_mat_mul.hpp"
 #include "ngraph/op/gather.hpp"
 #include "ngraph/op/max.hpp"
+#include "ngraph/op/min.hpp"
 #include "ngraph/op/maximum.hpp"
 #include "ngraph/op/minimum.hpp"
 #include "ngraph/op/multiply.hpp"
@@ -427,7 +428,7 @@ bool B200Backend::is_supported(const Node& node) const
            is_type<op::v1::Divide>(&node) || is_type<op::v1::Maximum>(&node) || is_type<op::v1::Minimum>(&node) ||
            is_type<op::v0::Abs>(&node) || is_type<op::v0::Negative>(&node) || is_type<op::v0::Sqrt>(&node) ||
            is_type<op::v0::Exp>(&node) || is_type<op::v0::Erf>(&node) || is_type<op::v0::Relu>(&node) ||
-           is_type<op::v0::Broadcast>(&node) || is_type<op::v0::Sum>(&node) || is_type<op::v0::Max>(&node) ||
+           is_type<op::v0::Broadcast>(&node) || is_type<op::v0::Sum>(&node) || is_type<op::v0::Max>(&node) || is_type<op::v0::Min>(&node) ||
            is_type<op::v0::Softmax>(&node) || is_type<op::v0::BatchMatMul>(&node) || is_type<op::v0::Dot>(&node) ||
            is_type<op::v0::Gather>(&node) || is_type<op::v0::Concat>(&node);
 }
@@ -958,20 +959,22 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
     auto emit_reduce = [&](int rop, int x, const Shape& in_shape, const AxisSet& axes_set, int y) {
         std::vector<int64_t> shape(in_shape.begin(), in_shape.end());
         std::vector<int64_t> axes(axes_set.begin(), axes_set.end());
-        emit(node, rop == B200_REDUCE_SUM ? "reduce_sum" : "reduce_max", [=](const Ptrs& p, cudaStream_t st) {
+        emit(node, rop == B200_REDUCE_SUM ? "reduce_sum" : rop == B200_REDUCE_MAX ? "reduce_max" : "reduce_min", [=](const Ptrs& p, cudaStream_t st) {
             return b200_reduce_f32(rop, static_cast<const float*>(p[x]), static_cast<float*>(p[y]), shape.data(), int(shape.size()),
                                    axes.data(), int(axes.size()), st);
         });
     };
-    const bool is_sum = is_type<op::v0::Sum>(node), is_max = is_type<op::v0::Max>(node);
-    if (is_sum || is_max)
+    const bool is_sum = is_type<op::v0::Sum>(node), is_max = is_type<op::v0::Max>(node), is_min = is_type<op::v0::Min>(node);
+    if (is_sum || is_max || is_min)
     {
         if (node->get_input_element_type(0) != element::f32 || node->get_input_shape(0).size() > 8)
             unsupported(*node, "reductions on element types other than f32");
-        AxisSet axes = is_sum ? as_type_ptr<op::v0::Sum>(node)->get_reduction_axes() : as_type_ptr<op::v0::Max>(node)->get_reduction_axes();
+        AxisSet axes = is_sum ? as_type_ptr<op::v0::Sum>(node)->get_reduction_axes()
+                              : is_max ? as_type_ptr<op::v0::Max>(node)->get_reduction_axes()
+                                       : as_type_ptr<op::v0::Min>(node)->get_reduction_axes();
         int x = canonical_slot(node->input_value(0));
         int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
-        emit_reduce(is_sum ? B200_REDUCE_SUM : B200_REDUCE_MAX, x, node->get_input_shape(0), axes, y);
+        emit_reduce(is_sum ? B200_REDUCE_SUM : is_max ? B200_REDUCE_MAX : B200_REDUCE_MIN, x, node->get_input_shape(0), axes, y);
         value_of(node->output(0)).canonical = y;
         return true;
     }

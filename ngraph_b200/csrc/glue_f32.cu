@@ -95,38 +95,42 @@ namespace b200
 
     // One thread per output element; the reduced coordinates are walked in row-major order, as the reference does.
     // keep: the kept axes (thread index -> input offset); red: the reduced axes.
-    template <bool IS_SUM>
+    // One step of the reference's compensated sum (runtime/reference/sum.hpp:56-90).
+    __device__ __forceinline__ void kahan_step(float& z, float& c, float x)
+    {
+        if (isfinite(x) && isfinite(z))
+        {
+            const float y = __fsub_rn(x, c);
+            const float t = __fadd_rn(z, y);
+            c = __fsub_rn(__fsub_rn(t, z), y);
+            z = t;
+        }
+        else
+            z = __fadd_rn(z, x);
+    }
+
+    template <int OP> // b200_reduce_op
     __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ in, float* __restrict__ out, Dims keep, Dims red,
                                                          int64_t n_out, int64_t n_red)
     {
         for (int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o < n_out; o += int64_t(gridDim.x) * blockDim.x)
         {
             const float* base = in + mapped_offset(keep, o);
-            if (IS_SUM)
+            if (OP == B200_REDUCE_SUM)
             {
                 float z = 0.0f, c = 0.0f;
                 for (int64_t r = 0; r < n_red; ++r)
-                {
-                    const float x = base[mapped_offset(red, r)];
-                    if (isfinite(x) && isfinite(z))
-                    {
-                        const float y = __fsub_rn(x, c);
-                        const float t = __fadd_rn(z, y);
-                        c = __fsub_rn(__fsub_rn(t, z), y);
-                        z = t;
-                    }
-                    else
-                        z = __fadd_rn(z, x);
-                }
+                    kahan_step(z, c, base[mapped_offset(red, r)]);
                 out[o] = z;
             }
             else
             {
-                float m = -INFINITY;
+                // max.hpp:32-58 / min.hpp: start from -inf / +inf, replace on a strict comparison (a NaN never wins)
+                float m = OP == B200_REDUCE_MAX ? -INFINITY : INFINITY;
                 for (int64_t r = 0; r < n_red; ++r)
                 {
                     const float x = base[mapped_offset(red, r)];
-                    if (x > m)
+                    if (OP == B200_REDUCE_MAX ? x > m : x < m)
                         m = x;
                 }
                 out[o] = m;
@@ -207,20 +211,6 @@ namespace b200
     {
         for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
             out[i] = value;
-    }
-
-    // One step of the reference's compensated sum (runtime/reference/sum.hpp:56-90).
-    __device__ __forceinline__ void kahan_step(float& z, float& c, float x)
-    {
-        if (isfinite(x) && isfinite(z))
-        {
-            const float y = __fsub_rn(x, c);
-            const float t = __fadd_rn(z, y);
-            c = __fsub_rn(__fsub_rn(t, z), y);
-            z = t;
-        }
-        else
-            z = __fadd_rn(z, x);
     }
 
     // Reductions and Softmax over the LAST axis of a [rows, L] matrix.  The compensated sum has to walk a row in order,
@@ -525,7 +515,7 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
                                void* stream)
 {
     using namespace b200;
-    if ((op != B200_REDUCE_SUM && op != B200_REDUCE_MAX) || !valid_shape(shape, rank) || n_axes < 0 || n_axes > rank ||
+    if ((op != B200_REDUCE_SUM && op != B200_REDUCE_MAX && op != B200_REDUCE_MIN) || !valid_shape(shape, rank) || n_axes < 0 || n_axes > rank ||
         (n_axes > 0 && !axes))
         return B200_ERR_INVALID_ARGUMENT;
     bool reduced[MAX_RANK] = {false};
@@ -571,9 +561,11 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
              launch_staged_rows<false>(in, out, n_out, n_red, st))
         ; // the last axis of a matrix with many rows: staged through shared memory
     else if (op == B200_REDUCE_SUM)
-        reduce_kernel<true><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+        reduce_kernel<B200_REDUCE_SUM><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+    else if (op == B200_REDUCE_MAX)
+        reduce_kernel<B200_REDUCE_MAX><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     else
-        reduce_kernel<false><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+        reduce_kernel<B200_REDUCE_MIN><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     return after_launch("b200_reduce_f32");
 }
 

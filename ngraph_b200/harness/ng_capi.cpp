@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "ngraph/ngraph.hpp"
+#include "ngraph/builder/quantized_concat_builder.hpp"
 #include "ngraph/op/experimental/quantized_conv_bias.hpp"
 #include "ngraph/op/experimental/quantized_conv_relu.hpp"
 #include "ngraph/op/experimental/quantized_dot_bias.hpp"
@@ -223,6 +224,22 @@ NGC_API void* ngc_concat(void** values, int n, int64_t axis)
         OutputVector parts;
         for (int i = 0; i < n; ++i) parts.push_back(val(values[i]));
         return box(std::make_shared<op::v0::Concat>(parts, axis));
+    }, nullptr);
+}
+
+// builder::QuantizedConcatBuilder (src/ngraph/builder/quantized_concat_builder.cpp): every operand is brought to the
+// scale of the widest [min, max] range by a Dequantize / Quantize pair, then concatenated
+NGC_API void* ngc_quantized_concat(void** values, void** mins, void** maxs, int n, int64_t axis)
+{
+    return guarded([&]() -> void* {
+        OutputVector parts, lo, hi;
+        for (int i = 0; i < n; ++i)
+        {
+            parts.push_back(val(values[i]));
+            lo.push_back(val(mins[i]));
+            hi.push_back(val(maxs[i]));
+        }
+        return box(builder::QuantizedConcatBuilder(parts, size_t(axis), lo, hi));
     }, nullptr);
 }
 

@@ -56,6 +56,7 @@ def capi():
             "ngc_bert_encoder": (vp, [ci] * 7 + [ctypes.c_uint64, ci]),
             "ngc_function_op_names": (ci, [vp, ci, ctypes.c_char_p, ci]),
             "ngc_concat": (vp, [pvp, ci, i64]),
+            "ngc_quantized_concat": (vp, [pvp, pvp, pvp, ci, i64]),
             "ngc_function_after_plugin_passes": (vp, [vp, ctypes.c_char_p]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
             "ngc_tensor_create": (vp, [vp, ci, p64, ci]), "ngc_tensor_wrap": (vp, [vp, ci, p64, ci, vp]),
@@ -213,6 +214,12 @@ def avg_pool(x, window, stride=(1, 1)):
 def concat(values, axis):
     arr = (ctypes.c_void_p * len(values))(*[v.h for v in values])
     return Value(capi().ngc_concat(arr, len(values), axis), "Concat")
+
+
+def quantized_concat(values, mins, maxs, axis):
+    """builder::QuantizedConcatBuilder: mins / maxs are f32 [1] values, one pair per operand"""
+    arr = lambda vs: (ctypes.c_void_p * len(vs))(*[v.h for v in vs])
+    return Value(capi().ngc_quantized_concat(arr(values), arr(mins), arr(maxs), len(values), axis), "QuantizedConcat")
 
 
 def convert(x, dtype):

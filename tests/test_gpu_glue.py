@@ -91,7 +91,8 @@ def test_sum_and_max_follow_the_reference_order(L, shape, axes):
     want_max = moved.max(axis=-1) if axes else x.copy()
     xd = dev(x)
     out = torch.empty(max(want_sum.size, 1), device="cuda")
-    for op, want in ((0, want_sum), (1, want_max)):
+    want_min = moved.min(axis=-1) if axes else x.copy()
+    for op, want in ((0, want_sum), (1, want_max), (2, want_min)):
         L.check(L.LIB.b200_reduce_f32(op, xd.data_ptr(), out.data_ptr(), i64(shape), len(shape), i64(axes), len(axes), stream()), "reduce")
         np.testing.assert_array_equal(bits(out.cpu().numpy()[:want.size]), bits(want).ravel())
 

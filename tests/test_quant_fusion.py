@@ -268,3 +268,33 @@ def test_hoisted_max_pool_and_concat_on_the_device(backends):
     fn = ng.Function([ng.concat([a, b], 1)], [a, b])
     xa, xb = rng.standard_normal((4, 3)).astype(np.float32), rng.standard_normal((4, 5)).astype(np.float32)
     np.testing.assert_array_equal(b200.compile(fn).run(xa, xb)[0], np.concatenate([xa, xb], 1))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8])
+def test_quantized_concat_builder_graph(backends, dtype):
+    """builder::QuantizedConcatBuilder (src/ngraph/builder/quantized_concat_builder.cpp:28-79): Dequantize / Quantize each
+    operand to the scale of the widest range, then Concat; the ranges are run-time values here, like in the
+    reference's tests (test/builder_quantization.cpp:847-944), so the scale arithmetic (Concat, Min, Max, Abs, Maximum,
+    Divide) runs on the device as well."""
+    b200, ref = backends
+    shapes = ((2, 2), (3, 2), (3, 2))
+    xs = [ng.parameter(dtype, s) for s in shapes]
+    mins = [ng.parameter(np.float32, (1,)) for _ in shapes]
+    maxs = [ng.parameter(np.float32, (1,)) for _ in shapes]
+    fn = ng.Function([ng.quantized_concat(xs, mins, maxs, 0)], xs + mins + maxs)
+    # the reference's own vectors: equal ranges leave every value as it is
+    lo = -2 if dtype == np.int8 else 2
+    data = [np.array([lo, 4, 8, 16], dtype).reshape(2, 2), np.array([lo, 2, 4, 8, 16, 15], dtype).reshape(3, 2),
+            np.array([lo, 3, 5, 7, 11, 16], dtype).reshape(3, 2)]
+    same = [np.float32([2.0])] * 3 + [np.float32([16.0])] * 3
+    got = b200.compile(fn).run(*data, *same)[0]
+    np.testing.assert_array_equal(got, np.concatenate(data, 0))
+    # different ranges: every operand is rescaled; INTERPRETER runs the same graph
+    rng = np.random.default_rng(8)
+    big = ((40, 16), (25, 16), (70, 16))
+    xs = [ng.parameter(dtype, s) for s in big]
+    fn = ng.Function([ng.quantized_concat(xs, mins, maxs, 0)], xs + mins + maxs)
+    data = [rng.integers(np.iinfo(dtype).min, np.iinfo(dtype).max + 1, size=s).astype(dtype) for s in big]
+    ranges = [np.float32([-1.5]), np.float32([-6.0]), np.float32([-0.25]), np.float32([3.0]), np.float32([5.5]), np.float32([9.75])]
+    np.testing.assert_array_equal(b200.compile(fn).run(*data, *ranges)[0], ref.compile(fn).run(*data, *ranges)[0])
