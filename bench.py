@@ -281,6 +281,117 @@ class ResNet50:
         return {"value": rate, "unit": "img/s", "cores": procs, "kind": "reference", "sample": sample}, ok
 
 
+class BertEncoder:
+    """BASELINE config 5: the int8 BERT-base-shaped encoder as an nGraph Function through the plugin.  The int8 dots are the
+    QuantizedDotBias layers; everything between them (dynamic activation scales, attention products, softmax, LayerNorm,
+    GELU) is f32 glue that keeps the reference kernels' arithmetic."""
+    name, metric, unit = "bert", "int8 BERT-base-shaped encoder inference throughput", "tokens/s"
+    dtype, bound = "i8*i8->i32 dots, f32 glue", "tensor"
+    dims = dict(layers=12, hidden=768, heads=12, ffn=3072, seq=384, vocab=30522)
+    cpu_kind = "reference"
+
+    def __init__(self, batch=64):
+        self.batch = batch
+
+    def describe(self, world=1):
+        d = self.dims
+        return {"workload": "int8 BERT-base-shaped encoder, nGraph Function through the B200 backend plugin: %d layers, hidden %d, "
+                            "%d heads, FFN %d, seq %d; QKV/out/FFN = QuantizedDotBias with dynamic per-tensor i8 activation scales"
+                            % (d["layers"], d["hidden"], d["heads"], d["ffn"], d["seq"]),
+                "batch_per_gpu": self.batch, "global_batch": self.batch * world, "input": "i32 token ids and segment ids [B*S]",
+                "weights": "random N(0, 0.02), per-output-channel i8", "parallelism": "batch-sharded replicas, no collective",
+                "l2": "per-layer activations (75 MB x several) > 126 MB L2"}
+
+    def host_inputs(self, seed):
+        rng = np.random.default_rng(seed)
+        m = self.batch * self.dims["seq"]
+        self.ids = rng.integers(0, self.dims["vocab"], m).astype(np.int32)
+        self.seg = (rng.random(m) < 0.5).astype(np.int32)
+
+    def setup(self, torch, rank, local_rank, world):
+        from ngraph_b200 import ngraph_api as ng
+        self.torch, self.ng = torch, ng
+        ng.load_b200()
+        self.host_inputs(1 + rank)
+        m, hidden = self.batch * self.dims["seq"], self.dims["hidden"]
+        stream = torch.cuda.current_stream().cuda_stream
+        self.backend = ng.Backend("B200:%d,stream=%d" % (local_rank, stream))
+        self.fn = ng.bert_encoder(seed=1, batch=self.batch, **self.dims)
+        self.exe = self.backend.compile(self.fn)
+        self.dev = [torch.from_numpy(self.ids).cuda(), torch.from_numpy(self.seg).cuda()]
+        self.out = torch.empty((m, hidden), dtype=torch.float32, device="cuda")
+        self.t_in = [self.backend.create_tensor(np.int32, (m,), t.data_ptr()) for t in self.dev]
+        self.t_out = self.backend.create_tensor(np.float32, (m, hidden), self.out.data_ptr())
+        self.pin_in = [torch.from_numpy(self.ids).pin_memory(), torch.from_numpy(self.seg).pin_memory()]
+        self.pin_out = torch.empty((m, hidden), dtype=torch.float32).pin_memory()
+
+    def units_per_step(self):
+        return float(self.batch * self.dims["seq"])
+
+    def step(self):
+        self.exe.call([self.t_out], self.t_in, validate=False)
+
+    def step_e2e(self):
+        for t, h in zip(self.t_in, self.pin_in):
+            t.write_ptr(h.data_ptr(), h.numel() * 4)
+        self.exe.call([self.t_out], self.t_in, validate=False)
+        self.t_out.read_ptr(self.pin_out.data_ptr(), self.pin_out.numel() * 4)
+
+    def io_bytes(self):
+        return sum(h.numel() * 4 for h in self.pin_in), self.pin_out.numel() * 4
+
+    def int8_ops_per_step(self):
+        d = self.dims
+        return 2.0 * (4 * d["hidden"] ** 2 + 2 * d["hidden"] * d["ffn"]) * d["layers"] * self.batch * d["seq"]
+
+    def roofline(self, peaks, per_step_ms):
+        """the int8 dots against the tensor peak, from per-node CUDA events of an instrumented pass; the f32 glue is listed
+        beside them because it is most of the step"""
+        exe = self.backend.compile(self.fn, perf=True)
+        passes = 3
+        for _ in range(passes):
+            exe.call([self.t_out], self.t_in, validate=False)
+        self.torch.cuda.synchronize()
+        rows = exe.performance_data()
+        by_op = {}
+        for n, us, c in rows:
+            by_op[n.split(":")[0]] = by_op.get(n.split(":")[0], 0.0) + us / passes
+        dots_us = by_op.get("QuantizedDotBias", 0.0)
+        total_us = sum(by_op.values())
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        achieved = self.int8_ops_per_step() / (dots_us * 1e-6) / 1e12
+        top = sorted(((round(v, 1), k) for k, v in by_op.items()), reverse=True)[:8]
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
+                "kernel": "qcontract_kernel (72 QuantizedDotBias layers)", "kernel_us_per_step": dots_us,
+                "all_nodes_us_per_step": total_us, "glue_share_of_step": 1.0 - dots_us / total_us, "op_types_us_per_step": top,
+                "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)"}
+
+    def cpu_sample(self):
+        """nGraph's INTERPRETER on ONE layer of the same width over one short sequence, scaled to the depth of the model"""
+        from ngraph_b200 import ngraph_api as ng
+        from oracle import interpreter
+        d = dict(self.dims, layers=1, seq=8)
+        fn = ng.bert_encoder(seed=1, batch=1, decomposed=True, **d)
+        rng = np.random.default_rng(3)
+        self.sample_inputs = [rng.integers(0, d["vocab"], 8).astype(np.int32), (rng.random(8) < 0.5).astype(np.int32)]
+        exe = interpreter.backend().compile(fn)
+        t = time.time()
+        self.sample_output = exe.run(*self.sample_inputs)[0]
+        dt = time.time() - t
+        rate = 8.0 / (dt * self.dims["layers"])
+        return rate, ("INTERPRETER, 1 thread: one encoder layer (hidden %d, FFN %d) on 8 tokens in %.1f s, scaled to %d layers"
+                      % (d["hidden"], d["ffn"], dt, self.dims["layers"]))
+
+    def check_and_cpu_baseline(self, skip_cpu):
+        if skip_cpu:
+            return None, None
+        rate, sample = self.cpu_sample()
+        d = dict(self.dims, layers=1, seq=8)
+        got = self.backend.compile(self.ng.bert_encoder(seed=1, batch=1, **d)).run(*self.sample_inputs)[0]
+        err = float(np.max(np.abs(got - self.sample_output)) / max(1e-30, float(np.max(np.abs(self.sample_output)))))
+        return {"value": rate, "unit": self.unit, "cores": 1, "kind": "reference", "sample": sample}, bool(err <= 1e-5)
+
+
 class MicroWorkload:
     """single-kernel workloads called through the C ABI (ngraph_b200.ops)"""
     bound = "tensor"
@@ -531,7 +642,7 @@ class QuantizeSweepPoint(MicroWorkload):
         return reps * 5.0 * self.h_x.size / 1e9 / dt, "C port of the reference arithmetic, %d elements, %d passes, %.1f s" % (self.h_x.size, reps, dt)
 
 
-WORKLOADS = {"resnet50": ResNet50, "qconv": QConvLayer, "qdot": QDotLayer, "quantize": QuantizeSweepPoint}
+WORKLOADS = {"resnet50": ResNet50, "qconv": QConvLayer, "qdot": QDotLayer, "quantize": QuantizeSweepPoint, "bert": BertEncoder}
 
 
 def run_reference(args, wl, rank):
@@ -547,7 +658,7 @@ def run_reference(args, wl, rank):
     else:
         wl.host_inputs(1)
         value, sample = wl.cpu_sample()
-        cores, kind = 1, "port"
+        cores, kind = 1, getattr(wl, "cpu_kind", "port")
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(args.gpus),

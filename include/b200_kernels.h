@@ -422,6 +422,10 @@ B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const in
  *   b200_softmax_rows_f32 op::v0::Softmax over the last axis of a [rows, row_elements] matrix (softmax.hpp: max, exp(x - max),
  *                        Kahan sum, divide -- the same values as those five ops run one after another); rows longer
  *                        than 1535 elements return B200_ERR_UNSUPPORTED
+ *   b200_layer_norm_rows_f32 op::v0::LayerNorm over the last axis with scale and bias (layer_norm.cpp:68-150): the values of
+ *                        its decomposition (mean and variance through Kahan sums, sqrt(var + epsilon), divide, scale,
+ *                        shift; every step rounded separately) from one kernel; rows longer than 1535 are unsupported
+ *   b200_gelu_f32        op::v0::Gelu as its decomposition computes it (gelu.cpp:46-60): (0.5 * x) * (1 + erf(x / sqrt 2))
  *   b200_bmm_f32         op::v0::BatchMatMul / 2-D op::v0::Dot on f32 (batch_mat_mul.hpp, dot.hpp:108-160): a[b,M,K] x
  *                        b[b,K,N], the sum over k in double, in order, rounded to float once
  *   b200_gather_rows_b32 op::v0::Gather with axis 0 on a 2-D table of 4-byte elements and an i32 / i64 index vector
@@ -458,6 +462,9 @@ B200_API int b200_permute_b32(const void* in, void* out, const int64_t* in_shape
 B200_API int b200_reduce_f32(int op, const float* in, float* out, const int64_t* shape, int rank, const int64_t* axes,
                              int n_axes, void* stream);
 B200_API int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, int64_t row_elements, void* stream);
+B200_API int b200_layer_norm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, int64_t rows,
+                                      int64_t row_elements, float epsilon, void* stream);
+B200_API int b200_gelu_f32(const float* x, float* out, int64_t n, void* stream);
 B200_API int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N,
                           void* stream);
 B200_API int b200_gather_rows_b32(const void* table, int64_t n_rows, int64_t row_elements, const void* indices, int index_type,

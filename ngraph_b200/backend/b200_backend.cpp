@@ -36,6 +36,8 @@
 #include "ngraph/op/exp.hpp"
 #include "ngraph/op/experimental/batch_mat_mul.hpp"
 #include "ngraph/op/gather.hpp"
+#include "ngraph/op/gelu.hpp"
+#include "ngraph/op/layer_norm.hpp"
 #include "ngraph/op/max.hpp"
 #include "ngraph/op/min.hpp"
 #include "ngraph/op/maximum.hpp"
@@ -382,11 +384,12 @@ std::shared_ptr<runtime::Tensor>
 std::shared_ptr<runtime::Executable> B200Backend::compile(std::shared_ptr<Function> func, bool enable_performance_data)
 {
     std::lock_guard<std::mutex> lock(m_mutex);
-    auto it = m_cache.find(func);
+    const auto key = std::make_pair(func, enable_performance_data);
+    auto it = m_cache.find(key);
     if (it != m_cache.end())
         return it->second;
     auto exec = std::make_shared<B200Executable>(m_ctx, func, enable_performance_data);
-    m_cache.insert({func, exec});
+    m_cache.insert({key, exec});
     return exec;
 }
 
@@ -412,6 +415,8 @@ bool B200Backend::is_device_memory(void* ptr)
     return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
 }
 
+static bool runs_undecomposed(const Node& node);
+
 bool B200Backend::is_supported(const Node& node) const
 {
     // the op set of the quantized-inference path; shapes/types are checked at compile()
@@ -430,7 +435,7 @@ bool B200Backend::is_supported(const Node& node) const
            is_type<op::v0::Exp>(&node) || is_type<op::v0::Erf>(&node) || is_type<op::v0::Relu>(&node) ||
            is_type<op::v0::Broadcast>(&node) || is_type<op::v0::Sum>(&node) || is_type<op::v0::Max>(&node) || is_type<op::v0::Min>(&node) ||
            is_type<op::v0::Softmax>(&node) || is_type<op::v0::BatchMatMul>(&node) || is_type<op::v0::Dot>(&node) ||
-           is_type<op::v0::Gather>(&node) || is_type<op::v0::Concat>(&node);
+           is_type<op::v0::Gather>(&node) || is_type<op::v0::Concat>(&node) || runs_undecomposed(node);
 }
 
 extern "C" B200_BACKEND_API void ngraph_register_b200_backend()
@@ -612,11 +617,33 @@ bool B200Executable::avgpool_head_member(const Node* node)
 
 // The graph-level pipeline of compile(): what nGraph's backends run before they lower (cpu_external_function.cpp:1289-1335
 // keeps the CPU backend's list), with the plugin's own quantisation fusion in the place CPUQuantFusion has there.
+// Fused ops the device runs as one kernel with the arithmetic of their decomposition; everything else is decomposed.
+static bool runs_undecomposed(const Node& node)
+{
+    if (auto ln = as_type<const op::v0::LayerNorm>(&node))
+    {
+        if (!ln->get_use_affine() || ln->get_keep_stats() || node.get_input_element_type(0) != element::f32 ||
+            !node.get_input_partial_shape(0).is_static())
+            return false;
+        const Shape shape = node.get_input_shape(0);
+        const int64_t rank = int64_t(shape.size());
+        const int64_t axis = ln->get_begin_norm_axis() >= 0 ? ln->get_begin_norm_axis() : rank + ln->get_begin_norm_axis();
+        return rank >= 1 && axis == rank - 1 && shape.back() >= 1 && shape.back() <= 1535 && node.get_input_shape(1).size() == 1 &&
+               node.get_input_shape(2).size() == 1;
+    }
+    if (is_type<op::v0::Gelu>(&node))
+        return node.get_input_element_type(0) == element::f32;
+    return false;
+}
+
 static void run_graph_passes(const std::shared_ptr<Function>& function)
 {
     ngraph::pass::Manager pm;
     pm.register_pass<ngraph::pass::LikeReplacement>();
-    pm.register_pass<ngraph::pass::FusedOpDecomposition>();
+    if (getenv("B200_DECOMPOSE_ALL")) // the float islands as chains of elementwise ops and reductions (for comparison)
+        pm.register_pass<ngraph::pass::FusedOpDecomposition>();
+    else
+        pm.register_pass<ngraph::pass::FusedOpDecomposition>(runs_undecomposed);
     if (ngraph::runtime::b200::pass::quant_fusion_enabled())
         pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
     pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind
@@ -979,6 +1006,33 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
         return true;
     }
 
+    if (auto ln = as_type_ptr<op::v0::LayerNorm>(node))
+    {
+        if (!runs_undecomposed(*node))
+            unsupported(*node, "LayerNorm other than f32, last axis, with scale and bias");
+        const int64_t row = int64_t(os.back()), rows = n_out / row;
+        const float eps = static_cast<float>(ln->get_epsilon()); // builder::make_constant(f32, ..., double epsilon)
+        int x = canonical_slot(node->input_value(0)), g = canonical_slot(node->input_value(1)), b = canonical_slot(node->input_value(2));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit(node, "layer_norm_rows", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_layer_norm_rows_f32(static_cast<const float*>(p[x]), static_cast<const float*>(p[g]), static_cast<const float*>(p[b]),
+                                            static_cast<float*>(p[y]), rows, row, eps, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
+    if (is_type<op::v0::Gelu>(node))
+    {
+        if (!all_f32())
+            unsupported(*node, "Gelu on element types other than f32");
+        int x = canonical_slot(node->input_value(0));
+        int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+        emit(node, "gelu", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_gelu_f32(static_cast<const float*>(p[x]), static_cast<float*>(p[y]), n_out, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return true;
+    }
     if (auto sm = as_type_ptr<op::v0::Softmax>(node))
     {
         // runtime/reference/softmax.hpp: max over the axes, exp(x - max), Kahan sum, divide: the same five steps

@@ -90,7 +90,8 @@ namespace ngraph
             private:
                 std::shared_ptr<DeviceContext> m_ctx;
                 std::mutex m_mutex;
-                std::unordered_map<std::shared_ptr<Function>, std::shared_ptr<runtime::Executable>> m_cache;
+                // one executable per (Function, performance counters on / off)
+                std::map<std::pair<std::shared_ptr<Function>, bool>, std::shared_ptr<runtime::Executable>> m_cache;
             };
 
             class B200Executable : public runtime::Executable

@@ -17,6 +17,7 @@
 // reference's summation order so that results are identical, not merely close).
 #include <cuda_runtime.h>
 #include <math.h>
+#include <initializer_list>
 #include "common.cuh"
 
 namespace b200
@@ -213,98 +214,257 @@ namespace b200
             out[i] = value;
     }
 
-    // Reductions and Softmax over the LAST axis of a [rows, L] matrix.  The compensated sum has to walk a row in order,
-    // so a row belongs to one thread; reading it straight from memory would make the 32 lanes of a warp touch 32
-    // different rows per load.  A block therefore stages 32 rows in shared memory with coalesced loads (row stride
-    // odd, so the lanes' walks hit different banks), lets all its threads do the order-free parts (max, exp, divide)
-    // and one warp the 32 ordered sums.
+    // Softmax and LayerNorm over the LAST axis of a [rows, L] matrix.  Their compensated sums have to walk a row in
+    // order, so a row belongs to one thread; reading it straight from memory would make the 32 lanes of a warp touch 32
+    // different rows per load.  A block therefore stages 32 rows in shared memory, lets all its threads do the
+    // order-free parts (max, exp, normalise, divide) and one warp the 32 ordered sums, one row per lane.
+    // VEC: L is a multiple of 4 and the pointers are 16-byte aligned, so rows move as float4 with eight loads in flight
+    // per thread (row stride L + 4: the ordered walks then meet 4-way bank conflicts, hidden behind the dependent
+    // additions); otherwise element by element with an odd row stride.
     constexpr int ROWS_PER_TILE = 32;
-    __host__ __device__ inline int staged_row_stride(int L) { return L | 1; }
+    __host__ __device__ inline int staged_row_stride(int L, bool vec) { return vec ? L + 4 : (L | 1); }
 
-    template <bool SOFTMAX>
-    __global__ void __launch_bounds__(128) staged_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int L)
+    template <bool VEC>
+    __device__ __forceinline__ void stage_rows(const float* __restrict__ src, float* tile, int n_rows, int L, int stride)
     {
-        extern __shared__ float tile[];
+        if (VEC)
+        {
+            const int L4 = L >> 2, total = n_rows * L4;
+            const float4* src4 = reinterpret_cast<const float4*>(src);
+            for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * 8)
+            {
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    const int i = i0 + j * blockDim.x;
+                    if (i < total)
+                        v[j] = __ldg(src4 + i);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    const int i = i0 + j * blockDim.x;
+                    if (i < total)
+                        *reinterpret_cast<float4*>(tile + (i / L4) * stride + 4 * (i % L4)) = v[j];
+                }
+            }
+        }
+        else
+            for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                tile[(i / L) * stride + i % L] = src[i];
+    }
+
+    template <bool VEC>
+    __global__ void __launch_bounds__(128) softmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int L)
+    {
+        extern __shared__ __align__(16) float tile[];
         __shared__ float row_max[ROWS_PER_TILE], row_sum[ROWS_PER_TILE];
-        const int stride = staged_row_stride(L);
+        const int stride = staged_row_stride(L, VEC);
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int64_t n_tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
         for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x)
         {
             const int64_t row0 = t * ROWS_PER_TILE;
             const int n_rows = int(rows - row0 < ROWS_PER_TILE ? rows - row0 : ROWS_PER_TILE);
-            const float* src = in + row0 * L;
-            for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
-                tile[(i / L) * stride + i % L] = src[i];
+            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride);
             __syncthreads();
-            if (SOFTMAX)
+            // softmax.hpp: max over the axis (the largest value whatever the order), then exp(x - max)
+            for (int r = warp; r < n_rows; r += 4)
             {
-                // softmax.hpp: max over the axis (the largest value whatever the order), then exp(x - max)
-                for (int r = warp; r < n_rows; r += 4)
+                float m = -INFINITY;
+                for (int c = lane; c < L; c += 32)
                 {
-                    float m = -INFINITY;
-                    for (int c = lane; c < L; c += 32)
-                    {
-                        const float x = tile[r * stride + c];
-                        m = x > m ? x : m;
-                    }
-                    for (int d = 16; d; d >>= 1)
-                    {
-                        const float o = __shfl_xor_sync(0xFFFFFFFFu, m, d);
-                        m = o > m ? o : m;
-                    }
-                    if (lane == 0)
-                        row_max[r] = m;
+                    const float x = tile[r * stride + c];
+                    m = x > m ? x : m;
                 }
-                __syncthreads();
-                for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                for (int d = 16; d; d >>= 1)
                 {
-                    const int r = i / L;
-                    float& v = tile[r * stride + i % L];
-                    v = static_cast<float>(exp(static_cast<double>(__fsub_rn(v, row_max[r]))));
+                    const float o = __shfl_xor_sync(0xFFFFFFFFu, m, d);
+                    m = o > m ? o : m;
                 }
-                __syncthreads();
+                // the same warp owns the row in the next step too, so no block-wide barrier is needed in between
+                for (int c = lane; c < L; c += 32)
+                {
+                    float& v = tile[r * stride + c];
+                    v = static_cast<float>(exp(static_cast<double>(__fsub_rn(v, m))));
+                }
             }
+            __syncthreads();
             if (warp == 0 && lane < n_rows)
             {
                 const float* row = tile + lane * stride;
                 float z = 0.0f, c = 0.0f;
                 for (int k = 0; k < L; ++k)
                     kahan_step(z, c, row[k]);
-                if (SOFTMAX)
-                    row_sum[lane] = z;
-                else
-                    out[row0 + lane] = z;
+                row_sum[lane] = z;
             }
             __syncthreads();
-            if (SOFTMAX)
+            float* dst = out + row0 * L;
+            if (VEC)
             {
-                float* dst = out + row0 * L;
+                const int L4 = L >> 2, total = n_rows * L4;
+                for (int i = threadIdx.x; i < total; i += blockDim.x)
+                {
+                    const int r = i / L4;
+                    float4 v = *reinterpret_cast<const float4*>(tile + r * stride + 4 * (i % L4));
+                    const float sum = row_sum[r];
+                    v.x = __fdiv_rn(v.x, sum), v.y = __fdiv_rn(v.y, sum), v.z = __fdiv_rn(v.z, sum), v.w = __fdiv_rn(v.w, sum);
+                    reinterpret_cast<float4*>(dst)[i] = v;
+                }
+            }
+            else
                 for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
                 {
                     const int r = i / L;
                     dst[i] = __fdiv_rn(tile[r * stride + i % L], row_sum[r]);
                 }
-                __syncthreads();
-            }
+            __syncthreads();
         }
     }
 
-    // Launch of the staged kernel; false when a tile of rows does not fit shared memory.
-    template <bool SOFTMAX>
-    bool launch_staged_rows(const float* in, float* out, int64_t rows, int64_t L, cudaStream_t st)
+    // op::v0::LayerNorm over the last axis with scale and bias, as ONE kernel with the rounding steps of its
+    // decomposition (src/ngraph/op/layer_norm.cpp:68-150 with builder::mean / builder::variance,
+    // src/ngraph/builder/reduce_ops.cpp:68-127), in that order:
+    //   mean = KahanSum(x) / N;  var = KahanSum((x - mean) * (x - mean)) / N;  sd = sqrt(var + eps);
+    //   y = ((x - mean) / sd) * gamma + beta          (every operation a separate IEEE rounding, no fused multiply-add)
+    template <bool VEC>
+    __global__ void __launch_bounds__(128) layer_norm_rows_kernel(const float* __restrict__ in, const float* __restrict__ gamma,
+                                                                  const float* __restrict__ beta, float* __restrict__ out, int64_t rows,
+                                                                  int L, float count, float eps)
     {
-        if (L < 1 || L > 1535)
-            return false;
-        const size_t bytes = size_t(ROWS_PER_TILE) * staged_row_stride(int(L)) * sizeof(float);
+        extern __shared__ __align__(16) float tile[];
+        __shared__ float row_mean[ROWS_PER_TILE], row_sd[ROWS_PER_TILE];
+        const int stride = staged_row_stride(L, VEC);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int64_t n_tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
+        for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x)
+        {
+            const int64_t row0 = t * ROWS_PER_TILE;
+            const int n_rows = int(rows - row0 < ROWS_PER_TILE ? rows - row0 : ROWS_PER_TILE);
+            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride);
+            __syncthreads();
+            if (warp == 0 && lane < n_rows)
+            {
+                const float* row = tile + lane * stride;
+                float z = 0.0f, c = 0.0f;
+                for (int k = 0; k < L; ++k)
+                    kahan_step(z, c, row[k]);
+                const float mean = __fdiv_rn(z, count);
+                z = 0.0f, c = 0.0f;
+                for (int k = 0; k < L; ++k)
+                {
+                    const float d = __fsub_rn(row[k], mean);
+                    kahan_step(z, c, __fmul_rn(d, d));
+                }
+                row_mean[lane] = mean;
+                row_sd[lane] = __fsqrt_rn(__fadd_rn(__fdiv_rn(z, count), eps));
+            }
+            __syncthreads();
+            float* dst = out + row0 * L;
+            if (VEC)
+            {
+                const int L4 = L >> 2, total = n_rows * L4;
+                for (int i = threadIdx.x; i < total; i += blockDim.x)
+                {
+                    const int r = i / L4, k4 = i % L4;
+                    float4 v = *reinterpret_cast<const float4*>(tile + r * stride + 4 * k4);
+                    const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + k4), b = __ldg(reinterpret_cast<const float4*>(beta) + k4);
+                    const float mean = row_mean[r], sd = row_sd[r];
+                    v.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v.x, mean), sd), g.x), b.x);
+                    v.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v.y, mean), sd), g.y), b.y);
+                    v.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v.z, mean), sd), g.z), b.z);
+                    v.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v.w, mean), sd), g.w), b.w);
+                    reinterpret_cast<float4*>(dst)[i] = v;
+                }
+            }
+            else
+                for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
+                {
+                    const int r = i / L, k = i % L;
+                    const float norm = __fdiv_rn(__fsub_rn(tile[r * stride + k], row_mean[r]), row_sd[r]);
+                    dst[i] = __fadd_rn(__fmul_rn(norm, __ldg(gamma + k)), __ldg(beta + k));
+                }
+            __syncthreads();
+        }
+    }
+
+    // op::v0::Gelu with the rounding steps of its decomposition (src/ngraph/op/gelu.cpp:46-60):
+    //   (0.5 * x) * (1 + erf(x / float(sqrt(2.0))))
+    __global__ void __launch_bounds__(256) gelu_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t n)
+    {
+        const float sqrt_two = static_cast<float>(1.4142135623730951);
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const float v = x[i];
+            const float e = static_cast<float>(erf(static_cast<double>(__fdiv_rn(v, sqrt_two))));
+            out[i] = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, e));
+        }
+    }
+
+    // Sum over the last axis for rows of any length: a warp owns 32 rows, one per lane, and walks them 64 columns at a
+    // time; each 32 x 64 panel is fetched with coalesced loads into shared memory (row stride 65: the lanes' walks hit
+    // 32 different banks) and then added in column order with the reference's compensated step.  Many one-warp blocks per
+    // SM overlap one block's loads with another's additions.
+    __global__ void __launch_bounds__(32) sum_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int64_t L)
+    {
+        constexpr int CH = 64;
+        __shared__ float panel[32][CH + 1];
+        const int lane = threadIdx.x;
+        for (int64_t row0 = int64_t(blockIdx.x) * 32; row0 < rows; row0 += int64_t(gridDim.x) * 32)
+        {
+            const int n_rows = int(rows - row0 < 32 ? rows - row0 : 32);
+            float z = 0.0f, c = 0.0f;
+            for (int64_t col0 = 0; col0 < L; col0 += CH)
+            {
+                const int n_col = int(L - col0 < CH ? L - col0 : CH);
+                // lane l fetches columns l and l + 32 of every row: 16 rows at a time, 32 loads in flight
+#pragma unroll
+                for (int r0 = 0; r0 < 32; r0 += 16)
+                {
+                    float v[16][2];
+#pragma unroll
+                    for (int r = 0; r < 16; ++r)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            v[r][h] = (r0 + r < n_rows && lane + 32 * h < n_col) ? in[(row0 + r0 + r) * L + col0 + lane + 32 * h] : 0.0f;
+#pragma unroll
+                    for (int r = 0; r < 16; ++r)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            panel[r0 + r][lane + 32 * h] = v[r][h];
+                }
+                __syncwarp();
+                if (lane < n_rows)
+                    for (int cc = 0; cc < n_col; ++cc)
+                        kahan_step(z, c, panel[lane][cc]);
+                __syncwarp();
+            }
+            if (lane < n_rows)
+                out[row0 + lane] = z;
+        }
+    }
+
+    // Grid and shared memory of the two staged kernels: as many 32-row tiles per SM as fit.
+    template <typename Kernel>
+    bool staged_launch_shape(Kernel kernel, int64_t rows, int L, bool vec, unsigned& grid, size_t& bytes)
+    {
+        bytes = size_t(ROWS_PER_TILE) * staged_row_stride(L, vec) * sizeof(float);
         if (bytes > 48 * 1024 && // the attribute belongs to the current device's copy of the kernel: set it on each use
-            cudaFuncSetAttribute(staged_rows_kernel<SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
             return false;
         const int64_t tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
         const int64_t per_sm = (200 * 1024) / int64_t(bytes) < 8 ? (200 * 1024) / int64_t(bytes) : 8;
-        const int64_t grid = tiles < 148 * per_sm ? tiles : 148 * per_sm;
-        staged_rows_kernel<SOFTMAX><<<unsigned(grid), 128, bytes, st>>>(in, out, rows, int(L));
+        grid = unsigned(tiles < 148 * per_sm ? tiles : 148 * per_sm);
         return true;
+    }
+
+    inline bool all_aligned16(std::initializer_list<const void*> ptrs)
+    {
+        uintptr_t bits = 0;
+        for (const void* p : ptrs)
+            bits |= reinterpret_cast<uintptr_t>(p);
+        return (bits & 15) == 0;
     }
 
     // out[b, m, n] = float(sum_k double(a[b, m, k]) * double(b[b, k, n])), k ascending.  One thread owns a 4 x 4 block
@@ -352,6 +512,94 @@ namespace b200
                     if (m0 + r < M && n0 + c < N)
                         out[(b * M + m0 + r) * N + n0 + c] = static_cast<float>(acc[r][c]);
         }
+    }
+
+    // The same product for large matrices: a block of 256 threads owns a TM x TN tile of one batch entry.  Operands are
+    // converted to double ONCE per block and K chunk into shared memory (the conversion, not the multiply-add, limits
+    // the register-only kernel above), and every thread keeps (TM/16) x (TN/16) double accumulators for the outputs
+    // (ty + 16 i, tx + 16 j).  Each accumulator still receives its products in ascending k, one rounding each, so the
+    // result is bit-identical to the kernel above.  Zero-filled padding beyond M, N or K adds fma(0, 0, acc) = acc.
+    template <int TM, int TN>
+    __global__ void __launch_bounds__(256) bmm_f32_tiled_kernel(const float* __restrict__ a, const float* __restrict__ bm,
+                                                                float* __restrict__ out, int M, int K, int N, int tiles_m, int tiles_n)
+    {
+        constexpr int KC = 32, RM = TM / 16, RN = TN / 16;
+        constexpr int LDA = TM + 2, LDB = TN; // LDA: the transposing store of the A panel spreads over the banks
+        extern __shared__ double panels[];
+        double* As = panels;            // [KC][LDA]  As[k][m]
+        double* Bs = panels + KC * LDA; // [KC][LDB]  Bs[k][n]
+        const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+        const int tile = blockIdx.x;
+        const int tn = tile % tiles_n, tm = (tile / tiles_n) % tiles_m;
+        const int64_t batch = tile / (tiles_n * tiles_m);
+        const int m0 = tm * TM, n0 = tn * TN;
+        const float* ab = a + batch * int64_t(M) * K;
+        const float* bb = bm + batch * int64_t(K) * N;
+        double acc[RM][RN];
+#pragma unroll
+        for (int i = 0; i < RM; ++i)
+#pragma unroll
+            for (int j = 0; j < RN; ++j)
+                acc[i][j] = 0.0;
+        for (int k0 = 0; k0 < K; k0 += KC)
+        {
+            // A panel: TM rows x KC floats, consecutive threads along k (contiguous in memory)
+            for (int i = tid; i < TM * KC; i += 256)
+            {
+                const int m = i / KC, k = i % KC;
+                const bool in = m0 + m < M && k0 + k < K;
+                As[k * LDA + m] = in ? double(ab[int64_t(m0 + m) * K + k0 + k]) : 0.0;
+            }
+            // B panel: KC rows x TN floats, consecutive threads along n
+            for (int i = tid; i < KC * TN; i += 256)
+            {
+                const int k = i / TN, n = i % TN;
+                const bool in = k0 + k < K && n0 + n < N;
+                Bs[k * LDB + n] = in ? double(bb[int64_t(k0 + k) * N + n0 + n]) : 0.0;
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int k = 0; k < KC; ++k)
+            {
+                double x[RM], y[RN];
+#pragma unroll
+                for (int i = 0; i < RM; ++i)
+                    x[i] = As[k * LDA + ty + 16 * i];
+#pragma unroll
+                for (int j = 0; j < RN; ++j)
+                    y[j] = Bs[k * LDB + tx + 16 * j];
+#pragma unroll
+                for (int i = 0; i < RM; ++i)
+#pragma unroll
+                    for (int j = 0; j < RN; ++j)
+                        acc[i][j] = fma(x[i], y[j], acc[i][j]);
+            }
+            __syncthreads();
+        }
+        float* ob = out + batch * int64_t(M) * N;
+#pragma unroll
+        for (int i = 0; i < RM; ++i)
+#pragma unroll
+            for (int j = 0; j < RN; ++j)
+            {
+                const int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
+                if (m < M && n < N)
+                    ob[int64_t(m) * N + n] = static_cast<float>(acc[i][j]);
+            }
+    }
+
+    template <int TM, int TN>
+    bool launch_bmm_tiled(const float* a, const float* b, float* out, int64_t batch, int M, int K, int N, cudaStream_t st)
+    {
+        constexpr size_t bytes = size_t(32) * (TM + 2 + TN) * sizeof(double);
+        if (cudaFuncSetAttribute(bmm_f32_tiled_kernel<TM, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
+            return false;
+        const int tiles_m = (M + TM - 1) / TM, tiles_n = (N + TN - 1) / TN;
+        const int64_t tiles = batch * tiles_m * tiles_n;
+        if (tiles > 0x7FFFFFFF)
+            return false;
+        bmm_f32_tiled_kernel<TM, TN><<<unsigned(tiles), 256, bytes, st>>>(a, b, out, M, K, N, tiles_m, tiles_n);
+        return true;
     }
 
     template <typename I>
@@ -557,9 +805,12 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
     }
     else if (op == B200_REDUCE_MAX && n_out <= 4096 && n_red >= 1024)
         reduce_max_block_kernel<<<unsigned(n_out), 256, 0, st>>>(in, out, keep, red, n_red);
-    else if (op == B200_REDUCE_SUM && n_axes == 1 && axes[0] == rank - 1 && n_out >= 64 &&
-             launch_staged_rows<false>(in, out, n_out, n_red, st))
-        ; // the last axis of a matrix with many rows: staged through shared memory
+    else if (op == B200_REDUCE_SUM && n_axes == 1 && axes[0] == rank - 1 && n_out >= 64)
+    {
+        // the last axis of a matrix with many rows: panels staged through shared memory
+        const int64_t warps = (n_out + 31) / 32, cap = 148 * 16;
+        sum_rows_kernel<<<unsigned(warps < cap ? warps : cap), 32, 0, st>>>(in, out, n_out, n_red);
+    }
     else if (op == B200_REDUCE_SUM)
         reduce_kernel<B200_REDUCE_SUM><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     else if (op == B200_REDUCE_MAX)
@@ -578,9 +829,62 @@ extern "C" int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, i
         return B200_OK;
     if (!x || !out)
         return B200_ERR_INVALID_ARGUMENT;
-    if (!launch_staged_rows<true>(x, out, rows, row_elements, static_cast<cudaStream_t>(stream)))
+    if (row_elements > 1535)
         return B200_ERR_UNSUPPORTED; // a row too long to stage: the caller composes the five steps instead
+    const int L = int(row_elements);
+    const bool vec = L % 4 == 0 && all_aligned16({x, out});
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned grid;
+    size_t bytes;
+    if (!(vec ? staged_launch_shape(softmax_rows_kernel<true>, rows, L, vec, grid, bytes)
+              : staged_launch_shape(softmax_rows_kernel<false>, rows, L, vec, grid, bytes)))
+        return B200_ERR_CUDA;
+    if (vec)
+        softmax_rows_kernel<true><<<grid, 128, bytes, st>>>(x, out, rows, L);
+    else
+        softmax_rows_kernel<false><<<grid, 128, bytes, st>>>(x, out, rows, L);
     return after_launch("b200_softmax_rows_f32");
+}
+
+extern "C" int b200_layer_norm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, int64_t rows,
+                                        int64_t row_elements, float epsilon, void* stream)
+{
+    using namespace b200;
+    if (rows < 0 || row_elements < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (rows * row_elements == 0)
+        return B200_OK;
+    if (!x || !gamma || !beta || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (row_elements > 1535)
+        return B200_ERR_UNSUPPORTED; // a row too long to stage: the caller runs the decomposition
+    const int L = int(row_elements);
+    const bool vec = L % 4 == 0 && all_aligned16({x, gamma, beta, out});
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float count = static_cast<float>(row_elements);
+    unsigned grid;
+    size_t bytes;
+    if (!(vec ? staged_launch_shape(layer_norm_rows_kernel<true>, rows, L, vec, grid, bytes)
+              : staged_launch_shape(layer_norm_rows_kernel<false>, rows, L, vec, grid, bytes)))
+        return B200_ERR_CUDA;
+    if (vec)
+        layer_norm_rows_kernel<true><<<grid, 128, bytes, st>>>(x, gamma, beta, out, rows, L, count, epsilon);
+    else
+        layer_norm_rows_kernel<false><<<grid, 128, bytes, st>>>(x, gamma, beta, out, rows, L, count, epsilon);
+    return after_launch("b200_layer_norm_rows_f32");
+}
+
+extern "C" int b200_gelu_f32(const float* x, float* out, int64_t n, void* stream)
+{
+    using namespace b200;
+    if (n < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (n == 0)
+        return B200_OK;
+    if (!x || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    gelu_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, out, n);
+    return after_launch("b200_gelu_f32");
 }
 
 extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N, void* stream)
@@ -592,8 +896,14 @@ extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t 
         return B200_OK;
     if (!out || (K > 0 && (!a || !b)))
         return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // large products go through the shared-memory kernel; both kernels give the same bits
+    if (M >= 64 && N >= 96 && K >= 16 && launch_bmm_tiled<128, 128>(a, b, out, batch, int(M), int(K), int(N), st))
+        return after_launch("b200_bmm_f32");
+    if (M >= 64 && N >= 48 && K >= 16 && launch_bmm_tiled<128, 64>(a, b, out, batch, int(M), int(K), int(N), st))
+        return after_launch("b200_bmm_f32");
     const int64_t blocks4 = batch * ((M + 3) / 4) * ((N + 3) / 4);
-    bmm_f32_kernel<<<grid_for(blocks4, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, batch, int(M), int(K), int(N));
+    bmm_f32_kernel<<<grid_for(blocks4, 128), 128, 0, st>>>(a, b, out, batch, int(M), int(K), int(N));
     return after_launch("b200_bmm_f32");
 }
 

@@ -372,9 +372,10 @@ class Executable:
         return [t.read() for t in outs]
 
     def performance_data(self):
-        names = ctypes.create_string_buffer(1 << 16)
-        us, calls = (ctypes.c_int64 * 1024)(), (ctypes.c_int64 * 1024)()
-        n = capi().ngc_performance_data(self.h, names, len(names), us, calls, 1024)
+        cap = 1 << 14  # nodes; a 12-layer encoder has a few thousand
+        names = ctypes.create_string_buffer(cap * 96)
+        us, calls = (ctypes.c_int64 * cap)(), (ctypes.c_int64 * cap)()
+        n = capi().ngc_performance_data(self.h, names, len(names), us, calls, cap)
         if n < 0:
             _err("get_performance_data")
         return [(nm, us[i], calls[i]) for i, nm in enumerate(names.value.decode().split("\n")[:n])]

@@ -123,6 +123,45 @@ def test_softmax_rows_equals_the_five_steps(L, rows, n):
     assert abs(float(g[1:].sum()) - (rows - 1)) < 1e-3 * rows
 
 
+@pytest.mark.parametrize("rows,n", [(100, 768), (33, 65), (5, 1535), (64, 1)])
+def test_layer_norm_rows_follows_the_decomposition(L, rows, n):
+    """op::v0::LayerNorm's decomposition (layer_norm.cpp:68-150, reduce_ops.cpp:68-127) step by step in float32"""
+    rng = np.random.default_rng(7)
+    f = np.float32
+    x = (rng.standard_normal((rows, n)) * 3 + 1).astype(f)
+    gamma, beta = rng.standard_normal(n).astype(f), rng.standard_normal(n).astype(f)
+    eps, count = f(1e-5), f(n)
+    mean = (kahan_sum_rows(x) / count).astype(f)
+    d = (x - mean[:, None]).astype(f)
+    var = (kahan_sum_rows((d * d).astype(f)) / count).astype(f)
+    sd = np.sqrt((var + eps).astype(f)).astype(f)
+    want = (((d / sd[:, None]).astype(f) * gamma).astype(f) + beta).astype(f)
+    xd, gd, bd = dev(x), dev(gamma), dev(beta)
+    out = torch.empty((rows, n), device="cuda")
+    L.check(L.LIB.b200_layer_norm_rows_f32(xd.data_ptr(), gd.data_ptr(), bd.data_ptr(), out.data_ptr(), rows, n, ctypes.c_float(1e-5),
+                                           stream()), "layer_norm")
+    np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(want))
+
+
+def test_gelu_equals_its_decomposition_on_the_device(L):
+    """(0.5 * x) * (1 + erf(x / sqrt 2)) of gelu.cpp:46-60 against the same five elementwise kernels run one by one"""
+    x = np.concatenate([np.linspace(-9, 9, 100001), [0.0, -0.0, np.inf, -np.inf]]).astype(np.float32)
+    n = x.size
+    xd = dev(x)
+    c = {k: dev(np.full(n, v, np.float32)) for k, v in (("half", 0.5), ("one", 1.0), ("sqrt2", np.float32(math.sqrt(2.0))))}
+    q, e, t, h, want, got = (torch.empty(n, device="cuda") for _ in range(6))
+    S, P = stream(), lambda a: a.data_ptr()
+    L.check(L.LIB.b200_f32_binary(OPS["div"], P(xd), P(c["sqrt2"]), P(q), n, S), "div")
+    L.check(L.LIB.b200_f32_unary(OPS["erf"], P(q), P(e), n, S), "erf")
+    L.check(L.LIB.b200_f32_binary(OPS["add"], P(c["one"]), P(e), P(t), n, S), "add")
+    L.check(L.LIB.b200_f32_binary(OPS["mul"], P(c["half"]), P(xd), P(h), n, S), "mul")
+    L.check(L.LIB.b200_f32_binary(OPS["mul"], P(h), P(t), P(want), n, S), "mul")
+    L.check(L.LIB.b200_gelu_f32(P(xd), P(got), n, S), "gelu")
+    w, g = want.cpu().numpy(), got.cpu().numpy()
+    np.testing.assert_array_equal(np.isnan(w), np.isnan(g))
+    np.testing.assert_array_equal(bits(np.nan_to_num(g)), bits(np.nan_to_num(w)))
+
+
 def test_broadcast_and_permute(L):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((5, 7)).astype(np.float32)
@@ -142,16 +181,18 @@ def test_broadcast_and_permute(L):
         np.testing.assert_array_equal(o.cpu().numpy(), np.transpose(y, order).ravel())
 
 
-def test_bmm_accumulates_in_double_in_order(L):
+@pytest.mark.parametrize("batch,m,k,n", [(3, 17, 96, 21), (2, 130, 70, 200), (2, 100, 33, 64), (1, 384, 64, 384), (5, 64, 16, 48)])
+def test_bmm_accumulates_in_double_in_order(L, batch, m, k, n):
+    """small products run one thread per 4 x 4 outputs, large ones through shared-memory panels: the same bits either way"""
     rng = np.random.default_rng(4)
-    a = rng.standard_normal((3, 17, 96)).astype(np.float32)
-    b = rng.standard_normal((3, 96, 21)).astype(np.float32)
-    acc = np.zeros((3, 17, 21), np.float64)
-    for k in range(96):
-        acc += a[:, :, k, None].astype(np.float64) * b[:, k, None, :].astype(np.float64)
-    out = torch.empty((3, 17, 21), device="cuda")
+    a = (rng.standard_normal((batch, m, k)) * 50).astype(np.float32)
+    b = (rng.standard_normal((batch, k, n)) * 50).astype(np.float32)
+    acc = np.zeros((batch, m, n), np.float64)
+    for kk in range(k):
+        acc += a[:, :, kk, None].astype(np.float64) * b[:, kk, None, :].astype(np.float64)
+    out = torch.empty((batch, m, n), device="cuda")
     ad, bd = dev(a), dev(b)  # kept alive until the result has been read
-    L.check(L.LIB.b200_bmm_f32(ad.data_ptr(), bd.data_ptr(), out.data_ptr(), 3, 17, 96, 21, stream()), "bmm")
+    L.check(L.LIB.b200_bmm_f32(ad.data_ptr(), bd.data_ptr(), out.data_ptr(), batch, m, k, n, stream()), "bmm")
     np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(acc.astype(np.float32)))
 
 

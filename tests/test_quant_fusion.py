@@ -240,7 +240,7 @@ def test_unfused_residual_block_tail(backends, sum_dtype):
     s_left, s_right = np.float32(0.05), np.float32(0.04)
     exe = b200.compile(conv_add_graph(filt, bias, scale, s_left, s_right, sum_dtype, out_shape, quantize_after=s_left), perf=True)
     got = exe.run(data, summand)[0]
-    steps = [n.split("_")[0] for n, _, _ in exe.performance_data()]
+    steps = [n.split(":")[0] for n, _, _ in exe.performance_data()]
     assert "Relu" not in steps and "Add" not in steps and "Quantize" not in steps and "Dequantize" not in steps
     d, s = ng.parameter(np.uint8, DS), ng.parameter(sum_dtype, out_shape)
     fused = interpreter.decomposed_conv(d, ng.constant(filt), ng.constant(bias), ng.constant(scale), np.uint8, True,
