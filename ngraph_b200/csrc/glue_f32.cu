@@ -86,12 +86,61 @@ namespace b200
             out[i] = unary_op<OP>(x[i]);
     }
 
-    // out[idx] = in[mapped(idx)] for 4-byte elements: Broadcast (stride 0 on the new axes) and axis permutations
-    __global__ void __launch_bounds__(256) remap_b32_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, Dims d,
-                                                            int64_t n)
+    // out[idx] = in[mapped(idx)] for 4-byte elements: Broadcast (stride 0 on the new axes) and axis permutations.
+    // T: one element (uint32_t) or four neighbours along a last axis that both tensors share (uint4); IDX: 32-bit index
+    // arithmetic when every index and offset fits (a 64-bit division costs several times a 32-bit one).
+    template <typename T, typename IDX>
+    __global__ void __launch_bounds__(256) remap_kernel(const T* __restrict__ in, T* __restrict__ out, Dims d, int64_t n)
     {
+        IDX dim[MAX_RANK], stride[MAX_RANK];
+#pragma unroll
+        for (int a = 0; a < MAX_RANK; ++a)
+        {
+            dim[a] = a < d.rank ? IDX(d.out_dim[a]) : IDX(1);
+            stride[a] = a < d.rank ? IDX(d.in_stride[a]) : IDX(0);
+        }
         for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
-            out[i] = in[mapped_offset(d, i)];
+        {
+            IDX idx = IDX(i), off = 0;
+#pragma unroll
+            for (int a = MAX_RANK - 1; a >= 0; --a)
+                if (a < d.rank)
+                {
+                    const IDX q = idx / dim[a];
+                    off += (idx - q * dim[a]) * stride[a];
+                    idx = q;
+                }
+            out[i] = in[off];
+        }
+    }
+
+    // Picks the widest form the tensors allow.  `d` describes the output axes and the input stride of each.
+    static void launch_remap(const void* in, void* out, Dims d, int64_t n, int64_t in_elements, cudaStream_t st)
+    {
+        const int last = d.rank - 1;
+        bool wide = d.rank >= 1 && d.in_stride[last] == 1 && d.out_dim[last] % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+        for (int a = 0; wide && a < last; ++a)
+            wide = d.in_stride[a] % 4 == 0;
+        if (wide)
+        {
+            d.out_dim[last] /= 4;
+            for (int a = 0; a < last; ++a)
+                d.in_stride[a] /= 4;
+            n /= 4;
+            in_elements /= 4;
+        }
+        const bool small = n < (int64_t(1) << 31) && in_elements < (int64_t(1) << 31);
+        const int64_t blocks = (n + 255) / 256, cap = 148 * 16;
+        const unsigned grid = unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+        if (wide && small)
+            remap_kernel<uint4, uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), d, n);
+        else if (wide)
+            remap_kernel<uint4, int64_t><<<grid, 256, 0, st>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), d, n);
+        else if (small)
+            remap_kernel<uint32_t, uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), d, n);
+        else
+            remap_kernel<uint32_t, int64_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), d, n);
     }
 
     // One thread per output element; the reduced coordinates are walked in row-major order, as the reference does.
@@ -718,8 +767,7 @@ extern "C" int b200_broadcast_b32(const void* in, void* out, const int64_t* out_
         if (!is_new[a])
             stride *= out_shape[a];
     }
-    remap_b32_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
-                                                                                      static_cast<uint32_t*>(out), d, n);
+    launch_remap(in, out, d, n, stride, static_cast<cudaStream_t>(stream)); // stride: the input's element count by now
     return after_launch("b200_broadcast_b32");
 }
 
@@ -754,8 +802,7 @@ extern "C" int b200_permute_b32(const void* in, void* out, const int64_t* in_sha
         d.out_dim[a] = in_shape[order[a]];
         d.in_stride[a] = in_stride[order[a]];
     }
-    remap_b32_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(in),
-                                                                                      static_cast<uint32_t*>(out), d, n);
+    launch_remap(in, out, d, n, n, static_cast<cudaStream_t>(stream));
     return after_launch("b200_permute_b32");
 }
 

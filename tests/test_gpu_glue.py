@@ -173,12 +173,21 @@ def test_broadcast_and_permute(L):
     one = dev(np.float32([2.5]))
     L.check(L.LIB.b200_broadcast_b32(one.data_ptr(), s.data_ptr(), i64([6]), 1, i64([0]), 1, stream()), "broadcast")
     assert (s.cpu().numpy() == 2.5).all()
-    y = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
-    yd = dev(y)
-    for order in ((0, 2, 1, 3), (0, 2, 3, 1), (3, 2, 1, 0)):
-        o = torch.empty(y.size, device="cuda")
-        L.check(L.LIB.b200_permute_b32(yd.data_ptr(), o.data_ptr(), i64(y.shape), 4, i64(order), stream()), "permute")
-        np.testing.assert_array_equal(o.cpu().numpy(), np.transpose(y, order).ravel())
+    for shape in ((2, 3, 4, 5), (3, 16, 5, 8)):  # last axis 8: four neighbours move together when it stays last
+        y = rng.standard_normal(shape).astype(np.float32)
+        yd = dev(y)
+        for order in ((0, 2, 1, 3), (0, 2, 3, 1), (3, 2, 1, 0), (1, 0, 2, 3)):
+            o = torch.empty(y.size, device="cuda")
+            L.check(L.LIB.b200_permute_b32(yd.data_ptr(), o.data_ptr(), i64(y.shape), 4, i64(order), stream()), "permute")
+            np.testing.assert_array_equal(o.cpu().numpy(), np.transpose(y, order).ravel())
+    x8 = rng.standard_normal((5, 8)).astype(np.float32)
+    x8d, out8 = dev(x8), torch.empty((3, 5, 4, 8), device="cuda")
+    L.check(L.LIB.b200_broadcast_b32(x8d.data_ptr(), out8.data_ptr(), i64(out8.shape), 4, i64([0, 2]), 2, stream()), "broadcast")
+    np.testing.assert_array_equal(out8.cpu().numpy(), np.broadcast_to(x8[None, :, None, :], (3, 5, 4, 8)))
+    col = rng.standard_normal(6).astype(np.float32)  # a new LAST axis: every output row repeats one value
+    cold, outc = dev(col), torch.empty((6, 8), device="cuda")
+    L.check(L.LIB.b200_broadcast_b32(cold.data_ptr(), outc.data_ptr(), i64([6, 8]), 2, i64([1]), 1, stream()), "broadcast")
+    np.testing.assert_array_equal(outc.cpu().numpy(), np.broadcast_to(col[:, None], (6, 8)))
 
 
 @pytest.mark.parametrize("batch,m,k,n", [(3, 17, 96, 21), (2, 130, 70, 200), (2, 100, 33, 64), (1, 384, 64, 384), (5, 64, 16, 48)])
