@@ -568,11 +568,11 @@ namespace b200
     // the register-only kernel above), and every thread keeps (TM/16) x (TN/16) double accumulators for the outputs
     // (ty + 16 i, tx + 16 j).  Each accumulator still receives its products in ascending k, one rounding each, so the
     // result is bit-identical to the kernel above.  Zero-filled padding beyond M, N or K adds fma(0, 0, acc) = acc.
-    template <int TM, int TN>
+    template <int TM, int TN, int KC>
     __global__ void __launch_bounds__(256) bmm_f32_tiled_kernel(const float* __restrict__ a, const float* __restrict__ bm,
                                                                 float* __restrict__ out, int M, int K, int N, int tiles_m, int tiles_n)
     {
-        constexpr int KC = 32, RM = TM / 16, RN = TN / 16;
+        constexpr int RM = TM / 16, RN = TN / 16;
         constexpr int LDA = TM + 2, LDB = TN; // LDA: the transposing store of the A panel spreads over the banks
         extern __shared__ double panels[];
         double* As = panels;            // [KC][LDA]  As[k][m]
@@ -590,23 +590,45 @@ namespace b200
 #pragma unroll
             for (int j = 0; j < RN; ++j)
                 acc[i][j] = 0.0;
+        // the panels of chunk c + 1 travel from memory into registers while chunk c is multiplied out of shared memory
+        constexpr int A_PER = TM * KC / 256, B_PER = KC * TN / 256;
+        float ra[A_PER], rb[B_PER];
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int j = 0; j < A_PER; ++j)
+            {
+                const int i = tid + j * 256, m = i / KC, k = i % KC; // consecutive threads along k (contiguous in memory)
+                ra[j] = (m0 + m < M && k0 + k < K) ? ab[int64_t(m0 + m) * K + k0 + k] : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < B_PER; ++j)
+            {
+                const int i = tid + j * 256, k = i / TN, n = i % TN; // consecutive threads along n
+                rb[j] = (k0 + k < K && n0 + n < N) ? bb[int64_t(k0 + k) * N + n0 + n] : 0.0f;
+            }
+        };
+        auto stash = [&]() {
+#pragma unroll
+            for (int j = 0; j < A_PER; ++j)
+            {
+                const int i = tid + j * 256;
+                As[(i % KC) * LDA + i / KC] = double(ra[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < B_PER; ++j)
+            {
+                const int i = tid + j * 256;
+                Bs[(i / TN) * LDB + i % TN] = double(rb[j]);
+            }
+        };
+        fetch(0);
+        stash();
+        __syncthreads();
         for (int k0 = 0; k0 < K; k0 += KC)
         {
-            // A panel: TM rows x KC floats, consecutive threads along k (contiguous in memory)
-            for (int i = tid; i < TM * KC; i += 256)
-            {
-                const int m = i / KC, k = i % KC;
-                const bool in = m0 + m < M && k0 + k < K;
-                As[k * LDA + m] = in ? double(ab[int64_t(m0 + m) * K + k0 + k]) : 0.0;
-            }
-            // B panel: KC rows x TN floats, consecutive threads along n
-            for (int i = tid; i < KC * TN; i += 256)
-            {
-                const int k = i / TN, n = i % TN;
-                const bool in = k0 + k < K && n0 + n < N;
-                Bs[k * LDB + n] = in ? double(bb[int64_t(k0 + k) * N + n0 + n]) : 0.0;
-            }
-            __syncthreads();
+            const bool more = k0 + KC < K;
+            if (more)
+                fetch(k0 + KC);
 #pragma unroll 4
             for (int k = 0; k < KC; ++k)
             {
@@ -624,6 +646,11 @@ namespace b200
                         acc[i][j] = fma(x[i], y[j], acc[i][j]);
             }
             __syncthreads();
+            if (more)
+            {
+                stash();
+                __syncthreads();
+            }
         }
         float* ob = out + batch * int64_t(M) * N;
 #pragma unroll
@@ -637,17 +664,17 @@ namespace b200
             }
     }
 
-    template <int TM, int TN>
+    template <int TM, int TN, int KC>
     bool launch_bmm_tiled(const float* a, const float* b, float* out, int64_t batch, int M, int K, int N, cudaStream_t st)
     {
-        constexpr size_t bytes = size_t(32) * (TM + 2 + TN) * sizeof(double);
-        if (cudaFuncSetAttribute(bmm_f32_tiled_kernel<TM, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
+        constexpr size_t bytes = size_t(KC) * (TM + 2 + TN) * sizeof(double);
+        if (cudaFuncSetAttribute(bmm_f32_tiled_kernel<TM, TN, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
             return false;
         const int tiles_m = (M + TM - 1) / TM, tiles_n = (N + TN - 1) / TN;
         const int64_t tiles = batch * tiles_m * tiles_n;
         if (tiles > 0x7FFFFFFF)
             return false;
-        bmm_f32_tiled_kernel<TM, TN><<<unsigned(tiles), 256, bytes, st>>>(a, b, out, M, K, N, tiles_m, tiles_n);
+        bmm_f32_tiled_kernel<TM, TN, KC><<<unsigned(tiles), 256, bytes, st>>>(a, b, out, M, K, N, tiles_m, tiles_n);
         return true;
     }
 
@@ -945,9 +972,9 @@ extern "C" int b200_bmm_f32(const float* a, const float* b, float* out, int64_t 
         return B200_ERR_INVALID_ARGUMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // large products go through the shared-memory kernel; both kernels give the same bits
-    if (M >= 64 && N >= 96 && K >= 16 && launch_bmm_tiled<128, 128>(a, b, out, batch, int(M), int(K), int(N), st))
+    if (M >= 64 && N >= 96 && K >= 16 && launch_bmm_tiled<128, 128, 16>(a, b, out, batch, int(M), int(K), int(N), st))
         return after_launch("b200_bmm_f32");
-    if (M >= 64 && N >= 48 && K >= 16 && launch_bmm_tiled<128, 64>(a, b, out, batch, int(M), int(K), int(N), st))
+    if (M >= 64 && N >= 48 && K >= 16 && launch_bmm_tiled<128, 64, 32>(a, b, out, batch, int(M), int(K), int(N), st))
         return after_launch("b200_bmm_f32");
     const int64_t blocks4 = batch * ((M + 3) / 4) * ((N + 3) / 4);
     bmm_f32_kernel<<<grid_for(blocks4, 128), 128, 0, st>>>(a, b, out, batch, int(M), int(K), int(N));
