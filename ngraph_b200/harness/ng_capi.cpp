@@ -368,6 +368,19 @@ NGC_API int ngc_tensor_read(void* t, void* data, int64_t bytes)
     return guarded([&]() -> int { (*static_cast<std::shared_ptr<runtime::Tensor>*>(t))->read(data, size_t(bytes)); return 0; }, -1);
 }
 
+// Executable::create_input_tensor / create_output_tensor with a pipeline depth (src/ngraph/runtime/executable.hpp):
+// `depth` tensors for parameter / result `index`, the double-buffering hook nbench's --double_buffer mode uses
+NGC_API int ngc_executable_create_tensors(void* exe, int is_input, int index, int depth, void** out)
+{
+    return guarded([&]() -> int {
+        auto& e = *static_cast<std::shared_ptr<runtime::Executable>*>(exe);
+        auto v = is_input ? e->create_input_tensor(size_t(index), size_t(depth)) : e->create_output_tensor(size_t(index), size_t(depth));
+        if (int(v.size()) != depth) throw std::runtime_error("create_*_tensor returned another pipeline depth");
+        for (int i = 0; i < depth; ++i) out[i] = new std::shared_ptr<runtime::Tensor>(v[i]);
+        return 0;
+    }, -1);
+}
+
 NGC_API int ngc_call(void* exe, void** outs, int n_out, void** ins, int n_in, int validate)
 {
     return guarded([&]() -> int {

@@ -63,6 +63,7 @@ def capi():
             "ngc_tensor_free": (None, [vp]),
             "ngc_tensor_write": (ci, [vp, vp, i64]), "ngc_tensor_read": (ci, [vp, vp, i64]),
             "ngc_call": (ci, [vp, pvp, ci, pvp, ci, ci]),
+            "ngc_executable_create_tensors": (ci, [vp, ci, ci, ci, pvp]),
             "ngc_performance_data": (ci, [vp, ctypes.c_char_p, ci, p64, p64, ci]),
         }
         for name, (res, args) in sigs.items():
@@ -314,6 +315,12 @@ class Tensor:
         if not self.h:
             _err("create_tensor")
 
+    @classmethod
+    def from_handle(cls, backend, dtype, shape, handle):
+        t = cls.__new__(cls)
+        t.dtype, t.shape, t.backend, t.h = np.dtype(dtype), tuple(int(s) for s in shape), backend, handle
+        return t
+
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
             _lib.ngc_tensor_free(self.h)
@@ -359,6 +366,20 @@ class Executable:
         i = (ctypes.c_void_p * max(len(inputs), 1))(*[t.h for t in inputs])
         if capi().ngc_call(self.h, o, len(outputs), i, len(inputs), int(validate)) != 0:
             _err("Executable::call")
+
+    def _pipeline_tensors(self, is_input, index, depth):
+        spec = (self.function.params if is_input else self.function.results)[index]
+        handles = (ctypes.c_void_p * depth)()
+        if capi().ngc_executable_create_tensors(self.h, int(is_input), index, depth, handles) != 0:
+            _err("Executable::create_%s_tensor" % ("input" if is_input else "output"))
+        return [Tensor.from_handle(self.backend, spec.dtype, spec.shape, h) for h in handles]
+
+    def create_input_tensors(self, index, depth):
+        """Executable::create_input_tensor(index, pipeline_depth): `depth` tensors for one Parameter"""
+        return self._pipeline_tensors(True, index, depth)
+
+    def create_output_tensors(self, index, depth):
+        return self._pipeline_tensors(False, index, depth)
 
     def run(self, *arrays):
         """create tensors, write the inputs, call_with_validate, read every result."""
