@@ -63,6 +63,7 @@
 #include "ngraph/op/reshape.hpp"
 #include "ngraph/op/result.hpp"
 #include "ngraph/pass/constant_folding.hpp"
+#include "ngraph/pass/implicit_broadcast_elimination.hpp"
 #include "ngraph/pass/fused_op_decomposition.hpp"
 #include "ngraph/pass/like_replacement.hpp"
 #include "ngraph/pass/manager.hpp"
@@ -644,6 +645,7 @@ static void run_graph_passes(const std::shared_ptr<Function>& function)
         pm.register_pass<ngraph::pass::FusedOpDecomposition>();
     else
         pm.register_pass<ngraph::pass::FusedOpDecomposition>(runs_undecomposed);
+    pm.register_pass<ngraph::pass::ImplicitBroadcastElimination>(); // NumPy-style operands become explicit Broadcast nodes
     if (ngraph::runtime::b200::pass::quant_fusion_enabled())
         pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
     pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind

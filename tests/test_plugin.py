@@ -373,6 +373,20 @@ def test_small_network_with_pooling_head(backends):
 
 @pytest.mark.gpu
 @needs_ngraph
+def test_numpy_style_broadcasting_in_elementwise_ops(backends):
+    """op::v1 binary ops broadcast their operands NumPy-style; compile() makes the broadcasts explicit
+    (pass::ImplicitBroadcastElimination) before it lowers"""
+    rng = np.random.default_rng(12)
+    a, b, c = ng.parameter(np.float32, (4, 3, 5)), ng.parameter(np.float32, (5,)), ng.parameter(np.float32, (3, 1))
+    fn = ng.Function([ng.multiply(ng.add(a, b), c)], [a, b, c])
+    xs = [rng.standard_normal(p.shape).astype(np.float32) for p in (a, b, c)]
+    got, exp = run_both(backends, fn, fn, xs)
+    same_bits(got[0], exp[0])
+    np.testing.assert_array_equal(got[0], ((xs[0] + xs[1]) * xs[2]).astype(np.float32))
+
+
+@pytest.mark.gpu
+@needs_ngraph
 def test_api_contract(backends):
     """create_tensor / validate / foreign tensors / unsupported ops (test/backend/api.in.cpp,
     validate_call.in.cpp, unhandled_op.in.cpp restated)."""
