@@ -412,6 +412,9 @@ B200_API int b200_qconv_stem_static(const void* in_nchw, int data_type, const in
  * kernel the INTERPRETER backend runs, so that results are identical and not merely close:
  *   b200_f32_binary      Add, Subtract, Multiply, Divide, Maximum, Minimum on equal shapes
  *                        (runtime/reference/add.hpp, subtract.hpp, multiply.hpp, divide.hpp, maximum.hpp, minimum.hpp)
+ *   b200_f32_binary_periodic the same ops where one operand is a small tensor v that an op::v0::Broadcast would repeat along
+ *                        new LEADING axes (a bias row added to every row, a scalar factor): out[i] = a[i] op v[i % period]
+ *                        (v op a[i] with v_is_left), without the broadcast copy; n must be a multiple of period
  *   b200_f32_unary       Abs, Negative, Sqrt, Exp, Erf, Relu (abs.hpp, negate.hpp, sqrt.hpp, exp.hpp, erf.hpp, relu.hpp);
  *                        Exp and Erf are the double routine rounded to float
  *   b200_broadcast_b32   op::v0::Broadcast for 4-byte elements (broadcast.hpp): out_shape and the axes that are new
@@ -451,10 +454,13 @@ typedef enum b200_reduce_op
 {
     B200_REDUCE_SUM = 0,
     B200_REDUCE_MAX = 1,
-    B200_REDUCE_MIN = 2
+    B200_REDUCE_MIN = 2,
+    B200_REDUCE_MAX_ABS = 3 /* Max over Abs(x): the two ops of a dynamic activation scale in one pass */
 } b200_reduce_op;
 
 B200_API int b200_f32_binary(int op, const float* a, const float* b, float* out, int64_t n, void* stream);
+B200_API int b200_f32_binary_periodic(int op, const float* a, const float* v, float* out, int64_t n, int64_t period,
+                                      int v_is_left, void* stream);
 B200_API int b200_f32_unary(int op, const float* x, float* out, int64_t n, void* stream);
 B200_API int b200_broadcast_b32(const void* in, void* out, const int64_t* out_shape, int rank, const int64_t* broadcast_axes,
                                 int n_axes, void* stream);

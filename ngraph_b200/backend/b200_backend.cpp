@@ -47,6 +47,7 @@
 #include "ngraph/op/relu.hpp"
 #include "ngraph/op/softmax.hpp"
 #include "ngraph/op/sqrt.hpp"
+#include "ngraph/op/stop_gradient.hpp"
 #include "ngraph/op/subtract.hpp"
 #include "ngraph/op/sum.hpp"
 #include "ngraph/op/constant.hpp"
@@ -637,19 +638,59 @@ static bool runs_undecomposed(const Node& node)
     return false;
 }
 
+// ConstantFolding turns Broadcast(Constant) into a Constant as large as the broadcast's output: a 768-element bias
+// row added to 24 576 rows becomes 75 MB of constant data, per layer.  Broadcasts of that kind (new leading axes only,
+// at least 64 Ki output elements) are fenced off with an identity op that has no folder (StopGradient) while the pass
+// runs; the elementwise op that reads the Broadcast then indexes the small constant directly (compile_f32_glue).
+static void fence_large_constant_broadcasts(const std::shared_ptr<Function>& function)
+{
+    for (auto& node : function->get_ordered_ops())
+    {
+        auto bc = as_type_ptr<op::v0::Broadcast>(node);
+        if (!bc || !is_type<op::v0::Constant>(bc->input_value(0).get_node()) || shape_size(bc->get_output_shape(0)) < 65536)
+            continue;
+        const AxisSet& added = bc->get_broadcast_axes();
+        bool leading = !added.empty();
+        for (size_t i = 0; i < added.size() && leading; ++i)
+            leading = added.count(i) == 1;
+        if (leading)
+            bc->input(0).replace_source_output(std::make_shared<op::v0::StopGradient>(bc->input_value(0))->output(0));
+    }
+}
+
+static void remove_fences(const std::shared_ptr<Function>& function)
+{
+    for (auto& node : function->get_ordered_ops())
+        if (is_type<op::v0::StopGradient>(node))
+            node->output(0).replace(node->input_value(0));
+}
+
 static void run_graph_passes(const std::shared_ptr<Function>& function)
 {
-    ngraph::pass::Manager pm;
-    pm.register_pass<ngraph::pass::LikeReplacement>();
-    if (getenv("B200_DECOMPOSE_ALL")) // the float islands as chains of elementwise ops and reductions (for comparison)
-        pm.register_pass<ngraph::pass::FusedOpDecomposition>();
-    else
-        pm.register_pass<ngraph::pass::FusedOpDecomposition>(runs_undecomposed);
-    pm.register_pass<ngraph::pass::ImplicitBroadcastElimination>(); // NumPy-style operands become explicit Broadcast nodes
-    if (ngraph::runtime::b200::pass::quant_fusion_enabled())
-        pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
-    pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind
-    pm.run_passes(function);
+    bool fenced = false;
+    for (auto& node : function->get_ordered_ops()) // a graph that has such nodes of its own is left as it is
+        fenced = fenced || is_type<op::v0::StopGradient>(node);
+    {
+        ngraph::pass::Manager pre;
+        pre.register_pass<ngraph::pass::LikeReplacement>();
+        if (getenv("B200_DECOMPOSE_ALL")) // the float islands as chains of elementwise ops and reductions (for comparison)
+            pre.register_pass<ngraph::pass::FusedOpDecomposition>();
+        else
+            pre.register_pass<ngraph::pass::FusedOpDecomposition>(runs_undecomposed);
+        pre.register_pass<ngraph::pass::ImplicitBroadcastElimination>(); // NumPy-style operands become explicit Broadcast nodes
+        pre.run_passes(function);
+    }
+    if (!fenced)
+        fence_large_constant_broadcasts(function);
+    {
+        ngraph::pass::Manager pm;
+        if (ngraph::runtime::b200::pass::quant_fusion_enabled())
+            pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
+        pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind
+        pm.run_passes(function);
+    }
+    if (!fenced)
+        remove_fences(function);
 }
 
 // For tests and tools: applies compile()'s graph passes to *function (a std::shared_ptr<ngraph::Function>*) in place,
@@ -939,6 +980,22 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
             unsupported(*node, "elementwise arithmetic on element types other than f32");
         if (node->get_input_shape(0) != os || node->get_input_shape(1) != os)
             unsupported(*node, "implicit broadcasting (use an explicit Broadcast)");
+        // an operand that is a Broadcast along new leading axes, left unmaterialised for this op (see below)
+        for (int side = 0; side < 2; ++side)
+        {
+            Output<Node> bc = node->input_value(side);
+            if (!value_of(bc).skipped || !is_type<op::v0::Broadcast>(bc.get_node()))
+                continue;
+            const int64_t period = int64_t(shape_size(bc.get_node()->get_input_shape(0)));
+            int v = canonical_slot(bc.get_node()->input_value(0)), a = canonical_slot(node->input_value(1 - side));
+            int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
+            emit(node, "f32_binary_periodic", [=](const Ptrs& p, cudaStream_t st) {
+                return b200_f32_binary_periodic(bop, static_cast<const float*>(p[a]), static_cast<const float*>(p[v]),
+                                                static_cast<float*>(p[y]), n_out, period, side == 0, st);
+            });
+            value_of(node->output(0)).canonical = y;
+            return true;
+        }
         int a = canonical_slot(node->input_value(0)), b = canonical_slot(node->input_value(1));
         int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
         emit(node, "f32_binary", [=](const Ptrs& p, cudaStream_t st) {
@@ -949,6 +1006,12 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
         return true;
     }
 
+    // Abs whose only reader is a Max (max |x| of a dynamic activation scale): the Max reads x itself
+    if (is_type<op::v0::Abs>(node) && all_f32() && only_user(node->output(0)) && is_type<op::v0::Max>(only_user(node->output(0))))
+    {
+        value_of(node->output(0)).skipped = true;
+        return true;
+    }
     int uop = -1;
     if (is_type<op::v0::Abs>(node)) uop = B200_F32_ABS;
     else if (is_type<op::v0::Negative>(node)) uop = B200_F32_NEG;
@@ -973,6 +1036,29 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
     {
         if (ot.size() != 4 || os.size() > 8)
             unsupported(*node, "Broadcast of element types that are not 4 bytes wide");
+        // A Broadcast that only adds LEADING axes repeats its input every shape_size(input) elements.  When its one
+        // reader is an f32 elementwise op whose other operand is a real tensor, that op indexes the small input itself and
+        // the copy (as large as the op's output) is never written.
+        {
+            const AxisSet& added = bc->get_broadcast_axes();
+            bool leading = ot == element::f32 && !added.empty();
+            for (size_t i = 0; i < added.size() && leading; ++i)
+                leading = added.count(i) == 1;
+            const Node* user = only_user(node->output(0));
+            const bool elementwise = user && (is_type<op::v1::Add>(user) || is_type<op::v1::Subtract>(user) || is_type<op::v1::Multiply>(user) ||
+                                              is_type<op::v1::Divide>(user) || is_type<op::v1::Maximum>(user) || is_type<op::v1::Minimum>(user));
+            if (leading && elementwise && user->get_input_size() == 2 && user->get_output_element_type(0) == element::f32 &&
+                user->get_input_shape(0) == os && user->get_input_shape(1) == os)
+            {
+                const Node* other = user->input_value(0).get_node() == node.get() ? user->input_value(1).get_node()
+                                                                                   : user->input_value(0).get_node();
+                if (other != node.get() && !is_type<op::v0::Broadcast>(other))
+                {
+                    value_of(node->output(0)).skipped = true;
+                    return true;
+                }
+            }
+        }
         int x = canonical_slot(node->input_value(0));
         int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
         std::vector<int64_t> shape(os.begin(), os.end());
@@ -988,7 +1074,7 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
     auto emit_reduce = [&](int rop, int x, const Shape& in_shape, const AxisSet& axes_set, int y) {
         std::vector<int64_t> shape(in_shape.begin(), in_shape.end());
         std::vector<int64_t> axes(axes_set.begin(), axes_set.end());
-        emit(node, rop == B200_REDUCE_SUM ? "reduce_sum" : rop == B200_REDUCE_MAX ? "reduce_max" : "reduce_min", [=](const Ptrs& p, cudaStream_t st) {
+        emit(node, rop == B200_REDUCE_SUM ? "reduce_sum" : rop == B200_REDUCE_MIN ? "reduce_min" : "reduce_max", [=](const Ptrs& p, cudaStream_t st) {
             return b200_reduce_f32(rop, static_cast<const float*>(p[x]), static_cast<float*>(p[y]), shape.data(), int(shape.size()),
                                    axes.data(), int(axes.size()), st);
         });
@@ -1001,9 +1087,16 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
         AxisSet axes = is_sum ? as_type_ptr<op::v0::Sum>(node)->get_reduction_axes()
                               : is_max ? as_type_ptr<op::v0::Max>(node)->get_reduction_axes()
                                        : as_type_ptr<op::v0::Min>(node)->get_reduction_axes();
-        int x = canonical_slot(node->input_value(0));
+        int rop = is_sum ? B200_REDUCE_SUM : is_max ? B200_REDUCE_MAX : B200_REDUCE_MIN;
+        Output<Node> source = node->input_value(0);
+        if (is_max && value_of(source).skipped && is_type<op::v0::Abs>(source.get_node()))
+        {
+            source = source.get_node()->input_value(0);
+            rop = B200_REDUCE_MAX_ABS;
+        }
+        int x = canonical_slot(source);
         int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
-        emit_reduce(is_sum ? B200_REDUCE_SUM : is_max ? B200_REDUCE_MAX : B200_REDUCE_MIN, x, node->get_input_shape(0), axes, y);
+        emit_reduce(rop, x, node->get_input_shape(0), axes, y);
         value_of(node->output(0)).canonical = y;
         return true;
     }

@@ -65,6 +65,51 @@ namespace b200
             out[i] = binary_op<OP>(a[i], b[i]);
     }
 
+    // One operand is a small tensor that op::v0::Broadcast would repeat along new leading axes (a bias row, a scalar
+    // factor): element i of the large operand meets v[i % period] instead of a materialised copy.  V_LEFT: v is the
+    // left-hand operand.  Four neighbours at a time when `period` allows it.
+    template <int OP, bool V_LEFT, bool VEC>
+    __global__ void __launch_bounds__(256) binary_periodic_kernel(const float* __restrict__ a, const float* __restrict__ v,
+                                                                  float* __restrict__ out, int64_t n, int64_t period)
+    {
+        if (VEC)
+        {
+            const int64_t n4 = n >> 2, p4 = period >> 2; // period == 1: p4 == 0
+            const float4* a4 = reinterpret_cast<const float4*>(a);
+            const float s = p4 == 0 ? __ldg(v) : 0.0f;
+            for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += int64_t(gridDim.x) * blockDim.x)
+            {
+                const float4 x = a4[i];
+                const float4 y = p4 == 0 ? make_float4(s, s, s, s) : __ldg(reinterpret_cast<const float4*>(v) + i % p4);
+                float4 r;
+                r.x = V_LEFT ? binary_op<OP>(y.x, x.x) : binary_op<OP>(x.x, y.x);
+                r.y = V_LEFT ? binary_op<OP>(y.y, x.y) : binary_op<OP>(x.y, y.y);
+                r.z = V_LEFT ? binary_op<OP>(y.z, x.z) : binary_op<OP>(x.z, y.z);
+                r.w = V_LEFT ? binary_op<OP>(y.w, x.w) : binary_op<OP>(x.w, y.w);
+                reinterpret_cast<float4*>(out)[i] = r;
+            }
+        }
+        else
+            for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+            {
+                const float x = a[i], y = __ldg(v + i % period);
+                out[i] = V_LEFT ? binary_op<OP>(y, x) : binary_op<OP>(x, y);
+            }
+    }
+
+    template <int OP>
+    void launch_binary_periodic(const float* a, const float* v, float* out, int64_t n, int64_t period, bool v_left, cudaStream_t st)
+    {
+        const bool vec = n % 4 == 0 && (period == 1 || period % 4 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out) | (period == 1 ? 0 : reinterpret_cast<uintptr_t>(v))) & 15) == 0;
+        const int64_t work = vec ? n / 4 : n, blocks = (work + 255) / 256, cap = 148 * 16;
+        const unsigned g = unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+        if (vec && v_left) binary_periodic_kernel<OP, true, true><<<g, 256, 0, st>>>(a, v, out, n, period);
+        else if (vec) binary_periodic_kernel<OP, false, true><<<g, 256, 0, st>>>(a, v, out, n, period);
+        else if (v_left) binary_periodic_kernel<OP, true, false><<<g, 256, 0, st>>>(a, v, out, n, period);
+        else binary_periodic_kernel<OP, false, false><<<g, 256, 0, st>>>(a, v, out, n, period);
+    }
+
     template <int OP>
     __device__ __forceinline__ float unary_op(float x)
     {
@@ -176,11 +221,13 @@ namespace b200
             else
             {
                 // max.hpp:32-58 / min.hpp: start from -inf / +inf, replace on a strict comparison (a NaN never wins)
-                float m = OP == B200_REDUCE_MAX ? -INFINITY : INFINITY;
+                float m = OP == B200_REDUCE_MIN ? INFINITY : -INFINITY;
                 for (int64_t r = 0; r < n_red; ++r)
                 {
-                    const float x = base[mapped_offset(red, r)];
-                    if (OP == B200_REDUCE_MAX ? x > m : x < m)
+                    float x = base[mapped_offset(red, r)];
+                    if (OP == B200_REDUCE_MAX_ABS)
+                        x = fabsf(x);
+                    if (OP == B200_REDUCE_MIN ? x < m : x > m)
                         m = x;
                 }
                 out[o] = m;
@@ -225,13 +272,14 @@ namespace b200
     // Whole-tensor max (one output): many blocks, each over a contiguous slice, combined with an atomic on the ordered
     // integer image of the float (non-negative floats order like signed ints, negative ones like reversed unsigned
     // ints).  NaNs never win, as in the reference loop; the output must hold -inf on entry.
+    template <bool ABS> // the max of |x|: op::v0::Max over op::v0::Abs without the tensor in between
     __global__ void __launch_bounds__(256) reduce_max_all_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n)
     {
         __shared__ float partial[8];
         float m = -INFINITY;
         for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
         {
-            const float x = in[i];
+            const float x = ABS ? fabsf(in[i]) : in[i];
             if (x > m)
                 m = x;
         }
@@ -723,6 +771,30 @@ extern "C" int b200_f32_binary(int op, const float* a, const float* b, float* ou
     return after_launch("b200_f32_binary");
 }
 
+extern "C" int b200_f32_binary_periodic(int op, const float* a, const float* v, float* out, int64_t n, int64_t period, int v_is_left,
+                                        void* stream)
+{
+    using namespace b200;
+    if (n < 0 || period < 1 || op < B200_F32_ADD || op > B200_F32_MIN)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (n == 0)
+        return B200_OK;
+    if (!a || !v || !out || n % period != 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool left = v_is_left != 0;
+    switch (op)
+    {
+    case B200_F32_ADD: launch_binary_periodic<B200_F32_ADD>(a, v, out, n, period, left, st); break;
+    case B200_F32_SUB: launch_binary_periodic<B200_F32_SUB>(a, v, out, n, period, left, st); break;
+    case B200_F32_MUL: launch_binary_periodic<B200_F32_MUL>(a, v, out, n, period, left, st); break;
+    case B200_F32_DIV: launch_binary_periodic<B200_F32_DIV>(a, v, out, n, period, left, st); break;
+    case B200_F32_MAX: launch_binary_periodic<B200_F32_MAX>(a, v, out, n, period, left, st); break;
+    default: launch_binary_periodic<B200_F32_MIN>(a, v, out, n, period, left, st); break;
+    }
+    return after_launch("b200_f32_binary_periodic");
+}
+
 extern "C" int b200_f32_unary(int op, const float* x, float* out, int64_t n, void* stream)
 {
     using namespace b200;
@@ -837,7 +909,7 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
                                void* stream)
 {
     using namespace b200;
-    if ((op != B200_REDUCE_SUM && op != B200_REDUCE_MAX && op != B200_REDUCE_MIN) || !valid_shape(shape, rank) || n_axes < 0 || n_axes > rank ||
+    if (op < B200_REDUCE_SUM || op > B200_REDUCE_MAX_ABS || !valid_shape(shape, rank) || n_axes < 0 || n_axes > rank ||
         (n_axes > 0 && !axes))
         return B200_ERR_INVALID_ARGUMENT;
     bool reduced[MAX_RANK] = {false};
@@ -870,11 +942,15 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
     if (!out || (!in && n_red > 0))
         return B200_ERR_INVALID_ARGUMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (op == B200_REDUCE_MAX && n_out == 1 && n_red >= (int64_t(1) << 16))
+    const bool any_max = op == B200_REDUCE_MAX || op == B200_REDUCE_MAX_ABS;
+    if (any_max && n_out == 1 && n_red >= (int64_t(1) << 16))
     {
         // every axis reduced: the input is one contiguous run
         fill_f32_kernel<<<1, 32, 0, st>>>(out, -INFINITY, 1);
-        reduce_max_all_kernel<<<grid_for(n_red / 4, 256), 256, 0, st>>>(in, out, n_red);
+        if (op == B200_REDUCE_MAX_ABS)
+            reduce_max_all_kernel<true><<<grid_for(n_red / 4, 256), 256, 0, st>>>(in, out, n_red);
+        else
+            reduce_max_all_kernel<false><<<grid_for(n_red / 4, 256), 256, 0, st>>>(in, out, n_red);
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
     else if (op == B200_REDUCE_MAX && n_out <= 4096 && n_red >= 1024)
@@ -889,6 +965,8 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
         reduce_kernel<B200_REDUCE_SUM><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     else if (op == B200_REDUCE_MAX)
         reduce_kernel<B200_REDUCE_MAX><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
+    else if (op == B200_REDUCE_MAX_ABS)
+        reduce_kernel<B200_REDUCE_MAX_ABS><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     else
         reduce_kernel<B200_REDUCE_MIN><<<grid_for(n_out, 128), 128, 0, st>>>(in, out, keep, red, n_out, n_red);
     return after_launch("b200_reduce_f32");

@@ -58,6 +58,7 @@ def _load():
         "b200_im2col_c4_u8": (ci, [vp, vp] + [i64] * 11 + [vp]),
         "b200_requant_scale": (ci, [vp, vp, vp, vp, vp]),
         "b200_f32_binary": (ci, [ci, vp, vp, vp, i64, vp]),
+        "b200_f32_binary_periodic": (ci, [ci, vp, vp, vp, i64, i64, ci, vp]),
         "b200_f32_unary": (ci, [ci, vp, vp, i64, vp]),
         "b200_broadcast_b32": (ci, [vp, vp, p64, ci, p64, ci, vp]),
         "b200_permute_b32": (ci, [vp, vp, p64, ci, p64, vp]),

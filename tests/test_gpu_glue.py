@@ -56,6 +56,22 @@ def test_elementwise_is_ieee_exact(L):
             assert ok.all(), name
 
 
+@pytest.mark.parametrize("rows,period", [(37, 768), (50, 6), (1000, 1), (3, 5)])
+def test_binary_with_a_repeating_operand(L, rows, period):
+    """out[i] = a[i] op v[i % period]: what the op computes on a Broadcast of v along new leading axes"""
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((rows, period)).astype(np.float32)
+    v = rng.standard_normal(period).astype(np.float32)
+    ad, vd, out = dev(a), dev(v), torch.empty(a.size, device="cuda")
+    fns = dict(add=np.add, sub=np.subtract, mul=np.multiply, div=np.divide, max=np.maximum, min=np.minimum)
+    for name, fn in fns.items():
+        for v_left in (0, 1):
+            L.check(L.LIB.b200_f32_binary_periodic(OPS[name], ad.data_ptr(), vd.data_ptr(), out.data_ptr(), a.size, period, v_left,
+                                                   stream()), name)
+            want = fn(v[None, :], a) if v_left else fn(a, v[None, :])
+            np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(want.astype(np.float32)).ravel(), err_msg="%s %d" % (name, v_left))
+
+
 def test_exp_and_erf_within_one_ulp(L):
     x = np.linspace(-20, 20, 200001).astype(np.float32)
     xd, out = dev(x), torch.empty(x.size, device="cuda")
@@ -92,7 +108,8 @@ def test_sum_and_max_follow_the_reference_order(L, shape, axes):
     xd = dev(x)
     out = torch.empty(max(want_sum.size, 1), device="cuda")
     want_min = moved.min(axis=-1) if axes else x.copy()
-    for op, want in ((0, want_sum), (1, want_max), (2, want_min)):
+    want_max_abs = np.abs(moved).max(axis=-1) if axes else np.abs(x)
+    for op, want in ((0, want_sum), (1, want_max), (2, want_min), (3, want_max_abs)):
         L.check(L.LIB.b200_reduce_f32(op, xd.data_ptr(), out.data_ptr(), i64(shape), len(shape), i64(axes), len(axes), stream()), "reduce")
         np.testing.assert_array_equal(bits(out.cpu().numpy()[:want.size]), bits(want).ravel())
 

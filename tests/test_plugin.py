@@ -387,6 +387,26 @@ def test_numpy_style_broadcasting_in_elementwise_ops(backends):
 
 @pytest.mark.gpu
 @needs_ngraph
+def test_broadcast_operands_are_read_in_place(backends):
+    """Broadcast(small constant or tensor) along new leading axes feeding an elementwise op: no copy is made, the result is
+    the same (large enough that ConstantFolding would otherwise have expanded the constant)"""
+    rng = np.random.default_rng(13)
+    x = ng.parameter(np.float32, (300, 256))
+    row = rng.standard_normal(256).astype(np.float32)
+    s = ng.parameter(np.float32, ())
+    y = ng.add(x, ng.broadcast(ng.constant(row), (300, 256), (0,)))                  # bias row
+    y = ng.multiply(ng.broadcast(s, (300, 256), (0, 1)), y)                          # run-time scalar on the left
+    y = ng.add(y, ng.broadcast(ng.constant(np.float32(0.5)), (300, 256), (0, 1)))    # constant scalar
+    fn = ng.Function([y], [x, s])
+    xs = [rng.standard_normal((300, 256)).astype(np.float32), np.float32(1.7) * np.ones((), np.float32)]
+    exe = backends[0].compile(fn, perf=True)
+    got = exe.run(*xs)[0]
+    same_bits(got, backends[1].compile(fn).run(*xs)[0])
+    assert not any(n.startswith("Broadcast") and us > 0 for n, us, _ in exe.performance_data())
+
+
+@pytest.mark.gpu
+@needs_ngraph
 def test_api_contract(backends):
     """create_tensor / validate / foreign tensors / unsupported ops (test/backend/api.in.cpp,
     validate_call.in.cpp, unhandled_op.in.cpp restated)."""
