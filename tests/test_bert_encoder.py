@@ -73,3 +73,24 @@ def test_bert_base_width_runs_and_repeats():
     b = be.compile(ng.bert_encoder(seed=2, **dims)).run(ids, seg)[0]
     assert np.isfinite(a).all() and np.array_equal(a, b)
     assert 0.5 < a.std() < 2.0
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_full_width_encoder_commutes_with_a_permutation_of_the_batch():
+    """At BERT-base width (hidden 768, 12 heads, FFN 3072, seq 384) the INTERPRETER would need hours, so the check is a
+    property the arithmetic guarantees: every op acts per token or per sequence, and the dynamic activation scales are
+    maxima over the whole tensor, which do not depend on the order of the sequences.  Reordering the sequences of the
+    batch therefore reorders the output rows and changes no bit; the run is also repeatable."""
+    from ngraph_b200 import ngraph_api as ng
+    ng.load_b200()
+    dims = dict(layers=2, hidden=768, heads=12, ffn=3072, seq=384, batch=6, vocab=30522)
+    ids, seg = _inputs(dims, 2)
+    exe = ng.Backend("B200").compile(ng.bert_encoder(seed=7, **dims))
+    out = exe.run(ids, seg)[0]
+    assert np.isfinite(out).all() and 0.5 < out.std() < 2.0
+    np.testing.assert_array_equal(exe.run(ids, seg)[0].view(np.uint32), out.view(np.uint32))
+    perm = np.array([4, 0, 5, 2, 1, 3])
+    rows = lambda a, width: a.reshape(dims["batch"], dims["seq"], *width)[perm].reshape(a.shape)
+    out_p = exe.run(rows(ids, ()), rows(seg, ()))[0]
+    np.testing.assert_array_equal(out_p.view(np.uint32), rows(out, (dims["hidden"],)).view(np.uint32))
