@@ -123,6 +123,30 @@ namespace b200
         return ex >= 127 - 40 && ex <= 127 + 40 && man != 0x7FFFFF;
     }
 
+    // The same strength-reduced division for the other rounding modes (8-bit outputs): the quotient has to be the
+    // correctly rounded x / s itself, because ceil / floor see its last bit.  q1 is that quotient while nothing
+    // underflows, which |x| >= 2^-60 guarantees for the admitted scales (2^-40 <= |s| < 2^41); zeros divide to zero;
+    // quotients of magnitude >= 2^24 (and inf / NaN) saturate or become 0 whatever their last bit; the few remaining
+    // inputs (0 < |x| < 2^-60) take the IEEE division.
+    template <typename Q, int MODE>
+    __device__ __forceinline__ Q quantize_one_fast(float x, float s, float y, float zp)
+    {
+        const float q0 = __fmul_rn(x, y);
+        const float e = __fmaf_rn(-q0, s, x);
+        const float q1 = __fmaf_rn(e, y, q0);
+        const float ax = fabsf(x);
+        float q;
+        if (!(fabsf(q0) < 16777216.0f) || ax == 0.0f)
+            q = q0;
+        else if (ax >= 8.673617379884035e-19f) // 2^-60
+            q = q1;
+        else
+            q = __fdiv_rn(x, s);
+        q = round_quant<MODE>(q);
+        q = __fadd_rn(q, zp);
+        return clamp_cast<Q>(q);
+    }
+
     template <typename Q>
     __device__ __forceinline__ int quantize_rne_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
     {

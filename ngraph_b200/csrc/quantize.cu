@@ -59,7 +59,7 @@ namespace b200
         *reinterpret_cast<int4*>(p) = make_int4(a, b, c, d);
     }
 
-    template <typename Q, int MODE>
+    template <typename Q, int MODE, bool FAST>
     __global__ void __launch_bounds__(QT) quantize_rows_kernel(const float* __restrict__ x,
                                                                const float* __restrict__ scale,
                                                                const Q* __restrict__ zp,
@@ -77,6 +77,10 @@ namespace b200
         const int64_t rem = inner - row_off; // elements of this row from the chunk start
         const float* xp = x + row * inner + row_off;
         Q* op = out + row * inner + row_off;
+        // one scale per block: the division becomes two multiply-adds where that is exact (8-bit outputs only; an
+        // int32 output can be large enough for the last bit of a quotient beyond 2^24 to matter)
+        const bool fast = FAST && sizeof(Q) == 1 && scale_allows_fast_division(s);
+        const float y = __frcp_rn(s);
 
         float4 v[QU];
 #pragma unroll
@@ -90,7 +94,15 @@ namespace b200
         for (int u = 0; u < QU; ++u)
         {
             int64_t off = (int64_t(u) * QT + threadIdx.x) * 4;
-            if (off + 4 <= rem)
+            if (off + 4 <= rem && fast)
+            {
+                store4<Q>(op + off,
+                          quantize_one_fast<Q, MODE>(v[u].x, s, y, z),
+                          quantize_one_fast<Q, MODE>(v[u].y, s, y, z),
+                          quantize_one_fast<Q, MODE>(v[u].z, s, y, z),
+                          quantize_one_fast<Q, MODE>(v[u].w, s, y, z));
+            }
+            else if (off + 4 <= rem)
             {
                 store4<Q>(op + off,
                           quantize_one<Q, MODE>(v[u].x, s, z),
@@ -395,8 +407,12 @@ namespace b200
         else if (use_rows(p, x, out))
         {
             uint32_t chunks = uint32_t((p.inner + QCHUNK - 1) / QCHUNK);
-            quantize_rows_kernel<Q, MODE><<<unsigned(chunks * p.rows), QT, 0, st>>>(
-                x, scale, static_cast<const Q*>(zp), static_cast<Q*>(out), p.inner, chunks, p.n_scales);
+            if (sizeof(Q) == 1 && g_fast_division.load(std::memory_order_relaxed))
+                quantize_rows_kernel<Q, MODE, true><<<unsigned(chunks * p.rows), QT, 0, st>>>(
+                    x, scale, static_cast<const Q*>(zp), static_cast<Q*>(out), p.inner, chunks, p.n_scales);
+            else
+                quantize_rows_kernel<Q, MODE, false><<<unsigned(chunks * p.rows), QT, 0, st>>>(
+                    x, scale, static_cast<const Q*>(zp), static_cast<Q*>(out), p.inner, chunks, p.n_scales);
         }
         else
         {

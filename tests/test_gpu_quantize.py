@@ -180,3 +180,36 @@ def test_fast_division_is_exact_for_every_float(ops):
                 finally:
                     lib.LIB.b200_set_fast_division(old)
                 assert torch.equal(fast, exact), "scale %r chunk %d: %d bytes differ" % (sv, c, int((fast != exact).sum()))
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 5, 6, 7, 8])
+def test_fast_division_is_exact_for_every_float_in_the_other_round_modes(ops, mode):
+    """The directed and half-away modes see the last bit of the quotient (ceil / floor of it), so their strength-reduced
+    division must return the correctly rounded x / s itself: all 2^32 bit patterns, device against device."""
+    from ngraph_b200 import lib
+    chunk = 1 << 28
+    base = torch.arange(chunk, dtype=torch.int64, device="cuda")
+    for qdt, zpv in ((torch.uint8, 128), (torch.int8, 0)):
+        zp = torch.full((), zpv, dtype=qdt, device="cuda")
+        for sv in (0.05, 3.0, 7.0 / 255.0, 1.0000001, 0.0137):
+            s = torch.full((), float(np.float32(sv)), device="cuda")
+            for c in range(16):
+                x = (base + c * chunk).to(torch.int32).view(torch.float32) if c < 8 else \
+                    (base + c * chunk - (1 << 32)).to(torch.int32).view(torch.float32)
+                fast = ops.quantize(x, s, zp, round_mode=mode)
+                old = lib.LIB.b200_set_fast_division(0)
+                try:
+                    exact = ops.quantize(x, s, zp, round_mode=mode)
+                finally:
+                    lib.LIB.b200_set_fast_division(old)
+                assert torch.equal(fast, exact), "mode %d scale %r chunk %d: %d bytes differ" % (mode, sv, c, int((fast != exact).sum()))
+
+
+@pytest.mark.gpu
+def test_bandwidth_sweep_tool_runs():
+    """python -m ngraph_b200.quantize_sweep (the BASELINE config-2 table) on its two smallest sizes"""
+    from ngraph_b200 import quantize_sweep
+    lines = []
+    rows = quantize_sweep.sweep(max_mb=4, iters=2, out=lines.append)
+    assert len(rows) == 2 * 2 * 2 + 9 and all(r[4] > 0 for r in rows)
+    assert any("ROUND_DOWN" in l for l in lines)
