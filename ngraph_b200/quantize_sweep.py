@@ -4,7 +4,8 @@
 
     python -m ngraph_b200.quantize_sweep [--max-mb 4096] [--out table.txt]
 
-Each figure is algorithmic bytes (5 per element: 4 + 1) over the mean device time of `--iters` launches, timed one by one
+The last column is a plain device copy of the same f32 tensor timed the same way (8 bytes per element): the bandwidth a
+single launch of that size can reach.  Each figure is algorithmic bytes (5 per element: 4 + 1) over the mean device time of `--iters` launches, timed one by one
 with CUDA events on the launching stream; before every timed launch a 512 MB buffer is rewritten so that neither the
 input nor a previous output is still in the 126 MB L2.  The kernels are called through the C ABI (ngraph_b200.ops)."""
 import argparse
@@ -49,12 +50,17 @@ def sweep(max_mb=4096, iters=10, out=print):
     zps = {"u8": torch.full((), 128, dtype=torch.uint8, device=dev), "i8": torch.zeros((), dtype=torch.int8, device=dev)}
     zps_axis = {"u8": torch.full((64,), 128, dtype=torch.uint8, device=dev), "i8": torch.zeros(64, dtype=torch.int8, device=dev)}
     rows = []
-    out("%-8s %-22s %-4s %-10s %10s %10s" % ("f32 MB", "shape", "type", "scale", "Quantize", "Dequantize"))
+    out("%-8s %-22s %-4s %-10s %12s %12s %12s" % ("f32 MB", "shape", "type", "scale", "Quantize", "Dequantize", "f32 copy"))
     for mb, shape in SHAPES.items():
         if mb > max_mb:
             continue
         x = torch.randn(shape, generator=gen, device=dev)
         n = x.numel()
+        # the same launch-by-launch timing of a plain device copy of the tensor (8 bytes per element): what the memory
+        # system gives a single launch of this size
+        spare = torch.empty_like(x)
+        g_copy = 8.0 * n / timed(lambda: spare.copy_(x), flush, iters) / 1e6
+        del spare
         for ty in ("u8", "i8"):
             for what, scale, zp, axes in (("per-tensor", scalar, zps[ty], ()), ("per-axis", per_axis, zps_axis[ty], (1,))):
                 q = torch.empty(shape, dtype=zp.dtype, device=dev)
@@ -63,7 +69,7 @@ def sweep(max_mb=4096, iters=10, out=print):
                 t_d = timed(lambda: ops.dequantize(q, scale, zp, axes=axes, out=back), flush, iters)
                 gq, gd = 5.0 * n / t_q / 1e6, 5.0 * n / t_d / 1e6
                 rows.append((mb, ty, what, "RNE", gq, gd))
-                out("%-8d %-22s %-4s %-10s %7.0f GB/s %7.0f GB/s" % (mb, list(shape), ty, what, gq, gd))
+                out("%-8d %-22s %-4s %-10s %7.0f GB/s %7.0f GB/s %7.0f GB/s" % (mb, list(shape), ty, what, gq, gd, g_copy))
                 del q, back
         del x
     mb = min(1024, max(m for m in SHAPES if m <= max_mb))
