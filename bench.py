@@ -521,10 +521,6 @@ class QDotLayer(MicroWorkload):
     def __init__(self, m=32768):
         self.M, self.N, self.K = m, 1024, 1024
 
-    def describe(self, world=1):
-        return {"workload": "QuantizedDotBias+Relu u8[%d,1024] x i8[1024,1024], i32 bias, scale 0.004 -> u8" % self.M,
-                "l2": "rotated over 8 input/output buffers"}
-
     def host_inputs(self, seed):
         from oracle import ref
         rng = np.random.default_rng(seed)
@@ -546,22 +542,53 @@ class QDotLayer(MicroWorkload):
         self.pin_in = torch.from_numpy(self.h_a).pin_memory()
         self.pin_out = torch.empty((self.M, self.N), dtype=torch.uint8).pin_memory()
         self.i = 0
+        # A launch of the small problems (BASELINE's own M = 256 is 0.5 GOP) is shorter than the host needs to issue it,
+        # so those are timed as a CUDA graph of back-to-back launches, replayed once per step.
+        self.graph, self.per_step = None, 1
+        if self.M <= 8192:
+            self.per_step = 64
+            for _ in range(3):
+                self._launch()
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                for _ in range(self.per_step):
+                    self._launch()
+
+    def describe(self, world=1):
+        d = {"workload": "QuantizedDotBias+Relu u8[%d,1024] x i8[1024,1024], i32 bias, scale 0.004 -> u8" % self.M,
+             "l2": "rotated over 8 input/output buffers"}
+        if self.M <= 8192:
+            d["launches"] = "one step = a CUDA graph of 64 back-to-back launches"
+        return d
 
     def units_per_step(self):
-        return 2.0 * self.M * self.N * self.K / 1e12
+        return self.per_step * 2.0 * self.M * self.N * self.K / 1e12
 
     def alg_per_launch(self):
         return self.units_per_step() * 1e12
 
-    def step(self):
+    def launches_per_step(self):
+        return self.per_step
+
+    def _launch(self):
         i = self.i = (self.i + 1) % self.nbuf
         self.ops.qgemm(self.a[i], self.w, self.scale, self.torch.uint8, bias=self.bias, relu=True, out=self.out[i])
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._launch()
 
     def step_e2e(self):
         i = self.i = (self.i + 1) % self.nbuf
         self.a[i].copy_(self.pin_in, non_blocking=True)
         self.ops.qgemm(self.a[i], self.w, self.scale, self.torch.uint8, bias=self.bias, relu=True, out=self.out[i])
         self.pin_out.copy_(self.out[i], non_blocking=True)
+
+    def e2e_units_per_step(self):
+        return 2.0 * self.M * self.N * self.K / 1e12
 
     def io_bytes(self):
         return self.pin_in.numel(), self.pin_out.numel()
@@ -738,6 +765,8 @@ def main():
     barrier()
     t1 = time.time()
     launches = lib.launch_count()
+    if hasattr(wl, "launches_per_step") and wl.launches_per_step() > 1:
+        launches = args.steps * wl.launches_per_step()  # replayed from a CUDA graph: the host-side counter does not see them
     ms = ev0.elapsed_time(ev1)
 
     # end to end: pinned host -> device, kernels, device -> pinned host, every step
@@ -762,7 +791,8 @@ def main():
     if rank == 0:
         per_step = ms / args.steps
         value = wl.units_per_step() * world / (per_step / 1e3)
-        e2e_value = wl.units_per_step() * world / (ms_e2e / args.steps / 1e3)
+        e2e_units = wl.e2e_units_per_step() if hasattr(wl, "e2e_units_per_step") else wl.units_per_step()
+        e2e_value = e2e_units * world / (ms_e2e / args.steps / 1e3)
         h2d, d2h = wl.io_bytes()
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
