@@ -470,6 +470,13 @@ B200_API int b200_reduce_f32(int op, const float* in, float* out, const int64_t*
 B200_API int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, int64_t row_elements, void* stream);
 B200_API int b200_layer_norm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, int64_t rows,
                                       int64_t row_elements, float epsilon, void* stream);
+/* the same two kernels with the elementwise op that produced their input folded into the load: Softmax(x * *factor) for an
+ * op::v1::Multiply by a broadcast scalar (factor: one element, device memory), LayerNorm(x + addend) for an op::v1::Add;
+ * each product / sum is rounded once, exactly as the separate op would have stored it */
+B200_API int b200_softmax_rows_scaled_f32(const float* x, const float* factor, float* out, int64_t rows, int64_t row_elements,
+                                          void* stream);
+B200_API int b200_layer_norm_rows_sum_f32(const float* x, const float* addend, const float* gamma, const float* beta, float* out,
+                                          int64_t rows, int64_t row_elements, float epsilon, void* stream);
 B200_API int b200_gelu_f32(const float* x, float* out, int64_t n, void* stream);
 B200_API int b200_bmm_f32(const float* a, const float* b, float* out, int64_t batch, int64_t M, int64_t K, int64_t N,
                           void* stream);

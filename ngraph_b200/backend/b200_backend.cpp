@@ -980,6 +980,31 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
             unsupported(*node, "elementwise arithmetic on element types other than f32");
         if (node->get_input_shape(0) != os || node->get_input_shape(1) != os)
             unsupported(*node, "implicit broadcasting (use an explicit Broadcast)");
+        // Producer ops folded into the row kernels that read them (b200_softmax_rows_scaled_f32 /
+        // b200_layer_norm_rows_sum_f32): a Multiply by a broadcast scalar whose one reader is a last-axis Softmax, and an
+        // Add of two tensors whose one reader is a LayerNorm that runs as one kernel.
+        if (const Node* user = only_user(node->output(0)))
+        {
+            if (bop == B200_F32_MUL && is_type<op::v0::Softmax>(user) && !os.empty() && os.back() <= 1535 &&
+                static_cast<const op::v0::Softmax*>(user)->get_axes() == AxisSet{os.size() - 1})
+                for (int side = 0; side < 2; ++side)
+                {
+                    Output<Node> bc = node->input_value(side);
+                    if (value_of(bc).skipped && is_type<op::v0::Broadcast>(bc.get_node()) &&
+                        shape_size(bc.get_node()->get_input_shape(0)) == 1 && !value_of(node->input_value(1 - side)).skipped)
+                    {
+                        value_of(node->output(0)).skipped = true;
+                        return true;
+                    }
+                }
+            if (bop == B200_F32_ADD && is_type<op::v0::LayerNorm>(user) && runs_undecomposed(*user) &&
+                user->input_value(0).get_node() == node.get() && !value_of(node->input_value(0)).skipped &&
+                !value_of(node->input_value(1)).skipped)
+            {
+                value_of(node->output(0)).skipped = true;
+                return true;
+            }
+        }
         // an operand that is a Broadcast along new leading axes, left unmaterialised for this op (see below)
         for (int side = 0; side < 2; ++side)
         {
@@ -1107,11 +1132,19 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
             unsupported(*node, "LayerNorm other than f32, last axis, with scale and bias");
         const int64_t row = int64_t(os.back()), rows = n_out / row;
         const float eps = static_cast<float>(ln->get_epsilon()); // builder::make_constant(f32, ..., double epsilon)
-        int x = canonical_slot(node->input_value(0)), g = canonical_slot(node->input_value(1)), b = canonical_slot(node->input_value(2));
+        Output<Node> source = node->input_value(0);
+        int addend = -1;
+        if (value_of(source).skipped && is_type<op::v1::Add>(source.get_node())) // the residual Add in front: summed while loading
+        {
+            addend = canonical_slot(source.get_node()->input_value(1));
+            source = source.get_node()->input_value(0);
+        }
+        int x = canonical_slot(source), g = canonical_slot(node->input_value(1)), b = canonical_slot(node->input_value(2));
         int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
         emit(node, "layer_norm_rows", [=](const Ptrs& p, cudaStream_t st) {
-            return b200_layer_norm_rows_f32(static_cast<const float*>(p[x]), static_cast<const float*>(p[g]), static_cast<const float*>(p[b]),
-                                            static_cast<float*>(p[y]), rows, row, eps, st);
+            return b200_layer_norm_rows_sum_f32(static_cast<const float*>(p[x]), addend >= 0 ? static_cast<const float*>(p[addend]) : nullptr,
+                                                static_cast<const float*>(p[g]), static_cast<const float*>(p[b]),
+                                                static_cast<float*>(p[y]), rows, row, eps, st);
         });
         value_of(node->output(0)).canonical = y;
         return true;
@@ -1139,14 +1172,25 @@ bool B200Executable::compile_f32_glue(const std::shared_ptr<Node>& node)
             if (!axes.count(i))
                 red.push_back(os[i]);
         const int64_t n_red = int64_t(shape_size(red));
-        int x = canonical_slot(node->input_value(0));
+        Output<Node> source = node->input_value(0);
+        int factor = -1;
+        if (value_of(source).skipped && is_type<op::v1::Multiply>(source.get_node()))
+        {
+            // Multiply by a broadcast scalar in front (see the elementwise ops above): applied while the rows are loaded
+            const Node* mul = source.get_node();
+            const int side = value_of(mul->input_value(0)).skipped ? 0 : 1;
+            factor = canonical_slot(mul->input_value(side).get_node()->input_value(0));
+            source = mul->input_value(1 - side);
+        }
+        int x = canonical_slot(source);
         if (axes.size() == 1 && *axes.begin() == os.size() - 1 && os.back() >= 1 && os.back() <= 1535)
         {
             // the last axis of a matrix of rows: one kernel that keeps the rows in shared memory between the steps
             const int64_t row = int64_t(os.back()), rows = n_out / row;
             int y = new_slot(Slot::ARENA, size_t(n_out) * 4);
             emit(node, "softmax_rows", [=](const Ptrs& p, cudaStream_t st) {
-                return b200_softmax_rows_f32(static_cast<const float*>(p[x]), static_cast<float*>(p[y]), rows, row, st);
+                return b200_softmax_rows_scaled_f32(static_cast<const float*>(p[x]), factor >= 0 ? static_cast<const float*>(p[factor]) : nullptr,
+                                                    static_cast<float*>(p[y]), rows, row, st);
             });
             value_of(node->output(0)).canonical = y;
             return true;

@@ -321,39 +321,64 @@ namespace b200
     constexpr int ROWS_PER_TILE = 32;
     __host__ __device__ inline int staged_row_stride(int L, bool vec) { return vec ? L + 4 : (L | 1); }
 
+    // The elementwise op that produced the rows can be applied while they are staged (one rounding, the same value the
+    // op's own kernel would have written): factor != nullptr multiplies by the scalar *factor (op::v1::Multiply by a
+    // broadcast scalar), addend != nullptr adds the rows of a second tensor (op::v1::Add).
     template <bool VEC>
-    __device__ __forceinline__ void stage_rows(const float* __restrict__ src, float* tile, int n_rows, int L, int stride)
+    __device__ __forceinline__ void stage_rows(const float* __restrict__ src, float* tile, int n_rows, int L, int stride,
+                                               const float* __restrict__ factor, const float* __restrict__ addend)
     {
+        const float f = factor ? __ldg(factor) : 1.0f;
         if (VEC)
         {
             const int L4 = L >> 2, total = n_rows * L4;
             const float4* src4 = reinterpret_cast<const float4*>(src);
+            const float4* add4 = reinterpret_cast<const float4*>(addend);
             for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * 8)
             {
-                float4 v[8];
+                float4 v[8], w[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                 {
                     const int i = i0 + j * blockDim.x;
                     if (i < total)
+                    {
                         v[j] = __ldg(src4 + i);
+                        if (addend)
+                            w[j] = __ldg(add4 + i);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                 {
                     const int i = i0 + j * blockDim.x;
                     if (i < total)
-                        *reinterpret_cast<float4*>(tile + (i / L4) * stride + 4 * (i % L4)) = v[j];
+                    {
+                        float4 r = v[j];
+                        if (factor)
+                            r = make_float4(__fmul_rn(r.x, f), __fmul_rn(r.y, f), __fmul_rn(r.z, f), __fmul_rn(r.w, f));
+                        if (addend)
+                            r = make_float4(__fadd_rn(r.x, w[j].x), __fadd_rn(r.y, w[j].y), __fadd_rn(r.z, w[j].z), __fadd_rn(r.w, w[j].w));
+                        *reinterpret_cast<float4*>(tile + (i / L4) * stride + 4 * (i % L4)) = r;
+                    }
                 }
             }
         }
         else
             for (int i = threadIdx.x; i < n_rows * L; i += blockDim.x)
-                tile[(i / L) * stride + i % L] = src[i];
+            {
+                float r = src[i];
+                if (factor)
+                    r = __fmul_rn(r, f);
+                if (addend)
+                    r = __fadd_rn(r, addend[i]);
+                tile[(i / L) * stride + i % L] = r;
+            }
     }
 
     template <bool VEC>
-    __global__ void __launch_bounds__(128) softmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int L)
+    __global__ void __launch_bounds__(128) softmax_rows_kernel(const float* __restrict__ in, const float* __restrict__ factor, float* __restrict__ out,
+                                                               int64_t rows, int L)
     {
         extern __shared__ __align__(16) float tile[];
         __shared__ float row_max[ROWS_PER_TILE], row_sum[ROWS_PER_TILE];
@@ -364,7 +389,7 @@ namespace b200
         {
             const int64_t row0 = t * ROWS_PER_TILE;
             const int n_rows = int(rows - row0 < ROWS_PER_TILE ? rows - row0 : ROWS_PER_TILE);
-            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride);
+            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride, factor, nullptr);
             __syncthreads();
             // softmax.hpp: max over the axis (the largest value whatever the order), then exp(x - max)
             for (int r = warp; r < n_rows; r += 4)
@@ -426,9 +451,9 @@ namespace b200
     //   mean = KahanSum(x) / N;  var = KahanSum((x - mean) * (x - mean)) / N;  sd = sqrt(var + eps);
     //   y = ((x - mean) / sd) * gamma + beta          (every operation a separate IEEE rounding, no fused multiply-add)
     template <bool VEC>
-    __global__ void __launch_bounds__(128) layer_norm_rows_kernel(const float* __restrict__ in, const float* __restrict__ gamma,
-                                                                  const float* __restrict__ beta, float* __restrict__ out, int64_t rows,
-                                                                  int L, float count, float eps)
+    __global__ void __launch_bounds__(128) layer_norm_rows_kernel(const float* __restrict__ in, const float* __restrict__ addend,
+                                                                  const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                  float* __restrict__ out, int64_t rows, int L, float count, float eps)
     {
         extern __shared__ __align__(16) float tile[];
         __shared__ float row_mean[ROWS_PER_TILE], row_sd[ROWS_PER_TILE];
@@ -439,7 +464,7 @@ namespace b200
         {
             const int64_t row0 = t * ROWS_PER_TILE;
             const int n_rows = int(rows - row0 < ROWS_PER_TILE ? rows - row0 : ROWS_PER_TILE);
-            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride);
+            stage_rows<VEC>(in + row0 * L, tile, n_rows, L, stride, nullptr, addend ? addend + row0 * L : nullptr);
             __syncthreads();
             if (warp == 0 && lane < n_rows)
             {
@@ -974,6 +999,12 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
 
 extern "C" int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, int64_t row_elements, void* stream)
 {
+    return b200_softmax_rows_scaled_f32(x, nullptr, out, rows, row_elements, stream);
+}
+
+extern "C" int b200_softmax_rows_scaled_f32(const float* x, const float* factor, float* out, int64_t rows, int64_t row_elements,
+                                            void* stream)
+{
     using namespace b200;
     if (rows < 0 || row_elements < 0)
         return B200_ERR_INVALID_ARGUMENT;
@@ -992,14 +1023,20 @@ extern "C" int b200_softmax_rows_f32(const float* x, float* out, int64_t rows, i
               : staged_launch_shape(softmax_rows_kernel<false>, rows, L, vec, grid, bytes)))
         return B200_ERR_CUDA;
     if (vec)
-        softmax_rows_kernel<true><<<grid, 128, bytes, st>>>(x, out, rows, L);
+        softmax_rows_kernel<true><<<grid, 128, bytes, st>>>(x, factor, out, rows, L);
     else
-        softmax_rows_kernel<false><<<grid, 128, bytes, st>>>(x, out, rows, L);
+        softmax_rows_kernel<false><<<grid, 128, bytes, st>>>(x, factor, out, rows, L);
     return after_launch("b200_softmax_rows_f32");
 }
 
 extern "C" int b200_layer_norm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, int64_t rows,
                                         int64_t row_elements, float epsilon, void* stream)
+{
+    return b200_layer_norm_rows_sum_f32(x, nullptr, gamma, beta, out, rows, row_elements, epsilon, stream);
+}
+
+extern "C" int b200_layer_norm_rows_sum_f32(const float* x, const float* addend, const float* gamma, const float* beta, float* out,
+                                            int64_t rows, int64_t row_elements, float epsilon, void* stream)
 {
     using namespace b200;
     if (rows < 0 || row_elements < 0)
@@ -1011,7 +1048,7 @@ extern "C" int b200_layer_norm_rows_f32(const float* x, const float* gamma, cons
     if (row_elements > 1535)
         return B200_ERR_UNSUPPORTED; // a row too long to stage: the caller runs the decomposition
     const int L = int(row_elements);
-    const bool vec = L % 4 == 0 && all_aligned16({x, gamma, beta, out});
+    const bool vec = L % 4 == 0 && all_aligned16({x, addend, gamma, beta, out});
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const float count = static_cast<float>(row_elements);
     unsigned grid;
@@ -1020,9 +1057,9 @@ extern "C" int b200_layer_norm_rows_f32(const float* x, const float* gamma, cons
               : staged_launch_shape(layer_norm_rows_kernel<false>, rows, L, vec, grid, bytes)))
         return B200_ERR_CUDA;
     if (vec)
-        layer_norm_rows_kernel<true><<<grid, 128, bytes, st>>>(x, gamma, beta, out, rows, L, count, epsilon);
+        layer_norm_rows_kernel<true><<<grid, 128, bytes, st>>>(x, addend, gamma, beta, out, rows, L, count, epsilon);
     else
-        layer_norm_rows_kernel<false><<<grid, 128, bytes, st>>>(x, gamma, beta, out, rows, L, count, epsilon);
+        layer_norm_rows_kernel<false><<<grid, 128, bytes, st>>>(x, addend, gamma, beta, out, rows, L, count, epsilon);
     return after_launch("b200_layer_norm_rows_f32");
 }
 

@@ -68,6 +68,8 @@ def _load():
         "b200_requant_zero_points": (ci, [vp, vp, vp, vp, ctypes.POINTER(Epilogue), vp, vp]),
         "b200_copy_rows": (ci, [vp, vp, i64, i64, i64, vp]),
         "b200_layer_norm_rows_f32": (ci, [vp, vp, vp, vp, i64, i64, ctypes.c_float, vp]),
+        "b200_softmax_rows_scaled_f32": (ci, [vp, vp, vp, i64, i64, vp]),
+        "b200_layer_norm_rows_sum_f32": (ci, [vp, vp, vp, vp, vp, i64, i64, ctypes.c_float, vp]),
         "b200_gelu_f32": (ci, [vp, vp, i64, vp]),
         "b200_softmax_rows_f32": (ci, [vp, vp, i64, i64, vp]),
         "b200_bmm_f32": (ci, [vp, vp, vp, i64, i64, i64, i64, vp]),

@@ -179,6 +179,26 @@ def test_gelu_equals_its_decomposition_on_the_device(L):
     np.testing.assert_array_equal(bits(np.nan_to_num(g)), bits(np.nan_to_num(w)))
 
 
+def test_row_kernels_with_the_producer_op_folded_in(L):
+    """Softmax(x * scalar) and LayerNorm(x + y) from one kernel each equal the elementwise kernel followed by the plain row kernel"""
+    rng = np.random.default_rng(11)
+    rows, n = 70, 384
+    x, y = (rng.standard_normal((rows, n)) * 3).astype(np.float32), rng.standard_normal((rows, n)).astype(np.float32)
+    gamma, beta = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    xd, yd, gd, bd = dev(x), dev(y), dev(gamma), dev(beta)
+    f = dev(np.float32([0.125]))
+    tmp, want, got = (torch.empty((rows, n), device="cuda") for _ in range(3))
+    S, P = stream(), lambda a: a.data_ptr()
+    L.check(L.LIB.b200_f32_binary_periodic(OPS["mul"], P(xd), P(f), P(tmp), x.size, 1, 0, S), "mul")
+    L.check(L.LIB.b200_softmax_rows_f32(P(tmp), P(want), rows, n, S), "softmax")
+    L.check(L.LIB.b200_softmax_rows_scaled_f32(P(xd), P(f), P(got), rows, n, S), "softmax scaled")
+    np.testing.assert_array_equal(bits(got.cpu().numpy()), bits(want.cpu().numpy()))
+    L.check(L.LIB.b200_f32_binary(OPS["add"], P(xd), P(yd), P(tmp), x.size, S), "add")
+    L.check(L.LIB.b200_layer_norm_rows_f32(P(tmp), P(gd), P(bd), P(want), rows, n, ctypes.c_float(1e-5), S), "ln")
+    L.check(L.LIB.b200_layer_norm_rows_sum_f32(P(xd), P(yd), P(gd), P(bd), P(got), rows, n, ctypes.c_float(1e-5), S), "ln sum")
+    np.testing.assert_array_equal(bits(got.cpu().numpy()), bits(want.cpu().numpy()))
+
+
 def test_broadcast_and_permute(L):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((5, 7)).astype(np.float32)
