@@ -196,18 +196,25 @@ class ResNet50:
 
     def step_e2e(self):
         """One batch end to end through the plugin's public API: Tensor::write of the batch (pinned host memory),
-        Executable::call, Tensor::read of the logits.  The write of batch i+1 is issued while batch i computes;
-        every batch is written exactly once and read exactly once."""
+        Executable::call, Tensor::read of the logits.  Two host threads and two input tensors, the scheme of nGraph's
+        nbench --double_buffer (src/tools/nbench/benchmark_pipelined.cpp): while this thread calls the executable on
+        batch i and reads its logits, the other writes batch i+1 into the second tensor (Tensor::write returns when the
+        copy is done, so a single thread could not start it before it has finished enqueueing the kernels).  Every batch
+        is written exactly once and read exactly once."""
         nbytes = self.pin_in.numel() * 4
         cur = self.e2e_i & 1
         if not self.e2e_primed:
+            from concurrent.futures import ThreadPoolExecutor
+            self.writer = ThreadPoolExecutor(max_workers=1)
             self.t_pipe[cur].write_ptr(self.pin_in.data_ptr(), nbytes)
             self.e2e_primed = True
+        # the other tensor is free: the call that read it was waited for by the previous step's read
+        pending = self.writer.submit(self.t_pipe[cur ^ 1].write_ptr, self.pin_in.data_ptr(), nbytes)
         self.exe.call([self.t_out], [self.t_pipe[cur]], validate=False)
         if self.gathered is not None:
             self.sharding.gather_rows(self.logits, [self.batch] * self.world, out=self.gathered)
-        self.t_pipe[cur ^ 1].write_ptr(self.pin_in.data_ptr(), nbytes)  # next batch, overlapping this one's kernels
         self.t_out.read_ptr(self.pin_out.data_ptr(), self.pin_out.numel() * 4)
+        pending.result()
         self.e2e_i += 1
 
     def io_bytes(self):
