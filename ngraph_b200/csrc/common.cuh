@@ -21,6 +21,16 @@ namespace b200
         return cuda_status(cudaGetLastError(), where);
     }
 
+    // Multiprocessors of the current device (grids of the streaming kernels are sized in multiples of it); 148 on a B200,
+    // which is also the answer if the query fails.
+    inline int sm_count()
+    {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        return n;
+    }
+
     inline size_t dtype_size(int t)
     {
         return (t == B200_U8 || t == B200_I8) ? 1 : 4;

@@ -102,7 +102,7 @@ namespace b200
     {
         const bool vec = n % 4 == 0 && (period == 1 || period % 4 == 0) &&
                          ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out) | (period == 1 ? 0 : reinterpret_cast<uintptr_t>(v))) & 15) == 0;
-        const int64_t work = vec ? n / 4 : n, blocks = (work + 255) / 256, cap = 148 * 16;
+        const int64_t work = vec ? n / 4 : n, blocks = (work + 255) / 256, cap = b200::sm_count() * 16;
         const unsigned g = unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
         if (vec && v_left) binary_periodic_kernel<OP, true, true><<<g, 256, 0, st>>>(a, v, out, n, period);
         else if (vec) binary_periodic_kernel<OP, false, true><<<g, 256, 0, st>>>(a, v, out, n, period);
@@ -176,7 +176,7 @@ namespace b200
             in_elements /= 4;
         }
         const bool small = n < (int64_t(1) << 31) && in_elements < (int64_t(1) << 31);
-        const int64_t blocks = (n + 255) / 256, cap = 148 * 16;
+        const int64_t blocks = (n + 255) / 256, cap = b200::sm_count() * 16;
         const unsigned grid = unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
         if (wide && small)
             remap_kernel<uint4, uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), d, n);
@@ -577,7 +577,7 @@ namespace b200
             return false;
         const int64_t tiles = (rows + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
         const int64_t per_sm = (200 * 1024) / int64_t(bytes) < 8 ? (200 * 1024) / int64_t(bytes) : 8;
-        grid = unsigned(tiles < 148 * per_sm ? tiles : 148 * per_sm);
+        grid = unsigned(tiles < b200::sm_count() * per_sm ? tiles : b200::sm_count() * per_sm);
         return true;
     }
 
@@ -768,7 +768,7 @@ namespace b200
     static unsigned grid_for(int64_t n, int threads)
     {
         int64_t blocks = (n + threads - 1) / threads;
-        const int64_t cap = int64_t(148) * 16;
+        const int64_t cap = int64_t(b200::sm_count()) * 16;
         return unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
     }
 }
@@ -983,7 +983,7 @@ extern "C" int b200_reduce_f32(int op, const float* in, float* out, const int64_
     else if (op == B200_REDUCE_SUM && n_axes == 1 && axes[0] == rank - 1 && n_out >= 64)
     {
         // the last axis of a matrix with many rows: panels staged through shared memory
-        const int64_t warps = (n_out + 31) / 32, cap = 148 * 16;
+        const int64_t warps = (n_out + 31) / 32, cap = b200::sm_count() * 16;
         sum_rows_kernel<<<unsigned(warps < cap ? warps : cap), 32, 0, st>>>(in, out, n_out, n_red);
     }
     else if (op == B200_REDUCE_SUM)

@@ -233,7 +233,7 @@ extern "C" int b200_copy_rows(const void* src, void* dst, int64_t rows, int64_t 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool wide = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | uintptr_t(row_bytes) | uintptr_t(dst_pitch_bytes)) & 15) == 0;
     const int64_t units = wide ? rows * (row_bytes / 16) : rows * row_bytes;
-    const int64_t blocks = (units + 255) / 256, cap = 148 * 16;
+    const int64_t blocks = (units + 255) / 256, cap = b200::sm_count() * 16;
     const unsigned grid = unsigned(blocks < cap ? blocks : cap);
     if (wide)
         b200::copy_rows_kernel<16><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, row_bytes / 16,
@@ -271,7 +271,7 @@ extern "C" int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_
         return B200_ERR_INVALID_ARGUMENT;
     int64_t total = N * P * Q * (C / 16);
     int64_t blocks = (total + 255) / 256;
-    unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
+    unsigned grid = unsigned(blocks < b200::sm_count() * 32 ? blocks : b200::sm_count() * 32);
     const bool small = total < (int64_t(1) << 31) && N * H * W * (C / 16) < (int64_t(1) << 31);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint4* in4 = static_cast<const uint4*>(in);
@@ -361,7 +361,7 @@ extern "C" int b200_im2col_c4_u8(const void* in, void* out, int64_t N, int64_t H
         return B200_ERR_INVALID_ARGUMENT;
     int64_t total = N * P * Q * R;
     int64_t blocks = (total + 255) / 256;
-    unsigned grid = unsigned(blocks < 148 * 64 ? blocks : 148 * 64);
+    unsigned grid = unsigned(blocks < b200::sm_count() * 64 ? blocks : b200::sm_count() * 64);
     im2col_c4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint32_t*>(in), static_cast<uint4*>(out), int(N), int(H), int(W), int(P), int(Q), int(R), int(S),
         int(stride_h), int(stride_w), int(pad_h), int(pad_w));
@@ -629,7 +629,7 @@ extern "C" int b200_stem_pack_input(const void* in_nchw, void* cells, int64_t N,
     const int64_t eh = pad_h + (pad_h & 1), ew = pad_w + (pad_w & 1);
     int64_t total = N * Hc * Wc;
     int64_t blocks = (total + 255) / 256;
-    unsigned grid = unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
+    unsigned grid = unsigned(blocks < b200::sm_count() * 32 ? blocks : b200::sm_count() * 32);
     s2d_pack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(in_nchw),
                                                                        static_cast<uint4*>(cells), int(N), int(C), int(H), int(W),
                                                                        int(Hc), int(Wc), int(eh), int(ew));

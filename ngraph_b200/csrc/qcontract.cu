@@ -1275,7 +1275,7 @@ namespace b200
             int dev = 0;
             if (cudaGetDevice(&dev) != cudaSuccess ||
                 cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-                n = 148;
+                n = 148; // a B200
         }
         return n;
     }

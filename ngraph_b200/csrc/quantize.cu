@@ -376,7 +376,7 @@ namespace b200
     static unsigned generic_grid(int64_t total)
     {
         int64_t b = (total + QT - 1) / QT;
-        const int64_t cap = 148 * 8 * 4;
+        const int64_t cap = b200::sm_count() * 8 * 4;
         return unsigned(b < cap ? (b > 0 ? b : 1) : cap);
     }
 

@@ -113,7 +113,7 @@ namespace b200
 
     static unsigned blocks_for(int64_t n)
     {
-        const int64_t blocks = (n + 255) / 256, cap = 148 * 16;
+        const int64_t blocks = (n + 255) / 256, cap = b200::sm_count() * 16;
         return unsigned(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
     }
 
