@@ -56,3 +56,29 @@ def test_argument_validation_without_device():
     cp.stride_h = 1
     assert lib.LIB.b200_qconv_out_shape(ctypes.byref(cp), ctypes.byref(p), ctypes.byref(q)) == 0
     assert (p.value, q.value) == (8, 8)
+
+
+def test_argument_validation_of_the_glue_entry_points():
+    """the f32 glue, Concat and zero-point entry points: bad arguments are refused on the host, empty work is a no-op"""
+    L = lib.LIB
+    i64 = ctypes.c_int64
+    assert L.b200_f32_binary(99, None, None, None, 4, None) == -1            # unknown op
+    assert L.b200_f32_binary(0, None, None, None, 0, None) == 0              # nothing to do
+    assert L.b200_f32_binary(0, None, None, None, 4, None) == -1             # null operands
+    assert L.b200_f32_binary_periodic(0, None, None, None, 8, 0, 0, None) == -1   # period 0
+    assert L.b200_f32_unary(-1, None, None, 4, None) == -1
+    assert L.b200_softmax_rows_f32(None, None, -1, 4, None) == -1
+    assert L.b200_softmax_rows_f32(None, None, 0, 4, None) == 0
+    assert L.b200_layer_norm_rows_f32(None, None, None, None, 3, 4, ctypes.c_float(1e-5), None) == -1
+    assert L.b200_gelu_f32(None, None, 0, None) == 0
+    assert L.b200_bmm_f32(None, None, None, 1, -1, 4, 4, None) == -1
+    assert L.b200_copy_rows(None, None, 2, 8, 4, None) == -1                 # pitch shorter than a row
+    assert L.b200_copy_rows(None, None, 0, 8, 8, None) == 0
+    shape, axes = (i64 * 2)(4, 5), (i64 * 2)(1, 1)
+    assert L.b200_reduce_f32(7, None, None, shape, 2, axes, 1, None) == -1   # unknown reduction
+    assert L.b200_reduce_f32(0, None, None, shape, 2, axes, 2, None) == -1   # an axis named twice
+    assert L.b200_strided_sums(None, lib.F32, None, 1, 1, 1, 1, 1, 1, None) == -1  # only u8 / i8 are summed
+    e = lib.Epilogue()
+    e.round_half_away, e.out_type = 2, lib.U8                                # raw accumulators exist as int32 only
+    assert L.b200_qgemm(None, lib.U8, None, None, 4, 4, 16, ctypes.byref(e), None) == -1
+    assert L.b200_requant_zero_points(None, None, None, None, ctypes.byref(e), None, None) == -1
