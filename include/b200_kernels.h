@@ -276,6 +276,11 @@ B200_API int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_t 
                                   int64_t win_h, int64_t win_w, int64_t stride_h, int64_t stride_w,
                                   int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
                                   void* stream);
+/* the same for i8 elements (padding positions are skipped; the lowest value is -128) */
+B200_API int b200_maxpool_nhwc_i8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C,
+                                  int64_t win_h, int64_t win_w, int64_t stride_h, int64_t stride_w,
+                                  int64_t pad_h, int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above,
+                                  void* stream);
 
 /*
  * Global average pooling head on channels-last u8 [N,H,W,C] -> u8 [N,C]:

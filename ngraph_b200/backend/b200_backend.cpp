@@ -1926,8 +1926,9 @@ void B200Executable::compile_max_pool(const std::shared_ptr<Node>& node)
 {
     auto op = as_type_ptr<op::v0::MaxPool>(node);
     const Shape is = node->get_input_shape(0), os = node->get_output_shape(0);
-    if (node->get_input_element_type(0) != element::u8 || is.size() != 4 || is[1] % 16 != 0)
-        unsupported(*node, "u8 NCHW input with a multiple of 16 channels");
+    const bool is_signed = node->get_input_element_type(0) == element::i8;
+    if ((node->get_input_element_type(0) != element::u8 && !is_signed) || is.size() != 4 || is[1] % 16 != 0)
+        unsupported(*node, "u8 / i8 NCHW input with a multiple of 16 channels");
     int x = nhwc_slot(node->input_value(0));
     int y = new_slot(Slot::ARENA, shape_size(os));
     int64_t N = is[0], C = is[1], H = is[2], W = is[3];
@@ -1936,7 +1937,8 @@ void B200Executable::compile_max_pool(const std::shared_ptr<Node>& node)
     int64_t pb0 = op->get_padding_below()[0], pb1 = op->get_padding_below()[1];
     int64_t pa0 = op->get_padding_above()[0], pa1 = op->get_padding_above()[1];
     emit(node, "maxpool", [=](const Ptrs& p, cudaStream_t st) {
-        return b200_maxpool_nhwc_u8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st);
+        return is_signed ? b200_maxpool_nhwc_i8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st)
+                         : b200_maxpool_nhwc_u8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st);
     });
     value_of(node->output(0)).nhwc = y;
 }

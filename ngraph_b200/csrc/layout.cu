@@ -75,7 +75,8 @@ namespace b200
     // ---- pooling on channels-last u8 --------------------------------------------------------
 
     // MaxPool: runtime::reference::max_pool (runtime/reference/max_pool.hpp:124-236), padding positions skipped.
-    // One thread per 16 channels of one output pixel (128-bit loads, __vmaxu4).
+    // One thread per 16 channels of one output pixel (128-bit loads, __vmaxu4; SIGNED: i8 elements, __vmaxs4).
+    template <bool SIGNED>
     __global__ void __launch_bounds__(256) maxpool_nhwc_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
                                                                   int N, int H, int W, int C16, int P, int Q, int win_h,
                                                                   int win_w, int stride_h, int stride_w, int pad_h,
@@ -90,7 +91,8 @@ namespace b200
             t /= Q;
             int p = int(t % P);
             int n = int(t / P);
-            uint4 m = make_uint4(0, 0, 0, 0);
+            const uint32_t lowest = SIGNED ? 0x80808080u : 0u; // the identity of the max: -128 / 0 in every byte
+            uint4 m = make_uint4(lowest, lowest, lowest, lowest);
             for (int r = 0; r < win_h; ++r)
             {
                 int h = p * stride_h - pad_h + r;
@@ -102,10 +104,10 @@ namespace b200
                     if (w < 0 || w >= W)
                         continue;
                     uint4 v = reinterpret_cast<const uint4*>(in)[((int64_t(n) * H + h) * W + w) * C16 + c];
-                    m.x = __vmaxu4(m.x, v.x);
-                    m.y = __vmaxu4(m.y, v.y);
-                    m.z = __vmaxu4(m.z, v.z);
-                    m.w = __vmaxu4(m.w, v.w);
+                    m.x = SIGNED ? __vmaxs4(m.x, v.x) : __vmaxu4(m.x, v.x);
+                    m.y = SIGNED ? __vmaxs4(m.y, v.y) : __vmaxu4(m.y, v.y);
+                    m.z = SIGNED ? __vmaxs4(m.z, v.z) : __vmaxu4(m.z, v.z);
+                    m.w = SIGNED ? __vmaxs4(m.w, v.w) : __vmaxu4(m.w, v.w);
                 }
             }
             reinterpret_cast<uint4*>(out)[i] = m;
@@ -255,9 +257,9 @@ extern "C" int b200_transpose_u8(const void* in, void* out, int64_t rows, int64_
     return b200::launch_transpose(in, out, 1, rows, cols, rows, static_cast<cudaStream_t>(stream), "b200_transpose_u8");
 }
 
-extern "C" int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C,
-                                    int64_t win_h, int64_t win_w, int64_t stride_h, int64_t stride_w, int64_t pad_h,
-                                    int64_t pad_w, int64_t pad_h_above, int64_t pad_w_above, void* stream)
+static int maxpool_nhwc_bytes(bool is_signed, const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t win_h,
+                              int64_t win_w, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t pad_h_above,
+                              int64_t pad_w_above, void* stream, const char* what)
 {
     using namespace b200;
     if (N < 0 || H <= 0 || W <= 0 || C <= 0 || win_h <= 0 || win_w <= 0 || stride_h <= 0 || stride_w <= 0)
@@ -276,17 +278,37 @@ extern "C" int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint4* in4 = static_cast<const uint4*>(in);
     uint4* out4 = static_cast<uint4*>(out);
-    if (small && win_h == 3 && win_w == 3)
+    if (is_signed)
+        maxpool_nhwc_u8_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H),
+                                                           int(W), int(C / 16), int(P), int(Q), int(win_h), int(win_w),
+                                                           int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    else if (small && win_h == 3 && win_w == 3)
         maxpool_nhwc_u8_fixed_kernel<3, 3><<<grid, 256, 0, st>>>(in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q),
                                                                  int(stride_h), int(stride_w), int(pad_h), int(pad_w));
     else if (small && win_h == 2 && win_w == 2)
         maxpool_nhwc_u8_fixed_kernel<2, 2><<<grid, 256, 0, st>>>(in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q),
                                                                  int(stride_h), int(stride_w), int(pad_h), int(pad_w));
     else
-        maxpool_nhwc_u8_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H),
+        maxpool_nhwc_u8_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H),
                                                      int(W), int(C / 16), int(P), int(Q), int(win_h), int(win_w),
                                                      int(stride_h), int(stride_w), int(pad_h), int(pad_w));
-    return after_launch("b200_maxpool_nhwc_u8");
+    return after_launch(what);
+}
+
+extern "C" int b200_maxpool_nhwc_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t win_h, int64_t win_w,
+                                    int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t pad_h_above,
+                                    int64_t pad_w_above, void* stream)
+{
+    return maxpool_nhwc_bytes(false, in, out, N, H, W, C, win_h, win_w, stride_h, stride_w, pad_h, pad_w, pad_h_above, pad_w_above, stream,
+                              "b200_maxpool_nhwc_u8");
+}
+
+extern "C" int b200_maxpool_nhwc_i8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t win_h, int64_t win_w,
+                                    int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t pad_h_above,
+                                    int64_t pad_w_above, void* stream)
+{
+    return maxpool_nhwc_bytes(true, in, out, N, H, W, C, win_h, win_w, stride_h, stride_w, pad_h, pad_w, pad_h_above, pad_w_above, stream,
+                              "b200_maxpool_nhwc_i8");
 }
 
 extern "C" int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const float* scale_in, const float* scale_out,

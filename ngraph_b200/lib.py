@@ -54,6 +54,7 @@ def _load():
         "b200_transpose_u8": (ci, [vp, vp, i64, i64, vp]),
         "b200_nhwc_to_nchw_b32": (ci, [vp, vp, i64, i64, i64, vp]),
         "b200_maxpool_nhwc_u8": (ci, [vp, vp] + [i64] * 12 + [vp]),
+        "b200_maxpool_nhwc_i8": (ci, [vp, vp] + [i64] * 12 + [vp]),
         "b200_global_avgpool_q_nhwc_u8": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
         "b200_im2col_c4_u8": (ci, [vp, vp] + [i64] * 11 + [vp]),
         "b200_requant_scale": (ci, [vp, vp, vp, vp, vp]),

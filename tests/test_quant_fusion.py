@@ -254,9 +254,10 @@ def test_unfused_residual_block_tail(backends, sum_dtype):
 def test_hoisted_max_pool_and_concat_on_the_device(backends):
     b200, ref = backends
     rng = np.random.default_rng(6)
-    fn = max_pool_graph(np.uint8, 0.037, 0, shape=(2, 32, 14, 14))
-    x = rng.integers(0, 256, size=(2, 32, 14, 14)).astype(np.uint8)
-    np.testing.assert_array_equal(bits(b200.compile(fn).run(x)[0]), bits(ref.compile(fn).run(x)[0]))
+    for dtype, zp in ((np.uint8, 0), (np.int8, -3)):
+        fn = max_pool_graph(dtype, 0.037, zp, shape=(2, 32, 14, 14))
+        x = rng.integers(np.iinfo(dtype).min, np.iinfo(dtype).max + 1, size=(2, 32, 14, 14)).astype(dtype)
+        np.testing.assert_array_equal(bits(b200.compile(fn).run(x)[0]), bits(ref.compile(fn).run(x)[0]))
     for axis, shapes in ((1, ((2, 16, 5, 5), (2, 32, 5, 5), (2, 16, 5, 5))), (3, ((2, 3, 5, 1), (2, 3, 5, 6))), (0, ((1, 8), (3, 8)))):
         fn = concat_graph([0.02] * len(shapes), shapes, axis)
         xs = [rng.integers(0, 256, size=s).astype(np.uint8) for s in shapes]
