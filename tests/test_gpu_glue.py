@@ -227,7 +227,7 @@ def test_broadcast_and_permute(L):
     np.testing.assert_array_equal(outc.cpu().numpy(), np.broadcast_to(col[:, None], (6, 8)))
 
 
-@pytest.mark.parametrize("batch,m,k,n", [(3, 17, 96, 21), (2, 130, 70, 200), (2, 100, 33, 64), (1, 384, 64, 384), (5, 64, 16, 48)])
+@pytest.mark.parametrize("batch,m,k,n", [(3, 17, 96, 21), (2, 130, 70, 200), (2, 100, 33, 64), (1, 384, 64, 384), (5, 64, 16, 48), (1, 140, 300, 130)])
 def test_bmm_accumulates_in_double_in_order(L, batch, m, k, n):
     """small products run one thread per 4 x 4 outputs, large ones through shared-memory panels: the same bits either way"""
     rng = np.random.default_rng(4)
