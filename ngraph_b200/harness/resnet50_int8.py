@@ -162,17 +162,31 @@ class QuantizedResNet50:
                 h, w, cin = ho, wo, cout
         return total + 2048 * self.classes
 
-    def build(self, ng, batch, fused=True, decomposed=None, image_hw=None, intermediate_results=False):
+    def build(self, ng, batch, fused=True, decomposed=None, image_hw=None, intermediate_results=False, framework_style=False):
         """Returns (Function, parameter).  fused=True: the graph a client hands to the B200 backend.
-        fused=False: every fused op replaced by `decomposed` (oracle.interpreter), for INTERPRETER."""
+        fused=False: every fused op replaced by `decomposed` (oracle.interpreter), for INTERPRETER.
+        framework_style=True: the graph a framework bridge emits before any backend fusion: every convolution is a
+        QuantizedConvolutionBias WITHOUT relu followed by Dequantize -> [Add(Dequantize(shortcut))] -> Relu -> Quantize,
+        with the same scales; a backend's quantisation fusion is expected to turn it back into the fused graph."""
         h, w = image_hw or (self.image_size, self.image_size)
         x = ng.parameter(np.float32, (batch, 3, h, w))
         a = ng.quantize(x, self.s_input, np.int8(0), np.int8, (), 4)
+        scale_of, alive = {}, []  # id of a quantized value -> its scale (for the shortcut's Dequantize); values kept alive
 
         def conv(name, inp, res=None):
             L = self.layers[name]
             geom = dict(stride=(L["stride"],) * 2, pad_below=(L["pad"],) * 2)
             out_dtype = np.uint8 if L["relu"] else np.int8
+            if framework_style:
+                y = ng.quantized_conv_bias(inp, L["w_q"], L["bias_q"], L["scale"], False, **geom)  # i8, scale s_out
+                if L["relu"]:
+                    f = ng.dequantize(y, L["s_out"], np.int8(0))
+                    if res is not None:
+                        f = ng.add(f, ng.dequantize(res, scale_of[id(res)], np.zeros((), np.dtype(res.dtype))))
+                    y = ng.quantize(ng.relu(f), L["s_out"], np.uint8(0), np.uint8, (), 4)
+                scale_of[id(y)] = L["s_out"]
+                alive.append(y)
+                return y
             if fused:
                 if res is None:
                     return ng.quantized_conv_bias(inp, L["w_q"], L["bias_q"], L["scale"], L["relu"], **geom)
@@ -188,7 +202,10 @@ class QuantizedResNet50:
         taps = []
         a = conv("stem", a)
         taps.append(a)
+        stem_out = a
         a = ng.max_pool(a, (3, 3), (2, 2), (1, 1))
+        scale_of[id(a)] = scale_of.get(id(stem_out))
+        alive.append(a)
         taps.append(a)
         for si, (blocks, mid, cout, stride) in enumerate(STAGES):
             for b in range(blocks):

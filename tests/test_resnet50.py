@@ -35,6 +35,38 @@ def test_fused_graph_is_what_a_quantizing_client_builds(model):
     assert ng.capi().ngc_function_op_count(fn.h) > 200
 
 
+@needs_ngraph
+def test_framework_style_graph_is_fused_back_by_the_plugin(model):
+    """Every convolution written as QuantizedConvolutionBias -> Dequantize -> [Add] -> Relu -> Quantize (what a bridge emits
+    before backend fusion): the plugin's graph passes must arrive at the op mix of the hand-fused graph, without a device."""
+    import collections
+    ng.load_b200()
+    loose, _ = model.build(ng, 2, framework_style=True, image_hw=(32, 32))
+    fused, _ = model.build(ng, 2, fused=True, image_hw=(32, 32))
+    before = collections.Counter(ng.function_op_names(loose, lowered=False))
+    assert before["Relu"] == 49 and before["Add"] == 16 and before["QuantizedConvolutionBiasAdd"] == 0
+    got = collections.Counter(ng.function_op_names(ng.after_b200_passes(loose), lowered=False))
+    want = collections.Counter(ng.function_op_names(ng.after_b200_passes(fused), lowered=False))
+    for op in ("QuantizedConvolutionBias", "QuantizedConvolutionBiasAdd", "QuantizedConvolutionBiasSignedAdd", "Convert", "MaxPool",
+               "Quantize", "Dequantize", "QuantizedDot", "AvgPool", "Relu", "Add", "Divide"):
+        assert got[op] == want[op], (op, got[op], want[op])
+    assert got["Relu"] == 0 and got["QuantizedConvolutionBiasAdd"] + got["QuantizedConvolutionBiasSignedAdd"] == 16
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_framework_style_graph_gives_the_fused_graphs_logits(model):
+    ng.load_b200()
+    b200 = ng.Backend("B200")
+    x = synthetic_images(2, 9, 224)[:, :, :64, :64]
+    loose, _ = model.build(ng, 2, framework_style=True, image_hw=(64, 64))
+    fused, _ = model.build(ng, 2, fused=True, image_hw=(64, 64))
+    exe = b200.compile(loose, perf=True)
+    got = exe.run(x)[0]
+    np.testing.assert_array_equal(got.view(np.uint32), b200.compile(fused).run(x)[0].view(np.uint32))
+    assert not any(n.split(":")[0] in ("Relu", "Add") for n, _, _ in exe.performance_data())
+
+
 @pytest.mark.gpu
 @needs_ngraph
 def test_resnet50_parity_with_interpreter(model):
