@@ -299,3 +299,42 @@ def test_quantized_concat_builder_graph(backends, dtype):
     data = [rng.integers(np.iinfo(dtype).min, np.iinfo(dtype).max + 1, size=s).astype(dtype) for s in big]
     ranges = [np.float32([-1.5]), np.float32([-6.0]), np.float32([-0.25]), np.float32([3.0]), np.float32([5.5]), np.float32([9.75])]
     np.testing.assert_array_equal(b200.compile(fn).run(*data, *ranges)[0], ref.compile(fn).run(*data, *ranges)[0])
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_exact_rewrites_compose_on_random_graphs(plugin, seed):
+    """Random small graphs built from the three rewrites that must not change a bit (Dequantize -> MaxPool, Dequantize... ->
+    Concat, Dequantize -> Quantize), nested in random order with random scales: the graph after the plugin's passes gives
+    the INTERPRETER the same bytes as the graph before them, and has lost at least one f32 op."""
+    rng = np.random.default_rng(seed)
+    scales = [np.float32(s) for s in (0.02, 0.037, 0.11)]
+    params, data = [], []
+
+    def leaf(shape):
+        p = ng.parameter(np.uint8, shape)
+        params.append(p)
+        data.append(rng.integers(0, 256, size=shape).astype(np.uint8))
+        return p
+
+    def dequantized(depth, shape, s):
+        """an f32 value of `shape` whose integer source was (or will be) quantized with scale s"""
+        kind = rng.integers(0, 3) if depth > 0 else 3
+        if kind == 0:      # MaxPool over a larger dequantized tensor
+            src = (shape[0], shape[1], shape[2] * 2, shape[3] * 2)
+            return ng.max_pool(dequantized(depth - 1, src, s), (2, 2), (2, 2))
+        if kind == 1:      # Concat of two dequantized halves along the channels
+            half = (shape[0], shape[1] // 2, shape[2], shape[3])
+            return ng.concat([dequantized(depth - 1, half, s), dequantized(depth - 1, half, s)], 1)
+        if kind == 2:      # a Quantize / Dequantize round trip in between, sometimes with another scale (not removable)
+            s2 = s if rng.random() < 0.7 else scales[int(rng.integers(0, 3))]
+            q = ng.quantize(dequantized(depth - 1, shape, s), s2, 0, np.uint8, round_mode=RNE)
+            return ng.dequantize(q, s2, 0)
+        return ng.dequantize(leaf(shape), s, 0)
+
+    y = dequantized(3, (1, 32, 4, 4), scales[int(rng.integers(0, 3))])
+    before = ng.Function([y], params)
+    after = ng.after_b200_passes(before)
+    got, want = run_interpreter(after, data), run_interpreter(before, data)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    f32_ops = lambda fn: sum(n in ("Dequantize", "Quantize") for n in names(fn))
+    assert f32_ops(after) <= f32_ops(before)
