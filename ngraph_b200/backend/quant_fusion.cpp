@@ -80,6 +80,11 @@ namespace
 
     size_t user_count(const Output<Node>& v) { return v.get_target_inputs().size(); }
 
+    // Relu commutes with a Dequantize only for a positive scale.  A run-time scale cannot be inspected (quantisation
+    // scales are positive by construction and the CPU backend fuses without looking); a Constant that is not positive
+    // rules the rewrite out.
+    bool may_be_positive_scale(const Output<Node>& v) { return !constant_of(v) || is_positive_scale(v); }
+
     // Steps back over Reshape / Broadcast nodes that change nothing (same shape in and out, no transposition): frameworks
     // leave such nodes between a Dequantize and the Add that consumes it.
     Output<Node> skip_identity_layout(Output<Node> v)
@@ -119,7 +124,7 @@ namespace
     bool fuse_conv_relu(const NodePtr& relu, Counts& counts)
     {
         auto dq = plain_dequantize(relu->input_value(0));
-        if (!dq || user_count(dq->input_value(0)) != 1)
+        if (!dq || user_count(dq->input_value(0)) != 1 || !may_be_positive_scale(dq->input_value(1)))
             return false;
         NodePtr conv = dq->input_value(0).get_node_shared_ptr();
         NodePtr fused;
@@ -187,7 +192,7 @@ namespace
         if (!add)
             return false;
         AddBranch left = add_branch(add->input_value(0)), right = add_branch(add->input_value(1));
-        if (!left.dq || !right.dq)
+        if (!left.dq || !right.dq || !may_be_positive_scale(left.dq->input_value(1)) || !may_be_positive_scale(right.dq->input_value(1)))
             return false;
         if (left.conv && right.conv)
         {

@@ -96,6 +96,8 @@ def test_conv_bias_relu_is_fused(plugin):
     # a non-zero zero point, or a second reader of the convolution, keeps the graph as it was
     assert "Relu" in names(ng.after_b200_passes(conv_bias_relu_graph(filt, bias, np.float32([30 / sigma]), zp=3)))
     assert "Relu" in names(ng.after_b200_passes(conv_bias_relu_graph(filt, bias, np.float32([30 / sigma]), second_user=True)))
+    # a negative Dequantize scale: Relu no longer commutes with it
+    assert "Relu" in names(ng.after_b200_passes(conv_bias_relu_graph(filt, bias, np.float32([30 / sigma]), dq_scale=-0.05)))
 
 
 def test_core_conv_relu_becomes_quantized_convolution_relu(plugin):
