@@ -94,3 +94,27 @@ def test_full_width_encoder_commutes_with_a_permutation_of_the_batch():
     rows = lambda a, width: a.reshape(dims["batch"], dims["seq"], *width)[perm].reshape(a.shape)
     out_p = exe.run(rows(ids, ()), rows(seg, ()))[0]
     np.testing.assert_array_equal(out_p.view(np.uint32), rows(out, (dims["hidden"],)).view(np.uint32))
+
+
+@needs_reference
+def test_plugin_keeps_layer_norm_and_gelu_whole_and_constants_small():
+    """compile()'s graph passes, without a device: LayerNorm and Gelu stay single ops (one kernel each on the device), and
+    the bias rows / scalar factors that are broadcast to [tokens, features] are NOT folded into constants of that size."""
+    import os
+    from ngraph_b200 import ngraph_api as ng
+    ng.load_b200()
+    dims = dict(layers=1, hidden=768, heads=12, ffn=3072, seq=384, batch=4, vocab=1000)  # 1536 tokens: above the folding fence
+    fn = ng.bert_encoder(seed=3, **dims)
+    ops = collections.Counter(ng.function_op_names(ng.after_b200_passes(fn), lowered=False))
+    assert ops["LayerNorm"] == 3 and ops["Gelu"] == 1 and ops["Sum"] == 0 and ops["Erf"] == 0
+    assert ops["Broadcast"] >= 7 and ops["StopGradient"] == 0   # bias rows and the attention factor stay Broadcast nodes
+    old = os.environ.get("B200_DECOMPOSE_ALL")
+    os.environ["B200_DECOMPOSE_ALL"] = "1"
+    try:
+        plain = collections.Counter(ng.function_op_names(ng.after_b200_passes(fn), lowered=False))
+    finally:
+        if old is None:
+            del os.environ["B200_DECOMPOSE_ALL"]
+        else:
+            os.environ["B200_DECOMPOSE_ALL"] = old
+    assert plain["LayerNorm"] == 0 and plain["Gelu"] == 0 and plain["Sum"] == 9 and plain["Erf"] == 1
