@@ -10,7 +10,10 @@
 
 #include "ngraph/ngraph.hpp"
 #include "ngraph/builder/quantized_concat_builder.hpp"
+#include "ngraph/op/experimental/batch_mat_mul.hpp"
 #include "ngraph/op/experimental/quantized_conv_bias.hpp"
+#include "ngraph/op/gelu.hpp"
+#include "ngraph/op/layer_norm.hpp"
 #include "ngraph/op/experimental/quantized_conv_relu.hpp"
 #include "ngraph/op/experimental/quantized_dot_bias.hpp"
 #include "ngraph/runtime/backend.hpp"
@@ -241,6 +244,42 @@ NGC_API void* ngc_quantized_concat(void** values, void** mins, void** maxs, int 
         }
         return box(builder::QuantizedConcatBuilder(parts, size_t(axis), lo, hi));
     }, nullptr);
+}
+
+// the float ops of quantized graphs' f32 islands (for the oracle pins; the encoder graph itself is built in bert_int8.cpp)
+NGC_API void* ngc_sum(void* x, const int64_t* axes, int n_axes)
+{
+    return guarded([&]() -> void* {
+        AxisSet ax;
+        for (int i = 0; i < n_axes; ++i) ax.insert(size_t(axes[i]));
+        return box(std::make_shared<op::v0::Sum>(val(x), ax));
+    }, nullptr);
+}
+
+NGC_API void* ngc_softmax(void* x, const int64_t* axes, int n_axes)
+{
+    return guarded([&]() -> void* {
+        AxisSet ax;
+        for (int i = 0; i < n_axes; ++i) ax.insert(size_t(axes[i]));
+        return box(std::make_shared<op::v0::Softmax>(val(x), ax));
+    }, nullptr);
+}
+
+NGC_API void* ngc_layer_norm(void* x, void* scale, void* bias, int64_t begin_norm_axis, double epsilon)
+{
+    return guarded([&]() -> void* {
+        return box(std::make_shared<op::v0::LayerNorm>(val(x), val(scale), val(bias), false, begin_norm_axis, epsilon));
+    }, nullptr);
+}
+
+NGC_API void* ngc_gelu(void* x)
+{
+    return guarded([&]() -> void* { return box(std::make_shared<op::v0::Gelu>(val(x))); }, nullptr);
+}
+
+NGC_API void* ngc_batch_mat_mul(void* a, void* b)
+{
+    return guarded([&]() -> void* { return box(std::make_shared<op::v0::BatchMatMul>(val(a), val(b))); }, nullptr);
 }
 
 NGC_API void* ngc_convert(void* x, int et)

@@ -56,6 +56,9 @@ def capi():
             "ngc_bert_encoder": (vp, [ci] * 7 + [ctypes.c_uint64, ci]),
             "ngc_function_op_names": (ci, [vp, ci, ctypes.c_char_p, ci]),
             "ngc_concat": (vp, [pvp, ci, i64]),
+            "ngc_sum": (vp, [vp, p64, ci]), "ngc_softmax": (vp, [vp, p64, ci]),
+            "ngc_layer_norm": (vp, [vp, vp, vp, i64, ctypes.c_double]), "ngc_gelu": (vp, [vp]),
+            "ngc_batch_mat_mul": (vp, [vp, vp]),
             "ngc_quantized_concat": (vp, [pvp, pvp, pvp, ci, i64]),
             "ngc_function_after_plugin_passes": (vp, [vp, ctypes.c_char_p]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
@@ -221,6 +224,29 @@ def quantized_concat(values, mins, maxs, axis):
     """builder::QuantizedConcatBuilder: mins / maxs are f32 [1] values, one pair per operand"""
     arr = lambda vs: (ctypes.c_void_p * len(vs))(*[v.h for v in vs])
     return Value(capi().ngc_quantized_concat(arr(values), arr(mins), arr(maxs), len(values), axis), "QuantizedConcat")
+
+
+def reduce_sum(x, axes):
+    axes = sorted(axes)
+    return Value(capi().ngc_sum(x.h, _i64(axes), len(axes)), "Sum")
+
+
+def softmax(x, axes):
+    axes = sorted(axes)
+    return Value(capi().ngc_softmax(x.h, _i64(axes), len(axes)), "Softmax")
+
+
+def layer_norm(x, scale, bias, begin_norm_axis=1, epsilon=1e-5):
+    scale, bias = _val(scale, np.float32), _val(bias, np.float32)  # kept alive across the call
+    return Value(capi().ngc_layer_norm(x.h, scale.h, bias.h, begin_norm_axis, epsilon), "LayerNorm")
+
+
+def gelu(x):
+    return Value(capi().ngc_gelu(x.h), "Gelu")
+
+
+def batch_mat_mul(a, b):
+    return Value(capi().ngc_batch_mat_mul(a.h, b.h), "BatchMatMul")
 
 
 def convert(x, dtype):
