@@ -91,6 +91,15 @@ B200_API void b200_reset_launch_count(void);
 B200_API int b200_device_status(int* status_out);
 
 /*
+ * Self-test of that give-up path (diagnostic; no reference counterpart - nGraph's backends have no device-side waits).
+ * Queues one small kernel whose single waiting thread polls, through the same bounded wait the contraction kernels
+ * use, an mbarrier that nothing arrives at.  After limit_ns (1 .. 100 000 000) the wait gives up, the kernel stores
+ * code 9001 in the device status word and returns normally; the context stays usable.  The next b200_device_status()
+ * then returns B200_ERR_DEVICE_STATUS once (and the plugin's Tensor::read throws once).  Nothing traps or spins forever.
+ */
+B200_API int b200_selftest_bounded_wait(int64_t limit_ns, void* stream);
+
+/*
  * Quantize: f32 -> u8 / i8 / i32.
  *
  * Replaces runtime::reference::quantize<float,QUANT>
@@ -399,7 +408,10 @@ B200_API int b200_qconv_stem(const void* cells, int data_type, const int8_t* pac
  * b200_stem_pack_input + b200_qconv_stem in one call that allocates nothing.  No counterpart in the reference: nGraph
  * backends allocate their workspaces when a Function is compiled.  The cell grid lives in a fixed 16 MiB device array
  * inside this library (b200_qconv_stem_static_capacity() bytes; a call needs b200_stem_cells_bytes(...) of it), looked up once per device at the first call on that device; that first call should be made before
- * a stream capture starts.  Larger problems are refused with B200_ERR_TOO_LARGE before anything is launched.  Nothing in
+ * a stream capture starts.  Larger problems are refused with B200_ERR_TOO_LARGE, and every other invalid argument (data
+ * type, channel counts, epilogue record, null pointers) with its own code, before anything is launched, so a refused call
+ * never writes the shared array.  The 16 MiB are part of the library's device image: every GPU context that loads the
+ * library holds them until it exits, whether or not this entry point is ever called.  Nothing in
  * the array has to be zero beforehand: every cell, padding cells included, is written by the packing kernel before the
  * convolution reads it.  The array is shared by all callers of the device: two calls whose kernels can overlap in time
  * (different streams, different threads) race on it; calls on one stream are ordered and safe.  in_nchw is the one-byte

@@ -21,6 +21,7 @@
 #include <sstream>
 
 #include "b200_kernels.h"
+#include "graph_passes.hpp"
 #include "quant_fusion.hpp"
 #include "ngraph/op/concat.hpp"
 #include "ngraph/descriptor/layout/dense_tensor_layout.hpp"
@@ -417,7 +418,6 @@ bool B200Backend::is_device_memory(void* ptr)
     return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
 }
 
-static bool runs_undecomposed(const Node& node);
 
 bool B200Backend::is_supported(const Node& node) const
 {
@@ -617,97 +617,6 @@ bool B200Executable::avgpool_head_member(const Node* node)
     return false;
 }
 
-// The graph-level pipeline of compile(): what nGraph's backends run before they lower (cpu_external_function.cpp:1289-1335
-// keeps the CPU backend's list), with the plugin's own quantisation fusion in the place CPUQuantFusion has there.
-// Fused ops the device runs as one kernel with the arithmetic of their decomposition; everything else is decomposed.
-static bool runs_undecomposed(const Node& node)
-{
-    if (auto ln = as_type<const op::v0::LayerNorm>(&node))
-    {
-        if (!ln->get_use_affine() || ln->get_keep_stats() || node.get_input_element_type(0) != element::f32 ||
-            !node.get_input_partial_shape(0).is_static())
-            return false;
-        const Shape shape = node.get_input_shape(0);
-        const int64_t rank = int64_t(shape.size());
-        const int64_t axis = ln->get_begin_norm_axis() >= 0 ? ln->get_begin_norm_axis() : rank + ln->get_begin_norm_axis();
-        return rank >= 1 && axis == rank - 1 && shape.back() >= 1 && shape.back() <= 1535 && node.get_input_shape(1).size() == 1 &&
-               node.get_input_shape(2).size() == 1;
-    }
-    if (is_type<op::v0::Gelu>(&node))
-        return node.get_input_element_type(0) == element::f32;
-    return false;
-}
-
-// ConstantFolding turns Broadcast(Constant) into a Constant as large as the broadcast's output: a 768-element bias
-// row added to 24 576 rows becomes 75 MB of constant data, per layer.  Broadcasts of that kind (new leading axes only,
-// at least 64 Ki output elements) are fenced off with an identity op that has no folder (StopGradient) while the pass
-// runs; the elementwise op that reads the Broadcast then indexes the small constant directly (compile_f32_glue).
-static void fence_large_constant_broadcasts(const std::shared_ptr<Function>& function)
-{
-    for (auto& node : function->get_ordered_ops())
-    {
-        auto bc = as_type_ptr<op::v0::Broadcast>(node);
-        if (!bc || !is_type<op::v0::Constant>(bc->input_value(0).get_node()) || shape_size(bc->get_output_shape(0)) < 65536)
-            continue;
-        const AxisSet& added = bc->get_broadcast_axes();
-        bool leading = !added.empty();
-        for (size_t i = 0; i < added.size() && leading; ++i)
-            leading = added.count(i) == 1;
-        if (leading)
-            bc->input(0).replace_source_output(std::make_shared<op::v0::StopGradient>(bc->input_value(0))->output(0));
-    }
-}
-
-static void remove_fences(const std::shared_ptr<Function>& function)
-{
-    for (auto& node : function->get_ordered_ops())
-        if (is_type<op::v0::StopGradient>(node))
-            node->output(0).replace(node->input_value(0));
-}
-
-static void run_graph_passes(const std::shared_ptr<Function>& function)
-{
-    bool fenced = false;
-    for (auto& node : function->get_ordered_ops()) // a graph that has such nodes of its own is left as it is
-        fenced = fenced || is_type<op::v0::StopGradient>(node);
-    {
-        ngraph::pass::Manager pre;
-        pre.register_pass<ngraph::pass::LikeReplacement>();
-        if (getenv("B200_DECOMPOSE_ALL")) // the float islands as chains of elementwise ops and reductions (for comparison)
-            pre.register_pass<ngraph::pass::FusedOpDecomposition>();
-        else
-            pre.register_pass<ngraph::pass::FusedOpDecomposition>(runs_undecomposed);
-        pre.register_pass<ngraph::pass::ImplicitBroadcastElimination>(); // NumPy-style operands become explicit Broadcast nodes
-        pre.run_passes(function);
-    }
-    if (!fenced)
-        fence_large_constant_broadcasts(function);
-    {
-        ngraph::pass::Manager pm;
-        if (ngraph::runtime::b200::pass::quant_fusion_enabled())
-            pm.register_pass<ngraph::runtime::b200::pass::QuantFusion>();
-        pm.register_pass<ngraph::pass::ConstantFolding>(); // also folds the scale arithmetic the fusion leaves behind
-        pm.run_passes(function);
-    }
-    if (!fenced)
-        remove_fences(function);
-}
-
-// For tests and tools: applies compile()'s graph passes to *function (a std::shared_ptr<ngraph::Function>*) in place,
-// without touching a device.  Returns 0, or -1 if a pass threw.
-extern "C" B200_BACKEND_API int b200_backend_run_graph_passes(void* function)
-{
-    try
-    {
-        run_graph_passes(*static_cast<std::shared_ptr<Function>*>(function));
-        return 0;
-    }
-    catch (const std::exception&)
-    {
-        return -1;
-    }
-}
-
 B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
                                const std::shared_ptr<Function>& func,
                                bool enable_performance_data)
@@ -798,8 +707,6 @@ void B200Executable::compile_node(const std::shared_ptr<Node>& node)
 // global memory only after the previous kernel has completed).
 void B200Executable::plan_arena()
 {
-    if (getenv("B200_NO_ARENA_REUSE"))
-        return;
     struct Live { size_t offset, bytes, last; };
     std::vector<Live> live;
     size_t peak = 0;
@@ -826,9 +733,6 @@ void B200Executable::plan_arena()
         live.push_back(Live{at, bytes, m_last[i]});
         peak = std::max(peak, at + bytes);
     }
-    if (getenv("B200_DEBUG_ARENA"))
-        fprintf(stderr, "B200 backend: arena %.1f MB (%.1f MB without reuse), %zu steps\n", peak / 1e6, m_arena_bytes / 1e6,
-                m_steps.size());
     m_arena_bytes = peak;
 }
 
@@ -1936,6 +1840,15 @@ void B200Executable::compile_max_pool(const std::shared_ptr<Node>& node)
     int64_t sh = op->get_window_movement_strides()[0], sw = op->get_window_movement_strides()[1];
     int64_t pb0 = op->get_padding_below()[0], pb1 = op->get_padding_below()[1];
     int64_t pa0 = op->get_padding_above()[0], pa1 = op->get_padding_above()[1];
+    // The kernel derives the output extent from the padded input with the floor formula.  In ceil mode the node's output
+    // may have one more row / column whose window hangs over the padded input; taps outside the image are skipped either
+    // way (reference::max_pool only visits source coordinates that exist), so padding above is widened until the floor
+    // formula gives the node's own output shape.
+    const int64_t need0 = (int64_t(os[2]) - 1) * sh + wh - H - pb0, need1 = (int64_t(os[3]) - 1) * sw + ww - W - pb1;
+    if (need0 > pa0) pa0 = need0;
+    if (need1 > pa1) pa1 = need1;
+    if ((H + pb0 + pa0 - wh) / sh + 1 != int64_t(os[2]) || (W + pb1 + pa1 - ww) / sw + 1 != int64_t(os[3]))
+        unsupported(*node, "an output shape the pooling geometry does not produce");
     emit(node, "maxpool", [=](const Ptrs& p, cudaStream_t st) {
         return is_signed ? b200_maxpool_nhwc_i8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st)
                          : b200_maxpool_nhwc_u8(p[x], p[y], N, H, W, C, wh, ww, sh, sw, pb0, pb1, pa0, pa1, st);

@@ -65,7 +65,9 @@ namespace
         return memcmp(ca->get_data_ptr(), cb->get_data_ptr(), bytes) == 0;
     }
 
-    // an f32 Constant whose every element is finite and > 0 (a quantisation scale that keeps the order of values)
+    // an f32 Constant whose every element is > 0 and far from both ends of the float range: a quantisation scale that keeps
+    // the order of values, and for which code * scale (|code| <= 255) neither overflows nor goes subnormal, so that
+    // (code * scale) / scale gives the code back and dequantised values compare like their codes
     bool is_positive_scale(const Output<Node>& v)
     {
         auto c = constant_of(v);
@@ -73,7 +75,7 @@ namespace
             return false;
         const float* p = static_cast<const float*>(c->get_data_ptr());
         for (size_t i = 0, n = shape_size(c->get_output_shape(0)); i < n; ++i)
-            if (!(p[i] > 0.0f) || p[i] > 3.0e38f)
+            if (!(p[i] >= 1.0e-30f) || p[i] > 1.0e30f)
                 return false;
         return true;
     }

@@ -28,6 +28,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 #include "common.cuh"
@@ -1489,6 +1490,41 @@ extern "C" int b200_device_status(int* status_out)
     return v == 0 ? B200_OK : B200_ERR_DEVICE_STATUS;
 }
 
+// ---- self-test of the bounded-wait path --------------------------------------------------------------------
+// One small CTA whose elected thread waits, through the same ptx::mbar_wait every role of the contraction kernel uses, on
+// an mbarrier that nothing ever arrives at.  The wait gives up after limit_ns, the kernel records code 9001 in the
+// device status word exactly like a role of the contraction kernel would, and returns normally: the context stays
+// usable, and the next b200_device_status() reports B200_ERR_DEVICE_STATUS once.
+namespace b200
+{
+    __global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(unsigned long long limit_ns)
+    {
+        __shared__ __align__(8) unsigned long long bar;
+        __shared__ int abort_flag;
+        if (threadIdx.x == 0)
+        {
+            abort_flag = 0;
+            ptx::mbar_init(ptx::smem_u32(&bar), 1);
+            ptx::fence_barrier_init();
+        }
+        __syncwarp();
+        int fail = 0;
+        if (threadIdx.x == 0 && !ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, 64, limit_ns))
+            fail = 9001;
+        if (fail)
+            atomicCAS(&g_contract_status, 0, fail);
+    }
+}
+
+extern "C" int b200_selftest_bounded_wait(int64_t limit_ns, void* stream)
+{
+    using namespace b200;
+    if (limit_ns <= 0 || limit_ns > 100000000) // at most 0.1 s: this is a test of the give-up path, not a delay
+        return B200_ERR_INVALID_ARGUMENT;
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long>(limit_ns));
+    return after_launch("bounded_wait_selftest_kernel");
+}
+
 static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, void* out, int64_t M, int64_t N, int64_t K,
                       const b200_epilogue* epilogue, void* stream)
 {
@@ -1916,28 +1952,38 @@ extern "C" int b200_qconv_stem_static(const void* in_nchw, int data_type, const 
     int rc = b200_stem_geometry(H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, &P, &Q, &Hc, &Wc, &Rc);
     if (rc != B200_OK)
         return rc;
-    if (N < 0)
+    // every argument is checked before the pack kernel is queued: a refused call must not touch the shared array
+    if (N < 0 || K <= 0 || C <= 0 || C > 4 || (data_type != B200_U8 && data_type != B200_I8))
         return B200_ERR_INVALID_ARGUMENT;
+    rc = check_epilogue(epilogue, K);
+    if (rc != B200_OK)
+        return rc;
     // sizes the fixed array cannot hold are refused before anything is launched
     const int64_t room = int64_t(STEM_SCRATCH_BYTES - STEM_CELLS_SLACK) / 16;
     if (Hc * Wc > room || N > room / (Hc * Wc))
         return B200_ERR_TOO_LARGE;
+    if (N * P * Q > 0x7FFFFFFF || Rc > MAX_TAPS)
+        return B200_ERR_TOO_LARGE;
+    if (N == 0)
+        return B200_OK;
+    if (!in_nchw || !packed_filters || !out || (reinterpret_cast<uintptr_t>(packed_filters) & 15))
+        return B200_ERR_INVALID_ARGUMENT;
     // one symbol lookup per device, at the first call on that device (it may load the module: do it before any
     // stream capture begins)
-    static void* scratch_of_device[64] = {nullptr};
+    static std::atomic<void*> scratch_of_device[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess)
         return cuda_status(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64)
         return B200_ERR_UNSUPPORTED;
-    void* scratch = scratch_of_device[dev];
+    void* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
     if (!scratch)
     {
         e = cudaGetSymbolAddress(&scratch, g_stem_scratch);
         if (e != cudaSuccess || !scratch)
             return cuda_status(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(stem scratch)");
-        scratch_of_device[dev] = scratch;
+        scratch_of_device[dev].store(scratch, std::memory_order_release);
     }
     rc = b200_stem_pack_input(in_nchw, scratch, N, C, H, W, R, S, pad_h, pad_w, pad_h_above, pad_w_above, stream);
     if (rc != B200_OK)

@@ -18,6 +18,7 @@
 #include "ngraph/op/experimental/quantized_dot_bias.hpp"
 #include "ngraph/runtime/backend.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
+#include "../backend/graph_passes.hpp"
 
 using namespace ngraph;
 
@@ -221,6 +222,31 @@ NGC_API void* ngc_avg_pool(void* x, const int64_t* win, const int64_t* stride)
     }, nullptr);
 }
 
+// pooling with every attribute: padding below / above, ceil mode, and (AvgPool) whether padding counts in the divisor
+NGC_API void* ngc_max_pool_ex(void* x, const int64_t* win, const int64_t* stride, const int64_t* below, const int64_t* above,
+                              int ceil_mode)
+{
+    return guarded([&]() -> void* {
+        return box(std::make_shared<op::v0::MaxPool>(val(x), Shape{size_t(win[0]), size_t(win[1])},
+                                                     Strides{size_t(stride[0]), size_t(stride[1])},
+                                                     Shape{size_t(below[0]), size_t(below[1])},
+                                                     Shape{size_t(above[0]), size_t(above[1])}, op::PadType::EXPLICIT,
+                                                     ceil_mode != 0));
+    }, nullptr);
+}
+
+NGC_API void* ngc_avg_pool_ex(void* x, const int64_t* win, const int64_t* stride, const int64_t* below, const int64_t* above,
+                              int include_padding, int ceil_mode)
+{
+    return guarded([&]() -> void* {
+        return box(std::make_shared<op::v0::AvgPool>(val(x), Shape{size_t(win[0]), size_t(win[1])},
+                                                     Strides{size_t(stride[0]), size_t(stride[1])},
+                                                     Shape{size_t(below[0]), size_t(below[1])},
+                                                     Shape{size_t(above[0]), size_t(above[1])}, include_padding != 0,
+                                                     op::PadType::EXPLICIT, ceil_mode != 0));
+    }, nullptr);
+}
+
 NGC_API void* ngc_concat(void** values, int n, int64_t axis)
 {
     return guarded([&]() -> void* {
@@ -347,18 +373,20 @@ NGC_API void* ngc_function(void** results, int n_results, void** params, int n_p
         return new std::shared_ptr<Function>(std::make_shared<Function>(rs, ps));
     }, nullptr);
 }
-// A copy of the Function after the graph passes a loaded plugin runs in compile(): `symbol` names the plugin's
-// exported pass runner (int f(std::shared_ptr<Function>*)), found among the libraries ngc_load_backend opened.
-NGC_API void* ngc_function_after_plugin_passes(void* function, const char* symbol)
+// A copy of the Function after the graph passes the B200 plugin runs in compile() (ngraph_b200/backend/graph_passes.cpp is
+// compiled into this library as well: the plugin itself exports nothing but its registration symbol).
+NGC_API void* ngc_function_after_b200_passes(void* function, int decompose_all)
 {
     return guarded([&]() -> void* {
-        auto run = reinterpret_cast<int (*)(void*)>(dlsym(RTLD_DEFAULT, symbol));
-        if (!run) throw std::runtime_error(std::string("symbol not found: ") + symbol);
         auto copy = new std::shared_ptr<Function>(clone_function(**static_cast<std::shared_ptr<Function>*>(function)));
-        if (run(copy) != 0)
+        try
+        {
+            runtime::b200::run_graph_passes(*copy, decompose_all != 0);
+        }
+        catch (...)
         {
             delete copy;
-            throw std::runtime_error("the plugin's graph passes failed");
+            throw;
         }
         return copy;
     }, nullptr);

@@ -86,6 +86,7 @@ def _load():
         "b200_stem_pack_input": (ci, [vp, vp] + [i64] * 10 + [vp]),
         "b200_stem_pack_input_f32": (ci, [vp, vp, vp, ci, ci, vp] + [i64] * 10 + [vp]),
         "b200_qconv_stem": (ci, [vp, ci, vp, vp] + [i64] * 10 + [ctypes.POINTER(Epilogue), vp]),
+        "b200_selftest_bounded_wait": (ci, [i64, vp]),
         "b200_qconv_stem_static_capacity": (i64, []),
         "b200_qconv_stem_static": (ci, [vp, ci, vp, vp] + [i64] * 11 + [ctypes.POINTER(Epilogue), vp]),
     }

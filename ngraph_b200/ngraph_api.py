@@ -47,6 +47,7 @@ def capi():
             "ngc_quantized_conv_relu": (vp, [vp, vp, p64, vp]),
             "ngc_convolution": (vp, [vp, vp, p64]),
             "ngc_max_pool": (vp, [vp, p64, p64, p64, p64]), "ngc_avg_pool": (vp, [vp, p64, p64]),
+            "ngc_max_pool_ex": (vp, [vp, p64, p64, p64, p64, ci]), "ngc_avg_pool_ex": (vp, [vp, p64, p64, p64, p64, ci, ci]),
             "ngc_convert": (vp, [vp, ci]), "ngc_reshape": (vp, [vp, p64, ci, p64, ci]), "ngc_relu": (vp, [vp]),
             "ngc_add": (vp, [vp, vp]), "ngc_multiply": (vp, [vp, vp]), "ngc_dot": (vp, [vp, vp, i64]),
             "ngc_broadcast": (vp, [vp, p64, ci, p64, ci]),
@@ -60,7 +61,7 @@ def capi():
             "ngc_layer_norm": (vp, [vp, vp, vp, i64, ctypes.c_double]), "ngc_gelu": (vp, [vp]),
             "ngc_batch_mat_mul": (vp, [vp, vp]),
             "ngc_quantized_concat": (vp, [pvp, pvp, pvp, ci, i64]),
-            "ngc_function_after_plugin_passes": (vp, [vp, ctypes.c_char_p]),
+            "ngc_function_after_b200_passes": (vp, [vp, ci]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
             "ngc_tensor_create": (vp, [vp, ci, p64, ci]), "ngc_tensor_wrap": (vp, [vp, ci, p64, ci, vp]),
             "ngc_tensor_free": (None, [vp]),
@@ -206,13 +207,15 @@ def convolution(data, filt, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pa
     return Value(capi().ngc_convolution(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above)), "Convolution")
 
 
-def max_pool(x, window, stride, pad_below=(0, 0), pad_above=None):
+def max_pool(x, window, stride, pad_below=(0, 0), pad_above=None, ceil_mode=False):
     pad_above = pad_below if pad_above is None else pad_above
-    return Value(capi().ngc_max_pool(x.h, _i64(window), _i64(stride), _i64(pad_below), _i64(pad_above)), "MaxPool")
+    return Value(capi().ngc_max_pool_ex(x.h, _i64(window), _i64(stride), _i64(pad_below), _i64(pad_above), int(ceil_mode)), "MaxPool")
 
 
-def avg_pool(x, window, stride=(1, 1)):
-    return Value(capi().ngc_avg_pool(x.h, _i64(window), _i64(stride)), "AvgPool")
+def avg_pool(x, window, stride=(1, 1), pad_below=(0, 0), pad_above=None, include_padding=False, ceil_mode=False):
+    pad_above = pad_below if pad_above is None else pad_above
+    return Value(capi().ngc_avg_pool_ex(x.h, _i64(window), _i64(stride), _i64(pad_below), _i64(pad_above), int(include_padding),
+                                        int(ceil_mode)), "AvgPool")
 
 
 def concat(values, axis):
@@ -314,10 +317,12 @@ def bert_encoder(layers, hidden, heads, ffn, seq, batch, vocab, seed=1, decompos
     return BuiltFunction(h, [_Spec(np.int32, (m,)), _Spec(np.int32, (m,))], [_Spec(np.float32, (m, hidden))], "bert_encoder")
 
 
-def after_b200_passes(function):
-    """a copy of `function` after the graph passes the B200 plugin runs in compile() (quantisation fusion included);
-    needs load_b200() but no device"""
-    h = capi().ngc_function_after_plugin_passes(function.h, b"b200_backend_run_graph_passes")
+def after_b200_passes(function, decompose_all=False):
+    """a copy of `function` after the graph passes the B200 plugin runs in compile() (quantisation fusion included); needs no
+    device.  decompose_all=True also decomposes the fused ops the device would run as one kernel (LayerNorm, Gelu)."""
+    h = capi().ngc_function_after_b200_passes(function.h, int(decompose_all))
+    if not h:
+        _err("after_b200_passes")
     return BuiltFunction(h, list(function.params), list(function.results), "after_b200_passes")
 
 

@@ -59,6 +59,47 @@ def test_encoder_matches_interpreter(dims):
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
 
 
+def _golden_case(name):
+    """(dims, ids, segments, INTERPRETER output) of one case of tests/golden/model_outputs.npz; make_model_golden.py holds the
+    recipe (one encoder layer at BERT-base width: minutes of INTERPRETER time, hence computed once and committed).  With
+    B200_LIVE_ORACLE set the INTERPRETER runs again instead."""
+    import importlib.util
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_model_golden", os.path.join(here, "golden", "make_model_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    c = gen.BERT_CASES[name]
+    dims = dict(gen.BERT, seq=c["seq"], batch=c["batch"])
+    ids, seg = gen.bert_inputs(c["seq"], c["batch"], gen.BERT["vocab"], c["input_seed"])
+    if os.environ.get("B200_LIVE_ORACLE"):
+        from ngraph_b200 import ngraph_api as ng
+        want = interpreter.backend().compile(ng.bert_encoder(seed=c["model_seed"], decomposed=True, **dims)).run(ids, seg)[0]
+    else:
+        want = np.load(os.path.join(here, "golden", "model_outputs.npz"))[name]
+    return dims, c["model_seed"], ids, seg, want
+
+
+@pytest.mark.gpu
+@needs_reference
+@pytest.mark.parametrize("case", ["bert768_seq384", "bert768_seq128_b2"])
+def test_bert_base_width_layer_matches_interpreter(case):
+    """One encoder layer at BERT-base width (hidden 768, 12 heads, FFN 3072) on a 384-token sequence, and on two 128-token
+    sequences: every QuantizedDotBias at its real K and N, softmax rows of 384, LayerNorm rows of 768, with the dynamic
+    activation scales taken over tensors of the real size.  Bound: 1e-5 relative to the output's largest magnitude per
+    element (LayerNorm output, values of order 1); the measured error is printed."""
+    from ngraph_b200 import ngraph_api as ng
+    ng.load_b200()
+    dims, model_seed, ids, seg, want = _golden_case(case)
+    got = ng.Backend("B200").compile(ng.bert_encoder(seed=model_seed, **dims)).run(ids, seg)[0]
+    assert got.shape == want.shape == (dims["batch"] * dims["seq"], dims["hidden"])
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    rel = err / np.maximum(np.abs(want.astype(np.float64)), 1.0)
+    print("%s: max abs err %.3g, max rel err %.3g, %d of %d elements differ in bits"
+          % (case, err.max(), rel.max(), int((got.view(np.uint32) != want.view(np.uint32)).sum()), got.size))
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
 @pytest.mark.gpu
 @needs_reference
 def test_bert_base_width_runs_and_repeats():
@@ -100,21 +141,11 @@ def test_full_width_encoder_commutes_with_a_permutation_of_the_batch():
 def test_plugin_keeps_layer_norm_and_gelu_whole_and_constants_small():
     """compile()'s graph passes, without a device: LayerNorm and Gelu stay single ops (one kernel each on the device), and
     the bias rows / scalar factors that are broadcast to [tokens, features] are NOT folded into constants of that size."""
-    import os
     from ngraph_b200 import ngraph_api as ng
-    ng.load_b200()
     dims = dict(layers=1, hidden=768, heads=12, ffn=3072, seq=384, batch=4, vocab=1000)  # 1536 tokens: above the folding fence
     fn = ng.bert_encoder(seed=3, **dims)
     ops = collections.Counter(ng.function_op_names(ng.after_b200_passes(fn), lowered=False))
     assert ops["LayerNorm"] == 3 and ops["Gelu"] == 1 and ops["Sum"] == 0 and ops["Erf"] == 0
     assert ops["Broadcast"] >= 7 and ops["StopGradient"] == 0   # bias rows and the attention factor stay Broadcast nodes
-    old = os.environ.get("B200_DECOMPOSE_ALL")
-    os.environ["B200_DECOMPOSE_ALL"] = "1"
-    try:
-        plain = collections.Counter(ng.function_op_names(ng.after_b200_passes(fn), lowered=False))
-    finally:
-        if old is None:
-            del os.environ["B200_DECOMPOSE_ALL"]
-        else:
-            os.environ["B200_DECOMPOSE_ALL"] = old
+    plain = collections.Counter(ng.function_op_names(ng.after_b200_passes(fn, decompose_all=True), lowered=False))
     assert plain["LayerNorm"] == 0 and plain["Gelu"] == 0 and plain["Sum"] == 9 and plain["Erf"] == 1

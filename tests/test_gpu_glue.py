@@ -138,6 +138,14 @@ def test_softmax_rows_equals_the_five_steps(L, rows, n):
     np.testing.assert_array_equal(np.isnan(w), np.isnan(g))
     np.testing.assert_array_equal(bits(np.nan_to_num(g)), bits(np.nan_to_num(w)))
     assert abs(float(g[1:].sum()) - (rows - 1)) < 1e-3 * rows
+    # and against the CPU restatement of reference::softmax (oracle/glue.py, pinned against INTERPRETER): exp is the one
+    # step whose last bit may differ between the device's routine and the host's, so a row may carry a one-ulp difference
+    # into its sum: held to two units in the last place, and to identity on all but a small share of the elements
+    from oracle import glue
+    with np.errstate(all="ignore"):
+        o = glue.softmax(x[1:])
+    np.testing.assert_allclose(g[1:], o, rtol=2.4e-7, atol=0)
+    assert (bits(g[1:]) != bits(o)).mean() < 0.02
 
 
 @pytest.mark.parametrize("rows,n", [(100, 768), (33, 65), (5, 1535), (64, 1)])
@@ -158,6 +166,8 @@ def test_layer_norm_rows_follows_the_decomposition(L, rows, n):
     L.check(L.LIB.b200_layer_norm_rows_f32(xd.data_ptr(), gd.data_ptr(), bd.data_ptr(), out.data_ptr(), rows, n, ctypes.c_float(1e-5),
                                            stream()), "layer_norm")
     np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(want))
+    from oracle import glue  # the CPU restatement pinned against INTERPRETER (tests/test_oracle_glue.py): bit for bit
+    np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(glue.layer_norm(x, gamma, beta, 1e-5)))
 
 
 def test_gelu_equals_its_decomposition_on_the_device(L):
@@ -177,6 +187,13 @@ def test_gelu_equals_its_decomposition_on_the_device(L):
     w, g = want.cpu().numpy(), got.cpu().numpy()
     np.testing.assert_array_equal(np.isnan(w), np.isnan(g))
     np.testing.assert_array_equal(bits(np.nan_to_num(g)), bits(np.nan_to_num(w)))
+    # against the CPU restatement of the reference's Gelu (oracle/glue.py, pinned against INTERPRETER): erf is computed in
+    # double and rounded on both sides, so the results agree except where the two double routines round differently
+    from oracle import glue
+    fin = np.isfinite(x)
+    o = glue.gelu(x[fin])
+    np.testing.assert_allclose(g[fin], o, rtol=2.4e-7, atol=1e-9)
+    assert (bits(g[fin]) != bits(o)).mean() < 0.01
 
 
 def test_row_kernels_with_the_producer_op_folded_in(L):

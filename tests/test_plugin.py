@@ -28,6 +28,20 @@ def test_plugin_exports_registration_symbol():
     assert hasattr(lib, "ngraph_register_b200_backend")
 
 
+def test_plugin_exports_nothing_but_the_registration_symbol():
+    """BackendManager finds a backend by dlsym of ngraph_register_<name>_backend (backend_manager.cpp:105-113): that is the
+    plugin's whole C ABI.  Its dynamic symbol table holds no other function or object of its own (weak template / inline
+    instantiations the C++ runtime may merge across libraries do not count)."""
+    import shutil
+    import subprocess
+    path = os.path.join(ROOT, "ngraph_b200", "libb200_backend.so")
+    if not os.path.exists(path) or not shutil.which("nm"):
+        pytest.skip("plugin not built, or no nm")
+    rows = subprocess.check_output(["nm", "-D", "--defined-only", path], text=True).split("\n")
+    strong = [r.split() for r in rows if r.strip() and r.split()[-2] in ("T", "D", "B", "R")]
+    assert [r[-1] for r in strong] == ["ngraph_register_b200_backend"], strong
+
+
 @needs_ngraph
 def test_backend_registers_and_fails_loudly_without_a_device():
     import torch
@@ -369,6 +383,24 @@ def test_small_network_with_pooling_head(backends):
     got, exp = run_both(backends, build(True), build(False), [x])
     same_bits(got[1], exp[1], "feature map")
     same_bits(got[0], exp[0], "logits")
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8])
+@pytest.mark.parametrize("hw,window,stride,pad,ceil_mode", [((14, 12), (3, 3), (2, 2), (0, 0), True), ((14, 12), (3, 3), (2, 2), (1, 1), True),
+                                                            ((15, 9), (2, 2), (2, 2), (0, 0), True), ((12, 12), (3, 3), (2, 2), (1, 1), False),
+                                                            ((7, 10), (3, 2), (3, 2), (0, 1), True)])
+def test_max_pool_with_ceil_mode_and_odd_sizes(backends, dtype, hw, window, stride, pad, ceil_mode):
+    """u8 / i8 MaxPool whose last window hangs over the (padded) input when the output extent is rounded up: the device writes
+    the node's own output shape and skips the taps that do not exist, like reference::max_pool (max_pool.hpp:124-236)."""
+    rng = np.random.default_rng(31)
+    x = rng.integers(np.iinfo(dtype).min, np.iinfo(dtype).max + 1, size=(2, 32) + hw).astype(dtype)
+    p = ng.parameter(dtype, x.shape)
+    fn = ng.Function([ng.max_pool(p, window, stride, pad, pad, ceil_mode=ceil_mode)], [p])
+    got, exp = run_both(backends, fn, fn, [x])
+    assert got[0].shape == exp[0].shape
+    np.testing.assert_array_equal(got[0], exp[0])
 
 
 @pytest.mark.gpu

@@ -155,6 +155,8 @@ def test_max_pool_moves_above_dequantize_without_changing_a_bit(plugin, dtype, z
     np.testing.assert_array_equal(run_interpreter(after, [x]).view(np.uint32), run_interpreter(before, [x]).view(np.uint32))
     # a negative scale reverses the order of values: left alone
     assert ops(ng.after_b200_passes(max_pool_graph(dtype, -0.037, zp))) == ["Dequantize", "MaxPool", "Result"]
+    # a scale so large that code * scale overflows: the dequantised values no longer compare like the codes
+    assert ops(ng.after_b200_passes(max_pool_graph(dtype, 3.0e37, zp))) == ["Dequantize", "MaxPool", "Result"]
 
 
 def test_concat_moves_above_dequantize_without_changing_a_bit(plugin):
@@ -176,6 +178,9 @@ def test_dequantize_quantize_pair_is_dropped_only_when_exact(plugin):
     np.testing.assert_array_equal(run_interpreter(after, [x]).view(np.uint32), run_interpreter(before, [x]).view(np.uint32))
     assert "Quantize" in names(ng.after_b200_passes(dq_q_graph(0.0371, 0.05)))          # another scale
     assert "Quantize" in names(ng.after_b200_passes(dq_q_graph(0.0371, 0.0371, mode=8)))  # ROUND_DOWN is not a nearest mode
+    # 255 * scale overflows to +inf, the original Quantize then saturates: not an identity any more
+    assert "Quantize" in names(ng.after_b200_passes(dq_q_graph(3.0e37, 3.0e37)))
+    assert "Quantize" in names(ng.after_b200_passes(dq_q_graph(1.0e-38, 1.0e-38)))      # products go subnormal
 
 
 def test_a_graph_of_fused_ops_is_left_alone(plugin):

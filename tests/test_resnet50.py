@@ -1,8 +1,11 @@
 """int8 ResNet-50 v1.5 (BASELINE's headline graph) through the B200 plugin against nGraph's INTERPRETER.
 
-INTERPRETER needs ~38 s per 224x224 image, so parity runs on reduced spatial sizes (the network is
-fully convolutional up to the pooling head; every layer, channel count, stride, residual join and the
-head are exercised) and checks batch independence at the full 224x224 size on the device."""
+INTERPRETER needs ~40 s per 224x224 image: parity runs on reduced spatial sizes (the network is fully
+convolutional up to the pooling head; every layer, channel count, stride, residual join and the head are
+exercised), on ONE image at the full 224x224 size (all 1000 logits, bit for bit, alone and inside a batch
+of two), and batch independence is checked at 224x224 on the device."""
+import os
+
 import numpy as np
 import pytest
 
@@ -81,6 +84,34 @@ def test_resnet50_parity_with_interpreter(model):
         assert got.shape == exp.shape == (batch, 1000)
         np.testing.assert_array_equal(got.view(np.uint32), exp.view(np.uint32), err_msg=str(hw))
         assert np.abs(exp).max() > 0
+
+
+def _full_size_reference(model):
+    """INTERPRETER's logits for image 0 of synthetic_images(2, 11): the committed fixture (tests/golden/make_model_golden.py wrote
+    it with the INTERPRETER built from the reference sources, a minute of CPU), or a live INTERPRETER run of the decomposed graph
+    when B200_LIVE_ORACLE is set."""
+    x = synthetic_images(2, 11, 224)
+    if os.environ.get("B200_LIVE_ORACLE"):
+        plain, _ = model.build(ng, 1, fused=False, decomposed=interpreter)
+        return x, interpreter.backend().compile(plain).run(x[:1])[0]
+    return x, np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "model_outputs.npz"))["resnet50_224_logits"]
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_resnet50_full_size_image_matches_interpreter(model):
+    """One 224x224 image through every layer at its real geometry (112/56/28/14/7-wide maps, ragged last tiles,
+    halo tiles at the image border): all 1000 logits equal INTERPRETER's bit for bit, whether the image is run
+    alone or as either member of a batch of two."""
+    ng.load_b200()
+    b200 = ng.Backend("B200")
+    x, exp = _full_size_reference(model)
+    assert exp.shape == (1, 1000) and np.abs(exp).max() > 0 and len(np.unique(exp)) > 20
+    alone = b200.compile(model.build(ng, 1, fused=True)[0]).run(x[:1])[0]
+    np.testing.assert_array_equal(alone.view(np.uint32), exp.view(np.uint32))
+    pair = b200.compile(model.build(ng, 2, fused=True)[0])
+    np.testing.assert_array_equal(pair.run(x)[0][:1].view(np.uint32), exp.view(np.uint32))
+    np.testing.assert_array_equal(pair.run(x[::-1].copy())[0][1:].view(np.uint32), exp.view(np.uint32))
 
 
 @pytest.mark.gpu
