@@ -305,6 +305,40 @@ B200_API int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const floa
                                            void* stream);
 
 /*
+ * AvgPool with a window: replaces runtime::reference::avg_pool<T>
+ * (src/ngraph/runtime/reference/avg_pool.hpp:160-236) as INTERPRETER dispatches it for op::v0::AvgPool
+ * (src/ngraph/runtime/interpreter/int_executable.hpp, case AvgPool).  The window is walked in (h, w) order over the padded
+ * image; image positions add their value, padding positions add 0 and count only with include_padding; the result is
+ * sum / count with the sum taken sequentially in the element type.  P x Q is the op's output extent (in ceil mode it may
+ * exceed the floor formula; positions beyond the padded image are not counted - the reference refuses such windows).
+ * A geometry in which some window would count nothing returns B200_ERR_INVALID_ARGUMENT (the reference throws).
+ *
+ *   b200_avgpool_f32_nchw    f32 [N,C,H,W] -> f32 [N,C,P,Q]
+ *   b200_avgpool_nhwc_bytes  the op applied to u8 / i8 directly, channels-last [N,H,W,C] -> [N,P,Q,C]: the reference keeps
+ *                            the running sum in the one-byte type (it wraps modulo 256) and stores
+ *                            nearbyint(float(sum) / count); reproduced literally
+ *   b200_avgpool_q_nhwc      Dequantize(scale_in, zp 0) -> AvgPool(f32) -> Quantize(scale_out, zp 0, RNE) in one pass over
+ *                            channels-last bytes (u8 or i8 on either side): the three ops' float operations in their order.
+ *                            This is the graph CPUQuantFusion::construct_qavg_pool starts from
+ *                            (src/ngraph/runtime/cpu/pass/cpu_fusion.cpp:2160-2200); scale_in / scale_out: one float each,
+ *                            device memory.
+ */
+typedef struct b200_pool_params
+{
+    int64_t N, C, H, W;            /* input */
+    int64_t P, Q;                  /* output extent */
+    int64_t win_h, win_w, stride_h, stride_w;
+    int64_t pad_h, pad_w;          /* padding below */
+    int64_t pad_h_above, pad_w_above;
+    int32_t include_padding;       /* include_padding_in_avg_computation */
+} b200_pool_params;
+
+B200_API int b200_avgpool_f32_nchw(const float* in, float* out, const b200_pool_params* geometry, void* stream);
+B200_API int b200_avgpool_nhwc_bytes(const void* in, void* out, int type, const b200_pool_params* geometry, void* stream);
+B200_API int b200_avgpool_q_nhwc(const void* in, int in_type, void* out, int out_type, const float* scale_in,
+                                 const float* scale_out, const b200_pool_params* geometry, void* stream);
+
+/*
  * Patch matrix for a convolution whose input has at most 4 channels (a network stem such as
  * 7x7 stride 2 on RGB): the tensor cores want 16-byte channel runs, which 3 channels cannot give.
  *   in  : channels-last u8 with exactly 4 channels per pixel [N,H,W,4] (see b200_nchw_to_nhwc_u8, c_pad 4)

@@ -21,6 +21,7 @@
 #include <sstream>
 
 #include "b200_kernels.h"
+#include "function_io.hpp"
 #include "graph_passes.hpp"
 #include "quant_fusion.hpp"
 #include "ngraph/op/concat.hpp"
@@ -71,6 +72,7 @@
 #include "ngraph/pass/manager.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
 #include "ngraph/util.hpp"
+#include "ngraph/cpio.hpp"
 
 using namespace ngraph;
 using namespace ngraph::runtime::b200;
@@ -78,6 +80,8 @@ using namespace ngraph::runtime::b200;
 // ------------------------------------------------------------------------------------ helpers
 namespace
 {
+    const char SAVE_INFO[] = "B200 Save File 1.0";
+
     void cuda_check(cudaError_t e, const char* what)
     {
         if (e != cudaSuccess)
@@ -163,28 +167,46 @@ namespace
     bool match_head(const Node* qn, AvgPoolHead& h)
     {
         auto q = as_type<const op::v0::Quantize>(qn);
-        if (!q || q->get_output_element_type(0) != element::u8 || !q->get_axes().empty() ||
+        const auto one_byte = [](const element::Type& t) { return t == element::u8 || t == element::i8; };
+        if (!q || !one_byte(q->get_output_element_type(0)) || !q->get_axes().empty() ||
             q->get_round_mode() != op::v0::Quantize::RoundMode::ROUND_NEAREST_TOWARD_EVEN ||
             !constant_zero(q->input_value(2)))
             return false;
         auto pool = as_type<const op::v0::AvgPool>(q->input_value(0).get_node());
         if (!pool || single_user_count(q->input_value(0)) != 1 || pool->get_output_element_type(0) != element::f32)
             return false;
-        const Shape& in = pool->get_input_shape(0);
-        if (in.size() != 4 || pool->get_window_shape() != Shape{in[2], in[3]})
+        if (pool->get_input_shape(0).size() != 4)
             return false;
-        for (size_t v : pool->get_padding_below())
-            if (v != 0) return false;
-        for (size_t v : pool->get_padding_above())
-            if (v != 0) return false;
         auto dq = as_type<const op::v0::Dequantize>(pool->input_value(0).get_node());
-        if (!dq || single_user_count(pool->input_value(0)) != 1 || dq->get_input_element_type(0) != element::u8 ||
+        if (!dq || single_user_count(pool->input_value(0)) != 1 || !one_byte(dq->get_input_element_type(0)) ||
             !dq->get_axes().empty() || !constant_zero(dq->input_value(2)))
             return false;
         h.dq = dq;
         h.pool = pool;
         h.q = q;
         return true;
+    }
+
+    // the op's attributes and shapes as the kernels take them
+    b200_pool_params pool_params_of(const op::v0::AvgPool& pool)
+    {
+        const Shape& in = pool.get_input_shape(0);
+        const Shape& out = pool.get_output_shape(0);
+        b200_pool_params g;
+        g.N = int64_t(in[0]); g.C = int64_t(in[1]); g.H = int64_t(in[2]); g.W = int64_t(in[3]);
+        g.P = int64_t(out[2]); g.Q = int64_t(out[3]);
+        g.win_h = int64_t(pool.get_window_shape()[0]); g.win_w = int64_t(pool.get_window_shape()[1]);
+        g.stride_h = int64_t(pool.get_window_movement_strides()[0]); g.stride_w = int64_t(pool.get_window_movement_strides()[1]);
+        g.pad_h = int64_t(pool.get_padding_below()[0]); g.pad_w = int64_t(pool.get_padding_below()[1]);
+        g.pad_h_above = int64_t(pool.get_padding_above()[0]); g.pad_w_above = int64_t(pool.get_padding_above()[1]);
+        g.include_padding = pool.get_include_padding_in_avg_computation() ? 1 : 0;
+        return g;
+    }
+
+    bool is_global_unpadded(const b200_pool_params& g)
+    {
+        return g.win_h == g.H && g.win_w == g.W && g.P == 1 && g.Q == 1 && g.pad_h == 0 && g.pad_w == 0 && g.pad_h_above == 0 &&
+               g.pad_w_above == 0;
     }
 }
 
@@ -467,15 +489,43 @@ int B200Executable::new_slot(Slot::Kind kind, size_t bytes, size_t index)
     return id;
 }
 
-int B200Executable::upload_constant(const void* data, size_t bytes)
+// `key` names the constant inside the image: what it is and the position, in the Function's node order, of the Constant(s)
+// it was made from.  A saved executable's image is looked up by the same keys, so the loading side does not depend on
+// the order in which the lowering asks for its constants.
+std::string B200Executable::constant_key(const char* purpose, std::initializer_list<const Node*> sources) const
+{
+    std::string key = purpose;
+    for (const Node* n : sources)
+    {
+        auto it = m_node_index.find(n);
+        key += ":" + (it == m_node_index.end() ? std::string("?") : std::to_string(it->second));
+    }
+    return key;
+}
+
+bool B200Executable::have_saved_constant(const std::string& key) const { return m_use_preloaded && m_constant_index.count(key) != 0; }
+
+int B200Executable::upload_constant(const std::string& key, const void* data, size_t bytes)
 {
     Slot s;
     s.kind = Slot::CONSTANT;
     s.bytes = bytes;
-    s.offset = align_up(m_constant_host.size(), 256);
-    m_constant_host.resize(s.offset + align_up(bytes ? bytes : 16, 256), 0);
-    if (bytes)
-        memcpy(m_constant_host.data() + s.offset, data, bytes);
+    if (m_use_preloaded)
+    {
+        // the image of a saved executable already holds this constant
+        auto it = m_constant_index.find(key);
+        if (it == m_constant_index.end() || it->second.second != bytes || it->second.first + bytes > m_preloaded.size())
+            throw std::runtime_error("B200 backend: the saved constant image does not belong to the saved model (" + key + ")");
+        s.offset = it->second.first;
+    }
+    else
+    {
+        s.offset = align_up(m_constant_host.size(), 256);
+        m_constant_host.resize(s.offset + align_up(bytes ? bytes : 16, 256), 0);
+        if (bytes)
+            memcpy(m_constant_host.data() + s.offset, data, bytes);
+        m_constant_index.emplace(key, std::make_pair(s.offset, bytes)); // a repeated key keeps its first (identical) copy
+    }
     m_slots.push_back(s);
     m_birth.push_back(0); // lifetimes are kept per slot index; constants live forever
     m_last.push_back(size_t(-1));
@@ -555,6 +605,14 @@ int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad, bo
 {
     const Shape& fs = filters.get_shape();
     auto c = as_constant(filters);
+    const std::string key = c ? constant_key(("filter_image/" + std::to_string(c_pad)).c_str(), {c.get()}) : std::string();
+    if (c && have_saved_constant(key))
+    {
+        const int64_t kg = int64_t(fs[2] * fs[3] * c_pad), bk = b200_qconv_weight_block(int64_t(c_pad));
+        if (is_image)
+            *is_image = true;
+        return upload_constant(key, nullptr, size_t(b200_packed_weights_bytes(int64_t(fs[0]), kg, bk)));
+    }
     if (c)
     {
         const int8_t* src = static_cast<const int8_t*>(c->get_data_ptr());
@@ -571,7 +629,7 @@ int B200Executable::packed_filters(const Output<Node>& filters, size_t c_pad, bo
         kernel_check(b200_pack_weights_host(packed.data(), image.data(), int64_t(K), kg, bk), "b200_pack_weights_host");
         if (is_image)
             *is_image = true;
-        return upload_constant(image.data(), image.size());
+        return upload_constant(key, image.data(), image.size());
     }
     if (is_image)
         *is_image = false;
@@ -589,7 +647,7 @@ int B200Executable::scalar_product_scale(const Output<Node>& a, const Output<Nod
         volatile float s = *static_cast<const float*>(ca->get_data_ptr()) * *static_cast<const float*>(cb->get_data_ptr());
         volatile float r = s / *static_cast<const float*>(cc->get_data_ptr());
         float v = r;
-        return upload_constant(&v, sizeof(float));
+        return upload_constant(constant_key("requant_scale", {ca.get(), cb.get(), cc.get()}), &v, sizeof(float));
     }
     int sa = canonical_slot(a), sb = canonical_slot(b), sc = canonical_slot(c);
     int dst = new_slot(Slot::ARENA, sizeof(float));
@@ -619,14 +677,34 @@ bool B200Executable::avgpool_head_member(const Node* node)
 
 B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
                                const std::shared_ptr<Function>& func,
-                               bool enable_performance_data)
+                               bool enable_performance_data,
+                               std::vector<char>* saved_constants,
+                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index)
     : m_ctx(ctx)
     , m_perf(enable_performance_data)
 {
     m_ctx->make_current();
-    m_function = clone_function(*func); // never mutate the caller's graph
-    run_graph_passes(m_function);
+    if (saved_constants)
+    {
+        // Backend::load: `func` is the graph a previous compile() arrived at after its passes, and the constant image is the
+        // one that compile() built (filters reordered and packed, weights transposed, scales folded): neither is redone
+        m_function = func;
+        m_preloaded.swap(*saved_constants);
+        m_use_preloaded = true;
+        if (saved_index)
+            m_constant_index = *saved_index;
+    }
+    else
+    {
+        m_function = clone_function(*func); // never mutate the caller's graph
+        run_graph_passes(m_function);
+    }
 
+    {
+        size_t position = 0;
+        for (auto& node : m_function->get_ordered_ops())
+            m_node_index[node.get()] = position++;
+    }
     size_t pi = 0;
     for (auto& param : m_function->get_parameters())
     {
@@ -661,6 +739,9 @@ B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
 
     if (m_arena_bytes)
         cuda_check(cudaMalloc(&m_arena, m_arena_bytes), "cudaMalloc(arena)");
+    if (m_use_preloaded)
+        m_constant_host.swap(m_preloaded);
+    m_constant_bytes = m_constant_host.size();
     if (!m_constant_host.empty())
     {
         cuda_check(cudaMalloc(&m_constants, m_constant_host.size()), "cudaMalloc(constants)");
@@ -747,7 +828,7 @@ void B200Executable::lower_node(const std::shared_ptr<Node>& node)
         v.shape = c->get_output_shape(0);
         v.constant = c;
         if (dtype_of(v.et) >= 0) // other element types can only feed ConstantFolding, never a kernel
-            v.canonical = upload_constant(c->get_data_ptr(), shape_size(v.shape) * v.et.size());
+            v.canonical = upload_constant(constant_key("plain", {c.get()}), c->get_data_ptr(), shape_size(v.shape) * v.et.size());
         m_values[&node->output(0).get_tensor()] = v;
         return;
     }
@@ -774,7 +855,7 @@ void B200Executable::lower_node(const std::shared_ptr<Node>& node)
             value_of(node->output(0)).skipped = true;
             return;
         }
-        unsupported(*node, "only the Dequantize -> global AvgPool -> Quantize head runs on the device");
+        return compile_avg_pool(node);
     }
     if (auto rs = as_type_ptr<op::v0::Reshape>(node))
     {
@@ -1271,21 +1352,62 @@ bool B200Executable::try_compile_avgpool_head(const std::shared_ptr<Node>& node)
     if (!match_head(node.get(), h))
         return false;
     Output<Node> data = h.dq->input_value(0);
-    const Shape& in = data.get_shape();
-    if (in.size() != 4)
-        return false;
+    const b200_pool_params g = pool_params_of(*h.pool);
+    const int in_type = dtype_of(data.get_element_type()), out_type = dtype_of(h.q->get_output_element_type(0));
     int x = nhwc_slot(data);
     int s_in = canonical_slot(h.dq->input_value(1)), s_out = canonical_slot(h.q->input_value(1));
-    int y = new_slot(Slot::ARENA, in[0] * in[1]);
-    int64_t N = in[0], C = in[1], H = in[2], W = in[3];
-    emit(node, "global_avgpool_q", [=](const Ptrs& p, cudaStream_t st) {
-        return b200_global_avgpool_q_nhwc_u8(p[x], p[y], static_cast<const float*>(p[s_in]),
-                                             static_cast<const float*>(p[s_out]), N, H, W, C, st);
-    });
+    int y = new_slot(Slot::ARENA, shape_size(h.q->get_output_shape(0)));
+    if (is_global_unpadded(g) && in_type == B200_U8 && out_type == B200_U8)
+    {
+        int64_t N = g.N, C = g.C, H = g.H, W = g.W;
+        emit(node, "global_avgpool_q", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_global_avgpool_q_nhwc_u8(p[x], p[y], static_cast<const float*>(p[s_in]),
+                                                 static_cast<const float*>(p[s_out]), N, H, W, C, st);
+        });
+    }
+    else
+    {
+        emit(node, "avgpool_q", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_avgpool_q_nhwc(p[x], in_type, p[y], out_type, static_cast<const float*>(p[s_in]),
+                                       static_cast<const float*>(p[s_out]), &g, st);
+        });
+    }
     Value& o = value_of(node->output(0));
-    o.canonical = y; // [N,C,1,1]: channels-last and NCHW coincide
     o.nhwc = y;
+    if (g.P * g.Q == 1)
+        o.canonical = y; // [N,C,1,1]: channels-last and NCHW coincide
     return true;
+}
+
+// op::v0::AvgPool outside that pattern: f32 on NCHW, or the op applied to u8 / i8 directly (channels-last), both with the
+// arithmetic of runtime::reference::avg_pool.
+void B200Executable::compile_avg_pool(const std::shared_ptr<Node>& node)
+{
+    auto pool = as_type_ptr<op::v0::AvgPool>(node);
+    const element::Type& et = node->get_input_element_type(0);
+    if (node->get_input_shape(0).size() != 4)
+        unsupported(*node, "pooling over other than two spatial dimensions");
+    const b200_pool_params g = pool_params_of(*pool);
+    if (et == element::f32)
+    {
+        int x = canonical_slot(node->input_value(0));
+        int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)) * sizeof(float));
+        emit(node, "avgpool_f32", [=](const Ptrs& p, cudaStream_t st) {
+            return b200_avgpool_f32_nchw(static_cast<const float*>(p[x]), static_cast<float*>(p[y]), &g, st);
+        });
+        value_of(node->output(0)).canonical = y;
+        return;
+    }
+    if (et != element::u8 && et != element::i8)
+        unsupported(*node, "element type " + et.get_type_name());
+    const int type = dtype_of(et);
+    int x = nhwc_slot(node->input_value(0));
+    int y = new_slot(Slot::ARENA, shape_size(node->get_output_shape(0)));
+    emit(node, "avgpool_bytes", [=](const Ptrs& p, cudaStream_t st) { return b200_avgpool_nhwc_bytes(p[x], p[y], type, &g, st); });
+    Value& o = value_of(node->output(0));
+    o.nhwc = y;
+    if (g.P * g.Q == 1)
+        o.canonical = y;
 }
 
 void B200Executable::compile_dequantize(const std::shared_ptr<Node>& node)
@@ -1417,7 +1539,7 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
             kernel_check(b200_stem_pack_filter_host(static_cast<const int8_t*>(cf->get_data_ptr()), w.data(), c.K, int64_t(C), c.R,
                                              c.S, c.pad_h, c.pad_w),
                   "b200_stem_pack_filter_host");
-            int wslot = upload_constant(w.data(), w.size());
+            int wslot = upload_constant(constant_key("stem_filter", {cf.get()}), w.data(), w.size());
             int cells = new_slot(Slot::ARENA, size_t(b200_stem_cells_bytes(c.N, c.H, c.W, c.R, c.S, c.pad_h, c.pad_w, c.pad_h_above,
                                                                            c.pad_w_above)));
             int64_t Ci = C;
@@ -1473,7 +1595,7 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
                 for (size_t r = 0; r < R; ++r)
                     for (size_t s = 0; s < S; ++s)
                         w[(k * R + r) * 32 + s * 4 + ch] = src[((k * C + ch) * R + r) * S + s];
-        int wslot = upload_constant(w.data(), w.size());
+        int wslot = upload_constant(constant_key("c4_filter", {cf.get()}), w.data(), w.size());
         int xc = canonical_slot(node->input_value(0));
         int x4 = new_slot(Slot::ARENA, ds[0] * ds[2] * ds[3] * 4);
         int64_t M = int64_t(ds[0]) * P * Q, KK = int64_t(R) * 32;
@@ -1688,13 +1810,19 @@ void B200Executable::compile_dot_bias(const std::shared_ptr<Node>& node)
     // constant weights [N,K] go to the device in the packed image
     int w;
     bool w_image = false;
-    if (auto cw = as_constant(node->input_value(1)))
+    const std::string wkey = constant_key("weight_image", {node->input_value(1).get_node()});
+    if (as_constant(node->input_value(1)) && have_saved_constant(wkey))
+    {
+        w = upload_constant(wkey, nullptr, size_t(b200_packed_weights_bytes(int64_t(ws[0]), int64_t(ws[1]), 128)));
+        w_image = true;
+    }
+    else if (auto cw = as_constant(node->input_value(1)))
     {
         std::vector<int8_t> image(size_t(b200_packed_weights_bytes(int64_t(ws[0]), int64_t(ws[1]), 128)));
         kernel_check(b200_pack_weights_host(static_cast<const int8_t*>(cw->get_data_ptr()), image.data(), int64_t(ws[0]),
                                             int64_t(ws[1]), 128),
                      "b200_pack_weights_host");
-        w = upload_constant(image.data(), image.size());
+        w = upload_constant(wkey, image.data(), image.size());
         w_image = true;
     }
     else
@@ -1746,7 +1874,13 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
     // call otherwise
     int w;
     bool w_image = false;
-    if (auto cb = as_constant(node->input_value(1)))
+    const std::string wkey = constant_key("transposed_weight_image", {node->input_value(1).get_node()});
+    if (as_constant(node->input_value(1)) && have_saved_constant(wkey))
+    {
+        w = upload_constant(wkey, nullptr, size_t(b200_packed_weights_bytes(N, K, 128)));
+        w_image = true;
+    }
+    else if (auto cb = as_constant(node->input_value(1)))
     {
         const int8_t* src = static_cast<const int8_t*>(cb->get_data_ptr());
         std::vector<int8_t> t(size_t(N) * K);
@@ -1755,7 +1889,7 @@ void B200Executable::compile_core_dot(const std::shared_ptr<Node>& node)
                 t[n * K + k] = src[k * N + n];
         std::vector<int8_t> image(size_t(b200_packed_weights_bytes(N, K, 128)));
         kernel_check(b200_pack_weights_host(t.data(), image.data(), N, K, 128), "b200_pack_weights_host");
-        w = upload_constant(image.data(), image.size());
+        w = upload_constant(wkey, image.data(), image.size());
         w_image = true;
     }
     else
@@ -1917,6 +2051,97 @@ bool B200Executable::call(const std::vector<std::shared_ptr<runtime::Tensor>>& o
         if (auto bt = std::dynamic_pointer_cast<B200Tensor>(t))
             bt->mark_used(st);
     return true;
+}
+
+// Executable::save (src/ngraph/runtime/executable.hpp:76-78): a cpio archive like the INTERPRETER's
+// (int_executable.cpp:345-352), holding what compile() produced so that Backend::load does not redo it:
+//   save_info  format tag
+//   model      the Function after the plugin's graph passes, in the plugin's own binary form (function_io.hpp)
+//   constants  the device constant image: packed filter / weight images, folded scales, plain constants, at the offsets
+//              the lowering assigned
+//   meta       text: hashes of the two entries above, arena size and the lowered step list
+void B200Executable::save(std::ostream& out)
+{
+    std::lock_guard<std::mutex> lock(m_call_mutex);
+    m_ctx->make_current();
+    const std::string model = write_function(*m_function);
+    std::vector<char> constants(m_constant_bytes);
+    if (m_constant_bytes)
+    {
+        cuda_check(cudaStreamSynchronize(m_ctx->stream), "cudaStreamSynchronize");
+        cuda_check(cudaMemcpy(constants.data(), m_constants, m_constant_bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(constants -> host)");
+    }
+    std::ostringstream meta;
+    meta << "model_fnv1a " << fnv1a(model.data(), model.size()) << "\nconstants_fnv1a " << fnv1a(constants.data(), constants.size())
+         << "\narena_bytes " << m_arena_bytes << "\nsteps " << m_steps.size() << "\n";
+    for (const auto& st : m_steps)
+        meta << st.what << " " << st.node->get_name() << "\n";
+    const std::string meta_text = meta.str();
+    cpio::Writer writer(out);
+    writer.write("save_info", SAVE_INFO, uint32_t(strlen(SAVE_INFO)));
+    writer.write("model", model.data(), uint32_t(model.size()));
+    if (constants.size() >= (size_t(1) << 32) || model.size() >= (size_t(1) << 32))
+        throw std::runtime_error("B200 backend: executable too large for the cpio container (4 GiB per entry)");
+    writer.write("constants", constants.data(), uint32_t(constants.size()));
+    std::ostringstream index; // key, offset and size of every constant inside the image
+    for (const auto& e : m_constant_index)
+        index << e.first << " " << e.second.first << " " << e.second.second << "\n";
+    const std::string index_text = index.str();
+    writer.write("constants_index", index_text.data(), uint32_t(index_text.size()));
+    writer.write("meta", meta_text.data(), uint32_t(meta_text.size()));
+}
+
+// Backend::load (src/ngraph/runtime/backend.hpp:122-125; INTERPRETER: int_backend.cpp:81-110)
+std::shared_ptr<runtime::Executable> B200Backend::load(std::istream& in)
+{
+    cpio::Reader reader(in);
+    std::string info, model, meta, index_text;
+    std::vector<char> constants;
+    bool have_constants = false;
+    for (const cpio::FileInfo& f : reader.get_file_info())
+    {
+        if (f.get_name() == "save_info" || f.get_name() == "model" || f.get_name() == "meta" || f.get_name() == "constants_index")
+        {
+            std::vector<char> b = reader.read(f);
+            (f.get_name() == "save_info" ? info : f.get_name() == "model" ? model : f.get_name() == "meta" ? meta : index_text)
+                .assign(b.data(), b.size());
+        }
+        else if (f.get_name() == "constants")
+        {
+            constants = reader.read(f);
+            have_constants = true;
+        }
+    }
+    if (info != SAVE_INFO)
+        throw std::runtime_error("B200 backend: not an executable saved by this plugin version (save_info '" + info + "')");
+    if (model.empty() || !have_constants)
+        throw std::runtime_error("B200 backend: saved executable lacks its model or its constant image");
+    // the hashes in `meta` tie the two entries to each other
+    {
+        std::istringstream ms(meta);
+        std::string key;
+        uint64_t value = 0, want_model = 0, want_constants = 0;
+        while (ms >> key >> value)
+        {
+            if (key == "model_fnv1a") want_model = value;
+            else if (key == "constants_fnv1a") want_constants = value;
+            else if (key == "steps") break;
+        }
+        if (want_model != fnv1a(model.data(), model.size()) || want_constants != fnv1a(constants.data(), constants.size()))
+            throw std::runtime_error("B200 backend: saved executable is damaged (hash mismatch)");
+    }
+    std::map<std::string, std::pair<size_t, size_t>> index;
+    {
+        std::istringstream is(index_text);
+        std::string key;
+        size_t offset = 0, bytes = 0;
+        while (is >> key >> offset >> bytes)
+            index[key] = std::make_pair(offset, bytes);
+    }
+    // nodes are rebuilt in the saved order, which is the order the keys of the index count in
+    std::shared_ptr<Function> function = read_function(model);
+    std::lock_guard<std::mutex> lock(m_mutex);
+    return std::make_shared<B200Executable>(m_ctx, function, false, &constants, &index);
 }
 
 std::vector<runtime::PerformanceCounter> B200Executable::get_performance_data() const

@@ -85,6 +85,7 @@ namespace ngraph
                                                              bool enable_performance_data = false) override;
                 bool is_supported(const Node& node) const override;
                 void remove_compiled_function(std::shared_ptr<runtime::Executable> exec) override;
+                std::shared_ptr<runtime::Executable> load(std::istream& input_stream) override;
                 bool is_device_memory(void* ptr) override;
                 const std::shared_ptr<DeviceContext>& context() const { return m_ctx; }
             private:
@@ -97,13 +98,18 @@ namespace ngraph
             class B200Executable : public runtime::Executable
             {
             public:
+                /// saved_constants != nullptr (Backend::load): `func` is an already lowered graph and *saved_constants the
+                /// constant image compile() built for it; the image is taken over
                 B200Executable(const std::shared_ptr<DeviceContext>& ctx,
                                const std::shared_ptr<Function>& func,
-                               bool enable_performance_data);
+                               bool enable_performance_data,
+                               std::vector<char>* saved_constants = nullptr,
+                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index = nullptr);
                 ~B200Executable() override;
                 bool call(const std::vector<std::shared_ptr<runtime::Tensor>>& outputs,
                           const std::vector<std::shared_ptr<runtime::Tensor>>& inputs) override;
                 std::vector<PerformanceCounter> get_performance_data() const override;
+                void save(std::ostream& output_stream) override;
                 std::shared_ptr<runtime::Tensor> create_input_tensor(size_t input_index) override;
                 std::shared_ptr<runtime::Tensor> create_output_tensor(size_t output_index) override;
                 std::vector<std::shared_ptr<runtime::Tensor>> create_input_tensor(size_t input_index,
@@ -140,7 +146,9 @@ namespace ngraph
                 };
 
                 int new_slot(Slot::Kind kind, size_t bytes, size_t index = 0);
-                int upload_constant(const void* data, size_t bytes);
+                int upload_constant(const std::string& key, const void* data, size_t bytes);
+                std::string constant_key(const char* purpose, std::initializer_list<const Node*> sources) const;
+                bool have_saved_constant(const std::string& key) const;
                 Value& value_of(const Output<Node>& out);
                 int canonical_slot(const Output<Node>& out);
                 int nhwc_slot(const Output<Node>& out);
@@ -156,6 +164,7 @@ namespace ngraph
                 void compile_dot_bias(const std::shared_ptr<Node>& node);
                 void compile_core_dot(const std::shared_ptr<Node>& node);
                 void compile_max_pool(const std::shared_ptr<Node>& node);
+                void compile_avg_pool(const std::shared_ptr<Node>& node);
                 bool compile_f32_glue(const std::shared_ptr<Node>& node);
                 bool try_compile_avgpool_head(const std::shared_ptr<Node>& quantize_node);
                 int packed_filters(const Output<Node>& filters, size_t c_pad, bool* is_image = nullptr);
@@ -170,6 +179,11 @@ namespace ngraph
                 std::vector<Step> m_steps;
                 std::map<const descriptor::Tensor*, Value> m_values;
                 std::vector<char> m_constant_host; // staged constants, uploaded once at the end of compile
+                std::vector<char> m_preloaded;     // Backend::load: the saved constant image, consumed in lowering order
+                std::map<std::string, std::pair<size_t, size_t>> m_constant_index; // key -> (offset, bytes) in the image
+                std::map<const Node*, size_t> m_node_index;                         // position in the Function's node order
+                bool m_use_preloaded = false;
+                size_t m_constant_bytes = 0;       // size of the device constant image
                 // lifetimes of the slots, in step indices: first step that may write / last step that reads
                 std::vector<size_t> m_birth, m_last;
                 std::vector<int> m_touched; // slots requested while the current node is lowered

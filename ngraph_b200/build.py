@@ -72,14 +72,14 @@ def build_plugin(force=False):
     """g++ the nGraph backend plugin against nGraph's headers and libngraph.so.  Skipped (returns None)
     where nGraph's headers or library are not available: the prebuilt .so is used there."""
     inc = ngraph_include_dir()
-    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "quant_fusion.cpp", "graph_passes.cpp", "b200_backend.hpp",
-                                                      "quant_fusion.hpp", "graph_passes.hpp")]
+    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "quant_fusion.cpp", "graph_passes.cpp", "function_io.cpp",
+                                                      "b200_backend.hpp", "quant_fusion.hpp", "graph_passes.hpp", "function_io.hpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return PLUGIN_LIB if os.path.exists(PLUGIN_LIB) else None
     build_kernels()
     if not force and _newer(PLUGIN_LIB, src + [KERNEL_LIB]):
         return PLUGIN_LIB
-    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], src[1], src[2], "-o", PLUGIN_LIB,
+    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], src[1], src[2], src[3], "-o", PLUGIN_LIB,
            "-L" + HERE, "-lb200_kernels", "-L" + NGRAPH_LIB_DIR, "-lngraph", "-L/usr/local/cuda/lib64", "-lcudart_static",
            "-ldl", "-lrt", "-lpthread", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
     subprocess.check_call(cmd)
@@ -94,7 +94,8 @@ def build_capi(force=False):
     inc = ngraph_include_dir()
     # the plugin's device-free graph passes are compiled in as well (tests look at the graph compile() would lower)
     srcs = [os.path.join(HERE, "harness", "ng_capi.cpp"), os.path.join(HERE, "harness", "bert_int8.cpp"),
-            os.path.join(HERE, "backend", "graph_passes.cpp"), os.path.join(HERE, "backend", "quant_fusion.cpp")]
+            os.path.join(HERE, "backend", "graph_passes.cpp"), os.path.join(HERE, "backend", "quant_fusion.cpp"),
+            os.path.join(HERE, "backend", "function_io.cpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return CAPI_LIB if os.path.exists(CAPI_LIB) else None
     if not force and _newer(CAPI_LIB, srcs + [os.path.join(HERE, "backend", "graph_passes.hpp"), os.path.join(HERE, "backend", "quant_fusion.hpp")]):

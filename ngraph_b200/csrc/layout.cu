@@ -174,6 +174,238 @@ namespace b200
     }
 }
 
+namespace b200
+{
+    // ---- AvgPool ------------------------------------------------------------------------------------------------
+    // runtime::reference::avg_pool (runtime/reference/avg_pool.hpp:160-236): the window is walked in (h, w) order over the
+    // PADDED image; a position inside the image adds its value and counts, a padding position adds 0 and counts only when
+    // include_padding_in_avg_computation is set; the result is sum / count, summed sequentially in the element type.
+    // Window positions beyond the padded image (ceil mode) do not exist for the reference (it refuses them): they are
+    // never counted here.
+    struct PoolGeom
+    {
+        int N, C, H, W, P, Q, win_h, win_w, stride_h, stride_w, pad_h, pad_w, pad_h_above, pad_w_above, include_padding;
+    };
+
+    // f32, NCHW in and out: one thread per output element
+    __global__ void __launch_bounds__(256) avgpool_f32_nchw_kernel(const float* __restrict__ in, float* __restrict__ out, PoolGeom g)
+    {
+        const int64_t total = int64_t(g.N) * g.C * g.P * g.Q;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int q = int(i % g.Q);
+            int64_t t = i / g.Q;
+            const int p = int(t % g.P);
+            const int64_t nc = t / g.P;
+            const float* img = in + nc * g.H * g.W;
+            float acc = 0.0f;
+            int count = 0;
+            for (int r = 0; r < g.win_h; ++r)
+            {
+                const int h = p * g.stride_h - g.pad_h + r;
+                if (h >= g.H + g.pad_h_above)
+                    break;
+                for (int sx = 0; sx < g.win_w; ++sx)
+                {
+                    const int w = q * g.stride_w - g.pad_w + sx;
+                    if (w >= g.W + g.pad_w_above)
+                        break;
+                    const bool inside = h >= 0 && h < g.H && w >= 0 && w < g.W;
+                    if (inside || g.include_padding)
+                    {
+                        acc = __fadd_rn(acc, inside ? img[int64_t(h) * g.W + w] : 0.0f);
+                        ++count;
+                    }
+                }
+            }
+            // the reference throws when a window holds no element; the host side refuses such geometries
+            out[i] = __fdiv_rn(acc, static_cast<float>(count));
+        }
+    }
+
+    // u8 / i8 AvgPool op, channels-last: the reference instantiated for a one-byte element type keeps the running sum IN
+    // that type (it wraps modulo 256) and stores nearbyint(float(sum) / count); reproduced literally.
+    template <bool SIGNED>
+    __global__ void __launch_bounds__(256) avgpool_bytes_nhwc_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, PoolGeom g)
+    {
+        const int64_t total = int64_t(g.N) * g.P * g.Q * g.C;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int c = int(i % g.C);
+            int64_t t = i / g.C;
+            const int q = int(t % g.Q);
+            t /= g.Q;
+            const int p = int(t % g.P);
+            const int n = int(t / g.P);
+            uint32_t sum = 0; // only the low byte is the reference's running sum
+            int count = 0;
+            for (int r = 0; r < g.win_h; ++r)
+            {
+                const int h = p * g.stride_h - g.pad_h + r;
+                if (h >= g.H + g.pad_h_above)
+                    break;
+                for (int sx = 0; sx < g.win_w; ++sx)
+                {
+                    const int w = q * g.stride_w - g.pad_w + sx;
+                    if (w >= g.W + g.pad_w_above)
+                        break;
+                    const bool inside = h >= 0 && h < g.H && w >= 0 && w < g.W;
+                    if (inside || g.include_padding)
+                    {
+                        if (inside)
+                            sum += in[((int64_t(n) * g.H + h) * g.W + w) * g.C + c];
+                        ++count;
+                    }
+                }
+            }
+            const float s = SIGNED ? static_cast<float>(static_cast<int8_t>(sum & 0xFF)) : static_cast<float>(sum & 0xFF);
+            const float avg = rintf(__fdiv_rn(s, static_cast<float>(count))); // nearbyint under round-to-nearest-even
+            out[i] = SIGNED ? uint8_t(static_cast<int8_t>(avg)) : static_cast<uint8_t>(avg);
+        }
+    }
+
+    // Dequantize(s_in, zp 0) -> AvgPool(f32, any window) -> Quantize(s_out, zp 0, ROUND_NEAREST_TOWARD_EVEN) on channels-last
+    // bytes in one pass, every float operation of the three ops in their order: the windowed form of the pooling head.
+    template <typename IN, typename OUT>
+    __global__ void __launch_bounds__(256) avgpool_q_nhwc_kernel(const IN* __restrict__ in, OUT* __restrict__ out,
+                                                                 const float* __restrict__ s_in, const float* __restrict__ s_out,
+                                                                 PoolGeom g)
+    {
+        const float si = *s_in, so = *s_out;
+        const int64_t total = int64_t(g.N) * g.P * g.Q * g.C;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int c = int(i % g.C);
+            int64_t t = i / g.C;
+            const int q = int(t % g.Q);
+            t /= g.Q;
+            const int p = int(t % g.P);
+            const int n = int(t / g.P);
+            float acc = 0.0f;
+            int count = 0;
+            for (int r = 0; r < g.win_h; ++r)
+            {
+                const int h = p * g.stride_h - g.pad_h + r;
+                if (h >= g.H + g.pad_h_above)
+                    break;
+                for (int sx = 0; sx < g.win_w; ++sx)
+                {
+                    const int w = q * g.stride_w - g.pad_w + sx;
+                    if (w >= g.W + g.pad_w_above)
+                        break;
+                    const bool inside = h >= 0 && h < g.H && w >= 0 && w < g.W;
+                    if (inside || g.include_padding)
+                    {
+                        const float v = inside ? __fmul_rn(static_cast<float>(int(in[((int64_t(n) * g.H + h) * g.W + w) * g.C + c])), si) : 0.0f;
+                        acc = __fadd_rn(acc, v);
+                        ++count;
+                    }
+                }
+            }
+            out[i] = quantize_one<OUT, B200_ROUND_NEAREST_TOWARD_EVEN>(__fdiv_rn(acc, static_cast<float>(count)), so, 0.0f);
+        }
+    }
+
+    // every output window must hold at least one counted element, and the sizes must fit the kernels' int fields
+    static int check_pool_geom(const b200_pool_params* g, PoolGeom& k)
+    {
+        if (!g || g->N < 0 || g->C <= 0 || g->H <= 0 || g->W <= 0 || g->P < 0 || g->Q < 0 || g->win_h <= 0 || g->win_w <= 0 ||
+            g->stride_h <= 0 || g->stride_w <= 0 || g->pad_h < 0 || g->pad_w < 0 || g->pad_h_above < 0 || g->pad_w_above < 0)
+            return B200_ERR_INVALID_ARGUMENT;
+        const int64_t big = int64_t(1) << 30;
+        if (g->N >= big || g->C >= big || g->H >= big || g->W >= big || g->P >= big || g->Q >= big || g->win_h >= big || g->win_w >= big ||
+            g->stride_h >= big || g->stride_w >= big || g->pad_h >= big || g->pad_w >= big || g->pad_h_above >= big || g->pad_w_above >= big)
+            return B200_ERR_TOO_LARGE;
+        if (g->P > 0 && g->Q > 0)
+        {
+            // the last window starts inside the padded image, and (without include_padding) reaches the image itself;
+            // the first windows must reach it too
+            const int64_t h_last = (g->P - 1) * g->stride_h - g->pad_h, w_last = (g->Q - 1) * g->stride_w - g->pad_w;
+            if (h_last >= g->H + g->pad_h_above || w_last >= g->W + g->pad_w_above)
+                return B200_ERR_INVALID_ARGUMENT;
+            if (!g->include_padding && (h_last >= g->H || w_last >= g->W || g->win_h <= g->pad_h || g->win_w <= g->pad_w))
+                return B200_ERR_INVALID_ARGUMENT;
+        }
+        k = PoolGeom{int(g->N), int(g->C), int(g->H), int(g->W), int(g->P), int(g->Q), int(g->win_h), int(g->win_w), int(g->stride_h),
+                     int(g->stride_w), int(g->pad_h), int(g->pad_w), int(g->pad_h_above), int(g->pad_w_above), g->include_padding ? 1 : 0};
+        return B200_OK;
+    }
+
+    static unsigned pool_grid(int64_t total)
+    {
+        const int64_t blocks = (total + 255) / 256, cap = int64_t(sm_count()) * 32;
+        return unsigned(blocks < cap ? blocks : cap);
+    }
+}
+
+extern "C" int b200_avgpool_f32_nchw(const float* in, float* out, const b200_pool_params* geometry, void* stream)
+{
+    using namespace b200;
+    PoolGeom g;
+    int rc = check_pool_geom(geometry, g);
+    if (rc != B200_OK)
+        return rc;
+    const int64_t total = int64_t(g.N) * g.C * g.P * g.Q;
+    if (total == 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    avgpool_f32_nchw_kernel<<<pool_grid(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, out, g);
+    return after_launch("b200_avgpool_f32_nchw");
+}
+
+extern "C" int b200_avgpool_nhwc_bytes(const void* in, void* out, int type, const b200_pool_params* geometry, void* stream)
+{
+    using namespace b200;
+    PoolGeom g;
+    int rc = check_pool_geom(geometry, g);
+    if (rc != B200_OK)
+        return rc;
+    if (type != B200_U8 && type != B200_I8)
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t total = int64_t(g.N) * g.C * g.P * g.Q;
+    if (total == 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (type == B200_I8)
+        avgpool_bytes_nhwc_kernel<true><<<pool_grid(total), 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g);
+    else
+        avgpool_bytes_nhwc_kernel<false><<<pool_grid(total), 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), g);
+    return after_launch("b200_avgpool_nhwc_bytes");
+}
+
+extern "C" int b200_avgpool_q_nhwc(const void* in, int in_type, void* out, int out_type, const float* scale_in, const float* scale_out,
+                                   const b200_pool_params* geometry, void* stream)
+{
+    using namespace b200;
+    PoolGeom g;
+    int rc = check_pool_geom(geometry, g);
+    if (rc != B200_OK)
+        return rc;
+    if ((in_type != B200_U8 && in_type != B200_I8) || (out_type != B200_U8 && out_type != B200_I8))
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t total = int64_t(g.N) * g.C * g.P * g.Q;
+    if (total == 0)
+        return B200_OK;
+    if (!in || !out || !scale_in || !scale_out)
+        return B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = pool_grid(total);
+    const uint8_t* iu = static_cast<const uint8_t*>(in);
+    const int8_t* is = static_cast<const int8_t*>(in);
+    if (in_type == B200_U8 && out_type == B200_U8)
+        avgpool_q_nhwc_kernel<uint8_t, uint8_t><<<grid, 256, 0, st>>>(iu, static_cast<uint8_t*>(out), scale_in, scale_out, g);
+    else if (in_type == B200_U8)
+        avgpool_q_nhwc_kernel<uint8_t, int8_t><<<grid, 256, 0, st>>>(iu, static_cast<int8_t*>(out), scale_in, scale_out, g);
+    else if (out_type == B200_U8)
+        avgpool_q_nhwc_kernel<int8_t, uint8_t><<<grid, 256, 0, st>>>(is, static_cast<uint8_t*>(out), scale_in, scale_out, g);
+    else
+        avgpool_q_nhwc_kernel<int8_t, int8_t><<<grid, 256, 0, st>>>(is, static_cast<int8_t*>(out), scale_in, scale_out, g);
+    return after_launch("b200_avgpool_q_nhwc");
+}
+
 extern "C" int b200_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W,
                                     int64_t c_pad, void* stream)
 {

@@ -1428,6 +1428,11 @@ namespace b200
 
     static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual)
     {
+#ifdef B200_PROFILE_WAITS
+        if (const char* f = getenv("B200_FORCE_BN")) // instrumented build only: tile-width experiments
+            if (atoi(f) > 0 && (atoi(f) != 256 || !(bk == 128 && residual)))
+                return atoi(f);
+#endif
         if (n_out <= 64)
             return 64;
         // a handful of tiles (small batch x wide layer): narrow tiles spread the weight stream over more SMs

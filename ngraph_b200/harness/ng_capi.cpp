@@ -18,7 +18,9 @@
 #include "ngraph/op/experimental/quantized_dot_bias.hpp"
 #include "ngraph/runtime/backend.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
+#include "../backend/function_io.hpp"
 #include "../backend/graph_passes.hpp"
+#include <fstream>
 
 using namespace ngraph;
 
@@ -321,6 +323,12 @@ NGC_API void* ngc_reshape(void* x, const int64_t* order, int n_order, const int6
     }, nullptr);
 }
 
+// an op outside the quantized path (tests: it must be refused, not mis-handled)
+NGC_API void* ngc_tanh(void* x)
+{
+    return guarded([&]() -> void* { return box(std::make_shared<op::v0::Tanh>(val(x))); }, nullptr);
+}
+
 NGC_API void* ngc_relu(void* x)
 {
     return guarded([&]() -> void* { return box(std::make_shared<op::v0::Relu>(val(x))); }, nullptr);
@@ -408,6 +416,39 @@ NGC_API void* ngc_compile(void* backend, void* function, int enable_performance_
         return new std::shared_ptr<runtime::Executable>(b->compile(f, enable_performance_data != 0));
     }, nullptr);
 }
+// Executable::save to a file / Backend::load from a file (executable.hpp:76-78, backend.hpp:122-125)
+NGC_API int ngc_executable_save(void* executable, const char* path)
+{
+    return guarded([&]() -> int {
+        std::ofstream out(path, std::ios::binary);
+        if (!out) throw std::runtime_error(std::string("cannot open ") + path);
+        (*static_cast<std::shared_ptr<runtime::Executable>*>(executable))->save(out);
+        out.flush();
+        if (!out) throw std::runtime_error(std::string("write failed: ") + path);
+        return 0;
+    }, -1);
+}
+NGC_API void* ngc_backend_load(void* backend, const char* path)
+{
+    return guarded([&]() -> void* {
+        std::ifstream in(path, std::ios::binary);
+        if (!in) throw std::runtime_error(std::string("cannot open ") + path);
+        auto exe = (*static_cast<std::shared_ptr<runtime::Backend>*>(backend))->load(in);
+        if (!exe) throw std::runtime_error("Backend::load returned no executable");
+        return new std::shared_ptr<runtime::Executable>(exe);
+    }, nullptr);
+}
+// The plugin's binary Function form (ngraph_b200/backend/function_io.cpp, compiled into this library too): a copy of the
+// Function after a write / read round trip, and the number of bytes written; no device needed.
+NGC_API void* ngc_function_roundtrip(void* function, int64_t* bytes_out)
+{
+    return guarded([&]() -> void* {
+        const std::string bytes = runtime::b200::write_function(**static_cast<std::shared_ptr<Function>*>(function));
+        if (bytes_out) *bytes_out = int64_t(bytes.size());
+        return new std::shared_ptr<Function>(runtime::b200::read_function(bytes));
+    }, nullptr);
+}
+
 NGC_API void ngc_executable_free(void* e) { delete static_cast<std::shared_ptr<runtime::Executable>*>(e); }
 
 NGC_API void* ngc_tensor_create(void* backend, int et, const int64_t* shape, int rank)

@@ -30,6 +30,11 @@ class ConvParams(ctypes.Structure):
                                               "pad_w", "pad_h_above", "pad_w_above", "dilation_h", "dilation_w")]
 
 
+class PoolParams(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("N", "C", "H", "W", "P", "Q", "win_h", "win_w", "stride_h", "stride_w", "pad_h", "pad_w",
+                                              "pad_h_above", "pad_w_above")] + [("include_padding", ctypes.c_int32)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError("%s is missing: run `python -m ngraph_b200.build` (needs nvcc); "
@@ -87,6 +92,9 @@ def _load():
         "b200_stem_pack_input_f32": (ci, [vp, vp, vp, ci, ci, vp] + [i64] * 10 + [vp]),
         "b200_qconv_stem": (ci, [vp, ci, vp, vp] + [i64] * 10 + [ctypes.POINTER(Epilogue), vp]),
         "b200_selftest_bounded_wait": (ci, [i64, vp]),
+        "b200_avgpool_f32_nchw": (ci, [vp, vp, ctypes.POINTER(PoolParams), vp]),
+        "b200_avgpool_nhwc_bytes": (ci, [vp, vp, ci, ctypes.POINTER(PoolParams), vp]),
+        "b200_avgpool_q_nhwc": (ci, [vp, ci, vp, ci, vp, vp, ctypes.POINTER(PoolParams), vp]),
         "b200_qconv_stem_static_capacity": (i64, []),
         "b200_qconv_stem_static": (ci, [vp, ci, vp, vp] + [i64] * 11 + [ctypes.POINTER(Epilogue), vp]),
     }

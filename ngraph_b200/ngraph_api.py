@@ -48,7 +48,7 @@ def capi():
             "ngc_convolution": (vp, [vp, vp, p64]),
             "ngc_max_pool": (vp, [vp, p64, p64, p64, p64]), "ngc_avg_pool": (vp, [vp, p64, p64]),
             "ngc_max_pool_ex": (vp, [vp, p64, p64, p64, p64, ci]), "ngc_avg_pool_ex": (vp, [vp, p64, p64, p64, p64, ci, ci]),
-            "ngc_convert": (vp, [vp, ci]), "ngc_reshape": (vp, [vp, p64, ci, p64, ci]), "ngc_relu": (vp, [vp]),
+            "ngc_convert": (vp, [vp, ci]), "ngc_reshape": (vp, [vp, p64, ci, p64, ci]), "ngc_relu": (vp, [vp]), "ngc_tanh": (vp, [vp]),
             "ngc_add": (vp, [vp, vp]), "ngc_multiply": (vp, [vp, vp]), "ngc_dot": (vp, [vp, vp, i64]),
             "ngc_broadcast": (vp, [vp, p64, ci, p64, ci]),
             "ngc_value_shape": (ci, [vp, p64, ci, ctypes.POINTER(ci)]),
@@ -63,6 +63,8 @@ def capi():
             "ngc_quantized_concat": (vp, [pvp, pvp, pvp, ci, i64]),
             "ngc_function_after_b200_passes": (vp, [vp, ci]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
+            "ngc_executable_save": (ci, [vp, ctypes.c_char_p]), "ngc_backend_load": (vp, [vp, ctypes.c_char_p]),
+            "ngc_function_roundtrip": (vp, [vp, p64]),
             "ngc_tensor_create": (vp, [vp, ci, p64, ci]), "ngc_tensor_wrap": (vp, [vp, ci, p64, ci, vp]),
             "ngc_tensor_free": (None, [vp]),
             "ngc_tensor_write": (ci, [vp, vp, i64]), "ngc_tensor_read": (ci, [vp, vp, i64]),
@@ -260,6 +262,10 @@ def reshape(x, order, shape):
     return Value(capi().ngc_reshape(x.h, _i64(order), len(order), _i64(shape), len(shape)), "Reshape")
 
 
+def tanh(x):
+    return Value(capi().ngc_tanh(x.h), "Tanh")
+
+
 def relu(x):
     return Value(capi().ngc_relu(x.h), "Relu")
 
@@ -326,6 +332,15 @@ def after_b200_passes(function, decompose_all=False):
     return BuiltFunction(h, list(function.params), list(function.results), "after_b200_passes")
 
 
+def function_roundtrip(function):
+    """(a copy of `function` written and read back through the plugin's binary Function form, bytes written)"""
+    n = ctypes.c_int64(0)
+    h = capi().ngc_function_roundtrip(function.h, ctypes.byref(n))
+    if not h:
+        _err("function_roundtrip")
+    return BuiltFunction(h, list(function.params), list(function.results), "function_roundtrip"), n.value
+
+
 def function_op_names(function, lowered=True):
     """op type names in topological order, optionally after the passes a backend runs before lowering"""
     buf = ctypes.create_string_buffer(1 << 22)
@@ -382,11 +397,16 @@ class Tensor:
 
 
 class Executable:
-    def __init__(self, backend, function, perf=False):
+    def __init__(self, backend, function, perf=False, handle=None):
         self.backend, self.function = backend, function
-        self.h = capi().ngc_compile(backend.h, function.h, int(perf))
+        self.h = handle if handle is not None else capi().ngc_compile(backend.h, function.h, int(perf))
         if not self.h:
             _err("Backend::compile")
+
+    def save(self, path):
+        """Executable::save into the file `path`"""
+        if capi().ngc_executable_save(self.h, str(path).encode()) != 0:
+            _err("Executable::save")
 
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
@@ -449,6 +469,14 @@ class Backend:
 
     def create_tensor(self, dtype, shape, device_pointer=None):
         return Tensor(self, dtype, shape, device_pointer)
+
+    def load(self, path, like):
+        """Backend::load of a file written by Executable.save; `like` (a Function or Executable with the same parameters and
+        results) only tells this Python wrapper the tensor types and shapes"""
+        h = capi().ngc_backend_load(self.h, str(path).encode())
+        if not h:
+            _err("Backend::load")
+        return Executable(self, like.function if isinstance(like, Executable) else like, handle=h)
 
 
 def registered_backends():

@@ -8,6 +8,9 @@ Pinned against nGraph's INTERPRETER in tests/test_oracle_glue.py.
   gelu             op/gelu.cpp:46-60                   (0.5 * x) * (1 + erf(x / sqrt(2)))
   batch_mat_mul    runtime/reference/dot.hpp:108-160   products summed over k in order; accumulated in double here
                                                        (the reference accumulates f32 dots in the element type)
+  avg_pool         runtime/reference/avg_pool.hpp:160-236  window walked in (h, w) order over the padded image, sum kept in
+                                                       the element type (f32: sequential float adds; u8 / i8: wraps), then
+                                                       sum / count (one-byte types: nearbyint of the float quotient)
 """
 import math
 
@@ -65,3 +68,37 @@ def batch_mat_mul(a, b):
     for k in range(a.shape[2]):
         acc += a[:, :, k, None].astype(np.float64) * b[:, k, None, :].astype(np.float64)
     return acc.astype(F)
+
+
+def avg_pool(x, window, stride=(1, 1), pad_below=(0, 0), pad_above=None, include_padding=False, out_hw=None):
+    """x [N, C, H, W], f32 / u8 / i8.  out_hw: the op's output extent when it differs from the floor formula (ceil mode);
+    window positions beyond the padded image are then not counted (the reference itself refuses such windows)."""
+    x = np.asarray(x)
+    pad_above = pad_below if pad_above is None else pad_above
+    n, c, h, w = x.shape
+    if out_hw is None:
+        out_hw = tuple((x.shape[2 + i] + pad_below[i] + pad_above[i] - window[i]) // stride[i] + 1 for i in (0, 1))
+    out = np.empty((n, c) + tuple(out_hw), x.dtype)
+    for p in range(out_hw[0]):
+        for q in range(out_hw[1]):
+            acc = np.zeros((n, c), x.dtype)
+            count = 0
+            for r in range(window[0]):
+                hh = p * stride[0] - pad_below[0] + r
+                if hh >= h + pad_above[0]:
+                    break
+                for s_ in range(window[1]):
+                    ww = q * stride[1] - pad_below[1] + s_
+                    if ww >= w + pad_above[1]:
+                        break
+                    inside = 0 <= hh < h and 0 <= ww < w
+                    if inside or include_padding:
+                        if inside:
+                            with np.errstate(over="ignore"):
+                                acc = (acc + x[:, :, hh, ww]).astype(x.dtype)  # the running sum has the element type
+                        count += 1
+            if x.dtype == np.float32:
+                out[:, :, p, q] = (acc / F(count)).astype(F)
+            else:
+                out[:, :, p, q] = np.rint((acc.astype(F) / F(count)).astype(F)).astype(x.dtype)
+    return out

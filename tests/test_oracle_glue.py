@@ -66,3 +66,23 @@ def test_batch_mat_mul_is_close_to_the_reference_and_more_exact():
     exact = np.einsum("bmk,bkn->bmn", a.astype(np.float64), b.astype(np.float64))
     np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
     assert np.abs(got - exact).max() <= np.abs(ref - exact).max()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.uint8, np.int8])
+@pytest.mark.parametrize("window,stride,pad_below,pad_above,include_padding",
+                         [((3, 3), (2, 2), (1, 1), (1, 1), False), ((3, 3), (2, 2), (1, 1), (1, 1), True),
+                          ((2, 3), (1, 2), (0, 1), (1, 0), True), ((5, 4), (5, 4), (0, 0), (0, 0), False), ((12, 10), (1, 1), (0, 0), (0, 0), False)])
+def test_avg_pool_matches_reference_avg_pool(dtype, window, stride, pad_below, pad_above, include_padding):
+    """f32 and the one-byte instantiations (whose running sum wraps in the element type) against INTERPRETER"""
+    rng = np.random.default_rng(5)
+    shape = (2, 3, 12, 10)
+    x = (rng.standard_normal(shape) * 50).astype(np.float32) if dtype == np.float32 else \
+        rng.integers(np.iinfo(dtype).min, np.iinfo(dtype).max + 1, size=shape).astype(dtype)
+    p = ng.parameter(dtype, shape)
+    want = run(ng.Function([ng.avg_pool(p, window, stride, pad_below, pad_above, include_padding)], [p]), x)
+    got = glue.avg_pool(x, window, stride, pad_below, pad_above, include_padding)
+    assert got.shape == want.shape
+    if dtype == np.float32:
+        np.testing.assert_array_equal(bits(got), bits(want))
+    else:
+        np.testing.assert_array_equal(got, want)
