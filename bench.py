@@ -42,6 +42,52 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def measure_int8_peak(torch, n=8192, reps=10):
+    """Dense int8 tensor-core peak of this GPU, measured now: (1) cuBLASLt's int8 -> int32 GEMM (torch._int_mm; off the product
+    path, used only as the roofline's denominator) and (2) this library's own b200_qgemm, both n^3, best of `reps` single launches
+    timed with CUDA events (a burst figure, like the bf16 burst figure of MEASURED_PEAKS.json)."""
+    from ngraph_b200 import ops
+    out = {"n": n, "cublaslt_int8_tops": None, "own_qgemm_tops": None}
+
+    def best(fn):
+        fn()
+        torch.cuda.synchronize()
+        b = 1e30
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            b = min(b, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (b * 1e-3) / 1e12
+
+    a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda")
+    b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda")
+    try:
+        out["cublaslt_int8_tops"] = best(lambda: torch._int_mm(a, b))
+    except Exception as e:  # the probe is optional: without it the own kernel's figure (or 2 x bf16) stands in
+        out["cublaslt_error"] = str(e)[:120]
+    au = a.view(torch.uint8)
+    s = torch.full((1,), 1e-5, device="cuda")
+    o = torch.empty((n, n), dtype=torch.uint8, device="cuda")
+    out["own_qgemm_tops"] = best(lambda: ops.qgemm(au, b, s, torch.uint8, relu=True, out=o))
+    del a, b, au, o
+    torch.cuda.empty_cache()
+    return out
+
+
+def int8_peak(peaks, probe):
+    """(peak TOP/s, text saying where it comes from): the larger of the two measured int8 figures; 2 x the measured bf16 burst
+    figure only when no int8 GEMM could be timed"""
+    cands = [(probe.get("cublaslt_int8_tops"), "measured in this run: cuBLASLt int8 GEMM %d^3, best of 10" % probe["n"]),
+             (probe.get("own_qgemm_tops"), "measured in this run: b200_qgemm %d^3, best of 10" % probe["n"])]
+    cands = [c for c in cands if c[0]]
+    if cands:
+        return max(cands)
+    return 2.0 * peaks["bf16_tflops"], peaks["source"] + ": 2 x bf16 burst (no int8 GEMM could be timed)"
+
+
 class ClockSampler:
     """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -220,9 +266,11 @@ class ResNet50:
     def io_bytes(self):
         return self.pin_in.numel() * 4, self.pin_out.numel() * 4
 
-    def roofline(self, peaks, per_step_ms):
-        """dominant kernel = the tcgen05 contraction kernel (all convolutions + the dot): its time per step
-        from per-node CUDA events in a separate instrumented pass over the same graph"""
+    def roofline(self, peaks, per_step_ms, probe):
+        """dominant kernel = the tcgen05 contraction kernel (all convolutions + the dot).  achieved = the step's int8 ops / the
+        part of the TIMED step that kernel takes: ms_per_step (CUDA events over the timed region, above) x the kernel's share of
+        the step.  The share comes from per-node CUDA events of a separate, instrumented pass over the same graph
+        (compile(f, true) -> get_performance_data()); that pass serialises the nodes, so only the ratio is taken from it."""
         ng = self.ng
         exe = self.backend.compile(self.model.build(ng, self.batch, fused=True)[0], perf=True)
         passes = 5
@@ -232,29 +280,34 @@ class ResNet50:
         rows = exe.performance_data()
         contr_us = sum(us for n, us, c in rows if n.startswith("QuantizedConvolution") or n.startswith("QuantizedDot")) / passes
         total_us = sum(us for n, us, c in rows) / passes
+        share = contr_us / total_us
+        kernel_us = per_step_ms * 1e3 * share
         ops = 2.0 * self.model.macs_per_image() * self.batch
-        achieved = ops / (contr_us * 1e-6) / 1e12
-        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        achieved = ops / (kernel_us * 1e-6) / 1e12
+        peak, peak_source = int8_peak(peaks, probe)
         top = sorted(((us / passes, n) for n, us, c in rows), reverse=True)[:6]
         if os.environ.get("B200_BENCH_NODE_TABLE"):  # per-node table for the profile notes
             with open(os.environ["B200_BENCH_NODE_TABLE"], "w") as f:
                 for n, us, c in rows:
                     f.write("%10.1f us  %s\n" % (us / passes, n))
-        # dram__bytes_read.sum + dram__bytes_write.sum of the 54 contraction launches of one batch-128 step, from the ncu
-        # capture summarised in profiles/resnet50_b128_launch_list.txt, averaged per launch and scaled by the batch
         # the same launches against their own rooflines: a layer can go no faster than its ops at the tensor peak or its
         # bytes at the HBM peak, whichever is longer; most 1x1 layers are on the HBM side
         work = self.model.layer_work()
         assert abs(sum(m for _, m, _, _ in work) - self.model.macs_per_image()) < 1
         floor_us = sum(max(2.0 * m * self.batch / (peak * 1e12), (by * self.batch + wt) / (peaks["hbm_gbs"] * 1e9)) * 1e6
                        for _, m, by, wt in work)
+        # dram__bytes_read.sum + dram__bytes_write.sum of the 54 contraction launches of one batch-128 step (one ncu capture,
+        # summarised in profiles/resnet50_b128_launch_list.txt), averaged per launch and scaled by the batch
         traffic = (1976.9e6 + 350.8e6) / 54 * (self.batch / 128.0)
-        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": traffic,
-                "traffic_note": "average per contraction launch (54 per step), ncu capture at batch 128",
-                "per_layer_floor_us": floor_us, "frac_of_per_layer_floor": floor_us / contr_us,
-                "kernel": "qcontract_kernel (53 convolutions + dot)", "kernel_us_per_step": contr_us, "all_nodes_us_per_step": total_us,
-                "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)",
-                "slowest_nodes_us": [[round(u, 1), n] for u, n in top]}
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
+                "ops_per_step": ops, "kernel_us_per_step": kernel_us, "kernel_share_of_step": share,
+                "kernel_share_source": "per-node CUDA events, instrumented pass: %.1f of %.1f us" % (contr_us, total_us),
+                "traffic": traffic, "traffic_source": "profiles/resnet50_b128_launch_list.txt (ncu dram bytes of the 54 contraction "
+                                                      "launches of a batch-128 step / 54, scaled by batch/128)",
+                "per_layer_floor_us": floor_us, "frac_of_per_layer_floor": floor_us / kernel_us,
+                "kernel": "qcontract_kernel (53 convolutions + dot)",
+                "peak_source": peak_source, "peak_i8_measured": probe, "peak_2x_bf16_burst": 2.0 * peaks["bf16_tflops"],
+                "slowest_nodes_us_instrumented": [[round(u, 1), n] for u, n in top]}
 
     def extra_cpu_baselines(self):
         """The north star asks for nGraph's DNNL CPU backend beside the number; that backend cannot be built offline, so the
@@ -351,9 +404,9 @@ class BertEncoder:
         d = self.dims
         return 2.0 * (4 * d["hidden"] ** 2 + 2 * d["hidden"] * d["ffn"]) * d["layers"] * self.batch * d["seq"]
 
-    def roofline(self, peaks, per_step_ms):
-        """the int8 dots against the tensor peak, from per-node CUDA events of an instrumented pass; the f32 glue is listed
-        beside them because it is most of the step"""
+    def roofline(self, peaks, per_step_ms, probe):
+        """the int8 dots against the tensor peak: their share of the step from per-node CUDA events of an instrumented pass,
+        applied to the timed step; the f32 glue is listed beside them because it is most of the step"""
         exe = self.backend.compile(self.fn, perf=True)
         passes = 3
         for _ in range(passes):
@@ -363,15 +416,16 @@ class BertEncoder:
         by_op = {}
         for n, us, c in rows:
             by_op[n.split(":")[0]] = by_op.get(n.split(":")[0], 0.0) + us / passes
-        dots_us = by_op.get("QuantizedDotBias", 0.0)
         total_us = sum(by_op.values())
-        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        share = by_op.get("QuantizedDotBias", 0.0) / total_us
+        dots_us = per_step_ms * 1e3 * share
+        peak, peak_source = int8_peak(peaks, probe)
         achieved = self.int8_ops_per_step() / (dots_us * 1e-6) / 1e12
         top = sorted(((round(v, 1), k) for k, v in by_op.items()), reverse=True)[:8]
         return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
-                "kernel": "qcontract_kernel (72 QuantizedDotBias layers)", "kernel_us_per_step": dots_us,
-                "all_nodes_us_per_step": total_us, "glue_share_of_step": 1.0 - dots_us / total_us, "op_types_us_per_step": top,
-                "peak_source": peaks["source"] + ": 2 x bf16 sustained (int8 peak not measured separately)"}
+                "kernel": "qcontract_kernel (72 QuantizedDotBias layers)", "kernel_us_per_step": dots_us, "kernel_share_of_step": share,
+                "kernel_share_source": "per-node CUDA events, instrumented pass", "glue_share_of_step": 1.0 - share,
+                "op_types_us_per_step_instrumented": top, "peak_source": peak_source, "peak_i8_measured": probe}
 
     def cpu_sample(self):
         """nGraph's INTERPRETER on ONE layer of the same width over one short sequence, scaled to the depth of the model"""
@@ -403,18 +457,20 @@ class MicroWorkload:
     """single-kernel workloads called through the C ABI (ngraph_b200.ops)"""
     bound = "tensor"
 
+    light = False  # True: device buffers only (no pinned host mirrors for the end-to-end loop)
+
     def setup(self, torch, rank, local_rank, world):
         from ngraph_b200 import ops
         self.torch, self.ops = torch, ops
         self.alloc(1 + rank)
 
-    def roofline(self, peaks, per_step_ms):
+    def roofline(self, peaks, per_step_ms, probe):
         alg = self.alg_per_launch()
         if self.bound == "hbm":
-            achieved, peak, unit, src = alg / (per_step_ms / 1e3) / 1e9, peaks["hbm_gbs"], "GB/s", peaks["source"]
+            achieved, peak, unit, src = alg / (per_step_ms / 1e3) / 1e9, peaks["hbm_gbs"], "GB/s", peaks["source"] + ": device copy"
         else:
-            achieved, peak, unit = alg / (per_step_ms / 1e3) / 1e12, 2.0 * peaks["bf16_tflops"], "TOP/s"
-            src = peaks["source"] + ": 2 x bf16 burst (int8 peak not measured separately)"
+            achieved, unit = alg / (per_step_ms / 1e3) / 1e12, "TOP/s"
+            peak, src = int8_peak(peaks, probe)
         return {"bound": self.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None,
                 "peak_source": src}
 
@@ -471,8 +527,9 @@ class QConvLayer(MicroWorkload):
         self.sum_scale = torch.full((1,), 0.37, device="cuda") if self.with_sum else None
         pad = self.R // 2
         self.cp = ops.conv_params((self.B, self.H, self.W, self.C), (self.K, self.R, self.R, self.C), (1, 1), (pad, pad))
-        self.pin_in = torch.from_numpy(h["data"]).pin_memory()
-        self.pin_out = torch.empty((self.B, self.H, self.W, self.K), dtype=torch.uint8).pin_memory()
+        if not self.light:
+            self.pin_in = torch.from_numpy(h["data"]).pin_memory()
+            self.pin_out = torch.empty((self.B, self.H, self.W, self.K), dtype=torch.uint8).pin_memory()
         self.i = 0
 
     def units_per_step(self):
@@ -546,8 +603,9 @@ class QDotLayer(MicroWorkload):
         self.a = [torch.from_numpy(self.h_a).cuda() for _ in range(self.nbuf)]
         self.out = [torch.empty((self.M, self.N), dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
         self.w, self.bias, self.scale = (torch.from_numpy(v).cuda() for v in (self.h_w, self.h_bias, self.h_scale))
-        self.pin_in = torch.from_numpy(self.h_a).pin_memory()
-        self.pin_out = torch.empty((self.M, self.N), dtype=torch.uint8).pin_memory()
+        if not self.light:
+            self.pin_in = torch.from_numpy(self.h_a).pin_memory()
+            self.pin_out = torch.empty((self.M, self.N), dtype=torch.uint8).pin_memory()
         self.i = 0
         # A launch of the small problems (BASELINE's own M = 256 is 0.5 GOP) is shorter than the host needs to issue it,
         # so those are timed as a CUDA graph of back-to-back launches, replayed once per step.
@@ -619,13 +677,18 @@ class QuantizeSweepPoint(MicroWorkload):
     name, metric, unit, dtype = "quantize", "Quantize f32->u8 bandwidth", "GB/s", "f32->u8"
     bound = "hbm"
 
-    def __init__(self, batch=64):
+    def __init__(self, batch=64, dequantize=False):
         self.shape = (batch, 64, 256, 256)
+        self.dequantize = dequantize
+        if dequantize:
+            self.metric, self.dtype = "Dequantize u8->f32 bandwidth", "u8->f32"
 
     def describe(self, world=1):
         n = int(np.prod(self.shape))
-        return {"workload": "Quantize f32%s -> u8 per-tensor scale 0.05 zp 128 RNE" % (list(self.shape),),
-                "l2": "input %.0f MB per step (> 126 MB L2)" % (n * 4 / 1e6)}
+        what = "Dequantize u8%s -> f32" if self.dequantize else "Quantize f32%s -> u8"
+        return {"workload": (what + " per-tensor scale 0.05 zp 128%s") % (list(self.shape), "" if self.dequantize else " RNE"),
+                "l2": "f32 side %.0f MB per step (> 126 MB L2)" % (n * 4 / 1e6) if n * 4 > 126e6 else
+                      "f32 side %.0f MB per step: fits the 126 MB L2, so the timed loop alternates between buffers that together exceed it" % (n * 4 / 1e6)}
 
     def host_inputs(self, seed):
         self.h_x = np.random.default_rng(seed).standard_normal(1 << 24).astype(np.float32)
@@ -635,27 +698,38 @@ class QuantizeSweepPoint(MicroWorkload):
         self.host_inputs(seed)
         g = torch.Generator(device="cuda")
         g.manual_seed(seed)
-        self.x = torch.randn(self.shape, device="cuda", generator=g)
-        self.y = torch.empty(self.shape, dtype=torch.uint8, device="cuda")
+        n = int(np.prod(self.shape))
+        self.nbuf = max(1, int(300e6 // (n * 5)) + 1) if n * 4 <= 126e6 else 1  # small tensors: rotate so that L2 does not serve them
+        self.x = [torch.randn(self.shape, device="cuda", generator=g) for _ in range(self.nbuf)]
+        self.y = [torch.empty(self.shape, dtype=torch.uint8, device="cuda") for _ in range(self.nbuf)]
         self.s = torch.full((), 0.05, device="cuda")
         self.z = torch.full((), 128, dtype=torch.uint8, device="cuda")
-        self.pin_in = torch.empty(self.shape, dtype=torch.float32).pin_memory()
-        self.pin_in.copy_(self.x)
-        self.pin_out = torch.empty(self.shape, dtype=torch.uint8).pin_memory()
+        self.i = 0
+        if self.dequantize:
+            for x, y in zip(self.x, self.y):
+                self.ops.quantize(x, self.s, self.z, (), 4, out=y)
+        if not self.light:
+            self.pin_in = torch.empty(self.shape, dtype=torch.float32).pin_memory()
+            self.pin_in.copy_(self.x[0])
+            self.pin_out = torch.empty(self.shape, dtype=torch.uint8).pin_memory()
 
     def units_per_step(self):
-        return 5.0 * self.x.numel() / 1e9
+        return 5.0 * self.x[0].numel() / 1e9
 
     def alg_per_launch(self):
-        return 5.0 * self.x.numel()
+        return 5.0 * self.x[0].numel()
 
     def step(self):
-        self.ops.quantize(self.x, self.s, self.z, (), 4, out=self.y)
+        i = self.i = (self.i + 1) % self.nbuf
+        if self.dequantize:
+            self.ops.dequantize(self.y[i], self.s, self.z, (), out=self.x[i])
+        else:
+            self.ops.quantize(self.x[i], self.s, self.z, (), 4, out=self.y[i])
 
     def step_e2e(self):
-        self.x.copy_(self.pin_in, non_blocking=True)
-        self.ops.quantize(self.x, self.s, self.z, (), 4, out=self.y)
-        self.pin_out.copy_(self.y, non_blocking=True)
+        self.x[0].copy_(self.pin_in, non_blocking=True)
+        self.ops.quantize(self.x[0], self.s, self.z, (), 4, out=self.y[0])
+        self.pin_out.copy_(self.y[0], non_blocking=True)
 
     def io_bytes(self):
         return self.pin_in.numel() * 4, self.pin_out.numel()
@@ -663,8 +737,12 @@ class QuantizeSweepPoint(MicroWorkload):
     def check(self):
         from oracle import ref
         n = 1 << 20
-        exp = ref.quantize(self.x.view(-1)[:n].cpu().numpy(), np.float32(0.05), np.uint8(128))
-        return bool(np.array_equal(self.y.view(-1)[:n].cpu().numpy(), exp))
+        i = self.i
+        if self.dequantize:
+            exp = ref.dequantize(self.y[i].view(-1)[:n].cpu().numpy(), np.float32(0.05), np.uint8(128))
+            return bool(np.array_equal(self.x[i].view(-1)[:n].cpu().numpy().view(np.uint32), exp.view(np.uint32)))
+        exp = ref.quantize(self.x[i].view(-1)[:n].cpu().numpy(), np.float32(0.05), np.uint8(128))
+        return bool(np.array_equal(self.y[i].view(-1)[:n].cpu().numpy(), exp))
 
     def cpu_sample(self):
         from oracle import ref
@@ -674,6 +752,45 @@ class QuantizeSweepPoint(MicroWorkload):
             reps += 1
         dt = time.time() - t
         return reps * 5.0 * self.h_x.size / 1e9 / dt, "C port of the reference arithmetic, %d elements, %d passes, %.1f s" % (self.h_x.size, reps, dt)
+
+
+def per_config_block(torch, peaks, probe, steps=20):
+    """The other workloads the baseline names, each timed for a moment through the C ABI on this GPU (device-resident
+    inputs, CUDA events, parity against the oracle on a sample): so that one default run records a roofline fraction for
+    every one of them, not only for the headline network."""
+    cases = [("QuantizedDotBias+Relu M=256 (CUDA graph of 64 launches)", QDotLayer(256)),
+             ("QuantizedDotBias+Relu M=4096", QDotLayer(4096)),
+             ("QuantizedDotBias+Relu M=32768", QDotLayer(32768)),
+             ("QuantizedConvolutionBias+Relu 3x3 C=K=64 56x56 batch 32", QConvLayer(32)),
+             ("QuantizedConvolutionBias+Relu 3x3 C=K=64 56x56 batch 128", QConvLayer(128)),
+             ("Quantize f32->u8 RNE 67 MB", QuantizeSweepPoint(4)), ("Quantize f32->u8 RNE 268 MB", QuantizeSweepPoint(16)),
+             ("Quantize f32->u8 RNE 1074 MB", QuantizeSweepPoint(64)),
+             ("Dequantize u8->f32 67 MB", QuantizeSweepPoint(4, True)), ("Dequantize u8->f32 268 MB", QuantizeSweepPoint(16, True)),
+             ("Dequantize u8->f32 1074 MB", QuantizeSweepPoint(64, True))]
+    out = []
+    for name, wl in cases:
+        try:
+            wl.light = True
+            wl.setup(torch, 0, torch.cuda.current_device(), 1)
+            for _ in range(5):
+                wl.step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                wl.step()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            r = wl.roofline(peaks, ms, probe)
+            launches = wl.launches_per_step() if hasattr(wl, "launches_per_step") else 1
+            out.append({"workload": name, "us_per_launch": ms * 1e3 / launches, "achieved": r["achieved"], "unit": r["unit"],
+                        "peak": r["peak"], "frac": r["frac"], "bound": r["bound"], "parity_vs_oracle": wl.check()})
+        except Exception as e:  # one case that cannot run must not lose the headline line
+            out.append({"workload": name, "error": str(e)[:160]})
+        del wl
+        torch.cuda.empty_cache()
+    return out
 
 
 WORKLOADS = {"resnet50": ResNet50, "qconv": QConvLayer, "qdot": QDotLayer, "quantize": QuantizeSweepPoint, "bert": BertEncoder}
@@ -713,6 +830,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (images / rows); for small profiler captures")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the short per-workload block of the default run")
+    ap.add_argument("--no-peak-probe", action="store_true", help="skip the in-run int8 GEMM peak measurement (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -790,10 +909,29 @@ def main():
     clocks = sampler.stop(t0, time.time())  # both timed regions (device-resident and end-to-end)
     lib.device_status()
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+    # the floor under the end-to-end number: this rank's pinned host -> device copy of one step's input alone, while every
+    # other rank does the same (the ranks share the host's memory and PCIe fabric)
+    h2d_floor_gbs = None
+    h2d_bytes = wl.io_bytes()[0]
+    if h2d_bytes >= (1 << 20):
+        src = torch.empty(h2d_bytes, dtype=torch.uint8).pin_memory()
+        dst = torch.empty(h2d_bytes, dtype=torch.uint8, device="cuda")
+        dst.copy_(src, non_blocking=True)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(10):
+            dst.copy_(src, non_blocking=True)
+        c1.record()
+        barrier()
+        h2d_floor_gbs = h2d_bytes * 10 / (c0.elapsed_time(c1) * 1e-3) / 1e9
+        del src, dst
+
+    t = torch.tensor([ms, ms_e2e, -(h2d_floor_gbs or 0.0)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
+    h2d_floor_gbs = -float(t[2]) if h2d_floor_gbs else None  # the slowest rank's copy rate
 
     if rank == 0:
         per_step = ms / args.steps
@@ -801,12 +939,20 @@ def main():
         e2e_units = wl.e2e_units_per_step() if hasattr(wl, "e2e_units_per_step") else wl.units_per_step()
         e2e_value = e2e_units * world / (ms_e2e / args.steps / 1e3)
         h2d, d2h = wl.io_bytes()
+        e2e = {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": ms_e2e / args.steps}
+        if h2d_floor_gbs:
+            # what the host -> device copy alone allows (slowest rank, all ranks copying at once) against what was reached
+            floor_ms = h2d / (h2d_floor_gbs * 1e9) * 1e3
+            e2e.update({"h2d_floor_gbs": h2d_floor_gbs, "h2d_floor_ms_per_step": floor_ms,
+                        "frac_of_h2d_floor": floor_ms / (ms_e2e / args.steps)})
+        probe = {"n": 0} if args.no_peak_probe or wl.bound != "tensor" else measure_int8_peak(torch)
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(world),
-                "gpu_launches": launches, "clocks": clocks,
-                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "roofline": wl.roofline(peaks, per_step)}
+                "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": wl.roofline(peaks, per_step, probe)}
+        if isinstance(wl, ResNet50) and world == 1 and not args.no_per_config:
+            line["per_config"] = per_config_block(torch, peaks, probe)
         cpu, ok = wl.check_and_cpu_baseline(args.no_cpu_baseline or world > 1)
         line["parity_vs_oracle"] = ok
         if cpu is not None:

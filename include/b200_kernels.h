@@ -300,6 +300,19 @@ B200_API int b200_maxpool_nhwc_i8(const void* in, void* out, int64_t N, int64_t 
  * therefore pool in f32, which is also where the CPU backend's fusion starts:
  * src/ngraph/runtime/cpu/pass/cpu_fusion.cpp:2160-2200.)  scale_in / scale_out: one float each, device memory.
  */
+/*
+ * Data dilation and negative padding of the convolutions, materialised on channels-last one-byte tensors (C a multiple of
+ * 16): out [N, Ho, Wo, C] with Ho = (H - 1) * dilation_h + 1 - crop_h_below - crop_h_above (Wo alike) is the input with
+ * dilation - 1 zero pixels between neighbours, less `crop` pixels at each border.  It stands for the data-dilation strides and
+ * the negative part of padding_below / padding_above of op::v0::QuantizedConvolution and the fused convolutions
+ * (src/ngraph/runtime/reference/convolution.hpp:59-265: CoordinateTransform with source dilation and signed padding, positions
+ * that are not source coordinates are skipped); an ordinary convolution of the result with the non-negative part of the
+ * padding then gives the reference's values.
+ */
+B200_API int b200_dilate_crop_nhwc_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t dilation_h,
+                                      int64_t dilation_w, int64_t crop_h_below, int64_t crop_w_below, int64_t crop_h_above,
+                                      int64_t crop_w_above, void* stream);
+
 B200_API int b200_global_avgpool_q_nhwc_u8(const void* in, void* out, const float* scale_in,
                                            const float* scale_out, int64_t N, int64_t H, int64_t W, int64_t C,
                                            void* stream);

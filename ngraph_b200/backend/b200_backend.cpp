@@ -1458,11 +1458,11 @@ static b200_conv_params make_conv_params(const Node& node, const ConvAttrs& a, c
         unsupported(node, "only 2-D convolutions");
     for (size_t v : a.data_dilation)
         if (v != 1)
-            unsupported(node, "data dilation");
+            unsupported(node, "data dilation on this path");
     for (auto v : a.below)
-        if (v < 0) unsupported(node, "negative padding");
+        if (v < 0) unsupported(node, "negative padding on this path");
     for (auto v : a.above)
-        if (v < 0) unsupported(node, "negative padding");
+        if (v < 0) unsupported(node, "negative padding on this path");
     b200_conv_params c;
     c.N = ds[0]; c.H = ds[2]; c.W = ds[3]; c.C = c_dev;
     c.K = fs[0]; c.R = fs[2]; c.S = fs[3];
@@ -1471,6 +1471,36 @@ static b200_conv_params make_conv_params(const Node& node, const ConvAttrs& a, c
     c.pad_h_above = a.above[0]; c.pad_w_above = a.above[1];
     c.dilation_h = a.dilation[0]; c.dilation_w = a.dilation[1];
     return c;
+}
+
+// Data dilation and negative padding (legal in every convolution op, runtime/reference/convolution.hpp:59-265) are taken out
+// of the convolution itself: the channels-last input `x` [N, H, W, c_dev] is dilated with zero pixels and cropped into a new
+// buffer (b200_dilate_crop_nhwc_u8), `ds` then describes that buffer and `below` / `above` keep their non-negative part.
+// Returns the slot to convolve.
+int B200Executable::dilate_and_crop_input(const std::shared_ptr<Node>& node, int x, Shape& ds, Strides& data_dilation,
+                                          CoordinateDiff& below, CoordinateDiff& above, size_t c_dev)
+{
+    const bool dilated = data_dilation[0] != 1 || data_dilation[1] != 1;
+    const bool cropped = below[0] < 0 || below[1] < 0 || above[0] < 0 || above[1] < 0;
+    if (!dilated && !cropped)
+        return x;
+    const int64_t N = ds[0], H = ds[2], W = ds[3], Cd = int64_t(c_dev);
+    const int64_t dh = int64_t(data_dilation[0]), dw = int64_t(data_dilation[1]);
+    const int64_t cb0 = std::max<int64_t>(-below[0], 0), cb1 = std::max<int64_t>(-below[1], 0);
+    const int64_t ca0 = std::max<int64_t>(-above[0], 0), ca1 = std::max<int64_t>(-above[1], 0);
+    const int64_t Ho = (H - 1) * dh + 1 - cb0 - ca0, Wo = (W - 1) * dw + 1 - cb1 - ca1;
+    if (Ho <= 0 || Wo <= 0)
+        unsupported(*node, "negative padding that leaves no input");
+    int xd = new_slot(Slot::ARENA, size_t(N * Ho * Wo * Cd));
+    emit(node, "dilate_crop", [=](const Ptrs& p, cudaStream_t st) {
+        return b200_dilate_crop_nhwc_u8(p[x], p[xd], N, H, W, Cd, dh, dw, cb0, cb1, ca0, ca1, st);
+    });
+    ds[2] = size_t(Ho);
+    ds[3] = size_t(Wo);
+    data_dilation = Strides{1, 1};
+    below = CoordinateDiff{std::max<std::ptrdiff_t>(below[0], 0), std::max<std::ptrdiff_t>(below[1], 0)};
+    above = CoordinateDiff{std::max<std::ptrdiff_t>(above[0], 0), std::max<std::ptrdiff_t>(above[1], 0)};
+    return xd;
 }
 
 void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
@@ -1495,7 +1525,11 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
         auto op2 = as_type_ptr<op::v0::QuantizedConvolutionRelu>(node);
         a = attrs_of(op2); relu = true; scale_in = 2;
     }
-    const Shape ds = node->get_input_shape(0), fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    Shape ds = node->get_input_shape(0);
+    const Shape fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    if (ds.size() != 4 || fs.size() != 4)
+        unsupported(*node, "only 2-D convolutions");
+    const bool plain_geometry = a.data_dilation == Strides{1, 1} && a.below[0] >= 0 && a.below[1] >= 0 && a.above[0] >= 0 && a.above[1] >= 0;
     int dt = dtype_of(node->get_input_element_type(0));
     if ((dt != B200_U8 && dt != B200_I8) || node->get_input_element_type(1) != element::i8)
         unsupported(*node, "data must be u8/i8 and filters i8");
@@ -1525,7 +1559,7 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
     int y = new_slot(Slot::ARENA, shape_size(os));
     const size_t C = ds[1];
 
-    if (C <= 4 && a.strides[0] == 2 && a.strides[1] == 2 && a.dilation[0] == 1 && a.dilation[1] == 1 &&
+    if (plain_geometry && C <= 4 && a.strides[0] == 2 && a.strides[1] == 2 && a.dilation[0] == 1 && a.dilation[1] == 1 &&
         as_constant(node->input_value(1)))
     {
         // stride-2 small-channel stem: 2x2x4 cells, then an implicit GEMM over overlapping 64-byte windows
@@ -1578,7 +1612,7 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
         }
     }
 
-    if (C <= 4 && fs[3] <= 8 && a.dilation[0] == 1 && a.dilation[1] == 1)
+    if (plain_geometry && C <= 4 && fs[3] <= 8 && a.dilation[0] == 1 && a.dilation[1] == 1)
     {
         // small-channel stem: 4-channel pixels -> patch matrix -> matrix product
         b200_conv_params c = make_conv_params(*node, a, ds, fs, 4);
@@ -1635,6 +1669,7 @@ void B200Executable::compile_fused_conv(const std::shared_ptr<Node>& node)
             return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
         });
     }
+    x = dilate_and_crop_input(node, x, ds, a.data_dilation, a.below, a.above, c_dev);
     bool image = false;
     int w = packed_filters(node->input_value(1), c_dev, &image);
     b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);
@@ -1669,7 +1704,10 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
 {
     auto op = as_type_ptr<op::v0::QuantizedConvolution>(node);
     ConvAttrs a = attrs_of(op);
-    const Shape ds = node->get_input_shape(0), fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    Shape ds = node->get_input_shape(0);
+    const Shape fs = node->get_input_shape(1), os = node->get_output_shape(0);
+    if (ds.size() != 4 || fs.size() != 4)
+        unsupported(*node, "only 2-D convolutions");
     int dt = dtype_of(node->get_input_element_type(0));
     const element::Type& ft = node->get_input_element_type(1);
     if (dt != B200_U8 || (ft != element::i8 && ft != element::u8))
@@ -1703,6 +1741,10 @@ void B200Executable::compile_core_conv(const std::shared_ptr<Node>& node)
             return b200_nchw_to_nhwc_u8(p[xc], p[x], N, Ci, H, W, Cp, st);
         });
     }
+    // with non-zero zero points the correction terms count the taps inside the image from the op's own geometry: there the
+    // dilated / cropped form is not offered
+    if (za == 0 && zf == 0)
+        x = dilate_and_crop_input(node, x, ds, a.data_dilation, a.below, a.above, c_dev);
     bool image = false;
     int w = packed_filters(node->input_value(1), c_dev, &image);
     b200_conv_params c = make_conv_params(*node, a, ds, fs, c_dev);

@@ -165,6 +165,8 @@ namespace ngraph
                 void compile_core_dot(const std::shared_ptr<Node>& node);
                 void compile_max_pool(const std::shared_ptr<Node>& node);
                 void compile_avg_pool(const std::shared_ptr<Node>& node);
+                int dilate_and_crop_input(const std::shared_ptr<Node>& node, int x, Shape& ds, Strides& data_dilation,
+                                          CoordinateDiff& below, CoordinateDiff& above, size_t c_dev);
                 bool compile_f32_glue(const std::shared_ptr<Node>& node);
                 bool try_compile_avgpool_head(const std::shared_ptr<Node>& quantize_node);
                 int packed_filters(const Output<Node>& filters, size_t c_pad, bool* is_image = nullptr);

@@ -406,6 +406,58 @@ extern "C" int b200_avgpool_q_nhwc(const void* in, int in_type, void* out, int o
     return after_launch("b200_avgpool_q_nhwc");
 }
 
+namespace b200
+{
+    // Data dilation and negative padding of a convolution, materialised: the channels-last input with dil - 1 zero pixels
+    // inserted between neighbours and crop pixels cut off each border of the dilated image.  Inserted pixels are zero BYTES:
+    // the reference never visits them (they are not source coordinates, runtime/reference/convolution.hpp:227-251), and a zero
+    // byte contributes nothing to the accumulator.  One thread per 16 channels of one output pixel.
+    __global__ void __launch_bounds__(256) dilate_crop_nhwc_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int N, int H, int W,
+                                                                   int C16, int Ho, int Wo, int dil_h, int dil_w, int crop_h, int crop_w)
+    {
+        const int64_t total = int64_t(N) * Ho * Wo * C16;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+        {
+            const int c = int(i % C16);
+            int64_t t = i / C16;
+            const int x = int(t % Wo);
+            t /= Wo;
+            const int y = int(t % Ho);
+            const int n = int(t / Ho);
+            const int yy = y + crop_h, xx = x + crop_w;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (yy % dil_h == 0 && xx % dil_w == 0 && yy / dil_h < H && xx / dil_w < W)
+                v = in[((int64_t(n) * H + yy / dil_h) * W + xx / dil_w) * C16 + c];
+            out[i] = v;
+        }
+    }
+}
+
+extern "C" int b200_dilate_crop_nhwc_u8(const void* in, void* out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t dilation_h,
+                                        int64_t dilation_w, int64_t crop_h_below, int64_t crop_w_below, int64_t crop_h_above,
+                                        int64_t crop_w_above, void* stream)
+{
+    using namespace b200;
+    if (N < 0 || H <= 0 || W <= 0 || C <= 0 || dilation_h <= 0 || dilation_w <= 0 || crop_h_below < 0 || crop_w_below < 0 ||
+        crop_h_above < 0 || crop_w_above < 0)
+        return B200_ERR_INVALID_ARGUMENT;
+    if (C % 16 != 0 || (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return B200_ERR_UNSUPPORTED;
+    const int64_t Ho = (H - 1) * dilation_h + 1 - crop_h_below - crop_h_above, Wo = (W - 1) * dilation_w + 1 - crop_w_below - crop_w_above;
+    if (N == 0 || Ho <= 0 || Wo <= 0)
+        return B200_OK;
+    if (!in || !out)
+        return B200_ERR_INVALID_ARGUMENT;
+    const int64_t big = int64_t(1) << 30;
+    if (N >= big || H >= big || W >= big || Ho >= big || Wo >= big || C >= big)
+        return B200_ERR_TOO_LARGE;
+    const int64_t total = N * Ho * Wo * (C / 16), blocks = (total + 255) / 256, cap = int64_t(sm_count()) * 32;
+    dilate_crop_nhwc_kernel<<<unsigned(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(in), static_cast<uint4*>(out), int(N), int(H), int(W), int(C / 16), int(Ho), int(Wo), int(dilation_h),
+        int(dilation_w), int(crop_h_below), int(crop_w_below));
+    return after_launch("b200_dilate_crop_nhwc_u8");
+}
+
 extern "C" int b200_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W,
                                     int64_t c_pad, void* stream)
 {

@@ -149,8 +149,8 @@ namespace b200
     constexpr uint32_t BACKOFF_EMPTY_NS = B200_BACKOFF_EMPTY_NS, BACKOFF_FULL_NS = B200_BACKOFF_FULL_NS,
                        BACKOFF_TEMPTY_NS = B200_BACKOFF_TEMPTY_NS, BACKOFF_TFULL_NS = B200_BACKOFF_TFULL_NS;
 
-    constexpr int MAX_STAGES = 16;
-    constexpr int BAR_BYTES = 1024;         // 2*MAX_STAGES + 2*MAX_ACC + 1 + 3*EPI_WARPS mbarriers
+    constexpr int MAX_STAGES = 40;          // small stages (the stem's 2 KB cell runs) need many in flight to cover the load latency
+    constexpr int BAR_BYTES = 2048;         // 2*MAX_STAGES + 2*MAX_ACC + 1 + 3*EPI_WARPS mbarriers of 8 bytes
     constexpr int B_RESIDENT_MAX = 73728;   // a whole filter / weight matrix up to this size stays in shared memory
 
     template <int BN, int BK>
@@ -459,21 +459,21 @@ namespace b200
             abort_flag = 0;
         {
             const int t = int(threadIdx.x) - 128;
-            if (t >= 0 && t < STAGES)
+            if (t >= 0 && t < STAGES) // STAGES <= MAX_STAGES <= 64
             {
                 ptx::mbar_init(full_bar(t), 1);
                 ptx::mbar_init(empty_bar(t), 1);
             }
-            else if (t >= 32 && t < 32 + NACC)
+            else if (t >= 64 && t < 64 + NACC)
             {
-                ptx::mbar_init(tfull_bar(t - 32), 1);
-                ptx::mbar_init(tempty_bar(t - 32), 4 * SPLIT);
+                ptx::mbar_init(tfull_bar(t - 64), 1);
+                ptx::mbar_init(tempty_bar(t - 64), 4 * SPLIT);
             }
-            else if (t == 48)
+            else if (t == 80)
                 ptx::mbar_init(bres_bar, 1);
-            else if (t >= 64 && t < 64 + 3 * EPI_WARPS)
-                ptx::mbar_init(sum_bar((t - 64) / 3, (t - 64) % 3), 1);
-            if (t >= 0 && t < 128)
+            else if (t >= 96 && t < 96 + 3 * EPI_WARPS)
+                ptx::mbar_init(sum_bar((t - 96) / 3, (t - 96) % 3), 1);
+            if (t >= 0 && t < 160)
                 ptx::fence_barrier_init();
         }
         if (warp == 0)
@@ -891,8 +891,14 @@ namespace b200
                     else if (j >= 2 && !F_F32)
                     {
                         // the TMA store issued two tiles ago must have finished reading this staging block
+                        PROF_MARK(t_w0);
                         if (ptx::elect_one())
                             asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+#ifdef B200_PROFILE_WAITS
+                        __syncwarp();
+#endif
+                        PROF_MARK(t_w1);
+                        PROF_SPAN(10, t_w0, t_w1);
                     }
                     if (tn != staged_tn)
                     {
@@ -1127,6 +1133,7 @@ namespace b200
 #endif
                     }
                     // all of this warp's TMEM reads are done: hand the accumulator back
+                    PROF_MARK(t_tail0);
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (ptx::elect_one())
@@ -1155,6 +1162,8 @@ namespace b200
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
+                    PROF_MARK(t_tail1);
+                    PROF_SPAN(14, t_tail0, t_tail1);
                     ++idx;
                     if (++blk == NBUF)
                     {
@@ -1309,6 +1318,8 @@ namespace b200
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
+        if (p.a_cells && sp.b_resident)
+            sp.stage_bytes = int((LINEAR_A_BYTES + 1023u) / 1024u * 1024u); // a run of 131 cells: 2096 bytes, not a 128 x 64 tile
         if (p.halo)
         {
             if (!sp.b_resident)
@@ -1426,7 +1437,7 @@ namespace b200
         return (t & ~(0xFF | B200_WEIGHTS_U8)) == 0 && ((t & 0xFF) == B200_U8 || (t & 0xFF) == B200_I8);
     }
 
-    static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual)
+    static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual, int64_t k_bytes)
     {
 #ifdef B200_PROFILE_WAITS
         if (const char* f = getenv("B200_FORCE_BN")) // instrumented build only: tile-width experiments
@@ -1440,9 +1451,14 @@ namespace b200
             return 64;
         if (n_out <= 128)
             return 128;
-        // wide outputs: 256-wide tiles halve the A re-reads, but keep enough tiles to fill the SMs
+        // Wide outputs.  Long reductions (>= 1024 bytes of K per output) are bound by operand delivery from L2: a 256-wide
+        // tile moves 48 KB per 128 x 256 x 128 block where two 128-wide tiles move 64 KB, which outweighs a poorer spread over
+        // the SMs (measured on the 14x14 and 7x7 layers of a ResNet-50 at batch 128: 25 -> 18 us for 3x3 512 -> 512).  Short
+        // reductions are bound by the epilogue: two 128-wide tiles keep two warp groups on different tiles, whose waits interleave.
         int64_t tiles256 = tiles_m * ((n_out + 255) / 256);
-        int bn = (tiles256 >= 2 * num_sms() && n_out % 256 == 0) ? 256 : 128;
+        int bn = 128;
+        if (n_out % 256 == 0)
+            bn = k_bytes >= 1024 ? 256 : (k_bytes > 128 && tiles256 >= 2 * num_sms()) ? 256 : 128;
         // a residual takes a third staging buffer: with 48 KB stages only two would be left
         if (bn == 256 && bk == 128 && residual)
             bn = 128;
@@ -1555,7 +1571,7 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
     p.ntaps = 1;
     p.cblocks = int((K + bk - 1) / bk);
     p.tiles_m = int((M + BM - 1) / BM);
-    const int bn = pick_bn(N, p.tiles_m, bk, epilogue && epilogue->sum_in);
+    const int bn = pick_bn(N, p.tiles_m, bk, epilogue && epilogue->sum_in, K);
     p.tiles_n = int((N + bn - 1) / bn);
     p.conv = 0;
     fill_epilogue(p, epilogue, out, a_type);
@@ -1740,7 +1756,7 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
         const int64_t tiles_h = ((Q + TWh - 1) / TWh) * ((P + THh - 1) / THh) * c->N;
         const int64_t tiles_n = int64_t(p.tiles_q = int((Q + p.TW - 1) / p.TW)) * ((P + p.TH - 1) / p.TH) * ((c->N + p.TN - 1) / p.TN);
         // the weights must stay resident: one column tile, all taps and channel blocks within the resident budget
-        const int bn_h = pick_bn(c->K, tiles_h, bk, epilogue && epilogue->sum_in);
+        const int bn_h = pick_bn(c->K, tiles_h, bk, epilogue && epilogue->sum_in, c->R * c->S * c->C);
         const bool weights_fit = bn_h >= c->K && c->R * c->S * c->C * int64_t(bn_h) <= B_RESIDENT_MAX;
         if (!no_halo && sh == 1 && sw == 1 && c->dilation_h == 1 && c->dilation_w == 1 && c->R * c->S > 1 && c->S <= 8 && weights_fit &&
             c->C <= 128 && tiles_h * 10 <= tiles_n * 13)
@@ -1765,7 +1781,7 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((c->N + p.TN - 1) / p.TN);
-    const int bn = pick_bn(c->K, p.tiles_m, bk, epilogue && epilogue->sum_in);
+    const int bn = pick_bn(c->K, p.tiles_m, bk, epilogue && epilogue->sum_in, c->R * c->S * c->C);
     p.tiles_n = int((c->K + bn - 1) / bn);
     fill_epilogue(p, epilogue, out, data_type);
     p.idesc = make_idesc(data_type, bn);
@@ -1902,7 +1918,7 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     p.tiles_q = int((Q + p.TW - 1) / p.TW);
     p.tiles_p = int((P + p.TH - 1) / p.TH);
     p.tiles_m = p.tiles_q * p.tiles_p * int((N + p.TN - 1) / p.TN);
-    const int bn = pick_bn(K, p.tiles_m, bk, epilogue && epilogue->sum_in);
+    const int bn = pick_bn(K, p.tiles_m, bk, epilogue && epilogue->sum_in, Rc * 64);
     p.tiles_n = int((K + bn - 1) / bn);
     fill_epilogue(p, epilogue, out, data_type);
     p.idesc = make_idesc(data_type, bn);

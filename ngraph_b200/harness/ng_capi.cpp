@@ -53,11 +53,12 @@ namespace
     {
         Strides strides, dilation;
         CoordinateDiff below, above;
+        Strides data_dilation;
     };
-    Geom geom_of(const int64_t* g) // stride h,w, dilation h,w, below h,w, above h,w
+    Geom geom_of(const int64_t* g) // stride h,w, dilation h,w, below h,w, above h,w, data dilation h,w
     {
         return Geom{Strides{size_t(g[0]), size_t(g[1])}, Strides{size_t(g[2]), size_t(g[3])},
-                    CoordinateDiff{g[4], g[5]}, CoordinateDiff{g[6], g[7]}};
+                    CoordinateDiff{g[4], g[5]}, CoordinateDiff{g[6], g[7]}, Strides{size_t(g[8]), size_t(g[9])}};
     }
 
     template <typename F>
@@ -159,7 +160,7 @@ NGC_API void* ngc_quantized_conv(void* data, void* filt, const int64_t* g, void*
     return guarded([&]() -> void* {
         Geom gg = geom_of(g);
         return box(std::make_shared<op::v0::QuantizedConvolution>(val(data), val(filt), gg.strides, gg.dilation, gg.below,
-                                                                  gg.above, Strides{1, 1}, val(si), val(zi), val(sf), val(zf),
+                                                                  gg.above, gg.data_dilation, val(si), val(zi), val(sf), val(zf),
                                                                   val(so), val(zo), et_of(out_et)));
     }, nullptr);
 }
@@ -169,7 +170,7 @@ NGC_API void* ngc_quantized_conv_bias(void* data, void* filt, void* bias, const 
     return guarded([&]() -> void* {
         Geom gg = geom_of(g);
         return box(std::make_shared<op::v0::QuantizedConvolutionBias>(val(data), val(filt), val(bias), gg.strides, gg.dilation,
-                                                                      gg.below, gg.above, Strides{1, 1}, val(scale), relu != 0));
+                                                                      gg.below, gg.above, gg.data_dilation, val(scale), relu != 0));
     }, nullptr);
 }
 
@@ -180,10 +181,10 @@ NGC_API void* ngc_quantized_conv_bias_add(void* data, void* filt, void* bias, vo
         Geom gg = geom_of(g);
         if (signed_add)
             return box(std::make_shared<op::v0::QuantizedConvolutionBiasSignedAdd>(
-                val(data), val(filt), val(bias), val(sum), gg.strides, gg.dilation, gg.below, gg.above, Strides{1, 1},
+                val(data), val(filt), val(bias), val(sum), gg.strides, gg.dilation, gg.below, gg.above, gg.data_dilation,
                 val(scale), val(sum_scale), relu != 0));
         return box(std::make_shared<op::v0::QuantizedConvolutionBiasAdd>(val(data), val(filt), val(bias), val(sum), gg.strides,
-                                                                         gg.dilation, gg.below, gg.above, Strides{1, 1},
+                                                                         gg.dilation, gg.below, gg.above, gg.data_dilation,
                                                                          val(scale), val(sum_scale), relu != 0));
     }, nullptr);
 }
@@ -193,7 +194,7 @@ NGC_API void* ngc_quantized_conv_relu(void* data, void* filt, const int64_t* g, 
     return guarded([&]() -> void* {
         Geom gg = geom_of(g);
         return box(std::make_shared<op::v0::QuantizedConvolutionRelu>(val(data), val(filt), gg.strides, gg.dilation, gg.below,
-                                                                      gg.above, Strides{1, 1}, val(scale)));
+                                                                      gg.above, gg.data_dilation, val(scale)));
     }, nullptr);
 }
 
@@ -202,7 +203,7 @@ NGC_API void* ngc_convolution(void* data, void* filt, const int64_t* g)
     return guarded([&]() -> void* {
         Geom gg = geom_of(g);
         return box(std::make_shared<op::v0::Convolution>(val(data), val(filt), gg.strides, gg.dilation, gg.below, gg.above,
-                                                         Strides{1, 1}));
+                                                         gg.data_dilation));
     }, nullptr);
 }
 

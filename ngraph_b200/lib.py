@@ -92,6 +92,7 @@ def _load():
         "b200_stem_pack_input_f32": (ci, [vp, vp, vp, ci, ci, vp] + [i64] * 10 + [vp]),
         "b200_qconv_stem": (ci, [vp, ci, vp, vp] + [i64] * 10 + [ctypes.POINTER(Epilogue), vp]),
         "b200_selftest_bounded_wait": (ci, [i64, vp]),
+        "b200_dilate_crop_nhwc_u8": (ci, [vp, vp] + [i64] * 10 + [vp]),
         "b200_avgpool_f32_nchw": (ci, [vp, vp, ctypes.POINTER(PoolParams), vp]),
         "b200_avgpool_nhwc_bytes": (ci, [vp, vp, ci, ctypes.POINTER(PoolParams), vp]),
         "b200_avgpool_q_nhwc": (ci, [vp, ci, vp, ci, vp, vp, ctypes.POINTER(PoolParams), vp]),

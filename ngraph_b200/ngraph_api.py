@@ -169,44 +169,44 @@ def quantized_dot_bias(x, w, bias, scale, requantize=True, relu=False):
     return Value(capi().ngc_quantized_dot_bias(x.h, w.h, bias.h, scale.h, int(requantize), int(relu)), "QuantizedDotBias")
 
 
-def _geom(stride, dilation, below, above):
+def _geom(stride, dilation, below, above, data_dilation=(1, 1)):
     above = below if above is None else above
-    return _i64(list(stride) + list(dilation) + list(below) + list(above))
+    return _i64(list(stride) + list(dilation) + list(below) + list(above) + list(data_dilation))
 
 
 def quantized_convolution(data, filt, sd, zd, sf, zf, so, zo, out_dtype, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0),
-                          pad_above=None):
+                          pad_above=None, data_dilation=(1, 1)):
     f = np.float32
     filt = _val(filt)
     c = [_val(np.array(sd, f)), _val(np.array(zd, data.dtype)), _val(np.array(sf, f)), _val(np.array(zf, filt.dtype)),
          _val(np.array(so, f)), _val(np.array(zo, out_dtype))]
-    return Value(capi().ngc_quantized_conv(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above), c[0].h, c[1].h, c[2].h,
+    return Value(capi().ngc_quantized_conv(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above, data_dilation), c[0].h, c[1].h, c[2].h,
                                            c[3].h, c[4].h, c[5].h, ET[np.dtype(out_dtype)]), "QuantizedConvolution")
 
 
-def quantized_conv_bias(data, filt, bias, scale, relu=False, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None):
+def quantized_conv_bias(data, filt, bias, scale, relu=False, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None, data_dilation=(1, 1)):
     filt, bias, scale = _val(filt), _val(bias), _val(scale, np.float32)
-    return Value(capi().ngc_quantized_conv_bias(data.h, filt.h, bias.h, _geom(stride, dilation, pad_below, pad_above), scale.h,
+    return Value(capi().ngc_quantized_conv_bias(data.h, filt.h, bias.h, _geom(stride, dilation, pad_below, pad_above, data_dilation), scale.h,
                                                 int(relu)), "QuantizedConvolutionBias")
 
 
 def quantized_conv_bias_add(data, filt, bias, sum_in, scale, sum_scale, relu=True, signed=False, stride=(1, 1), dilation=(1, 1),
-                            pad_below=(0, 0), pad_above=None):
+                            pad_below=(0, 0), pad_above=None, data_dilation=(1, 1)):
     filt, bias, scale, sum_scale = _val(filt), _val(bias), _val(scale, np.float32), _val(sum_scale, np.float32)
-    return Value(capi().ngc_quantized_conv_bias_add(data.h, filt.h, bias.h, sum_in.h, _geom(stride, dilation, pad_below, pad_above),
+    return Value(capi().ngc_quantized_conv_bias_add(data.h, filt.h, bias.h, sum_in.h, _geom(stride, dilation, pad_below, pad_above, data_dilation),
                                                     scale.h, sum_scale.h, int(relu), int(signed)),
                  "QuantizedConvolutionBias(Signed)Add")
 
 
-def quantized_conv_relu(data, filt, scale, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None):
+def quantized_conv_relu(data, filt, scale, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None, data_dilation=(1, 1)):
     filt, scale = _val(filt), _val(scale, np.float32)
-    return Value(capi().ngc_quantized_conv_relu(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above), scale.h),
+    return Value(capi().ngc_quantized_conv_relu(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above, data_dilation), scale.h),
                  "QuantizedConvolutionRelu")
 
 
-def convolution(data, filt, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None):
+def convolution(data, filt, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None, data_dilation=(1, 1)):
     filt = _val(filt)
-    return Value(capi().ngc_convolution(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above)), "Convolution")
+    return Value(capi().ngc_convolution(data.h, filt.h, _geom(stride, dilation, pad_below, pad_above, data_dilation)), "Convolution")
 
 
 def max_pool(x, window, stride, pad_below=(0, 0), pad_above=None, ceil_mode=False):

@@ -50,14 +50,14 @@ def _tail(acc, bias, scale, chan_axis, out_dtype, relu, sum_in=None, sum_scale=N
 
 
 def decomposed_conv(data, filt, bias, scale, out_dtype, relu, stride=(1, 1), dilation=(1, 1), pad_below=(0, 0), pad_above=None,
-                    sum_in=None, sum_scale=None, signed=False):
+                    sum_in=None, sum_scale=None, signed=False, data_dilation=(1, 1)):
     """Oracle graph of QuantizedConvolutionBias / Relu / BiasAdd / BiasSignedAdd (bias may be None)."""
     if np.dtype(data.dtype) == np.uint8:
-        acc = ng.quantized_convolution(data, filt, 1.0, 0, 1.0, 0, 1.0, 0, np.int32, stride, dilation, pad_below, pad_above)
+        acc = ng.quantized_convolution(data, filt, 1.0, 0, 1.0, 0, 1.0, 0, np.int32, stride, dilation, pad_below, pad_above, data_dilation)
     else:
         # i8 activations: INTERPRETER's QuantizedConvolution takes u8 data only, its plain Convolution on
         # i32 (reference::convolution<int32_t>, same loop nest) gives the same exact accumulators
-        acc = ng.convolution(ng.convert(data, np.int32), ng.convert(filt, np.int32), stride, dilation, pad_below, pad_above)
+        acc = ng.convolution(ng.convert(data, np.int32), ng.convert(filt, np.int32), stride, dilation, pad_below, pad_above, data_dilation)
     y = _tail(acc, bias, scale, 1, np.int8 if signed else out_dtype, relu, sum_in, sum_scale)
     return ng.convert(y, np.uint8) if signed and np.dtype(out_dtype) == np.uint8 else y
 
