@@ -129,6 +129,7 @@ namespace b200
     constexpr int CHUNKS = COLS / 32;
     constexpr int MAX_ACC = 8;       // accumulator buffers in TMEM: 512 columns / BN
     constexpr uint32_t LINEAR_A_BYTES = (128 + 3) * 16; // stem: 128 windows of 4 cells = a run of 131 cells
+    constexpr uint32_t LINEAR_A_PITCH = 2112;           // distance between the runs of two taps inside one pipeline stage
     constexpr int64_t STEM_CELLS_SLACK = 2112;          // bytes a run may reach past the last cell of the grid
     constexpr int SMEM_LIMIT = 232448 - 9216; // 227 KB per CTA less the kernel's static shared variables (up to 8 KB + 16 B)
 
@@ -531,7 +532,8 @@ namespace b200
                 }
             }
             // pipeline stages one tile consumes: one per (tap, channel block), or one per channel block in halo mode
-            const int nkb = p.halo ? p.cblocks : p.ntaps * p.cblocks;
+            // (the stem's cell runs: every tap of a tile in ONE stage - per-stage bookkeeping, not bytes, bounds that path)
+            const int nkb = p.halo ? p.cblocks : p.a_cells ? 1 : p.ntaps * p.cblocks;
             int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
             int idx = 32;
             // this producer's next k-block, as (offset inside the current tile, pipeline stage, stage parity); it advances
@@ -573,7 +575,7 @@ namespace b200
                     // packed weights: this column tile's 64-row blocks of a k-block are one contiguous piece
                     const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
                     const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
-                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES)) + b_bytes;
+                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES * uint32_t(p.ntaps) : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES)) + b_bytes;
                     int tap = 0, cb = j; // k-block j of the tile = (tap, channel block)
                     while (cb >= p.cblocks)
                     {
@@ -602,9 +604,13 @@ namespace b200
                         }
                         else if (p.a_cells)
                         {
-                            // 128 output pixels of one output row need cells q0 .. q0+130 of cell row p0 + tap: one run
-                            const size_t cell = (size_t(n0) * p.cells_h + size_t(p0 + tp.dh)) * p.cells_w + size_t(q0);
-                            ptx::bulk_load(a_dst, p.a_cells + cell * 16, LINEAR_A_BYTES, full_bar(s));
+                            // 128 output pixels of one output row need cells q0 .. q0+130 of cell rows p0 + tap: one run per tap,
+                            // all of them in this stage
+                            for (int t = 0; t < p.ntaps; ++t)
+                            {
+                                const size_t cell = (size_t(n0) * p.cells_h + size_t(p0 + p.taps[t].dh)) * p.cells_w + size_t(q0);
+                                ptx::bulk_load(a_dst + uint32_t(t) * LINEAR_A_PITCH, p.a_cells + cell * 16, LINEAR_A_BYTES, full_bar(s));
+                            }
                         }
                         else if (p.conv)
                             ptx::tma_load_4d(a_dst, &maps.a[tp.map], full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
@@ -716,6 +722,38 @@ namespace b200
                         }
                         if (fail)
                             break;
+                        ptx::mma_commit(tfull_bar(acc));
+                        continue;
+                    }
+                    if (p.a_cells)
+                    {
+                        // one stage holds the cell runs of every tap of the tile (weights resident): one wait, ntaps * BK / 32
+                        // instructions, one commit
+                        {
+                            PROF_T0();
+                            if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
+                            {
+                                fail = 2002;
+                                break;
+                            }
+                            PROF_ADD(1);
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint64_t a_stage = a_desc0 + uint64_t(s) * (stage_bytes >> 4);
+                        for (int tap = 0; tap < p.ntaps; ++tap)
+                        {
+                            const uint64_t a_desc = a_stage + uint64_t(tap) * (LINEAR_A_PITCH >> 4);
+                            const uint64_t b_desc = b_desc0 + uint64_t(tap) * b_step;
+#pragma unroll
+                            for (int k = 0; k < BK / 32; ++k)
+                                ptx::mma_i8(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc, (tap | k) != 0 ? 1u : 0u);
+                        }
+                        ptx::mma_commit(empty_bar(s));
+                        if (++s == STAGES)
+                        {
+                            s = 0;
+                            ph ^= 1;
+                        }
                         ptx::mma_commit(tfull_bar(acc));
                         continue;
                     }
@@ -1318,8 +1356,12 @@ namespace b200
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
-        if (p.a_cells && sp.b_resident)
-            sp.stage_bytes = int((LINEAR_A_BYTES + 1023u) / 1024u * 1024u); // a run of 131 cells: 2096 bytes, not a 128 x 64 tile
+        if (p.a_cells)
+        {
+            if (!sp.b_resident)
+                return B200_ERR_UNSUPPORTED; // the caller takes the window path when the filters do not stay in shared memory
+            sp.stage_bytes = int((uint32_t(p.ntaps) * LINEAR_A_PITCH + 1023u) / 1024u * 1024u); // one 2096-byte cell run per tap
+        }
         if (p.halo)
         {
             if (!sp.b_resident)
@@ -1350,7 +1392,11 @@ namespace b200
         // Programmatic dependent launch: the CTAs of this launch may become resident while the previous kernel of the
         // stream drains (SM by SM), set up their barriers, tensor memory and descriptors, and then wait in
         // griddepcontrol.wait for that kernel's completion and memory flush before touching global memory.
-        static const bool pdl = getenv("B200_NO_PDL") == nullptr;
+#ifdef B200_PROFILE_WAITS
+        static const bool pdl = getenv("B200_NO_PDL") == nullptr; // instrumented build only
+#else
+        const bool pdl = true;
+#endif
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(unsigned(grid));
@@ -1750,7 +1796,11 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     // rows of 32 positions of which the first 32-(S-1) are output pixels; its input patch, halo included, is loaded ONCE
     // per channel block and every tap reads it through a row-shifted descriptor, instead of one displaced copy per tap.
     // It pays when operand delivery bounds the layer (few channels: short TMA box rows) and the wasted positions are few.
-    static const bool no_halo = getenv("B200_NO_HALO") != nullptr;
+#ifdef B200_PROFILE_WAITS
+    static const bool no_halo = getenv("B200_NO_HALO") != nullptr; // instrumented build only
+#else
+    const bool no_halo = false;
+#endif
     {
         const int64_t RW = 32, TWh = RW - (c->S - 1), THh = 4;
         const int64_t tiles_h = ((Q + TWh - 1) / TWh) * ((P + THh - 1) / THh) * c->N;
@@ -1900,8 +1950,13 @@ extern "C" int b200_qconv_stem(const void* cells, int data_type, const int8_t* p
     // Wide outputs: a tile is 128 consecutive pixels of one output row and its A operand is a linear run of cells
     // read as overlapping windows (one bulk copy per tap instead of 128 box rows).  Narrow outputs would waste most
     // of such a tile and take tensor-map windows over a 2-D/3-D patch instead.
-    static const bool windows_only = getenv("B200_STEM_WINDOWS") != nullptr;
-    const bool linear = Q >= 64 && !windows_only;
+#ifdef B200_PROFILE_WAITS
+    static const bool windows_only = getenv("B200_STEM_WINDOWS") != nullptr; // instrumented build only
+#else
+    const bool windows_only = false;
+#endif
+    // the cell-run path keeps the filters resident in shared memory: one column tile, all taps within the resident budget
+    const bool linear = Q >= 64 && K <= 128 && Rc * 128 * 64 <= B_RESIDENT_MAX && !windows_only;
     if (linear)
     {
         p.TW = 128;

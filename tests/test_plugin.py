@@ -483,3 +483,31 @@ def test_api_contract(backends):
     exe2.call([good_out], [good_in])
     names = [n for n, us, calls in exe2.performance_data()]
     assert any(n.startswith("Quantize") for n in names)
+
+
+@pytest.mark.gpu
+@needs_ngraph
+@pytest.mark.parametrize("data_dilation,pad_below,pad_above,stride,dilation",
+                         [((2, 2), (1, 1), (1, 1), (1, 1), (1, 1)),     # zero pixels between neighbours
+                          ((1, 1), (-1, -2), (0, -1), (1, 1), (1, 1)),   # negative padding crops the input
+                          ((2, 3), (-1, 0), (2, -2), (2, 1), (1, 1)),    # both, with a stride
+                          ((3, 2), (2, 2), (-3, 1), (1, 1), (2, 1))])    # and with a dilated window
+def test_convolution_data_dilation_and_negative_padding(backends, data_dilation, pad_below, pad_above, stride, dilation):
+    """legal in every convolution op (reference::general_convolution walks the dilated, signed-padded input and skips what is
+    not a source coordinate, convolution.hpp:59-265): QuantizedConvolution -> i32 and the fused QuantizedConvolutionBias+Relu"""
+    rng = np.random.default_rng(21)
+    ds, fs = (2, 64, 9, 11), (32, 64, 3, 3)
+    data = rng.integers(0, 256, size=ds).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=fs).astype(np.int8)
+    geometry = dict(stride=stride, dilation=dilation, pad_below=pad_below, pad_above=pad_above, data_dilation=data_dilation)
+    d = ng.parameter(np.uint8, ds)
+    core = ng.Function([ng.quantized_convolution(d, ng.constant(filt), 1.0, 0, 1.0, 0, 1.0, 0, np.int32, **geometry)], [d])
+    got, exp = run_both(backends, core, core, [data])
+    same_bits(got[0], exp[0], "core")
+    assert np.abs(exp[0]).max() > 0
+    bias = rng.integers(-500, 500, size=32).astype(np.int32)
+    scale = (np.exp(rng.uniform(-0.5, 0.5, size=32)) * 2e-4).astype(np.float32)
+    fused = ng.Function([ng.quantized_conv_bias(d, filt, bias, scale, True, **geometry)], [d])
+    plain = ng.Function([interpreter.decomposed_conv(d, ng.constant(filt), ng.constant(bias), ng.constant(scale), np.uint8, True, **geometry)], [d])
+    got, exp = run_both(backends, fused, plain, [data])
+    same_bits(got[0], exp[0], "fused")
