@@ -187,8 +187,9 @@ class ResNet50:
     name, metric, unit = "resnet50", "int8 ResNet-50 v1.5 inference throughput", "img/s"
     dtype, bound = "u8*i8->i32 (f32 in, f32 logits out)", "tensor"
 
-    def __init__(self, batch=128):
+    def __init__(self, batch=128, pipeline=2):
         self.batch = batch
+        self.pipeline = pipeline
         self.model = None
 
     def describe(self, world=1):
@@ -197,6 +198,9 @@ class ResNet50:
                 "batch_per_gpu": self.batch, "global_batch": self.batch * world, "input": "f32 NCHW [B,3,224,224] normalised",
                 "weights": "random He-normal, per-channel i8; activation scales from a seeded 8-image calibration",
                 "parallelism": "batch-sharded replicas, outputs gathered with NCCL all_gather",
+                "pipeline_depth": self.pipeline,
+                "pipeline": "two executables of the same Function on two CUDA streams, steps alternate between them: two batches "
+                            "in flight per GPU" if self.pipeline == 2 else "one executable, one stream",
                 "l2": "per-step activation working set (~2 GB) >> 126 MB L2"}
 
     def build_model(self):
@@ -219,9 +223,26 @@ class ResNet50:
         x = synthetic_images(min(self.batch, 16), 100 + rank)
         x = np.tile(x, ((self.batch + x.shape[0] - 1) // x.shape[0], 1, 1, 1))[:self.batch]
         self.x_dev = torch.from_numpy(x).cuda()
-        self.logits = torch.empty((self.batch, model.classes), dtype=torch.float32, device="cuda")
+        # two result buffers: with several GPUs the gather of step i runs on a stream of its own beside step i + 1
+        self.logits2 = [torch.empty((self.batch, model.classes), dtype=torch.float32, device="cuda") for _ in range(2)]
+        self.t_out2 = [self.backend.create_tensor(np.float32, tuple(b.shape), b.data_ptr()) for b in self.logits2]
+        self.logits, self.t_out = self.logits2[0], self.t_out2[0]
         self.t_in = self.backend.create_tensor(np.float32, x.shape, self.x_dev.data_ptr())
-        self.t_out = self.backend.create_tensor(np.float32, tuple(self.logits.shape), self.logits.data_ptr())
+        self.gather_stream = torch.cuda.Stream() if world > 1 else None
+        self.step_i = 0
+        self.logits_read = [None, None]
+        # Pipeline depth 2, on the client side and through the public API only: a second Backend on a second CUDA stream
+        # compiles the same Function, and the timed steps alternate between the two executables, so that two batches are in
+        # flight and the tail of one batch's kernels overlaps the head of the other's (what nGraph's own nbench does with
+        # --double_buffer for the copies).  Every step is still one [B,3,224,224] batch through the unchanged graph.
+        self.lane_streams = [torch.cuda.current_stream(), torch.cuda.Stream()] if self.pipeline == 2 else [torch.cuda.current_stream()]
+        self.lane_exe, self.lane_in, self.lane_out, self.lane_backends = [self.exe], [self.t_in], [self.t_out2[0]], [self.backend]
+        if self.pipeline == 2:
+            b2 = ng.Backend("B200:%d,stream=%d" % (local_rank, self.lane_streams[1].cuda_stream))
+            self.lane_backends.append(b2)
+            self.lane_exe.append(b2.compile(self.fn))
+            self.lane_in.append(b2.create_tensor(np.float32, x.shape, self.x_dev.data_ptr()))  # the same resident input, read only
+            self.lane_out.append(b2.create_tensor(np.float32, tuple(self.logits2[1].shape), self.logits2[1].data_ptr()))
         # end-to-end loop: two input tensors, so that Tensor::write of the next batch (copy stream) overlaps the
         # kernels of the current one; the pipelined-tensor pattern of nGraph's own nbench
         self.x_pipe = [torch.empty_like(self.x_dev) for _ in range(2)]
@@ -235,10 +256,42 @@ class ResNet50:
     def units_per_step(self):
         return float(self.batch)
 
+    def _gather_beside_next_step(self, logits, producer_stream=None):
+        """the one collective of the path (NCCL all_gather of this step's logits), on its own stream, ordered after the
+        kernels that produced them; the next step's kernels do not wait for it"""
+        torch = self.torch
+        done = torch.cuda.Event()
+        done.record(producer_stream if producer_stream is not None else torch.cuda.current_stream())
+        with torch.cuda.stream(self.gather_stream):
+            self.gather_stream.wait_event(done)
+            self.sharding.gather_rows(logits, [self.batch] * self.world, out=self.gathered)
+            read = torch.cuda.Event()
+            read.record()
+        return read  # the buffer may be written again after this event
+
     def step(self):
-        self.exe.call([self.t_out], [self.t_in], validate=False)
+        k = self.step_i & 1
+        self.step_i += 1
+        lane = k if self.pipeline == 2 else 0
+        st = self.lane_streams[lane]
+        if self.gathered is not None and self.logits_read[k] is not None:
+            st.wait_event(self.logits_read[k])  # the gather of two steps ago has read this buffer
+        out = self.lane_out[lane] if self.pipeline == 2 else self.t_out2[k]
+        self.lane_exe[lane].call([out], [self.lane_in[lane]], validate=False)
         if self.gathered is not None:
-            self.sharding.gather_rows(self.logits, [self.batch] * self.world, out=self.gathered)
+            self.logits_read[k] = self._gather_beside_next_step(self.logits2[k], st)
+
+    def begin(self):
+        """the second lane starts no earlier than the timed region's opening event on the first"""
+        for st in self.lane_streams[1:]:
+            st.wait_stream(self.lane_streams[0])
+
+    def finish(self):
+        """joins the second lane and the gather stream: the timed region ends when the last steps' logits are there"""
+        for st in self.lane_streams[1:]:
+            self.torch.cuda.current_stream().wait_stream(st)
+        if self.gather_stream is not None:
+            self.torch.cuda.current_stream().wait_stream(self.gather_stream)
 
     def step_e2e(self):
         """One batch end to end through the plugin's public API: Tensor::write of the batch (pinned host memory),
@@ -256,9 +309,11 @@ class ResNet50:
             self.e2e_primed = True
         # the other tensor is free: the call that read it was waited for by the previous step's read
         pending = self.writer.submit(self.t_pipe[cur ^ 1].write_ptr, self.pin_in.data_ptr(), nbytes)
+        if self.gathered is not None and self.logits_read[0] is not None:
+            self.torch.cuda.current_stream().wait_event(self.logits_read[0])
         self.exe.call([self.t_out], [self.t_pipe[cur]], validate=False)
         if self.gathered is not None:
-            self.sharding.gather_rows(self.logits, [self.batch] * self.world, out=self.gathered)
+            self.logits_read[0] = self._gather_beside_next_step(self.logits)
         self.t_out.read_ptr(self.pin_out.data_ptr(), self.pin_out.numel() * 4)
         pending.result()
         self.e2e_i += 1
@@ -342,7 +397,7 @@ class ResNet50:
 
 
 class BertEncoder:
-    """BASELINE config 5: the int8 BERT-base-shaped encoder as an nGraph Function through the plugin.  The int8 dots are the
+    """The int8 BERT-base-shaped encoder (12 layers, hidden 768, 12 heads, FFN 3072, seq 384, batch 64) as an nGraph Function through the plugin.  The int8 dots are the
     QuantizedDotBias layers; everything between them (dynamic activation scales, attention products, softmax, LayerNorm,
     GELU) is f32 glue that keeps the reference kernels' arithmetic."""
     name, metric, unit = "bert", "int8 BERT-base-shaped encoder inference throughput", "tokens/s"
@@ -486,7 +541,7 @@ class QConvLayer(MicroWorkload):
     name, metric, unit, dtype = "qconv", "QuantizedConvolutionBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
 
     def __init__(self, batch=32):
-        # BASELINE's layer by default; B200_BENCH_CONV="C,K,R,HW[,sum]" times another ResNet layer shape (stride 1,
+        # the 3x3 64 -> 64 channel layer on 56x56 images by default; B200_BENCH_CONV="C,K,R,HW[,sum]" times another ResNet layer shape (stride 1,
         # same padding); a fifth field 1 adds a u8 residual input (QuantizedConvolutionBiasAdd)
         f = [int(v) for v in os.environ.get("B200_BENCH_CONV", "64,64,3,56").split(",")]
         c, k, r, hw = f[:4]
@@ -607,7 +662,7 @@ class QDotLayer(MicroWorkload):
             self.pin_in = torch.from_numpy(self.h_a).pin_memory()
             self.pin_out = torch.empty((self.M, self.N), dtype=torch.uint8).pin_memory()
         self.i = 0
-        # A launch of the small problems (BASELINE's own M = 256 is 0.5 GOP) is shorter than the host needs to issue it,
+        # A launch of the small problems (M = 256 is 0.5 GOP) is shorter than the host needs to issue it,
         # so those are timed as a CUDA graph of back-to-back launches, replayed once per step.
         self.graph, self.per_step = None, 1
         if self.M <= 8192:
@@ -830,6 +885,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (images / rows); for small profiler captures")
+    ap.add_argument("--pipeline", type=int, default=2, choices=[1, 2], help="resnet50: batches in flight per GPU (2 = two "
+                    "executables on two streams, steps alternate; 1 = one executable on one stream)")
     ap.add_argument("--no-per-config", action="store_true", help="skip the short per-workload block of the default run")
     ap.add_argument("--no-peak-probe", action="store_true", help="skip the in-run int8 GEMM peak measurement (profiler captures)")
     args = ap.parse_args()
@@ -839,6 +896,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     wl = WORKLOADS[args.workload](args.batch) if args.batch else WORKLOADS[args.workload]()
+    if isinstance(wl, ResNet50):
+        wl.pipeline = args.pipeline
 
     if args.impl == "reference":
         run_reference(args, wl, rank)
@@ -885,8 +944,12 @@ def main():
     barrier()
     t0 = time.time()
     ev0.record()
+    if hasattr(wl, "begin"):
+        wl.begin()
     for _ in range(args.steps):
         wl.step()
+    if hasattr(wl, "finish"):
+        wl.finish()
     ev1.record()
     barrier()
     t1 = time.time()
@@ -894,6 +957,23 @@ def main():
     if hasattr(wl, "launches_per_step") and wl.launches_per_step() > 1:
         launches = args.steps * wl.launches_per_step()  # replayed from a CUDA graph: the host-side counter does not see them
     ms = ev0.elapsed_time(ev1)
+
+    # the same steps without the pipelining (one executable, one stream), for comparison
+    ms_single = None
+    if isinstance(wl, ResNet50) and wl.pipeline == 2:
+        wl.pipeline = 1
+        for _ in range(3):
+            wl.step()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            wl.step()
+        wl.finish()
+        s1.record()
+        barrier()
+        ms_single = s0.elapsed_time(s1)
+        wl.pipeline = 2
 
     # end to end: pinned host -> device, kernels, device -> pinned host, every step
     for _ in range(2):
@@ -903,6 +983,8 @@ def main():
     e0.record()
     for _ in range(args.steps):
         wl.step_e2e()
+    if hasattr(wl, "finish"):
+        wl.finish()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
@@ -927,10 +1009,11 @@ def main():
         h2d_floor_gbs = h2d_bytes * 10 / (c0.elapsed_time(c1) * 1e-3) / 1e9
         del src, dst
 
-    t = torch.tensor([ms, ms_e2e, -(h2d_floor_gbs or 0.0)], dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms, ms_e2e, -(h2d_floor_gbs or 0.0), ms_single or 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
+    ms_single = float(t[3]) if ms_single else None
     h2d_floor_gbs = -float(t[2]) if h2d_floor_gbs else None  # the slowest rank's copy rate
 
     if rank == 0:
@@ -951,6 +1034,9 @@ def main():
                 "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(world),
                 "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": wl.roofline(peaks, per_step, probe)}
+        if ms_single:
+            line["single_stream"] = {"ms_per_step": ms_single / args.steps, "value": wl.units_per_step() * world / (ms_single / args.steps / 1e3),
+                                     "unit": wl.unit, "note": "one executable on one stream (pipeline depth 1), same steps"}
         if isinstance(wl, ResNet50) and world == 1 and not args.no_per_config:
             line["per_config"] = per_config_block(torch, peaks, probe)
         cpu, ok = wl.check_and_cpu_baseline(args.no_cpu_baseline or world > 1)

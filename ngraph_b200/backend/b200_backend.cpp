@@ -679,7 +679,8 @@ B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
                                const std::shared_ptr<Function>& func,
                                bool enable_performance_data,
                                std::vector<char>* saved_constants,
-                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index)
+                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index,
+                               const std::vector<std::shared_ptr<Node>>* saved_order)
     : m_ctx(ctx)
     , m_perf(enable_performance_data)
 {
@@ -700,6 +701,13 @@ B200Executable::B200Executable(const std::shared_ptr<DeviceContext>& ctx,
         run_graph_passes(m_function);
     }
 
+    if (saved_order)
+    {
+        // Backend::load: the positions the saved constant keys count in are those of the saved node order
+        for (size_t position = 0; position < saved_order->size(); ++position)
+            m_node_index[(*saved_order)[position].get()] = position;
+    }
+    else
     {
         size_t position = 0;
         for (auto& node : m_function->get_ordered_ops())
@@ -2181,9 +2189,10 @@ std::shared_ptr<runtime::Executable> B200Backend::load(std::istream& in)
             index[key] = std::make_pair(offset, bytes);
     }
     // nodes are rebuilt in the saved order, which is the order the keys of the index count in
-    std::shared_ptr<Function> function = read_function(model);
+    std::vector<std::shared_ptr<Node>> order;
+    std::shared_ptr<Function> function = read_function(model, &order);
     std::lock_guard<std::mutex> lock(m_mutex);
-    return std::make_shared<B200Executable>(m_ctx, function, false, &constants, &index);
+    return std::make_shared<B200Executable>(m_ctx, function, false, &constants, &index, &order);
 }
 
 std::vector<runtime::PerformanceCounter> B200Executable::get_performance_data() const

@@ -104,7 +104,8 @@ namespace ngraph
                                const std::shared_ptr<Function>& func,
                                bool enable_performance_data,
                                std::vector<char>* saved_constants = nullptr,
-                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index = nullptr);
+                               const std::map<std::string, std::pair<size_t, size_t>>* saved_index = nullptr,
+                               const std::vector<std::shared_ptr<Node>>* saved_order = nullptr);
                 ~B200Executable() override;
                 bool call(const std::vector<std::shared_ptr<runtime::Tensor>>& outputs,
                           const std::vector<std::shared_ptr<runtime::Tensor>>& inputs) override;

@@ -513,7 +513,7 @@ std::string runtime::b200::write_function(const Function& function)
     return w.s;
 }
 
-std::shared_ptr<Function> runtime::b200::read_function(const std::string& bytes)
+std::shared_ptr<Function> runtime::b200::read_function(const std::string& bytes, std::vector<std::shared_ptr<Node>>* nodes_in_saved_order)
 {
     Reader r{bytes.data(), bytes.data() + bytes.size()};
     char magic[8];
@@ -561,5 +561,7 @@ std::shared_ptr<Function> runtime::b200::read_function(const std::string& bytes)
             throw std::runtime_error("B200 saved model: result list names another op");
         results.push_back(res);
     }
+    if (nodes_in_saved_order)
+        *nodes_in_saved_order = nodes;
     return std::make_shared<Function>(results, params);
 }

@@ -7,6 +7,7 @@
 
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "ngraph/function.hpp"
 
@@ -19,7 +20,9 @@ namespace ngraph
             /// Serialises `function`.  Throws ngraph::unsupported_op for an op type outside the plugin's set.
             std::string write_function(const Function& function);
             /// Rebuilds a Function from write_function's output.  Throws std::runtime_error on malformed data.
-            std::shared_ptr<Function> read_function(const std::string& bytes);
+            /// `nodes_in_saved_order`, when given, receives the rebuilt nodes in the order they were written.
+            std::shared_ptr<Function> read_function(const std::string& bytes,
+                                                    std::vector<std::shared_ptr<Node>>* nodes_in_saved_order = nullptr);
             /// FNV-1a of a byte string (identifies a saved model / constant image pair)
             uint64_t fnv1a(const void* data, size_t bytes);
         }

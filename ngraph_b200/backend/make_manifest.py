@@ -21,7 +21,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    from ngraph_b200.build import ngraph_checkout
+    ap.add_argument("--ref", default=ngraph_checkout(), help="root of the nGraph checkout (default: $NGRAPH_REF or the reference build recipe's)")
     a = ap.parse_args()
     verified = {c["name"] for c in json.load(open(os.path.join(ROOT, "tests", "golden", "reference_tests.json")))}
     per_file = {}

@@ -55,12 +55,30 @@ PLUGIN_LIB = os.path.join(HERE, "libb200_backend.so")
 NGRAPH_LIB_DIR = os.path.join(ROOT, "oracle", "_ref", "lib")
 
 
-def ngraph_include_dir():
-    """nGraph's public headers (the plugin compiles against them, like every nGraph backend)."""
-    for d in (os.environ.get("NGRAPH_SRC", ""), "/root/reference/src"):
-        if d and os.path.exists(os.path.join(d, "ngraph", "runtime", "backend.hpp")):
+def ngraph_checkout():
+    """Root of the nGraph source tree, or None: $NGRAPH_REF, else the default the reference build recipe names
+    (`REF ?= ...` in oracle/Makefile.ngraph, the one place that default is written down)."""
+    cands = [os.environ.get("NGRAPH_REF", "")]
+    try:
+        for line in open(os.path.join(ROOT, "oracle", "Makefile.ngraph")):
+            if line.startswith("REF ?="):
+                cands.append(line.split("=", 1)[1].strip())
+    except OSError:
+        pass
+    for d in cands:
+        if d and os.path.isdir(os.path.join(d, "src", "ngraph")):
             return d
     return None
+
+
+def ngraph_include_dir():
+    """nGraph's public headers (the plugin compiles against them, like every nGraph backend): $NGRAPH_SRC, else the src
+    directory of the checkout."""
+    d = os.environ.get("NGRAPH_SRC", "")
+    if d and os.path.exists(os.path.join(d, "ngraph", "runtime", "backend.hpp")):
+        return d
+    root = ngraph_checkout()
+    return os.path.join(root, "src") if root else None
 
 
 def host_cxx_flags(inc):

@@ -133,28 +133,65 @@ namespace b200
         return ex >= 127 - 40 && ex <= 127 + 40 && man != 0x7FFFFF;
     }
 
-    // The same strength-reduced division for the other rounding modes (8-bit outputs): the quotient has to be the
-    // correctly rounded x / s itself, because ceil / floor see its last bit.  q1 is that quotient while nothing
-    // underflows, which |x| >= 2^-60 guarantees for the admitted scales (2^-40 <= |s| < 2^41); zeros divide to zero;
-    // quotients of magnitude >= 2^24 (and inf / NaN) saturate or become 0 whatever their last bit; the few remaining
-    // inputs (0 < |x| < 2^-60) take the IEEE division.
+    // The rounding step of reference::quantize as ONE float -> int32 conversion with a directed rounding mode (plus the
+    // literal +-0.5 add of the half-way modes and a sign fix for the modes defined on |q|).  Equal to
+    // int(round_quant<MODE>(q)) wherever that integer is representable, saturated beyond, 0 for NaN; the caller clamps
+    // to the 8-bit range, so saturation never shows.  (floorf / ceilf followed by a float add of the zero point, two
+    // float clamps and a truncating conversion is what this replaces.)
+    template <int MODE>
+    __device__ __forceinline__ int round_quant_to_int(float q)
+    {
+        if (MODE == B200_ROUND_NEAREST_TOWARD_INFINITY)
+        {
+            const int a = __float2int_rd(__fadd_rn(fabsf(q), 0.5f));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_NEAREST_TOWARD_ZERO)
+        {
+            const int a = __float2int_ru(__fsub_rn(fabsf(q), 0.5f));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_NEAREST_UPWARD)
+            return __float2int_rd(__fadd_rn(q, 0.5f));
+        else if (MODE == B200_ROUND_NEAREST_DOWNWARD)
+            return __float2int_ru(__fsub_rn(q, 0.5f));
+        else if (MODE == B200_ROUND_NEAREST_TOWARD_EVEN)
+            return __float2int_rn(q); // the floor / ceil / parity sequence is round-half-even for |q| < 2^23; beyond, both saturate
+        else if (MODE == B200_ROUND_TOWARD_INFINITY)
+        {
+            const int a = __float2int_ru(fabsf(q));
+            return (q < 0.0f) ? -a : a;
+        }
+        else if (MODE == B200_ROUND_TOWARD_ZERO)
+            return __float2int_rz(q); // sign * floor|q|
+        else if (MODE == B200_ROUND_UP)
+            return __float2int_ru(q);
+        else
+            return __float2int_rd(q);
+    }
+
+    // The strength-reduced division for the modes other than round-half-even (8-bit outputs): the quotient has to be the
+    // correctly rounded x / s itself, because the directed conversions see its last bit.  q1 is that quotient while nothing
+    // underflows, which |x| >= 2^-60 guarantees for the admitted scales (2^-40 <= |s| < 2^41).  Quotients of magnitude
+    // >= 2^24 (and inf / NaN) saturate or become 0 whatever their last bit, so q0 serves.  Smaller inputs take the IEEE
+    // division in the directed modes: whether such a quotient is a tiny non-zero number (ceil gives 1) or underflows to
+    // zero (ceil gives 0) is decided by the division's own rounding.  The branch is all but never taken.
+    // lo_minus_zp / hi_minus_zp / zp as in quantize_rne_fast.
     template <typename Q, int MODE>
-    __device__ __forceinline__ Q quantize_one_fast(float x, float s, float y, float zp)
+    __device__ __forceinline__ int quantize_int_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
     {
         const float q0 = __fmul_rn(x, y);
         const float e = __fmaf_rn(-q0, s, x);
         const float q1 = __fmaf_rn(e, y, q0);
-        const float ax = fabsf(x);
-        float q;
-        if (!(fabsf(q0) < 16777216.0f) || ax == 0.0f)
-            q = q0;
-        else if (ax >= 8.673617379884035e-19f) // 2^-60
-            q = q1;
-        else
+        float q = (fabsf(q0) < 16777216.0f) ? q1 : q0;
+        constexpr bool nearest = MODE == B200_ROUND_NEAREST_TOWARD_INFINITY || MODE == B200_ROUND_NEAREST_TOWARD_ZERO ||
+                                 MODE == B200_ROUND_NEAREST_UPWARD || MODE == B200_ROUND_NEAREST_DOWNWARD ||
+                                 MODE == B200_ROUND_NEAREST_TOWARD_EVEN;
+        if (!nearest && fabsf(x) < 8.673617379884035e-19f) // 2^-60; the half-way modes send every |q| < 2^-19 to 0 anyway
             q = __fdiv_rn(x, s);
-        q = round_quant<MODE>(q);
-        q = __fadd_rn(q, zp);
-        return clamp_cast<Q>(q);
+        const int i = round_quant_to_int<MODE>(q);
+        const int r = min(max(i, lo_minus_zp), hi_minus_zp) + zp;
+        return (x != x) ? 0 : r; // NaN -> 0, as clamp_cast
     }
 
     template <typename Q>

@@ -152,6 +152,51 @@ namespace b200
         }
     }
 
+    // The 3x3 / stride 2 window of the network stems with TWO neighbouring output pixels per thread: their windows share a
+    // column, so 15 instead of 18 loads serve 32 output bytes, and a thread keeps 240 bytes in flight (the kernel is bound by
+    // load latency).  Out-of-image taps read as 0, the identity of an unsigned max.
+    __global__ void __launch_bounds__(256) maxpool_nhwc_u8_3x3s2_pair_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int N, int H,
+                                                                             int W, int C16, int P, int Q, int pad_h, int pad_w)
+    {
+        const uint32_t Q2 = uint32_t(Q + 1) / 2;
+        const uint32_t total = uint32_t(N) * P * Q2 * C16;
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+        {
+            uint32_t c = i % C16, t = i / C16;
+            const uint32_t q2 = t % Q2;
+            t /= Q2;
+            const uint32_t p = t % P, n = t / P;
+            const int h0 = 2 * int(p) - pad_h, w0 = 4 * int(q2) - pad_w; // columns w0 .. w0 + 4 serve outputs 2 q2 and 2 q2 + 1
+            uint4 v[3][5];
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int sx = 0; sx < 5; ++sx)
+                {
+                    const int h = h0 + r, w = w0 + sx;
+                    const bool ok = h >= 0 && h < H && w >= 0 && w < W;
+                    v[r][sx] = ok ? in[(size_t(n) * H + h) * W * C16 + size_t(w) * C16 + c] : make_uint4(0, 0, 0, 0);
+                }
+            uint4 col[5];
+#pragma unroll
+            for (int sx = 0; sx < 5; ++sx)
+            {
+                col[sx].x = __vmaxu4(__vmaxu4(v[0][sx].x, v[1][sx].x), v[2][sx].x);
+                col[sx].y = __vmaxu4(__vmaxu4(v[0][sx].y, v[1][sx].y), v[2][sx].y);
+                col[sx].z = __vmaxu4(__vmaxu4(v[0][sx].z, v[1][sx].z), v[2][sx].z);
+                col[sx].w = __vmaxu4(__vmaxu4(v[0][sx].w, v[1][sx].w), v[2][sx].w);
+            }
+            auto max3 = [](const uint4& a, const uint4& b, const uint4& d) {
+                return make_uint4(__vmaxu4(__vmaxu4(a.x, b.x), d.x), __vmaxu4(__vmaxu4(a.y, b.y), d.y), __vmaxu4(__vmaxu4(a.z, b.z), d.z),
+                                  __vmaxu4(__vmaxu4(a.w, b.w), d.w));
+            };
+            const size_t o = ((size_t(n) * P + p) * Q + 2 * size_t(q2)) * C16 + c;
+            out[o] = max3(col[0], col[1], col[2]);
+            if (2 * q2 + 1 < uint32_t(Q))
+                out[o + C16] = max3(col[2], col[3], col[4]);
+        }
+    }
+
     // Global average head on channels-last u8: Dequantize(s_in, zp 0) -> AvgPool over H x W
     // (runtime::reference::avg_pool: sequential float sum in H,W order, one division by the count)
     // -> Quantize(s_out, zp 0, ROUND_NEAREST_TOWARD_EVEN).  One thread per (n, c); threads of a warp
@@ -566,6 +611,12 @@ static int maxpool_nhwc_bytes(bool is_signed, const void* in, void* out, int64_t
         maxpool_nhwc_u8_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), int(N), int(H),
                                                            int(W), int(C / 16), int(P), int(Q), int(win_h), int(win_w),
                                                            int(stride_h), int(stride_w), int(pad_h), int(pad_w));
+    else if (small && win_h == 3 && win_w == 3 && stride_h == 2 && stride_w == 2)
+    {
+        const int64_t threads = N * P * ((Q + 1) / 2) * (C / 16), pair_blocks = (threads + 255) / 256;
+        maxpool_nhwc_u8_3x3s2_pair_kernel<<<unsigned(pair_blocks < b200::sm_count() * 32 ? pair_blocks : b200::sm_count() * 32), 256, 0, st>>>(
+            in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q), int(pad_h), int(pad_w));
+    }
     else if (small && win_h == 3 && win_w == 3)
         maxpool_nhwc_u8_fixed_kernel<3, 3><<<grid, 256, 0, st>>>(in4, out4, int(N), int(H), int(W), int(C / 16), int(P), int(Q),
                                                                  int(stride_h), int(stride_w), int(pad_h), int(pad_w));
@@ -873,6 +924,73 @@ namespace b200
             out[i] = make_uint4(words[0], words[1], words[2], words[3]);
         }
     }
+
+    // The same for images whose rows can be read four floats at a time (W and the column shift multiples of 4, 16-byte
+    // aligned rows): one thread makes TWO neighbouring cells from six 16-byte loads, all issued before the first use,
+    // which doubles the bytes a thread keeps in flight (the kernel is bound by load latency, not by arithmetic).
+    template <typename Q, bool FAST>
+    __global__ void __launch_bounds__(256) s2d_pack_f32_quad_kernel(const float* __restrict__ in, const float* __restrict__ scale,
+                                                                    const Q* __restrict__ zero_point, int mode, uint4* __restrict__ out,
+                                                                    int N, int C, int H, int W, int Hc, int Wc, int eh, int ew)
+    {
+        const float s = __ldg(scale);
+        const int zi = int(__ldg(zero_point));
+        const float zp = float(zi), y = __frcp_rn(s);
+        const int lo = int(QLimits<Q>::lo) - zi, hi = int(QLimits<Q>::hi) - zi;
+        const bool fast = FAST && scale_allows_fast_division(s);
+        auto quant = [&](float x) -> uint32_t {
+            if (fast)
+                return uint32_t(quantize_rne_fast<Q>(x, s, y, lo, hi, zi)) & 0xFFu;
+            return quantize_byte<Q>(x, s, zp, mode);
+        };
+        const uint32_t Wc2 = uint32_t(Wc + 1) / 2;
+        const uint32_t total = uint32_t(N) * Hc * Wc2;
+        const size_t plane = size_t(H) * W;
+        const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= total)
+            return;
+        const uint32_t cp = i % Wc2, t = i / Wc2;
+        const uint32_t ch = t % Hc, n = t / Hc;
+        const int w0 = 4 * int(cp) - ew, h0 = 2 * int(ch) - eh; // four pixels w0 .. w0 + 3: cells 2 cp and 2 cp + 1
+        const bool cols_ok = w0 >= 0 && w0 + 3 < W;              // W and w0 are multiples of 4: all four inside, or none
+        float4 v[2][4];
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+        {
+            const int h = h0 + dy;
+            const bool ok = cols_ok && h >= 0 && h < H;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+            {
+                v[dy][c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (c < C && ok)
+                    v[dy][c] = *reinterpret_cast<const float4*>(in + (size_t(n) * C + c) * plane + size_t(h) * W + w0);
+            }
+        }
+        // pixels outside the image stay zero BYTES (the convolution pads the quantized tensor)
+        uint32_t words[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}; // [cell][dy * 2 + dx]
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+        {
+            const int h = h0 + dy;
+            if (cols_ok && h >= 0 && h < H)
+            {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (c < C)
+                    {
+                        words[0][dy * 2 + 0] |= quant(v[dy][c].x) << (8 * c);
+                        words[0][dy * 2 + 1] |= quant(v[dy][c].y) << (8 * c);
+                        words[1][dy * 2 + 0] |= quant(v[dy][c].z) << (8 * c);
+                        words[1][dy * 2 + 1] |= quant(v[dy][c].w) << (8 * c);
+                    }
+            }
+        }
+        const size_t cell = (size_t(n) * Hc + ch) * Wc + 2 * size_t(cp);
+        out[cell] = make_uint4(words[0][0], words[0][1], words[0][2], words[0][3]);
+        if (2 * cp + 1 < uint32_t(Wc))
+            out[cell + 1] = make_uint4(words[1][0], words[1][1], words[1][2], words[1][3]);
+    }
 }
 
 extern "C" int b200_stem_geometry(int64_t H, int64_t W, int64_t R, int64_t S, int64_t pad_h, int64_t pad_w,
@@ -973,6 +1091,29 @@ extern "C" int b200_stem_pack_input_f32(const float* in_nchw, const float* scale
     s2d_pack_f32_kernel<Q, FAST, PAIRS><<<grid, 256, 0, st>>>(in_nchw, scale, static_cast<const Q*>(zero_point), round_mode,     \
                                                               static_cast<uint4*>(cells), int(N), int(C), int(H), int(W), int(Hc), \
                                                               int(Wc), int(eh), int(ew))
+    // rows that can be read four floats at a time: two cells per thread
+    const bool quads = (W % 4 == 0) && (ew % 4 == 0) && (reinterpret_cast<uintptr_t>(in_nchw) & 15) == 0;
+    if (quads)
+    {
+        const int64_t threads = N * Hc * ((Wc + 1) / 2);
+        const unsigned qgrid = unsigned((threads + 255) / 256);
+#define B200_S2D_QUAD(Q, FAST)                                                                                                  \
+    s2d_pack_f32_quad_kernel<Q, FAST><<<qgrid, 256, 0, st>>>(in_nchw, scale, static_cast<const Q*>(zero_point), round_mode,      \
+                                                             static_cast<uint4*>(cells), int(N), int(C), int(H), int(W), int(Hc), \
+                                                             int(Wc), int(eh), int(ew))
+        if (q_type == B200_U8)
+        {
+            if (rne) B200_S2D_QUAD(uint8_t, true);
+            else B200_S2D_QUAD(uint8_t, false);
+        }
+        else
+        {
+            if (rne) B200_S2D_QUAD(int8_t, true);
+            else B200_S2D_QUAD(int8_t, false);
+        }
+#undef B200_S2D_QUAD
+        return after_launch("b200_stem_pack_input_f32");
+    }
     if (q_type == B200_U8)
     {
         if (rne && pairs) B200_S2D_LAUNCH(uint8_t, true, true);

@@ -28,6 +28,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <type_traits>
@@ -107,6 +108,7 @@ namespace b200
         int f32_staged;      // f32 output, regular shape: transposed through the staging blocks for coalesced stores
         int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
         int vec_params;      // scale / bias pointers are 16-byte aligned
+        int pair;            // 1, or 2: a CTA works on two row tiles (2u, 2u + 1) at a time, which share every B stage
         void* out;
         uint32_t idesc;
         SmemPlan smem;
@@ -535,6 +537,7 @@ namespace b200
             // (the stem's cell runs: every tap of a tile in ONE stage - per-stage bookkeeping, not bytes, bounds that path)
             const int nkb = p.halo ? p.cblocks : p.a_cells ? 1 : p.ntaps * p.cblocks;
             int info_a = 0, info_b = 0, info_c = 0, info_d = 0;
+            int info_a2 = 0, info_b2 = 0, info_c2 = 0; // paired mode: the second row tile of the unit (same column tile)
             int idx = 32;
             // this producer's next k-block, as (offset inside the current tile, pipeline stage, stage parity); it advances
             // by NUM_PRODUCERS k-blocks at a time and carries over from tile to tile
@@ -545,19 +548,29 @@ namespace b200
                 s -= STAGES;
                 ph ^= 1;
             }
-            for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x)
+            // a unit of work: one tile, or in paired mode the two row tiles 2u and 2u + 1 (the host makes tiles_m even)
+            const int pair = p.pair;
+            const int num_units = num_tiles / pair;
+            for (int unit = blockIdx.x; unit < num_units && !fail; unit += gridDim.x)
             {
                 if (idx == 32)
                 {
-                    const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * gridDim.x;
-                    if (t < num_tiles)
+                    const long long t = static_cast<long long>(unit) + static_cast<long long>(lane) * gridDim.x;
+                    if (t < num_units)
                     {
                         int tm_, tn_, q0_, p0_, n0_;
-                        decode_tile(p, static_cast<int>(t), tm_, tn_, q0_, p0_, n0_);
+                        decode_tile(p, static_cast<int>(t) * pair, tm_, tn_, q0_, p0_, n0_);
                         info_a = p.conv ? q0_ : tm_;
                         info_b = p0_;
                         info_c = n0_;
                         info_d = tn_;
+                        if (pair == 2)
+                        {
+                            decode_tile(p, static_cast<int>(t) * 2 + 1, tm_, tn_, q0_, p0_, n0_);
+                            info_a2 = p.conv ? q0_ : tm_;
+                            info_b2 = p0_;
+                            info_c2 = n0_;
+                        }
                     }
                     idx = 0;
                 }
@@ -565,6 +578,9 @@ namespace b200
                 const int p0 = __shfl_sync(0xffffffffu, info_b, idx);
                 const int n0 = __shfl_sync(0xffffffffu, info_c, idx);
                 const int tn = __shfl_sync(0xffffffffu, info_d, idx);
+                const int ia2 = __shfl_sync(0xffffffffu, info_a2, idx);
+                const int p02 = __shfl_sync(0xffffffffu, info_b2, idx);
+                const int n02 = __shfl_sync(0xffffffffu, info_c2, idx);
                 ++idx;
                 // exactly one lane issues (elect.sync lets the compiler keep the TMA operands in uniform registers)
                 bool issued_here = false;
@@ -575,7 +591,7 @@ namespace b200
                     // packed weights: this column tile's 64-row blocks of a k-block are one contiguous piece
                     const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
                     const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
-                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES * uint32_t(p.ntaps) : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES)) + b_bytes;
+                    const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES * uint32_t(p.ntaps) : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES) * uint32_t(pair)) + b_bytes;
                     int tap = 0, cb = j; // k-block j of the tile = (tap, channel block)
                     while (cb >= p.cblocks)
                     {
@@ -595,7 +611,7 @@ namespace b200
                         const Tap tp = p.taps[tap];
                         const int kcol = j * BK; // byte column of the k-block in the B matrix
                         const uint32_t a_dst = smem_base + s * stage_bytes;
-                        const uint32_t b_dst = a_dst + C::A_BYTES;
+                        const uint32_t b_dst = a_dst + uint32_t(pair) * C::A_BYTES; // [A of tile 2u][A of tile 2u + 1][B]
                         ptx::mbar_expect_tx(full_bar(s), tx_bytes);
                         if (p.halo)
                         {
@@ -613,9 +629,17 @@ namespace b200
                             }
                         }
                         else if (p.conv)
+                        {
                             ptx::tma_load_4d(a_dst, &maps.a[tp.map], full_bar(s), cb * BK, q0 + tp.dw, p0 + tp.dh, n0);
+                            if (pair == 2)
+                                ptx::tma_load_4d(a_dst + C::A_BYTES, &maps.a[tp.map], full_bar(s), cb * BK, ia2 + tp.dw, p02 + tp.dh, n02);
+                        }
                         else
+                        {
                             ptx::tma_load_2d(a_dst, &maps.a[0], full_bar(s), kcol, tm * BM);
+                            if (pair == 2)
+                                ptx::tma_load_2d(a_dst + C::A_BYTES, &maps.a[0], full_bar(s), kcol, ia2 * BM);
+                        }
                         if (!p.smem.b_resident)
                         {
                             if (p.b_packed)
@@ -632,7 +656,7 @@ namespace b200
                             ++tap;
                         }
                         s += NUM_PRODUCERS;
-                        if (s >= STAGES)
+                        while (s >= STAGES) // a ring shorter than the number of producers wraps more than once
                         {
                             s -= STAGES;
                             ph ^= 1;
@@ -660,18 +684,22 @@ namespace b200
                 // stem cells: row m of the A tile is the 64 bytes starting at cell m of a linear run, so rows overlap:
                 // 16-byte K pieces 16 bytes apart, rows 16 bytes apart, 8-row groups 128 bytes apart, no swizzle
                 const uint64_t a_desc0 = p.a_cells ? ptx::smem_desc_overlapping_rows(smem_base) : ptx::smem_desc_kmajor(smem_base, BK);
-                const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + C::A_BYTES, BK);
+                const int pair = p.pair;
+                const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + uint32_t(pair) * C::A_BYTES, BK);
                 // descriptor address fields count 16-byte units
                 const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
                 if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp, BACKOFF_FULL_NS))
                     fail = 2003;
-                for (int tile = blockIdx.x; tile < num_tiles && !fail; tile += gridDim.x, ++tile_it)
+                // one unit per iteration: a tile, or the two row tiles of a pair (accumulators acc and acc + 1; NACC is even)
+                const int num_units = num_tiles / pair;
+                for (int unit = blockIdx.x; unit < num_units && !fail; unit += gridDim.x, tile_it += pair)
                 {
                     const int acc = tile_it % NACC;
                     const uint32_t acc_ph = (tile_it / NACC) & 1;
                     {
                         PROF_T0();
-                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS))
+                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS) ||
+                            (pair == 2 && !ptx::mbar_wait(tempty_bar(acc + 1), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS)))
                         {
                             fail = 2001;
                             break;
@@ -779,6 +807,14 @@ namespace b200
                             ptx::mma_i8(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc,
                                         (kb | k) != 0 ? 1u : 0u);
                         }
+                        if (pair == 2)
+                        {
+                            // the second row tile of the pair: its A block follows the first one's, the B block is the same
+#pragma unroll
+                            for (int k = 0; k < BK / 32; ++k)
+                                ptx::mma_i8(d_tmem + BN, a_desc + uint64_t((C::A_BYTES >> 4) + 2 * k), b_desc + uint64_t(2 * k), p.idesc,
+                                            (kb | k) != 0 ? 1u : 0u);
+                        }
                         ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
 #ifdef B200_PROFILE_WAITS
                         if (blockIdx.x == 0)
@@ -793,6 +829,8 @@ namespace b200
                     if (fail)
                         break;
                     ptx::mma_commit(tfull_bar(acc)); // accumulator complete
+                    if (pair == 2)
+                        ptx::mma_commit(tfull_bar(acc + 1));
                 }
             }
         }
@@ -841,7 +879,13 @@ namespace b200
             const uint32_t sc_base = ptx::smem_u32(&epi_scale[ew][0]), bi_base = ptx::smem_u32(&epi_bias[ew][0]);
             // per-row addresses are only needed for residual loads and for stores that do not go through TMA
             const bool need_rows = has_sum || !p.tma_store;
-            const int tile_step = GROUPS * int(gridDim.x); // distance between two tiles of this warp
+            // the tile this CTA handles as its it-th one: tiles blockIdx, blockIdx + grid, ... or, in paired mode, the row
+            // tiles 2u and 2u + 1 of the units u = blockIdx, blockIdx + grid, ...
+            const int pair = p.pair;
+            auto tile_of = [&](uint32_t it) -> long long {
+                return pair == 2 ? 2ll * (static_cast<long long>(blockIdx.x) + static_cast<long long>(it >> 1) * gridDim.x) + (it & 1u)
+                                 : static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * gridDim.x;
+            };
             // One thread per warp issues the warp's TMA loads / stores, bulk-group waits and barrier arrivals.  It is
             // chosen by elect.sync at points where the warp is converged: the election is deterministic for a full
             // mask (the bulk groups stay with one thread) and lets the compiler keep the operands in uniform registers.
@@ -884,11 +928,11 @@ namespace b200
                 };
                 uint32_t tile_it = uint32_t(group);
                 int j = 0;
-                for (int tile = int(blockIdx.x) + group * int(gridDim.x); tile < num_tiles && !fail; tile += tile_step, tile_it += GROUPS, ++j)
+                for (long long tile = tile_of(tile_it); tile < num_tiles && !fail; tile_it += GROUPS, tile = tile_of(tile_it), ++j)
                 {
                     if (idx == 31)
                     {
-                        const long long t = static_cast<long long>(tile) + static_cast<long long>(lane) * tile_step;
+                        const long long t = tile_of(tile_it + uint32_t(lane) * GROUPS);
                         if (t < num_tiles)
                         {
                             int tm_, tn_, q0_, p0_, n0_;
@@ -912,7 +956,7 @@ namespace b200
                     {
                         // Residual of this warp's NEXT tile -> the block that tile's result will be stored from.  That block
                         // was last used two tiles ago: all but the most recent store must have finished reading.
-                        const bool has_next = tile + tile_step < num_tiles;
+                        const bool has_next = tile_of(tile_it + GROUPS) < num_tiles;
                         int na, np0, nn0, ntn;
                         coords_of(idx + 1, na, np0, nn0, ntn);
                         if (ptx::elect_one())
@@ -1355,7 +1399,15 @@ namespace b200
         SmemPlan& sp = p.smem;
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
-        sp.stage_bytes = C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
+        if (p.pair != 2)
+            p.pair = 1;
+        if ((p.a_cells || p.halo) && p.pair != 1)
+            return B200_ERR_INVALID_ARGUMENT; // pairing is for the plain tile pipeline only
+        if (p.pair == 2 && (p.tiles_m & 1))
+            return B200_ERR_INVALID_ARGUMENT; // the caller pads the row tiles to an even count
+        const int tma_store_asked = p.tma_store, tma_sum_asked = p.tma_sum;
+    plan_again:
+        sp.stage_bytes = p.pair * C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
         if (p.a_cells)
         {
             if (!sp.b_resident)
@@ -1384,10 +1436,19 @@ namespace b200
         sp.out_bytes = sp.out_bufs * C::OUT_BYTES;
         int fit = (room - sp.out_bytes) / sp.stage_bytes;
         sp.stages = fit > MAX_STAGES ? MAX_STAGES : fit;
+        if (p.pair == 2 && sp.stages < 3)
+        {
+            // the wider stages of a pair leave too short a ring: the same tiles one at a time (an even, padded tile count is
+            // as good as the exact one)
+            p.pair = 1;
+            p.tma_store = tma_store_asked;
+            p.tma_sum = tma_sum_asked;
+            goto plan_again;
+        }
         if (sp.stages < 2)
             return B200_ERR_UNSUPPORTED;
         sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + sp.out_bytes + C::FIXED;
-        int tiles = p.tiles_m * p.tiles_n;
+        int tiles = p.tiles_m * p.tiles_n / p.pair; // units of work: tiles, or pairs of row tiles
         int grid = tiles < num_sms() ? tiles : num_sms();
         // Programmatic dependent launch: the CTAs of this launch may become resident while the previous kernel of the
         // stream drains (SM by SM), set up their barriers, tensor memory and descriptors, and then wait in
@@ -1481,6 +1542,48 @@ namespace b200
     static bool valid_operand_types(int t)
     {
         return (t & ~(0xFF | B200_WEIGHTS_U8)) == 0 && ((t & 0xFF) == B200_U8 || (t & 0xFF) == B200_I8);
+    }
+
+    // Whether a CTA should work on two row tiles at a time that share every B stage (ContractParams::pair = 2).
+    // A k-block of a 128 x BN tile moves (128 + BN) * BK bytes from L2 for 128 * BN * BK MACs; a pair moves
+    // (256 + BN) * BK bytes for twice the MACs.  Long reductions run at the rate the SM can pull operands from L2 (measured
+    // here: ~45 bytes per clock per SM, against 8192 MACs per clock of the tensor pipe), so the pair is faster per MAC, but it
+    // halves the number of work units, which costs when the units no longer spread evenly over the SMs.  Both are put into
+    // one estimate (cycles per SM): waves of units x the time of a unit, a unit's epilogue overlapping the next unit's
+    // products only while two accumulator sets fit the 512 TMEM columns.
+    static double contract_cost(int64_t tiles_m, int64_t n_out, int bn, int bk, int64_t nkb, int pair, bool residual, bool b_resident)
+    {
+        const double l2_bytes_per_clk = 45.0, mac_per_clk = bn >= 128 ? 8192.0 : 4096.0, epilogue_clk_per_kb = residual ? 80.0 : 50.0;
+        const int64_t units = ((tiles_m + pair - 1) / pair) * ((n_out + bn - 1) / bn);
+        const double waves = double((units + num_sms() - 1) / num_sms());
+        const double bytes = double(pair * BM + (b_resident ? 0 : bn)) * bk;
+        const double kb_clk = std::max(double(pair) * BM * bn * bk / mac_per_clk, bytes / l2_bytes_per_clk) + 60.0;
+        const double epi_clk = double(pair) * BM * bn / 1024.0 * epilogue_clk_per_kb;
+        const bool overlapped = 2 * pair * bn <= 512;
+        const double unit_clk = overlapped ? std::max(double(nkb) * kb_clk, epi_clk) + 400.0 : double(nkb) * kb_clk + epi_clk + 400.0;
+        return waves * unit_clk;
+    }
+
+    static int pick_pair(int64_t tiles_m, int64_t n_out, int bn, int bk, int64_t nkb, bool residual, bool halo)
+    {
+#ifdef B200_PROFILE_WAITS
+        if (const char* f = getenv("B200_FORCE_PAIR")) // instrumented build only
+            return (atoi(f) == 2 && !halo) ? 2 : 1;
+#endif
+        if (halo || nkb < 4 || tiles_m < 2)
+            return 1;
+        // shared memory: a paired stage is 2 A blocks + 1 B block; at least three stages must fit beside the output staging
+        // (which long reductions give up, see launch_contract)
+        const bool b_resident = (n_out + bn - 1) / bn == 1 && nkb * int64_t(bn) * bk <= B_RESIDENT_MAX;
+        const int64_t stage = 2 * int64_t(BM) * bk + (b_resident ? 0 : int64_t(bn) * bk);
+        const int64_t staging = (residual ? 3 : 2) * int64_t(EPI_WARPS * 32 * COLS);
+        const int64_t room = SMEM_LIMIT - 4096 - (b_resident ? nkb * int64_t(bn) * bk : 0);
+        const bool keeps_tma_store = !(nkb >= 16 && (room - staging) / stage < 4);
+        if ((room - (keeps_tma_store ? staging : 0)) / stage < 3)
+            return 1;
+        const double one = contract_cost(tiles_m, n_out, bn, bk, nkb, 1, residual, b_resident);
+        const double two = contract_cost(tiles_m, n_out, bn, bk, nkb, 2, residual, b_resident);
+        return two < 0.93 * one ? 2 : 1;
     }
 
     static int pick_bn(int64_t n_out, int64_t tiles_m, int bk, bool residual, int64_t k_bytes)
@@ -1619,6 +1722,9 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
     p.tiles_m = int((M + BM - 1) / BM);
     const int bn = pick_bn(N, p.tiles_m, bk, epilogue && epilogue->sum_in, K);
     p.tiles_n = int((N + bn - 1) / bn);
+    p.pair = pick_pair(p.tiles_m, N, bn, bk, p.cblocks, epilogue && epilogue->sum_in, false);
+    if (p.pair == 2)
+        p.tiles_m = (p.tiles_m + 1) & ~1; // a row tile beyond M loads zeros and stores nothing
     p.conv = 0;
     fill_epilogue(p, epilogue, out, a_type);
     p.idesc = make_idesc(a_type, bn);
@@ -1833,6 +1939,16 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     p.tiles_m = p.tiles_q * p.tiles_p * int((c->N + p.TN - 1) / p.TN);
     const int bn = pick_bn(c->K, p.tiles_m, bk, epilogue && epilogue->sum_in, c->R * c->S * c->C);
     p.tiles_n = int((c->K + bn - 1) / bn);
+    // Row-tile pairs are not taken for convolutions: on the ResNet-50 layers they could apply to (3x3 on 28x28 and 14x14
+    // images at batch 128) the halved number of work units costs what the shared weight stages save (measured: 24.8 -> 27 us
+    // for 3x3 256 -> 256 on 14x14, no change on 28x28).  The kernel supports them (instrumented builds can force them).
+    p.pair = 1;
+#ifdef B200_PROFILE_WAITS
+    if (getenv("B200_FORCE_PAIR"))
+        p.pair = pick_pair(p.tiles_m, c->K, bn, bk, int64_t(p.ntaps) * p.cblocks, epilogue && epilogue->sum_in, p.halo != 0);
+#endif
+    if (p.pair == 2)
+        p.tiles_m = (p.tiles_m + 1) & ~1; // a patch beyond the batch loads zeros and stores nothing
     fill_epilogue(p, epilogue, out, data_type);
     p.idesc = make_idesc(data_type, bn);
 

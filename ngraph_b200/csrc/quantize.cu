@@ -81,6 +81,8 @@ namespace b200
         // int32 output can be large enough for the last bit of a quotient beyond 2^24 to matter)
         const bool fast = FAST && sizeof(Q) == 1 && scale_allows_fast_division(s);
         const float y = __frcp_rn(s);
+        const int zi = static_cast<int>(zp[sidx]);
+        const int lo = sizeof(Q) == 1 ? int(QLimits<Q>::lo) - zi : 0, hi = sizeof(Q) == 1 ? int(QLimits<Q>::hi) - zi : 0; // 8-bit path only
 
         float4 v[QU];
 #pragma unroll
@@ -97,10 +99,10 @@ namespace b200
             if (off + 4 <= rem && fast)
             {
                 store4<Q>(op + off,
-                          quantize_one_fast<Q, MODE>(v[u].x, s, y, z),
-                          quantize_one_fast<Q, MODE>(v[u].y, s, y, z),
-                          quantize_one_fast<Q, MODE>(v[u].z, s, y, z),
-                          quantize_one_fast<Q, MODE>(v[u].w, s, y, z));
+                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].x, s, y, lo, hi, zi)),
+                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].y, s, y, lo, hi, zi)),
+                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].z, s, y, lo, hi, zi)),
+                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].w, s, y, lo, hi, zi)));
             }
             else if (off + 4 <= rem)
             {

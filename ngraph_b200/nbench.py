@@ -134,13 +134,13 @@ def build_model(name, batch):
     if name == "bert":
         return ng.bert_encoder(layers=12, hidden=768, heads=12, ffn=3072, seq=384, batch=batch or 64, vocab=30522, seed=1), [30522, 2]
     rng = np.random.default_rng(0)
-    if name == "qdot":  # BASELINE config 1: QuantizedDotBias + Relu, u8 [M,1024] x i8 [1024,1024]
+    if name == "qdot":  # the single-layer workload: QuantizedDotBias + Relu, u8 [M,1024] x i8 [1024,1024]
         m = batch or 256
         x = ng.parameter(np.uint8, (m, 1024))
         w = rng.integers(-127, 128, size=(1024, 1024)).astype(np.int8)
         bias = rng.integers(-1000, 1001, size=1024).astype(np.int32)
         return ng.Function([ng.quantized_dot_bias(x, w, bias, np.float32([0.004]), True, True)], [x]), None
-    if name == "qconv":  # BASELINE config 3: QuantizedConvolutionBias + Relu, 64 -> 64 channels, 3x3, 56x56
+    if name == "qconv":  # the single-convolution workload: QuantizedConvolutionBias + Relu, 64 -> 64 channels, 3x3, 56x56
         n = batch or 32
         x = ng.parameter(np.uint8, (n, 64, 56, 56))
         w = rng.integers(-127, 128, size=(64, 64, 3, 3)).astype(np.int8)

@@ -1,4 +1,4 @@
-"""Quantize / Dequantize bandwidth sweep on one GPU (BASELINE config 2): x f32 ~ N(0,1) of shape [N,64,H,W] from 1 MB to
+"""Quantize / Dequantize bandwidth sweep on one GPU (the Quantize / Dequantize bandwidth workload): x f32 ~ N(0,1) of shape [N,64,H,W] from 1 MB to
 4 GB of f32, element types u8 (zero point 128) and i8 (zero point 0), one scale per tensor (0.05) or per channel
 (axes = {1}, log-uniform in [1e-3, 1e-1]), every RoundMode, and Dequantize of the produced tensors.
 

@@ -207,7 +207,8 @@ def parse_builder_dot(body):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    from ngraph_b200.build import ngraph_checkout
+    ap.add_argument("--ref", default=ngraph_checkout(), help="root of the nGraph checkout (default: $NGRAPH_REF or the reference build recipe's)")
     args = ap.parse_args()
     if not os.path.exists(GEN):
         sys.exit("build the reference first: make -C oracle ref")

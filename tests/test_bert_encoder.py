@@ -1,4 +1,4 @@
-"""BASELINE config 5 in miniature: an int8 BERT-base-shaped encoder (QuantizedDotBias with per-channel i8 weights and
+"""In miniature and at full width: an int8 BERT-base-shaped encoder (QuantizedDotBias with per-channel i8 weights and
 dynamic per-tensor i8 activation scales; softmax, LayerNorm, GELU and residual adds in f32) through the B200 plugin
 against nGraph's INTERPRETER on the decomposed graph.  The CPU part checks the graph itself; the GPU part the parity."""
 import collections

@@ -237,7 +237,7 @@ def test_qconv_vs_oracle(ops, cfg):
 
 
 def test_qconv_baseline_layer(ops):
-    """BASELINE config 3: QuantizedConvolutionBias+Relu, u8 [32,64,56,56] * i8 [64,64,3,3], per-channel
+    """The single-convolution workload: QuantizedConvolutionBias+Relu, u8 [32,64,56,56] * i8 [64,64,3,3], per-channel
     scales, i32 bias, stride 1 pad 1 -> u8.  The oracle runs on a batch slice (a few seconds); the rest
     of the batch is checked through linearity in the batch index (each image is independent)."""
     rng = np.random.default_rng(3)
@@ -281,6 +281,11 @@ def test_layout_and_pooling(ops):
     big = rng.integers(0, 256, size=(4, 64, 30, 30)).astype(np.uint8)
     got = ops.maxpool_nhwc(dev(nhwc(big)), (3, 3), (2, 2), (1, 1), (1, 1)).cpu().numpy()
     np.testing.assert_array_equal(got.transpose(0, 3, 1, 2), ref.maxpool_u8(big, (3, 3), (2, 2), (1, 1), (1, 1)))
+    # odd output widths and asymmetric padding through the two-outputs-per-thread form of the 3x3 / stride 2 window
+    for shape, pb, pa in (((2, 32, 29, 33), (1, 1), (1, 1)), ((3, 16, 18, 21), (0, 1), (1, 0)), ((1, 64, 112, 112), (1, 1), (1, 1))):
+        xs = rng.integers(0, 256, size=shape).astype(np.uint8)
+        got = ops.maxpool_nhwc(dev(nhwc(xs)), (3, 3), (2, 2), pb, pa).cpu().numpy()
+        np.testing.assert_array_equal(got.transpose(0, 3, 1, 2), ref.maxpool_u8(xs, (3, 3), (2, 2), pb, pa), err_msg=str(shape))
 
 
 # ---------------------------------------------------------------- stride-2 small-channel stem (space-to-depth path)
@@ -344,7 +349,7 @@ def test_stem_pack_with_fused_quantize(ops, q_np):
 
 HALO_CASES = [
     # N, C, H, W, K, R, S, pad: stride 1, weights small enough to stay in shared memory -> the patch-with-halo path
-    (2, 64, 56, 56, 64, 3, 3, (1, 1)),    # BASELINE's layer geometry, small batch
+    (2, 64, 56, 56, 64, 3, 3, (1, 1)),    # the 56x56 64 -> 64 layer geometry, small batch
     (3, 64, 31, 45, 64, 3, 3, (1, 1)),    # ragged in both directions
     (2, 64, 20, 33, 32, 3, 3, (0, 0)),    # no padding
     (1, 128, 17, 64, 32, 3, 3, (1, 1)),   # 128-byte rows
@@ -373,3 +378,48 @@ def test_qconv_halo_path_vs_oracle(ops, case):
     exp = ref.qconv_core(data, filt, cs, 1.0, 0, 1.0, 0, 1.0, 0, np.int32)
     got = run_conv(ops, data, filt, None, np.float32(1.0), cs, np.int32, False, core=True)
     np.testing.assert_array_equal(got, exp, err_msg="core i32")
+
+
+# ---------------------------------------------------------------- two row tiles per CTA sharing each B stage
+@pytest.mark.parametrize("m,n,k", [(24576, 768, 3072), (24576 + 100, 768, 3072), (8192, 1024, 4096)])
+def test_large_qgemm_with_paired_row_tiles(ops, m, n, k):
+    """Problems large enough that a CTA takes two 128-row tiles at a time (they share every weight stage): every output type
+    the kernel has a store path for, against the oracle on rows taken from first / second tiles of pairs, from the ragged last
+    tile and from the tile that only exists as padding of an odd tile count."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(0, 256, size=(m, k)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(n, k)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=n).astype(np.int32)
+    scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=n)) * 40.0 / (np.sqrt(k) * 74 * 147)).astype(np.float32)
+    rows = np.concatenate([np.arange(0, 40), np.arange(128 + 90, 128 + 130), np.arange(5 * 256 + 120, 5 * 256 + 140),
+                           np.arange((m // 128 - 1) * 128 - 8, m)])
+    ad, wd, sd, bd = dev(a), dev(w), dev(scale), dev(bias)
+    for out_dt, relu in ((np.uint8, True), (np.float32, False), (np.int8, False), (np.int32, False)):
+        exp = ref.qgemm_fused(a[rows], w, bias, scale, out_dt, relu=relu)
+        for packed in (True, False):
+            got = ops.qgemm(ad, wd, sd, TDT[np.dtype(out_dt)], bias=bd, relu=relu, packed=packed)[torch.from_numpy(rows).cuda()].cpu().numpy()
+            if out_dt == np.float32:
+                same_f32(got, exp)
+            else:
+                np.testing.assert_array_equal(got, exp, err_msg="%s relu=%d packed=%d" % (out_dt, relu, packed))
+
+
+@pytest.mark.parametrize("n,c,hw,k,r", [(128, 128, 28, 128, 3), (128, 256, 14, 256, 3), (65, 256, 14, 256, 3), (128, 512, 7, 512, 3)])
+def test_large_qconv_at_full_batch(ops, n, c, hw, k, r):
+    """ResNet-50 layer shapes at batch 128 (and an odd count of row tiles), where tile width and scheduling are chosen for a
+    full device: images from the first, a middle and the last tiles against the oracle, with and without a residual input"""
+    rng = np.random.default_rng(n + c + hw)
+    data = rng.integers(0, 256, size=(n, c, hw, hw)).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=(k, c, r, r)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=k).astype(np.int32)
+    scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=k)) * 60.0 / (np.sqrt(c * r * r) * 74 * 147)).astype(np.float32)
+    pad = (r // 2, r // 2)
+    cs = ref.conv_shape(data.shape, filt.shape, (1, 1), pad, pad, (1, 1))
+    sl = [0, 1, n // 2, n - 2, n - 1]
+    cs_s = ref.conv_shape((len(sl),) + data.shape[1:], filt.shape, (1, 1), pad, pad, (1, 1))
+    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, packed=True)
+    np.testing.assert_array_equal(got[sl], ref.qconv_fused(data[sl], filt, bias, scale, cs_s, np.uint8, relu=True))
+    sum_u8 = rng.integers(0, 256, size=(n, k, hw, hw)).astype(np.uint8)
+    got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.61, packed=True)
+    np.testing.assert_array_equal(got[sl], ref.qconv_fused(data[sl], filt, bias, scale, cs_s, np.uint8, relu=True, sum_in=sum_u8[sl],
+                                                           sum_scale=np.float32(0.61)))

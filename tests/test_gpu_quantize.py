@@ -137,7 +137,7 @@ def test_empty_and_errors(ops):
 
 
 def test_roundtrip_property_full_size(ops):
-    """Size-independent property on a BASELINE-sized tensor (256 MB f32): for u8 zp 128 scale 0.05,
+    """Size-independent property on a full-size tensor (256 MB f32): for u8 zp 128 scale 0.05,
     dequantize(quantize(x)) differs from clamp(x) by at most scale/2, and quantize is idempotent on it."""
     g = torch.Generator(device="cuda")
     g.manual_seed(7)
@@ -207,7 +207,7 @@ def test_fast_division_is_exact_for_every_float_in_the_other_round_modes(ops, mo
 
 @pytest.mark.gpu
 def test_bandwidth_sweep_tool_runs():
-    """python -m ngraph_b200.quantize_sweep (the BASELINE config-2 table) on its two smallest sizes"""
+    """python -m ngraph_b200.quantize_sweep (the bandwidth sweep table) on its two smallest sizes"""
     from ngraph_b200 import quantize_sweep
     lines = []
     rows = quantize_sweep.sweep(max_mb=4, iters=2, out=lines.append)

@@ -240,10 +240,10 @@ def test_quantized_dot_bias(backends):
 @pytest.mark.parametrize("act_dtype", [np.uint8, np.int8])
 @pytest.mark.parametrize("out_scale", [0.05, 5.0])
 def test_baseline_quantized_dot_bias_layer(backends, act_dtype, out_scale):
-    """BASELINE config 1 as a graph: X f32 [256,1024] ~N(0,1) -> Quantize(0.02, zp 0, RNE) -> QuantizedDotBias+Relu with
+    """The single-layer workload as a graph: X f32 [256,1024] ~N(0,1) -> Quantize(0.02, zp 0, RNE) -> QuantizedDotBias+Relu with
     W i8 [1024,1024] (scale 0.01), bias f32 ~N(0,0.1) quantised to i32 with scale 0.02*0.01, requantised with
     0.02*0.01/out_scale.  out_scale 0.05 is the config as written (most outputs saturate); 5.0 is its non-saturating twin
-    that exercises the rounding.  u8 activations are the reference-runnable variant, i8 the one BASELINE names."""
+    that exercises the rounding.  u8 activations are the reference-runnable variant, i8 the one the workload names."""
     rng = np.random.default_rng(1)
     x = rng.standard_normal((256, 1024)).astype(np.float32)
     w = rng.integers(-127, 128, size=(1024, 1024)).astype(np.int8)

@@ -18,7 +18,9 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BINDING_DIR = os.path.join(ROOT, "oracle", "_ref", "python")
-REFERENCE_PY = "/root/reference/python/src"
+from ngraph_b200.build import ngraph_checkout  # noqa: E402
+
+REFERENCE_PY = os.path.join(ngraph_checkout() or "", "python", "src")
 
 pytestmark = pytest.mark.skipif(not glob.glob(os.path.join(BINDING_DIR, "_pyngraph*.so")),
                                 reason="the reference's Python binding has not been built (oracle/Makefile.pyngraph)")

@@ -1,4 +1,4 @@
-"""int8 ResNet-50 v1.5 (BASELINE's headline graph) through the B200 plugin against nGraph's INTERPRETER.
+"""int8 ResNet-50 v1.5 (the headline graph) through the B200 plugin against nGraph's INTERPRETER.
 
 INTERPRETER needs ~40 s per 224x224 image: parity runs on reduced spatial sizes (the network is fully
 convolutional up to the pooling head; every layer, channel count, stride, residual join and the head are
