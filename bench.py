@@ -153,7 +153,7 @@ def cpu_worker(pickle_path, patch, reps):
         exe.call([tout], [tin])
         times.append(time.time() - t0)
     out = tout.read()
-    print(json.dumps({"seconds": times, "checksum": float(np.abs(out).sum()), "logits": out[0, :8].tolist()}))
+    print(json.dumps({"seconds": times, "logit_bits": out.view(np.uint32).ravel().tolist()}))
 
 
 def cpu_reference_rate(model, budget_s, procs=None, reps=1):
@@ -237,6 +237,9 @@ class ResNet50:
         # --double_buffer for the copies).  Every step is still one [B,3,224,224] batch through the unchanged graph.
         self.lane_streams = [torch.cuda.current_stream(), torch.cuda.Stream()] if self.pipeline == 2 else [torch.cuda.current_stream()]
         self.lane_exe, self.lane_in, self.lane_out, self.lane_backends = [self.exe], [self.t_in], [self.t_out2[0]], [self.backend]
+        from concurrent.futures import ThreadPoolExecutor
+        self.lane_threads = [ThreadPoolExecutor(max_workers=1) for _ in range(2)]
+        self.lane_pending = [[], []]
         if self.pipeline == 2:
             b2 = ng.Backend("B200:%d,stream=%d" % (local_rank, self.lane_streams[1].cuda_stream))
             self.lane_backends.append(b2)
@@ -277,6 +280,11 @@ class ResNet50:
         if self.gathered is not None and self.logits_read[k] is not None:
             st.wait_event(self.logits_read[k])  # the gather of two steps ago has read this buffer
         out = self.lane_out[lane] if self.pipeline == 2 else self.t_out2[k]
+        if self.pipeline == 2 and self.gathered is None:
+            # one host thread per lane issues that lane's launches (Executable::call only enqueues; ctypes releases the
+            # interpreter lock for its duration), so neither stream waits for the other's 58 launches to be issued
+            self.lane_pending[lane].append(self.lane_threads[lane].submit(self.lane_exe[lane].call, [out], [self.lane_in[lane]], False))
+            return
         self.lane_exe[lane].call([out], [self.lane_in[lane]], validate=False)
         if self.gathered is not None:
             self.logits_read[k] = self._gather_beside_next_step(self.logits2[k], st)
@@ -288,6 +296,10 @@ class ResNet50:
 
     def finish(self):
         """joins the second lane and the gather stream: the timed region ends when the last steps' logits are there"""
+        for pending in self.lane_pending:
+            for f in pending:
+                f.result()
+            del pending[:]
         for st in self.lane_streams[1:]:
             self.torch.cuda.current_stream().wait_stream(st)
         if self.gather_stream is not None:
@@ -391,8 +403,8 @@ class ResNet50:
         x = synthetic_images(1, 77, 224)[:, :, :ph, :pw]  # the patch the workers ran, through the plugin
         fn, _ = model.build(ng, 1, fused=True, image_hw=(ph, pw))
         got = self.backend.compile(fn).run(x)[0]
-        ok = bool(np.array_equal(np.asarray(first["logits"], np.float32), got[0, :8])) and \
-            abs(float(np.abs(got).sum()) - first["checksum"]) <= 1e-5 * max(1.0, first["checksum"])
+        # every logit of the patch, bit for bit (the float tail of the graph is one Dequantize: a single IEEE multiply)
+        ok = bool(np.array_equal(np.asarray(first["logit_bits"], np.uint32), got.view(np.uint32).ravel()))
         return {"value": rate, "unit": "img/s", "cores": procs, "kind": "reference", "sample": sample}, ok
 
 
@@ -933,6 +945,8 @@ def main():
 
     for _ in range(args.warmup):
         wl.step()
+    if hasattr(wl, "finish"):
+        wl.finish()
     barrier()
     lib.device_status()
 

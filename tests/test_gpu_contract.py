@@ -423,3 +423,31 @@ def test_large_qconv_at_full_batch(ops, n, c, hw, k, r):
     got = run_conv(ops, data, filt, bias, scale, cs, np.uint8, True, sum_in=sum_u8, sum_scale=0.61, packed=True)
     np.testing.assert_array_equal(got[sl], ref.qconv_fused(data[sl], filt, bias, scale, cs_s, np.uint8, relu=True, sum_in=sum_u8[sl],
                                                            sum_scale=np.float32(0.61)))
+
+
+def test_repeated_calls_reuse_the_launch_plan_not_the_data(ops):
+    """The entry points keep the launch set-up of an argument list they have seen (tile choice, tensor maps, shared-memory
+    plan).  Same pointers with new contents must give new results; same contents at other addresses the same results."""
+    rng = np.random.default_rng(17)
+    a = rng.integers(0, 256, size=(300, 256)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(96, 256)).astype(np.int8)
+    scale = np.full(96, 3e-4, np.float32)
+    ad, wd, sd = dev(a), dev(w), dev(scale)
+    out = torch.empty((300, 96), dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        ops.qgemm(ad, wd, sd, torch.uint8, relu=True, out=out)
+    np.testing.assert_array_equal(out.cpu().numpy(), ref.qgemm_fused(a, w, None, scale, np.uint8, relu=True))
+    a2 = rng.integers(0, 256, size=a.shape).astype(np.uint8)
+    ad.copy_(torch.from_numpy(a2))  # same address, other bytes
+    ops.qgemm(ad, wd, sd, torch.uint8, relu=True, out=out)
+    np.testing.assert_array_equal(out.cpu().numpy(), ref.qgemm_fused(a2, w, None, scale, np.uint8, relu=True))
+    other = ops.qgemm(dev(a2), dev(w), dev(scale), torch.uint8, relu=True)  # other addresses, same bytes
+    assert torch.equal(other, out)
+    data = rng.integers(0, 256, size=(2, 64, 12, 12)).astype(np.uint8)
+    filt = rng.integers(-127, 128, size=(64, 64, 3, 3)).astype(np.int8)
+    bias = rng.integers(-1000, 1001, size=64).astype(np.int32)
+    cs = ref.conv_shape(data.shape, filt.shape, (1, 1), (1, 1), (1, 1), (1, 1))
+    first = run_conv(ops, data, filt, bias, scale[:64], cs, np.uint8, True)
+    again = run_conv(ops, data, filt, bias, scale[:64], cs, np.uint8, True)
+    np.testing.assert_array_equal(first, again)
+    np.testing.assert_array_equal(first, ref.qconv_fused(data, filt, bias, scale[:64], cs, np.uint8, relu=True))
