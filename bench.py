@@ -240,6 +240,7 @@ class ResNet50:
         from concurrent.futures import ThreadPoolExecutor
         self.lane_threads = [ThreadPoolExecutor(max_workers=1) for _ in range(2)]
         self.lane_pending = [[], []]
+        self.gather_due = None
         if self.pipeline == 2:
             b2 = ng.Backend("B200:%d,stream=%d" % (local_rank, self.lane_streams[1].cuda_stream))
             self.lane_backends.append(b2)
@@ -280,14 +281,27 @@ class ResNet50:
         if self.gathered is not None and self.logits_read[k] is not None:
             st.wait_event(self.logits_read[k])  # the gather of two steps ago has read this buffer
         out = self.lane_out[lane] if self.pipeline == 2 else self.t_out2[k]
-        if self.pipeline == 2 and self.gathered is None:
+        if self.pipeline == 2:
             # one host thread per lane issues that lane's launches (Executable::call only enqueues; ctypes releases the
             # interpreter lock for its duration), so neither stream waits for the other's 58 launches to be issued
-            self.lane_pending[lane].append(self.lane_threads[lane].submit(self.lane_exe[lane].call, [out], [self.lane_in[lane]], False))
+            issued = self.lane_threads[lane].submit(self.lane_exe[lane].call, [out], [self.lane_in[lane]], False)
+            self.lane_pending[lane].append(issued)
+            if self.gathered is not None:
+                # the collectives stay on this thread, in step order on every rank: the gather of the PREVIOUS step goes out
+                # now (its launches have been issued by the time this step's have been handed over)
+                self._flush_gather()
+                self.gather_due = (issued, k, st)
             return
         self.lane_exe[lane].call([out], [self.lane_in[lane]], validate=False)
         if self.gathered is not None:
             self.logits_read[k] = self._gather_beside_next_step(self.logits2[k], st)
+
+    def _flush_gather(self):
+        if self.gather_due is not None:
+            issued, k, st = self.gather_due
+            issued.result()
+            self.logits_read[k] = self._gather_beside_next_step(self.logits2[k], st)
+            self.gather_due = None
 
     def begin(self):
         """the second lane starts no earlier than the timed region's opening event on the first"""
@@ -300,6 +314,8 @@ class ResNet50:
             for f in pending:
                 f.result()
             del pending[:]
+        if self.gathered is not None:
+            self._flush_gather()
         for st in self.lane_streams[1:]:
             self.torch.cuda.current_stream().wait_stream(st)
         if self.gather_stream is not None:
