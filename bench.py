@@ -199,8 +199,9 @@ class ResNet50:
                 "weights": "random He-normal, per-channel i8; activation scales from a seeded 8-image calibration",
                 "parallelism": "batch-sharded replicas, outputs gathered with NCCL all_gather",
                 "pipeline_depth": self.pipeline,
-                "pipeline": "two executables of the same Function on two CUDA streams, steps alternate between them: two batches "
-                            "in flight per GPU" if self.pipeline == 2 else "one executable, one stream",
+                "pipeline": ("%d executables of the same Function on %d CUDA streams, steps rotate over them: %d batches "
+                             "in flight per GPU" % (self.pipeline, self.pipeline, self.pipeline)) if self.pipeline > 1
+                            else "one executable, one stream",
                 "l2": "per-step activation working set (~2 GB) >> 126 MB L2"}
 
     def build_model(self):
@@ -224,29 +225,30 @@ class ResNet50:
         x = np.tile(x, ((self.batch + x.shape[0] - 1) // x.shape[0], 1, 1, 1))[:self.batch]
         self.x_dev = torch.from_numpy(x).cuda()
         # two result buffers: with several GPUs the gather of step i runs on a stream of its own beside step i + 1
-        self.logits2 = [torch.empty((self.batch, model.classes), dtype=torch.float32, device="cuda") for _ in range(2)]
+        self.nbuf = max(2, self.pipeline)
+        self.logits2 = [torch.empty((self.batch, model.classes), dtype=torch.float32, device="cuda") for _ in range(self.nbuf)]
         self.t_out2 = [self.backend.create_tensor(np.float32, tuple(b.shape), b.data_ptr()) for b in self.logits2]
         self.logits, self.t_out = self.logits2[0], self.t_out2[0]
         self.t_in = self.backend.create_tensor(np.float32, x.shape, self.x_dev.data_ptr())
         self.gather_stream = torch.cuda.Stream() if world > 1 else None
         self.step_i = 0
-        self.logits_read = [None, None]
+        self.logits_read = [None] * self.nbuf
         # Pipeline depth 2, on the client side and through the public API only: a second Backend on a second CUDA stream
         # compiles the same Function, and the timed steps alternate between the two executables, so that two batches are in
         # flight and the tail of one batch's kernels overlaps the head of the other's (what nGraph's own nbench does with
         # --double_buffer for the copies).  Every step is still one [B,3,224,224] batch through the unchanged graph.
-        self.lane_streams = [torch.cuda.current_stream(), torch.cuda.Stream()] if self.pipeline == 2 else [torch.cuda.current_stream()]
+        self.lane_streams = [torch.cuda.current_stream()] + [torch.cuda.Stream() for _ in range(self.pipeline - 1)]
         self.lane_exe, self.lane_in, self.lane_out, self.lane_backends = [self.exe], [self.t_in], [self.t_out2[0]], [self.backend]
         from concurrent.futures import ThreadPoolExecutor
-        self.lane_threads = [ThreadPoolExecutor(max_workers=1) for _ in range(2)]
-        self.lane_pending = [[], []]
+        self.lane_threads = [ThreadPoolExecutor(max_workers=1) for _ in range(self.pipeline)]
+        self.lane_pending = [[] for _ in range(self.pipeline)]
         self.gather_due = None
-        if self.pipeline == 2:
-            b2 = ng.Backend("B200:%d,stream=%d" % (local_rank, self.lane_streams[1].cuda_stream))
+        for lane in range(1, self.pipeline):
+            b2 = ng.Backend("B200:%d,stream=%d" % (local_rank, self.lane_streams[lane].cuda_stream))
             self.lane_backends.append(b2)
             self.lane_exe.append(b2.compile(self.fn))
             self.lane_in.append(b2.create_tensor(np.float32, x.shape, self.x_dev.data_ptr()))  # the same resident input, read only
-            self.lane_out.append(b2.create_tensor(np.float32, tuple(self.logits2[1].shape), self.logits2[1].data_ptr()))
+            self.lane_out.append(b2.create_tensor(np.float32, tuple(self.logits2[lane].shape), self.logits2[lane].data_ptr()))
         # end-to-end loop: two input tensors, so that Tensor::write of the next batch (copy stream) overlaps the
         # kernels of the current one; the pipelined-tensor pattern of nGraph's own nbench
         self.x_pipe = [torch.empty_like(self.x_dev) for _ in range(2)]
@@ -274,14 +276,14 @@ class ResNet50:
         return read  # the buffer may be written again after this event
 
     def step(self):
-        k = self.step_i & 1
+        k = self.step_i % self.nbuf
         self.step_i += 1
-        lane = k if self.pipeline == 2 else 0
+        lane = k if self.pipeline > 1 else 0
         st = self.lane_streams[lane]
         if self.gathered is not None and self.logits_read[k] is not None:
             st.wait_event(self.logits_read[k])  # the gather of two steps ago has read this buffer
-        out = self.lane_out[lane] if self.pipeline == 2 else self.t_out2[k]
-        if self.pipeline == 2:
+        out = self.lane_out[lane] if self.pipeline > 1 else self.t_out2[k]
+        if self.pipeline > 1:
             # one host thread per lane issues that lane's launches (Executable::call only enqueues; ctypes releases the
             # interpreter lock for its duration), so neither stream waits for the other's 58 launches to be issued
             issued = self.lane_threads[lane].submit(self.lane_exe[lane].call, [out], [self.lane_in[lane]], False)
@@ -665,8 +667,8 @@ class QConvLayer(MicroWorkload):
 class QDotLayer(MicroWorkload):
     name, metric, unit, dtype = "qdot", "QuantizedDotBias+Relu int8 throughput", "TOPS", "u8*i8->i32"
 
-    def __init__(self, m=32768):
-        self.M, self.N, self.K = m, 1024, 1024
+    def __init__(self, m=32768, nk=1024):
+        self.M, self.N, self.K = m, nk, nk
 
     def host_inputs(self, seed):
         from oracle import ref
@@ -704,7 +706,7 @@ class QDotLayer(MicroWorkload):
                     self._launch()
 
     def describe(self, world=1):
-        d = {"workload": "QuantizedDotBias+Relu u8[%d,1024] x i8[1024,1024], i32 bias, scale 0.004 -> u8" % self.M,
+        d = {"workload": "QuantizedDotBias+Relu u8[%d,%d] x i8[%d,%d], i32 bias, scale 0.004 -> u8" % (self.M, self.K, self.K, self.N),
              "l2": "rotated over 8 input/output buffers"}
         if self.M <= 8192:
             d["launches"] = "one step = a CUDA graph of 64 back-to-back launches"
@@ -913,7 +915,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (images / rows); for small profiler captures")
-    ap.add_argument("--pipeline", type=int, default=2, choices=[1, 2], help="resnet50: batches in flight per GPU (2 = two "
+    ap.add_argument("--nk", type=int, default=0, help="qdot: reduction length and output width (default 1024 x 1024); with --batch "
+                    "for a square GEMM")
+    ap.add_argument("--pipeline", type=int, default=2, choices=[1, 2, 3, 4], help="resnet50: batches in flight per GPU (2 = two "
                     "executables on two streams, steps alternate; 1 = one executable on one stream)")
     ap.add_argument("--no-per-config", action="store_true", help="skip the short per-workload block of the default run")
     ap.add_argument("--no-peak-probe", action="store_true", help="skip the in-run int8 GEMM peak measurement (profiler captures)")
@@ -923,7 +927,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = WORKLOADS[args.workload](args.batch) if args.batch else WORKLOADS[args.workload]()
+    if args.workload == "qdot" and args.nk:
+        wl = QDotLayer(args.batch or 32768, args.nk)
+    else:
+        wl = WORKLOADS[args.workload](args.batch) if args.batch else WORKLOADS[args.workload]()
     if isinstance(wl, ResNet50):
         wl.pipeline = args.pipeline
 
@@ -990,7 +997,8 @@ def main():
 
     # the same steps without the pipelining (one executable, one stream), for comparison
     ms_single = None
-    if isinstance(wl, ResNet50) and wl.pipeline == 2:
+    if isinstance(wl, ResNet50) and wl.pipeline > 1:
+        depth = wl.pipeline
         wl.pipeline = 1
         for _ in range(3):
             wl.step()
@@ -1003,7 +1011,7 @@ def main():
         s1.record()
         barrier()
         ms_single = s0.elapsed_time(s1)
-        wl.pipeline = 2
+        wl.pipeline = depth
 
     # end to end: pinned host -> device, kernels, device -> pinned host, every step
     for _ in range(2):

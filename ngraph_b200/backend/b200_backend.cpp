@@ -72,6 +72,7 @@
 #include "ngraph/pass/manager.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
 #include "ngraph/util.hpp"
+#include "ngraph/chrome_trace.hpp"
 #include "ngraph/cpio.hpp"
 
 using namespace ngraph;
@@ -2045,6 +2046,11 @@ bool B200Executable::call(const std::vector<std::shared_ptr<runtime::Tensor>>& o
                           const std::vector<std::shared_ptr<runtime::Tensor>>& inputs)
 {
     std::lock_guard<std::mutex> lock(m_call_mutex);
+    // Chrome-trace events like the INTERPRETER's (int_executable.cpp:122,171), written when NGRAPH_ENABLE_TRACING is set:
+    // one for the call and one per lowered step.  Kernels are asynchronous, so with tracing on each step is followed by
+    // a stream synchronisation: the step's event then spans its device time, and the call is no longer asynchronous.
+    const bool tracing = event::Manager::is_tracing_enabled();
+    event::Duration call_event("call", "B200");
     m_ctx->make_current();
     if (inputs.size() != m_function->get_parameters().size() || outputs.size() != m_function->get_results().size())
         throw std::runtime_error("B200 backend: call() tensor count does not match the Function");
@@ -2075,7 +2081,15 @@ bool B200Executable::call(const std::vector<std::shared_ptr<runtime::Tensor>>& o
     for (size_t i = 0; i < m_steps.size(); ++i)
     {
         if (m_perf) cudaEventRecord(m_events[2 * i], st);
-        kernel_check(m_steps[i].run(ptrs, st), m_steps[i].what + " for " + m_steps[i].node->get_name());
+        if (tracing)
+        {
+            event::Duration step_event(m_steps[i].node->description(), "B200",
+                                       "{\"name\": \"" + m_steps[i].node->get_name() + "\", \"kernel\": \"" + m_steps[i].what + "\"}");
+            kernel_check(m_steps[i].run(ptrs, st), m_steps[i].what + " for " + m_steps[i].node->get_name());
+            cuda_check(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+        }
+        else
+            kernel_check(m_steps[i].run(ptrs, st), m_steps[i].what + " for " + m_steps[i].node->get_name());
         if (m_perf) cudaEventRecord(m_events[2 * i + 1], st);
     }
     for (auto& rc : m_result_copies)

@@ -511,3 +511,37 @@ def test_convolution_data_dilation_and_negative_padding(backends, data_dilation,
     plain = ng.Function([interpreter.decomposed_conv(d, ng.constant(filt), ng.constant(bias), ng.constant(scale), np.uint8, True, **geometry)], [d])
     got, exp = run_both(backends, fused, plain, [data])
     same_bits(got[0], exp[0], "fused")
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_chrome_trace_events(tmp_path):
+    """NGRAPH_ENABLE_TRACING (src/ngraph/chrome_trace.hpp:77-130): like INTERPRETER's call (int_executable.cpp:122,171) the
+    plugin's call writes one Duration for the call and one per executed step, category "B200".  The switch is read when
+    libngraph is loaded, so the traced run is a process of its own."""
+    import json
+    import subprocess
+    import sys
+    script = (
+        "import sys, numpy as np\n"
+        "sys.path.insert(0, %r)\n"
+        "from ngraph_b200 import ngraph_api as ng\n"
+        "b = ng.Backend('B200')\n"
+        "p = ng.parameter(np.float32, (4, 64))\n"
+        "q = ng.quantize(p, np.float32(0.05), np.array(128, np.uint8), np.uint8, (), 4)\n"
+        "fn = ng.Function([ng.dequantize(q, np.float32(0.05), np.array(128, np.uint8), ())], [p])\n"
+        "out = b.compile(fn).run(np.ones((4, 64), np.float32))\n"
+        "assert out[0].shape == (4, 64)\n" % ROOT)
+    env = dict(os.environ, NGRAPH_ENABLE_TRACING="1")
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=600, cwd=str(tmp_path), env=env)
+    assert done.returncode == 0, done.stderr[-2000:]
+    text = (tmp_path / "runtime_event_trace.json").read_text()
+    # the file is a JSON array that the library closes at exit; tolerate a missing bracket
+    text = text.strip().rstrip(",")
+    if not text.endswith("]"):
+        text += "]"
+    events = [e for e in json.loads(text) if e.get("cat") == "B200"]
+    names = [e["name"] for e in events]
+    assert "call" in names and "Quantize" in names and "Dequantize" in names, names
+    step = [e for e in events if e["name"] == "Quantize"][0]
+    assert step["args"]["kernel"] and step["dur"] >= 0
