@@ -72,6 +72,7 @@
 #include "ngraph/pass/manager.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
 #include "ngraph/util.hpp"
+#include "multi_device.hpp"
 #include "ngraph/chrome_trace.hpp"
 #include "ngraph/cpio.hpp"
 
@@ -339,6 +340,39 @@ void B200Tensor::read(void* p, size_t n) const
                                  std::to_string(code) + ")");
 }
 
+void B200Tensor::write_async(const void* p, size_t offset, size_t n)
+{
+    if (offset > m_bytes || n > m_bytes - offset)
+        throw std::out_of_range("B200Tensor::write: access past the end of the tensor");
+    m_ctx->make_current();
+    order_copy_after_use();
+    cuda_check(cudaMemcpyAsync(static_cast<char*>(m_ptr) + offset, p, n, cudaMemcpyHostToDevice, m_ctx->copy_stream), "cudaMemcpy H2D");
+}
+
+void B200Tensor::read_async(void* p, size_t offset, size_t n) const
+{
+    if (offset > m_bytes || n > m_bytes - offset)
+        throw std::out_of_range("B200Tensor::read: access past the end of the tensor");
+    m_ctx->make_current();
+    order_copy_after_use();
+    cuda_check(cudaMemcpyAsync(p, static_cast<const char*>(m_ptr) + offset, n, cudaMemcpyDeviceToHost, m_ctx->copy_stream), "cudaMemcpy D2H");
+}
+
+void B200Tensor::finish_copies() const
+{
+    m_ctx->make_current();
+    cuda_check(cudaStreamSynchronize(m_ctx->copy_stream), "cudaStreamSynchronize");
+    int code = 0;
+    if (b200_device_status(&code) != B200_OK)
+        throw std::runtime_error("B200 backend: a kernel gave up on a bounded wait (device status " + std::to_string(code) + ")");
+}
+
+void B200Tensor::order_copies_after(cudaEvent_t event) const
+{
+    m_ctx->make_current();
+    cuda_check(cudaStreamWaitEvent(m_ctx->copy_stream, event, 0), "cudaStreamWaitEvent");
+}
+
 void B200Tensor::copy_from(const runtime::Tensor& source)
 {
     auto src = dynamic_cast<const B200Tensor*>(&source);
@@ -465,8 +499,12 @@ bool B200Backend::is_supported(const Node& node) const
 
 extern "C" B200_BACKEND_API void ngraph_register_b200_backend()
 {
-    runtime::BackendManager::register_backend(
-        "B200", [](const std::string& config) { return std::make_shared<B200Backend>(config); });
+    // "B200" / "B200:<device>[,stream=...]": one device; "B200:all" / "B200:0+1+...": several devices behind one Backend
+    runtime::BackendManager::register_backend("B200", [](const std::string& config) -> std::shared_ptr<runtime::Backend> {
+        if (ShardedBackend::wants(config))
+            return std::make_shared<ShardedBackend>(config);
+        return std::make_shared<B200Backend>(config);
+    });
 }
 
 // ------------------------------------------------------------------------------------ executable: compile

@@ -3,7 +3,8 @@
 // ngraph_register_b200_backend() (src/ngraph/runtime/backend_manager.cpp:78-142 in nGraph).
 //
 // Backend options (the text after ':' in Backend::create("B200:<options>")):
-// "<CUDA device ordinal>[,stream=<cudaStream_t as an integer>]", default device 0 and a stream of its own.
+// "<CUDA device ordinal>[,stream=<cudaStream_t as an integer>]", default device 0 and a stream of its own; or "all" /
+// "<ordinal>+<ordinal>...": several devices behind one Backend (multi_device.hpp).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -59,6 +60,13 @@ namespace ngraph
                 void read(void* p, size_t n) const override;
                 void copy_from(const runtime::Tensor& source) override;
                 void* device_ptr() const { return m_ptr; }
+                // The pieces write() / read() are made of, for a caller that keeps copies to several devices in flight at
+                // once (the multi-device tensor): enqueue on this tensor's copy stream, then wait for them.
+                void write_async(const void* p, size_t offset, size_t n);
+                void read_async(void* p, size_t offset, size_t n) const;
+                void finish_copies() const; // waits for the copy stream; raises on a device status word
+                // orders this tensor's next copies after `event` (recorded on another device's stream)
+                void order_copies_after(cudaEvent_t event) const;
                 // called by Executable::call after its last kernel: later write()s and read()s of this tensor wait for it
                 void mark_used(cudaStream_t compute_stream);
                 const std::shared_ptr<DeviceContext>& context() const { return m_ctx; }

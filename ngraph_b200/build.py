@@ -90,14 +90,15 @@ def build_plugin(force=False):
     """g++ the nGraph backend plugin against nGraph's headers and libngraph.so.  Skipped (returns None)
     where nGraph's headers or library are not available: the prebuilt .so is used there."""
     inc = ngraph_include_dir()
-    src = [os.path.join(HERE, "backend", f) for f in ("b200_backend.cpp", "quant_fusion.cpp", "graph_passes.cpp", "function_io.cpp",
-                                                      "b200_backend.hpp", "quant_fusion.hpp", "graph_passes.hpp", "function_io.hpp")]
+    cpp = ("b200_backend.cpp", "quant_fusion.cpp", "graph_passes.cpp", "function_io.cpp", "batch_split.cpp", "multi_device.cpp")
+    src = [os.path.join(HERE, "backend", f) for f in cpp + ("b200_backend.hpp", "quant_fusion.hpp", "graph_passes.hpp", "function_io.hpp",
+                                                            "batch_split.hpp", "multi_device.hpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return PLUGIN_LIB if os.path.exists(PLUGIN_LIB) else None
     build_kernels()
     if not force and _newer(PLUGIN_LIB, src + [KERNEL_LIB]):
         return PLUGIN_LIB
-    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden", src[0], src[1], src[2], src[3], "-o", PLUGIN_LIB,
+    cmd = ["/usr/bin/g++"] + host_cxx_flags(inc) + ["-shared", "-fvisibility=hidden"] + src[:len(cpp)] + ["-o", PLUGIN_LIB,
            "-L" + HERE, "-lb200_kernels", "-L" + NGRAPH_LIB_DIR, "-lngraph", "-L/usr/local/cuda/lib64", "-lcudart_static",
            "-ldl", "-lrt", "-lpthread", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../oracle/_ref/lib"]
     subprocess.check_call(cmd)
@@ -113,10 +114,11 @@ def build_capi(force=False):
     # the plugin's device-free graph passes are compiled in as well (tests look at the graph compile() would lower)
     srcs = [os.path.join(HERE, "harness", "ng_capi.cpp"), os.path.join(HERE, "harness", "bert_int8.cpp"),
             os.path.join(HERE, "backend", "graph_passes.cpp"), os.path.join(HERE, "backend", "quant_fusion.cpp"),
-            os.path.join(HERE, "backend", "function_io.cpp")]
+            os.path.join(HERE, "backend", "function_io.cpp"), os.path.join(HERE, "backend", "batch_split.cpp")]
     if inc is None or not os.path.exists(os.path.join(NGRAPH_LIB_DIR, "libngraph.so")):
         return CAPI_LIB if os.path.exists(CAPI_LIB) else None
-    if not force and _newer(CAPI_LIB, srcs + [os.path.join(HERE, "backend", "graph_passes.hpp"), os.path.join(HERE, "backend", "quant_fusion.hpp")]):
+    if not force and _newer(CAPI_LIB, srcs + [os.path.join(HERE, "backend", "graph_passes.hpp"), os.path.join(HERE, "backend", "quant_fusion.hpp"),
+                                           os.path.join(HERE, "backend", "batch_split.hpp")]):
         return CAPI_LIB
     flags = [f for f in host_cxx_flags(inc) if f != "-std=c++14"] + ["-std=c++11"]
     cmd = ["/usr/bin/g++"] + flags + ["-shared"] + srcs + ["-o", CAPI_LIB, "-L" + NGRAPH_LIB_DIR, "-lngraph", "-ldl",

@@ -19,6 +19,7 @@
 #include "ngraph/runtime/backend.hpp"
 #include "ngraph/runtime/backend_manager.hpp"
 #include "../backend/function_io.hpp"
+#include "../backend/batch_split.hpp"
 #include "../backend/graph_passes.hpp"
 #include <fstream>
 
@@ -398,6 +399,40 @@ NGC_API void* ngc_function_after_b200_passes(void* function, int decompose_all)
             throw;
         }
         return copy;
+    }, nullptr);
+}
+
+// The batch split of the multi-device backend option (ngraph_b200/backend/batch_split.cpp, compiled into this library as well):
+// a new Function for `rows` of the batch, from a copy of `function` after the plugin's passes; nullptr when the graph
+// cannot be split (ngc_last_error() then says why).  split_flags receives one byte per Parameter, then one per Result.
+// shapes_out receives rank + extents (8 slots) per Parameter, then per Result, of the split Function.
+NGC_API void* ngc_function_split_batch(void* function, int64_t rows, unsigned char* split_flags, int64_t* shapes_out)
+{
+    return guarded([&]() -> void* {
+        std::shared_ptr<Function> lowered = clone_function(**static_cast<std::shared_ptr<Function>*>(function));
+        runtime::b200::run_graph_passes(lowered);
+        runtime::b200::BatchSplit split;
+        std::string why;
+        if (!runtime::b200::split_batch(*lowered, size_t(rows), split, why))
+            throw std::runtime_error("not split: " + why);
+        size_t k = 0, slot = 0;
+        auto put_shape = [&](const Shape& sh) {
+            shapes_out[9 * slot] = int64_t(sh.size());
+            for (size_t i = 0; i < sh.size() && i < 8; ++i)
+                shapes_out[9 * slot + 1 + i] = int64_t(sh[i]);
+            ++slot;
+        };
+        for (size_t i = 0; i < split.parameter_split.size(); ++i)
+        {
+            split_flags[k++] = split.parameter_split[i];
+            put_shape(split.function->get_parameters()[i]->get_output_shape(0));
+        }
+        for (size_t i = 0; i < split.result_split.size(); ++i)
+        {
+            split_flags[k++] = split.result_split[i];
+            put_shape(split.function->get_results()[i]->get_output_shape(0));
+        }
+        return new std::shared_ptr<Function>(split.function);
     }, nullptr);
 }
 

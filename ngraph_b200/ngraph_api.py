@@ -62,6 +62,7 @@ def capi():
             "ngc_batch_mat_mul": (vp, [vp, vp]),
             "ngc_quantized_concat": (vp, [pvp, pvp, pvp, ci, i64]),
             "ngc_function_after_b200_passes": (vp, [vp, ci]),
+            "ngc_function_split_batch": (vp, [vp, i64, ctypes.c_char_p, p64]),
             "ngc_compile": (vp, [vp, vp, ci]), "ngc_executable_free": (None, [vp]),
             "ngc_executable_save": (ci, [vp, ctypes.c_char_p]), "ngc_backend_load": (vp, [vp, ctypes.c_char_p]),
             "ngc_function_roundtrip": (vp, [vp, p64]),
@@ -330,6 +331,24 @@ def after_b200_passes(function, decompose_all=False):
     if not h:
         _err("after_b200_passes")
     return BuiltFunction(h, list(function.params), list(function.results), "after_b200_passes")
+
+
+def split_batch(function, rows):
+    """The Function the multi-device backend option ("B200:all") gives each device: `function` (after the plugin's passes) for
+    `rows` of its batch.  Returns (split Function, [is Parameter i split], [is Result j split]); raises NgraphError with the
+    reason when the graph cannot be proven independent along the batch.  Needs no device."""
+    n = len(function.params) + len(function.results)
+    flags = ctypes.create_string_buffer(n)
+    shapes = (ctypes.c_int64 * (9 * n))()
+    h = capi().ngc_function_split_batch(function.h, rows, flags, shapes)
+    if not h:
+        _err("split_batch")
+    specs = []
+    for i, old in enumerate(list(function.params) + list(function.results)):
+        rank = shapes[9 * i]
+        specs.append(_Spec(old.dtype, tuple(shapes[9 * i + 1 + k] for k in range(rank))))
+    np_, f = len(function.params), [bool(b) for b in flags.raw]
+    return BuiltFunction(h, specs[:np_], specs[np_:], "split_batch"), f[:np_], f[np_:]
 
 
 def function_roundtrip(function):
