@@ -194,6 +194,49 @@ namespace b200
         return (x != x) ? 0 : r; // NaN -> 0, as clamp_cast
     }
 
+    // Four elements at once for the directed modes (round toward infinity / zero / up / down), without a test per element on
+    // the way.  For the admitted scales (2^-40 <= |s| < 2^41) q1 below is the correctly rounded x / s whenever nothing
+    // underflows, and where something does (|x| < 2^-60, hence |x / s| < 2^-20) it still is within one denormal step of it.
+    // A directed rounding of a quotient of magnitude below 1 depends only on its sign and on whether it is zero, so q1 can
+    // only give a wrong integer when the IEEE quotient is 0 or +-2^-149 and q1 is the other of the two: |q1| <= 2^-149.
+    // Those (and every x = 0, harmlessly) are settled exactly: RN(x / s) != 0  <=>  |x| / |s| > 2^-150 (a tie at 2^-150 goes to
+    // the even neighbour, 0)  <=>  |x| * 2^126 > |s| * 2^-24, both products exact here (|x| <= 2^-148 * 2^41; |s| * 2^-24 is
+    // normal).  `s_low` = |s| * 2^-24.  One test per group of four on the common path.
+    template <int MODE>
+    __device__ __forceinline__ void quantize4_directed_fast(const float4& x4, float s, float y, float s_low, int lo_minus_zp,
+                                                            int hi_minus_zp, int zp, int (&r)[4])
+    {
+        const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+        float q[4];
+        bool risky = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const float q0 = __fmul_rn(x[i], y);
+            const float e = __fmaf_rn(-q0, s, x[i]);
+            const float q1 = __fmaf_rn(e, y, q0);
+            q[i] = (fabsf(q0) < 16777216.0f) ? q1 : q0;
+            risky = risky || fabsf(q[i]) <= 1.401298464e-45f;
+        }
+        if (risky)
+        {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (fabsf(q[i]) <= 1.401298464e-45f)
+                {
+                    const bool nonzero = __fmul_rn(fabsf(x[i]), 8.507059173e37f) > s_low; // 2^126
+                    const uint32_t sign = (__float_as_uint(x[i]) ^ __float_as_uint(s)) & 0x80000000u;
+                    q[i] = __uint_as_float(sign | (nonzero ? 1u : 0u)); // +-2^-149 or +-0
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const int v = min(max(round_quant_to_int<MODE>(q[i]), lo_minus_zp), hi_minus_zp) + zp;
+            r[i] = (x[i] != x[i]) ? 0 : v; // NaN -> 0, as clamp_cast
+        }
+    }
+
     template <typename Q>
     __device__ __forceinline__ int quantize_rne_fast(float x, float s, float y, int lo_minus_zp, int hi_minus_zp, int zp)
     {

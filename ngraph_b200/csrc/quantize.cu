@@ -81,6 +81,7 @@ namespace b200
         // int32 output can be large enough for the last bit of a quotient beyond 2^24 to matter)
         const bool fast = FAST && sizeof(Q) == 1 && scale_allows_fast_division(s);
         const float y = __frcp_rn(s);
+        const float s_low = __fmul_rn(fabsf(s), 5.9604644775390625e-8f); // |s| * 2^-24 (quantize4_directed_fast)
         const int zi = static_cast<int>(zp[sidx]);
         const int lo = sizeof(Q) == 1 ? int(QLimits<Q>::lo) - zi : 0, hi = sizeof(Q) == 1 ? int(QLimits<Q>::hi) - zi : 0; // 8-bit path only
 
@@ -98,11 +99,20 @@ namespace b200
             int64_t off = (int64_t(u) * QT + threadIdx.x) * 4;
             if (off + 4 <= rem && fast)
             {
-                store4<Q>(op + off,
-                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].x, s, y, lo, hi, zi)),
-                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].y, s, y, lo, hi, zi)),
-                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].z, s, y, lo, hi, zi)),
-                          static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].w, s, y, lo, hi, zi)));
+                constexpr bool directed = MODE == B200_ROUND_TOWARD_INFINITY || MODE == B200_ROUND_TOWARD_ZERO ||
+                                          MODE == B200_ROUND_UP || MODE == B200_ROUND_DOWN;
+                if (directed)
+                {
+                    int r[4];
+                    quantize4_directed_fast<MODE>(v[u], s, y, s_low, lo, hi, zi, r);
+                    store4<Q>(op + off, static_cast<Q>(r[0]), static_cast<Q>(r[1]), static_cast<Q>(r[2]), static_cast<Q>(r[3]));
+                }
+                else
+                    store4<Q>(op + off,
+                              static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].x, s, y, lo, hi, zi)),
+                              static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].y, s, y, lo, hi, zi)),
+                              static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].z, s, y, lo, hi, zi)),
+                              static_cast<Q>(quantize_int_fast<Q, MODE>(v[u].w, s, y, lo, hi, zi)));
             }
             else if (off + 4 <= rem)
             {

@@ -191,7 +191,9 @@ def test_fast_division_is_exact_for_every_float_in_the_other_round_modes(ops, mo
     base = torch.arange(chunk, dtype=torch.int64, device="cuda")
     for qdt, zpv in ((torch.uint8, 128), (torch.int8, 0)):
         zp = torch.full((), zpv, dtype=qdt, device="cuda")
-        for sv in (0.05, 3.0, 7.0 / 255.0, 1.0000001, 0.0137):
+        # 1.5e6 / 3e-9 / 2^40: scales for which the quotient of small inputs underflows (the directed modes then depend on
+        # whether the IEEE quotient is zero or the smallest denormal)
+        for sv in (0.05, 3.0, 7.0 / 255.0, 1.0000001, 0.0137, 1.5e6, 3e-9, 1.0995116e12):
             s = torch.full((), float(np.float32(sv)), device="cuda")
             for c in range(16):
                 x = (base + c * chunk).to(torch.int32).view(torch.float32) if c < 8 else \
