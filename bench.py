@@ -1084,6 +1084,12 @@ def main():
             extra = wl.extra_cpu_baselines() if hasattr(wl, "extra_cpu_baselines") else None
             if extra:
                 line.update(extra)
+            # the end-to-end figure over each host baseline of this run (vs_baseline stays null: no published number
+            # exists for this metric)
+            for key in ("cpu_baseline", "cpu_baseline_onednn_proxy"):
+                base = line.get(key)
+                if isinstance(base, dict) and base.get("value") and base.get("unit") == e2e.get("unit"):
+                    base["e2e_over_this_baseline"] = e2e["value"] / base["value"]
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
