@@ -66,16 +66,60 @@ namespace b200
             return ok != 0;
         }
 
+        // The same with cluster scope, for a barrier that threads of the peer CTA arrive on (mbar_arrive_remote), as a plain
+        // test (no system-chosen nap between polls).
+        __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+        {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t"
+                ".reg .pred P;\n\t"
+                "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, P;\n\t"
+                "}"
+                : "=r"(ok)
+                : "r"(bar), "r"(parity)
+                : "memory");
+            return ok != 0;
+        }
+
+        // ---- thread-block clusters (CTA pairs) ----------------------------------------------------
+        __device__ __forceinline__ uint32_t cluster_ctarank()
+        {
+            uint32_t r;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+            return r;
+        }
+        // every thread of every CTA of the cluster arrives, then waits: a cluster-wide __syncthreads
+        __device__ __forceinline__ void cluster_sync()
+        {
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+        // the address, in the cluster's shared window, of this CTA's shared-memory address `addr` in CTA `rank`
+        __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
+        {
+            uint32_t r;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+            return r;
+        }
+        // arrive on a barrier of another CTA of the cluster (address from mapa)
+        __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
+        {
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+        }
+
         // Bounded wait: gives up after `limit_ns` (or as soon as another thread of the CTA
         // has given up), records that in *abort_flag and returns false.  Never spins forever.
         // `backoff_ns` > 0 sleeps between polls so that a waiting warp does not take issue slots
         // from the warps that do the arithmetic on the same scheduler.
+        template <bool CLUSTER_SCOPE = false>
         __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   uint32_t backoff_ns = 0, uint64_t limit_ns = 2000000000ull)
         {
             uint32_t spins = 0;
             uint64_t t0 = 0;
-            while (!mbar_try_wait(bar, parity))
+            while (!(CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)))
             {
                 if (backoff_ns)
                     __nanosleep(backoff_ns);
@@ -138,6 +182,21 @@ namespace b200
         {
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
         }
+        // The same for a CTA pair (cta_group::2): the allocating warp of BOTH CTAs issues each of these, the pair gets the
+        // same columns in both tensor memories.
+        __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols)
+        {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                         : "memory");
+        }
+        __device__ __forceinline__ void tmem_relinquish_pair()
+        {
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        }
+        __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+        {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+        }
         __device__ __forceinline__ void tc_fence_before_sync()
         {
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -158,6 +217,30 @@ namespace b200
                 "}"
                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                 : "memory");
+        }
+        // One instruction for a CTA pair: D is 256 rows (128 in each CTA's tensor memory), A comes from both CTAs' shared
+        // memory at the descriptor's offset (128 rows each), B likewise (N / 2 rows each).  Issued by ONE thread of the
+        // even CTA of the pair.
+        __device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t accumulate)
+        {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+                "}"
+                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                : "memory");
+        }
+        // Arrive, in BOTH CTAs of the pair, on the barrier at this shared-memory offset once every pair MMA issued so far
+        // by this thread has completed (the multicast is of the barrier arrival, not of data).
+        __device__ __forceinline__ void mma_commit_pair(uint32_t bar)
+        {
+            const uint16_t both = 3;
+            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                         ::"r"(bar), "h"(both)
+                         : "memory");
         }
         // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
         __device__ __forceinline__ void mma_commit(uint32_t bar)

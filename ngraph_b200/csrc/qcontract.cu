@@ -42,6 +42,11 @@ namespace b200
     // debug build only: wait cycles per role of CTA 0 ([0] producer/empty, [1] mma/full, [2] mma/tempty,
     // [3] epilogue/tfull, [4] epilogue body, [5] kernel total, [6] tiles of CTA 0)
     __device__ long long g_wait_cycles[16];
+    // CTA pairs: %globaltimer stamps of the first 64 stage uses of pair 0: [0] even CTA commits the stage's MMAs, [1] odd CTA's
+    // producer sees the stage free, [2] odd CTA's relay sees the stage landed, [3] even CTA sees the relayed arrival,
+    // [4] even CTA's producer sees the stage free, [5] even CTA sees its own stage landed
+    __device__ unsigned long long g_pair_stamps[6][64];
+#define PAIR_STAMP(row, i) do { if (CTA2 && worker == 0 && (i) < 64) g_pair_stamps[row][i] = ptx::globaltimer(); } while (0)
 #define PROF_MARK(var) long long var = clock64()
 #define PROF_SPAN(i, a, b) do { if (blockIdx.x == 0 && warp == 4 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[i]), (unsigned long long)((b) - (a))); } while (0)
 #define PROF_T0() long long prof_t0 = clock64()
@@ -51,6 +56,7 @@ namespace b200
 #define PROF_ADD(i) do { } while (0)
 #define PROF_MARK(var) do { } while (0)
 #define PROF_SPAN(i, a, b) do { } while (0)
+#define PAIR_STAMP(row, i) do { } while (0)
 #endif
 
     __device__ int g_contract_status = 0; // 0 ok; otherwise 1000*role + detail of the wait that gave up
@@ -110,6 +116,14 @@ namespace b200
         int tma_sum;         // the residual is fetched by TMA into the staging block its result will be stored from
         int vec_params;      // scale / bias pointers are 16-byte aligned
         int pair;            // 1, or 2: a CTA works on two row tiles (2u, 2u + 1) at a time, which share every B stage
+        int cta2;            // CTA pairs (thread-block clusters of two, tcgen05 cta_group::2): the pair works on row tiles 2u and
+                             // 2u + 1 of a 256-wide column tile with ONE 256 x 256 instruction stream; each CTA loads its own
+                             // 128 rows of A and its own half (128 rows) of the B tile, holds its 128 rows of the accumulator
+                             // in its own tensor memory and runs its own epilogue.  Correct (the contraction tests pass with it
+                             // forced on) but measured at half the rate of two row tiles per CTA on large matrix products
+                             // (8192^3: 1.5 against 3.0 POP/s): with the same bytes in flight per SM the stage loop is twice
+                             // as long (free -> landed takes 3 us per 32 KB stage, six stages per 4 us).  Never chosen; the
+                             // variant is compiled into instrumented builds only, which can force it.
         void* out;
         uint32_t idesc;
         SmemPlan smem;
@@ -125,7 +139,10 @@ namespace b200
     };
 
     constexpr int BM = 128;
-    constexpr int NUM_PRODUCERS = 3;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
+#ifndef B200_NUM_PRODUCERS
+#define B200_NUM_PRODUCERS 3
+#endif
+    constexpr int NUM_PRODUCERS = B200_NUM_PRODUCERS;  // TMA issue is serialised per warp (about 6-8 cycles per box row): three warps share the k-blocks
     constexpr int NUM_THREADS = 640; // warp 0: MMA issue, warps 1-3: TMA producers, warps 4-19: epilogue
     constexpr int EPI_WARPS = 16;
     constexpr int COLS = 64;         // output columns (= bytes of a one-byte row) per epilogue warp and tile
@@ -154,7 +171,7 @@ namespace b200
                        BACKOFF_TEMPTY_NS = B200_BACKOFF_TEMPTY_NS, BACKOFF_TFULL_NS = B200_BACKOFF_TFULL_NS;
 
     constexpr int MAX_STAGES = 40;          // small stages (the stem's 2 KB cell runs) need many in flight to cover the load latency
-    constexpr int BAR_BYTES = 2048;         // 2*MAX_STAGES + 2*MAX_ACC + 1 + 3*EPI_WARPS mbarriers of 8 bytes
+    constexpr int BAR_BYTES = 2048;         // 3*MAX_STAGES + 2*MAX_ACC + 1 + 3*EPI_WARPS mbarriers of 8 bytes
     constexpr int B_RESIDENT_MAX = 73728;   // a whole filter / weight matrix up to this size stays in shared memory
 
     template <int BN, int BK>
@@ -421,12 +438,18 @@ namespace b200
         }
     }
 
-    template <int BN, int BK>
+    template <int BN, int BK, bool CTA2 = false>
     __global__ void __launch_bounds__(NUM_THREADS, 1)
         qcontract_kernel(const __grid_constant__ TensorMaps maps, const __grid_constant__ ContractParams p)
     {
         using C = Cfg<BN, BK>;
         constexpr int SPLIT = C::SPLIT, GROUPS = C::GROUPS, NACC = C::NACC;
+        // CTA pairs: rank 0 issues the pair's MMAs; a "worker" is what takes units of work in turn (a CTA, or a pair)
+        const uint32_t cta_rank = CTA2 ? ptx::cluster_ctarank() : 0u;
+        const int worker = CTA2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
+        const int nworkers = CTA2 ? int(gridDim.x >> 1) : int(gridDim.x);
+        // bytes of B one CTA stages per k-block: the whole column tile, or this CTA's half of it
+        constexpr uint32_t B_STAGE_BYTES = CTA2 ? uint32_t(C::B_BYTES) / 2 : uint32_t(C::B_BYTES);
 #ifdef B200_PROFILE_WAITS
         const unsigned long long prof_entry_ns = ptx::globaltimer();
         const long long prof_entry_clk = clock64();
@@ -452,6 +475,8 @@ namespace b200
         const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 2 * MAX_ACC);
         // residual landed in staging block b of epilogue warp w
         auto sum_bar = [&](int w, int b) { return bars + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 1 + 3 * w + b); };
+        // CTA pairs: stage s of the odd CTA has landed (arrived on from there, in the even CTA's shared memory)
+        auto peer_full_bar = [&](int s) { return bars + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 1 + 3 * EPI_WARPS + s); };
 
         const int warp = threadIdx.x >> 5;
         const int lane = threadIdx.x & 31;
@@ -471,22 +496,34 @@ namespace b200
             else if (t >= 64 && t < 64 + NACC)
             {
                 ptx::mbar_init(tfull_bar(t - 64), 1);
-                ptx::mbar_init(tempty_bar(t - 64), 4 * SPLIT);
+                ptx::mbar_init(tempty_bar(t - 64), (CTA2 ? 8 : 4) * SPLIT); // pairs: both CTAs' epilogue warps hand back to the issuer
             }
             else if (t == 80)
                 ptx::mbar_init(bres_bar, 1);
             else if (t >= 96 && t < 96 + 3 * EPI_WARPS)
                 ptx::mbar_init(sum_bar((t - 96) / 3, (t - 96) % 3), 1);
-            if (t >= 0 && t < 160)
+            else if (CTA2 && t >= 160 && t < 160 + STAGES)
+                ptx::mbar_init(peer_full_bar(t - 160), 1);
+            if (t >= 0 && t < 224)
                 ptx::fence_barrier_init();
         }
         if (warp == 0)
         {
-            ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), C::TMEM_COLS);
-            ptx::tmem_relinquish();
+            if (CTA2)
+            {
+                ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_slot), C::TMEM_COLS);
+                ptx::tmem_relinquish_pair();
+            }
+            else
+            {
+                ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), C::TMEM_COLS);
+                ptx::tmem_relinquish();
+            }
         }
         ptx::tc_fence_before_sync();
         __syncthreads();
+        if (CTA2)
+            ptx::cluster_sync(); // the peer's barriers exist before anything arrives on them from here
         ptx::tc_fence_after_sync();
         const uint32_t tmem_base = tmem_base_slot;
         // everything above touched only this CTA's own state; from here on global memory of earlier kernels is read
@@ -543,6 +580,8 @@ namespace b200
             // this producer's next k-block, as (offset inside the current tile, pipeline stage, stage parity); it advances
             // by NUM_PRODUCERS k-blocks at a time and carries over from tile to tile
             int j = pw, s = pw;
+            int use_p = pw; // running index of this producer's k-block over the whole launch (instrumentation)
+            (void)use_p;
             uint32_t ph = 0;
             while (s >= STAGES)
             {
@@ -551,16 +590,17 @@ namespace b200
             }
             // a unit of work: one tile, or in paired mode the two row tiles 2u and 2u + 1 (the host makes tiles_m even)
             const int pair = p.pair;
-            const int num_units = num_tiles / pair;
-            for (int unit = blockIdx.x; unit < num_units && !fail; unit += gridDim.x)
+            const int num_units = CTA2 ? num_tiles / 2 : num_tiles / pair;
+            for (int unit = worker; unit < num_units && !fail; unit += nworkers)
             {
                 if (idx == 32)
                 {
-                    const long long t = static_cast<long long>(unit) + static_cast<long long>(lane) * gridDim.x;
+                    const long long t = static_cast<long long>(unit) + static_cast<long long>(lane) * nworkers;
                     if (t < num_units)
                     {
                         int tm_, tn_, q0_, p0_, n0_;
-                        decode_tile(p, static_cast<int>(t) * pair, tm_, tn_, q0_, p0_, n0_);
+                        // a pair of CTAs: unit t = row tiles 2t and 2t + 1, this CTA's is 2t + rank
+                        decode_tile(p, CTA2 ? static_cast<int>(t) * 2 + int(cta_rank) : static_cast<int>(t) * pair, tm_, tn_, q0_, p0_, n0_);
                         info_a = p.conv ? q0_ : tm_;
                         info_b = p0_;
                         info_c = n0_;
@@ -590,8 +630,8 @@ namespace b200
                     issued_here = true;
                     const int tm = ia, q0 = ia;
                     // packed weights: this column tile's 64-row blocks of a k-block are one contiguous piece
-                    const int b_blocks = min(BN / 64, p.b_blocks_n - tn * (BN / 64));
-                    const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : uint32_t(C::B_BYTES));
+                    const int b_blocks = CTA2 ? BN / 128 : min(BN / 64, p.b_blocks_n - tn * (BN / 64));
+                    const uint32_t b_bytes = p.smem.b_resident ? 0u : (p.b_packed ? uint32_t(b_blocks) * (64 * BK) : B_STAGE_BYTES);
                     const uint32_t tx_bytes = (p.a_cells ? LINEAR_A_BYTES * uint32_t(p.ntaps) : p.halo ? uint32_t(p.halo_bytes) : uint32_t(C::A_BYTES) * uint32_t(pair)) + b_bytes;
                     int tap = 0, cb = j; // k-block j of the tile = (tap, channel block)
                     while (cb >= p.cblocks)
@@ -609,6 +649,8 @@ namespace b200
                         }
                         if (pw == 0)
                             PROF_ADD(0);
+                        PAIR_STAMP(cta_rank ? 1 : 4, use_p);
+                        use_p += NUM_PRODUCERS;
                         const Tap tp = p.taps[tap];
                         const int kcol = j * BK; // byte column of the k-block in the B matrix
                         const uint32_t a_dst = smem_base + s * stage_bytes;
@@ -643,11 +685,13 @@ namespace b200
                         }
                         if (!p.smem.b_resident)
                         {
+                            // a CTA of a pair stages its own half of the column tile's rows (the map's box is that tall)
                             if (p.b_packed)
-                                ptx::bulk_load(b_dst, p.b_packed + (size_t(j) * p.b_blocks_n + size_t(tn) * (BN / 64)) * (64 * BK), b_bytes,
-                                               full_bar(s));
+                                ptx::bulk_load(b_dst, p.b_packed + (size_t(j) * p.b_blocks_n + size_t(tn) * (BN / 64) +
+                                                                    (CTA2 ? size_t(cta_rank) * (BN / 128) : 0)) * (64 * BK),
+                                               b_bytes, full_bar(s));
                             else
-                                ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN);
+                                ptx::tma_load_2d(b_dst, &maps.b, full_bar(s), kcol, tn * BN + (CTA2 ? int(cta_rank) * (BN / 2) : 0));
                         }
                         // advance to this producer's next k-block
                         cb += NUM_PRODUCERS;
@@ -674,12 +718,50 @@ namespace b200
                 fail = __shfl_sync(0xffffffffu, fail, src);
             }
         }
+        else if (warp >= 1 && warp <= 3)
+        {
+            // warps 1-3 are reserved for the producers; one that is not used as such has nothing to do
+        }
+        else if (warp == 0 && CTA2 && cta_rank != 0)
+        {
+            // ------------------------------------------------------------ odd CTA of a pair: no MMAs are issued here
+            // Its stages are read by the even CTA's instructions.  One thread watches this CTA's "stage landed" barriers in
+            // the order the stages are used and passes each on to the even CTA (release at cluster scope after the wait).
+            if (ptx::elect_one())
+            {
+                int s = 0;
+                int use_r = 0;
+                (void)use_r;
+                uint32_t ph = 0;
+                const int num_kblocks = p.ntaps * p.cblocks;
+                const int num_units = num_tiles / 2;
+                for (int unit = worker; unit < num_units && !fail; unit += nworkers)
+                    for (int kb = 0; kb < num_kblocks; ++kb)
+                    {
+                        if (!ptx::mbar_wait(full_bar(s), ph, abortp, BACKOFF_FULL_NS))
+                        {
+                            fail = 2004;
+                            break;
+                        }
+                        PAIR_STAMP(2, use_r);
+                        ++use_r;
+                        ptx::mbar_arrive_remote(ptx::mapa(peer_full_bar(s), 0));
+                        if (++s == STAGES)
+                        {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+            }
+        }
         else if (warp == 0)
         {
             // ------------------------------------------------------------ MMA issuer
             if (ptx::elect_one())
             {
                 int s = 0;
+                int use_m = 0;
+                (void)use_m;
                 uint32_t ph = 0, tile_it = 0;
                 const int num_kblocks = p.ntaps * p.cblocks;
                 // stem cells: row m of the A tile is the 64 bytes starting at cell m of a linear run, so rows overlap:
@@ -687,19 +769,20 @@ namespace b200
                 const uint64_t a_desc0 = p.a_cells ? ptx::smem_desc_overlapping_rows(smem_base) : ptx::smem_desc_kmajor(smem_base, BK);
                 const int pair = p.pair;
                 const uint64_t b_desc0 = ptx::smem_desc_kmajor(p.smem.b_resident ? bres_base : smem_base + uint32_t(pair) * C::A_BYTES, BK);
+                // CTA pairs: the hardware reads the other 128 rows of A and the other half of B at the same offsets of the odd CTA
                 // descriptor address fields count 16-byte units
                 const uint32_t b_step = p.smem.b_resident ? (C::B_BYTES >> 4) : (stage_bytes >> 4);
                 if (p.smem.b_resident && !ptx::mbar_wait(bres_bar, 0, abortp, BACKOFF_FULL_NS))
                     fail = 2003;
                 // one unit per iteration: a tile, or the two row tiles of a pair (accumulators acc and acc + 1; NACC is even)
-                const int num_units = num_tiles / pair;
-                for (int unit = blockIdx.x; unit < num_units && !fail; unit += gridDim.x, tile_it += pair)
+                const int num_units = CTA2 ? num_tiles / 2 : num_tiles / pair;
+                for (int unit = worker; unit < num_units && !fail; unit += nworkers, tile_it += pair)
                 {
                     const int acc = tile_it % NACC;
                     const uint32_t acc_ph = (tile_it / NACC) & 1;
                     {
                         PROF_T0();
-                        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS) ||
+                        if (!ptx::mbar_wait<CTA2>(tempty_bar(acc), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS) ||
                             (pair == 2 && !ptx::mbar_wait(tempty_bar(acc + 1), acc_ph ^ 1, abortp, BACKOFF_TEMPTY_NS)))
                         {
                             fail = 2001;
@@ -795,6 +878,13 @@ namespace b200
                                 fail = 2002;
                                 break;
                             }
+                            PAIR_STAMP(5, use_m);
+                            if (CTA2 && !ptx::mbar_wait<true>(peer_full_bar(s), ph, abortp, 0))
+                            {
+                                fail = 2002;
+                                break;
+                            }
+                            PAIR_STAMP(3, use_m);
                             PROF_ADD(1);
                         }
                         ptx::tc_fence_after_sync();
@@ -805,8 +895,12 @@ namespace b200
                         for (int k = 0; k < BK / 32; ++k)
                         {
                             // advance 32 bytes (one K=32 int8 MMA) inside the swizzled row: +2 in 16-byte units
-                            ptx::mma_i8(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc,
-                                        (kb | k) != 0 ? 1u : 0u);
+                            if (CTA2)
+                                ptx::mma_i8_pair(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc,
+                                                 (kb | k) != 0 ? 1u : 0u);
+                            else
+                                ptx::mma_i8(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), p.idesc,
+                                            (kb | k) != 0 ? 1u : 0u);
                         }
                         if (pair == 2)
                         {
@@ -816,7 +910,12 @@ namespace b200
                                 ptx::mma_i8(d_tmem + BN, a_desc + uint64_t((C::A_BYTES >> 4) + 2 * k), b_desc + uint64_t(2 * k), p.idesc,
                                             (kb | k) != 0 ? 1u : 0u);
                         }
-                        ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
+                        PAIR_STAMP(0, use_m);
+                        ++use_m;
+                        if (CTA2)
+                            ptx::mma_commit_pair(empty_bar(s)); // in both CTAs
+                        else
+                            ptx::mma_commit(empty_bar(s)); // frees the stage once these MMAs have read it
 #ifdef B200_PROFILE_WAITS
                         if (blockIdx.x == 0)
                             atomicAdd(reinterpret_cast<unsigned long long*>(&g_wait_cycles[7]), (unsigned long long)(clock64() - t_issue0));
@@ -829,7 +928,10 @@ namespace b200
                     }
                     if (fail)
                         break;
-                    ptx::mma_commit(tfull_bar(acc)); // accumulator complete
+                    if (CTA2)
+                        ptx::mma_commit_pair(tfull_bar(acc)); // each CTA's epilogue warps wait on their own copy
+                    else
+                        ptx::mma_commit(tfull_bar(acc)); // accumulator complete
                     if (pair == 2)
                         ptx::mma_commit(tfull_bar(acc + 1));
                 }
@@ -884,8 +986,10 @@ namespace b200
             // tiles 2u and 2u + 1 of the units u = blockIdx, blockIdx + grid, ...
             const int pair = p.pair;
             auto tile_of = [&](uint32_t it) -> long long {
-                return pair == 2 ? 2ll * (static_cast<long long>(blockIdx.x) + static_cast<long long>(it >> 1) * gridDim.x) + (it & 1u)
-                                 : static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * gridDim.x;
+                if (CTA2) // the pair's it-th unit, this CTA's row tile of it
+                    return 2ll * (static_cast<long long>(worker) + static_cast<long long>(it) * nworkers) + cta_rank;
+                return pair == 2 ? 2ll * (static_cast<long long>(worker) + static_cast<long long>(it >> 1) * nworkers) + (it & 1u)
+                                 : static_cast<long long>(worker) + static_cast<long long>(it) * nworkers;
             };
             // One thread per warp issues the warp's TMA loads / stores, bulk-group waits and barrier arrivals.  It is
             // chosen by elect.sync at points where the warp is converged: the election is deterministic for a full
@@ -1220,7 +1324,12 @@ namespace b200
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (ptx::elect_one())
-                        ptx::mbar_arrive(tempty_bar(acc));
+                    {
+                        if (CTA2 && cta_rank != 0)
+                            ptx::mbar_arrive_remote(ptx::mapa(tempty_bar(acc), 0)); // the issuing thread lives in the even CTA
+                        else
+                            ptx::mbar_arrive(tempty_bar(acc));
+                    }
                     if (FAST || (!F_F32 && p.tma_store))
                     {
                         // make the generic-proxy writes visible to the TMA unit, then one lane stores the block;
@@ -1294,10 +1403,15 @@ namespace b200
                 __nanosleep(1000);
             __syncthreads();
         }
+        if (CTA2)
+            ptx::cluster_sync(); // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
         if (warp == 0)
         {
             ptx::tc_fence_after_sync();
-            ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+            if (CTA2)
+                ptx::tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+            else
+                ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
         }
 #ifdef B200_PROFILE_WAITS
         if (threadIdx.x == 0)
@@ -1462,12 +1576,33 @@ namespace b200
         cfg.blockDim = dim3(NUM_THREADS);
         cfg.dynamicSmemBytes = size_t(p.smem.total_bytes);
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
+        int nattr = 0;
+        if (pdl)
+        {
+            attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+            ++nattr;
+        }
+        if (p.cta2)
+        {
+            attr[nattr].id = cudaLaunchAttributeClusterDimension; // CTAs 2i and 2i + 1 form a pair
+            attr[nattr].val.clusterDim.x = 2;
+            attr[nattr].val.clusterDim.y = 1;
+            attr[nattr].val.clusterDim.z = 1;
+            ++nattr;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = pdl ? 1 : 0;
+        cfg.numAttrs = unsigned(nattr);
+#ifdef B200_PROFILE_WAITS
+        // the CTA-pair variant is compiled into instrumented builds only (see ContractParams::cta2)
+        cudaError_t le = p.cta2 ? cudaLaunchKernelEx(&cfg, qcontract_kernel<BN, BK, (BN == 256)>, maps, p)
+                                : cudaLaunchKernelEx(&cfg, qcontract_kernel<BN, BK>, maps, p);
+#else
+        if (p.cta2)
+            return B200_ERR_UNSUPPORTED;
         cudaError_t le = cudaLaunchKernelEx(&cfg, qcontract_kernel<BN, BK>, maps, p);
+#endif
         if (le != cudaSuccess)
             return cuda_status(le, "cudaLaunchKernelEx(qcontract_kernel)");
         return after_launch("qcontract_kernel");
@@ -1498,6 +1633,10 @@ namespace b200
         {
             cudaError_t e = cudaFuncSetAttribute(qcontract_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  SMEM_LIMIT);
+#ifdef B200_PROFILE_WAITS
+            if (e == cudaSuccess && BN == 256)
+                e = cudaFuncSetAttribute(qcontract_kernel<BN, BK, (BN == 256)>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+#endif
             if (e != cudaSuccess)
                 return cuda_status(e, "cudaFuncSetAttribute(qcontract)");
             attr_set[dev] = true;
@@ -1512,6 +1651,13 @@ namespace b200
         const int nkb = p.ntaps * p.cblocks;
         SmemPlan& sp = p.smem;
         sp.b_resident = (p.tiles_n == 1 && nkb * C::B_BYTES <= B_RESIDENT_MAX) ? 1 : 0;
+        if (p.cta2)
+        {
+            // CTA pairs: the plain tile pipeline with 256-wide column tiles, an even number of row tiles (the caller pads)
+            if (BN != 256 || p.a_cells || p.halo || p.pair == 2 || (p.tiles_m & 1) || p.N % 256 != 0)
+                return B200_ERR_INVALID_ARGUMENT;
+            sp.b_resident = 0;
+        }
         sp.b_res_bytes = sp.b_resident ? nkb * C::B_BYTES : 0;
         if (p.pair != 2)
             p.pair = 1;
@@ -1521,7 +1667,7 @@ namespace b200
             return B200_ERR_INVALID_ARGUMENT; // the caller pads the row tiles to an even count
         const int tma_store_asked = p.tma_store, tma_sum_asked = p.tma_sum;
     plan_again:
-        sp.stage_bytes = p.pair * C::A_BYTES + (sp.b_resident ? 0 : C::B_BYTES);
+        sp.stage_bytes = p.pair * C::A_BYTES + (sp.b_resident ? 0 : p.cta2 ? C::B_BYTES / 2 : C::B_BYTES);
         if (p.a_cells)
         {
             if (!sp.b_resident)
@@ -1536,7 +1682,7 @@ namespace b200
             sp.stage_bytes = ((p.halo_bytes + 64 * BK + 1023) / 1024) * 1024;
         }
         const int room = SMEM_LIMIT - C::FIXED - sp.b_res_bytes - 64;
-        if (p.tma_store && nkb >= 16 && (room - 2 * C::OUT_BYTES) / sp.stage_bytes < 4)
+        if (p.tma_store && nkb >= 16 && (room - 2 * C::OUT_BYTES) / sp.stage_bytes < (p.cta2 ? 7 : 4))
         {
             // long reductions are MMA-bound: pipeline depth matters more than store efficiency, so the
             // output staging blocks are given to the stage ring and results are written from registers
@@ -1564,6 +1710,8 @@ namespace b200
         sp.total_bytes = sp.b_res_bytes + sp.stages * sp.stage_bytes + sp.out_bytes + C::FIXED;
         int tiles = p.tiles_m * p.tiles_n / p.pair; // units of work: tiles, or pairs of row tiles
         int grid = tiles < num_sms() ? tiles : num_sms();
+        if (p.cta2) // two CTAs per unit of two row tiles
+            grid = 2 * std::min(tiles / 2, num_sms() / 2);
         if (t_capture)
         {
             t_capture->maps = maps;
@@ -1631,11 +1779,11 @@ namespace b200
 
     // tcgen05 instruction descriptor, kind::i8: [4,6) D format (2 = s32), [7,10) A format
     // (0 = u8, 1 = s8), [10,13) B format, bits 15/16 A/B major (0 = K-major), [17,23) N>>3, [24,29) M>>4.
-    static uint32_t make_idesc(int operand_types, int bn)
+    static uint32_t make_idesc(int operand_types, int bn, int m = BM)
     {
         const uint32_t a_fmt = (operand_types & 0xFF) == B200_I8 ? 1u : 0u;
         const uint32_t b_fmt = (operand_types & B200_WEIGHTS_U8) ? 0u : 1u;
-        return (2u << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+        return (2u << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(m >> 4) << 24);
     }
 
     // data / activation type in the low byte, B200_WEIGHTS_U8 for unsigned weights
@@ -1734,6 +1882,12 @@ namespace b200
 }
 
 #ifdef B200_PROFILE_WAITS
+extern "C" __attribute__((visibility("default"))) int b200_debug_pair_stamps(unsigned long long* out_6x64)
+{
+    cudaDeviceSynchronize();
+    return int(cudaMemcpyFromSymbol(out_6x64, b200::g_pair_stamps, sizeof(unsigned long long) * 6 * 64));
+}
+
 extern "C" __attribute__((visibility("default"))) int b200_debug_wait_cycles(long long* out8, int reset)
 {
     long long z[16] = {0};
@@ -1837,11 +1991,18 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
     const int bn = pick_bn(N, p.tiles_m, bk, epilogue && epilogue->sum_in, K);
     p.tiles_n = int((N + bn - 1) / bn);
     p.pair = pick_pair(p.tiles_m, N, bn, bk, p.cblocks, epilogue && epilogue->sum_in, false);
-    if (p.pair == 2)
+#ifdef B200_PROFILE_WAITS
+    if (getenv("B200_FORCE_CTA2") && bn == 256 && N % 256 == 0 && p.tiles_m >= 2 && !(p.tiles_n == 1 && int64_t(p.cblocks) * bn * bk <= B_RESIDENT_MAX))
+    {
+        p.cta2 = 1; // instrumented build only: CTA pairs (measured slower than two row tiles per CTA, see ContractParams::cta2)
+        p.pair = 1;
+    }
+#endif
+    if (p.pair == 2 || p.cta2)
         p.tiles_m = (p.tiles_m + 1) & ~1; // a row tile beyond M loads zeros and stores nothing
     p.conv = 0;
     fill_epilogue(p, epilogue, out, a_type);
-    p.idesc = make_idesc(a_type, bn);
+    p.idesc = make_idesc(a_type, bn, p.cta2 ? 2 * BM : BM);
 
     TensorMaps maps;
     memset(&maps, 0, sizeof(maps));
@@ -1858,7 +2019,7 @@ static int qgemm_impl(const void* A, int a_type, const int8_t* W, bool packed, v
     else
     {
         uint64_t dims_b[2] = {uint64_t(K), uint64_t(N)};
-        uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
+        uint32_t box_b[2] = {uint32_t(bk), uint32_t(p.cta2 ? bn / 2 : bn)}; // a CTA of a pair loads its half of the column tile
         rc = make_map(&maps.b, W, 2, dims_b, str, box_b, bk);
         if (rc != B200_OK)
             return rc;
@@ -2079,10 +2240,18 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     if (getenv("B200_FORCE_PAIR"))
         p.pair = pick_pair(p.tiles_m, c->K, bn, bk, int64_t(p.ntaps) * p.cblocks, epilogue && epilogue->sum_in, p.halo != 0);
 #endif
-    if (p.pair == 2)
+#ifdef B200_PROFILE_WAITS
+    if (getenv("B200_FORCE_CTA2") && bn == 256 && c->K % 256 == 0 && p.tiles_m >= 2 && !p.halo && !p.a_cells &&
+        !(p.tiles_n == 1 && int64_t(p.ntaps) * p.cblocks * bn * bk <= B_RESIDENT_MAX))
+    {
+        p.cta2 = 1; // instrumented build only
+        p.pair = 1;
+    }
+#endif
+    if (p.pair == 2 || p.cta2)
         p.tiles_m = (p.tiles_m + 1) & ~1; // a patch beyond the batch loads zeros and stores nothing
     fill_epilogue(p, epilogue, out, data_type);
-    p.idesc = make_idesc(data_type, bn);
+    p.idesc = make_idesc(data_type, bn, p.cta2 ? 2 * BM : BM);
 
     TensorMaps maps;
     memset(&maps, 0, sizeof(maps));
@@ -2113,7 +2282,7 @@ static int qconv_impl(const void* data, int data_type, const int8_t* filters, bo
     {
         const uint64_t kg = uint64_t(c->R * c->S * c->C);
         uint64_t dims_b[2] = {kg, uint64_t(c->K)}, str_b[1] = {kg};
-        uint32_t box_b[2] = {uint32_t(bk), uint32_t(bn)};
+        uint32_t box_b[2] = {uint32_t(bk), uint32_t(p.cta2 ? bn / 2 : bn)};
         rc = make_map(&maps.b, filters, 2, dims_b, str_b, box_b, bk);
         if (rc != B200_OK)
             return rc;
