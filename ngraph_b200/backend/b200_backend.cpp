@@ -82,8 +82,6 @@ using namespace ngraph::runtime::b200;
 // ------------------------------------------------------------------------------------ helpers
 namespace
 {
-    const char SAVE_INFO[] = "B200 Save File 1.0";
-
     void cuda_check(cudaError_t e, const char* what)
     {
         if (e != cudaSuccess)

@@ -31,6 +31,9 @@ namespace ngraph
     {
         namespace b200
         {
+            // format tag of Executable::save's archive (entry "save_info"); Backend::load refuses any other
+            constexpr char SAVE_INFO[] = "B200 Save File 1.0";
+
             // Per-backend CUDA state: device ordinal and the one stream every tensor copy and
             // kernel of this backend instance is ordered on.
             struct DeviceContext

@@ -4,7 +4,9 @@
 #include <sstream>
 
 #include "b200_kernels.h"
+#include "function_io.hpp"
 #include "graph_passes.hpp"
+#include "ngraph/cpio.hpp"
 #include "ngraph/descriptor/layout/dense_tensor_layout.hpp"
 #include "ngraph/graph_util.hpp"
 
@@ -197,6 +199,7 @@ void IssueThread::loop()
 ShardedExecutable::ShardedExecutable(const std::vector<std::shared_ptr<B200Backend>>& members, const std::shared_ptr<Function>& func,
                                      bool enable_performance_data)
     : m_members(members)
+    , m_function(func)
 {
     set_parameters_and_results(*func);
     for (const auto& m : m_members)
@@ -374,6 +377,15 @@ std::vector<runtime::PerformanceCounter> ShardedExecutable::get_performance_data
     return m_subs[0]->get_performance_data(); // the first device's view (every device runs the same steps)
 }
 
+void ShardedExecutable::save(std::ostream& out)
+{
+    if (!m_split)
+        return m_subs[0]->save(out);
+    auto whole = m_members[0]->compile(m_function, false);
+    whole->save(out);
+    m_members[0]->remove_compiled_function(whole);
+}
+
 std::shared_ptr<runtime::Tensor> ShardedExecutable::create_input_tensor(size_t input_index)
 {
     auto p = get_parameters().at(input_index);
@@ -475,6 +487,23 @@ std::shared_ptr<runtime::Executable> ShardedBackend::compile(std::shared_ptr<Fun
     auto exec = std::make_shared<ShardedExecutable>(m_members, func, enable_performance_data);
     m_cache.insert({key, exec});
     return exec;
+}
+
+std::shared_ptr<runtime::Executable> ShardedBackend::load(std::istream& in)
+{
+    cpio::Reader reader(in);
+    std::string info, model;
+    for (const cpio::FileInfo& f : reader.get_file_info())
+        if (f.get_name() == "save_info" || f.get_name() == "model")
+        {
+            std::vector<char> b = reader.read(f);
+            (f.get_name() == "save_info" ? info : model).assign(b.data(), b.size());
+        }
+    if (info != SAVE_INFO)
+        throw std::runtime_error("B200 backend: not an executable saved by this plugin version (save_info '" + info + "')");
+    if (model.empty())
+        throw std::runtime_error("B200 backend: saved executable lacks its model");
+    return compile(read_function(model));
 }
 
 bool ShardedBackend::is_supported(const Node& node) const

@@ -83,6 +83,9 @@ namespace ngraph
                 bool call(const std::vector<std::shared_ptr<runtime::Tensor>>& outputs,
                           const std::vector<std::shared_ptr<runtime::Tensor>>& inputs) override;
                 std::vector<PerformanceCounter> get_performance_data() const override;
+                /// the archive a single-device executable of the whole Function writes (compiled on the first member for the
+                /// purpose): either form of the backend can load it
+                void save(std::ostream& output_stream) override;
                 std::shared_ptr<runtime::Tensor> create_input_tensor(size_t input_index) override;
                 std::shared_ptr<runtime::Tensor> create_output_tensor(size_t output_index) override;
                 std::vector<std::shared_ptr<runtime::Tensor>> create_input_tensor(size_t input_index, size_t pipeline_depth) override;
@@ -97,6 +100,7 @@ namespace ngraph
 
                 std::vector<std::shared_ptr<B200Backend>> m_members;
                 std::vector<std::shared_ptr<DeviceContext>> m_devices;
+                std::shared_ptr<Function> m_function;                     // as given to compile()
                 std::vector<std::shared_ptr<runtime::Executable>> m_subs; // per member device, or one
                 std::vector<std::unique_ptr<IssueThread>> m_threads;
                 bool m_split = false;
@@ -123,6 +127,9 @@ namespace ngraph
                                                              bool enable_performance_data = false) override;
                 bool is_supported(const Node& node) const override;
                 void remove_compiled_function(std::shared_ptr<runtime::Executable> exec) override;
+                /// rebuilds the saved Function and compiles it for the member devices (the saved constant image belongs to a
+                /// whole-batch executable and is not used: every member packs the weights for its share again)
+                std::shared_ptr<runtime::Executable> load(std::istream& input_stream) override;
                 size_t devices() const { return m_members.size(); }
 
             private:

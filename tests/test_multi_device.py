@@ -245,3 +245,25 @@ def test_option_string_errors(single):
     with pytest.raises(ng.NgraphError):  # a tensor of the single-device backend is foreign to the multi-device one
         fn, xs = batch_sum_network(4)
         multi.compile(fn).call([single.create_tensor(np.float32, (16,))], [single.create_tensor(np.float32, (4, 16))])
+
+
+@pytest.mark.gpu
+@needs_ngraph
+def test_save_and_load_across_the_two_forms(single, tmp_path):
+    """a multi-device executable saves the archive of the whole Function; the single-device form loads it as it is, the
+    multi-device form rebuilds the Function from it and splits it again"""
+    multi = ng.Backend("B200:0+0")
+    fn, xs = conv_network(6)
+    exp = single.compile(fn).run(*xs)
+    path = str(tmp_path / "net.b200")
+    multi.compile(fn).save(path)
+    for backend in (single, multi):
+        got = backend.load(path, fn).run(*xs)
+        for g, e in zip(got, exp):
+            np.testing.assert_array_equal(bits(g), bits(e))
+    # and the other way round: saved by the single-device form, loaded by the multi-device one
+    path2 = str(tmp_path / "net_single.b200")
+    single.compile(fn).save(path2)
+    got = multi.load(path2, fn).run(*xs)
+    for g, e in zip(got, exp):
+        np.testing.assert_array_equal(bits(g), bits(e))
