@@ -211,23 +211,30 @@ ShardedExecutable::ShardedExecutable(const std::vector<std::shared_ptr<B200Backe
         std::shared_ptr<Function> lowered = clone_function(*func);
         run_graph_passes(lowered);
         m_batch = batch_of(*lowered);
-        if (m_batch < D)
-            m_why = "fewer samples than devices";
+        if (m_batch < 2)
+            m_why = "a batch of fewer than two samples";
         else
         {
-            const size_t small = m_batch / D, last = small + m_batch % D; // the remainder goes to the last device
-            BatchSplit a, b;
-            if (split_batch(*lowered, small, a, m_why) && (last == small || split_batch(*lowered, last, b, m_why)))
+            // balanced shares: the first (batch % D) members take one sample more; with fewer samples than members the last
+            // members take none and stay idle
+            const size_t lo = m_batch / D, extra = m_batch % D;
+            BatchSplit more, fewer;
+            const bool ok = (extra == 0 || split_batch(*lowered, lo + 1, more, m_why)) && (lo == 0 || split_batch(*lowered, lo, fewer, m_why));
+            if (ok)
             {
                 m_split = true;
-                m_parameter_split = a.parameter_split;
-                m_result_split = a.result_split;
-                for (size_t d = 0; d <= D; ++d)
-                    m_begin.push_back(d == D ? m_batch : d * small);
+                m_parameter_split = extra ? more.parameter_split : fewer.parameter_split;
+                m_result_split = extra ? more.result_split : fewer.result_split;
+                m_begin.push_back(0);
                 for (size_t d = 0; d < D; ++d)
-                    m_subs.push_back(m_members[d]->compile((d == D - 1 && last != small) ? b.function : a.function, enable_performance_data));
+                    m_begin.push_back(m_begin.back() + lo + (d < extra ? 1 : 0));
                 for (size_t d = 0; d < D; ++d)
-                    m_threads.emplace_back(new IssueThread());
+                {
+                    const size_t rows = m_begin[d + 1] - m_begin[d];
+                    m_subs.push_back(rows == 0 ? nullptr
+                                               : m_members[d]->compile(rows == lo + 1 && extra ? more.function : fewer.function, enable_performance_data));
+                    m_threads.emplace_back(rows == 0 ? nullptr : new IssueThread());
+                }
             }
         }
     }
@@ -322,6 +329,8 @@ bool ShardedExecutable::call(const std::vector<std::shared_ptr<runtime::Tensor>>
         t.prefer_rows(rows); // from now on write() sends each device its rows only
         for (size_t d = 0; d < D; ++d)
         {
+            if (!m_subs[d])
+                continue;
             Shape s = t.get_shape();
             s[0] = rows[d + 1] - rows[d];
             in_d[d].push_back(view(d, t, s, rows[d]));
@@ -335,6 +344,8 @@ bool ShardedExecutable::call(const std::vector<std::shared_ptr<runtime::Tensor>>
         const std::vector<size_t> rows = tensor_rows(t);
         for (size_t d = 0; d < D; ++d)
         {
+            if (!m_subs[d])
+                continue;
             Shape s = t.get_shape();
             s[0] = rows[d + 1] - rows[d];
             out_d[d].push_back(view(d, t, s, rows[d]));
@@ -343,6 +354,8 @@ bool ShardedExecutable::call(const std::vector<std::shared_ptr<runtime::Tensor>>
     // all devices at once: each member's launches are issued by its own thread (a call only enqueues)
     for (size_t d = 0; d < D; ++d)
     {
+        if (!m_subs[d])
+            continue; // fewer samples than members: this one has no share
         m_threads[d]->post([this, d, &in_d, &out_d, &ins, &outs] {
             m_subs[d]->call(out_d[d], in_d[d]);
             // copies of the whole tensors (write / read) order themselves after this call on this device
@@ -357,7 +370,8 @@ bool ShardedExecutable::call(const std::vector<std::shared_ptr<runtime::Tensor>>
     {
         try
         {
-            m_threads[d]->wait();
+            if (m_threads[d])
+                m_threads[d]->wait();
         }
         catch (...)
         {
@@ -374,7 +388,7 @@ bool ShardedExecutable::call(const std::vector<std::shared_ptr<runtime::Tensor>>
 
 std::vector<runtime::PerformanceCounter> ShardedExecutable::get_performance_data() const
 {
-    return m_subs[0]->get_performance_data(); // the first device's view (every device runs the same steps)
+    return m_subs[0]->get_performance_data(); // the first member's view (every member with a share runs the same steps)
 }
 
 void ShardedExecutable::save(std::ostream& out)

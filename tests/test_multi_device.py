@@ -129,7 +129,7 @@ def test_dynamic_whole_tensor_scales_keep_the_encoder_on_one_device():
 # ---------------------------------------------------------------- GPU
 def member_lists():
     import torch
-    names = ["B200:0+0"]
+    names = ["B200:0+0", "B200:0+0+0+0+0+0"]  # the second: more members than samples, the last ones stay idle
     if torch.cuda.is_available() and torch.cuda.device_count() >= 2:
         names.append("B200:all")
     return names
@@ -146,7 +146,7 @@ def single():
 
 @pytest.mark.gpu
 @needs_ngraph
-@pytest.mark.parametrize("name", ["B200:0+0", "B200:all"])
+@pytest.mark.parametrize("name", ["B200:0+0", "B200:0+0+0+0+0+0", "B200:all"])
 @pytest.mark.parametrize("batch", [4, 5])
 def test_split_execution_matches_one_device(single, name, batch):
     from ngraph_b200 import lib
