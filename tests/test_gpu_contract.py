@@ -174,6 +174,39 @@ def test_qgemm_vs_oracle(ops, mnk, a_signed):
         np.testing.assert_array_equal(got, exp, err_msg="core %s %s" % (mnk, out_dt))
 
 
+@pytest.mark.parametrize("k,a_signed", [(64, False), (128, False), (192, False), (128, True), (256, True)])
+def test_short_reductions_with_small_and_large_biases(ops, k, a_signed):
+    """Extreme operands (every product at its largest magnitude, both signs) with biases that bring accumulator + bias to the
+    edge of +-2^22, just beyond it and far beyond (up to +-2^30), side by side in one launch, with and without a residual:
+    the int32 sum, its conversion to float and the saturation must hold over the whole int32 range, not only for the
+    magnitudes random data produces."""
+    rng = np.random.default_rng(k + a_signed)
+    m, n = 384, 512
+    a = (rng.integers(-128, 128, size=(m, k)).astype(np.int8) if a_signed else rng.integers(0, 256, size=(m, k)).astype(np.uint8))
+    w = rng.integers(-128, 128, size=(n, k)).astype(np.int8)
+    a[0], a[1] = (-128 if a_signed else 255), (127 if a_signed else 255)   # rows of extreme activations
+    w[0::64], w[1::64] = -128, 127                                            # columns of extreme weights in every 64-column block
+    bound = k * (128 if a_signed else 255) * 128
+    room = (1 << 22) - 1 - bound
+    bias = rng.integers(-1000, 1001, size=n).astype(np.int64)
+    if room > 0:
+        bias[0:64] = rng.integers(-room, room + 1, size=64)        # everything the guarantee admits
+        bias[0], bias[1] = -room, room                             # ... up to the very edge, on the extreme columns
+        bias[64:128] = rng.integers(-room, room + 1, size=64)
+        bias[70] = room + 1                                        # one bias just beyond: this block converts the usual way
+    bias[128:192] = rng.integers(-(1 << 30), 1 << 30, size=64)     # far beyond
+    bias = bias.astype(np.int32)
+    scale = (np.exp(rng.uniform(np.log(0.5), np.log(2.0), size=n)) * 3e-5).astype(np.float32)
+    s = rng.integers(0, 256, size=(m, n)).astype(np.uint8)
+    for out_dt, relu in ((np.uint8, True), (np.int8, False), (np.int8, True)):
+        for sum_in in (None, s):
+            kw = {} if sum_in is None else {"sum_in": sum_in, "sum_scale": np.float32(0.41)}
+            exp = ref.qgemm_fused(a, w, bias, scale, out_dt, relu=relu, **kw)
+            dkw = {} if sum_in is None else {"sum_in": dev(sum_in), "sum_scale": dev(np.array([0.41], np.float32))}
+            got = ops.qgemm(dev(a), dev(w), dev(scale), TDT[np.dtype(out_dt)], bias=dev(bias), relu=relu, **dkw).cpu().numpy()
+            np.testing.assert_array_equal(got, exp, err_msg="k=%d %s relu=%d sum=%s" % (k, out_dt, relu, sum_in is not None))
+
+
 def test_qgemm_sum_input(ops):
     rng = np.random.default_rng(5)
     m, n, k = 2000, 96, 256  # enough outputs that a product fused with the residual addition (one rounding) would show
