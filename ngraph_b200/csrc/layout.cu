@@ -177,23 +177,34 @@ namespace b200
                     const bool ok = h >= 0 && h < H && w >= 0 && w < W;
                     v[r][sx] = ok ? in[(size_t(n) * H + h) * W * C16 + size_t(w) * C16 + c] : make_uint4(0, 0, 0, 0);
                 }
-            uint4 col[5];
+            // Byte-wise maxima through the three-input 16-bit-lane maximum the hardware has (__vimax3_u16x2), since the byte-lane
+            // SIMD maximum is emulated: the even and the odd bytes of a word are spread into two words of 16-bit lanes (one byte
+            // permute each), three rows give a column's maximum in one instruction per word half, three columns an output's, and
+            // a last permute interleaves the halves again.
+            const uint32_t(*vw)[5][4] = reinterpret_cast<const uint32_t(*)[5][4]>(v);
+            uint32_t ce[5][4], co[5][4]; // per column and word: maxima of the even / odd bytes over the three rows
 #pragma unroll
             for (int sx = 0; sx < 5; ++sx)
-            {
-                col[sx].x = __vmaxu4(__vmaxu4(v[0][sx].x, v[1][sx].x), v[2][sx].x);
-                col[sx].y = __vmaxu4(__vmaxu4(v[0][sx].y, v[1][sx].y), v[2][sx].y);
-                col[sx].z = __vmaxu4(__vmaxu4(v[0][sx].z, v[1][sx].z), v[2][sx].z);
-                col[sx].w = __vmaxu4(__vmaxu4(v[0][sx].w, v[1][sx].w), v[2][sx].w);
-            }
-            auto max3 = [](const uint4& a, const uint4& b, const uint4& d) {
-                return make_uint4(__vmaxu4(__vmaxu4(a.x, b.x), d.x), __vmaxu4(__vmaxu4(a.y, b.y), d.y), __vmaxu4(__vmaxu4(a.z, b.z), d.z),
-                                  __vmaxu4(__vmaxu4(a.w, b.w), d.w));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                {
+                    ce[sx][k] = __vimax3_u16x2(__byte_perm(vw[0][sx][k], 0, 0x4240), __byte_perm(vw[1][sx][k], 0, 0x4240),
+                                               __byte_perm(vw[2][sx][k], 0, 0x4240));
+                    co[sx][k] = __vimax3_u16x2(__byte_perm(vw[0][sx][k], 0, 0x4341), __byte_perm(vw[1][sx][k], 0, 0x4341),
+                                               __byte_perm(vw[2][sx][k], 0, 0x4341));
+                }
+            auto max3 = [&](int s0) {
+                uint32_t r[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    r[k] = __byte_perm(__vimax3_u16x2(ce[s0][k], ce[s0 + 1][k], ce[s0 + 2][k]),
+                                       __vimax3_u16x2(co[s0][k], co[s0 + 1][k], co[s0 + 2][k]), 0x6240);
+                return make_uint4(r[0], r[1], r[2], r[3]);
             };
             const size_t o = ((size_t(n) * P + p) * Q + 2 * size_t(q2)) * C16 + c;
-            out[o] = max3(col[0], col[1], col[2]);
+            out[o] = max3(0);
             if (2 * q2 + 1 < uint32_t(Q))
-                out[o + C16] = max3(col[2], col[3], col[4]);
+                out[o + C16] = max3(2);
         }
     }
 
