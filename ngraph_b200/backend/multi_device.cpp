@@ -259,6 +259,8 @@ std::shared_ptr<runtime::Tensor> ShardedExecutable::view(size_t d, const Sharded
     auto it = m_views.find(key);
     if (it != m_views.end())
         return it->second;
+    if (m_views.size() >= 4096)
+        m_views.clear(); // views of tensors long gone; the ones a call is using are held by that call
     auto v = std::make_shared<B200Tensor>(m_devices[d], t.get_element_type(), shard_shape, p);
     m_views.emplace(key, v);
     return v;
